@@ -1,0 +1,474 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands
+// staged by TMA into 128-byte-swizzled shared memory), persistent and warp-specialised:
+//   warp 0      TMA producer (one lane)
+//   warp 1      MMA issuer   (one lane)
+//   warps 2..5  epilogue: TMEM -> registers -> fused epilogue -> global
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main
+// loop of tile i+1.  Both operands may be K-major or MN-major, which covers the three GEMMs
+// of a linear layer whose weight is stored [in, out] row-major (the layout of math::matmul in
+// the reference, plugins/model-transformer/src/lib.rs:50-74):
+//   forward  Y[M,N]  = X[M,K]   . W[K,N]      A K-major,  B MN-major
+//   dgrad    dX[M,K] = dY[M,N]  . W[K,N]^T    A K-major,  B K-major
+//   wgrad    dW[K,N] = X[M,K]^T . dY[M,N]     A MN-major, B MN-major (split along tokens,
+//                                             fp32 atomic accumulation)
+// Fused epilogues: alpha scale, +bias[N], GELU(tanh) with the pre-activation kept, dGELU,
+// +residual, bf16 / fp32 / fp32-atomic-add output.
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace cb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_SWIGLU_BWD = 3 };
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
+
+struct GemmArgs {
+  int M, N, K;
+  void* D;
+  int ldd;
+  const __nv_bfloat16* bias;    // [N] or null
+  const __nv_bfloat16* resid;   // [M, N] (ldr) or null
+  int ldr;
+  const __nv_bfloat16* aux_in;  // [M, N] (ldaux): pre-activation for EPI_DGELU
+  __nv_bfloat16* aux_out;       // [M, N] (ldaux): pre-activation written by EPI_GELU
+  int ldaux;
+  int epi;
+  int out_mode;
+  float alpha;
+  int ksplit;
+  int* status;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + STAGES * Cfg::STAGE_BYTES);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  auto full_bar = [&](int s) { return smem_u32(bars + s); };
+  auto empty_bar = [&](int s) { return smem_u32(bars + STAGES + s); };
+  auto tfull_bar = [&](int a) { return smem_u32(bars + 2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return smem_u32(bars + 2 * STAGES + 2 + a); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int kb_per = (kblocks + p.ksplit - 1) / p.ksplit;
+  const int total = tiles_m * tiles_n * p.ksplit;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed = 0;  // number of stage fills issued
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const int split = w % p.ksplit;
+        const int tile = w / p.ksplit;
+        const int m0 = (tile / tiles_n) * GEMM_BM;
+        const int n0 = (tile % tiles_n) * BN;
+        const int kb0 = split * kb_per;
+        const int kb1 = min(kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            record_status(p.status, ST_WAIT_TIMEOUT, 100);
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint32_t fb = full_bar(stage);
+          mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d(sA, &tmA, fb, kb * GEMM_BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d(sA + c * 8192, &tmA, fb, m0 + c * 64, kb * GEMM_BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sB, &tmB, fb, kb * GEMM_BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * 8192, &tmB, fb, n0 + c * 64, kb * GEMM_BK);
+          }
+          ++armed;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Let copies that were already issued land before the CTA's shared memory goes away.
+        const uint32_t n_wait = armed < (uint32_t)STAGES ? armed : (uint32_t)STAGES;
+        for (uint32_t i = 0; i < n_wait; ++i) {
+          const uint32_t idx = armed - 1 - i;  // fill index
+          const int s = idx % STAGES;
+          const uint32_t par = (idx / STAGES) & 1u;
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(full_bar(s), par)) {
+            if (globaltimer_ns() - t0 > 200000000ull) break;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+        const int split = w % p.ksplit;
+        const int kb0 = split * kb_per;
+        const int kb1 = min(kblocks, kb0 + kb_per);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          record_status(p.status, ST_WAIT_TIMEOUT, 200);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            record_status(p.status, ST_WAIT_TIMEOUT, 201);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t ad = A_MN ? umma_desc_sw128(sA + k * 2048, 8192, 1024)
+                                     : umma_desc_sw128(sA + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? umma_desc_sw128(sB + k * 2048, 8192, 1024)
+                                     : umma_desc_sw128(sB + k * 32, 16, 1024);
+            umma_bf16_ss(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+      const int tile = w / p.ksplit;
+      const int m0 = (tile / tiles_n) * GEMM_BM;
+      const int n0 = (tile % tiles_n) * BN;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {  // warp-uniform: tcgen05.ld needs the whole warp
+        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 300);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const int ncols = min(32, p.N - col0);  // multiple of 8 (N % 8 == 0)
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g * 8 < ncols) {
+              const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
+              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16x2(bw[j]);
+                v[g * 8 + 2 * j] += f.x;
+                v[g * 8 + 2 * j + 1] += f.y;
+              }
+            }
+          }
+        }
+        if (p.epi == EPI_GELU) {
+          if (p.aux_out != nullptr) {
+            __nv_bfloat16* ap = p.aux_out + static_cast<size_t>(row) * p.ldaux + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (g * 8 < ncols) {
+                uint4 o;
+                o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+                o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+                o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+                o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+                *reinterpret_cast<uint4*>(ap + g * 8) = o;
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        } else if (p.epi == EPI_DGELU) {
+          const __nv_bfloat16* ap = p.aux_in + static_cast<size_t>(row) * p.ldaux + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g * 8 < ncols) {
+              const uint4 a = *reinterpret_cast<const uint4*>(ap + g * 8);
+              const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16x2(aw[j]);
+                v[g * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+                v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+              }
+            }
+          }
+        }
+        if (p.resid != nullptr) {
+          const __nv_bfloat16* rp = p.resid + static_cast<size_t>(row) * p.ldr + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g * 8 < ncols) {
+              const uint4 a = *reinterpret_cast<const uint4*>(rp + g * 8);
+              const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16x2(aw[j]);
+                v[g * 8 + 2 * j] += f.x;
+                v[g * 8 + 2 * j + 1] += f.y;
+              }
+            }
+          }
+        }
+        if (p.out_mode == OUT_BF16) {
+          __nv_bfloat16* dp =
+              reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g * 8 < ncols) {
+              uint4 o;
+              o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+              o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+              o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+              o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+              *reinterpret_cast<uint4*>(dp + g * 8) = o;
+            }
+          }
+        } else if (p.out_mode == OUT_F32) {
+          float* dp = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (g * 4 < ncols)
+              *reinterpret_cast<float4*>(dp + g * 4) =
+                  make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+          }
+        } else {
+          float* dp = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (g * 4 < ncols) {
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                           ::"l"(dp + g * 4), "f"(v[g * 4]), "f"(v[g * 4 + 1]),
+                             "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                           : "memory");
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch ld
+// elements, 128-byte swizzle.  Returns 0 on success.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t ld, uint32_t box_inner, uint32_t box_outer) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld * 2) % 16 != 0) return -2;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                       int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  const int tiles = ((args.M + GEMM_BM - 1) / GEMM_BM) * ((args.N + BN - 1) / BN) * args.ksplit;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace cb
+
+// D[M,N] = epilogue(alpha * A . B^T)
+//   A: logical [M,K]; a_mn == 0: memory [M,K] row-major (pitch lda); a_mn == 1: memory [K,M].
+//   B: logical [N,K]; b_mn == 0: memory [N,K] row-major (pitch ldb); b_mn == 1: memory [K,N].
+// Requirements: K, N (and M when a_mn) multiples of 8; 16-byte aligned pointers and pitches.
+extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
+                            int ldb, int ldd, int a_mn, int b_mn, const void* bias,
+                            const void* resid, int ldr, const void* aux_in, void* aux_out,
+                            int ldaux, int epi, int out_mode, float alpha, int ksplit, int bn,
+                            int* status, int max_ctas, void* stream) {
+  using namespace cb;
+  if (M <= 0 || N <= 0 || K <= 0) return -20;
+  if ((N % 8) != 0 || (K % 8) != 0 || (ldd % 4) != 0) return -21;
+  if (out_mode == OUT_BF16 && (ldd % 8) != 0) return -21;
+  if (bn != 128 && bn != 256) return -22;
+  const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
+  if (ksplit < 1) ksplit = 1;
+  if (ksplit > kblocks) ksplit = kblocks;
+  // every split must own at least one k-block
+  {
+    const int per = (kblocks + ksplit - 1) / ksplit;
+    ksplit = (kblocks + per - 1) / per;
+  }
+  if (ksplit > 1 && out_mode != OUT_F32_ATOMIC) return -23;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn == 0)
+    rc = make_tmap_bf16_2d(&ta, A, K, M, lda, 64, GEMM_BM);
+  else
+    rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, 64);
+  if (rc != 0) return rc - 30;
+  if (b_mn == 0)
+    rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, bn);
+  else
+    rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, 64);
+  if (rc != 0) return rc - 40;
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K;
+  g.D = D; g.ldd = ldd;
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
+  g.resid = static_cast<const __nv_bfloat16*>(resid);
+  g.ldr = ldr;
+  g.aux_in = static_cast<const __nv_bfloat16*>(aux_in);
+  g.aux_out = static_cast<__nv_bfloat16*>(aux_out);
+  g.ldaux = ldaux;
+  g.epi = epi; g.out_mode = out_mode; g.alpha = alpha; g.ksplit = ksplit; g.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define CB_DISPATCH(BN_)                                                            \
+  do {                                                                              \
+    if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(ta, tb, g, max_ctas, st); \
+    if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(ta, tb, g, max_ctas, st);   \
+    if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(ta, tb, g, max_ctas, st);   \
+    return launch_gemm<BN_, true, true>(ta, tb, g, max_ctas, st);                       \
+  } while (0)
+  if (bn == 256) CB_DISPATCH(256);
+  CB_DISPATCH(128);
+#undef CB_DISPATCH
+}

@@ -1,0 +1,139 @@
+"""bf16 GEMM with fused epilogues on the tcgen05 tensor cores (``csrc/gemm.cu``).
+
+``gemm`` is the general entry; ``linear_fwd`` / ``linear_dgrad`` / ``linear_wgrad`` are the
+three products of a linear layer whose weight is stored ``[in, out]`` row-major, the layout
+``math::matmul`` uses in the reference (plugins/model-transformer/src/lib.rs:50-74).
+
+CPU tensors take a float32 PyTorch restatement of the same math (the oracle the GPU tests
+compare against); CUDA tensors always run the hand-written kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+EPI = {"none": 0, "gelu": 1, "dgelu": 2}
+_OUT_BF16, _OUT_F32, _OUT_F32_ATOMIC = 0, 1, 2
+
+
+def _gelu_ref(x: torch.Tensor) -> torch.Tensor:
+    return 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * x * (1.0 + 0.044715 * x * x)))
+
+
+def _gelu_grad_ref(x: torch.Tensor) -> torch.Tensor:
+    x2 = x * x
+    u = 0.7978845608028654 * x * (1.0 + 0.044715 * x2)
+    t = torch.tanh(u)
+    du = 0.7978845608028654 * (1.0 + 3.0 * 0.044715 * x2)
+    return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * du
+
+
+def _pick_bn(M: int, N: int, ksplit: int, sms: int = 148) -> int:
+    """Choose the N tile: 256 unless that leaves the last wave badly filled."""
+    if N <= 128:
+        return 128
+    tm = (M + 127) // 128
+
+    def waste(bn: int) -> float:
+        tiles = tm * ((N + bn - 1) // bn) * ksplit
+        waves = math.ceil(tiles / sms)
+        return waves * sms / tiles
+
+    # a 256-wide tile is ~10 % more efficient per tile; prefer it unless quantisation costs more
+    return 256 if waste(256) <= 1.10 * waste(128) else 128
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+         resid: Optional[torch.Tensor] = None, epi: str = "none",
+         aux_in: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, alpha: float = 1.0,
+         ksplit: int = 1, bn: Optional[int] = None, max_ctas: int = 0) -> torch.Tensor:
+    """``out[M,N] = epilogue(alpha * A @ B^T)`` with A logical ``[M,K]`` and B logical ``[N,K]``.
+
+    ``a_mn`` / ``b_mn`` say that the tensor passed is the transpose in memory (``[K,M]`` /
+    ``[K,N]`` row-major).  ``accumulate=True`` adds into an fp32 ``out`` with atomic adds,
+    which is what allows ``ksplit > 1``.
+    """
+    assert a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm: contraction mismatch {K} vs {Kb}")
+    if accumulate:
+        out_dtype = torch.float32
+        if out is None:
+            raise ValueError("gemm: accumulate=True needs an fp32 `out`")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if not a.is_cuda:
+        A = (a.t() if a_mn else a).float()
+        B = (b.t() if b_mn else b).float()
+        v = alpha * (A @ B.t())
+        if bias is not None:
+            v = v + bias.float()
+        if epi == "gelu":
+            if aux_out is not None:
+                aux_out.copy_(v.to(aux_out.dtype))
+            v = _gelu_ref(v)
+        elif epi == "dgelu":
+            v = v * _gelu_grad_ref(aux_in.float())
+        if resid is not None:
+            v = v + resid.float()
+        if accumulate:
+            out.add_(v.to(out.dtype))
+        else:
+            out.copy_(v.to(out.dtype))
+        return out
+
+    for t in (a, b):
+        if t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise ValueError("gemm: operands must be bf16 with unit inner stride")
+    if out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("gemm: bad output tensor")
+    out_mode = _OUT_F32_ATOMIC if accumulate else (
+        _OUT_F32 if out.dtype == torch.float32 else _OUT_BF16)
+    if bn is None:
+        bn = _pick_bn(M, N, ksplit)
+    aux = aux_in if aux_in is not None else aux_out
+    st = _lib.status_buffer(a.device)
+    rc = _lib.lib().cb_gemm_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
+        out.stride(0), int(a_mn), int(b_mn), _lib.ptr(bias), _lib.ptr(resid),
+        resid.stride(0) if resid is not None else 0, _lib.ptr(aux_in), _lib.ptr(aux_out),
+        aux.stride(0) if aux is not None else 0, EPI[epi], out_mode, ctypes.c_float(alpha),
+        ksplit, bn, _lib.ptr(st), max_ctas, _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_gemm_bf16")
+    return out
+
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+               resid: Optional[torch.Tensor] = None, epi: str = "none",
+               aux_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               out_dtype: torch.dtype = torch.bfloat16, max_ctas: int = 0) -> torch.Tensor:
+    """``y[T,out] = epilogue(x[T,in] @ w[in,out] + bias) (+ resid)``."""
+    return gemm(x, w, b_mn=True, bias=bias, resid=resid, epi=epi, aux_out=aux_out, out=out,
+                out_dtype=out_dtype, max_ctas=max_ctas)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, *, epi: str = "none",
+                 aux_in: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
+    """``dx[T,in] = dy[T,out] @ w[in,out]^T`` (optionally times GELU'(aux_in), plus resid)."""
+    return gemm(dy, w, epi=epi, aux_in=aux_in, resid=resid, out=out, max_ctas=max_ctas)
+
+
+def linear_wgrad(x: torch.Tensor, dy: torch.Tensor, grad_w: torch.Tensor, *,
+                 ksplit: Optional[int] = None, max_ctas: int = 0) -> torch.Tensor:
+    """``grad_w[in,out] += x[T,in]^T @ dy[T,out]`` accumulated in fp32."""
+    T = x.shape[0]
+    if ksplit is None:
+        tiles = ((x.shape[1] + 127) // 128) * ((dy.shape[1] + 255) // 256)
+        ksplit = max(1, min((T + 63) // 64 // 8, 148 * 2 // max(1, tiles)))
+    return gemm(x, dy, a_mn=True, b_mn=True, out=grad_w, accumulate=True, ksplit=ksplit,
+                max_ctas=max_ctas)
