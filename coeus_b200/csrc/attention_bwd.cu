@@ -1,0 +1,526 @@
+// Flash-style attention backward on tcgen05.  One CTA owns one (batch, head, 128-row K/V tile)
+// and streams the query tiles that attend to it; all five products run on the tensor cores
+// with accumulators in tensor memory, in the transposed orientation (K/V rows on the TMEM lanes)
+// so that P^T and dS^T are produced row-per-thread and feed the next MMAs from shared memory:
+//   S^T  = K_j . Q_i^T          dP^T = V_j . dO_i^T
+//   P^T  = exp2(S^T * c - LSE_i)       dS^T = P^T o (dP^T - delta_i)
+//   dV_j += P^T . dO_i          dK_j += dS^T . Q_i
+//   dQ_i  = dS . K_j  (dh = 64; for dh = 128 the transposed dQ_i^T = K_j^T . dS^T), drained from
+//           TMEM with fp32 atomic adds into an accumulation buffer shared by all K/V tiles.
+// delta_i = rowsum(dO_i o O_i) comes from a small pre-kernel; a post-kernel scales and casts dQ.
+//   warp 0      TMA producer (K_j, V_j once; Q_i, dO_i through a 2-stage ring)
+//   warp 1      MMA issuer
+//   warps 2..5  softmax / dS (one thread per K/V row)
+//   warps 6..9  dQ drain (TMEM -> red.global.add) and, with warps 2..5, the dK/dV epilogue
+#include <algorithm>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace cb {
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t ld, uint32_t box_inner, uint32_t box_outer);
+int sm_count();
+
+constexpr int ATB_BKV = 128;
+constexpr int ATB_THREADS = 320;
+
+struct AttnBwdArgs {
+  int B, S, nh;
+  const float* lse;     // [B, nh, S]
+  const float* delta;   // [B, nh, S]
+  float* dq_acc;        // fp32 [B*S, nh*dh], zero-initialised
+  __nv_bfloat16* dk;    // [B*S, ...] pitch ldd, already offset to the K slice
+  __nv_bfloat16* dv;
+  int ldd;
+  float scale;
+  float scale_log2;
+  int causal;
+  int* status;
+};
+
+template <int DH>
+struct AttnBwdCfg {
+  static constexpr int BQ = (DH == 64) ? 128 : 64;
+  static constexpr int KV_BYTES = ATB_BKV * DH * 2;     // K_j or V_j
+  static constexpr int Q_BYTES = BQ * DH * 2;           // Q_i or dO_i
+  static constexpr int PT_BYTES = ATB_BKV * BQ * 2;     // P^T or dS^T
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = KV_BYTES;
+  static constexpr int OFF_Q = 2 * KV_BYTES;                    // 2 stages of (Q_i | dO_i)
+  static constexpr int OFF_PT = OFF_Q + 2 * 2 * Q_BYTES;
+  static constexpr int OFF_DST = OFF_PT + PT_BYTES;
+  static constexpr int OFF_STAT = OFF_DST + PT_BYTES;           // [2 stages][2][BQ] floats
+  static constexpr int OFF_BAR = OFF_STAT + 2 * 2 * BQ * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int ST_COL = 0;
+  static constexpr int DPT_COL = BQ;
+  static constexpr int DV_COL = 2 * BQ;
+  static constexpr int DK_COL = 2 * BQ + DH;
+  static constexpr int DQ_COL = 2 * BQ + 2 * DH;
+  static constexpr int TMEM_COLS = 512;
+};
+
+// delta[b,h,s] = sum_d dO[s, h*dh + d] * O[s, h*dh + d]
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO,
+                                  const __nv_bfloat16* __restrict__ O, float* __restrict__ delta,
+                                  int B, int S, int nh, int dh, int lddo, int ldo) {
+  const int tpg = dh / 8;  // threads per (token, head)
+  const size_t total = static_cast<size_t>(B) * S * nh * tpg;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+       i < ((total + 31) / 32) * 32; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float s = 0.f;
+    const bool live = i < total;
+    size_t tok = 0;
+    int h = 0;
+    if (live) {
+      const int part = static_cast<int>(i % tpg);
+      h = static_cast<int>((i / tpg) % nh);
+      tok = i / (static_cast<size_t>(tpg) * nh);
+      float a[8], b[8];
+      load8(dO + tok * lddo + h * dh + part * 8, a);
+      load8(O + tok * ldo + h * dh + part * 8, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += a[e] * b[e];
+    }
+    for (int o = tpg / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live && (i % tpg) == 0) {
+      const size_t bb = tok / S, ss = tok % S;
+      delta[(bb * nh + h) * S + ss] = s;
+    }
+  }
+}
+
+// dq[t, c] = bf16(dq_acc[t, c] * scale)
+__global__ void attn_dq_finalize_kernel(const float* __restrict__ acc,
+                                        __nv_bfloat16* __restrict__ dq, size_t T, int H, int ldd,
+                                        float scale) {
+  const int nv = H / 8;
+  const size_t total = T * nv;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / nv;
+    const int vec = static_cast<int>(i % nv);
+    const float4 a = *reinterpret_cast<const float4*>(acc + t * H + vec * 8);
+    const float4 b = *reinterpret_cast<const float4*>(acc + t * H + vec * 8 + 4);
+    const float v[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale,
+                        b.x * scale, b.y * scale, b.z * scale, b.w * scale};
+    store8(dq + t * ldd + vec * 8, v);
+  }
+}
+
+template <int DH>
+__global__ void __launch_bounds__(ATB_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const AttnBwdArgs p) {
+  using Cfg = AttnBwdCfg<DH>;
+  constexpr int BQ = Cfg::BQ;
+  constexpr int BKV = ATB_BKV;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5 s_full | 6 pds_full | 7 pds_empty | 8 dq_full |
+  // 9 dq_empty | 10 done | 11 stat_full
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 12);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+  float* s_stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((sbase & 1023u) != 0u) {
+    if (threadIdx.x == 0) record_status(p.status, ST_BAD_ARG, 1000);
+    return;
+  }
+  const int n_kv_tiles = (p.S + BKV - 1) / BKV;
+  const int bh = blockIdx.x % (p.B * p.nh);
+  const int j = blockIdx.x / (p.B * p.nh);  // early K/V tiles see the most queries: first
+  const int b = bh / p.nh, h = bh % p.nh;
+  const int kv0 = j * BKV;
+  const int n_q_tiles = (p.S + BQ - 1) / BQ;
+  const int i_start = p.causal ? kv0 / BQ : 0;
+  const int n_it = n_q_tiles - i_start;
+  (void)n_kv_tiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(0), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(1 + s), 1);
+      mbar_init(bar(3 + s), 1);
+    }
+    mbar_init(bar(5), 1);
+    mbar_init(bar(6), 128);
+    mbar_init(bar(7), 1);
+    mbar_init(bar(8), 1);
+    mbar_init(bar(9), 128);
+    mbar_init(bar(10), 1);
+    mbar_init(bar(11), 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t sK = sbase + Cfg::OFF_K, sV = sbase + Cfg::OFF_V;
+  const uint32_t sPT = sbase + Cfg::OFF_PT, sDST = sbase + Cfg::OFF_DST;
+  auto sQ = [&](int st) { return sbase + Cfg::OFF_Q + st * 2 * Cfg::Q_BYTES; };
+  auto sDO = [&](int st) { return sQ(st) + Cfg::Q_BYTES; };
+  const int row0 = b * p.S;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar(0), 2 * Cfg::KV_BYTES);
+#pragma unroll
+      for (int c = 0; c < DH / 64; ++c) {
+        tma_load_2d(sK + c * (BKV * 128), &tmK, bar(0), h * DH + c * 64, row0 + kv0);
+        tma_load_2d(sV + c * (BKV * 128), &tmV, bar(0), h * DH + c * 64, row0 + kv0);
+      }
+      int issued = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1u;
+        if (!mbar_wait(bar(3 + st), ph ^ 1u, abort_flag)) {
+          record_status(p.status, ST_WAIT_TIMEOUT, 1010);
+          break;
+        }
+        const int qrow = row0 + (i_start + it) * BQ;
+        mbar_arrive_expect_tx(bar(1 + st), 2 * Cfg::Q_BYTES);
+#pragma unroll
+        for (int c = 0; c < DH / 64; ++c) {
+          tma_load_2d(sQ(st) + c * (BQ * 128), &tmQ, bar(1 + st), h * DH + c * 64, qrow);
+          tma_load_2d(sDO(st) + c * (BQ * 128), &tmdO, bar(1 + st), h * DH + c * 64, qrow);
+        }
+        ++issued;
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        for (int i = max(0, issued - 2); i < issued; ++i) {
+          while (!mbar_try_wait(bar(1 + (i & 1)), (i >> 1) & 1u)) {
+            if (globaltimer_ns() - t0 > 200000000ull) break;
+          }
+        }
+        while (!mbar_try_wait(bar(0), 0)) {
+          if (globaltimer_ns() - t0 > 200000000ull) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = umma_idesc_bf16(BKV, BQ, 0, 0);   // S^T, dP^T
+      constexpr uint32_t idesc_dv = umma_idesc_bf16(BKV, DH, 0, 1);   // dV, dK
+      constexpr uint32_t idesc_dq =
+          (DH == 64) ? umma_idesc_bf16(BQ, DH, 1, 1) : umma_idesc_bf16(DH, BQ, 1, 1);
+      bool ok = mbar_wait(bar(0), 0, abort_flag);
+      if (!ok) record_status(p.status, ST_WAIT_TIMEOUT, 1020);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1u;
+        if (!mbar_wait(bar(1 + st), ph, abort_flag)) {
+          record_status(p.status, ST_WAIT_TIMEOUT, 1021);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sK + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sQ(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
+          umma_bf16_ss(tmem_base + Cfg::ST_COL, ad, bd, idesc_st, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sV + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sDO(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
+          umma_bf16_ss(tmem_base + Cfg::DPT_COL, ad, bd, idesc_st, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(5));
+        if (!mbar_wait(bar(6), it & 1u, abort_flag)) {
+          record_status(p.status, ST_WAIT_TIMEOUT, 1022);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        // dV += P^T . dO_i     dK += dS^T . Q_i      (contraction over the BQ query rows)
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sPT + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sDO(st) + kk * 2048, BQ * 128, 1024);
+          umma_bf16_ss(tmem_base + Cfg::DV_COL, ad, bd, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sDST + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sQ(st) + kk * 2048, BQ * 128, 1024);
+          umma_bf16_ss(tmem_base + Cfg::DK_COL, ad, bd, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        if (it > 0) {
+          if (!mbar_wait(bar(9), (it - 1) & 1u, abort_flag)) {
+            record_status(p.status, ST_WAIT_TIMEOUT, 1023);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
+        // contraction over the 128 K/V rows
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          if constexpr (DH == 64) {
+            // dQ_i[q, d] = sum_kv dS^T[kv, q] K_j[kv, d]
+            const uint64_t ad = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
+            const uint64_t bd = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
+            umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
+          } else {
+            // dQ_i^T[d, q] = sum_kv K_j[kv, d] dS^T[kv, q]
+            const uint64_t ad = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
+            const uint64_t bd = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
+            umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(bar(8));       // dQ ready to drain
+        umma_commit(bar(3 + st));  // Q_i / dO_i stage free
+        umma_commit(bar(7));       // P^T / dS^T buffers free
+      }
+      if (ok) umma_commit(bar(10));
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- softmax / dS
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // K/V row within the tile
+    const int kv_idx = kv0 + r;
+    const int tid = threadIdx.x - 64;   // 0..127
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const size_t stat_base = (static_cast<size_t>(b) * p.nh + h) * p.S;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int q0 = (i_start + it) * BQ;
+      float* s_lse = s_stat + (it & 1) * 2 * BQ;
+      float* s_dl = s_lse + BQ;
+      if (tid < BQ) {
+        const int qi = q0 + tid;
+        s_lse[tid] = qi < p.S ? p.lse[stat_base + qi] * 1.4426950408889634f : INFINITY;
+        s_dl[tid] = qi < p.S ? p.delta[stat_base + qi] : 0.f;
+      }
+      mbar_arrive(bar(11));
+      bool got = mbar_wait(bar(11), it & 1u, abort_flag);
+      if (got) got = mbar_wait(bar(5), it & 1u, abort_flag);
+      if (got && it > 0) got = mbar_wait(bar(7), (it - 1) & 1u, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1030);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool diag = p.causal && (kv0 + BKV - 1 > q0);
+      const bool row_dead = kv_idx >= p.S;
+#pragma unroll 1
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(lane_addr + Cfg::ST_COL + c * 32, sv);
+        tmem_ld_32x32b_x32(lane_addr + Cfg::DPT_COL + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int qc = c * 32 + e;
+          float p0 = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - s_lse[qc]);
+          float p1 = fast_exp2(__uint_as_float(sv[e + 1]) * p.scale_log2 - s_lse[qc + 1]);
+          if (row_dead || (diag && kv_idx > q0 + qc)) p0 = 0.f;
+          if (row_dead || (diag && kv_idx > q0 + qc + 1)) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dv[e]) - s_dl[qc]);
+          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - s_dl[qc + 1]);
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+          dk[e >> 1] = pack_bf16x2(d0, d1);
+        }
+        const uint32_t off = ((c * 32) / 64) * (BKV * 128) + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t chunk = static_cast<uint32_t>(((c * 4) & 7) + g);
+          const uint32_t sw = (chunk ^ (r & 7)) << 4;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPT + off + sw),
+                       "r"(pk[4 * g]), "r"(pk[4 * g + 1]), "r"(pk[4 * g + 2]), "r"(pk[4 * g + 3])
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDST + off + sw),
+                       "r"(dk[4 * g]), "r"(dk[4 * g + 1]), "r"(dk[4 * g + 2]), "r"(dk[4 * g + 3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar(6));
+    }
+    // ---- epilogue: dV and dK of this K/V tile
+    if (ok) {
+      const bool got = mbar_wait(bar(10), 0, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1031);
+        ok = false;
+      }
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = kv_idx < p.S;
+      const size_t orow = (static_cast<size_t>(row0) + kv_idx) * p.ldd + static_cast<size_t>(h) * DH;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + orow;
+        const float mul = which == 0 ? 1.0f : p.scale;
+        const int col = which == 0 ? Cfg::DV_COL : Cfg::DK_COL;
+#pragma unroll 1
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + col + c * 32, o);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[8 * g + 0]) * mul, __uint_as_float(o[8 * g + 1]) * mul);
+              w.y = pack_bf16x2(__uint_as_float(o[8 * g + 2]) * mul, __uint_as_float(o[8 * g + 3]) * mul);
+              w.z = pack_bf16x2(__uint_as_float(o[8 * g + 4]) * mul, __uint_as_float(o[8 * g + 5]) * mul);
+              w.w = pack_bf16x2(__uint_as_float(o[8 * g + 6]) * mul, __uint_as_float(o[8 * g + 7]) * mul);
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- dQ drain
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int Hd = p.nh * DH;
+    for (int it = 0; it < n_it; ++it) {
+      const bool got = mbar_wait(bar(8), it & 1u, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1040);
+        break;
+      }
+      tc_fence_after();
+      const int q0 = (i_start + it) * BQ;
+      if constexpr (DH == 64) {
+        const int qi = q0 + r;
+        float* dst = p.dq_acc + (static_cast<size_t>(row0) + qi) * Hd + static_cast<size_t>(h) * DH;
+#pragma unroll 1
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + Cfg::DQ_COL + c * 32, o);
+          tmem_ld_wait();
+          if (qi < p.S) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                           ::"l"(dst + c * 32 + g * 4), "f"(__uint_as_float(o[4 * g])),
+                             "f"(__uint_as_float(o[4 * g + 1])), "f"(__uint_as_float(o[4 * g + 2])),
+                             "f"(__uint_as_float(o[4 * g + 3]))
+                           : "memory");
+          }
+        }
+      } else {
+        // lanes hold the head dimension, columns the BQ queries
+        float* dst = p.dq_acc + static_cast<size_t>(row0) * Hd + static_cast<size_t>(h) * DH + r;
+#pragma unroll 1
+        for (int c = 0; c < BQ / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + Cfg::DQ_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int qi = q0 + c * 32 + e;
+            if (qi < p.S) atomicAdd(dst + static_cast<size_t>(qi) * Hd, __uint_as_float(o[e]));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(9));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int DH>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const CUtensorMap& tdo, const AttnBwdArgs& a, cudaStream_t st) {
+  using Cfg = AttnBwdCfg<DH>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  const int n_kv_tiles = (a.S + ATB_BKV - 1) / ATB_BKV;
+  attn_bwd_kernel<DH><<<n_kv_tiles * a.B * a.nh, ATB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv,
+                                                                                    tdo, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace cb
+
+// dqkv: bf16 [B*S, 3*nh*dh] (pitch ldd) receiving dQ | dK | dV.  dq_acc: zeroed fp32
+// [B*S, nh*dh] scratch; delta: fp32 [B, nh, S] scratch.
+extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const void* v,
+                           const void* o, const float* lse, float* delta, float* dq_acc,
+                           void* dqkv, int B, int S, int nh, int dh, int lddo, int ldq, int ldk,
+                           int ldv, int ldo, int ldd, float scale, int causal, int* status,
+                           void* stream) {
+  using namespace cb;
+  if (dh != 64 && dh != 128) return -1;
+  if (B <= 0 || S <= 0 || nh <= 0 || (ldd % 8) != 0) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int H = nh * dh;
+  const uint64_t rows = static_cast<uint64_t>(B) * S;
+  {
+    const size_t work = rows * nh * (dh / 8);
+    const int blocks = static_cast<int>(std::min<size_t>((work + 255) / 256, sm_count() * 16));
+    attn_delta_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dO),
+                                              static_cast<const __nv_bfloat16*>(o), delta, B, S,
+                                              nh, dh, lddo, ldo);
+  }
+  const uint32_t bq = dh == 64 ? 128 : 64;
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_tmap_bf16_2d(&tq, q, H, rows, ldq, 64, bq) != 0) return -3;
+  if (make_tmap_bf16_2d(&tk, k, H, rows, ldk, 64, ATB_BKV) != 0) return -4;
+  if (make_tmap_bf16_2d(&tv, v, H, rows, ldv, 64, ATB_BKV) != 0) return -5;
+  if (make_tmap_bf16_2d(&tdo, dO, H, rows, lddo, 64, bq) != 0) return -6;
+  AttnBwdArgs a;
+  a.B = B; a.S = S; a.nh = nh;
+  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
+  a.dk = static_cast<__nv_bfloat16*>(dqkv) + H;
+  a.dv = static_cast<__nv_bfloat16*>(dqkv) + 2 * H;
+  a.ldd = ldd;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal;
+  a.status = status;
+  int rc = dh == 64 ? launch_attn_bwd<64>(tq, tk, tv, tdo, a, st)
+                    : launch_attn_bwd<128>(tq, tk, tv, tdo, a, st);
+  if (rc != 0) return rc;
+  {
+    const size_t work = rows * (H / 8);
+    const int blocks = static_cast<int>(std::min<size_t>((work + 255) / 256, sm_count() * 16));
+    attn_dq_finalize_kernel<<<blocks, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dqkv),
+                                                    rows, H, ldd, scale);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}

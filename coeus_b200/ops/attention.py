@@ -1,0 +1,88 @@
+"""Flash-style attention on tcgen05 (``csrc/attention_fwd.cu``, ``csrc/attention_bwd.cu``).
+
+Tensors are token-major: ``q``, ``k``, ``v`` are ``[B*S, nh*dh]`` views (they may be column
+slices of one fused ``[B*S, 3*nh*dh]`` projection output), ``o`` is ``[B*S, nh*dh]``.  The
+``S x S`` score matrix of the reference (plugins/model-transformer/src/lib.rs:237-277) is never
+materialised.  CPU tensors use a float32 PyTorch restatement.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+def _ref_fwd(q, k, v, B, S, nh, dh, scale, causal):
+    qf = q.float().reshape(B, S, nh, dh).transpose(1, 2)
+    kf = k.float().reshape(B, S, nh, dh).transpose(1, 2)
+    vf = v.float().reshape(B, S, nh, dh).transpose(1, 2)
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.softmax(s, -1)
+    o = (p @ vf).transpose(1, 2).reshape(B * S, nh * dh)
+    return o, lse, p, (qf, kf, vf)
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: int, nh: int,
+                  dh: int, *, causal: bool = True, scale: Optional[float] = None
+                  ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(o [B*S, nh*dh], lse [B, nh, S] fp32)``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    if not q.is_cuda:
+        o, lse, _, _ = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
+        return o.to(q.dtype), lse
+    for t in (q, k, v):
+        assert t.dtype == torch.bfloat16 and t.stride(1) == 1
+    o = torch.empty((B * S, nh * dh), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
+    st = _lib.status_buffer(q.device)
+    rc = _lib.lib().cb_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse),
+                                B, S, nh, dh, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
+                                ctypes.c_float(scale), int(causal), _lib.ptr(st),
+                                _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_attn_fwd")
+    return o, lse
+
+
+def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  o: torch.Tensor, lse: torch.Tensor, B: int, S: int, nh: int, dh: int, *,
+                  causal: bool = True, scale: Optional[float] = None,
+                  dqkv: Optional[torch.Tensor] = None
+                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns ``(dq, dk, dv)`` as column slices of one fused ``[B*S, 3*nh*dh]`` bf16 buffer
+    (``dqkv`` if given), ready to be the input of the QKV projection's backward GEMMs."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    H = nh * dh
+    if not q.is_cuda:
+        _, _, p, (qf, kf, vf) = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
+        dof = do.float().reshape(B, S, nh, dh).transpose(1, 2)
+        of = o.float().reshape(B, S, nh, dh).transpose(1, 2)
+        dv = p.transpose(-1, -2) @ dof
+        dp = dof @ vf.transpose(-1, -2)
+        delta = (dof * of).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dq = ds @ kf
+        dk = ds.transpose(-1, -2) @ qf
+        out = dqkv if dqkv is not None else torch.empty((B * S, 3 * H), dtype=q.dtype)
+        for i, t in enumerate((dq, dk, dv)):
+            out[:, i * H:(i + 1) * H] = t.transpose(1, 2).reshape(B * S, H).to(out.dtype)
+        return out[:, :H], out[:, H:2 * H], out[:, 2 * H:]
+    out = dqkv if dqkv is not None else torch.empty((B * S, 3 * H), dtype=torch.bfloat16,
+                                                    device=q.device)
+    dq_acc = torch.zeros((B * S, H), dtype=torch.float32, device=q.device)
+    delta = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
+    st = _lib.status_buffer(q.device)
+    rc = _lib.lib().cb_attn_bwd(
+        _lib.ptr(do), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse),
+        _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(out), B, S, nh, dh, do.stride(0), q.stride(0),
+        k.stride(0), v.stride(0), o.stride(0), out.stride(0), ctypes.c_float(scale), int(causal),
+        _lib.ptr(st), _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_attn_bwd")
+    return out[:, :H], out[:, H:2 * H], out[:, 2 * H:]

@@ -1,0 +1,226 @@
+"""Numerics of every hand-written CUDA kernel against the plain PyTorch fp32 restatement of the
+same op (the CPU branch of each function in ``coeus_b200.ops``)."""
+import math
+
+import pytest
+import torch
+
+from coeus_b200.ops import _lib
+from coeus_b200.ops import attention as A
+from coeus_b200.ops import elementwise as E
+from coeus_b200.ops import gemm as G
+from coeus_b200.ops import norm as N
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _status_clean():
+    assert _lib.status_buffer(torch.device("cuda", 0)).tolist()[0] == 0
+
+
+def _bf(x):
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (384, 512, 320), (200, 264, 72), (1024, 2048, 512)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_layouts(a_mn, b_mn, shape, bn):
+    M, Nn, K = shape
+    torch.manual_seed(1)
+    a = _bf(torch.randn((K, M) if a_mn else (M, K), device=DEV))
+    b = _bf(torch.randn((K, Nn) if b_mn else (Nn, K), device=DEV))
+    out = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    ref = G.gemm(a.cpu(), b.cpu(), a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    err = (out.float().cpu() - ref).abs().max().item()
+    assert err <= 0.01 * ref.abs().max().item() + 1e-3
+    _status_clean()
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(2)
+    M, Nn, K = 512, 768, 256
+    x = _bf(torch.randn(M, K, device=DEV))
+    w = _bf(torch.randn(K, Nn, device=DEV) * 0.05)
+    bias = _bf(torch.randn(Nn, device=DEV))
+    r = _bf(torch.randn(M, Nn, device=DEV))
+    dy = _bf(torch.randn(M, Nn, device=DEV))
+    y = G.linear_fwd(x, w, bias, resid=r)
+    ref = G.linear_fwd(x.cpu(), w.cpu(), bias.cpu(), resid=r.cpu(), out_dtype=torch.float32)
+    assert (y.float().cpu() - ref).abs().max() < 0.05
+    pre = torch.empty(M, Nn, device=DEV, dtype=torch.bfloat16)
+    y = G.linear_fwd(x, w, bias, epi="gelu", aux_out=pre)
+    pre_ref = torch.empty(M, Nn, dtype=torch.float32)
+    ref = G.linear_fwd(x.cpu(), w.cpu(), bias.cpu(), epi="gelu", aux_out=pre_ref,
+                       out_dtype=torch.float32)
+    assert (y.float().cpu() - ref).abs().max() < 0.03
+    assert (pre.float().cpu() - pre_ref).abs().max() < 0.03
+    dx = G.linear_dgrad(dy, w)
+    assert (dx.float().cpu() - dy.float().cpu() @ w.float().cpu().t()).abs().max() < 0.05
+    aux = _bf(torch.randn(M, K, device=DEV))
+    dx = G.linear_dgrad(dy, w, epi="dgelu", aux_in=aux)
+    ref = (dy.float().cpu() @ w.float().cpu().t()) * G._gelu_grad_ref(aux.float().cpu())
+    assert (dx.float().cpu() - ref).abs().max() < 0.05
+    gw = torch.zeros(K, Nn, device=DEV)
+    G.linear_wgrad(x, dy, gw, ksplit=4)
+    G.linear_wgrad(x, dy, gw, ksplit=1)
+    ref = 2 * (x.float().cpu().t() @ dy.float().cpu())
+    assert (gw.cpu() - ref).abs().max() < 1e-2
+    yf = G.linear_fwd(x, w, out_dtype=torch.float32)
+    assert (yf.cpu() - x.float().cpu() @ w.float().cpu()).abs().max() < 1e-3
+    _status_clean()
+
+
+@pytest.mark.parametrize("H", [64, 768, 1024, 2048, 4096])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_bwd(H, rms):
+    torch.manual_seed(3)
+    T = 517
+    x = _bf(torch.randn(T, H, device=DEV) * 2 + 0.5)
+    g = _bf(torch.randn(H, device=DEV))
+    b = None if rms else _bf(torch.randn(H, device=DEV))
+    dy = _bf(torch.randn(T, H, device=DEV))
+    dres = _bf(torch.randn(T, H, device=DEV))
+    y, mean, rstd = N.norm_fwd(x, g, b, 1e-5, rms)
+    yr, meanr, rstdr = N.norm_fwd(x.cpu(), g.cpu(), None if b is None else b.cpu(), 1e-5, rms)
+    assert (y.float().cpu() - yr.float()).abs().max() < 0.06
+    assert (rstd.cpu() - rstdr).abs().max() < 1e-3
+    dg = torch.zeros(H, device=DEV)
+    db = None if rms else torch.zeros(H, device=DEV)
+    dx = N.norm_bwd(dy, x, g, mean, rstd, dg, db, dres, rms)
+    dgr = torch.zeros(H)
+    dbr = None if rms else torch.zeros(H)
+    dxr = N.norm_bwd(dy.cpu(), x.cpu(), g.cpu(), meanr, rstdr, dgr, dbr, dres.cpu(), rms)
+    assert (dx.float().cpu() - dxr.float()).abs().max() < 0.08
+    assert (dg.cpu() - dgr).abs().max() < 0.02 * dgr.abs().max() + 0.05
+    if not rms:
+        assert (db.cpu() - dbr).abs().max() < 0.02 * dbr.abs().max() + 0.05
+
+
+def test_embedding_and_positions():
+    torch.manual_seed(4)
+    V, H, S, B = 1000, 256, 64, 3
+    table = _bf(torch.randn(V, H, device=DEV))
+    ids = torch.randint(0, V, (B * S,), device=DEV)
+    pe = E.sinusoid_table(S, H, DEV)
+    per = E.sinusoid_table(S, H, "cpu")
+    assert (pe.cpu() - per).abs().max() < 2e-4
+    out = E.embed_fwd(ids, table, pe, S)
+    ref = E.embed_fwd(ids.cpu(), table.cpu(), per, S)
+    assert (out.float().cpu() - ref.float()).abs().max() < 0.03
+    dy = _bf(torch.randn(B * S, H, device=DEV))
+    gt = torch.zeros(V, H, device=DEV)
+    E.embed_bwd(ids, dy, gt)
+    gtr = torch.zeros(V, H)
+    E.embed_bwd(ids.cpu(), dy.cpu(), gtr)
+    assert (gt.cpu() - gtr).abs().max() < 1e-4
+    _status_clean()
+
+
+def test_embedding_out_of_range_sets_status():
+    V, H = 100, 64
+    table = _bf(torch.randn(V, H, device=DEV))
+    ids = torch.tensor([1, 2, 100], device=DEV)
+    out = E.embed_fwd(ids, table, None, 3)
+    torch.cuda.synchronize()
+    st = _lib.status_buffer(torch.device("cuda", 0))
+    assert st.tolist()[:2] == [2, 2]
+    assert out[2].abs().max() == 0
+    st.zero_()
+
+
+@pytest.mark.parametrize("V", [512, 32000])
+def test_cross_entropy(V):
+    torch.manual_seed(5)
+    T = 300
+    logits = _bf(torch.randn(T, V, device=DEV) * 3)
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    tgt[5] = -100
+    lc, tc = logits.clone().cpu(), tgt.cpu()
+    loss = E.cross_entropy_fwd_bwd(logits, tgt, 1.0 / T)
+    lr = E.cross_entropy_fwd_bwd(lc, tc, 1.0 / T)
+    assert (loss.cpu() - lr).abs().max() < 2e-3
+    assert (logits.float().cpu() - lc.float()).abs().max() < 2e-4
+    # vocab-parallel halves on two shards reproduce the fused result
+    full = _bf(torch.randn(T, V, device=DEV) * 3)
+    half = V // 2
+    stats = [E.cross_entropy_stats(full[:, i * half:(i + 1) * half], tgt, i * half) for i in range(2)]
+    m = torch.maximum(stats[0][:, 0], stats[1][:, 0])
+    s = sum(st[:, 1] * torch.exp(st[:, 0] - m) for st in stats)
+    lse = m + torch.log(s)
+    tl = stats[0][:, 2] + stats[1][:, 2]
+    ref = torch.nn.functional.cross_entropy(full.float(), tgt, reduction="none", ignore_index=-100)
+    assert ((lse - tl) * (tgt >= 0) - ref).abs().max() < 2e-3
+
+
+def test_adamw_matches_torch():
+    torch.manual_seed(6)
+    n = 100003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    pb = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in (1, 2, 3):
+        ref.grad = g.clone()
+        opt.step()
+        E.adamw_step(p, m, v, g, pb, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                     step=step)
+    assert (p - ref.data).abs().max() < 1e-5
+    assert (pb.float() - p).abs().max() < 0.02
+
+
+def test_activations_softmax_rope_colsum_init():
+    torch.manual_seed(7)
+    x = _bf(torch.randn(333, 512, device=DEV) * 2)
+    dy = _bf(torch.randn(333, 512, device=DEV))
+    assert (E.gelu_fwd(x).float().cpu() - E.gelu_fwd(x.cpu()).float()).abs().max() < 0.02
+    assert (E.gelu_bwd(x, dy).float().cpu() - E.gelu_bwd(x.cpu(), dy.cpu()).float()).abs().max() < 0.03
+    gu = _bf(torch.randn(100, 1024, device=DEV))
+    d2 = _bf(torch.randn(100, 512, device=DEV))
+    assert (E.swiglu_fwd(gu).float().cpu() - E.swiglu_fwd(gu.cpu()).float()).abs().max() < 0.03
+    assert (E.swiglu_bwd(gu, d2).float().cpu() - E.swiglu_bwd(gu.cpu(), d2.cpu()).float()).abs().max() < 0.05
+    z = torch.randn(77, 1000, device=DEV)
+    assert (E.softmax_rows(z).cpu() - torch.softmax(z.cpu(), -1)).abs().max() < 1e-6
+    q = _bf(torch.randn(64, 4 * 64, device=DEV))
+    qc = q.clone().cpu()
+    E.rope_(q, 4, 64, 16, pos_offset=3)
+    E.rope_(qc, 4, 64, 16, pos_offset=3)
+    assert (q.float().cpu() - qc.float()).abs().max() < 0.03
+    cs = torch.zeros(512, device=DEV)
+    E.colsum_into(x, cs)
+    assert (cs.cpu() - x.float().cpu().sum(0)).abs().max() < 1e-2
+    p = torch.empty(5000, device=DEV)
+    E.sin_init_(p, 768, index_offset=20_000_000)
+    pr = torch.empty(5000)
+    E.sin_init_(pr, 768, index_offset=20_000_000)
+    assert (p.cpu() - pr).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dh", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("S", [128, 200, 512])
+def test_attention_fwd_bwd(dh, causal, S):
+    torch.manual_seed(8)
+    B, nh = 2, 3
+    H = nh * dh
+    qkv = _bf(torch.randn(B * S, 3 * H, device=DEV))
+    q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+    o, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal)
+    qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
+    orf, lser = A.attention_fwd(qc, kc, vc, B, S, nh, dh, causal=causal)
+    torch.cuda.synchronize()
+    _status_clean()
+    assert (o.float().cpu() - orf.float()).abs().max() < 0.03
+    assert (lse.cpu() - lser).abs().max() < 0.02
+    do = _bf(torch.randn(B * S, H, device=DEV))
+    dq, dk, dv = A.attention_bwd(do, q, k, v, o, lse, B, S, nh, dh, causal=causal)
+    dqr, dkr, dvr = A.attention_bwd(do.cpu(), qc, kc, vc, orf, lser, B, S, nh, dh, causal=causal)
+    torch.cuda.synchronize()
+    _status_clean()
+    for got, ref, name in ((dq, dqr, "dq"), (dk, dkr, "dk"), (dv, dvr, "dv")):
+        err = (got.float().cpu() - ref.float()).abs().max().item()
+        assert err < 0.02 * ref.float().abs().max().item() + 0.03, (name, err)
