@@ -193,15 +193,17 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
   }
 }
 
-// sum of squares of an fp32 buffer accumulated into *out (for the global gradient norm)
-__global__ void sumsq_kernel(const float* __restrict__ g, size_t n, float* __restrict__ out) {
+// *out += scale * sum(g) (square == 0) or scale * sum(g*g) (square == 1) of an fp32 buffer:
+// the mean loss and the global gradient norm.
+__global__ void sumsq_kernel(const float* __restrict__ g, size_t n, float* __restrict__ out,
+                             int square, float scale) {
   __shared__ float red[32];
   float s = 0.f;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<size_t>(gridDim.x) * blockDim.x)
-    s += g[i] * g[i];
+    s += square ? g[i] * g[i] : g[i];
   s = block_sum(s, red);
-  if (threadIdx.x == 0) atomicAdd(out, s);
+  if (threadIdx.x == 0) atomicAdd(out, s * scale);
 }
 // coef = min(1, max_norm / (sqrt(sumsq * scale^2) + 1e-6))
 __global__ void clip_coef_kernel(const float* sumsq, float scale, float max_norm, float* coef,
@@ -429,7 +431,13 @@ extern "C" int cb_adamw(float* p, float* m, float* v, const float* g, void* p_bf
 extern "C" int cb_sumsq(const float* g, size_t n, float* out, void* stream) {
   if (n == 0) return 0;
   sumsq_kernel<<<grid_for(n, 1024) > 1184 ? 1184 : grid_for(n, 1024), 1024, 0, CB_ST(stream)>>>(
-      g, n, out);
+      g, n, out, 1, 1.0f);
+  CB_RET();
+}
+extern "C" int cb_sum_scaled(const float* g, size_t n, float* out, float scale, void* stream) {
+  if (n == 0) return 0;
+  sumsq_kernel<<<grid_for(n, 1024) > 1184 ? 1184 : grid_for(n, 1024), 1024, 0, CB_ST(stream)>>>(
+      g, n, out, 0, scale);
   CB_RET();
 }
 extern "C" int cb_clip_coef(const float* sumsq, float scale, float max_norm, float* coef,

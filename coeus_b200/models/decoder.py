@@ -1,0 +1,420 @@
+"""Decoder-only transformer with an explicit forward and backward pass over the hand-written
+kernels of :mod:`coeus_b200.ops`.
+
+The math is the reference's forward pass (plugins/model-transformer/src/lib.rs:791-919): token
+embedding plus sinusoidal positions, ``num_layers`` pre-norm blocks of causal multi-head
+attention and a GELU feed-forward network with residual connections, a final norm and an output
+projection ``[H, V]`` without bias.  Weights are stored ``[in, out]`` row-major like the
+reference's; Q, K and V are kept as one fused ``[H, 3H]`` matrix so the three projections are one
+GEMM.  Normalisation is per token (the reference normalises over the whole ``[S*H]`` buffer,
+which equals this at ``S == 1``).  ``DecoderConfig`` additionally selects RMSNorm, rotary
+positions and a SwiGLU feed-forward for the larger configurations.
+
+Training state lives in three flat buffers (fp32 master weights, bf16 working copy, fp32
+gradients) so that the optimizer, gradient reduction and checkpointing see one contiguous range;
+matrices (weight-decayed) come first, vectors (biases, norm scales) after them.  No autograd
+graph is built: ``forward_loss`` keeps the activations the hand-written ``backward`` needs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..foundation.error import ProcessingError
+from ..ops import attention as A
+from ..ops import elementwise as E
+from ..ops import gemm as G
+from ..ops import norm as N
+from .config import DecoderConfig
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: Tuple[int, ...]
+    decay: bool
+    kind: str  # "weight" | "bias" | "scale" | "embed"
+    offset: int = 0
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+
+class ParamLayout:
+    """Ordered parameter list of a :class:`DecoderConfig` and its placement in the flat buffers.
+
+    Tensor names follow the reference's field names (``token_embed``, ``layers.{l}.ln1_scale``,
+    ``layers.{l}.attn.*``, ``layers.{l}.ff.*``, ``final_ln_*``, ``output_proj``) with the fused
+    ``attn.qkv_weights`` standing for ``q_weights | k_weights | v_weights``.
+    """
+
+    ALIGN = 64  # elements; every tensor starts on a 256-byte (fp32) / 128-byte (bf16) boundary
+
+    def __init__(self, cfg: DecoderConfig, tp: int = 1) -> None:
+        self.cfg = cfg
+        H, I, V, L = cfg.hidden_dim, cfg.intermediate_dim, cfg.vocab_size, cfg.num_layers
+        ln = cfg.norm == "layernorm"
+        s1, s2 = ("ln1", "ln2") if ln else ("norm1", "norm2")
+        specs: List[ParamSpec] = [ParamSpec("token_embed", (V, H), True, "embed")]
+        for l in range(L):
+            p = f"layers.{l}."
+            specs.append(ParamSpec(p + "attn.qkv_weights", (H, 3 * H), True, "weight"))
+            specs.append(ParamSpec(p + "attn.o_weights", (H, H), True, "weight"))
+            if cfg.num_experts:
+                E_ = cfg.num_experts
+                specs.append(ParamSpec(p + "moe.router_weights", (H, E_), True, "weight"))
+                specs.append(ParamSpec(p + "moe.experts.gate_up_weights", (E_, H, 2 * I), True, "weight"))
+                specs.append(ParamSpec(p + "moe.experts.down_weights", (E_, I, H), True, "weight"))
+            elif cfg.activation == "swiglu":
+                specs.append(ParamSpec(p + "ff.gate_up_weights", (H, 2 * I), True, "weight"))
+                specs.append(ParamSpec(p + "ff.down_weights", (I, H), True, "weight"))
+            else:
+                specs.append(ParamSpec(p + "ff.up_weights", (H, I), True, "weight"))
+                specs.append(ParamSpec(p + "ff.down_weights", (I, H), True, "weight"))
+        if not cfg.tie_embeddings:
+            specs.append(ParamSpec("output_proj", (H, V), True, "weight"))
+        vec: List[ParamSpec] = []
+        for l in range(L):
+            p = f"layers.{l}."
+            vec.append(ParamSpec(p + s1 + "_scale", (H,), False, "scale"))
+            if ln:
+                vec.append(ParamSpec(p + s1 + "_bias", (H,), False, "bias"))
+            vec.append(ParamSpec(p + s2 + "_scale", (H,), False, "scale"))
+            if ln:
+                vec.append(ParamSpec(p + s2 + "_bias", (H,), False, "bias"))
+            if cfg.use_bias:
+                vec.append(ParamSpec(p + "attn.qkv_bias", (3 * H,), False, "bias"))
+                vec.append(ParamSpec(p + "attn.o_bias", (H,), False, "bias"))
+                if not cfg.num_experts and cfg.activation == "gelu":
+                    vec.append(ParamSpec(p + "ff.up_bias", (I,), False, "bias"))
+                    vec.append(ParamSpec(p + "ff.down_bias", (H,), False, "bias"))
+        fn = "final_ln" if ln else "final_norm"
+        vec.append(ParamSpec(fn + "_scale", (H,), False, "scale"))
+        if ln:
+            vec.append(ParamSpec(fn + "_bias", (H,), False, "bias"))
+        off = 0
+        for s in specs + vec:
+            s.offset = off
+            off += (s.numel + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+            if s is specs[-1]:
+                self.decay_end = off
+        self.specs: List[ParamSpec] = specs + vec
+        self.by_name: Dict[str, ParamSpec] = {s.name: s for s in self.specs}
+        self.total = off
+        self.norm_names = (s1, s2, fn)
+
+    def num_parameters(self) -> int:
+        return sum(s.numel for s in self.specs)
+
+    def padded_total(self, multiple: int) -> int:
+        return (self.total + multiple - 1) // multiple * multiple
+
+
+class DecoderLM:
+    """The decoder-only language model on one GPU (or on CPU through the ops' oracle path)."""
+
+    def __init__(self, cfg: DecoderConfig, device="cuda", init: str = "normal", seed: int = 0,
+                 pad_multiple: int = 8 * 1024, training: bool = True) -> None:
+        cfg.validate()
+        if cfg.num_experts:
+            raise ProcessingError.unsupported(
+                "DecoderLM with num_experts > 0", "use coeus_b200.parallel.ep.MoEDecoderLM")
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.layout = ParamLayout(cfg)
+        n = self.layout.padded_total(pad_multiple)
+        self.n_flat = n
+        self.p32 = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.p16 = torch.zeros(n, dtype=torch.bfloat16, device=self.device)
+        self.g32 = torch.zeros(n, dtype=torch.float32, device=self.device) if training else None
+        self.training = training
+        self.w: Dict[str, torch.Tensor] = {}
+        self.g: Dict[str, torch.Tensor] = {}
+        self.master: Dict[str, torch.Tensor] = {}
+        self._bind_views()
+        self._ws: Dict[str, torch.Tensor] = {}
+        self._pe: Optional[torch.Tensor] = None
+        self._saved: Optional[dict] = None
+        self.max_ctas = 0
+        self.init_parameters(init, seed)
+
+    # ------------------------------------------------------------------ parameters
+    def _bind_views(self) -> None:
+        for s in self.layout.specs:
+            sl = slice(s.offset, s.offset + s.numel)
+            self.w[s.name] = self.p16[sl].view(s.shape)
+            self.master[s.name] = self.p32[sl].view(s.shape)
+            if self.g32 is not None:
+                self.g[s.name] = self.g32[sl].view(s.shape)
+
+    def rebind(self, p16: Optional[torch.Tensor] = None, g32: Optional[torch.Tensor] = None) -> None:
+        """Point the views at externally allocated flat buffers (e.g. symmetric memory shared
+        with the other data-parallel ranks); current contents are copied over."""
+        if p16 is not None:
+            p16[: self.n_flat].copy_(self.p16)
+            self.p16 = p16[: self.n_flat]
+        if g32 is not None:
+            if self.g32 is not None:
+                g32[: self.n_flat].copy_(self.g32)
+            self.g32 = g32[: self.n_flat]
+        self._bind_views()
+
+    def init_parameters(self, init: str = "normal", seed: int = 0) -> None:
+        """``normal``: weights N(0, init_std), scales 1, biases 0.  ``reference``: the
+        reference's deterministic ``clamp(sin(i * 0.1234567) * sqrt(2/H), ±0.1)`` for every
+        element, norm scales and biases included (plugins/model-transformer/src/lib.rs:604-611);
+        ``i`` is the element's index in the reference's flat layout."""
+        cfg = self.cfg
+        if init == "reference":
+            from .layout_ref import reference_offsets
+            offs = reference_offsets(cfg)
+            for name, (off, shape) in offs.items():
+                flat = torch.empty(int(math.prod(shape)), dtype=torch.float32, device=self.device)
+                E.sin_init_(flat, cfg.hidden_dim, index_offset=off)
+                self._assign_reference_tensor(name, flat.view(shape))
+        elif init == "normal":
+            gen = torch.Generator(device=self.device)
+            gen.manual_seed(seed)
+            for s in self.layout.specs:
+                t = self.master[s.name]
+                if s.kind in ("weight", "embed"):
+                    t.normal_(0.0, cfg.init_std, generator=gen)
+                elif s.kind == "scale":
+                    t.fill_(1.0)
+                else:
+                    t.zero_()
+        elif init == "zeros":
+            self.p32.zero_()
+        else:
+            raise ProcessingError.invalid_input(f"unknown init '{init}'")
+        self.sync_working_copy()
+
+    def _assign_reference_tensor(self, name: str, value: torch.Tensor) -> None:
+        """Store a tensor given under its reference name (q/k/v separate) into the fused layout."""
+        H = self.cfg.hidden_dim
+        for i, part in enumerate(("q", "k", "v")):
+            if name.endswith(f"attn.{part}_weights"):
+                fused = name.replace(f"attn.{part}_weights", "attn.qkv_weights")
+                self.master[fused][:, i * H:(i + 1) * H] = value
+                return
+            if name.endswith(f"attn.{part}_bias"):
+                fused = name.replace(f"attn.{part}_bias", "attn.qkv_bias")
+                self.master[fused][i * H:(i + 1) * H] = value
+                return
+        self.master[name].copy_(value)
+
+    def sync_working_copy(self) -> None:
+        self.p16.copy_(self.p32)
+
+    def num_parameters(self) -> int:
+        return self.layout.num_parameters()
+
+    def named_parameters(self):
+        for s in self.layout.specs:
+            yield s.name, self.master[s.name]
+
+    # ------------------------------------------------------------------ workspace
+    def _buf(self, name: str, shape, dtype=None) -> torch.Tensor:
+        key = name
+        dtype = dtype or self.p16.dtype
+        t = self._ws.get(key)
+        if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
+            t = torch.empty(shape, dtype=dtype, device=self.device)
+            self._ws[key] = t
+        return t
+
+    def _positions(self, S: int) -> Optional[torch.Tensor]:
+        if self.cfg.pos != "sinusoidal":
+            return None
+        if self._pe is None or self._pe.shape[0] < S:
+            self._pe = E.sinusoid_table(max(S, self.cfg.max_seq_len), self.cfg.hidden_dim,
+                                        self.device)
+        return self._pe
+
+    # ------------------------------------------------------------------ forward
+    def _norm(self, x, prefix):
+        cfg = self.cfg
+        rms = cfg.norm == "rmsnorm"
+        return N.norm_fwd(x, self.w[prefix + "_scale"], None if rms else self.w[prefix + "_bias"],
+                          cfg.norm_eps, rms)
+
+    def _block_fwd(self, l: int, x: torch.Tensor, B: int, S: int, save: Optional[dict]):
+        cfg = self.cfg
+        H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
+        p = f"layers.{l}."
+        n1n, n2n, _ = self.layout.norm_names
+        bias = (lambda n: self.w[p + n]) if cfg.use_bias else (lambda n: None)
+        T = x.shape[0]
+        mc = self.max_ctas
+        n1, mean1, rstd1 = self._norm(x, p + n1n)
+        qkv = G.linear_fwd(n1, self.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"),
+                           out=self._buf(f"qkv{l}" if save is not None else "qkv", (T, 3 * H)),
+                           max_ctas=mc)
+        if cfg.pos == "rope":
+            E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)  # q and k heads are adjacent
+        q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+        attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+        x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
+                             max_ctas=mc)
+        n2, mean2, rstd2 = self._norm(x_mid, p + n2n)
+        if cfg.activation == "swiglu":
+            gu = G.linear_fwd(n2, self.w[p + "ff.gate_up_weights"], None, max_ctas=mc)
+            act = E.swiglu_fwd(gu)
+            u = gu
+            x_out = G.linear_fwd(act, self.w[p + "ff.down_weights"], None, resid=x_mid, max_ctas=mc)
+        else:
+            u = torch.empty((T, cfg.intermediate_dim), dtype=self.p16.dtype, device=x.device) \
+                if save is not None else None
+            act = G.linear_fwd(n2, self.w[p + "ff.up_weights"], bias("ff.up_bias"), epi="gelu",
+                               aux_out=u, max_ctas=mc)
+            x_out = G.linear_fwd(act, self.w[p + "ff.down_weights"], bias("ff.down_bias"),
+                                 resid=x_mid, max_ctas=mc)
+        if save is not None:
+            save[l] = dict(x=x, n1=n1, mean1=mean1, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse,
+                           x_mid=x_mid, n2=n2, mean2=mean2, rstd2=rstd2, u=u, act=act)
+        return x_out
+
+    def _check_ids(self, ids: torch.Tensor) -> Tuple[int, int]:
+        if ids.dim() == 1:
+            ids = ids[None]
+        B, S = ids.shape
+        if S < 1 or S > self.cfg.max_seq_len:
+            raise ProcessingError.invalid_input(
+                f"Sequence length {S} out of range [1, {self.cfg.max_seq_len}]")
+        return B, S
+
+    def forward_hidden(self, ids: torch.Tensor, save: Optional[dict] = None) -> torch.Tensor:
+        """Final-norm output ``[B*S, H]`` for ``ids [B, S]`` (int64)."""
+        B, S = self._check_ids(ids)
+        x = E.embed_fwd(ids.reshape(-1), self.w["token_embed"], self._positions(S), S)
+        for l in range(self.cfg.num_layers):
+            x = self._block_fwd(l, x, B, S, save)
+        fn = self.layout.norm_names[2]
+        xf, meanf, rstdf = self._norm(x, fn)
+        if save is not None:
+            save["final"] = dict(x=x, xf=xf, mean=meanf, rstd=rstdf)
+        return xf
+
+    def output_weight(self) -> Tuple[torch.Tensor, bool]:
+        """``(weight, b_mn)`` of the LM head as the GEMM's B operand."""
+        if self.cfg.tie_embeddings:
+            return self.w["token_embed"], False   # [V, H] is already [N, K]
+        return self.w["output_proj"], True        # [H, V] = [K, N]
+
+    def forward_logits(self, ids: torch.Tensor, last_only: bool = False) -> torch.Tensor:
+        """Logits in bf16: ``[B, S, V]``, or ``[B, V]`` of the last position (the reference's
+        ``forward`` returns the last position only, lib.rs:913-918)."""
+        B, S = self._check_ids(ids)
+        xf = self.forward_hidden(ids)
+        V = self.cfg.vocab_size
+        if last_only:
+            xf = xf.view(B, S, -1)[:, -1, :].contiguous()
+        w, b_mn = self.output_weight()
+        logits = G.gemm(xf, w, b_mn=b_mn, max_ctas=self.max_ctas)
+        return logits.view(B, V) if last_only else logits.view(B, S, V)
+
+    def forward_loss(self, ids: torch.Tensor, targets: torch.Tensor,
+                     grad_scale: Optional[float] = None) -> torch.Tensor:
+        """Mean next-token cross-entropy (fp32 scalar tensor) of ``ids [B,S]`` against
+        ``targets [B,S]``; keeps what :meth:`backward` needs.  ``grad_scale`` is the factor the
+        logit gradients are multiplied with (default ``1 / (B*S)``)."""
+        B, S = self._check_ids(ids)
+        T = B * S
+        save: dict = {"ids": ids.reshape(-1), "B": B, "S": S}
+        xf = self.forward_hidden(ids, save)
+        w, b_mn = self.output_weight()
+        logits = G.gemm(xf, w, b_mn=b_mn, out=self._buf("logits", (T, self.cfg.vocab_size)),
+                        max_ctas=self.max_ctas)
+        scale = grad_scale if grad_scale is not None else 1.0 / T
+        loss_tok = E.cross_entropy_fwd_bwd(logits, targets.reshape(-1), scale)
+        save["dlogits"] = logits
+        self._saved = save
+        loss = torch.zeros(1, dtype=torch.float32, device=self.device)
+        E.sum_scaled_into(loss_tok, loss, 1.0 / T)
+        return loss
+
+    # ------------------------------------------------------------------ backward
+    def zero_grad(self) -> None:
+        self.g32.zero_()
+
+    def backward(self, on_layer_done=None) -> None:
+        """Accumulate parameter gradients (fp32) for the last :meth:`forward_loss`.
+        ``on_layer_done(l)`` is called once the gradients of layer ``l`` are complete (``-1`` for
+        the LM head and final norm, ``-2`` after the embedding), which is where the data-parallel
+        reduction of a bucket may start."""
+        sv = self._saved
+        if sv is None:
+            raise ProcessingError.not_initialized("backward (no forward_loss saved)")
+        cfg = self.cfg
+        H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
+        B, S = sv["B"], sv["S"]
+        rms = cfg.norm == "rmsnorm"
+        n1n, n2n, fn = self.layout.norm_names
+        mc = self.max_ctas
+        dlog = sv["dlogits"]
+        fin = sv["final"]
+        w, b_mn = self.output_weight()
+        if cfg.tie_embeddings:
+            # d token_embed[V,H] += dlogits^T[V,T] @ xf[T,H]
+            G.gemm(dlog, fin["xf"], a_mn=True, b_mn=True, out=self.g["token_embed"],
+                   accumulate=True, ksplit=2, max_ctas=mc)
+            dxf = G.gemm(dlog, w, b_mn=True, max_ctas=mc)
+        else:
+            G.linear_wgrad(fin["xf"], dlog, self.g["output_proj"], max_ctas=mc)
+            dxf = G.linear_dgrad(dlog, w, max_ctas=mc)
+        dx = N.norm_bwd(dxf, fin["x"], self.w[fn + "_scale"], fin["mean"], fin["rstd"],
+                        self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None, rms)
+        if on_layer_done is not None:
+            on_layer_done(-1)
+        for l in reversed(range(cfg.num_layers)):
+            a = sv[l]
+            p = f"layers.{l}."
+            if cfg.activation == "swiglu":
+                G.linear_wgrad(a["act"], dx, self.g[p + "ff.down_weights"], max_ctas=mc)
+                dact = G.linear_dgrad(dx, self.w[p + "ff.down_weights"], max_ctas=mc)
+                du = E.swiglu_bwd(a["u"], dact)
+                G.linear_wgrad(a["n2"], du, self.g[p + "ff.gate_up_weights"], max_ctas=mc)
+                dn2 = G.linear_dgrad(du, self.w[p + "ff.gate_up_weights"], max_ctas=mc)
+            else:
+                G.linear_wgrad(a["act"], dx, self.g[p + "ff.down_weights"], max_ctas=mc)
+                du = G.linear_dgrad(dx, self.w[p + "ff.down_weights"], epi="dgelu", aux_in=a["u"],
+                                    max_ctas=mc)
+                G.linear_wgrad(a["n2"], du, self.g[p + "ff.up_weights"], max_ctas=mc)
+                if cfg.use_bias:
+                    E.colsum_into(dx, self.g[p + "ff.down_bias"])
+                    E.colsum_into(du, self.g[p + "ff.up_bias"])
+                dn2 = G.linear_dgrad(du, self.w[p + "ff.up_weights"], max_ctas=mc)
+            dx_mid = N.norm_bwd(dn2, a["x_mid"], self.w[p + n2n + "_scale"], a["mean2"], a["rstd2"],
+                                self.g[p + n2n + "_scale"],
+                                None if rms else self.g[p + n2n + "_bias"], dx, rms)
+            G.linear_wgrad(a["attn"], dx_mid, self.g[p + "attn.o_weights"], max_ctas=mc)
+            if cfg.use_bias:
+                E.colsum_into(dx_mid, self.g[p + "attn.o_bias"])
+            dattn = G.linear_dgrad(dx_mid, self.w[p + "attn.o_weights"], max_ctas=mc)
+            qkv = a["qkv"]
+            q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+            dqkv = self._buf("dqkv", (B * S, 3 * H))
+            A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, causal=True,
+                            dqkv=dqkv)
+            if cfg.pos == "rope":
+                E.rope_(dqkv, 2 * nh, dh, S, theta=cfg.rope_theta, inverse=True)
+            G.linear_wgrad(a["n1"], dqkv, self.g[p + "attn.qkv_weights"], max_ctas=mc)
+            if cfg.use_bias:
+                E.colsum_into(dqkv, self.g[p + "attn.qkv_bias"])
+            dn1 = G.linear_dgrad(dqkv, self.w[p + "attn.qkv_weights"], max_ctas=mc)
+            dx = N.norm_bwd(dn1, a["x"], self.w[p + n1n + "_scale"], a["mean1"], a["rstd1"],
+                            self.g[p + n1n + "_scale"],
+                            None if rms else self.g[p + n1n + "_bias"], dx_mid, rms)
+            if on_layer_done is not None:
+                on_layer_done(l)
+        E.embed_bwd(sv["ids"], dx, self.g["token_embed"])
+        if on_layer_done is not None:
+            on_layer_done(-2)
+        self._saved = None

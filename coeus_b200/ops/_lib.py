@@ -76,6 +76,12 @@ def check_status(device: Optional[torch.device] = None) -> None:
         raise DeviceError.from_status(code, where)
 
 
-def check_rc(rc: int, name: str) -> None:
+launch_count = 0  # number of kernel launches issued through this module
+
+
+def check_rc(rc: int, name: str, launches: int = 1) -> None:
+    """Raise on a non-zero host-side return code; count the launches the call made."""
+    global launch_count
     if rc != 0:
         raise KernelLibraryError(f"{name} failed on the host side with code {rc}")
+    launch_count += launches

@@ -84,5 +84,5 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
         _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(out), B, S, nh, dh, do.stride(0), q.stride(0),
         k.stride(0), v.stride(0), o.stride(0), out.stride(0), ctypes.c_float(scale), int(causal),
         _lib.ptr(st), _lib.stream_ptr())
-    _lib.check_rc(rc, "cb_attn_bwd")
+    _lib.check_rc(rc, "cb_attn_bwd", launches=3)
     return out[:, :H], out[:, H:2 * H], out[:, 2 * H:]

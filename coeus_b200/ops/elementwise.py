@@ -180,6 +180,16 @@ def sumsq_into(g: torch.Tensor, out: torch.Tensor) -> None:
     _lib.check_rc(rc, "cb_sumsq")
 
 
+def sum_scaled_into(x: torch.Tensor, out: torch.Tensor, scale: float) -> None:
+    """``out[0] += scale * sum(x)`` for a flat fp32 tensor (mean loss)."""
+    if not x.is_cuda:
+        out.add_(x.float().sum() * scale)
+        return
+    rc = _lib.lib().cb_sum_scaled(_lib.ptr(x), c_size_t(x.numel()), _lib.ptr(out),
+                                  c_float(scale), _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_sum_scaled")
+
+
 def clip_coef_from_sumsq(sumsq: torch.Tensor, scale: float, max_norm: float,
                          coef: torch.Tensor, norm_out: Optional[torch.Tensor] = None) -> None:
     """``coef = min(1, max_norm / (sqrt(sumsq) * scale + 1e-6))`` computed on the device."""

@@ -70,6 +70,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         if out is None:
             raise ValueError("gemm: accumulate=True needs an fp32 `out`")
     if out is None:
+        if not a.is_cuda and a.dtype != torch.bfloat16 and out_dtype == torch.bfloat16:
+            out_dtype = a.dtype  # the CPU oracle keeps the precision it is given
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     if not a.is_cuda:
         A = (a.t() if a_mn else a).float()

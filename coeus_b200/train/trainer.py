@@ -1,0 +1,91 @@
+"""Trainer: one object that owns the model, the optimizer state and the data-parallel plan and
+runs whole training steps.
+
+It keeps the shape of the reference's ``TrainableModel`` trait (``train_step``,
+``update_parameters``, ``compute_loss``, ``is_training``, ``set_training``;
+src/core/model.rs:107-131) and of its example loop (examples/training_example.rs:257-276), and
+supplies what the reference leaves out: a real backward pass, AdamW, and sharded data
+parallelism over NVLink.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..models.decoder import DecoderLM
+from ..optim.adamw import AdamW, AdamWConfig
+
+
+@dataclass
+class TrainConfig:
+    """Counterpart of the reference's ``TrainingConfig{learning_rate, batch_size, epochs}``
+    (src/domain/training/mod.rs:14-20) with the fields a real step needs."""
+
+    learning_rate: float = 3e-4
+    batch_size: int = 8
+    epochs: int = 1
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    grad_clip: Optional[float] = None
+    grad_accum: int = 1
+
+    def adamw(self) -> AdamWConfig:
+        return AdamWConfig(self.learning_rate, self.beta1, self.beta2, self.eps,
+                           self.weight_decay, self.grad_clip)
+
+
+class Trainer:
+    def __init__(self, model: DecoderLM, cfg: Optional[TrainConfig] = None, dp=None) -> None:
+        """``dp`` is a :class:`coeus_b200.parallel.zero.ShardedDataParallel` (or ``None`` for a
+        single replica)."""
+        self.model = model
+        self.cfg = cfg or TrainConfig()
+        self.dp = dp
+        self._training = True
+        self.step_index = 0
+        self.listeners: List[Callable[[dict], None]] = []
+        if dp is None:
+            self.opt = AdamW(self.cfg.adamw(), 0, model.n_flat, model.layout.decay_end,
+                             model.device)
+        else:
+            dp.attach(model, self.cfg.adamw())
+            self.opt = dp.opt
+
+    # ---- TrainableModel surface
+    def is_training(self) -> bool:
+        return self._training
+
+    def set_training(self, training: bool) -> None:
+        self._training = training
+
+    def compute_loss(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        return self.model.forward_loss(ids, targets)
+
+    def update_parameters(self, grad_scale: float = 1.0) -> None:
+        m = self.model
+        if self.dp is None:
+            self.opt.step(m.p32, m.g32, m.p16, grad_scale)
+        else:
+            self.dp.reduce_and_step(grad_scale)
+
+    def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Forward, backward and optimizer update for one (micro-)batch per rank; returns the
+        rank-local mean loss as a device scalar."""
+        m = self.model
+        world = 1 if self.dp is None else self.dp.world
+        if self.dp is not None:
+            self.dp.begin_step()
+        m.zero_grad()
+        loss = m.forward_loss(ids, targets)
+        m.backward(on_layer_done=None if self.dp is None else self.dp.on_layer_done)
+        self.update_parameters(1.0 / world)
+        self.step_index += 1
+        return loss
+
+    # ---- Checkpoint trait (src/core/traits.rs:181-189)
+    def state_dict(self) -> Dict[str, object]:
+        return {"p32": self.model.p32, "opt": self.opt.state_dict(), "step": self.step_index}
