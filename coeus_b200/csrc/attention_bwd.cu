@@ -524,3 +524,65 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -12;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in no_alloc.h): the dQ accumulator and the
+// delta rows come from a fixed array inside the library image instead of from the caller.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[CB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address is asked for
+// once per device (with that device current) and cached.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return CB_NOALLOC_ERR_SYMBOL;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess ||
+        p == nullptr)
+      return CB_NOALLOC_ERR_SYMBOL;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int cb_attn_bwd_noalloc(const void* dO, const void* q, const void* k, const void* v,
+                                   const void* o, const float* lse, void* dqkv, int B, int S,
+                                   int nh, int dh, int lddo, int ldq, int ldk, int ldv, int ldo,
+                                   int ldd, float scale, int causal, int* status, void* stream) {
+  if (B <= 0 || S <= 0 || nh <= 0 || dh <= 0) return -2;
+  const size_t dq_floats = static_cast<size_t>(B) * S * nh * dh;
+  const size_t delta_floats = static_cast<size_t>(B) * nh * S;
+  if (dq_floats + delta_floats > CB_NOALLOC_SCRATCH_FLOATS) return CB_NOALLOC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  // The accumulator must start at zero; delta is fully overwritten by its producer kernel.
+  if (cudaMemsetAsync(scratch, 0, dq_floats * sizeof(float),
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return -102;
+  return cb_attn_bwd(dO, q, k, v, o, lse, scratch + dq_floats, scratch, dqkv, B, S, nh, dh, lddo,
+                     ldq, ldk, ldv, ldo, ldd, scale, causal, status, stream);
+}
+
+extern "C" const char* cb_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case CB_NOALLOC_ERR_TOO_LARGE:
+      return "problem too large for the built-in scratch: B*S*nh*dh + B*nh*S exceeds the maximum "
+             "of CB_NOALLOC_SCRATCH_FLOATS (4 Mi floats, 16 MiB)";
+    case CB_NOALLOC_ERR_SYMBOL:
+      return "could not obtain the device address of the built-in scratch array";
+    case -102: return "clearing the scratch failed";
+    default: return "attention backward failed (see cb_attn_bwd return codes)";
+  }
+}
