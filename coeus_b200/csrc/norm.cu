@@ -140,13 +140,17 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const float mean = (live && !RMS) ? mean_in[row] : 0.f;
     const float rstd = live ? rstd_in[row] : 0.f;
     float xh[NORM_NV][8], dyv[NORM_NV][8];
+    uint4 rres[NORM_NV];  // residual gradient, fetched up front so it overlaps the reductions
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int j = 0; j < NORM_NV; ++j) {
       const int vec = tid_in_row + j * 32 * WPR;
+      rres[j] = make_uint4(0u, 0u, 0u, 0u);
       if (live && vec < nv) {
         load8(x + static_cast<size_t>(row) * H + vec * 8, xh[j]);
         load8(dy + static_cast<size_t>(row) * H + vec * 8, dyv[j]);
+        if (dres != nullptr)
+          rres[j] = *reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * H + vec * 8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           xh[j][e] = (xh[j][e] - mean) * rstd;
@@ -168,16 +172,15 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     for (int j = 0; j < NORM_NV; ++j) {
       const int vec = tid_in_row + j * 32 * WPR;
       if (live && vec < nv) {
-        float o[8], r[8];
-        if (dres != nullptr) {
-          load8(dres + static_cast<size_t>(row) * H + vec * 8, r);
-        } else {
+        float o[8];
+        const uint32_t rw[4] = {rres[j].x, rres[j].y, rres[j].z, rres[j].w};
 #pragma unroll
-          for (int e = 0; e < 8; ++e) r[e] = 0.f;
+        for (int e = 0; e < 4; ++e) {
+          const float2 r2 = unpack_bf16x2(rw[e]);
+          o[2 * e] = rstd * (dyv[j][2 * e] * g[j][2 * e] - m1 - xh[j][2 * e] * m2) + r2.x;
+          o[2 * e + 1] =
+              rstd * (dyv[j][2 * e + 1] * g[j][2 * e + 1] - m1 - xh[j][2 * e + 1] * m2) + r2.y;
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          o[e] = rstd * (dyv[j][e] * g[j][e] - m1 - xh[j][e] * m2) + r[e];
         store8(dx + static_cast<size_t>(row) * H + vec * 8, o);
       }
     }
@@ -245,7 +248,7 @@ int launch_bwd(const __nv_bfloat16* DY, const __nv_bfloat16* X, const __nv_bfloa
                const float* mean, const float* rstd, const __nv_bfloat16* DR,
                __nv_bfloat16* DX, float* dgamma, float* dbeta, int T, int H, cudaStream_t st) {
   constexpr int RPB = 4 / WPR;
-  const int blocks = min((T + RPB - 1) / RPB, sm_count() * 2);
+  const int blocks = min((T + RPB - 1) / RPB, sm_count() * 3);
   const size_t sh = RPB > 1 ? 2 * RPB * static_cast<size_t>(H) * sizeof(float) : 0;
   static bool configured = false;
   if (!configured && sh > 0) {

@@ -78,6 +78,7 @@ class Trainer:
         m = self.model
         world = 1 if self.dp is None else self.dp.world
         if self.dp is not None:
+            self.dp.set_grad_scale(1.0 / world)
             self.dp.begin_step()
         m.zero_grad()
         loss = m.forward_loss(ids, targets)

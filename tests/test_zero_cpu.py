@@ -1,0 +1,93 @@
+"""Sharded data parallelism on CPU ranks (Gloo, world size 2): the sharding plan tiles the flat
+buffer exactly, and two ranks with half the batch each reproduce one rank with the whole batch."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from coeus_b200.models.config import DecoderConfig
+from coeus_b200.models.decoder import DecoderLM, ParamLayout
+from coeus_b200.parallel.plans import build_buckets, moment_offsets, shard_table
+from coeus_b200.train.trainer import TrainConfig, Trainer
+
+CFG = DecoderConfig(hidden_dim=128, num_layers=2, num_heads=2, intermediate_dim=256,
+                    vocab_size=512, max_seq_len=64)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_shards_tile_the_flat_buffer(world):
+    layout = ParamLayout(DecoderConfig.transformer_250m())
+    n = layout.padded_total(8 * 1024)
+    buckets = build_buckets(layout, n)
+    covered = sorted((s, e) for r, lst in shard_table(buckets, world).items()
+                     for _, s, e in lst if e > s)
+    pos = 0
+    for s, e in covered:
+        assert s == pos and s % 8 == 0
+        pos = e
+    assert pos == n
+    triggers = [b.trigger for b in buckets]
+    assert triggers[0] == -1 and triggers[-1] == -2
+    assert triggers[1:-2] == list(reversed(range(layout.cfg.num_layers)))
+    for r in range(world):
+        offs, total = moment_offsets(buckets, r, world)
+        assert len(offs) == len(buckets) and total >= sum(
+            b.shard(r, world)[1] - b.shard(r, world)[0] for b in buckets)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, batch, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.parallel.zero import ShardedDataParallel
+    torch.manual_seed(0)
+    model = DecoderLM(CFG, device="cpu", seed=0)
+    dp = ShardedDataParallel(dist.group.WORLD, "cpu")
+    tr = Trainer(model, TrainConfig(learning_rate=1e-2), dp=dp)
+    per = batch.shape[0] // world
+    mine = batch[rank * per:(rank + 1) * per]
+    losses = [float(tr.train_step(mine[:, :-1], mine[:, 1:])) for _ in range(3)]
+    full = dp.gather_master()
+    if rank == 0:
+        out.put((losses, full.clone(), model.p16.float().clone()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_match_one_rank():
+    torch.manual_seed(0)
+    batch = torch.randint(0, CFG.vocab_size, (4, 33))
+    ref = DecoderLM(CFG, device="cpu", seed=0)
+    tr = Trainer(ref, TrainConfig(learning_rate=1e-2))
+    ref_losses = [float(tr.train_step(batch[:, :-1], batch[:, 1:])) for _ in range(3)]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, batch, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    losses, master, p16 = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # The parameters must agree.  The key bias (and through it a few key-projection weights) has
+    # an analytically zero gradient (softmax ignores a shift of all keys); Adam turns its rounding
+    # noise into +-lr steps, so those entries are compared by the fraction that moved apart.
+    for s in ref.layout.specs:
+        sl = slice(s.offset, s.offset + s.numel)
+        d = (master[sl] - ref.p32[sl]).abs()
+        if "qkv" in s.name:
+            assert (d > 1e-3).float().mean() < 0.3, s.name
+        else:
+            assert d.max() < 2e-3, (s.name, d.max())
+            assert (p16[sl] - ref.p16[sl].float()).abs().max() < 2e-2, s.name
+    assert losses[2] < losses[0] and ref_losses[2] < ref_losses[0]
