@@ -88,7 +88,7 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
           float* __restrict__ loss, float* __restrict__ stats, const float* __restrict__ lse_in,
           int T, int V, int ld, int vocab_start, float grad_scale, int mode) {
   __shared__ float red[32];
-  const int nv = V >> 3;
+  const int nv = (V + 7) >> 3;  // the row buffer is padded to a multiple of 8 columns
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
     __nv_bfloat16* row = logits + static_cast<size_t>(t) * ld;
     const int64_t tgt = targets[t];
@@ -100,6 +100,11 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
       for (int vec = threadIdx.x; vec < nv; vec += CE_THREADS) {
         float v[8];
         load8(row + vec * 8, v);
+        if (vec * 8 + 8 > V) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (vec * 8 + e >= V) v[e] = -INFINITY;
+        }
         float lm = v[0];
 #pragma unroll
         for (int e = 1; e < 8; ++e) lm = fmaxf(lm, v[e]);
@@ -136,7 +141,7 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
       for (int e = 0; e < 8; ++e) {
         float p = __expf(v[e] - lse);
         if (vec * 8 + e == local_tgt) p -= 1.0f;
-        v[e] = p * scale;
+        v[e] = (vec * 8 + e < V) ? p * scale : 0.f;
       }
       store8(row + vec * 8, v);
     }
@@ -410,7 +415,7 @@ extern "C" int cb_sinusoid_pe(float* pe, int S, int H, void* stream) {
 extern "C" int cb_cross_entropy(void* logits, const int64_t* targets, float* loss, float* stats,
                                 const float* lse_in, int T, int V, int ld, int vocab_start,
                                 float grad_scale, int mode, void* stream) {
-  if (V % 8 != 0 || ld % 8 != 0 || T <= 0) return -1;
+  if (ld % 8 != 0 || ld < ((V + 7) / 8) * 8 || T <= 0) return -1;
   const int blocks = min(T, sm_count() * 4);
   ce_kernel<<<blocks, CE_THREADS, 0, CB_ST(stream)>>>(static_cast<__nv_bfloat16*>(logits),
                                                      targets, loss, stats, lse_in, T, V, ld,

@@ -1,0 +1,158 @@
+"""Generation engine: batched prefill with the flash-attention kernel, then one decode step per
+token over a paged KV cache (``csrc/decode_attn.cu``).  Implements what the reference's
+``GenerativeModel::generate`` and ``InferenceRequest{tokens, max_length}`` /
+``InferenceResult{predictions}`` only name (src/core/model.rs:138-144,
+src/domain/inference/mod.rs:6-32); the reference itself recomputes the full sequence for every
+token and returns one position."""
+from __future__ import annotations
+
+import math
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+from ..foundation.error import ProcessingError
+from ..models.decoder import DecoderLM
+from ..ops import attention as A
+from ..ops import decode as D
+from ..ops import elementwise as E
+from ..ops import gemm as G
+from ..ops import norm as N
+from .kv_cache import PagedKVCache
+from .sampler import select
+
+
+class InferenceEngine:
+    def __init__(self, model: DecoderLM, max_batch: int = 64, max_len: Optional[int] = None,
+                 decode_splits: int = 1) -> None:
+        self.m = model
+        self.cfg = model.cfg
+        self.max_batch = max_batch
+        self.max_len = max_len or self.cfg.max_seq_len
+        self.decode_splits = decode_splits
+        self.cache: Optional[PagedKVCache] = None
+        self.stats: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ building blocks
+    def _ensure_cache(self, B: int, total: int) -> PagedKVCache:
+        c = self.cache
+        need_pages = (total + D.PAGE - 1) // D.PAGE
+        if c is None or c.page_table.shape[0] < B or c.page_table.shape[1] < need_pages:
+            c = PagedKVCache.for_model(self.cfg, max(B, 1), max(total, D.PAGE), self.m.device)
+            self.cache = c
+        for b in list(c.owned):
+            c.release(b)
+        for b in range(B):
+            c.reserve(b, total)
+        return c
+
+    def _norm(self, x, prefix):
+        m, cfg = self.m, self.cfg
+        rms = cfg.norm == "rmsnorm"
+        y, _, _ = N.norm_fwd(x, m.w[prefix + "_scale"], None if rms else m.w[prefix + "_bias"],
+                             cfg.norm_eps, rms)
+        return y
+
+    def _mlp(self, p: str, n2: torch.Tensor, resid: torch.Tensor) -> torch.Tensor:
+        m, cfg = self.m, self.cfg
+        bias = (lambda n: m.w[p + n]) if cfg.use_bias else (lambda n: None)
+        if cfg.activation == "swiglu":
+            act = E.swiglu_fwd(G.linear_fwd(n2, m.w[p + "ff.gate_up_weights"], None))
+            return G.linear_fwd(act, m.w[p + "ff.down_weights"], None, resid=resid)
+        act = G.linear_fwd(n2, m.w[p + "ff.up_weights"], bias("ff.up_bias"), epi="gelu")
+        return G.linear_fwd(act, m.w[p + "ff.down_weights"], bias("ff.down_bias"), resid=resid)
+
+    def _layers(self, x: torch.Tensor, B: int, S: int, pos0: torch.Tensor, pos0_host: int,
+                cache: PagedKVCache, prefill: bool) -> torch.Tensor:
+        m, cfg = self.m, self.cfg
+        H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
+        n1n, n2n, _ = m.layout.norm_names
+        for l in range(cfg.num_layers):
+            p = f"layers.{l}."
+            bias = (lambda n: m.w[p + n]) if cfg.use_bias else (lambda n: None)
+            n1 = self._norm(x, p + n1n)
+            qkv = G.linear_fwd(n1, m.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"))
+            if cfg.pos == "rope":
+                E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos0_host, theta=cfg.rope_theta)
+            q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+            D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, nh, dh)
+            if prefill:
+                attn, _ = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+            else:
+                attn = D.decode_attention(q, cache.k[l], cache.v[l], cache.page_table,
+                                          self._ctx, nh, dh, splits=self.decode_splits)
+            x_mid = G.linear_fwd(attn, m.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x)
+            x = self._mlp(p, self._norm(x_mid, p + n2n), x_mid)
+        return x
+
+    def _logits(self, x_last: torch.Tensor) -> torch.Tensor:
+        m = self.m
+        xf = self._norm(x_last, m.layout.norm_names[2])
+        w, b_mn = m.output_weight()
+        return G.gemm(xf, w, b_mn=b_mn)
+
+    # ------------------------------------------------------------------ public API
+    def prefill(self, ids: torch.Tensor, total_len: int) -> torch.Tensor:
+        """Runs the prompt ``ids [B, S]`` through the model, fills the cache, returns the logits
+        of the last position ``[B, V]``."""
+        B, S = ids.shape
+        cache = self._ensure_cache(B, total_len)
+        m, cfg = self.m, self.cfg
+        pos0 = torch.zeros(B, dtype=torch.int32, device=m.device)
+        x = E.embed_fwd(ids.reshape(-1), m.w["token_embed"], m._positions(max(S, total_len)), S)
+        x = self._layers(x, B, S, pos0, 0, cache, prefill=True)
+        last = x.view(B, S, -1)[:, -1, :].contiguous()
+        self._pos = S
+        self._ctx = torch.full((B,), S, dtype=torch.int32, device=m.device)
+        return self._logits(last)
+
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Feeds one token per sequence (``[B]`` int64) at the next position; returns ``[B, V]``."""
+        m, cfg = self.m, self.cfg
+        B = tokens.shape[0]
+        pos = self._pos
+        pos0 = torch.full((B,), pos, dtype=torch.int32, device=m.device)
+        pe = m._positions(pos + 1)
+        x = E.embed_fwd(tokens, m.w["token_embed"], pe, 1, pos_offset=pos)
+        self._ctx = torch.full((B,), pos + 1, dtype=torch.int32, device=m.device)
+        x = self._layers(x, B, 1, pos0, pos, self.cache, prefill=False)
+        self._pos = pos + 1
+        return self._logits(x)
+
+    def generate(self, ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
+                 top_k: Optional[int] = None, top_p: Optional[float] = None, seed: int = 0,
+                 eos_id: Optional[int] = None) -> torch.Tensor:
+        """Returns ``[B, S + max_new_tokens]`` token ids (prompt included)."""
+        if ids.dim() == 1:
+            ids = ids[None]
+        B, S = ids.shape
+        total = S + max_new_tokens
+        if total > max(self.max_len, self.cfg.max_seq_len) and self.cfg.pos != "rope":
+            raise ProcessingError.limit_exceeded("sequence length", self.cfg.max_seq_len, total)
+        gen = None
+        if temperature and temperature > 0:
+            gen = torch.Generator(device=ids.device)
+            gen.manual_seed(seed)
+        out = torch.empty((B, total), dtype=torch.int64, device=ids.device)
+        out[:, :S] = ids
+        if max_new_tokens == 0:
+            return out
+        t0 = time.perf_counter()
+        logits = self.prefill(ids, total)
+        if ids.is_cuda:
+            torch.cuda.synchronize(ids.device)
+        t1 = time.perf_counter()
+        nxt = select(logits, temperature, top_k, top_p, gen)
+        out[:, S] = nxt
+        for i in range(1, max_new_tokens):
+            logits = self.decode_step(nxt)
+            nxt = select(logits, temperature, top_k, top_p, gen)
+            out[:, S + i] = nxt
+        if ids.is_cuda:
+            torch.cuda.synchronize(ids.device)
+        t2 = time.perf_counter()
+        self.stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1,
+                      "prefill_tokens_per_s": B * S / max(t1 - t0, 1e-9),
+                      "decode_tokens_per_s": B * max(0, max_new_tokens - 1) / max(t2 - t1, 1e-9)}
+        return out

@@ -161,6 +161,12 @@ class DecoderConfig:
     def head_dim(self) -> int:
         return self.hidden_dim // self.num_heads
 
+    @property
+    def vocab_padded(self) -> int:
+        """Vocabulary rounded up to a multiple of 8: the width of the logits buffer and of the
+        stored output projection (padding columns stay zero and are ignored by the loss)."""
+        return (self.vocab_size + 7) // 8 * 8
+
     @classmethod
     def transformer_250m(cls, max_seq_len: int = 2048) -> "DecoderConfig":
         return Transformer250MConfig.benchmark_250m(max_seq_len).to_decoder()
@@ -190,14 +196,10 @@ class DecoderConfig:
         if self.pos not in ("sinusoidal", "rope", "none"):
             raise ConfigError.invalid("pos", self.pos,
                                       "Positions must be 'sinusoidal', 'rope' or 'none'")
-        if self.head_dim not in (64, 128):
-            raise ConfigError.invalid("hidden_dim",
-                                      f"{self.hidden_dim} (num_heads={self.num_heads})",
-                                      "Head dimension must be 64 or 128 for the attention kernels")
-        if self.hidden_dim % 8 or self.intermediate_dim % 8 or self.vocab_size % 8:
+        if self.hidden_dim % 8 or self.intermediate_dim % 8:
             raise ConfigError.invalid("hidden_dim", self.hidden_dim,
-                                      "hidden_dim, intermediate_dim and vocab_size must be "
-                                      "multiples of 8 (16-byte rows)")
+                                      "hidden_dim and intermediate_dim must be multiples of 8 "
+                                      "(16-byte rows)")
         if self.num_experts and not (0 < self.top_k <= self.num_experts):
             raise ConfigError.invalid("top_k", self.top_k, "top_k must be in [1, num_experts]")
 

@@ -60,9 +60,11 @@ class ParamLayout:
     def __init__(self, cfg: DecoderConfig, tp: int = 1) -> None:
         self.cfg = cfg
         H, I, V, L = cfg.hidden_dim, cfg.intermediate_dim, cfg.vocab_size, cfg.num_layers
+        Vp = cfg.vocab_padded
         ln = cfg.norm == "layernorm"
         s1, s2 = ("ln1", "ln2") if ln else ("norm1", "norm2")
-        specs: List[ParamSpec] = [ParamSpec("token_embed", (V, H), True, "embed")]
+        specs: List[ParamSpec] = [
+            ParamSpec("token_embed", (Vp if cfg.tie_embeddings else V, H), True, "embed")]
         for l in range(L):
             p = f"layers.{l}."
             specs.append(ParamSpec(p + "attn.qkv_weights", (H, 3 * H), True, "weight"))
@@ -79,7 +81,7 @@ class ParamLayout:
                 specs.append(ParamSpec(p + "ff.up_weights", (H, I), True, "weight"))
                 specs.append(ParamSpec(p + "ff.down_weights", (I, H), True, "weight"))
         if not cfg.tie_embeddings:
-            specs.append(ParamSpec("output_proj", (H, V), True, "weight"))
+            specs.append(ParamSpec("output_proj", (H, Vp), True, "weight"))
         vec: List[ParamSpec] = []
         for l in range(L):
             p = f"layers.{l}."
@@ -121,7 +123,10 @@ class DecoderLM:
     """The decoder-only language model on one GPU (or on CPU through the ops' oracle path)."""
 
     def __init__(self, cfg: DecoderConfig, device="cuda", init: str = "normal", seed: int = 0,
-                 pad_multiple: int = 8 * 1024, training: bool = True) -> None:
+                 pad_multiple: int = 8 * 1024, training: bool = True,
+                 dtype: torch.dtype = torch.bfloat16) -> None:
+        """``dtype`` is the working precision of weights and activations: bf16 on the GPU (the
+        kernels accept nothing else); fp32 is allowed on CPU, where the ops run their oracle."""
         cfg.validate()
         if cfg.num_experts:
             raise ProcessingError.unsupported(
@@ -132,7 +137,12 @@ class DecoderLM:
         n = self.layout.padded_total(pad_multiple)
         self.n_flat = n
         self.p32 = torch.zeros(n, dtype=torch.float32, device=self.device)
-        self.p16 = torch.zeros(n, dtype=torch.bfloat16, device=self.device)
+        if self.device.type == "cuda" and cfg.head_dim not in (64, 128):
+            raise ProcessingError.unsupported(
+                f"head dimension {cfg.head_dim} on CUDA", "the attention kernels cover 64 and 128")
+        if self.device.type == "cuda" and dtype != torch.bfloat16:
+            raise ProcessingError.unsupported(f"working dtype {dtype} on CUDA", "kernels are bf16")
+        self.p16 = torch.zeros(n, dtype=dtype, device=self.device)
         self.g32 = torch.zeros(n, dtype=torch.float32, device=self.device) if training else None
         self.training = training
         self.w: Dict[str, torch.Tensor] = {}
@@ -194,6 +204,12 @@ class DecoderLM:
             self.p32.zero_()
         else:
             raise ProcessingError.invalid_input(f"unknown init '{init}'")
+        V = cfg.vocab_size
+        if cfg.vocab_padded != V:   # padding columns / rows of the vocabulary stay zero
+            if cfg.tie_embeddings:
+                self.master["token_embed"][V:].zero_()
+            else:
+                self.master["output_proj"][:, V:].zero_()
         self.sync_working_copy()
 
     def _assign_reference_tensor(self, name: str, value: torch.Tensor) -> None:
@@ -208,7 +224,12 @@ class DecoderLM:
                 fused = name.replace(f"attn.{part}_bias", "attn.qkv_bias")
                 self.master[fused][i * H:(i + 1) * H] = value
                 return
-        self.master[name].copy_(value)
+        dst = self.master[name]
+        if tuple(dst.shape) != tuple(value.shape):   # vocabulary padding
+            dst.zero_()
+            dst[tuple(slice(0, n) for n in value.shape)] = value
+        else:
+            dst.copy_(value)
 
     def sync_working_copy(self) -> None:
         self.p16.copy_(self.p32)
@@ -313,12 +334,12 @@ class DecoderLM:
         ``forward`` returns the last position only, lib.rs:913-918)."""
         B, S = self._check_ids(ids)
         xf = self.forward_hidden(ids)
-        V = self.cfg.vocab_size
+        V, Vp = self.cfg.vocab_size, self.cfg.vocab_padded
         if last_only:
             xf = xf.view(B, S, -1)[:, -1, :].contiguous()
         w, b_mn = self.output_weight()
         logits = G.gemm(xf, w, b_mn=b_mn, max_ctas=self.max_ctas)
-        return logits.view(B, V) if last_only else logits.view(B, S, V)
+        return logits.view(B, Vp)[:, :V] if last_only else logits.view(B, S, Vp)[..., :V]
 
     def forward_loss(self, ids: torch.Tensor, targets: torch.Tensor,
                      grad_scale: Optional[float] = None) -> torch.Tensor:
@@ -330,10 +351,11 @@ class DecoderLM:
         save: dict = {"ids": ids.reshape(-1), "B": B, "S": S}
         xf = self.forward_hidden(ids, save)
         w, b_mn = self.output_weight()
-        logits = G.gemm(xf, w, b_mn=b_mn, out=self._buf("logits", (T, self.cfg.vocab_size)),
+        logits = G.gemm(xf, w, b_mn=b_mn, out=self._buf("logits", (T, self.cfg.vocab_padded)),
                         max_ctas=self.max_ctas)
         scale = grad_scale if grad_scale is not None else 1.0 / T
-        loss_tok = E.cross_entropy_fwd_bwd(logits, targets.reshape(-1), scale)
+        loss_tok = E.cross_entropy_fwd_bwd(logits, targets.reshape(-1), scale,
+                                           vocab=self.cfg.vocab_size)
         save["dlogits"] = logits
         self._saved = save
         loss = torch.zeros(1, dtype=torch.float32, device=self.device)

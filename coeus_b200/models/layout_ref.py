@@ -121,6 +121,10 @@ def named_from_model(model) -> Dict[str, torch.Tensor]:
         elif name.endswith("attn.qkv_bias"):
             for i, part in enumerate(("q", "k", "v")):
                 out[name.replace("qkv_bias", f"{part}_bias")] = t[i * H:(i + 1) * H].contiguous()
+        elif name == "output_proj":
+            out[name] = t[:, :cfg.vocab_size].contiguous()
+        elif name == "token_embed":
+            out[name] = t[:cfg.vocab_size].contiguous()
         else:
             out[name] = t
     return out

@@ -75,11 +75,18 @@ def embed_bwd(ids: torch.Tensor, dy: torch.Tensor, grad_table: torch.Tensor) -> 
 
 # ------------------------------------------------------------------------------ loss
 def cross_entropy_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor,
-                          grad_scale: float) -> torch.Tensor:
+                          grad_scale: float, vocab: Optional[int] = None) -> torch.Tensor:
     """Per-token loss ``[T]`` (fp32); ``logits`` is overwritten by
-    ``(softmax - onehot) * grad_scale``.  A negative target is ignored (loss 0, zero gradient)."""
-    T, V = logits.shape
+    ``(softmax - onehot) * grad_scale``.  A negative target is ignored (loss 0, zero gradient).
+    ``vocab`` (default: the full width) limits the softmax to the first ``vocab`` columns; the
+    padding columns beyond it receive zero gradient."""
+    T, W = logits.shape
+    V = vocab if vocab is not None else W
     if not logits.is_cuda:
+        if V != W:
+            loss = cross_entropy_fwd_bwd(logits[:, :V], targets, grad_scale)
+            logits[:, V:] = 0
+            return loss
         lf = logits.float()
         lse = torch.logsumexp(lf, -1)
         tgt = targets.reshape(-1)
