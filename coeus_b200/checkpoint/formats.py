@@ -117,7 +117,7 @@ def _load_indexed(path: str, index: dict, names=None, slicer=None) -> Dict[str, 
         arr = np.frombuffer(raw, dtype=_NP[t["dtype"]]).reshape(t["shape"])
         if slicer is not None:
             arr = slicer(t["name"], arr)
-        ten = torch.from_numpy(np.ascontiguousarray(arr))
+        ten = torch.from_numpy(np.array(arr, copy=True))
         if t["dtype"] == "BF16":
             ten = ten.view(torch.int16).view(torch.bfloat16)
         out[t["name"]] = ten
@@ -219,6 +219,8 @@ def load_model(path: str, device="cuda", fmt: Optional[str] = None, training: bo
         cfg = config_from_metadata(meta)
     else:
         raise ProcessingError.unsupported(f"Loading file format: {path}")
-    model = DecoderLM(cfg, device=device, init="zeros", training=training)
+    dev = torch.device(device)
+    model = DecoderLM(cfg, device=dev, init="zeros", training=training,
+                      dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
     load_named_into_model(model, named)
     return model, tail

@@ -43,7 +43,12 @@ class Error(Exception):
     def context(self, ctx: "ErrorContext") -> "ContextualError":
         return ContextualError(self, ctx)
 
-    def with_context(self, f: Callable[[], "ErrorContext"]) -> "ContextualError":
+    def with_context(self, f) -> "ContextualError":
+        """``f`` is an operation name, an ``ErrorContext`` or a callable returning one."""
+        if isinstance(f, str):
+            return ContextualError(self, ErrorContext(f))
+        if isinstance(f, ErrorContext):
+            return ContextualError(self, f)
         return ContextualError(self, f())
 
 

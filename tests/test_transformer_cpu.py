@@ -1,0 +1,163 @@
+"""The transformer plugin on CPU: reference unit assertions (plugins/model-transformer/src/lib.rs
+tests), agreement with the native CPU oracle, checkpoint round trips in all three formats, and
+generation with the paged KV cache against full recomputation."""
+import io
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from coeus_b200.checkpoint.formats import load_gguf, load_safetensors
+from coeus_b200.core.model import BasicGenerationConfig
+from coeus_b200.foundation.error import ConfigError, ProcessingError
+from coeus_b200.foundation.types import Version
+from coeus_b200.models.config import DecoderConfig, Transformer250MConfig
+from coeus_b200.ops import elementwise as E
+from coeus_b200.ops import norm as N
+from coeus_b200.plugins.builtin import TransformerModel, TransformerModelPlugin
+from coeus_b200.utils import native
+
+SMALL = Transformer250MConfig(hidden_dim=64, num_layers=2, num_heads=2, intermediate_dim=128,
+                              vocab_size=301, max_seq_len=32)
+
+
+@pytest.fixture(scope="module")
+def model():
+    return TransformerModelPlugin().create_builder(device="cpu").build(SMALL)
+
+
+def _oracle(model, ids, ref_compat=False, all_positions=False):
+    c = model.decoder_config()
+    flat = model._reference_flat().numpy()
+    return native.module().oracle_forward(flat, c.hidden_dim, c.num_layers, c.num_heads,
+                                          c.intermediate_dim, c.vocab_size, c.max_seq_len,
+                                          c.norm_eps, c.use_bias, np.array(ids, dtype=np.int64),
+                                          ref_compat, all_positions)
+
+
+def test_plugin_identity():
+    p = TransformerModelPlugin()
+    assert p.id() == "transformer_model" and p.version() == Version(0, 1, 0)
+    for f in ("model_building", "transformer", "250M_params"):
+        assert p.capabilities().has_feature(f)
+
+
+def test_forward_matches_oracle(model):
+    logits = np.array(model.forward([1, 2, 3]))
+    assert logits.shape == (301,)
+    assert np.abs(logits - _oracle(model, [1, 2, 3])).max() < 1e-5
+    # at S = 1 the reference's whole-buffer layer norm equals the per-token one
+    assert np.abs(np.array(model.forward([7])) - _oracle(model, [7], ref_compat=True)).max() < 1e-5
+    full = model.forward_batch([[1, 2, 3, 4]])[0].float().numpy()
+    assert np.abs(full - _oracle(model, [1, 2, 3, 4], all_positions=True).reshape(4, 301)).max() < 1e-5
+
+
+def test_input_validation(model):
+    with pytest.raises(ProcessingError) as e:
+        model.forward([1, 301])
+    assert "Token ID 301 out of range [0, 300]" in str(e.value)
+    with pytest.raises(ProcessingError) as e:
+        model.forward(list(range(33)))
+    assert "Sequence length 33 out of range [1, 32]" in str(e.value)
+    with pytest.raises(ProcessingError):
+        model.forward([])
+    with pytest.raises(ConfigError):
+        TransformerModelPlugin().create_builder(device="cpu").build(
+            Transformer250MConfig(hidden_dim=65, num_heads=2))
+
+
+def test_parameter_counts(model):
+    assert model.num_parameters() == SMALL.buffer_parameters()
+    c = Transformer250MConfig()
+    assert 160_000_000 < c.buffer_parameters() < 170_000_000
+
+
+def test_sin_init_matches_oracle(model):
+    flat = model._reference_flat().numpy()
+    want = native.module().oracle_sin_init(flat.size, 64)
+    assert np.abs(flat - want).max() < 1e-6
+    big = torch.empty(64)
+    E.sin_init_(big, 768, index_offset=40_000_000)
+    idx = (np.arange(64) + 40_000_000).astype(np.float32)   # `i as f32` loses precision here
+    ref = np.clip(np.sin(idx * np.float32(0.1234567)) * np.float32(np.sqrt(2 / 768)), -0.1, 0.1)
+    assert np.abs(big.numpy() - ref).max() < 1e-6
+
+
+def test_math_unit_values():
+    x = torch.arange(1, 9, dtype=torch.float32)[None]
+    y, _, _ = N.norm_fwd(x, torch.ones(8), torch.zeros(8), 1e-5)
+    assert abs(float(y.mean())) < 1e-5 and abs(float(y.var(unbiased=False)) - 1) < 1e-3
+    g = E.gelu_fwd(torch.tensor([0.0, 1.0, -1.0]))
+    assert g[0] == 0 and g[1] > 0.8 and g[2] < -0.1
+    s = E.softmax_rows(torch.tensor([[1.0, 2.0, 3.0]]))[0]
+    assert abs(float(s.sum()) - 1) < 1e-6 and s[0] < s[1] < s[2]
+    pe = E.sinusoid_table(4, 8, "cpu")
+    assert not torch.equal(pe[0], pe[1]) and pe[0, 0] == 0 and pe[0, 1] == 1
+
+
+def test_rustllm_roundtrip_is_byte_exact(model, tmp_path):
+    b = io.BytesIO()
+    model.write_to(b)
+    data = b.getvalue()
+    assert data[:8] == b"RUSTLLM\x00" and len(data) > 136 + 4 * model.num_parameters()
+    m2 = TransformerModel.read_from(io.BytesIO(data), device="cpu")
+    assert m2.forward([1, 2, 3]) == model.forward([1, 2, 3])
+    b2 = io.BytesIO()
+    m2.write_to(b2)
+    assert b2.getvalue() == data
+    p = tmp_path / "m.rustllm"
+    model.save(str(p))
+    assert p.read_bytes() == data
+    # flip one parameter byte: the checksum must catch it
+    bad = bytearray(data)
+    bad[136 + 40] ^= 0x01
+    with pytest.raises(ProcessingError) as e:
+        TransformerModel.read_from(io.BytesIO(bytes(bad)), device="cpu")
+    assert "Checksum mismatch" in str(e.value)
+
+
+@pytest.mark.parametrize("fmt", ["safetensors", "gguf"])
+def test_named_tensor_formats(model, tmp_path, fmt):
+    p = str(tmp_path / f"m.{fmt}")
+    model.save(p)
+    tensors, meta = (load_safetensors if fmt == "safetensors" else load_gguf)(p)
+    assert meta["hidden_dim"] == "64" and meta["intermediate_dim"] == "128"
+    assert tuple(tensors["token_embed"].shape) == (301, 64)
+    assert tuple(tensors["layers.0.attn.q_weights"].shape) == (64, 64)
+    assert tuple(tensors["layers.1.ff.up_weights"].shape) == (64, 128)
+    assert tuple(tensors["output_proj"].shape) == (64, 301)
+    m2 = TransformerModel.load(p, device="cpu")
+    assert np.abs(np.array(m2.forward([5, 6])) - np.array(model.forward([5, 6]))).max() < 1e-6
+    if fmt == "safetensors":
+        from safetensors.numpy import load_file   # independent reader of the same file
+        other = load_file(p)
+        assert np.array_equal(other["final_ln_scale"], tensors["final_ln_scale"].numpy())
+    else:
+        import gguf
+        r = gguf.GGUFReader(p)
+        names = {t.name for t in r.tensors}
+        assert "token_embed" in names and "layers.0.ff.down_weights" in names
+
+
+def test_generate_with_kv_cache_equals_recomputation(model):
+    out = model.generate([1, 2, 3], BasicGenerationConfig(max_length=9, temperature=0.0))
+    seq = [1, 2, 3]
+    for _ in range(6):
+        seq.append(int(np.argmax(model.forward(seq))))
+    assert out == seq
+    sampled = model.generate([1, 2, 3], BasicGenerationConfig(max_length=8, temperature=0.8,
+                                                              top_k=20, top_p=0.9), seed=1)
+    assert len(sampled) == 8 and sampled[:3] == [1, 2, 3]
+
+
+def test_llama_style_config_on_cpu():
+    cfg = DecoderConfig(hidden_dim=64, num_layers=2, num_heads=2, intermediate_dim=96,
+                        vocab_size=128, max_seq_len=32, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope")
+    m = TransformerModelPlugin().create_builder(device="cpu", init="normal").build(cfg)
+    out = m.generate([3, 4, 5], BasicGenerationConfig(max_length=8, temperature=0.0))
+    seq = [3, 4, 5]
+    for _ in range(5):
+        seq.append(int(np.argmax(m.forward(seq))))
+    assert out == seq
