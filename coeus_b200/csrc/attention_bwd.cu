@@ -10,8 +10,10 @@
 // delta_i = rowsum(dO_i o O_i) comes from a small pre-kernel; a post-kernel scales and casts dQ.
 //   warp 0      TMA producer (K_j, V_j once; Q_i, dO_i through a 2-stage ring)
 //   warp 1      MMA issuer
-//   warps 2..5  softmax / dS (one thread per K/V row)
-//   warps 6..9  dQ drain (TMEM -> red.global.add) and, with warps 2..5, the dK/dV epilogue
+//   warps 2..9   softmax / dS: two threads per K/V row, each taking half of the query columns
+//                (warps 2..5 the first half, 6..9 the second); afterwards the dV (first group)
+//                and dK (second group) epilogue
+//   warps 10..13 dQ drain (TMEM -> red.global.add)
 #include <algorithm>
 
 #include "common.cuh"
@@ -24,7 +26,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
 int sm_count();
 
 constexpr int ATB_BKV = 128;
-constexpr int ATB_THREADS = 320;
+constexpr int ATB_THREADS = 448;
 
 struct AttnBwdArgs {
   int B, S, nh;
@@ -150,12 +152,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(bar(3 + s), 1);
     }
     mbar_init(bar(5), 1);
-    mbar_init(bar(6), 128);
+    mbar_init(bar(6), 256);
     mbar_init(bar(7), 1);
     mbar_init(bar(8), 1);
     mbar_init(bar(9), 128);
     mbar_init(bar(10), 1);
-    mbar_init(bar(11), 128);
+    mbar_init(bar(11), 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -296,12 +298,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) umma_commit(bar(10));
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ---------------------------------------------------------------- softmax / dS
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;   // which half of the query columns this thread covers
     const int r = quarter * 32 + lane;  // K/V row within the tile
     const int kv_idx = kv0 + r;
-    const int tid = threadIdx.x - 64;   // 0..127
+    const int tid = threadIdx.x - 64;   // 0..255
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const size_t stat_base = (static_cast<size_t>(b) * p.nh + h) * p.S;
     bool ok = true;
@@ -327,7 +330,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool diag = p.causal && (kv0 + BKV - 1 > q0);
       const bool row_dead = kv_idx >= p.S;
 #pragma unroll 1
-      for (int c = 0; c < BQ / 32; ++c) {
+      for (int c = half * (BQ / 64); c < (half + 1) * (BQ / 64); ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(lane_addr + Cfg::ST_COL + c * 32, sv);
         tmem_ld_32x32b_x32(lane_addr + Cfg::DPT_COL + c * 32, dv);
@@ -374,8 +377,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const bool row_ok = kv_idx < p.S;
       const size_t orow = (static_cast<size_t>(row0) + kv_idx) * p.ldd + static_cast<size_t>(h) * DH;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;   // first group writes dV, second group dK
         __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + orow;
         const float mul = which == 0 ? 1.0f : p.scale;
         const int col = which == 0 ? Cfg::DV_COL : Cfg::DK_COL;

@@ -214,21 +214,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = j * BKV;
       const bool need_mask = (p.causal && kv0 + BKV - 1 > q0) || (kv0 + BKV > p.S);
       const int kv_limit = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);  // last visible kv index
-      // pass 1: row maximum of the scaled scores
+      // The whole score row goes to registers with back-to-back TMEM loads and one wait, so the
+      // load latency is paid once per tile and S is read from tensor memory only once.
+      uint32_t v[BKV];
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) tmem_ld_32x32b_x32(lane_addr + Cfg::S_COL + c * 32, v + c * 32);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + Cfg::S_COL + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (kv0 + c * 32 + e <= kv_limit) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
+        for (int e = 0; e < BKV; ++e)
+          if (kv0 + e <= kv_limit) mx = fmaxf(mx, __uint_as_float(v[e]));
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        }
+        for (int e = 0; e < BKV; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
       }
       mx *= p.scale_log2;  // scale > 0, so max commutes with it
       const float m_new = fmaxf(m_used, mx);
@@ -258,17 +257,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       if (grow) m_used = (m_new == -INFINITY) ? 0.f : m_new;
-      // pass 2: P = exp2(s * scale - m), row sum, bf16 P into swizzled shared memory
-#pragma unroll 1
+      // P = exp2(s * scale - m), row sum, bf16 P into swizzled shared memory
+#pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + Cfg::S_COL + c * 32, v);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(__uint_as_float(v[e]) * p.scale_log2 - m_used);
-          float p1 = fast_exp2(__uint_as_float(v[e + 1]) * p.scale_log2 - m_used);
+          float p0 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e]), p.scale_log2, -m_used));
+          float p1 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e + 1]), p.scale_log2, -m_used));
           if (need_mask) {
             if (kv0 + c * 32 + e > kv_limit) p0 = 0.f;
             if (kv0 + c * 32 + e + 1 > kv_limit) p1 = 0.f;

@@ -2,7 +2,8 @@
 // staged by TMA into 128-byte-swizzled shared memory), persistent and warp-specialised:
 //   warp 0      TMA producer (one lane)
 //   warp 1      MMA issuer   (one lane)
-//   warps 2..5  epilogue: TMEM -> registers -> fused epilogue -> global
+//   warps 2..5  epilogue: TMEM -> registers -> fused epilogue -> swizzled shared memory -> TMA
+//               store (bf16 outputs; fp32 and atomic outputs are stored directly)
 // The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main
 // loop of tile i+1.  Both operands may be K-major or MN-major, which covers the three GEMMs
 // of a linear layer whose weight is stored [in, out] row-major (the layout of math::matmul in
@@ -25,7 +26,7 @@ constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 
 enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_SWIGLU_BWD = 3 };
-enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2, OUT_DISCARD = 3 };
 
 struct GemmArgs {
   int M, N, K;
@@ -41,8 +42,11 @@ struct GemmArgs {
   int out_mode;
   float alpha;
   int ksplit;
+  int tma_store;                // bf16 outputs leave through shared memory and TMA stores
   int* status;
 };
+
+constexpr int GEMM_STAGING_BYTES = 32768;   // two [128 rows x 64 bf16] swizzled store tiles
 
 template <int BN>
 struct GemmCfg {
@@ -51,22 +55,110 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int OFF_STAGING = STAGES * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_STAGING + GEMM_STAGING_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 1024 /*align*/ + 256 /*barriers*/;
 };
+
+// Fused epilogue math on 32 consecutive columns of one output row.  `u` receives the
+// pre-activation when EPI_GELU keeps it.
+__device__ __forceinline__ void epilogue_math(const GemmArgs& p, float* v, float* u, int row,
+                                              int col0, int ncols, bool row_ok) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(bw[j]);
+          v[g * 8 + 2 * j] += f.x;
+          v[g * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
+  }
+  if (p.epi == EPI_GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      u[j] = v[j];
+      v[j] = gelu_tanh(v[j]);
+    }
+  } else if (p.epi == EPI_DGELU && row_ok) {
+    const __nv_bfloat16* ap = p.aux_in + static_cast<size_t>(row) * p.ldaux + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        const uint4 a = *reinterpret_cast<const uint4*>(ap + g * 8);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(aw[j]);
+          v[g * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+          v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+        }
+      }
+    }
+  }
+  if (p.resid != nullptr && row_ok) {
+    const __nv_bfloat16* rp = p.resid + static_cast<size_t>(row) * p.ldr + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        const uint4 a = *reinterpret_cast<const uint4*>(rp + g * 8);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(aw[j]);
+          v[g * 8 + 2 * j] += f.x;
+          v[g * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  return o;
+}
+
+// 32 bf16 columns of row r into a 128-byte-swizzled [128 x 64] store tile; `half` selects
+// columns 0..31 or 32..63 of the tile.
+__device__ __forceinline__ void stage_row(uint32_t tile, int r, int half, const float* v) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint4 o = pack8(v + g * 8);
+    const uint32_t chunk = static_cast<uint32_t>(half * 4 + g);
+    const uint32_t addr = tile + r * 128 + ((chunk ^ (r & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x), "r"(o.y),
+                 "r"(o.z), "r"(o.w) : "memory");
+  }
+}
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux,
                  const GemmArgs p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + Cfg::OFF_BAR);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile int* epi_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  const uint32_t s_staging = smem_base + Cfg::OFF_STAGING;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -86,9 +178,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tempty_bar(a), 128);
     }
     *abort_flag = 0;
+    *epi_ok = 1;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tma_store) tma_prefetch_desc(&tmD);
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
@@ -210,131 +304,110 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool leader = (warp == 2 && lane == 0);
+    const bool aux_staged = p.tma_store && p.epi == EPI_GELU && p.aux_out != nullptr;
     int it = 0;
-    bool ok = true;
-    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+    uint32_t step = 0;  // running count of staged 64-column steps (selects the store tile)
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
       const int tile = w / p.ksplit;
       const int m0 = (tile / tiles_n) * GEMM_BM;
       const int n0 = (tile % tiles_n) * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {  // warp-uniform: tcgen05.ld needs the whole warp
-        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 300);
-        ok = false;
-        break;
+      // The four epilogue warps must take the same decision: they meet at named barriers below.
+      if (!__all_sync(0xffffffffu, got) && lane == 0) {
+        *epi_ok = 0;
+        record_status(p.status, ST_WAIT_TIMEOUT, 300);
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*epi_ok == 0) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
+      const int r_in_tile = q * 32 + lane;
+      const int row = m0 + r_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (p.tma_store) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const int ncols = min(32, p.N - col0);  // multiple of 8 (N % 8 == 0)
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g * 8 < ncols) {
-              const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
-              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = unpack_bf16x2(bw[j]);
-                v[g * 8 + 2 * j] += f.x;
-                v[g * 8 + 2 * j + 1] += f.y;
-              }
-            }
+        for (int qs = 0; qs < BN / 64; ++qs) {
+          const int colq = n0 + qs * 64;
+          if (colq >= p.N) break;
+          const uint32_t buf = aux_staged ? 0u : (step & 1u);
+          const uint32_t s_out = s_staging + buf * 16384;
+          const uint32_t s_aux = s_staging + 16384;
+          // the store that last read this tile must be done with it
+          if (leader) {
+            if (aux_staged) tma_store_wait_read_all();
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int col0 = colq + h * 32;
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + qs * 64 + h * 32, r);
+            tmem_ld_wait();
+            float v[32], u[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            const int ncols = max(0, min(32, p.N - col0));
+            epilogue_math(p, v, u, row, col0, ncols, row_ok);
+            stage_row(s_out, r_in_tile, h, v);
+            if (aux_staged) stage_row(s_aux, r_in_tile, h, u);
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (leader) {
+            tma_store_2d(&tmD, s_out, colq, m0);
+            if (aux_staged) tma_store_2d(&tmAux, s_aux, colq, m0);
+            tma_store_commit();
+          }
+          ++step;
         }
-        if (p.epi == EPI_GELU) {
-          if (p.aux_out != nullptr) {
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          float v[32], u[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          const int ncols = min(32, p.N - col0);  // multiple of 8 (N % 8 == 0)
+          epilogue_math(p, v, u, row, col0, ncols, true);
+          if (p.epi == EPI_GELU && p.aux_out != nullptr) {
             __nv_bfloat16* ap = p.aux_out + static_cast<size_t>(row) * p.ldaux + col0;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (g * 8 < ncols) {
-                uint4 o;
-                o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-                o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-                o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-                o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
-                *reinterpret_cast<uint4*>(ap + g * 8) = o;
+            for (int g = 0; g < 4; ++g)
+              if (g * 8 < ncols) *reinterpret_cast<uint4*>(ap + g * 8) = pack8(u + g * 8);
+          }
+          if (p.out_mode == OUT_BF16) {
+            __nv_bfloat16* dp =
+                reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              if (g * 8 < ncols) *reinterpret_cast<uint4*>(dp + g * 8) = pack8(v + g * 8);
+          } else if (p.out_mode == OUT_F32) {
+            float* dp = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (g * 4 < ncols)
+                *reinterpret_cast<float4*>(dp + g * 4) =
+                    make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+            }
+          } else if (p.out_mode == OUT_F32_ATOMIC) {
+            float* dp = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (g * 4 < ncols) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                             ::"l"(dp + g * 4), "f"(v[g * 4]), "f"(v[g * 4 + 1]),
+                               "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                             : "memory");
               }
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-        } else if (p.epi == EPI_DGELU) {
-          const __nv_bfloat16* ap = p.aux_in + static_cast<size_t>(row) * p.ldaux + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g * 8 < ncols) {
-              const uint4 a = *reinterpret_cast<const uint4*>(ap + g * 8);
-              const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = unpack_bf16x2(aw[j]);
-                v[g * 8 + 2 * j] *= gelu_tanh_grad(f.x);
-                v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
-              }
-            }
-          }
-        }
-        if (p.resid != nullptr) {
-          const __nv_bfloat16* rp = p.resid + static_cast<size_t>(row) * p.ldr + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g * 8 < ncols) {
-              const uint4 a = *reinterpret_cast<const uint4*>(rp + g * 8);
-              const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = unpack_bf16x2(aw[j]);
-                v[g * 8 + 2 * j] += f.x;
-                v[g * 8 + 2 * j + 1] += f.y;
-              }
-            }
-          }
-        }
-        if (p.out_mode == OUT_BF16) {
-          __nv_bfloat16* dp =
-              reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g * 8 < ncols) {
-              uint4 o;
-              o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-              o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-              o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-              o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
-              *reinterpret_cast<uint4*>(dp + g * 8) = o;
-            }
-          }
-        } else if (p.out_mode == OUT_F32) {
-          float* dp = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (g * 4 < ncols)
-              *reinterpret_cast<float4*>(dp + g * 4) =
-                  make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-          }
-        } else {
-          float* dp = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (g * 4 < ncols) {
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                           ::"l"(dp + g * 4), "f"(v[g * 4]), "f"(v[g * 4 + 1]),
-                             "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
-                           : "memory");
             }
           }
         }
@@ -342,6 +415,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));
     }
+    // every bulk store must have finished (reading shared memory and writing global memory)
+    if (leader && p.tma_store) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -394,8 +469,9 @@ int sm_count() {
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
-                       int max_ctas, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                       const CUtensorMap& taux, const GemmArgs& args, int max_ctas,
+                       cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
@@ -409,7 +485,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, td, taux, args);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -450,7 +526,20 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   else
     rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, 64);
   if (rc != 0) return rc - 40;
+  // bf16 results (and the kept pre-activation) go out through swizzled shared memory and TMA
+  // stores whenever the output rows are 16-byte aligned; fp32 / atomic outputs are stored directly
+  CUtensorMap td = ta, taux = ta;
+  int tma_store = 0;
+  if (out_mode == OUT_BF16 && (reinterpret_cast<uintptr_t>(D) & 15u) == 0 && (ldd % 8) == 0) {
+    tma_store = make_tmap_bf16_2d(&td, D, N, M, ldd, 64, GEMM_BM) == 0 ? 1 : 0;
+    if (tma_store && epi == EPI_GELU && aux_out != nullptr) {
+      if ((reinterpret_cast<uintptr_t>(aux_out) & 15u) != 0 || (ldaux % 8) != 0 ||
+          make_tmap_bf16_2d(&taux, aux_out, N, M, ldaux, 64, GEMM_BM) != 0)
+        tma_store = 0;
+    }
+  }
   GemmArgs g;
+  g.tma_store = tma_store;
   g.M = M; g.N = N; g.K = K;
   g.D = D; g.ldd = ldd;
   g.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -463,10 +552,10 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define CB_DISPATCH(BN_)                                                            \
   do {                                                                              \
-    if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(ta, tb, g, max_ctas, st); \
-    if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(ta, tb, g, max_ctas, st);   \
-    if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(ta, tb, g, max_ctas, st);   \
-    return launch_gemm<BN_, true, true>(ta, tb, g, max_ctas, st);                       \
+    if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(ta, tb, td, taux, g, max_ctas, st); \
+    if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(ta, tb, td, taux, g, max_ctas, st);   \
+    if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(ta, tb, td, taux, g, max_ctas, st);   \
+    return launch_gemm<BN_, true, true>(ta, tb, td, taux, g, max_ctas, st);                       \
   } while (0)
   if (bn == 256) CB_DISPATCH(256);
   CB_DISPATCH(128);
