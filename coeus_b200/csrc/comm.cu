@@ -150,6 +150,36 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, float* __restrict__ p32,
   }
 }
 
+// out[r, c] = sum_s slots[s][r, c] (+ resid[r, c]) : the owner side of the reduce-scatter that
+// the GEMM epilogues push into (bf16 slots, fp32 accumulation in slot order, so every run adds
+// in the same order).  slots is one buffer of `tp` consecutive [rows, ld] matrices.
+__global__ void reduce_slots_kernel(const __nv_bfloat16* __restrict__ slots, int tp, int rows,
+                                    int cols, int ld, const __nv_bfloat16* __restrict__ resid,
+                                    int ldr, __nv_bfloat16* __restrict__ out, int ldo) {
+  const int nv = cols >> 3;
+  const size_t total = static_cast<size_t>(rows) * nv;
+  const size_t slot_stride = static_cast<size_t>(rows) * ld;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = i / nv;
+    const int vec = static_cast<int>(i % nv);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < tp; ++s) {
+      float v[8];
+      load8(slots + s * slot_stride + r * ld + vec * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    if (resid != nullptr) {
+      float v[8];
+      load8(resid + r * ldr + vec * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    store8(out + r * ldo + vec * 8, acc);
+  }
+}
+
 // Plain peer copy kernel: dst[i] = src[i] for 16-byte vectors (src may be a peer pointer).
 __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                  size_t nvec) {
@@ -228,6 +258,17 @@ extern "C" int cb_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, f
   rs_adamw_ag_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       g, p, p32, m, v, gstart, gend, moff, decay_end, a, n, static_cast<const uint64_t*>(flags),
       slot, expect, limit_ns, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int cb_reduce_slots(const void* slots, int tp, int rows, int cols, int ld,
+                               const void* resid, int ldr, void* out, int ldo, void* stream) {
+  if (cols % 8 != 0 || ld % 8 != 0 || ldo % 8 != 0) return -1;
+  const size_t work = static_cast<size_t>(rows) * (cols / 8);
+  const int blocks = static_cast<int>(min(static_cast<size_t>(sm_count()) * 8, (work + 255) / 256));
+  reduce_slots_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(slots), tp, rows, cols, ld,
+      static_cast<const __nv_bfloat16*>(resid), ldr, static_cast<__nv_bfloat16*>(out), ldo);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

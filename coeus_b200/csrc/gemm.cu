@@ -16,6 +16,8 @@
 // +residual, bf16 / fp32 / fp32-atomic-add output.
 #include <cudaTypedefs.h>
 
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -24,6 +26,8 @@ namespace cb {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int MAX_TP = 8;
+enum : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
 
 enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_SWIGLU_BWD = 3 };
 enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2, OUT_DISCARD = 3 };
@@ -44,6 +48,19 @@ struct GemmArgs {
   int ksplit;
   int tma_store;                // bf16 outputs leave through shared memory and TMA stores
   int* status;
+  // ---- fused collectives over peer memory (COMM template parameter)
+  int tp, rank;                 // ranks of the tensor-parallel group, this rank
+  int tiles_per_shard;          // 128-row tiles per rank's sequence shard
+  const void* ag_src[MAX_TP];   // COMM_AG: every rank's copy of the gathered operand (peer mapped)
+  __nv_bfloat16* ag_dst;        //          this rank's copy (the A operand of the GEMM)
+  int ag_ld;                    //          its row pitch (elements)
+  uint32_t* ag_flags;           //          local per-tile arrival epochs
+  uint32_t ag_epoch;
+  const uint64_t* peer_flags;   //          local signal pad: peer_flags[s] >= peer_expect once
+  uint64_t peer_expect;         //          rank s has written its shard
+  uint64_t wait_limit_ns;
+  void* rs_dst[MAX_TP];         // COMM_RS: rank s's receive slot for this rank's partial rows
+  int rs_ld;
 };
 
 constexpr int GEMM_STAGING_BYTES = 32768;   // two [128 rows x 64 bf16] swizzled store tiles
@@ -143,8 +160,27 @@ __device__ __forceinline__ void stage_row(uint32_t tile, int r, int half, const 
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t ld_acquire_sys_u64_g(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// COMM_AG: the A operand is the all-gather of per-rank row shards.  Two extra warps of every
+// CTA pull the other ranks' shards over NVLink (plain peer loads) into this GPU's own copy, 128
+// rows at a time, and publish a per-tile flag; the TMA producer waits for the flag of a remote
+// tile and then loads it from LOCAL memory.  Tiles are visited local shard first, then the
+// peers in ring order, which is also the order of the pulls.
+// COMM_RS: the result is reduce-scattered by rows.  The epilogue pushes each tile of partial
+// sums straight into the owner rank's receive slot (coalesced peer stores from the staging
+// tile); the owner adds the slots in its next kernel.
+template <int BN, bool A_MN, bool B_MN, int COMM>
+__global__ void __launch_bounds__(COMM == COMM_AG ? GEMM_THREADS + 64 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux,
                  const GemmArgs p) {
@@ -179,6 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     *abort_flag = 0;
     *epi_ok = 1;
+    *(epi_ok + 1) = 1;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -198,6 +235,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
   const int kb_per = (kblocks + p.ksplit - 1) / p.ksplit;
   const int total = tiles_m * tiles_n * p.ksplit;
+  // With a fused collective the m-blocks are visited starting at this rank's own shard.
+  auto m_block_of = [&](int tile) {
+    const int mi = tile / tiles_n;
+    if constexpr (COMM == COMM_NONE) return mi;
+    else return (mi + p.rank * p.tiles_per_shard) % tiles_m;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -209,10 +252,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
         const int split = w % p.ksplit;
         const int tile = w / p.ksplit;
-        const int m0 = (tile / tiles_n) * GEMM_BM;
+        const int m_blk = m_block_of(tile);
+        const int m0 = m_blk * GEMM_BM;
         const int n0 = (tile % tiles_n) * BN;
         const int kb0 = split * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
+        if constexpr (COMM == COMM_AG) {
+          if (m_blk / p.tiles_per_shard != p.rank) {  // rows that come from a peer
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t n = 0;
+            while (ld_acquire_gpu_u32(p.ag_flags + m_blk) != p.ag_epoch) {
+              if ((++n & 15u) == 0u &&
+                  (*abort_flag || globaltimer_ns() - t0 > p.wait_limit_ns)) {
+                *abort_flag = 1u;
+                record_status(p.status, ST_COMM_TIMEOUT, m_blk);
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async.global;" ::: "memory");  // generic writes -> TMA reads
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             record_status(p.status, ST_WAIT_TIMEOUT, 100);
@@ -301,6 +362,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     __syncwarp();
+  } else if (COMM == COMM_AG && warp >= 6) {
+    // ------------------------------------------------------------------ all-gather pull warps
+    const int ct = threadIdx.x - GEMM_THREADS;  // 0..63
+    volatile int* comm_ok = epi_ok + 1;
+    const int n_remote = (p.tp - 1) * p.tiles_per_shard;
+    const size_t row_bytes = static_cast<size_t>(p.K) * 2;  // gathered rows are K elements wide
+    for (int c = blockIdx.x; c < n_remote; c += gridDim.x) {
+      const int dist = c / p.tiles_per_shard + 1;
+      const int src = (p.rank + dist) % p.tp;
+      const int m_blk = src * p.tiles_per_shard + c % p.tiles_per_shard;
+      if (ct == 0) {
+        int good = 1;
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t n = 0;
+        while (ld_acquire_sys_u64_g(p.peer_flags + src) < p.peer_expect) {
+          if ((++n & 15u) == 0u &&
+              (*abort_flag || globaltimer_ns() - t0 > p.wait_limit_ns)) {
+            *abort_flag = 1u;
+            record_status(p.status, ST_COMM_TIMEOUT, src);
+            good = 0;
+            break;
+          }
+        }
+        *comm_ok = good;
+      }
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+      if (*comm_ok == 0) break;
+      const int rows = min(GEMM_BM, p.M - m_blk * GEMM_BM);
+      const char* sbase = static_cast<const char*>(p.ag_src[src]) +
+                          static_cast<size_t>(m_blk) * GEMM_BM * p.ag_ld * 2;
+      char* dbase = reinterpret_cast<char*>(p.ag_dst) +
+                    static_cast<size_t>(m_blk) * GEMM_BM * p.ag_ld * 2;
+      const int vec_per_row = static_cast<int>(row_bytes / 16);
+      const int total_vec = rows * vec_per_row;
+      for (int v0 = ct; v0 < total_vec; v0 += 64 * 8) {
+        uint4 buf[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int v = v0 + u * 64;
+          if (v < total_vec) {
+            const size_t off = static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
+                               static_cast<size_t>(v % vec_per_row) * 16;
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(buf[u].x), "=r"(buf[u].y), "=r"(buf[u].z), "=r"(buf[u].w)
+                         : "l"(sbase + off) : "memory");
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int v = v0 + u * 64;
+          if (v < total_vec) {
+            const size_t off = static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
+                               static_cast<size_t>(v % vec_per_row) * 16;
+            *reinterpret_cast<uint4*>(dbase + off) = buf[u];
+          }
+        }
+      }
+      __threadfence();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+      if (ct == 0)
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(p.ag_epoch)
+                     : "memory");
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -310,7 +435,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t step = 0;  // running count of staged 64-column steps (selects the store tile)
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
       const int tile = w / p.ksplit;
-      const int m0 = (tile / tiles_n) * GEMM_BM;
+      const int m_blk = m_block_of(tile);
+      const int m0 = m_blk * GEMM_BM;
       const int n0 = (tile % tiles_n) * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
@@ -336,9 +462,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t s_out = s_staging + buf * 16384;
           const uint32_t s_aux = s_staging + 16384;
           // the store that last read this tile must be done with it
-          if (leader) {
-            if (aux_staged) tma_store_wait_read_all();
-            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          if constexpr (COMM != COMM_RS) {
+            if (leader) {
+              if (aux_staged) tma_store_wait_read_all();
+              else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
@@ -355,12 +483,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             stage_row(s_out, r_in_tile, h, v);
             if (aux_staged) stage_row(s_aux, r_in_tile, h, u);
           }
-          fence_proxy_async_smem();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (leader) {
-            tma_store_2d(&tmD, s_out, colq, m0);
-            if (aux_staged) tma_store_2d(&tmAux, s_aux, colq, m0);
-            tma_store_commit();
+          if constexpr (COMM == COMM_RS) {
+            // push the [128 x 64] tile of partial sums into the owner's receive slot: eight
+            // lanes write one 128-byte row segment, so every peer store is a full line
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int owner = m_blk / p.tiles_per_shard;
+            const int lrow0 = (m_blk % p.tiles_per_shard) * GEMM_BM;
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.rs_dst[owner]);
+            const int t = threadIdx.x - 64;          // 0..127 over the epilogue warps
+            const int chunk = t & 7;
+            const int col = colq + chunk * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 16 + (t >> 3);
+              uint4 val;
+              const uint32_t addr = s_out + rr * 128 + ((static_cast<uint32_t>(chunk) ^ (rr & 7)) << 4);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
+              if (m0 + rr < p.M && col < p.N)
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(lrow0 + rr) * p.rs_ld + col) = val;
+            }
+          } else {
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (leader) {
+              tma_store_2d(&tmD, s_out, colq, m0);
+              if (aux_staged) tma_store_2d(&tmAux, s_aux, colq, m0);
+              tma_store_commit();
+            }
           }
           ++step;
         }
@@ -468,13 +618,13 @@ int sm_count() {
   return n;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                        const CUtensorMap& taux, const GemmArgs& args, int max_ctas,
                        cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, COMM>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
@@ -485,7 +635,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, td, taux, args);
+  kern<<<grid, COMM == COMM_AG ? GEMM_THREADS + 64 : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
+      ta, tb, td, taux, args);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -539,7 +690,10 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
     }
   }
   GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
   g.tma_store = tma_store;
+  g.tp = 1;
+  g.tiles_per_shard = 1;
   g.M = M; g.N = N; g.K = K;
   g.D = D; g.ldd = ldd;
   g.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -560,4 +714,73 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (bn == 256) CB_DISPATCH(256);
   CB_DISPATCH(128);
 #undef CB_DISPATCH
+}
+
+// ------------------------------------------------------------------------------------------
+// Fused tensor-parallel GEMMs.  `comm` selects:
+//   1 (all-gather -> GEMM): A is this rank's [tp * rows_per_shard, K] gathered operand, of which
+//     only rows [rank * rows_per_shard, ...) are valid on entry; ag_src[s] is rank s's copy of the
+//     same buffer (peer mapped).  Weights: B as in cb_gemm_bf16.  Output: plain D[M, N].
+//   2 (GEMM -> reduce-scatter): D is not written locally; rs_dst[s] is the receive slot on rank
+//     s (already offset to this rank's slot), [rows_per_shard, N] with pitch rs_ld.
+struct CbCommArgs {
+  int comm, tp, rank, rows_per_shard;
+  const void* ag_src[8];
+  void* ag_flags;
+  unsigned int ag_epoch;
+  const void* peer_flags;
+  unsigned long long peer_expect;
+  unsigned long long wait_limit_ns;
+  void* rs_dst[8];
+  int rs_ld;
+};
+
+extern "C" int cb_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int K,
+                                  int lda, int ldb, int ldd, int b_mn, const void* bias, int bn,
+                                  const CbCommArgs* c, int* status, int max_ctas, void* stream) {
+  using namespace cb;
+  if (c == nullptr || (c->comm != COMM_AG && c->comm != COMM_RS)) return -50;
+  if (c->tp < 1 || c->tp > MAX_TP || c->rows_per_shard % GEMM_BM != 0) return -51;
+  if (M != c->tp * c->rows_per_shard) return -52;
+  if ((N % 8) != 0 || (K % 8) != 0) return -21;
+  if (bn != 128 && bn != 256) return -22;
+  CUtensorMap ta, tb, td;
+  if (make_tmap_bf16_2d(&ta, A, K, M, lda, 64, GEMM_BM) != 0) return -31;
+  int rc = b_mn == 0 ? make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, bn)
+                     : make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, 64);
+  if (rc != 0) return rc - 40;
+  td = ta;
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.M = M; g.N = N; g.K = K;
+  g.D = D; g.ldd = ldd;
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
+  g.epi = EPI_NONE; g.out_mode = OUT_BF16; g.alpha = 1.0f; g.ksplit = 1; g.status = status;
+  g.tp = c->tp; g.rank = c->rank; g.tiles_per_shard = c->rows_per_shard / GEMM_BM;
+  g.wait_limit_ns = c->wait_limit_ns;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (c->comm == COMM_AG) {
+    if (make_tmap_bf16_2d(&td, D, N, M, ldd, 64, GEMM_BM) != 0) return -32;
+    g.tma_store = 1;
+    for (int i = 0; i < c->tp; ++i) g.ag_src[i] = c->ag_src[i];
+    g.ag_dst = static_cast<__nv_bfloat16*>(const_cast<void*>(A));
+    g.ag_ld = lda;
+    g.ag_flags = static_cast<uint32_t*>(c->ag_flags);
+    g.ag_epoch = c->ag_epoch;
+    g.peer_flags = static_cast<const uint64_t*>(c->peer_flags);
+    g.peer_expect = c->peer_expect;
+    if (bn == 256)
+      return b_mn ? launch_gemm<256, false, true, COMM_AG>(ta, tb, td, td, g, max_ctas, st)
+                  : launch_gemm<256, false, false, COMM_AG>(ta, tb, td, td, g, max_ctas, st);
+    return b_mn ? launch_gemm<128, false, true, COMM_AG>(ta, tb, td, td, g, max_ctas, st)
+                : launch_gemm<128, false, false, COMM_AG>(ta, tb, td, td, g, max_ctas, st);
+  }
+  g.tma_store = 1;   // staged epilogue; the tile leaves through peer stores instead of TMA
+  for (int i = 0; i < c->tp; ++i) g.rs_dst[i] = c->rs_dst[i];
+  g.rs_ld = c->rs_ld;
+  if (bn == 256)
+    return b_mn ? launch_gemm<256, false, true, COMM_RS>(ta, tb, td, td, g, max_ctas, st)
+                : launch_gemm<256, false, false, COMM_RS>(ta, tb, td, td, g, max_ctas, st);
+  return b_mn ? launch_gemm<128, false, true, COMM_RS>(ta, tb, td, td, g, max_ctas, st)
+              : launch_gemm<128, false, false, COMM_RS>(ta, tb, td, td, g, max_ctas, st);
 }
