@@ -106,20 +106,22 @@ class TensorParallel:
 
     # ------------------------------------------------------------------ all-gather -> GEMM
     def ag_gemm(self, name: str, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-        """``y[T, N] = gather(x)[T, K] @ w[K, N] (+ bias)`` for the site's gather buffer whose own
-        rows were just written.  Returns ``(y, gathered x)``."""
+                out: Optional[torch.Tensor] = None, b_mn: bool = True
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``y[T, N] = gather(x)[T, K] @ w (+ bias)`` for the site's gather buffer whose own rows
+        were just written; ``w`` is ``[K, N]`` (``b_mn=True``) or ``[N, K]`` (``b_mn=False``, the
+        transposed use in the backward pass).  Returns ``(y, gathered x)``."""
         s = self.sites[name]
         T, K = s.shape
         Ts = T // self.tp
-        N = w.shape[1]
+        N = w.shape[1] if b_mn else w.shape[0]
         x = s.buf
         s.epoch += 1
         if self.backend == "nccl" or self.tp == 1:
             if self.tp > 1:
                 own = x[self.rank * Ts:(self.rank + 1) * Ts].contiguous()
                 dist.all_gather_into_tensor(x, own, group=self.group)
-            y = G.linear_fwd(x, w, bias, out=out)
+            y = G.gemm(x, w, b_mn=b_mn, bias=bias, out=out)
             return y, x
         if Ts % 128 != 0:
             raise ProcessingError.invalid_input(
@@ -139,7 +141,7 @@ class TensorParallel:
         st = _lib.status_buffer(self.device)
         rc = _lib.lib().cb_gemm_bf16_fused(
             _lib.ptr(x), _lib.ptr(w), _lib.ptr(out), T, N, K, x.stride(0), w.stride(0),
-            out.stride(0), 1, _lib.ptr(bias), 256 if N > 128 else 128, ctypes.byref(c),
+            out.stride(0), int(b_mn), _lib.ptr(bias), 256 if N > 128 else 128, ctypes.byref(c),
             _lib.ptr(st), 0, _lib.stream_ptr())
         _lib.check_rc(rc, "cb_gemm_bf16_fused(ag)")
         self.pad.signal(2 * s.index + 1, s.epoch)   # "I have pulled your rows"

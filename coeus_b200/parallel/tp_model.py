@@ -1,0 +1,295 @@
+"""Tensor-parallel decoder (Megatron column/row split with sequence-parallel activations).
+
+Per layer: ``norm -> [all-gather -> QKV GEMM] -> attention over the local heads ->
+[O GEMM -> reduce-scatter] + residual -> norm -> [all-gather -> gate/up GEMM] -> SwiGLU/GELU ->
+[down GEMM -> reduce-scatter] + residual``.  The bracketed pairs are the fused kernels of
+:class:`coeus_b200.parallel.tp.TensorParallel`; activations between blocks stay sharded by token
+(``[T/tp, H]``).  The LM head is vocabulary-parallel and the loss exchanges only per-token
+``(max, sum-exp, target logit)`` triples.  The backward pass mirrors the forward with the two
+kernels swapped.  Weights keep the ``[in, out]`` layout; QKV / gate-up are split along ``out``,
+O / down along ``in``, the embedding table is replicated.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..foundation.error import ProcessingError
+from ..models.config import DecoderConfig
+from ..ops import attention as A
+from ..ops import elementwise as E
+from ..ops import gemm as G
+from ..ops import norm as N
+from .tp import TensorParallel
+
+
+class TPDecoderLM:
+    def __init__(self, cfg: DecoderConfig, tp: TensorParallel, device, seed: int = 0,
+                 dtype: torch.dtype = torch.bfloat16, full=None) -> None:
+        cfg.validate()
+        if cfg.use_bias or cfg.num_experts or cfg.tie_embeddings:
+            raise ProcessingError.unsupported(
+                "tensor-parallel decoder with biases, experts or tied embeddings",
+                "use use_bias=False, num_experts=0, tie_embeddings=False")
+        n = tp.tp
+        if cfg.num_heads % n or cfg.intermediate_dim % (8 * n) or cfg.vocab_padded % (8 * n):
+            raise ProcessingError.invalid_input(
+                "heads, intermediate_dim/8 and padded vocab/8 must be divisible by the "
+                "tensor-parallel degree")
+        self.cfg, self.tp, self.device = cfg, tp, torch.device(device)
+        self.rank, self.n = tp.rank, n
+        H, I, L = cfg.hidden_dim, cfg.intermediate_dim, cfg.num_layers
+        self.Hl, self.Il, self.Vl = H // n, I // n, cfg.vocab_padded // n
+        self.nh_l = cfg.num_heads // n
+        self.swiglu = cfg.activation == "swiglu"
+        self.rms = cfg.norm == "rmsnorm"
+        up_w = 2 * self.Il if self.swiglu else self.Il
+        specs: List[Tuple[str, Tuple[int, ...], bool]] = [("token_embed", (cfg.vocab_size, H), True)]
+        for l in range(L):
+            p = f"layers.{l}."
+            specs += [(p + "attn.qkv_weights", (H, 3 * self.Hl), True),
+                      (p + "attn.o_weights", (self.Hl, H), True),
+                      (p + "ff.up_weights", (H, up_w), True),
+                      (p + "ff.down_weights", (self.Il, H), True)]
+        specs.append(("output_proj", (H, self.Vl), True))
+        self.decay_specs = len(specs)
+        for l in range(L):
+            p = f"layers.{l}."
+            specs.append((p + "norm1_scale", (H,), False))
+            if not self.rms:
+                specs.append((p + "norm1_bias", (H,), False))
+            specs.append((p + "norm2_scale", (H,), False))
+            if not self.rms:
+                specs.append((p + "norm2_bias", (H,), False))
+        specs.append(("final_norm_scale", (H,), False))
+        if not self.rms:
+            specs.append(("final_norm_bias", (H,), False))
+        self.specs = specs
+        off, self.offsets = 0, {}
+        for i, (name, shape, _) in enumerate(specs):
+            self.offsets[name] = (off, shape)
+            off += (math.prod(shape) + 63) // 64 * 64
+            if i == self.decay_specs - 1:
+                self.decay_end = off
+        self.n_flat = (off + 1023) // 1024 * 1024
+        self.p32 = torch.zeros(self.n_flat, dtype=torch.float32, device=self.device)
+        self.p16 = torch.zeros(self.n_flat, dtype=dtype, device=self.device)
+        self.g32 = torch.zeros(self.n_flat, dtype=torch.float32, device=self.device)
+        self.w, self.g, self.master = {}, {}, {}
+        for name, (o, shape) in self.offsets.items():
+            k = math.prod(shape)
+            self.w[name] = self.p16[o:o + k].view(shape)
+            self.g[name] = self.g32[o:o + k].view(shape)
+            self.master[name] = self.p32[o:o + k].view(shape)
+        self.replicated = ["token_embed"] + [nme for nme, _, d in specs if not d]
+        self._pe = None
+        self._saved = None
+        if full is not None:
+            self.load_from_full(full)
+        else:
+            gen = torch.Generator(device=self.device)
+            gen.manual_seed(seed * 1000 + 17)
+            for name, shape, decay in specs:
+                t = self.master[name]
+                if decay:
+                    # replicated tensors must agree across ranks; shards get rank-specific seeds
+                    g2 = torch.Generator(device=self.device)
+                    import zlib
+                    g2.manual_seed(zlib.crc32(f"{seed}/{name}/"
+                                              f"{0 if name == 'token_embed' else self.rank}".encode()))
+                    t.normal_(0.0, cfg.init_std, generator=g2)
+                elif name.endswith("_scale"):
+                    t.fill_(1.0)
+            self.p16.copy_(self.p32)
+
+    # ------------------------------------------------------------------ parameters
+    def load_from_full(self, full) -> None:
+        """Take this rank's shards out of an unsharded :class:`DecoderLM` with the same config."""
+        cfg, r = self.cfg, self.rank
+        H, I = cfg.hidden_dim, cfg.intermediate_dim
+        Hl, Il, Vl = self.Hl, self.Il, self.Vl
+        fm = full.master
+        n1, n2, fn = full.layout.norm_names
+        self.master["token_embed"].copy_(fm["token_embed"][:cfg.vocab_size])
+        for l in range(cfg.num_layers):
+            p = f"layers.{l}."
+            wq = fm[p + "attn.qkv_weights"]
+            parts = [wq[:, i * H + r * Hl:i * H + (r + 1) * Hl] for i in range(3)]
+            self.master[p + "attn.qkv_weights"].copy_(torch.cat(parts, 1))
+            self.master[p + "attn.o_weights"].copy_(fm[p + "attn.o_weights"][r * Hl:(r + 1) * Hl])
+            if self.swiglu:
+                wg = fm[p + "ff.gate_up_weights"]
+                self.master[p + "ff.up_weights"].copy_(torch.cat(
+                    [wg[:, r * Il:(r + 1) * Il], wg[:, I + r * Il:I + (r + 1) * Il]], 1))
+            else:
+                self.master[p + "ff.up_weights"].copy_(fm[p + "ff.up_weights"][:, r * Il:(r + 1) * Il])
+            self.master[p + "ff.down_weights"].copy_(fm[p + "ff.down_weights"][r * Il:(r + 1) * Il])
+            for mine, theirs in (("norm1", n1), ("norm2", n2)):
+                self.master[p + mine + "_scale"].copy_(fm[p + theirs + "_scale"])
+                if not self.rms:
+                    self.master[p + mine + "_bias"].copy_(fm[p + theirs + "_bias"])
+        self.master["output_proj"].copy_(fm["output_proj"][:, r * Vl:(r + 1) * Vl])
+        self.master["final_norm_scale"].copy_(fm[fn + "_scale"])
+        if not self.rms:
+            self.master["final_norm_bias"].copy_(fm[fn + "_bias"])
+        self.p16.copy_(self.p32)
+
+    def num_parameters_local(self) -> int:
+        return sum(math.prod(s) for _, s, _ in self.specs)
+
+    def zero_grad(self) -> None:
+        self.g32.zero_()
+
+    def _norm(self, x, prefix):
+        return N.norm_fwd(x, self.w[prefix + "_scale"],
+                          None if self.rms else self.w[prefix + "_bias"], self.cfg.norm_eps, self.rms)
+
+    def _norm_bwd(self, dy, x, prefix, mean, rstd, dres):
+        return N.norm_bwd(dy, x, self.w[prefix + "_scale"], mean, rstd, self.g[prefix + "_scale"],
+                          None if self.rms else self.g[prefix + "_bias"], dres, self.rms)
+
+    def _positions(self, S: int):
+        if self.cfg.pos != "sinusoidal":
+            return None
+        if self._pe is None or self._pe.shape[0] < S:
+            self._pe = E.sinusoid_table(max(S, self.cfg.max_seq_len), self.cfg.hidden_dim, self.device)
+        return self._pe
+
+    # ------------------------------------------------------------------ forward
+    def forward_loss(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """``ids``, ``targets``: the SAME ``[B, S]`` batch on every rank of the group.  Returns the
+        mean loss (identical on all ranks) and keeps what :meth:`backward` needs."""
+        cfg, tp = self.cfg, self.tp
+        B, S = ids.shape
+        T = B * S
+        n, r = self.n, self.rank
+        if T % n:
+            raise ProcessingError.invalid_input(f"B*S = {T} must be divisible by tp = {n}")
+        Ts = T // n
+        if Ts % S and S % Ts:
+            raise ProcessingError.invalid_input("tokens per rank must divide or be a multiple of S")
+        H, dh, nh = cfg.hidden_dim, cfg.head_dim, self.nh_l
+        Hl = self.Hl
+        my_ids = ids.reshape(-1)[r * Ts:(r + 1) * Ts].contiguous()
+        pos_off = (r * Ts) % S if Ts < S else 0
+        x = E.embed_fwd(my_ids, self.w["token_embed"], self._positions(S), S, pos_offset=pos_off)
+        sv: dict = {"ids": my_ids, "B": B, "S": S, "T": T, "Ts": Ts, "layers": []}
+        for l in range(cfg.num_layers):
+            p = f"layers.{l}."
+            n1, mean1, rstd1 = self._norm(x, p + "norm1")
+            tp.own_rows("ag_attn", T, H).copy_(n1)
+            qkv, n1_full = tp.ag_gemm("ag_attn", self.w[p + "attn.qkv_weights"])
+            n1_full = n1_full.clone()
+            if cfg.pos == "rope":
+                E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)
+            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+            attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+            x_mid = tp.gemm_rs("rs_attn", attn, self.w[p + "attn.o_weights"], resid=x)
+            n2, mean2, rstd2 = self._norm(x_mid, p + "norm2")
+            tp.own_rows("ag_mlp", T, H).copy_(n2)
+            u, n2_full = tp.ag_gemm("ag_mlp", self.w[p + "ff.up_weights"])
+            n2_full = n2_full.clone()
+            act = E.swiglu_fwd(u) if self.swiglu else E.gelu_fwd(u)
+            x_out = tp.gemm_rs("rs_mlp", act, self.w[p + "ff.down_weights"], resid=x_mid)
+            sv["layers"].append(dict(x=x, mean1=mean1, rstd1=rstd1, n1_full=n1_full, qkv=qkv,
+                                     attn=attn, lse=lse, x_mid=x_mid, mean2=mean2, rstd2=rstd2,
+                                     n2_full=n2_full, u=u, act=act))
+            x = x_out
+        xf, meanf, rstdf = self._norm(x, "final_norm")
+        tp.own_rows("ag_head", T, H).copy_(xf)
+        logits, xf_full = tp.ag_gemm("ag_head", self.w["output_proj"])
+        sv.update(x_last=x, meanf=meanf, rstdf=rstdf, xf_full=xf_full.clone())
+        # vocabulary-parallel cross entropy: exchange (max, sum-exp, target logit) per token
+        V, Vl = cfg.vocab_size, self.Vl
+        v0 = r * Vl
+        width = max(0, min(Vl, V - v0))          # real (unpadded) columns of this shard
+        tg = targets.reshape(-1)
+        stats = E.cross_entropy_stats(logits[:, :max(width, 1)] if width else logits[:, :1], tg, v0)
+        if width == 0:
+            stats[:, 0] = float("-inf"); stats[:, 1] = 0; stats[:, 2] = 0
+        allst = [torch.empty_like(stats) for _ in range(n)]
+        if n > 1:
+            dist.all_gather(allst, stats, group=tp.group)
+        else:
+            allst = [stats]
+        st = torch.stack(allst)                                    # [n, T, 3]
+        gm = st[:, :, 0].max(0).values
+        gs = (st[:, :, 1] * torch.exp(st[:, :, 0] - gm)).sum(0)
+        lse_tok = gm + torch.log(gs)
+        tl = st[:, :, 2].sum(0)
+        valid = (tg >= 0).float()
+        loss = ((lse_tok - tl) * valid).sum() / T
+        if width:
+            E.cross_entropy_bwd_from_lse(logits[:, :width], tg, lse_tok.contiguous(), v0, 1.0 / T)
+        if width < Vl:
+            logits[:, width:] = 0
+        sv["dlogits"] = logits
+        self._saved = sv
+        return loss.reshape(1)
+
+    # ------------------------------------------------------------------ backward
+    def backward(self) -> None:
+        """Gradients of the local shards (fp32, accumulated); replicated parameters (norms,
+        embedding) are summed over the group at the end because every rank saw different tokens."""
+        sv = self._saved
+        if sv is None:
+            raise ProcessingError.not_initialized("backward (no forward_loss saved)")
+        cfg, tp = self.cfg, self.tp
+        B, S, T = sv["B"], sv["S"], sv["T"]
+        H, dh, nh, Hl = cfg.hidden_dim, cfg.head_dim, self.nh_l, self.Hl
+        dlog = sv["dlogits"]
+        G.linear_wgrad(sv["xf_full"], dlog, self.g["output_proj"])
+        dxf = tp.gemm_rs("rs_head_b", dlog, self.w["output_proj"], b_mn=False)
+        dx = self._norm_bwd(dxf, sv["x_last"], "final_norm", sv["meanf"], sv["rstdf"], None)
+        for l in reversed(range(cfg.num_layers)):
+            a = sv["layers"][l]
+            p = f"layers.{l}."
+            # ---- feed-forward
+            tp.own_rows("ag_mlp_b", T, H).copy_(dx)
+            dact, dx_full = tp.ag_gemm("ag_mlp_b", self.w[p + "ff.down_weights"], b_mn=False)
+            G.linear_wgrad(a["act"], dx_full, self.g[p + "ff.down_weights"])
+            du = E.swiglu_bwd(a["u"], dact) if self.swiglu else E.gelu_bwd(a["u"], dact)
+            G.linear_wgrad(a["n2_full"], du, self.g[p + "ff.up_weights"])
+            dn2 = tp.gemm_rs("rs_mlp_b", du, self.w[p + "ff.up_weights"], b_mn=False)
+            dx_mid = self._norm_bwd(dn2, a["x_mid"], p + "norm2", a["mean2"], a["rstd2"], dx)
+            # ---- attention
+            tp.own_rows("ag_attn_b", T, H).copy_(dx_mid)
+            dattn, dxm_full = tp.ag_gemm("ag_attn_b", self.w[p + "attn.o_weights"], b_mn=False)
+            G.linear_wgrad(a["attn"], dxm_full, self.g[p + "attn.o_weights"])
+            qkv = a["qkv"]
+            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+            dq, dk, dv = A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh,
+                                         causal=True)
+            dqkv = dq._base if dq._base is not None else torch.cat([dq, dk, dv], 1)
+            if cfg.pos == "rope":
+                E.rope_(dqkv, 2 * nh, dh, S, theta=cfg.rope_theta, inverse=True)
+            G.linear_wgrad(a["n1_full"], dqkv, self.g[p + "attn.qkv_weights"])
+            dn1 = tp.gemm_rs("rs_attn_b", dqkv, self.w[p + "attn.qkv_weights"], b_mn=False)
+            dx = self._norm_bwd(dn1, a["x"], p + "norm1", a["mean1"], a["rstd1"], dx_mid)
+        E.embed_bwd(sv["ids"], dx, self.g["token_embed"])
+        if self.n > 1:
+            # one all-reduce over the vector tail (all replicated) and one over the embedding
+            dist.all_reduce(self.g32[self.decay_end:], group=tp.group)
+            dist.all_reduce(self.g["token_embed"], group=tp.group)
+        self._saved = None
+
+
+class TPTrainer:
+    """Training step of a tensor-parallel model: every rank applies AdamW to its own shards (the
+    replicated tensors receive identical summed gradients, so they stay identical)."""
+
+    def __init__(self, model: TPDecoderLM, opt_cfg=None) -> None:
+        from ..optim.adamw import AdamW, AdamWConfig
+        self.model = model
+        self.opt = AdamW(opt_cfg or AdamWConfig(), 0, model.n_flat, model.decay_end, model.device)
+
+    def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        m = self.model
+        m.zero_grad()
+        loss = m.forward_loss(ids, targets)
+        m.backward()
+        self.opt.step(m.p32, m.g32, m.p16)
+        return loss

@@ -1,0 +1,80 @@
+"""Tensor-parallel decoder on CPU ranks (Gloo, tp = 2): loss and gradients equal the unsharded
+model's, shard by shard."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from coeus_b200.models.config import DecoderConfig
+from coeus_b200.models.decoder import DecoderLM
+
+CFG = DecoderConfig(hidden_dim=64, num_layers=2, num_heads=4, intermediate_dim=96,
+                    vocab_size=250, max_seq_len=32, use_bias=False, activation="swiglu",
+                    norm="rmsnorm", pos="rope")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, batch, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM
+    full = DecoderLM(CFG, device="cpu", seed=0, dtype=torch.float32)
+    tp = TensorParallel(dist.group.WORLD, "cpu")
+    m = TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, full=full)
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    m.zero_grad()
+    loss = m.forward_loss(x, y)
+    m.backward()
+    out.put((rank, float(loss), {k: v.numpy().copy() for k, v in m.g.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp2_matches_unsharded():
+    torch.manual_seed(0)
+    batch = torch.randint(0, CFG.vocab_size, (2, 17))
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    full = DecoderLM(CFG, device="cpu", seed=0, dtype=torch.float32)
+    full.zero_grad()
+    ref_loss = float(full.forward_loss(x, y))
+    full.backward()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, batch, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    H, I = CFG.hidden_dim, CFG.intermediate_dim
+    Hl, Il, Vl = H // 2, I // 2, CFG.vocab_padded // 2
+    for rank, loss, g in results:
+        g = {k: torch.from_numpy(v) for k, v in g.items()}
+        assert abs(loss - ref_loss) < 1e-4
+        fg = full.g
+        assert (g["token_embed"] - fg["token_embed"]).abs().max() < 1e-5
+        assert (g["output_proj"] - fg["output_proj"][:, rank * Vl:(rank + 1) * Vl]).abs().max() < 1e-5
+        for l in range(CFG.num_layers):
+            p = f"layers.{l}."
+            want = torch.cat([fg[p + "attn.qkv_weights"][:, i * H + rank * Hl:i * H + (rank + 1) * Hl]
+                              for i in range(3)], 1)
+            assert (g[p + "attn.qkv_weights"] - want).abs().max() < 1e-5
+            assert (g[p + "attn.o_weights"] - fg[p + "attn.o_weights"][rank * Hl:(rank + 1) * Hl]).abs().max() < 1e-5
+            wg = fg[p + "ff.gate_up_weights"]
+            want = torch.cat([wg[:, rank * Il:(rank + 1) * Il], wg[:, I + rank * Il:I + (rank + 1) * Il]], 1)
+            assert (g[p + "ff.up_weights"] - want).abs().max() < 1e-5
+            assert (g[p + "ff.down_weights"] - fg[p + "ff.down_weights"][rank * Il:(rank + 1) * Il]).abs().max() < 1e-5
+            assert (g[p + "norm1_scale"] - fg[p + "norm1_scale"]).abs().max() < 1e-5
+            assert (g[p + "norm2_scale"] - fg[p + "norm2_scale"]).abs().max() < 1e-5
+        assert (g["final_norm_scale"] - fg["final_norm_scale"]).abs().max() < 1e-5

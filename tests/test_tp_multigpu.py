@@ -76,3 +76,66 @@ def test_fused_tp_kernels_match_nccl():
         assert torch.equal(res[f"ag_f{it}"], res[f"ag_r{it}"])          # same GEMM on same data
         d = (res[f"rs_f{it}"] - res[f"rs_r{it}"]).abs().max().item()
         assert d < 0.06 * res[f"rs_r{it}"].abs().max().item() + 0.05, d   # bf16 partial sums
+
+
+def _model_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.ops import _lib
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM, TPTrainer
+    cfg = DecoderConfig(hidden_dim=256, num_layers=2, num_heads=4, intermediate_dim=512,
+                        vocab_size=2000, max_seq_len=256, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope")
+    full = DecoderLM(cfg, device=dev, seed=0)
+    gen = torch.Generator().manual_seed(3)
+    batch = torch.randint(0, cfg.vocab_size, (2, 257), generator=gen).to(dev)
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    full.zero_grad()
+    ref_loss = float(full.forward_loss(x, y))
+    full.backward()
+    res = {"ref": ref_loss}
+    for backend in ("fused", "nccl"):
+        tp = TensorParallel(dist.group.WORLD, dev, backend=backend)
+        m = TPDecoderLM(cfg, tp, dev, full=full)
+        m.zero_grad()
+        res[backend] = float(m.forward_loss(x, y))
+        m.backward()
+        Hl = cfg.hidden_dim // world
+        want = full.g["layers.0.attn.o_weights"][rank * Hl:(rank + 1) * Hl]
+        got = m.g["layers.0.attn.o_weights"]
+        res[backend + "_gerr"] = ((got - want).abs().max() / (want.abs().max() + 1e-9)).item()
+        res[backend + "_embed"] = ((m.g["token_embed"] - full.g["token_embed"]).abs().max()
+                                   / (full.g["token_embed"].abs().max() + 1e-9)).item()
+        tr = TPTrainer(m)
+        losses = [float(tr.train_step(x, y)) for _ in range(4)]
+        res[backend + "_train"] = losses
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    if rank == 0:
+        out.put(res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_model_matches_single_gpu():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_model_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=600)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for b in ("fused", "nccl"):
+        assert abs(res[b] - res["ref"]) < 0.03, res
+        assert res[b + "_gerr"] < 0.06 and res[b + "_embed"] < 0.06, res
+        assert res[b + "_train"][-1] < res[b + "_train"][0], res
