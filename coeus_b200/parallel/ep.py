@@ -1,0 +1,277 @@
+"""Expert parallelism for mixture-of-experts feed-forward layers.
+
+Tokens are routed (softmax, top-k, capacity ``C`` per (source rank, expert)), permuted into an
+expert-major send buffer and exchanged with the ranks that own the experts; the experts run a
+gate/up GEMM, SwiGLU and a down GEMM; results return to the source rank, which sums the ``k``
+weighted expert outputs per token.
+
+``backend="fused"``: the exchange happens inside the expert GEMMs (``csrc/gemm.cu``).  The
+gate/up GEMM of a local expert pulls that expert's region of every peer's send buffer over
+NVLink while it already multiplies the rows that arrived (the all-gather->GEMM kernel with the
+peer pointers biased to the expert's region); the down GEMM pushes each finished tile straight
+into the source rank's return buffer from its epilogue (the GEMM->reduce-scatter kernel).  No
+separate all-to-all runs.  ``backend="nccl"`` uses ``all_to_all_single`` around plain GEMMs: the
+baseline, and the path of CPU ranks.  The reference has no experts and no parallelism.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..foundation.error import ProcessingError
+from ..ops import _lib
+from ..ops import elementwise as E
+from ..ops import gemm as G
+from ..ops import moe as M
+from .tp import _CommArgs
+
+
+def capacity_for(tokens_per_rank: int, num_experts: int, top_k: int, factor: float) -> int:
+    """Rows reserved per (source rank, expert): ``factor * T * k / E`` rounded up to 128."""
+    c = int(math.ceil(factor * tokens_per_rank * top_k / num_experts))
+    return (c + 127) // 128 * 128
+
+
+class ExpertParallel:
+    """Communication state of one expert-parallel group (buffers are shared by all layers)."""
+
+    def __init__(self, group, device, backend: Optional[str] = None,
+                 wait_limit_ms: float = 5000.0) -> None:
+        self.group = group
+        self.device = torch.device(device)
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.ep = dist.get_world_size(group) if group is not None else 1
+        if backend is None:
+            backend = "fused" if self.device.type == "cuda" and self.ep > 1 else "nccl"
+        self.backend = backend
+        self.limit_ns = int(wait_limit_ms * 1e6)
+        self._bufs: Dict[str, dict] = {}
+        self.pad = None
+        if backend == "fused":
+            from .symm import SignalPad
+            self.pad = SignalPad(8, group, self.device, wait_limit_ms)   # 4 slots x {fwd, bwd}
+
+    def buffers(self, tag: str, E_: int, C: int, H: int, dtype) -> dict:
+        """``send`` / ``ret`` ``[E*C, H]`` (symmetric when fused), per-direction epoch."""
+        key = f"{tag}:{E_}:{C}:{H}"
+        b = self._bufs.get(key)
+        if b is None:
+            b = {"epoch": 0, "slot0": 0 if tag == "f" else 4}
+            n = E_ * C * H
+            if self.backend == "fused":
+                from .symm import SymmetricBuffer
+                b["send_sym"] = SymmetricBuffer(n * 2, self.group, self.device)
+                b["ret_sym"] = SymmetricBuffer(n * 2, self.group, self.device)
+                b["send"] = b["send_sym"].view(torch.bfloat16, 0, n).view(E_ * C, H)
+                b["ret"] = b["ret_sym"].view(torch.bfloat16, 0, n).view(E_ * C, H)
+                b["flags"] = torch.zeros((E_, (self.ep * C) // 128), dtype=torch.int32,
+                                         device=self.device)
+            else:
+                b["send"] = torch.zeros((E_ * C, H), dtype=dtype, device=self.device)
+                b["ret"] = torch.zeros((E_ * C, H), dtype=dtype, device=self.device)
+            self._bufs[key] = b
+        return b
+
+    # ------------------------------------------------------------------ fused GEMM calls
+    def _fused(self, comm: int, a, w, out, C: int, e_global: int, b: dict, j: int, b_mn: bool):
+        c = _CommArgs()
+        H_bytes = 2
+        c.comm, c.tp, c.rank, c.rows_per_shard = comm, self.ep, self.rank, C
+        K = a.shape[1]
+        N = w.shape[1] if b_mn else w.shape[0]
+        if comm == 1:
+            width = K
+            for s in range(self.ep):
+                c.ag_src[s] = b["send_sym"].ptrs[s] + (e_global * C - s * C) * width * H_bytes
+            c.ag_flags = b["flags"][j].data_ptr()
+            c.ag_epoch = b["epoch"]
+            c.peer_flags = self.pad.buf.local_ptr + 8 * b["slot0"] * self.ep
+            c.peer_expect = b["epoch"]
+        else:
+            for s in range(self.ep):
+                c.rs_dst[s] = b["ret_sym"].ptrs[s] + e_global * C * N * H_bytes
+            c.rs_ld = N
+        c.wait_limit_ns = self.limit_ns
+        st = _lib.status_buffer(self.device)
+        rc = _lib.lib().cb_gemm_bf16_fused(
+            _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), a.shape[0], N, K, a.stride(0), w.stride(0),
+            out.stride(0) if out is not None else N, int(b_mn), _lib.ptr(None),
+            256 if N > 128 else 128, ctypes.byref(c), _lib.ptr(st), 0, _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_gemm_bf16_fused(moe)")
+
+    # ------------------------------------------------------------------ exchange + expert FFN
+    def run_experts(self, tag: str, b: dict, C: int, El: int, first, second) -> None:
+        """Generic two-GEMM expert pass over exchanged rows.
+
+        ``first(j, xg, fused_ag)`` must return the ``[ep*C, K2]`` input of the second GEMM given
+        the gathered rows ``xg`` of local expert ``j`` (``fused_ag(w, b_mn)`` performs the GEMM
+        that pulls the rows when the fused backend is active, else ``None``);
+        ``second(j, a2)`` returns ``(w2, b_mn)`` for the GEMM whose result rows go back."""
+        ep, r = self.ep, self.rank
+        send, ret = b["send"], b["ret"]
+        H = send.shape[1]
+        b["epoch"] += 1
+        epoch, s0 = b["epoch"], b["slot0"]
+        if self.backend == "fused" and ep > 1:
+            self.pad.signal(s0 + 0, epoch)                         # my send buffer is written
+            a2s = []
+            for j in range(El):
+                e = r * El + j
+                xg = torch.empty((ep * C, H), dtype=send.dtype, device=self.device)
+                xg[r * C:(r + 1) * C].copy_(send[e * C:(e + 1) * C])
+                a2s.append(first(j, xg, lambda w, b_mn, out, j=j, e=e, xg=xg:
+                                 self._fused(1, xg, w, out, C, e, b, j, b_mn)))
+            self.pad.signal(s0 + 1, epoch)                         # I have pulled everything
+            if epoch > 1:
+                self.pad.wait(s0 + 3, epoch - 1)                   # sources consumed last results
+            for j in range(El):
+                w2, b_mn = second(j, a2s[j])
+                self._fused(2, a2s[j], w2, None, C, r * El + j, b, j, b_mn)
+            self.pad.signal(s0 + 2, epoch)                         # results are in your buffers
+            self.pad.wait(s0 + 2, epoch)                           # ... and theirs are in mine
+            return
+        # collective / single-rank path
+        if ep > 1:
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=self.group)    # [ep(src), El, C, H]
+            rv = recv.view(ep, El, C, H)
+        outs = []
+        for j in range(El):
+            xg = rv[:, j].reshape(ep * C, H).contiguous() if ep > 1 else send[j * C:(j + 1) * C]
+            a2 = first(j, xg, None)
+            w2, b_mn = second(j, a2)
+            outs.append(G.gemm(a2, w2, b_mn=b_mn))
+        if ep > 1:
+            back = torch.stack([o.view(ep, C, -1) for o in outs], 1).contiguous()  # [ep, El, C, H]
+            dist.all_to_all_single(ret.view(ep, El, C, -1), back, group=self.group)
+        else:
+            for j, o in enumerate(outs):
+                ret[j * C:(j + 1) * C].copy_(o)
+
+    def before_send_write(self, b: dict) -> None:
+        if self.backend == "fused" and self.ep > 1 and b["epoch"] > 0:
+            self.pad.wait(b["slot0"] + 1, b["epoch"])              # everyone pulled my last send
+
+    def after_combine(self, b: dict) -> None:
+        if self.backend == "fused" and self.ep > 1:
+            self.pad.signal(b["slot0"] + 3, b["epoch"])
+
+
+class MoEFFN:
+    """One mixture-of-experts feed-forward layer: router ``[H, E]`` (replicated), local experts'
+    ``gate_up [El, H, 2I]`` and ``down [El, I, H]``.  Weights live in fp32 masters with a working
+    copy in the activation dtype; gradients accumulate in fp32."""
+
+    def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int,
+                 capacity_factor: float, epx: ExpertParallel, aux_coef: float = 0.01,
+                 init_std: float = 0.02, seed: int = 0, dtype=torch.bfloat16) -> None:
+        if num_experts % epx.ep:
+            raise ProcessingError.invalid_input("num_experts must be divisible by the EP degree")
+        self.H, self.I, self.E, self.k = hidden, inter, num_experts, top_k
+        self.cf, self.epx, self.aux_coef = capacity_factor, epx, aux_coef
+        self.El = num_experts // epx.ep
+        dev = epx.device
+        self.dtype = dtype
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)                       # router: same on every rank
+        self.master = {"router": torch.empty(hidden, num_experts, device=dev).normal_(0, init_std, generator=gen)}
+        gen.manual_seed(seed * 7919 + 1 + epx.rank)  # experts: rank specific
+        self.master["gate_up"] = torch.empty(self.El, hidden, 2 * inter, device=dev).normal_(0, init_std, generator=gen)
+        self.master["down"] = torch.empty(self.El, inter, hidden, device=dev).normal_(0, init_std, generator=gen)
+        self.w = {k: v.to(dtype) for k, v in self.master.items()}
+        self.g = {k: torch.zeros_like(v) for k, v in self.master.items()}
+        self._saved = None
+        self.last_aux = None
+
+    def sync_working_copy(self) -> None:
+        for k, v in self.master.items():
+            self.w[k].copy_(v)
+
+    def zero_grad(self) -> None:
+        for v in self.g.values():
+            v.zero_()
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor, resid: Optional[torch.Tensor] = None,
+                save: bool = True) -> torch.Tensor:
+        """``x [T, H]`` (already normalised); returns ``resid + moe(x)``."""
+        epx = self.epx
+        T = x.shape[0]
+        C = capacity_for(T, self.E, self.k, self.cf)
+        logits = G.gemm(x, self.w["router"], b_mn=True, out_dtype=torch.float32)
+        expert, w, probs, slot, counts = M.route(logits, self.k, C)
+        b = epx.buffers("f", self.E, C, self.H, x.dtype)
+        epx.before_send_write(b)
+        b["send"].zero_()
+        M.gather_rows(x, expert, slot, b["send"], C)
+        kept = {}
+
+        def first(j, xg, fused_ag):
+            if fused_ag is not None:
+                gu = torch.empty((xg.shape[0], 2 * self.I), dtype=xg.dtype, device=xg.device)
+                fused_ag(self.w["gate_up"][j], True, gu)
+            else:
+                gu = G.gemm(xg, self.w["gate_up"][j], b_mn=True)
+            act = E.swiglu_fwd(gu)
+            kept[j] = (xg, gu, act)
+            return act
+
+        epx.run_experts("f", b, C, self.El, first, lambda j, a2: (self.w["down"][j], True))
+        out = M.combine_rows(b["ret"], expert, slot, C, w, resid)
+        # load-balancing auxiliary loss: E * sum_e f_e * P_e
+        frac = torch.zeros(self.E, dtype=torch.float32, device=x.device)
+        frac.index_add_(0, expert.reshape(-1).long(), torch.ones(T * self.k, device=x.device))
+        frac /= float(T * self.k)
+        self.last_aux = self.aux_coef * self.E * (frac * probs.mean(0)).sum()
+        if save:
+            self._saved = dict(x=x, expert=expert, w=w, probs=probs, slot=slot, C=C, frac=frac,
+                               ret=b["ret"].clone(), kept=kept)
+        epx.after_combine(b)
+        return out
+
+    # ------------------------------------------------------------------ backward
+    def backward(self, dout: torch.Tensor) -> torch.Tensor:
+        """Gradient w.r.t. the layer input ``x`` (the residual path is the caller's)."""
+        sv, epx = self._saved, self.epx
+        x, expert, w, probs, slot, C = sv["x"], sv["expert"], sv["w"], sv["probs"], sv["slot"], sv["C"]
+        T = x.shape[0]
+        dw = M.pair_dot(dout, sv["ret"], expert, slot, C)                     # [T, k]
+        b = epx.buffers("b", self.E, C, self.H, x.dtype)
+        epx.before_send_write(b)
+        b["send"].zero_()
+        M.gather_rows(dout, expert, slot, b["send"], C, scale=w)
+        kept = sv["kept"]
+
+        def first(j, dyg, fused_ag):
+            xg, gu, act = kept[j]
+            if fused_ag is not None:
+                dact = torch.empty((dyg.shape[0], self.I), dtype=dyg.dtype, device=dyg.device)
+                fused_ag(self.w["down"][j], False, dact)
+            else:
+                dact = G.gemm(dyg, self.w["down"][j], b_mn=False)
+            G.linear_wgrad(act, dyg, self.g["down"][j])
+            dgu = E.swiglu_bwd(gu, dact)
+            G.linear_wgrad(xg, dgu, self.g["gate_up"][j])
+            return dgu
+
+        epx.run_experts("b", b, C, self.El, first, lambda j, a2: (self.w["gate_up"][j], False))
+        dx = M.combine_rows(b["ret"], expert, slot, C, None, None)
+        epx.after_combine(b)
+        # router: w_k = p_k / sum_j p_j over the chosen experts, plus the auxiliary loss
+        idx = expert.long()
+        pk = probs.gather(1, idx)
+        s = pk.sum(-1, keepdim=True)
+        dpk = (dw - (dw * w).sum(-1, keepdim=True)) / s
+        dprobs = torch.zeros_like(probs).scatter_add_(1, idx, dpk)
+        dprobs += self.aux_coef * self.E * sv["frac"][None, :] / T
+        dlogits = probs * (dprobs - (dprobs * probs).sum(-1, keepdim=True))
+        dl = dlogits.to(x.dtype)
+        self.g["router"] += x.float().t() @ dlogits if not x.is_cuda else \
+            G.gemm(x, dl, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dx_r = G.gemm(dl, self.w["router"], b_mn=False)
+        self._saved = None
+        return (dx.float() + dx_r.float()).to(x.dtype)
