@@ -153,6 +153,7 @@ class DecoderConfig:
     num_experts: int = 0            # 0 = dense MLP
     top_k: int = 2
     capacity_factor: float = 1.25
+    aux_loss_coef: float = 0.01   # weight of the router load-balancing term
     router_aux_coef: float = 0.01
     tie_embeddings: bool = False
     init_std: float = 0.02

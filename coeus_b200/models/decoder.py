@@ -38,6 +38,7 @@ class ParamSpec:
     decay: bool
     kind: str  # "weight" | "bias" | "scale" | "embed"
     offset: int = 0
+    expert: bool = False  # rows of dimension 0 are experts, sharded over the expert-parallel group
 
     @property
     def numel(self) -> int:
@@ -57,8 +58,9 @@ class ParamLayout:
 
     ALIGN = 64  # elements; every tensor starts on a 256-byte (fp32) / 128-byte (bf16) boundary
 
-    def __init__(self, cfg: DecoderConfig, tp: int = 1) -> None:
+    def __init__(self, cfg: DecoderConfig, tp: int = 1, ep: int = 1) -> None:
         self.cfg = cfg
+        self.ep = ep
         H, I, V, L = cfg.hidden_dim, cfg.intermediate_dim, cfg.vocab_size, cfg.num_layers
         Vp = cfg.vocab_padded
         ln = cfg.norm == "layernorm"
@@ -71,9 +73,12 @@ class ParamLayout:
             specs.append(ParamSpec(p + "attn.o_weights", (H, H), True, "weight"))
             if cfg.num_experts:
                 E_ = cfg.num_experts
+                El = E_ // ep   # experts owned by one rank of the expert-parallel group
                 specs.append(ParamSpec(p + "moe.router_weights", (H, E_), True, "weight"))
-                specs.append(ParamSpec(p + "moe.experts.gate_up_weights", (E_, H, 2 * I), True, "weight"))
-                specs.append(ParamSpec(p + "moe.experts.down_weights", (E_, I, H), True, "weight"))
+                specs.append(ParamSpec(p + "moe.experts.gate_up_weights", (El, H, 2 * I), True,
+                                       "weight", expert=True))
+                specs.append(ParamSpec(p + "moe.experts.down_weights", (El, I, H), True,
+                                       "weight", expert=True))
             elif cfg.activation == "swiglu":
                 specs.append(ParamSpec(p + "ff.gate_up_weights", (H, 2 * I), True, "weight"))
                 specs.append(ParamSpec(p + "ff.down_weights", (I, H), True, "weight"))
@@ -124,16 +129,23 @@ class DecoderLM:
 
     def __init__(self, cfg: DecoderConfig, device="cuda", init: str = "normal", seed: int = 0,
                  pad_multiple: int = 8 * 1024, training: bool = True,
-                 dtype: torch.dtype = torch.bfloat16) -> None:
+                 dtype: torch.dtype = torch.bfloat16, epx=None) -> None:
         """``dtype`` is the working precision of weights and activations: bf16 on the GPU (the
-        kernels accept nothing else); fp32 is allowed on CPU, where the ops run their oracle."""
+        kernels accept nothing else); fp32 is allowed on CPU, where the ops run their oracle.
+        ``epx`` is the :class:`coeus_b200.parallel.ep.ExpertParallel` state of a mixture-of-experts
+        configuration (``None``: all experts on this rank)."""
         cfg.validate()
-        if cfg.num_experts:
-            raise ProcessingError.unsupported(
-                "DecoderLM with num_experts > 0", "use coeus_b200.parallel.ep.MoEDecoderLM")
         self.cfg = cfg
         self.device = torch.device(device)
-        self.layout = ParamLayout(cfg)
+        self.epx = None
+        self.moe: List = []
+        if cfg.num_experts:
+            from ..parallel.ep import ExpertParallel
+            self.epx = epx if epx is not None else ExpertParallel(None, self.device)
+            if cfg.num_experts % self.epx.ep:
+                raise ProcessingError.invalid_input(
+                    "num_experts must be divisible by the expert-parallel degree")
+        self.layout = ParamLayout(cfg, ep=self.epx.ep if self.epx is not None else 1)
         n = self.layout.padded_total(pad_multiple)
         self.n_flat = n
         self.p32 = torch.zeros(n, dtype=torch.float32, device=self.device)
@@ -153,6 +165,12 @@ class DecoderLM:
         self._pe: Optional[torch.Tensor] = None
         self._saved: Optional[dict] = None
         self.max_ctas = 0
+        if cfg.num_experts:
+            from ..parallel.ep import MoEFFN
+            self.moe = [MoEFFN(cfg.hidden_dim, cfg.intermediate_dim, cfg.num_experts, cfg.top_k,
+                               cfg.capacity_factor, self.epx, aux_coef=cfg.aux_loss_coef,
+                               dtype=dtype, allocate=False) for _ in range(cfg.num_layers)]
+            self._bind_moe()
         self.init_parameters(init, seed)
 
     # ------------------------------------------------------------------ parameters
@@ -163,6 +181,16 @@ class DecoderLM:
             self.master[s.name] = self.p32[sl].view(s.shape)
             if self.g32 is not None:
                 self.g[s.name] = self.g32[sl].view(s.shape)
+        self._bind_moe()
+
+    def _bind_moe(self) -> None:
+        names = {"router": "moe.router_weights", "gate_up": "moe.experts.gate_up_weights",
+                 "down": "moe.experts.down_weights"}
+        for l, m in enumerate(self.moe):
+            p = f"layers.{l}."
+            m.bind({k: self.w[p + n] for k, n in names.items()},
+                   {k: self.g[p + n] for k, n in names.items()} if self.g32 is not None else {},
+                   {k: self.master[p + n] for k, n in names.items()})
 
     def rebind(self, p16: Optional[torch.Tensor] = None, g32: Optional[torch.Tensor] = None) -> None:
         """Point the views at externally allocated flat buffers (e.g. symmetric memory shared
@@ -194,7 +222,16 @@ class DecoderLM:
             gen.manual_seed(seed)
             for s in self.layout.specs:
                 t = self.master[s.name]
-                if s.kind in ("weight", "embed"):
+                if s.expert and self.layout.ep > 1:
+                    # every rank draws all experts and keeps its own, so the values do not
+                    # depend on the expert-parallel degree
+                    El = s.shape[0]
+                    full = torch.empty((El * self.layout.ep,) + tuple(s.shape[1:]),
+                                       dtype=torch.float32, device=self.device)
+                    full.normal_(0.0, cfg.init_std, generator=gen)
+                    t.copy_(full[self.epx.rank * El:(self.epx.rank + 1) * El])
+                    del full
+                elif s.kind in ("weight", "embed"):
                     t.normal_(0.0, cfg.init_std, generator=gen)
                 elif s.kind == "scale":
                     t.fill_(1.0)
@@ -285,7 +322,10 @@ class DecoderLM:
         x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
                              max_ctas=mc)
         n2, mean2, rstd2 = self._norm(x_mid, p + n2n)
-        if cfg.activation == "swiglu":
+        if self.moe:
+            u = act = None
+            x_out = self.moe[l].forward(n2, x_mid, save=save is not None)
+        elif cfg.activation == "swiglu":
             gu = G.linear_fwd(n2, self.w[p + "ff.gate_up_weights"], None, max_ctas=mc)
             act = E.swiglu_fwd(gu)
             u = gu
@@ -357,9 +397,13 @@ class DecoderLM:
         loss_tok = E.cross_entropy_fwd_bwd(logits, targets.reshape(-1), scale,
                                            vocab=self.cfg.vocab_size)
         save["dlogits"] = logits
+        save["aux_scale"] = scale * T   # the auxiliary losses follow the scaling of the main loss
         self._saved = save
         loss = torch.zeros(1, dtype=torch.float32, device=self.device)
         E.sum_scaled_into(loss_tok, loss, 1.0 / T)
+        self.last_ce = loss
+        if self.moe:   # router load-balancing terms (already multiplied by their coefficient)
+            loss = loss + torch.stack([m.last_aux for m in self.moe]).sum()
         return loss
 
     # ------------------------------------------------------------------ backward
@@ -398,7 +442,9 @@ class DecoderLM:
         for l in reversed(range(cfg.num_layers)):
             a = sv[l]
             p = f"layers.{l}."
-            if cfg.activation == "swiglu":
+            if self.moe:
+                dn2 = self.moe[l].backward(dx, aux_grad_scale=sv["aux_scale"])
+            elif cfg.activation == "swiglu":
                 G.linear_wgrad(a["act"], dx, self.g[p + "ff.down_weights"], max_ctas=mc)
                 dact = G.linear_dgrad(dx, self.w[p + "ff.down_weights"], max_ctas=mc)
                 du = E.swiglu_bwd(a["u"], dact)

@@ -141,7 +141,8 @@ class ExpertParallel:
             rv = recv.view(ep, El, C, H)
         outs = []
         for j in range(El):
-            xg = rv[:, j].reshape(ep * C, H).contiguous() if ep > 1 else send[j * C:(j + 1) * C]
+            # a private copy: the send buffer is reused by the next layer while backward needs these rows
+            xg = rv[:, j].reshape(ep * C, H).contiguous() if ep > 1 else send[j * C:(j + 1) * C].clone()
             a2 = first(j, xg, None)
             w2, b_mn = second(j, a2)
             outs.append(G.gemm(a2, w2, b_mn=b_mn))
@@ -168,7 +169,8 @@ class MoEFFN:
 
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int,
                  capacity_factor: float, epx: ExpertParallel, aux_coef: float = 0.01,
-                 init_std: float = 0.02, seed: int = 0, dtype=torch.bfloat16) -> None:
+                 init_std: float = 0.02, seed: int = 0, dtype=torch.bfloat16,
+                 allocate: bool = True) -> None:
         if num_experts % epx.ep:
             raise ProcessingError.invalid_input("num_experts must be divisible by the EP degree")
         self.H, self.I, self.E, self.k = hidden, inter, num_experts, top_k
@@ -176,6 +178,11 @@ class MoEFFN:
         self.El = num_experts // epx.ep
         dev = epx.device
         self.dtype = dtype
+        self._saved = None
+        self.last_aux = None
+        self.master, self.w, self.g = {}, {}, {}
+        if not allocate:        # the owner binds views of its flat buffers
+            return
         gen = torch.Generator(device=dev)
         gen.manual_seed(seed)                       # router: same on every rank
         self.master = {"router": torch.empty(hidden, num_experts, device=dev).normal_(0, init_std, generator=gen)}
@@ -184,8 +191,10 @@ class MoEFFN:
         self.master["down"] = torch.empty(self.El, inter, hidden, device=dev).normal_(0, init_std, generator=gen)
         self.w = {k: v.to(dtype) for k, v in self.master.items()}
         self.g = {k: torch.zeros_like(v) for k, v in self.master.items()}
-        self._saved = None
-        self.last_aux = None
+
+    def bind(self, w: dict, g: dict, master: dict) -> None:
+        """Use externally owned tensors (keys ``router``, ``gate_up``, ``down``)."""
+        self.w, self.g, self.master = w, g, master
 
     def sync_working_copy(self) -> None:
         for k, v in self.master.items():
@@ -202,7 +211,10 @@ class MoEFFN:
         epx = self.epx
         T = x.shape[0]
         C = capacity_for(T, self.E, self.k, self.cf)
-        logits = G.gemm(x, self.w["router"], b_mn=True, out_dtype=torch.float32)
+        if self.E % 8:      # the GEMM kernel wants 16-byte rows; tiny routers take the library path
+            logits = x.float() @ self.w["router"].float()
+        else:
+            logits = G.gemm(x, self.w["router"], b_mn=True, out_dtype=torch.float32)
         expert, w, probs, slot, counts = M.route(logits, self.k, C)
         b = epx.buffers("f", self.E, C, self.H, x.dtype)
         epx.before_send_write(b)
@@ -234,8 +246,9 @@ class MoEFFN:
         return out
 
     # ------------------------------------------------------------------ backward
-    def backward(self, dout: torch.Tensor) -> torch.Tensor:
-        """Gradient w.r.t. the layer input ``x`` (the residual path is the caller's)."""
+    def backward(self, dout: torch.Tensor, aux_grad_scale: float = 1.0) -> torch.Tensor:
+        """Gradient w.r.t. the layer input ``x`` (the residual path is the caller's).
+        ``aux_grad_scale`` multiplies the gradient of the load-balancing term."""
         sv, epx = self._saved, self.epx
         x, expert, w, probs, slot, C = sv["x"], sv["expert"], sv["w"], sv["probs"], sv["slot"], sv["C"]
         T = x.shape[0]
@@ -267,11 +280,86 @@ class MoEFFN:
         s = pk.sum(-1, keepdim=True)
         dpk = (dw - (dw * w).sum(-1, keepdim=True)) / s
         dprobs = torch.zeros_like(probs).scatter_add_(1, idx, dpk)
-        dprobs += self.aux_coef * self.E * sv["frac"][None, :] / T
+        dprobs += (aux_grad_scale * self.aux_coef * self.E / T) * sv["frac"][None, :]
         dlogits = probs * (dprobs - (dprobs * probs).sum(-1, keepdim=True))
         dl = dlogits.to(x.dtype)
-        self.g["router"] += x.float().t() @ dlogits if not x.is_cuda else \
-            G.gemm(x, dl, a_mn=True, b_mn=True, out_dtype=torch.float32)
-        dx_r = G.gemm(dl, self.w["router"], b_mn=False)
+        if not x.is_cuda or self.E % 8:
+            self.g["router"] += x.float().t() @ dlogits
+            dx_r = (dlogits @ self.w["router"].float().t()).to(x.dtype)
+        else:
+            G.gemm(x, dl, a_mn=True, b_mn=True, out=self.g["router"], accumulate=True)
+            dx_r = G.gemm(dl, self.w["router"], b_mn=False)
         self._saved = None
         return (dx.float() + dx_r.float()).to(x.dtype)
+
+
+def dense_spans(layout) -> List[Tuple[int, int]]:
+    """Maximal ``[start, end)`` ranges of the flat buffers that hold no expert weights (these are
+    replicated over the expert-parallel group and need the gradient all-reduce)."""
+    spans, start = [], 0
+    for s in sorted(layout.specs, key=lambda s: s.offset):
+        if s.expert:
+            if s.offset > start:
+                spans.append((start, s.offset))
+            a = layout.ALIGN
+            start = s.offset + (s.numel + a - 1) // a * a
+    if layout.total > start:
+        spans.append((start, layout.total))
+    return spans
+
+
+class ExpertParallelTrainer:
+    """Training step of a mixture-of-experts decoder whose expert-parallel group is also its
+    data-parallel group: every rank runs its own tokens, expert weights are owned by one rank
+    (their gradients are complete once the exchanged rows have been processed), all other
+    gradients are summed over the group while backward is still running."""
+
+    def __init__(self, model, cfg=None) -> None:
+        from ..optim.adamw import AdamW
+        from ..train.trainer import TrainConfig
+        self.model, self.cfg = model, cfg or TrainConfig()
+        self.epx: ExpertParallel = model.epx
+        self.opt = AdamW(self.cfg.adamw(), 0, model.n_flat, model.layout.decay_end, model.device)
+        self.spans = dense_spans(model.layout)
+        L = model.cfg.num_layers
+        if len(self.spans) != L + 1:
+            raise ProcessingError.invalid_input("unexpected parameter layout for expert parallelism")
+        # the last span holds the LM head (complete after the head's backward) and the vectors
+        # (complete at the very end)
+        lo, hi = self.spans[-1]
+        d = min(max(model.layout.decay_end, lo), hi)
+        self._head, self._tail = (lo, d), (d, hi)
+        self.step_index = 0
+        self._stream = torch.cuda.Stream(model.device) if model.device.type == "cuda" else None
+
+    def _reduce(self, span: Tuple[int, int]) -> None:
+        if self.epx.ep == 1 or span[1] <= span[0]:
+            return
+        g = self.model.g32[span[0]:span[1]]
+        if self._stream is None:
+            dist.all_reduce(g, group=self.epx.group)
+            return
+        self._stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._stream):
+            dist.all_reduce(g, group=self.epx.group)
+
+    def _on_layer_done(self, l: int) -> None:
+        if l == -1:
+            self._reduce(self._head)
+        elif l >= 1:
+            self._reduce(self.spans[l])     # attention + router weights of layer l
+        # l == 0 and l == -2: the first span also holds the embedding; it goes last
+
+    def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        m, ep = self.model, self.epx.ep
+        T = ids.numel()
+        m.zero_grad()
+        loss = m.forward_loss(ids, targets, grad_scale=1.0 / (T * ep))
+        m.backward(on_layer_done=self._on_layer_done)
+        self._reduce(self.spans[0])
+        self._reduce(self._tail)
+        if self._stream is not None:
+            torch.cuda.current_stream().wait_stream(self._stream)
+        self.opt.step(m.p32, m.g32, m.p16, 1.0)
+        self.step_index += 1
+        return loss

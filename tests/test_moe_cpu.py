@@ -115,3 +115,91 @@ def test_two_rank_expert_parallel_matches_autograd():
         g = res[rank][3]
         assert abs(torch.from_numpy(g["gate_up"]) - ggu[rank * El:(rank + 1) * El]).max() < 1e-5
         assert abs(torch.from_numpy(g["down"]) - gdn[rank * El:(rank + 1) * El]).max() < 1e-5
+
+
+# ---------------------------------------------------------------------------- whole model
+def _moe_cfg():
+    from coeus_b200.models.config import DecoderConfig
+    return DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=48,
+                         vocab_size=96, max_seq_len=16, use_bias=False, activation="swiglu",
+                         norm="rmsnorm", pos="rope", num_experts=4, top_k=2, capacity_factor=2.0)
+
+
+def test_moe_decoder_gradients_by_finite_differences():
+    from coeus_b200.models.decoder import DecoderLM
+    torch.manual_seed(0)
+    m = DecoderLM(_moe_cfg(), device="cpu", dtype=torch.float32, seed=1)
+    ids = torch.randint(0, 96, (2, 16))
+    tgt = torch.randint(0, 96, (2, 16))
+    m.zero_grad()
+    m.forward_loss(ids, tgt)
+    m.backward()
+    for name in ("layers.0.moe.router_weights", "layers.1.moe.experts.gate_up_weights",
+                 "layers.0.moe.experts.gate_up_weights", "layers.0.moe.experts.down_weights", "layers.0.attn.qkv_weights"):
+        # directional derivative along the gradient: (L(w + e d) - L(w - e d)) / 2e = |g|
+        w, g = m.master[name], m.g[name].clone()
+        d = g / g.norm()
+        eps = 3e-3   # small enough that no token changes its experts
+        keep = w.clone()
+        w.copy_(keep + eps * d); m.sync_working_copy(); lp = float(m.forward_loss(ids, tgt))
+        w.copy_(keep - eps * d); m.sync_working_copy(); lm = float(m.forward_loss(ids, tgt))
+        w.copy_(keep); m.sync_working_copy()
+        fd = (lp - lm) / (2 * eps)
+        assert abs(fd - float(g.norm())) < 4e-2 * float(g.norm()), (name, fd, float(g.norm()))
+
+
+def _train_cfg():
+    # eps = 1 keeps Adam from amplifying rounding noise of near-zero gradients into full steps
+    from coeus_b200.train.trainer import TrainConfig
+    return TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0)
+
+
+def _train_worker(rank, world, port, ids, tgt, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.parallel.ep import ExpertParallelTrainer
+    cfg = _moe_cfg()
+    cfg.aux_loss_coef = 0.0
+    m = DecoderLM(cfg, device="cpu", dtype=torch.float32, seed=1,
+                  epx=ExpertParallel(dist.group.WORLD, "cpu"))
+    tr = ExpertParallelTrainer(m, _train_cfg())
+    losses = [float(tr.train_step(ids[rank], tgt[rank])) for _ in range(2)]
+    out.put((rank, losses, {k: v.numpy().copy() for k, v in m.master.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_training_matches_single_rank():
+    """Two ranks with two experts each and half of the batch each == one rank with everything
+    (capacity is ample, so no token is dropped on either side)."""
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.parallel.ep import ExpertParallelTrainer
+    torch.manual_seed(2)
+    ids = torch.randint(0, 96, (2, 2, 16))
+    tgt = torch.randint(0, 96, (2, 2, 16))
+    cfg = _moe_cfg()
+    cfg.aux_loss_coef = 0.0
+    single = DecoderLM(cfg, device="cpu", dtype=torch.float32, seed=1)
+    tr = ExpertParallelTrainer(single, _train_cfg())
+    ref_losses = [float(tr.train_step(ids.view(4, 16), tgt.view(4, 16))) for _ in range(2)]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_train_worker, args=(r, 2, port, ids, tgt, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {r[0]: r for r in (q.get(timeout=300) for _ in range(2))}
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for step in range(2):
+        mean = 0.5 * (res[0][1][step] + res[1][1][step])
+        assert abs(mean - ref_losses[step]) < 1e-4
+    for rank in range(2):
+        for name, ref in single.master.items():
+            got = torch.from_numpy(res[rank][2][name])
+            if ".experts." in name:
+                ref = ref[rank * 2:(rank + 1) * 2]
+            assert (got - ref).abs().max() < 1e-5, name
