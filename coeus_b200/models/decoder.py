@@ -58,16 +58,27 @@ class ParamLayout:
 
     ALIGN = 64  # elements; every tensor starts on a 256-byte (fp32) / 128-byte (bf16) boundary
 
-    def __init__(self, cfg: DecoderConfig, tp: int = 1, ep: int = 1) -> None:
+    def __init__(self, cfg: DecoderConfig, tp: int = 1, ep: int = 1,
+                 layers: Optional[Tuple[int, int]] = None, embed: bool = True,
+                 head: bool = True) -> None:
+        """``layers=(lo, hi)``, ``embed`` and ``head`` restrict the list to one pipeline stage:
+        blocks ``lo..hi-1`` (named by their index in the whole model), with or without the
+        embedding, and with or without the final norm and LM head."""
         self.cfg = cfg
         self.ep = ep
+        self.layer_ids = list(range(*(layers if layers is not None else (0, cfg.num_layers))))
+        self.has_embed, self.has_head = embed, head
+        if cfg.tie_embeddings and not (embed and head):
+            raise ProcessingError.unsupported("tied embeddings across pipeline stages",
+                                              "embedding and head would live on different ranks")
         H, I, V, L = cfg.hidden_dim, cfg.intermediate_dim, cfg.vocab_size, cfg.num_layers
         Vp = cfg.vocab_padded
         ln = cfg.norm == "layernorm"
         s1, s2 = ("ln1", "ln2") if ln else ("norm1", "norm2")
-        specs: List[ParamSpec] = [
-            ParamSpec("token_embed", (Vp if cfg.tie_embeddings else V, H), True, "embed")]
-        for l in range(L):
+        specs: List[ParamSpec] = []
+        if embed:
+            specs.append(ParamSpec("token_embed", (Vp if cfg.tie_embeddings else V, H), True, "embed"))
+        for l in self.layer_ids:
             p = f"layers.{l}."
             specs.append(ParamSpec(p + "attn.qkv_weights", (H, 3 * H), True, "weight"))
             specs.append(ParamSpec(p + "attn.o_weights", (H, H), True, "weight"))
@@ -85,10 +96,10 @@ class ParamLayout:
             else:
                 specs.append(ParamSpec(p + "ff.up_weights", (H, I), True, "weight"))
                 specs.append(ParamSpec(p + "ff.down_weights", (I, H), True, "weight"))
-        if not cfg.tie_embeddings:
+        if head and not cfg.tie_embeddings:
             specs.append(ParamSpec("output_proj", (H, Vp), True, "weight"))
         vec: List[ParamSpec] = []
-        for l in range(L):
+        for l in self.layer_ids:
             p = f"layers.{l}."
             vec.append(ParamSpec(p + s1 + "_scale", (H,), False, "scale"))
             if ln:
@@ -103,9 +114,10 @@ class ParamLayout:
                     vec.append(ParamSpec(p + "ff.up_bias", (I,), False, "bias"))
                     vec.append(ParamSpec(p + "ff.down_bias", (H,), False, "bias"))
         fn = "final_ln" if ln else "final_norm"
-        vec.append(ParamSpec(fn + "_scale", (H,), False, "scale"))
-        if ln:
-            vec.append(ParamSpec(fn + "_bias", (H,), False, "bias"))
+        if head:
+            vec.append(ParamSpec(fn + "_scale", (H,), False, "scale"))
+            if ln:
+                vec.append(ParamSpec(fn + "_bias", (H,), False, "bias"))
         off = 0
         for s in specs + vec:
             s.offset = off
@@ -129,7 +141,9 @@ class DecoderLM:
 
     def __init__(self, cfg: DecoderConfig, device="cuda", init: str = "normal", seed: int = 0,
                  pad_multiple: int = 8 * 1024, training: bool = True,
-                 dtype: torch.dtype = torch.bfloat16, epx=None) -> None:
+                 dtype: torch.dtype = torch.bfloat16, epx=None,
+                 layers: Optional[Tuple[int, int]] = None, embed: bool = True,
+                 head: bool = True) -> None:
         """``dtype`` is the working precision of weights and activations: bf16 on the GPU (the
         kernels accept nothing else); fp32 is allowed on CPU, where the ops run their oracle.
         ``epx`` is the :class:`coeus_b200.parallel.ep.ExpertParallel` state of a mixture-of-experts
@@ -145,7 +159,9 @@ class DecoderLM:
             if cfg.num_experts % self.epx.ep:
                 raise ProcessingError.invalid_input(
                     "num_experts must be divisible by the expert-parallel degree")
-        self.layout = ParamLayout(cfg, ep=self.epx.ep if self.epx is not None else 1)
+        self.layout = ParamLayout(cfg, ep=self.epx.ep if self.epx is not None else 1,
+                                  layers=layers, embed=embed, head=head)
+        self.layer_ids = self.layout.layer_ids
         n = self.layout.padded_total(pad_multiple)
         self.n_flat = n
         self.p32 = torch.zeros(n, dtype=torch.float32, device=self.device)
@@ -162,6 +178,7 @@ class DecoderLM:
         self.master: Dict[str, torch.Tensor] = {}
         self._bind_views()
         self._ws: Dict[str, torch.Tensor] = {}
+        self._ws_tag = ""
         self._pe: Optional[torch.Tensor] = None
         self._saved: Optional[dict] = None
         self.max_ctas = 0
@@ -169,7 +186,7 @@ class DecoderLM:
             from ..parallel.ep import MoEFFN
             self.moe = [MoEFFN(cfg.hidden_dim, cfg.intermediate_dim, cfg.num_experts, cfg.top_k,
                                cfg.capacity_factor, self.epx, aux_coef=cfg.aux_loss_coef,
-                               dtype=dtype, allocate=False) for _ in range(cfg.num_layers)]
+                               dtype=dtype, allocate=False) for _ in self.layer_ids]
             self._bind_moe()
         self.init_parameters(init, seed)
 
@@ -186,7 +203,7 @@ class DecoderLM:
     def _bind_moe(self) -> None:
         names = {"router": "moe.router_weights", "gate_up": "moe.experts.gate_up_weights",
                  "down": "moe.experts.down_weights"}
-        for l, m in enumerate(self.moe):
+        for l, m in zip(self.layer_ids, self.moe):
             p = f"layers.{l}."
             m.bind({k: self.w[p + n] for k, n in names.items()},
                    {k: self.g[p + n] for k, n in names.items()} if self.g32 is not None else {},
@@ -218,10 +235,13 @@ class DecoderLM:
                 E.sin_init_(flat, cfg.hidden_dim, index_offset=off)
                 self._assign_reference_tensor(name, flat.view(shape))
         elif init == "normal":
+            import zlib
             gen = torch.Generator(device=self.device)
-            gen.manual_seed(seed)
             for s in self.layout.specs:
                 t = self.master[s.name]
+                # one stream per tensor name: the values do not depend on which other tensors
+                # this rank holds (pipeline stages, expert shards)
+                gen.manual_seed(seed * 1000003 + zlib.crc32(s.name.encode()))
                 if s.expert and self.layout.ep > 1:
                     # every rank draws all experts and keeps its own, so the values do not
                     # depend on the expert-parallel degree
@@ -245,7 +265,7 @@ class DecoderLM:
         if cfg.vocab_padded != V:   # padding columns / rows of the vocabulary stay zero
             if cfg.tie_embeddings:
                 self.master["token_embed"][V:].zero_()
-            else:
+            elif "output_proj" in self.master:
                 self.master["output_proj"][:, V:].zero_()
         self.sync_working_copy()
 
@@ -280,7 +300,7 @@ class DecoderLM:
 
     # ------------------------------------------------------------------ workspace
     def _buf(self, name: str, shape, dtype=None) -> torch.Tensor:
-        key = name
+        key = self._ws_tag + name   # the tag separates micro-batches that are in flight together
         dtype = dtype or self.p16.dtype
         t = self._ws.get(key)
         if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
@@ -324,7 +344,7 @@ class DecoderLM:
         n2, mean2, rstd2 = self._norm(x_mid, p + n2n)
         if self.moe:
             u = act = None
-            x_out = self.moe[l].forward(n2, x_mid, save=save is not None)
+            x_out = self.moe[l - self.layer_ids[0]].forward(n2, x_mid, save=save is not None)
         elif cfg.activation == "swiglu":
             gu = G.linear_fwd(n2, self.w[p + "ff.gate_up_weights"], None, max_ctas=mc)
             act = E.swiglu_fwd(gu)
@@ -355,8 +375,16 @@ class DecoderLM:
         """Final-norm output ``[B*S, H]`` for ``ids [B, S]`` (int64)."""
         B, S = self._check_ids(ids)
         x = E.embed_fwd(ids.reshape(-1), self.w["token_embed"], self._positions(S), S)
-        for l in range(self.cfg.num_layers):
+        x = self.forward_blocks(x, B, S, save)
+        return self.forward_final_norm(x, save)
+
+    def forward_blocks(self, x: torch.Tensor, B: int, S: int, save: Optional[dict]) -> torch.Tensor:
+        """This model's blocks applied to ``x [B*S, H]``."""
+        for l in self.layer_ids:
             x = self._block_fwd(l, x, B, S, save)
+        return x
+
+    def forward_final_norm(self, x: torch.Tensor, save: Optional[dict]) -> torch.Tensor:
         fn = self.layout.norm_names[2]
         xf, meanf, rstdf = self._norm(x, fn)
         if save is not None:
@@ -387,9 +415,14 @@ class DecoderLM:
         ``targets [B,S]``; keeps what :meth:`backward` needs.  ``grad_scale`` is the factor the
         logit gradients are multiplied with (default ``1 / (B*S)``)."""
         B, S = self._check_ids(ids)
-        T = B * S
         save: dict = {"ids": ids.reshape(-1), "B": B, "S": S}
         xf = self.forward_hidden(ids, save)
+        return self.loss_from_hidden(xf, targets, save, grad_scale)
+
+    def loss_from_hidden(self, xf: torch.Tensor, targets: torch.Tensor, save: dict,
+                         grad_scale: Optional[float] = None) -> torch.Tensor:
+        """LM head and cross-entropy on the final-norm output; stores ``save`` for backward."""
+        T = xf.shape[0]
         w, b_mn = self.output_weight()
         logits = G.gemm(xf, w, b_mn=b_mn, out=self._buf("logits", (T, self.cfg.vocab_padded)),
                         max_ctas=self.max_ctas)
@@ -418,11 +451,17 @@ class DecoderLM:
         sv = self._saved
         if sv is None:
             raise ProcessingError.not_initialized("backward (no forward_loss saved)")
+        dx = self.backward_head(sv)
+        if on_layer_done is not None:
+            on_layer_done(-1)
+        dx = self.backward_blocks(dx, sv, on_layer_done)
+        E.embed_bwd(sv["ids"], dx, self.g["token_embed"])
+
+    def backward_head(self, sv: dict) -> torch.Tensor:
+        """Gradients of the LM head and final norm; returns d loss / d (last block output)."""
         cfg = self.cfg
-        H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
-        B, S = sv["B"], sv["S"]
         rms = cfg.norm == "rmsnorm"
-        n1n, n2n, fn = self.layout.norm_names
+        fn = self.layout.norm_names[2]
         mc = self.max_ctas
         dlog = sv["dlogits"]
         fin = sv["final"]
@@ -435,15 +474,22 @@ class DecoderLM:
         else:
             G.linear_wgrad(fin["xf"], dlog, self.g["output_proj"], max_ctas=mc)
             dxf = G.linear_dgrad(dlog, w, max_ctas=mc)
-        dx = N.norm_bwd(dxf, fin["x"], self.w[fn + "_scale"], fin["mean"], fin["rstd"],
-                        self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None, rms)
-        if on_layer_done is not None:
-            on_layer_done(-1)
-        for l in reversed(range(cfg.num_layers)):
+        return N.norm_bwd(dxf, fin["x"], self.w[fn + "_scale"], fin["mean"], fin["rstd"],
+                          self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None, rms)
+
+    def backward_blocks(self, dx: torch.Tensor, sv: dict, on_layer_done=None) -> torch.Tensor:
+        """Backward through this model's blocks; returns d loss / d (first block input)."""
+        cfg = self.cfg
+        H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
+        B, S = sv["B"], sv["S"]
+        rms = cfg.norm == "rmsnorm"
+        n1n, n2n, fn = self.layout.norm_names
+        mc = self.max_ctas
+        for l in reversed(self.layer_ids):
             a = sv[l]
             p = f"layers.{l}."
             if self.moe:
-                dn2 = self.moe[l].backward(dx, aux_grad_scale=sv["aux_scale"])
+                dn2 = self.moe[l - self.layer_ids[0]].backward(dx, aux_grad_scale=sv["aux_scale"])
             elif cfg.activation == "swiglu":
                 G.linear_wgrad(a["act"], dx, self.g[p + "ff.down_weights"], max_ctas=mc)
                 dact = G.linear_dgrad(dx, self.w[p + "ff.down_weights"], max_ctas=mc)
@@ -482,7 +528,7 @@ class DecoderLM:
                             None if rms else self.g[p + n1n + "_bias"], dx_mid, rms)
             if on_layer_done is not None:
                 on_layer_done(l)
-        E.embed_bwd(sv["ids"], dx, self.g["token_embed"])
+        return dx
         if on_layer_done is not None:
             on_layer_done(-2)
         self._saved = None

@@ -1,0 +1,188 @@
+"""Pipeline parallelism: the decoder's blocks are split into contiguous stages, one per rank, and
+micro-batches flow through them in the one-forward-one-backward (1F1B) order.
+
+Stage ``s`` of ``P`` runs ``min(P - 1 - s, M)`` warm-up forwards, then alternates one forward and
+one backward, then drains the remaining backwards; at most ``P - s`` micro-batches are alive on a
+stage at a time, which bounds the activation stash.  Activations and their gradients travel with
+point-to-point sends (NCCL on GPUs, Gloo on CPU ranks).  The forward and the backward direction
+use separate process groups, so a receive that was posted early never blocks a send of the other
+direction; receives for the next micro-batch are posted before the current one is computed and
+sends are not waited for until their buffer is reused, which is what overlaps the transfers with
+the math.  The reference is a single process and has no pipeline (no send/recv anywhere in its
+sources); this is one of the parallelism strategies the larger training configurations need.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..foundation.error import ProcessingError
+from ..models.config import DecoderConfig
+from ..models.decoder import DecoderLM
+from ..ops import elementwise as E
+
+
+def split_layers(num_layers: int, stages: int) -> List[Tuple[int, int]]:
+    """Contiguous ``(lo, hi)`` block ranges, the remainder going to the earliest stages."""
+    if stages < 1 or stages > num_layers:
+        raise ProcessingError.invalid_input(
+            f"cannot split {num_layers} layers into {stages} pipeline stages")
+    base, rem = divmod(num_layers, stages)
+    out, lo = [], 0
+    for s in range(stages):
+        hi = lo + base + (1 if s < rem else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+def schedule_1f1b(stage: int, stages: int, micro_batches: int) -> List[Tuple[str, int]]:
+    """The order of ``("F", i)`` / ``("B", i)`` steps of one stage."""
+    warm = min(stages - 1 - stage, micro_batches)
+    steps: List[Tuple[str, int]] = [("F", i) for i in range(warm)]
+    f, b = warm, 0
+    while f < micro_batches:
+        steps.append(("F", f))
+        steps.append(("B", b))
+        f += 1
+        b += 1
+    while b < micro_batches:
+        steps.append(("B", b))
+        b += 1
+    return steps
+
+
+class _Channel:
+    """One direction between two neighbouring stages: posts receives ahead and keeps sends alive."""
+
+    def __init__(self, group, peer_global: int, shape, dtype, device, count: int, recv: bool) -> None:
+        self.group, self.peer, self.count = group, peer_global, count
+        self.shape, self.dtype, self.device = shape, dtype, device
+        self.posted = 0
+        self.pending: List[Tuple[object, torch.Tensor]] = []
+        self.recv = recv
+
+    def post_recv(self) -> None:
+        if self.posted >= self.count:
+            return
+        buf = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+        self.pending.append((dist.irecv(buf, src=self.peer, group=self.group), buf))
+        self.posted += 1
+
+    def take(self) -> torch.Tensor:
+        if not self.pending:
+            self.post_recv()
+        req, buf = self.pending.pop(0)
+        req.wait()
+        self.post_recv()          # the next one travels while this one is computed on
+        return buf
+
+    def send(self, t: torch.Tensor) -> None:
+        t = t.contiguous()
+        self.pending.append((dist.isend(t, dst=self.peer, group=self.group), t))
+        while len(self.pending) > 2:     # bound the number of buffers kept alive
+            req, _ = self.pending.pop(0)
+            req.wait()
+
+    def drain(self) -> None:
+        for req, _ in self.pending:
+            req.wait()
+        self.pending.clear()
+
+
+class PipelineStage:
+    """One rank's share of a pipelined decoder plus the 1F1B step loop."""
+
+    def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, seed: int = 0,
+                 dtype: torch.dtype = torch.bfloat16, train_cfg=None) -> None:
+        from ..optim.adamw import AdamW
+        from ..train.trainer import TrainConfig
+        self.group = group
+        self.stage = dist.get_rank(group) if group is not None else 0
+        self.stages = dist.get_world_size(group) if group is not None else 1
+        self.M = micro_batches
+        self.device = torch.device(device)
+        lo, hi = split_layers(cfg.num_layers, self.stages)[self.stage]
+        self.first, self.last = self.stage == 0, self.stage == self.stages - 1
+        self.model = DecoderLM(cfg, self.device, seed=seed, dtype=dtype, layers=(lo, hi),
+                               embed=self.first, head=self.last)
+        self.cfg = cfg
+        self.train_cfg = train_cfg or TrainConfig()
+        self.opt = AdamW(self.train_cfg.adamw(), 0, self.model.n_flat, self.model.layout.decay_end,
+                         self.device)
+        if self.stages > 1:
+            ranks = dist.get_process_group_ranks(group)
+            # two groups: traffic of one direction never queues behind the other
+            self.fwd_group = dist.new_group(ranks)
+            self.bwd_group = dist.new_group(ranks)
+            self._ranks = ranks
+        self.step_index = 0
+
+    def load_from_full(self, full: DecoderLM) -> None:
+        """Copy this stage's tensors out of a model that holds every layer."""
+        for name, t in self.model.master.items():
+            t.copy_(full.master[name])
+        self.model.sync_working_copy()
+
+    def train_step(self, ids: Optional[torch.Tensor], targets: Optional[torch.Tensor]) -> torch.Tensor:
+        """One optimizer step over ``M`` micro-batches.  ``ids [M, b, S]`` is needed on the first
+        stage, ``targets [M, b, S]`` on the last; both may be given everywhere.  Returns the mean
+        loss on the last stage (zeros elsewhere)."""
+        m, M = self.model, self.M
+        ref = ids if ids is not None else targets
+        b, S = ref.shape[1], ref.shape[2]
+        T, H = b * S, self.cfg.hidden_dim
+        act_dtype = m.p16.dtype
+        chans: Dict[str, _Channel] = {}
+        if self.stages > 1:
+            if not self.first:
+                chans["rf"] = _Channel(self.fwd_group, self._ranks[self.stage - 1], (T, H),
+                                       act_dtype, self.device, M, True)
+                chans["sb"] = _Channel(self.bwd_group, self._ranks[self.stage - 1], (T, H),
+                                       act_dtype, self.device, M, False)
+            if not self.last:
+                chans["sf"] = _Channel(self.fwd_group, self._ranks[self.stage + 1], (T, H),
+                                       act_dtype, self.device, M, False)
+                chans["rb"] = _Channel(self.bwd_group, self._ranks[self.stage + 1], (T, H),
+                                       act_dtype, self.device, M, True)
+        m.zero_grad()
+        saves: Dict[int, dict] = {}
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if "rf" in chans:
+            chans["rf"].post_recv()
+        for kind, i in schedule_1f1b(self.stage, self.stages, M):
+            m._ws_tag = f"mb{i % (self.stages - self.stage)}:"   # slots of micro-batches in flight
+            if kind == "F":
+                save: dict = {"B": b, "S": S}
+                if self.first:
+                    flat = ids[i].reshape(-1)
+                    save["ids"] = flat
+                    x = E.embed_fwd(flat, m.w["token_embed"], m._positions(S), S)
+                else:
+                    x = chans["rf"].take()
+                x = m.forward_blocks(x, b, S, save)
+                if self.last:
+                    xf = m.forward_final_norm(x, save)
+                    loss = m.loss_from_hidden(xf, targets[i], save, grad_scale=1.0 / (T * M))
+                    loss_sum += loss / M
+                else:
+                    chans["sf"].send(x)
+                saves[i] = save
+                if "rb" in chans and not chans["rb"].pending:
+                    chans["rb"].post_recv()
+            else:
+                save = saves.pop(i)
+                dx = m.backward_head(save) if self.last else chans["rb"].take()
+                dx = m.backward_blocks(dx, save)
+                if self.first:
+                    E.embed_bwd(save["ids"], dx, m.g["token_embed"])
+                else:
+                    chans["sb"].send(dx)
+        for c in chans.values():
+            c.drain()
+        m._ws_tag = ""
+        self.opt.step(m.p32, m.g32, m.p16, 1.0)
+        self.step_index += 1
+        return loss_sum

@@ -1,0 +1,106 @@
+"""Pipeline parallelism on CPU ranks (Gloo): the 1F1B schedule itself, and a two- and three-stage
+training step against the same model on one rank with gradient accumulation."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from coeus_b200.parallel.pp import schedule_1f1b, split_layers
+
+
+def test_split_layers():
+    assert split_layers(5, 2) == [(0, 3), (3, 5)]
+    assert split_layers(24, 8) == [(3 * i, 3 * i + 3) for i in range(8)]
+    with pytest.raises(Exception):
+        split_layers(2, 3)
+
+
+@pytest.mark.parametrize("P,M", [(1, 3), (2, 4), (4, 8), (4, 2), (3, 3)])
+def test_schedule_is_valid_1f1b(P, M):
+    for s in range(P):
+        steps = schedule_1f1b(s, P, M)
+        assert sorted(i for k, i in steps if k == "F") == list(range(M))
+        assert sorted(i for k, i in steps if k == "B") == list(range(M))
+        alive, peak = set(), 0
+        for k, i in steps:
+            if k == "F":
+                alive.add(i)
+            else:
+                assert i in alive       # a backward only after its forward
+                alive.remove(i)
+            peak = max(peak, len(alive))
+        assert peak <= min(P - s, M)    # bounded activation stash
+
+
+def _cfg(moe=False):
+    from coeus_b200.models.config import DecoderConfig
+    kw = dict(num_experts=4, top_k=2, capacity_factor=2.0, aux_loss_coef=0.0) if moe else {}
+    return DecoderConfig(hidden_dim=32, num_layers=3, num_heads=2, intermediate_dim=48,
+                         vocab_size=96, max_seq_len=16, use_bias=False, activation="swiglu",
+                         norm="rmsnorm", pos="rope", **kw)
+
+
+def _train_cfg():
+    from coeus_b200.train.trainer import TrainConfig
+    return TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ids, tgt, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.parallel.pp import PipelineStage
+    st = PipelineStage(_cfg(), dist.group.WORLD, "cpu", micro_batches=ids.shape[0], seed=4,
+                       dtype=torch.float32, train_cfg=_train_cfg())
+    losses = [float(st.train_step(ids, tgt)) for _ in range(2)]
+    out.put((rank, losses, {k: v.numpy().copy() for k, v in st.model.master.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_pipeline_training_matches_single_rank(world):
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.optim.adamw import AdamW
+    torch.manual_seed(0)
+    M, b, S = 4, 2, 16
+    ids = torch.randint(0, 96, (M, b, S))
+    tgt = torch.randint(0, 96, (M, b, S))
+    full = DecoderLM(_cfg(), "cpu", seed=4, dtype=torch.float32)
+    opt = AdamW(_train_cfg().adamw(), 0, full.n_flat, full.layout.decay_end, "cpu")
+    ref_losses = []
+    for _ in range(2):
+        full.zero_grad()
+        tot = 0.0
+        for i in range(M):
+            tot += float(full.forward_loss(ids[i], tgt[i], grad_scale=1.0 / (b * S * M))) / M
+            full.backward()
+        opt.step(full.p32, full.g32, full.p16, 1.0)
+        ref_losses.append(tot)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ids, tgt, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {r[0]: r for r in (q.get(timeout=300) for _ in range(world))}
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for step in range(2):
+        assert abs(res[world - 1][1][step] - ref_losses[step]) < 1e-5
+    seen = set()
+    for rank in range(world):
+        for name, got in res[rank][2].items():
+            assert (torch.from_numpy(got) - full.master[name]).abs().max() < 1e-5, name
+            seen.add(name)
+    assert seen == set(full.master)     # every tensor lives on exactly the stages that need it
