@@ -26,6 +26,7 @@ namespace cb {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int AG_PARTS = 8;   // row groups a pulled tile is split into
 constexpr int MAX_TP = 8;
 enum : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
 
@@ -54,7 +55,8 @@ struct GemmArgs {
   const void* ag_src[MAX_TP];   // COMM_AG: every rank's copy of the gathered operand (peer mapped)
   __nv_bfloat16* ag_dst;        //          this rank's copy (the A operand of the GEMM)
   int ag_ld;                    //          its row pitch (elements)
-  uint32_t* ag_flags;           //          local per-tile arrival epochs
+  uint32_t* ag_flags;           //          local per-tile arrival counters: AG_PARTS per epoch,
+                                //          zero before the first use and never reset
   uint32_t ag_epoch;
   const uint64_t* peer_flags;   //          local signal pad: peer_flags[s] >= peer_expect once
   uint64_t peer_expect;         //          rank s has written its shard
@@ -261,7 +263,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (m_blk / p.tiles_per_shard != p.rank) {  // rows that come from a peer
             const uint64_t t0 = globaltimer_ns();
             uint32_t n = 0;
-            while (ld_acquire_gpu_u32(p.ag_flags + m_blk) != p.ag_epoch) {
+            // the tile arrives in AG_PARTS row groups, each adding one to the tile's counter
+            while (ld_acquire_gpu_u32(p.ag_flags + m_blk) < p.ag_epoch * AG_PARTS) {
               if ((++n & 15u) == 0u &&
                   (*abort_flag || globaltimer_ns() - t0 > p.wait_limit_ns)) {
                 *abort_flag = 1u;
@@ -368,10 +371,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     volatile int* comm_ok = epi_ok + 1;
     const int n_remote = (p.tp - 1) * p.tiles_per_shard;
     const size_t row_bytes = static_cast<size_t>(p.K) * 2;  // gathered rows are K elements wide
-    for (int c = blockIdx.x; c < n_remote; c += gridDim.x) {
-      const int dist = c / p.tiles_per_shard + 1;
+    // unit of work: one of the AG_PARTS row groups of one remote tile, so that even a short
+    // operand keeps every CTA's pull warps (and with them enough bytes in flight) busy
+    for (int c = blockIdx.x; c < n_remote * AG_PARTS; c += gridDim.x) {
+      const int tile_c = c / AG_PARTS, part = c % AG_PARTS;
+      const int dist = tile_c / p.tiles_per_shard + 1;
       const int src = (p.rank + dist) % p.tp;
-      const int m_blk = src * p.tiles_per_shard + c % p.tiles_per_shard;
+      const int m_blk = src * p.tiles_per_shard + tile_c % p.tiles_per_shard;
       if (ct == 0) {
         int good = 1;
         const uint64_t t0 = globaltimer_ns();
@@ -389,11 +395,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       asm volatile("bar.sync 2, 64;" ::: "memory");
       if (*comm_ok == 0) break;
-      const int rows = min(GEMM_BM, p.M - m_blk * GEMM_BM);
+      constexpr int PART_ROWS = GEMM_BM / AG_PARTS;
+      const int row0 = m_blk * GEMM_BM + part * PART_ROWS;
+      const int rows = max(0, min(PART_ROWS, p.M - row0));
       const char* sbase = static_cast<const char*>(p.ag_src[src]) +
-                          static_cast<size_t>(m_blk) * GEMM_BM * p.ag_ld * 2;
-      char* dbase = reinterpret_cast<char*>(p.ag_dst) +
-                    static_cast<size_t>(m_blk) * GEMM_BM * p.ag_ld * 2;
+                          static_cast<size_t>(row0) * p.ag_ld * 2;
+      char* dbase = reinterpret_cast<char*>(p.ag_dst) + static_cast<size_t>(row0) * p.ag_ld * 2;
       const int vec_per_row = static_cast<int>(row_bytes / 16);
       const int total_vec = rows * vec_per_row;
       for (int v0 = ct; v0 < total_vec; v0 += 64 * 8) {
@@ -423,8 +430,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       asm volatile("fence.proxy.async.global;" ::: "memory");
       asm volatile("bar.sync 2, 64;" ::: "memory");
       if (ct == 0)
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(p.ag_epoch)
-                     : "memory");
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + m_blk) : "memory");
     }
   } else {
     // ------------------------------------------------------------------ epilogue
