@@ -143,14 +143,20 @@ class DecoderLM:
                  pad_multiple: int = 8 * 1024, training: bool = True,
                  dtype: torch.dtype = torch.bfloat16, epx=None,
                  layers: Optional[Tuple[int, int]] = None, embed: bool = True,
-                 head: bool = True) -> None:
-        """``dtype`` is the working precision of weights and activations: bf16 on the GPU (the
+                 head: bool = True, cp=None) -> None:
+        """``cp`` is a :class:`coeus_b200.parallel.cp.ContextParallel` (token ids then come as this
+        rank's two zig-zag chunks ``[2, B, Sc]`` and attention runs as ring attention over the
+        group) or a :class:`coeus_b200.parallel.ulysses.UlyssesParallel` (ids ``[1, B, S/sp]``,
+        all-to-all between sequence and head sharding around attention); ``cp.shard(ids)`` makes
+        the local ids.
+        ``dtype`` is the working precision of weights and activations: bf16 on the GPU (the
         kernels accept nothing else); fp32 is allowed on CPU, where the ops run their oracle.
         ``epx`` is the :class:`coeus_b200.parallel.ep.ExpertParallel` state of a mixture-of-experts
         configuration (``None``: all experts on this rank)."""
         cfg.validate()
         self.cfg = cfg
         self.device = torch.device(device)
+        self.cp = cp
         self.epx = None
         self.moe: List = []
         if cfg.num_experts:
@@ -323,6 +329,19 @@ class DecoderLM:
         return N.norm_fwd(x, self.w[prefix + "_scale"], None if rms else self.w[prefix + "_bias"],
                           cfg.norm_eps, rms)
 
+    def _rope(self, qkv: torch.Tensor, B: int, S: int, inverse: bool) -> None:
+        """Rotary embedding of the q and k heads (adjacent in the fused buffer); under context
+        parallelism each of the two chunks starts at its own position."""
+        cfg = self.cfg
+        nh, dh = cfg.num_heads, cfg.head_dim
+        if self.cp is None:
+            E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta, inverse=inverse)
+            return
+        Tc = B * S
+        for c, off in enumerate(self.cp.position_offsets(S)):
+            E.rope_(qkv[c * Tc:(c + 1) * Tc], 2 * nh, dh, S, pos_offset=off, theta=cfg.rope_theta,
+                    inverse=inverse)
+
     def _block_fwd(self, l: int, x: torch.Tensor, B: int, S: int, save: Optional[dict]):
         cfg = self.cfg
         H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
@@ -336,9 +355,12 @@ class DecoderLM:
                            out=self._buf(f"qkv{l}" if save is not None else "qkv", (T, 3 * H)),
                            max_ctas=mc)
         if cfg.pos == "rope":
-            E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)  # q and k heads are adjacent
-        q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
-        attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+            self._rope(qkv, B, S, False)
+        if self.cp is not None:
+            attn, lse = self.cp.attention_fwd(qkv, B, S, nh, dh)
+        else:
+            q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+            attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
         x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
                              max_ctas=mc)
         n2, mean2, rstd2 = self._norm(x_mid, p + n2n)
@@ -363,6 +385,16 @@ class DecoderLM:
         return x_out
 
     def _check_ids(self, ids: torch.Tensor) -> Tuple[int, int]:
+        if self.cp is not None:
+            nc = self.cp.n_chunks
+            if ids.dim() != 3 or ids.shape[0] != nc:
+                raise ProcessingError.invalid_input(
+                    f"sequence parallelism expects ids [{nc}, B, S_local] (use its shard())")
+            B, S = ids.shape[1], ids.shape[2]
+            if S * nc * self.cp.cp > self.cfg.max_seq_len:
+                raise ProcessingError.invalid_input(
+                    f"Sequence length {S * nc * self.cp.cp} out of range [1, {self.cfg.max_seq_len}]")
+            return B, S
         if ids.dim() == 1:
             ids = ids[None]
         B, S = ids.shape
@@ -374,9 +406,17 @@ class DecoderLM:
     def forward_hidden(self, ids: torch.Tensor, save: Optional[dict] = None) -> torch.Tensor:
         """Final-norm output ``[B*S, H]`` for ``ids [B, S]`` (int64)."""
         B, S = self._check_ids(ids)
-        x = E.embed_fwd(ids.reshape(-1), self.w["token_embed"], self._positions(S), S)
+        x = self.embed(ids, B, S)
         x = self.forward_blocks(x, B, S, save)
         return self.forward_final_norm(x, save)
+
+    def embed(self, ids: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        table = self.w["token_embed"]
+        if self.cp is None:
+            return E.embed_fwd(ids.reshape(-1), table, self._positions(S), S)
+        pe = self._positions(S * self.cp.n_chunks * self.cp.cp)
+        return torch.cat([E.embed_fwd(ids[c].reshape(-1), table, pe, S, pos_offset=off)
+                          for c, off in enumerate(self.cp.position_offsets(S))], 0)
 
     def forward_blocks(self, x: torch.Tensor, B: int, S: int, save: Optional[dict]) -> torch.Tensor:
         """This model's blocks applied to ``x [B*S, H]``."""
@@ -514,11 +554,14 @@ class DecoderLM:
             dattn = G.linear_dgrad(dx_mid, self.w[p + "attn.o_weights"], max_ctas=mc)
             qkv = a["qkv"]
             q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
-            dqkv = self._buf("dqkv", (B * S, 3 * H))
-            A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, causal=True,
-                            dqkv=dqkv)
+            dqkv = self._buf("dqkv", (dattn.shape[0], 3 * H))
+            if self.cp is not None:
+                self.cp.attention_bwd(dattn, qkv, a["attn"], a["lse"], B, S, nh, dh, dqkv=dqkv)
+            else:
+                A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, causal=True,
+                                dqkv=dqkv)
             if cfg.pos == "rope":
-                E.rope_(dqkv, 2 * nh, dh, S, theta=cfg.rope_theta, inverse=True)
+                self._rope(dqkv, B, S, True)
             G.linear_wgrad(a["n1"], dqkv, self.g[p + "attn.qkv_weights"], max_ctas=mc)
             if cfg.use_bias:
                 E.colsum_into(dqkv, self.g[p + "attn.qkv_bias"])

@@ -61,7 +61,10 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
     H = nh * dh
     if not q.is_cuda:
-        _, _, p, (qf, kf, vf) = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
+        _, lse_own, p, (qf, kf, vf) = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
+        # probabilities relative to the normaliser that was passed in (it covers more keys than
+        # these when the call is one block pair of ring attention), as the kernel computes them
+        p = p * torch.exp(lse_own - lse.float())[..., None]
         dof = do.float().reshape(B, S, nh, dh).transpose(1, 2)
         of = o.float().reshape(B, S, nh, dh).transpose(1, 2)
         dv = p.transpose(-1, -2) @ dof

@@ -33,6 +33,8 @@ from ..ops import ring as R
 
 
 class ContextParallel:
+    n_chunks = 2     # sequence chunks a rank owns (leading dimension of the ids it is given)
+
     def __init__(self, group, device, backend: Optional[str] = None,
                  wait_limit_ms: float = 5000.0) -> None:
         self.group = group

@@ -159,7 +159,7 @@ class PipelineStage:
                 if self.first:
                     flat = ids[i].reshape(-1)
                     save["ids"] = flat
-                    x = E.embed_fwd(flat, m.w["token_embed"], m._positions(S), S)
+                    x = m.embed(ids[i], b, S)
                 else:
                     x = chans["rf"].take()
                 x = m.forward_blocks(x, b, S, save)
