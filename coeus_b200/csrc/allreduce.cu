@@ -1,0 +1,183 @@
+// One-shot all-reduce over NVLink peer memory fused with the residual add and the following
+// normalisation -- the collective of tensor-parallel decoding, where the message is a few
+// hundred KB and latency is everything.
+//
+// Every rank has written its partial result [rows, H] (bf16) into a buffer that all peers have
+// mapped.  One kernel per rank then
+//   1. tells every peer "my partial of call e is ready" (st.release.sys into the peer's flags),
+//   2. waits (bounded) until all peers have said the same,
+//   3. loads the row from every rank's buffer, sums in rank order in fp32 (so all ranks get the
+//      same bits), adds the residual, stores x_out, and
+//   4. optionally normalises the row (RMSNorm or LayerNorm) into n_out.
+// The call counter e lives in device memory and is advanced by the last block, so the launch
+// parameters never change and the kernel can sit in a CUDA graph.  Callers alternate between two
+// partial buffers: a rank can only be one call ahead of a peer (step 2), so the buffer of call e
+// is not rewritten before every peer has finished reading it.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace cb {
+int sm_count();
+
+constexpr int AR_MAX_RANKS = 8;
+constexpr int AR_THREADS = 256;
+constexpr int AR_MAX_VEC = 4;   // 8-element vectors per thread: H <= 256 * 4 * 8 = 8192
+
+struct ArArgs {
+  const __nv_bfloat16* parts[AR_MAX_RANKS];
+  unsigned long long* peer_flags[AR_MAX_RANKS];   // rank s's flag array (this rank writes [rank])
+  const unsigned long long* my_flags;
+  unsigned long long* epoch;                      // completed calls on this flag array
+  unsigned int* done;                             // blocks that have finished this call
+  const __nv_bfloat16* resid;
+  __nv_bfloat16* x_out;
+  const __nv_bfloat16* scale;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* n_out;
+  int tp, rank, rows, H, rms;
+  float eps;
+  unsigned long long limit_ns;
+  int* status;
+};
+
+__global__ void __launch_bounds__(AR_THREADS) ar_resid_norm_kernel(ArArgs a) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(a.epoch) + 1ull;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < a.tp) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;"
+                 :: "l"(a.peer_flags[threadIdx.x] + a.rank), "l"(e) : "memory");
+  }
+  if (threadIdx.x < a.tp) {
+    const unsigned long long* f = a.my_flags + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    unsigned long long v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+      if (v >= e) break;
+      if ((++it & 63u) == 0u && globaltimer_ns() - t0 > a.limit_ns) {
+        record_status(a.status, ST_COMM_TIMEOUT, threadIdx.x);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_ok != 0) {
+    const int nv = a.H >> 3;
+    for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      float x[AR_MAX_VEC][8];
+      float sum = 0.f, sq = 0.f;
+#pragma unroll
+      for (int j = 0; j < AR_MAX_VEC; ++j) {
+        const int v = threadIdx.x + j * AR_THREADS;
+        if (v < nv) {
+          const size_t off = static_cast<size_t>(row) * a.H + v * 8;
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int s = 0; s < a.tp; ++s) {
+            uint4 raw;
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                         : "l"(a.parts[s] + off) : "memory");
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = __bfloat1622float2(h[q]);
+              acc[2 * q] += f.x;
+              acc[2 * q + 1] += f.y;
+            }
+          }
+          if (a.resid != nullptr) {
+            float r[8];
+            load8(a.resid + off, r);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[q] += r[q];
+          }
+          store8(a.x_out + off, acc);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {   // normalise what was stored (bf16-rounded values)
+            x[j][q] = __bfloat162float(__float2bfloat16(acc[q]));
+            sum += x[j][q];
+            sq += x[j][q] * x[j][q];
+          }
+        }
+      }
+      if (a.n_out != nullptr) {
+        float mean = 0.f, rstd;
+        if (a.rms) {
+          sq = block_sum(sq, red);
+          rstd = rsqrtf(sq / a.H + a.eps);
+        } else {
+          sum = block_sum(sum, red);
+          mean = sum / a.H;
+          float var = 0.f;
+#pragma unroll
+          for (int j = 0; j < AR_MAX_VEC; ++j)
+            if (threadIdx.x + j * AR_THREADS < nv)
+#pragma unroll
+              for (int q = 0; q < 8; ++q) var += (x[j][q] - mean) * (x[j][q] - mean);
+          var = block_sum(var, red);
+          rstd = rsqrtf(var / a.H + a.eps);
+        }
+#pragma unroll
+        for (int j = 0; j < AR_MAX_VEC; ++j) {
+          const int v = threadIdx.x + j * AR_THREADS;
+          if (v < nv) {
+            float g[8], b[8], y[8];
+            load8(a.scale + v * 8, g);
+            if (a.bias != nullptr) load8(a.bias + v * 8, b);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              y[q] = (x[j][q] - mean) * rstd * g[q] + (a.bias != nullptr ? b[q] : 0.f);
+            store8(a.n_out + static_cast<size_t>(row) * a.H + v * 8, y);
+          }
+        }
+      }
+    }
+  }
+  // the last block to finish closes the call
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(a.done, 1u);
+    if (prev == gridDim.x - 1) {
+      *a.done = 0u;
+      *reinterpret_cast<volatile unsigned long long*>(a.epoch) = e;
+      __threadfence();
+    }
+  }
+}
+}  // namespace cb
+
+// state: [0] = epoch (u64), [1] = done counter (u32 in the low half); zero before the first call
+extern "C" int cb_ar_resid_norm(void* const* parts, void* const* peer_flags, const void* my_flags,
+                                void* state, const void* resid, void* x_out, const void* scale,
+                                const void* bias, void* n_out, int tp, int rank, int rows, int H,
+                                int rms, float eps, unsigned long long limit_ns, int* status,
+                                void* stream) {
+  using namespace cb;
+  if (tp < 1 || tp > AR_MAX_RANKS || H % 8 != 0 || H > AR_THREADS * AR_MAX_VEC * 8) return -1;
+  if (rows <= 0) return 0;
+  ArArgs a;
+  for (int i = 0; i < tp; ++i) {
+    a.parts[i] = static_cast<const __nv_bfloat16*>(parts[i]);
+    a.peer_flags[i] = static_cast<unsigned long long*>(peer_flags[i]);
+  }
+  a.my_flags = static_cast<const unsigned long long*>(my_flags);
+  a.epoch = static_cast<unsigned long long*>(state);
+  a.done = reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(state) + 1);
+  a.resid = static_cast<const __nv_bfloat16*>(resid);
+  a.x_out = static_cast<__nv_bfloat16*>(x_out);
+  a.scale = static_cast<const __nv_bfloat16*>(scale);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.n_out = static_cast<__nv_bfloat16*>(n_out);
+  a.tp = tp; a.rank = rank; a.rows = rows; a.H = H; a.rms = rms; a.eps = eps;
+  a.limit_ns = limit_ns; a.status = status;
+  const int grid = rows < sm_count() * 2 ? rows : sm_count() * 2;
+  ar_resid_norm_kernel<<<grid, AR_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

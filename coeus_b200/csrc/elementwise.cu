@@ -309,7 +309,10 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restri
 // half-split convention: (x[i], x[i+dh/2]) rotated by pos * theta^(-2i/dh).  inverse = 1
 // applies the transposed rotation (the backward pass).
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, int T, int nheads, int dh, int ld,
-                            int S, int pos_offset, float theta, int inverse) {
+                            int S, int pos_offset, const int* __restrict__ pos_dev, float theta,
+                            int inverse) {
+  // pos_dev (optional): first position of every sequence, read on the device so that a captured
+  // graph can be replayed while the positions advance
   const int half = dh >> 1;
   const size_t total = static_cast<size_t>(T) * nheads * half;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -317,7 +320,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, int T, int nheads, in
     const int k = static_cast<int>(i % half);
     const int h = static_cast<int>((i / half) % nheads);
     const size_t t = i / (static_cast<size_t>(half) * nheads);
-    const int pos = static_cast<int>(t % S) + pos_offset;
+    const int pos = static_cast<int>(t % S) + (pos_dev != nullptr ? pos_dev[t / S] : pos_offset);
     const float inv_freq = __powf(theta, -2.0f * k / dh);
     float sn, cs;
     sincosf(pos * inv_freq, &sn, &cs);
@@ -487,7 +490,15 @@ extern "C" int cb_rope(void* x, int T, int nheads, int dh, int ld, int S, int po
   if (dh % 2 != 0) return -1;
   rope_kernel<<<grid_for(static_cast<size_t>(T) * nheads * (dh / 2), 256), 256, 0,
                 CB_ST(stream)>>>(static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S,
-                                 pos_offset, theta, inverse);
+                                 pos_offset, nullptr, theta, inverse);
+  CB_RET();
+}
+extern "C" int cb_rope_dev(void* x, int T, int nheads, int dh, int ld, int S, const int* pos_dev,
+                           float theta, int inverse, void* stream) {
+  if (dh % 2 != 0 || pos_dev == nullptr) return -1;
+  rope_kernel<<<grid_for(static_cast<size_t>(T) * nheads * (dh / 2), 256), 256, 0,
+                CB_ST(stream)>>>(static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S, 0, pos_dev,
+                                 theta, inverse);
   CB_RET();
 }
 extern "C" int cb_colsum(const void* x, float* out, int T, int C, int ld, void* stream) {

@@ -272,13 +272,16 @@ def softmax_rows(x: torch.Tensor) -> torch.Tensor:
 
 
 def rope_(x: torch.Tensor, nheads: int, dh: int, S: int, pos_offset: int = 0,
-          theta: float = 10000.0, inverse: bool = False) -> torch.Tensor:
+          theta: float = 10000.0, inverse: bool = False,
+          pos_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """In-place half-split rotary embedding on a ``[T, >= nheads*dh]`` view (row pitch
-    ``x.stride(0)``); position of row t is ``t % S + pos_offset``."""
+    ``x.stride(0)``); position of row t is ``t % S + pos_offset``, or ``t % S + pos_dev[t // S]``
+    when the int32 tensor ``pos_dev`` (first position of every sequence, on the device) is given."""
     T = x.shape[0]
     if not x.is_cuda:
         half = dh // 2
-        pos = ((torch.arange(T) % S) + pos_offset).float()
+        base = pos_dev.long()[torch.arange(T) // S] if pos_dev is not None else pos_offset
+        pos = ((torch.arange(T) % S) + base).float()
         inv = theta ** (-2.0 * torch.arange(half).float() / dh)
         ang = pos[:, None] * inv[None, :]
         sn, cs = torch.sin(ang)[:, None, :], torch.cos(ang)[:, None, :]
@@ -288,6 +291,12 @@ def rope_(x: torch.Tensor, nheads: int, dh: int, S: int, pos_offset: int = 0,
         a, b = xv[..., :half], xv[..., half:]
         out = torch.cat([a * cs - b * sn, a * sn + b * cs], -1).reshape(T, nheads * dh)
         x[:, :nheads * dh] = out.to(x.dtype)
+        return x
+    if pos_dev is not None:
+        assert pos_dev.dtype == torch.int32 and pos_dev.numel() * S >= T
+        rc = _lib.lib().cb_rope_dev(_lib.ptr(x), T, nheads, dh, x.stride(0), S, _lib.ptr(pos_dev),
+                                    c_float(theta), int(inverse), _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_rope_dev")
         return x
     rc = _lib.lib().cb_rope(_lib.ptr(x), T, nheads, dh, x.stride(0), S, pos_offset,
                             c_float(theta), int(inverse), _lib.stream_ptr())

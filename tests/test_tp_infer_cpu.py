@@ -1,0 +1,59 @@
+"""Tensor-parallel generation on two Gloo ranks against the single-rank engine."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _cfg():
+    from coeus_b200.models.config import DecoderConfig
+    return DecoderConfig(hidden_dim=32, num_layers=2, num_heads=4, intermediate_dim=48,
+                         vocab_size=96, max_seq_len=64, use_bias=False, activation="swiglu",
+                         norm="rmsnorm", pos="rope")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ids, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.infer.tp_engine import TPInferenceEngine
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM
+    full = DecoderLM(_cfg(), "cpu", seed=5, dtype=torch.float32, training=False)
+    tp = TensorParallel(dist.group.WORLD, "cpu", backend="nccl")
+    m = TPDecoderLM(_cfg(), tp, "cpu", dtype=torch.float32, full=full)
+    eng = TPInferenceEngine(m, max_batch=4)
+    toks = eng.generate(ids, 6)
+    out.put((rank, toks.numpy().copy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_generation_matches_single_rank_engine():
+    from coeus_b200.infer.engine import InferenceEngine
+    from coeus_b200.models.decoder import DecoderLM
+    torch.manual_seed(0)
+    ids = torch.randint(0, 96, (4, 8))
+    full = DecoderLM(_cfg(), "cpu", seed=5, dtype=torch.float32, training=False)
+    want = InferenceEngine(full, max_batch=4).generate(ids, 6)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ids, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, toks in res:
+        assert torch.equal(torch.from_numpy(toks), want), rank
