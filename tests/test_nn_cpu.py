@@ -1,0 +1,75 @@
+"""Autograd wrappers: gradients of every layer against plain PyTorch autograd on the same math
+(CPU restatement of the kernels; the GPU kernels themselves are covered by the kernel tests)."""
+import torch
+
+from coeus_b200 import nn as cnn
+from coeus_b200.nn import functional as F
+
+
+def _ref_attention(qkv, B, S, nh, dh):
+    H = nh * dh
+    q, k, v = (t.reshape(B, S, nh, dh).transpose(1, 2) for t in (qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]))
+    o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    return o.transpose(1, 2).reshape(B * S, H)
+
+
+def test_block_gradients_match_pytorch():
+    torch.manual_seed(0)
+    B, S, D, nh, I = 2, 8, 16, 2, 24
+    blk = cnn.Block(D, nh, I, rms=False, bias=True, swiglu=False, rope=False, device="cpu")
+    x = torch.randn(B * S, D, requires_grad=True)
+    y = blk(x, B, S)
+    y.square().sum().backward()
+    got = {n: p.grad.clone() for n, p in blk.named_parameters()}
+    gx = x.grad.clone()
+    # the same block written with stock PyTorch ops
+    x2 = x.detach().clone().requires_grad_(True)
+    p = {n: t.detach().clone().requires_grad_(True) for n, t in blk.named_parameters()}
+    ln = torch.nn.functional.layer_norm
+    n1 = ln(x2, (D,), p["norm1.scale"], p["norm1.bias"], 1e-5)
+    qkv = n1 @ p["attn.qkv.weight"] + p["attn.qkv.bias"]
+    a = _ref_attention(qkv, B, S, nh, D // nh) @ p["attn.o.weight"] + p["attn.o.bias"]
+    xm = x2 + a
+    n2 = ln(xm, (D,), p["norm2.scale"], p["norm2.bias"], 1e-5)
+    h = torch.nn.functional.gelu(n2 @ p["mlp.up.weight"] + p["mlp.up.bias"], approximate="tanh")
+    out = xm + h @ p["mlp.down.weight"] + p["mlp.down.bias"]
+    out.square().sum().backward()
+    assert (y - out).abs().max() < 1e-4
+    assert (gx - x2.grad).abs().max() < 1e-3
+    for n in got:
+        assert (got[n] - p[n].grad).abs().max() < 1e-3 * max(1.0, p[n].grad.abs().max()), n
+
+
+def test_swiglu_rope_rms_embedding_and_loss():
+    torch.manual_seed(1)
+    B, S, D, nh, V = 2, 8, 16, 2, 40
+    emb = cnn.Embedding(V, D, device="cpu")
+    blk = cnn.Block(D, nh, 24, rms=True, bias=False, swiglu=True, rope=True, device="cpu")
+    head = cnn.Linear(D, V, bias=False, device="cpu")
+    with torch.no_grad():       # larger weights: gradients well above fp32 rounding of the loss
+        for prm in list(blk.parameters()) + [head.weight, emb.weight]:
+            if prm.dim() == 2:
+                prm.mul_(10.0)
+    ids = torch.randint(0, V, (B, S))
+    tgt = torch.randint(0, V, (B, S))
+    loss = cnn.CrossEntropyLoss()(head(blk(emb(ids), B, S)), tgt)
+    loss.backward()
+    # finite differences along the gradient of a few parameters
+    for prm in (emb.weight, blk.attn.qkv.weight, blk.mlp.up.weight, blk.norm2.scale, head.weight):
+        g = prm.grad.clone()
+        d = g / g.norm()
+        eps = 2e-3
+        with torch.no_grad():
+            prm.add_(eps * d); lp = float(cnn.CrossEntropyLoss()(head(blk(emb(ids), B, S)), tgt))
+            prm.sub_(2 * eps * d); lm = float(cnn.CrossEntropyLoss()(head(blk(emb(ids), B, S)), tgt))
+            prm.add_(eps * d)
+        fd = (lp - lm) / (2 * eps)
+        assert abs(fd - float(g.norm())) < 3e-2 * float(g.norm()) + 1e-5
+
+
+def test_functional_softmax_and_gelu_values():
+    # unit values the reference tests (plugins/model-transformer/src/lib.rs:1153-1192)
+    s = F.softmax(torch.tensor([[1.0, 2.0, 3.0]]))
+    assert abs(float(s.sum()) - 1.0) < 1e-6 and s[0, 2] > s[0, 1] > s[0, 0]
+    assert abs(float(F.gelu(torch.tensor([[0.0]])))) < 1e-6
+    assert float(F.gelu(torch.tensor([[1.0]]))) > 0 > float(F.gelu(torch.tensor([[-1.0]])))
