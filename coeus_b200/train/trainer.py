@@ -90,3 +90,90 @@ class Trainer:
     # ---- Checkpoint trait (src/core/traits.rs:181-189)
     def state_dict(self) -> Dict[str, object]:
         return {"p32": self.model.p32, "opt": self.opt.state_dict(), "step": self.step_index}
+
+    # ---- sharded checkpoints (resume on any number of ranks)
+    def _owned_segments(self):
+        m = self.model
+        if self.dp is None:
+            return [(0, m.n_flat)]
+        return [b.shard(self.dp.rank, self.dp.world) for b in self.dp.buckets]
+
+    def _moment_view(self, name: str, s: int, e: int) -> torch.Tensor:
+        """The ``[s, e)`` slice of Adam's ``m`` or ``v`` (flat coordinates)."""
+        if self.dp is None:
+            return getattr(self.opt, name)[s:e]
+        for b, off in zip(self.dp.buckets, self.dp.moffs):
+            bs, be = b.shard(self.dp.rank, self.dp.world)
+            if bs <= s and e <= be:
+                return getattr(self.opt, name)[off + s - bs: off + e - bs]
+        raise KeyError(f"range [{s}, {e}) is not owned by this rank")
+
+    def save_checkpoint(self, directory: str, data_cursor: int = 0, background: bool = False) -> None:
+        """Write this rank's shard (fp32 master weights and Adam moments of the ranges it owns)
+        and, on rank 0, the manifest.  ``background=True`` returns once the device-to-host copies
+        are enqueued; :meth:`wait_checkpoint` finishes the job."""
+        import random
+
+        import torch.distributed as dist
+
+        from ..checkpoint import sharded as S
+        m = self.model
+        rank = 0 if self.dp is None else self.dp.rank
+        world = 1 if self.dp is None else self.dp.world
+        if self.dp is not None:
+            self.dp.finish()
+
+        def fetch(name, s, e):
+            return m.p32[s:e] if name == "p32" else self._moment_view(name, s, e)
+
+        meta = {"config": m.cfg.to_dict(), "n_flat": m.n_flat, "data_cursor": data_cursor,
+                "opt_step": self.opt.step_count, "train_step": self.step_index,
+                "python_rng": repr(random.getstate()[1][:4])}
+        barrier = (lambda: dist.barrier(group=self.dp.group)) if self.dp is not None else None
+        if background:
+            if not hasattr(self, "_ckpt_writer"):
+                self._ckpt_writer = S.AsyncWriter()
+            self._ckpt_pending = (directory, world, self.step_index, meta, barrier, rank)
+            S.save_shard(directory, rank, world, self._owned_segments(), fetch, self.step_index,
+                         meta, writer=self._ckpt_writer)
+        else:
+            S.save_shard(directory, rank, world, self._owned_segments(), fetch, self.step_index,
+                         meta, barrier=barrier)
+        for fn in self.listeners:
+            fn({"event": "PersistenceEvent::Saved", "path": directory, "step": self.step_index})
+
+    def wait_checkpoint(self) -> None:
+        """Finish a background save: join the writer, then write the manifest on rank 0."""
+        from ..checkpoint import sharded as S
+        pend = getattr(self, "_ckpt_pending", None)
+        if pend is None:
+            return
+        directory, world, step, meta, barrier, rank = pend
+        self._ckpt_writer.wait()
+        if barrier is not None:
+            barrier()
+        if rank == 0:
+            S.finalize_manifest(directory, world, step, meta)
+        if barrier is not None:
+            barrier()
+        self._ckpt_pending = None
+
+    def load_checkpoint(self, directory: str) -> dict:
+        """Restore weights (all of them, every rank needs the full working copy) and the Adam
+        moments of the ranges this rank owns now, whatever the world size at save time was."""
+        from ..checkpoint import sharded as S
+        m = self.model
+
+        def put_w(name, s, e, t):
+            m.p32[s:e].copy_(t)
+
+        def put_m(name, s, e, t):
+            self._moment_view(name, s, e).copy_(t)
+
+        man = S.load_ranges(directory, [(0, m.n_flat)], put_w, state_names=("p32",))
+        S.load_ranges(directory, self._owned_segments(), put_m, verify=False, state_names=("m", "v"))
+        m.sync_working_copy()
+        meta = man["meta"]
+        self.opt.step_count = int(meta["opt_step"])
+        self.step_index = int(meta["train_step"])
+        return meta
