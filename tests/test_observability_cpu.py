@@ -1,0 +1,70 @@
+"""Tracing, metrics, health and events on CPU."""
+import json
+
+import torch
+
+from coeus_b200.utils.metrics import (EventBus, JsonlSink, TrainerMonitor, device_memory_stats,
+                                      model_flops_per_token)
+from coeus_b200.utils.tracing import PhaseTimer, nvtx_range
+
+
+def _trainer():
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.train.trainer import TrainConfig, Trainer
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    return Trainer(DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32), TrainConfig(learning_rate=1e-2))
+
+
+def test_phase_timer_and_nvtx_are_usable_without_a_gpu():
+    t = PhaseTimer("cpu")
+    with nvtx_range("outer"):
+        with t.phase("a"):
+            sum(range(1000))
+        with t.phase("a"):
+            pass
+        with t.phase("b"):
+            pass
+    s = t.summary()
+    assert set(s) == {"a", "b"} and s["a"] >= 0 and t.counts() == {"a": 2, "b": 1}
+    assert t.summary() == {}
+
+
+def test_monitor_metrics_health_and_events(tmp_path):
+    tr = _trainer()
+    bus = EventBus()
+    seen = []
+    bus.subscribe(seen.append)
+    sink = JsonlSink(str(tmp_path / "events.jsonl"))
+    bus.subscribe(sink)
+    mon = TrainerMonitor(tr, seq_len=16, peak_tflops=1.0, bus=bus)
+    def batches():
+        g = torch.Generator().manual_seed(0)       # the same three batches every epoch
+        for _ in range(3):
+            b = torch.randint(0, 64, (2, 17), generator=g)
+            yield b[:, :-1].contiguous(), b[:, 1:].contiguous()
+
+    mon.fit(batches, epochs=2)
+    sink.close()
+    kinds = [e["event"] for e in seen]
+    assert kinds == ["TrainingEvent::Started", "TrainingEvent::EpochCompleted",
+                     "TrainingEvent::EpochCompleted"]
+    m = {x.name: x.value for x in mon.metrics()}
+    assert m["steps"] == 6 and m["tokens"] == 6 * 32 and m["tokens_per_s"] > 0 and m["mfu"] > 0
+    assert seen[2]["mean_loss"] < seen[1]["mean_loss"]          # it learns the repeated stream
+    assert mon.health().healthy
+    lines = [json.loads(l) for l in open(tmp_path / "events.jsonl")]
+    assert len(lines) == 3
+    mon.reset_metrics()
+    assert {x.name: x.value for x in mon.metrics()}["steps"] == 0
+
+
+def test_flops_model_and_memory_stats_shape():
+    from coeus_b200.models.config import DecoderConfig
+    cfg = DecoderConfig.transformer_250m()
+    f = model_flops_per_token(cfg, 2048, True)
+    n_matrix = 16 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 1024 * 32000
+    assert f > 6 * n_matrix and f < 8 * n_matrix
+    st = device_memory_stats("cpu")
+    assert st.used_bytes == 0 and st.fragmentation_ratio() == 0.0
