@@ -129,16 +129,8 @@ def test_sequence_parallel_transports_on_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = q.get(timeout=600)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from mp_util import run_ranks
+    res = run_ranks(_worker, world, ())[0]
     l0, g0 = res["plain"]
     for key in ("ring:p2p", "ring:collective", "ulysses:p2p", "ulysses:collective"):
         l, g = res[key]

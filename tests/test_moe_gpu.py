@@ -121,16 +121,8 @@ def test_fused_expert_exchange_matches_all_to_all():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 4 if torch.cuda.device_count() >= 4 else 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = q.get(timeout=600)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from mp_util import run_ranks
+    res = run_ranks(_worker, world, ())[0]
     for it in range(3):
         f, n = res[f"fused{it}"], res[f"nccl{it}"]
         assert torch.equal(f["o"], n["o"])       # same GEMMs on the same rows

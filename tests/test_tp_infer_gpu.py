@@ -124,16 +124,8 @@ def test_tp_engine_on_two_gpus():
         pytest.skip("needs two GPUs")
     torch.manual_seed(0)
     ids = torch.randint(0, 1000, (8, 256))
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, ids, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = q.get(timeout=600)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from mp_util import run_ranks
+    res = run_ranks(_worker, 2, (ids,))[0]
     # the three tensor-parallel variants run the same arithmetic in the same order
     assert torch.equal(res["graph"], res["eager"])
     assert torch.equal(res["graph"][:, :256], res["single"][:, :256])
