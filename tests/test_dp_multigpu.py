@@ -49,16 +49,8 @@ def _worker(rank, world, port, backend, out):
 
 
 def _run(backend, world=2):
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, backend, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = q.get(timeout=600)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from mp_util import run_ranks
+    res = run_ranks(_worker, world, (backend,))[0]
     return res
 
 

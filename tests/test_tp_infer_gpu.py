@@ -78,7 +78,7 @@ def test_allreduce_wait_runs_out_when_a_peer_never_signals():
 def _cfg():
     from coeus_b200.models.config import DecoderConfig
     return DecoderConfig(hidden_dim=512, num_layers=2, num_heads=8, intermediate_dim=1024,
-                         vocab_size=1000, max_seq_len=512, use_bias=False, activation="swiglu",
+                         vocab_size=1024, max_seq_len=512, use_bias=False, activation="swiglu",
                          norm="rmsnorm", pos="rope")
 
 
@@ -123,7 +123,7 @@ def test_tp_engine_on_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     torch.manual_seed(0)
-    ids = torch.randint(0, 1000, (8, 256))
+    ids = torch.randint(0, 1024, (8, 256))
     from mp_util import run_ranks
     res = run_ranks(_worker, 2, (ids,))[0]
     # the three tensor-parallel variants run the same arithmetic in the same order

@@ -61,16 +61,8 @@ def _worker(rank, world, port, out):
 def test_fused_tp_kernels_match_nccl():
     world = min(torch.cuda.device_count(), 4)
     world = 2 if world < 4 else world
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = q.get(timeout=600)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from mp_util import run_ranks
+    res = run_ranks(_worker, world, ())[0]
     for it in range(3):
         assert torch.equal(res[f"xg_f{it}"], res[f"xg_r{it}"])          # the gather is bitwise
         assert torch.equal(res[f"ag_f{it}"], res[f"ag_r{it}"])          # same GEMM on same data
@@ -125,16 +117,8 @@ def _model_worker(rank, world, port, out):
 
 
 def test_tp_model_matches_single_gpu():
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_model_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = q.get(timeout=600)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from mp_util import run_ranks
+    res = run_ranks(_model_worker, 2, ())[0]
     for b in ("fused", "nccl"):
         assert abs(res[b] - res["ref"]) < 0.03, res
         assert res[b + "_gerr"] < 0.06 and res[b + "_embed"] < 0.06, res
