@@ -41,6 +41,9 @@ class TPInferenceEngine:
         self.ar = FusedAllReduce(self.tp.group, self.device, max_batch, self.cfg.hidden_dim,
                                  backend=ar_backend, dtype=model.p16.dtype)
         self.cache: Optional[PagedKVCache] = None
+        # positions live in buffers that are never reallocated: a captured graph reads them
+        self._pos_buf = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self._ctx_buf = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
         self._graph = None
         self._graph_B = 0
         self.stats: Dict[str, float] = {}
@@ -114,8 +117,11 @@ class TPInferenceEngine:
             last[mine] = x[(t_last[mine] - r * Ts)]
         if n > 1:
             dist.all_reduce(last, group=tp.group)
-        self._pos0 = torch.full((B,), S, dtype=torch.int32, device=self.device)
-        self._ctx = torch.full((B,), S, dtype=torch.int32, device=self.device)
+        if B > self.max_batch:
+            raise ProcessingError.limit_exceeded("batch size", self.max_batch, B)
+        self._pos0, self._ctx = self._pos_buf[:B], self._ctx_buf[:B]
+        self._pos0.fill_(S)
+        self._ctx.fill_(S)
         self._pos_host = S
         xf = self._norm(last, "final_norm")
         return G.gemm(xf, m.w["output_proj"], b_mn=True)

@@ -110,6 +110,8 @@ def _worker(rank, world, port, ids, out):
                      ("nccl", dict(use_graph=False, ar_backend="nccl"))):
         eng = TPInferenceEngine(m, max_batch=8, **kw)
         res[name] = eng.generate(ids, 12).cpu()
+        if name == "graph":      # a second request replays the graph captured by the first
+            res["graph_again"] = eng.generate(ids, 12).cpu()
     torch.cuda.synchronize()
     _lib.check_status(dev)
     if rank == 0:
@@ -128,6 +130,7 @@ def test_tp_engine_on_two_gpus():
     res = run_ranks(_worker, 2, (ids,))[0]
     # the three tensor-parallel variants run the same arithmetic in the same order
     assert torch.equal(res["graph"], res["eager"])
+    assert torch.equal(res["graph"], res["graph_again"])
     assert torch.equal(res["graph"][:, :256], res["single"][:, :256])
     # against one GPU the split contractions round differently: random-init logits are nearly
     # flat, so compare the first generated tokens only, and allow a few to differ
