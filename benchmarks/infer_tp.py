@@ -91,6 +91,8 @@ def main() -> int:
                           "prefill_tokens_per_s": round(a.batch * a.prompt / pf * 1e3, 1),
                           "decode_ms_per_step": round(dc / (a.new - 1), 4),
                           "decode_tokens_per_s": round(a.batch * (a.new - 1) / dc * 1e3, 1)}))
+    eng.close()
+    torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
     return 0

@@ -181,3 +181,129 @@ extern "C" int cb_ar_resid_norm(void* const* parts, void* const* peer_flags, con
   ar_resid_norm_kernel<<<grid, AR_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// ------------------------------------------------------------------------------------------
+// Greedy token selection over a vocabulary that is split across ranks, without a library
+// collective: block b finds the arg-max of row b of this rank's logits slice, stores the pair
+// (value, global index) into slot [rank][b] of EVERY rank's pair table, raises the slot's flag,
+// waits (bounded) for the slots of all ranks and keeps the best pair (lowest rank wins ties,
+// which is the first index, as one arg-max over the whole row would give).  Same call counter
+// scheme as the all-reduce above.
+namespace cb {
+
+struct GreedyArgs {
+  const __nv_bfloat16* logits;   // [B, ld]
+  int ld, valid, col0;           // columns that compete; global index of column 0
+  unsigned long long* pairs[AR_MAX_RANKS];   // rank s's table: [tp][B] packed (value bits << 32 | index)
+  unsigned long long* flags[AR_MAX_RANKS];   // rank s's flags: [tp][B] call numbers
+  unsigned long long* epoch;
+  unsigned int* done;
+  long long* out;                // [B] chosen token ids
+  int tp, rank, B;
+  unsigned long long limit_ns;
+  int* status;
+};
+
+__global__ void __launch_bounds__(AR_THREADS) greedy_select_kernel(GreedyArgs a) {
+  __shared__ float s_val[AR_THREADS / 32];
+  __shared__ int s_idx[AR_THREADS / 32];
+  __shared__ unsigned long long s_pair[AR_MAX_RANKS];
+  __shared__ int s_ok;
+  const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(a.epoch) + 1ull;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) s_ok = 1;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  const __nv_bfloat16* row = a.logits + static_cast<size_t>(b) * a.ld;
+  for (int c = threadIdx.x; c < a.valid; c += AR_THREADS) {
+    const float v = __bfloat162float(row[c]);
+    if (v > best || (v == best && c < bi)) { best = v; bi = c; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < AR_THREADS / 32; ++w)
+      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < bi)) { best = s_val[w]; bi = s_idx[w]; }
+    const unsigned long long packed =
+        (static_cast<unsigned long long>(__float_as_uint(best)) << 32) |
+        static_cast<unsigned int>(a.valid > 0 ? bi + a.col0 : 0x7fffffff);
+    s_pair[0] = packed;
+  }
+  __syncthreads();
+  if (threadIdx.x < a.tp) {      // one thread per destination rank
+    const size_t slot = static_cast<size_t>(a.rank) * a.B + b;
+    unsigned long long* dp = a.pairs[threadIdx.x] + slot;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(dp), "l"(s_pair[0]) : "memory");
+    asm volatile("st.release.sys.global.u64 [%0], %1;"
+                 :: "l"(a.flags[threadIdx.x] + slot), "l"(e) : "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x < a.tp) {      // one thread per source rank
+    const size_t slot = static_cast<size_t>(threadIdx.x) * a.B + b;
+    const unsigned long long* f = a.flags[a.rank] + slot;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    unsigned long long v;
+    bool ok = true;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+      if (v >= e) break;
+      if ((++it & 63u) == 0u && globaltimer_ns() - t0 > a.limit_ns) {
+        record_status(a.status, ST_COMM_TIMEOUT, threadIdx.x);
+        s_ok = 0;
+        ok = false;
+        break;
+      }
+    }
+    unsigned long long p = 0;
+    if (ok) asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(p) : "l"(a.pairs[a.rank] + slot) : "memory");
+    s_pair[threadIdx.x] = p;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_ok != 0) {
+      float bv = -INFINITY;
+      long long bidx = 0;
+      for (int s = 0; s < a.tp; ++s) {
+        const float v = __uint_as_float(static_cast<unsigned int>(s_pair[s] >> 32));
+        const unsigned int idx = static_cast<unsigned int>(s_pair[s] & 0xffffffffull);
+        if (idx != 0x7fffffffu && (s == 0 || v > bv)) { bv = v; bidx = idx; }
+      }
+      a.out[b] = bidx;
+    }
+    __threadfence();
+    const unsigned int prev = atomicAdd(a.done, 1u);
+    if (prev == gridDim.x - 1) {
+      *a.done = 0u;
+      *reinterpret_cast<volatile unsigned long long*>(a.epoch) = e;
+      __threadfence();
+    }
+  }
+}
+}  // namespace cb
+
+extern "C" int cb_greedy_select(const void* logits, int ld, int valid, int col0,
+                                void* const* pairs, void* const* flags, void* state, void* out,
+                                int tp, int rank, int B, unsigned long long limit_ns, int* status,
+                                void* stream) {
+  using namespace cb;
+  if (tp < 1 || tp > AR_MAX_RANKS || B <= 0) return -1;
+  GreedyArgs a;
+  a.logits = static_cast<const __nv_bfloat16*>(logits);
+  a.ld = ld; a.valid = valid; a.col0 = col0;
+  for (int i = 0; i < tp; ++i) {
+    a.pairs[i] = static_cast<unsigned long long*>(pairs[i]);
+    a.flags[i] = static_cast<unsigned long long*>(flags[i]);
+  }
+  a.epoch = static_cast<unsigned long long*>(state);
+  a.done = reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(state) + 1);
+  a.out = static_cast<long long*>(out);
+  a.tp = tp; a.rank = rank; a.B = B; a.limit_ns = limit_ns; a.status = status;
+  greedy_select_kernel<<<B, AR_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

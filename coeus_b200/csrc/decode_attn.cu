@@ -39,28 +39,65 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   for (int e = 0; e < 8; ++e) qv[e] *= scale_log2;
   float m = -INFINITY, l = 0.f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int* pt = page_table + static_cast<size_t>(b) * max_pages;
-  for (int tb = t0; tb < t1; tb += GROUPS) {  // same trip count for every lane of a warp
-    const int t = tb + g;
-    const bool act = t < t1;
-    float kv[8], vv[8];
-    float s = 0.f;
-    if (act) {
-      const int page = pt[t / KV_PAGE];
-      const size_t off =
-          ((static_cast<size_t>(page) * KV_PAGE + (t % KV_PAGE)) * nh + h) * DH + part * 8;
-      load8(k_cache + off, kv);
-      load8(v_cache + off, vv);
+  // U tokens per thread group and iteration: all their K and V loads are issued before any of
+  // them is used (the kernel lives on bytes in flight), one running-max update per chunk.
+  constexpr int U = 8;
+  for (int tb = t0; tb < t1; tb += GROUPS * U) {  // same trip count for every lane of a warp
+    uint4 kr[U], vr[U];
+    bool act[U];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s += qv[e] * kv[e];
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + g + u * GROUPS;
+      act[u] = t < t1;
+      kr[u] = make_uint4(0u, 0u, 0u, 0u);
+      vr[u] = kr[u];
+      if (act[u]) {
+        const int page = pt[t / KV_PAGE];
+        const size_t off =
+            ((static_cast<size_t>(page) * KV_PAGE + (t % KV_PAGE)) * nh + h) * DH + part * 8;
+        kr[u] = __ldg(reinterpret_cast<const uint4*>(k_cache + off));
+        vr[u] = __ldg(reinterpret_cast<const uint4*>(v_cache + off));
+      }
+    }
+    float s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kr[u]);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(kh[e]);
+        d += qv[2 * e] * f.x + qv[2 * e + 1] * f.y;
+      }
+      s[u] = d;
     }
 #pragma unroll
-    for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (act) {
-      const float mn = fmaxf(m, s);
-      const float c = fast_exp2(m - mn), p = fast_exp2(s - mn);
-      l = l * c + p;
+    for (int o = LPT / 2; o > 0; o >>= 1)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = acc[e] * c + p * vv[e];
+      for (int u = 0; u < U; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+    float mx = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (act[u]) mx = fmaxf(mx, s[u]);
+    const float mn = fmaxf(m, mx);
+    if (mn != -INFINITY) {
+      const float c = fast_exp2(m - mn);     // m = -inf on the first chunk: c = 0
+      l *= c;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= c;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (act[u]) {
+          const float p = fast_exp2(s[u] - mn);
+          l += p;
+          const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vr[u]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(vh[e]);
+            acc[2 * e] += p * f.x;
+            acc[2 * e + 1] += p * f.y;
+          }
+        }
+      }
       m = mn;
     }
   }

@@ -25,7 +25,7 @@ from .sampler import select
 
 class InferenceEngine:
     def __init__(self, model: DecoderLM, max_batch: int = 64, max_len: Optional[int] = None,
-                 decode_splits: int = 1) -> None:
+                 decode_splits: int = 0) -> None:
         self.m = model
         self.cfg = model.cfg
         self.max_batch = max_batch

@@ -31,7 +31,7 @@ from .kv_cache import PagedKVCache
 
 class TPInferenceEngine:
     def __init__(self, model: TPDecoderLM, max_batch: int = 64, use_graph: Optional[bool] = None,
-                 ar_backend: Optional[str] = None, decode_splits: int = 1) -> None:
+                 ar_backend: Optional[str] = None, decode_splits: int = 0) -> None:
         self.m, self.cfg, self.tp = model, model.cfg, model.tp
         self.device = model.device
         self.max_batch = max_batch
@@ -40,6 +40,10 @@ class TPInferenceEngine:
         self.use_graph = (cuda and self.cfg.pos != "sinusoidal") if use_graph is None else use_graph
         self.ar = FusedAllReduce(self.tp.group, self.device, max_batch, self.cfg.hidden_dim,
                                  backend=ar_backend, dtype=model.p16.dtype)
+        self._select = None
+        if self.ar.backend == "fused":
+            from ..parallel.allreduce import GreedySelect
+            self._select = GreedySelect(self.tp.group, self.device, max_batch)
         self.cache: Optional[PagedKVCache] = None
         # positions live in buffers that are never reallocated: a captured graph reads them
         self._pos_buf = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
@@ -167,6 +171,8 @@ class TPInferenceEngine:
         B = logits_l.shape[0]
         V, Vl = self.cfg.vocab_size, m.Vl
         valid = min(Vl, max(0, V - m.rank * Vl))        # padding columns do not compete
+        if self._select is not None and (self._select._batch in (None, B)):
+            return self._select.select(logits_l, valid, m.rank * Vl)
         idx = D.argmax_rows(logits_l[:, :valid]) if valid > 0 else \
             torch.zeros(B, dtype=torch.int64, device=logits_l.device)
         val = logits_l.float().gather(1, idx[:, None])[:, 0] if valid > 0 else \
@@ -209,6 +215,11 @@ class TPInferenceEngine:
         self._graph.replay()
         self._pos_host += 1
         return self._graph_out.clone()
+
+    def close(self) -> None:
+        """Drop the captured graph (before the process group is destroyed)."""
+        self._graph = None
+        self._graph_out = None
 
     def generate(self, ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
         """Greedy generation: ``[B, S] -> [B, S + max_new_tokens]`` (identical on every rank)."""

@@ -41,8 +41,15 @@ def kv_write(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: t
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      page_table: torch.Tensor, ctx_len: torch.Tensor, nh: int, dh: int,
                      scale: Optional[float] = None, splits: int = 1) -> torch.Tensor:
-    """``q`` is a ``[B, nh*dh]`` view; returns ``[B, nh*dh]``."""
+    """``q`` is a ``[B, nh*dh]`` view; returns ``[B, nh*dh]``.  ``splits`` cuts every context
+    into that many pieces handled by separate CTAs and merged afterwards; ``0`` picks the count
+    that gives about four CTAs per SM (bounded so that a piece keeps at least 256 tokens of the
+    longest context the page table allows)."""
     B = q.shape[0]
+    if splits <= 0:
+        ctas = max(1, B * nh)
+        splits = max(1, min(16, (4 * 148 + ctas - 1) // ctas,
+                            (page_table.shape[1] * PAGE) // 256 or 1))
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
     if not q.is_cuda:
         out = torch.zeros((B, nh * dh), dtype=q.dtype)

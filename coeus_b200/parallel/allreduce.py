@@ -77,3 +77,42 @@ class FusedAllReduce:
             ctypes.c_ulonglong(self.limit_ns), _lib.ptr(st), _lib.stream_ptr())
         _lib.check_rc(rc, "cb_ar_resid_norm")
         return x, n
+
+
+class GreedySelect:
+    """Arg-max over a vocabulary split across ranks (``csrc/allreduce.cu: greedy_select``): each
+    rank pushes one (value, index) pair per sequence into every peer's table over NVLink and picks
+    the best of all ranks -- no library collective, fixed launch parameters (graph-replayable)."""
+
+    def __init__(self, group, device, max_batch: int, wait_limit_ms: float = 5000.0) -> None:
+        from .symm import SymmetricBuffer
+        self.group, self.device = group, torch.device(device)
+        self.rank, self.tp = dist.get_rank(group), dist.get_world_size(group)
+        self.max_batch = max_batch
+        self.limit_ns = int(wait_limit_ms * 1e6)
+        n = self.tp * max_batch * 8
+        self._pairs = SymmetricBuffer(n, group, self.device)
+        self._flags = SymmetricBuffer(n, group, self.device)
+        self._flags.local.zero_()
+        self._state = torch.zeros(2, dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+        self._pair_ptrs, self._flag_ptrs = self._pairs.ptr_array(), self._flags.ptr_array()
+        self._batch = None
+
+    def select(self, logits_l: torch.Tensor, valid: int, col0: int) -> torch.Tensor:
+        """``logits_l [B, >=valid]`` bf16 (this rank's columns, the first ``valid`` compete,
+        column 0 is token ``col0``) -> chosen token ids ``[B]`` int64, identical on all ranks."""
+        B = logits_l.shape[0]
+        if self._batch is None:
+            self._batch = B          # the slot layout [tp][B] is fixed by the first call
+        if B != self._batch or B > self.max_batch:
+            raise ValueError("GreedySelect is bound to the batch size of its first call")
+        out = torch.empty(B, dtype=torch.int64, device=self.device)
+        st = _lib.status_buffer(self.device)
+        rc = _lib.lib().cb_greedy_select(
+            _lib.ptr(logits_l), logits_l.stride(0), valid, col0, self._pair_ptrs, self._flag_ptrs,
+            _lib.ptr(self._state), _lib.ptr(out), self.tp, self.rank, B,
+            ctypes.c_ulonglong(self.limit_ns), _lib.ptr(st), _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_greedy_select")
+        return out

@@ -112,6 +112,7 @@ def _worker(rank, world, port, ids, out):
         res[name] = eng.generate(ids, 12).cpu()
         if name == "graph":      # a second request replays the graph captured by the first
             res["graph_again"] = eng.generate(ids, 12).cpu()
+        eng.close()
     torch.cuda.synchronize()
     _lib.check_status(dev)
     if rank == 0:
