@@ -40,7 +40,7 @@ def kv_write(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: t
 
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      page_table: torch.Tensor, ctx_len: torch.Tensor, nh: int, dh: int,
-                     scale: Optional[float] = None, splits: int = 1) -> torch.Tensor:
+                     scale: Optional[float] = None, splits: int = 0) -> torch.Tensor:
     """``q`` is a ``[B, nh*dh]`` view; returns ``[B, nh*dh]``.  ``splits`` cuts every context
     into that many pieces handled by separate CTAs and merged afterwards; ``0`` picks the count
     that gives about four CTAs per SM (bounded so that a piece keeps at least 256 tokens of the
