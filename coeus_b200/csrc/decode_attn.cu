@@ -19,7 +19,7 @@ constexpr int KV_PAGE = 64;
 constexpr int DEC_THREADS = 128;
 
 template <int DH>
-__global__ void __launch_bounds__(DEC_THREADS, 6)
+__global__ void __launch_bounds__(DEC_THREADS)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
                    const __nv_bfloat16* __restrict__ k_cache,
                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table,
