@@ -25,7 +25,10 @@ from .sampler import select
 
 class InferenceEngine:
     def __init__(self, model: DecoderLM, max_batch: int = 64, max_len: Optional[int] = None,
-                 decode_splits: int = 0) -> None:
+                 decode_splits: int = 0, use_graph: Optional[bool] = None) -> None:
+        """``use_graph``: capture the decode step in a CUDA graph and replay it per token (default:
+        on for CUDA models whose positions are not taken from a host-indexed table).  Positions
+        then live in device buffers that are never reallocated."""
         self.m = model
         self.cfg = model.cfg
         self.max_batch = max_batch
@@ -33,6 +36,12 @@ class InferenceEngine:
         self.decode_splits = decode_splits
         self.cache: Optional[PagedKVCache] = None
         self.stats: Dict[str, float] = {}
+        cuda = model.device.type == "cuda"
+        self.use_graph = (cuda and self.cfg.pos != "sinusoidal") if use_graph is None else use_graph
+        self._pos_buf = torch.zeros(max_batch, dtype=torch.int32, device=model.device)
+        self._ctx_buf = torch.zeros(max_batch, dtype=torch.int32, device=model.device)
+        self._graph = None
+        self._graph_B = 0
 
     # ------------------------------------------------------------------ building blocks
     def _ensure_cache(self, B: int, total: int) -> PagedKVCache:
@@ -41,6 +50,7 @@ class InferenceEngine:
         if c is None or c.page_table.shape[0] < B or c.page_table.shape[1] < need_pages:
             c = PagedKVCache.for_model(self.cfg, max(B, 1), max(total, D.PAGE), self.m.device)
             self.cache = c
+            self._graph = None
         for b in list(c.owned):
             c.release(b)
         for b in range(B):
@@ -64,7 +74,8 @@ class InferenceEngine:
         return G.linear_fwd(act, m.w[p + "ff.down_weights"], bias("ff.down_bias"), resid=resid)
 
     def _layers(self, x: torch.Tensor, B: int, S: int, pos0: torch.Tensor, pos0_host: int,
-                cache: PagedKVCache, prefill: bool) -> torch.Tensor:
+                cache: PagedKVCache, prefill: bool, pos_dev: Optional[torch.Tensor] = None
+                ) -> torch.Tensor:
         m, cfg = self.m, self.cfg
         H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
         n1n, n2n, _ = m.layout.norm_names
@@ -74,7 +85,8 @@ class InferenceEngine:
             n1 = self._norm(x, p + n1n)
             qkv = G.linear_fwd(n1, m.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"))
             if cfg.pos == "rope":
-                E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos0_host, theta=cfg.rope_theta)
+                E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos0_host, theta=cfg.rope_theta,
+                        pos_dev=pos_dev)
             q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
             D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, nh, dh)
             if prefill:
@@ -103,22 +115,57 @@ class InferenceEngine:
         x = E.embed_fwd(ids.reshape(-1), m.w["token_embed"], m._positions(max(S, total_len)), S)
         x = self._layers(x, B, S, pos0, 0, cache, prefill=True)
         last = x.view(B, S, -1)[:, -1, :].contiguous()
+        if B > self.max_batch:
+            raise ProcessingError.limit_exceeded("batch size", self.max_batch, B)
         self._pos = S
-        self._ctx = torch.full((B,), S, dtype=torch.int32, device=m.device)
+        self._pos0, self._ctx = self._pos_buf[:B], self._ctx_buf[:B]
+        self._pos0.fill_(S)
+        self._ctx.fill_(S)
         return self._logits(last)
 
-    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
-        """Feeds one token per sequence (``[B]`` int64) at the next position; returns ``[B, V]``."""
+    def _decode_body(self, tokens: torch.Tensor) -> torch.Tensor:
+        """One token per sequence at the device-side position; advances the positions."""
         m, cfg = self.m, self.cfg
         B = tokens.shape[0]
         pos = self._pos
-        pos0 = torch.full((B,), pos, dtype=torch.int32, device=m.device)
-        pe = m._positions(pos + 1)
-        x = E.embed_fwd(tokens, m.w["token_embed"], pe, 1, pos_offset=pos)
-        self._ctx = torch.full((B,), pos + 1, dtype=torch.int32, device=m.device)
-        x = self._layers(x, B, 1, pos0, pos, self.cache, prefill=False)
-        self._pos = pos + 1
+        if cfg.pos == "sinusoidal":
+            x = E.embed_fwd(tokens, m.w["token_embed"], m._positions(pos + 1), 1, pos_offset=pos)
+        else:
+            x = E.embed_fwd(tokens, m.w["token_embed"], None, 1)
+        self._ctx.add_(1)
+        x = self._layers(x, B, 1, self._pos0, pos, self.cache, prefill=False,
+                         pos_dev=self._pos0 if cfg.pos == "rope" else None)
+        self._pos0.add_(1)
         return self._logits(x)
+
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Feeds one token per sequence (``[B]`` int64) at the next position; returns ``[B, V]``."""
+        B = tokens.shape[0]
+        if not self.use_graph:
+            out = self._decode_body(tokens)
+            self._pos += 1
+            return out
+        if self._graph is None or self._graph_B != B:
+            dev = self.m.device
+            self._tok_in = tokens.clone()
+            keep = (self._pos0.clone(), self._ctx.clone())
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                # warm-up outside the capture
+                self._decode_body(self._tok_in)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(dev)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._graph_out = self._decode_body(self._tok_in)
+            # warm-up and capture advanced the positions and wrote one cache slot: rewind
+            self._pos0.copy_(keep[0])
+            self._ctx.copy_(keep[1])
+            self._graph_B = B
+        self._tok_in.copy_(tokens)
+        self._graph.replay()
+        self._pos += 1
+        return self._graph_out
 
     def generate(self, ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
                  top_k: Optional[int] = None, top_p: Optional[float] = None, seed: int = 0,
