@@ -1,0 +1,56 @@
+"""Every example program runs on CPU and produces what it says."""
+import importlib.util
+import os
+
+ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+
+
+def _load(name):
+    spec = importlib.util.spec_from_file_location(f"example_{name}", os.path.join(ROOT, name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_basic_usage():
+    r = _load("basic_usage").main()
+    assert r["decoded"].strip() == "Hello, RustLLM Core! This is a simple example."
+    assert r["trigrams"] == r["tokens"] - 2 and r["cow"] == "hello world" and r["built"] == "zero-copy"
+    assert r["loaded"] == ["basic_tokenizer"] and r["arena_used"] > 0
+
+
+def test_config_usage():
+    r = _load("config_usage").main(["--verbose", "positional"])
+    assert r == {"layers": 24, "lr": 1e-4, "steps": 200, "vocab": 50000, "name": "example",
+                 "rest": ["positional"]}
+
+
+def test_streaming():
+    r = _load("streaming").main(lines=500, sentences=30)
+    assert r["stream_tokens"] > 500 * 10 and r["windows3"] == 7 and r["windows5"] == 5
+    assert r["bpe_tokens"] > 0 and r["top"]
+
+
+def test_training_example():
+    r = _load("training_example").main(["--device", "cpu", "--steps", "12"])
+    assert r["toy"][-1] < r["toy"][0] * 0.5
+    assert r["lm"][-1] < r["lm"][0]
+
+
+def test_transformer_example_small():
+    r = _load("transformer_250m").main(["--small", "--device", "cpu"])
+    assert r["logits"] == 320 and r["roundtrip_identical"] and len(r["generated"]) == 8
+    assert r["file_bytes"] > 136 + 4 * r["params"] and r["loaded"] == ["transformer_model"]
+
+
+def test_diffusion_example():
+    r = _load("diffusion_example").main(40)
+    assert r["end_mse"] < r["start_mse"] * 0.25 and r["deterministic"] and r["view_len"] == 16
+    assert 0 < r["alpha_bar_last"] < 1
+
+
+def test_wordpiece_example():
+    r = _load("wordpiece_tokenizer").main(5)
+    assert r["pieces"]["unaffable"] == ["un", "##aff", "##able"]
+    assert r["pieces"]["playing played"] == ["play", "##ing", "play", "##ed"]
+    assert r["chars_per_s"] > 0
