@@ -12,8 +12,9 @@ from coeus_b200.prelude import WordPieceTokenizerPlugin
 
 def main(iterations: int = 100) -> dict:
     tok = WordPieceTokenizerPlugin().create_tokenizer()
-    for piece in ("un", "##aff", "##able", "play", "##ing", "##ed", "the", "quick", "brown", "fox"):
-        tok.add_token(piece)
+    pieces = ("un", "##aff", "##able", "play", "##ing", "##ed", "the", "quick", "brown", "fox")
+    for i, piece in enumerate(pieces):
+        tok.add_token(piece, tok.vocab_size() + i)
     samples = ["unaffable", "playing played", "the quick brown fox", "xylophone"]
     shown = {s: [t.as_str() for t in tok.tokenize_str(s)] for s in samples}
     for s, pieces in shown.items():

@@ -51,6 +51,7 @@ def test_diffusion_example():
 
 def test_wordpiece_example():
     r = _load("wordpiece_tokenizer").main(5)
-    assert r["pieces"]["unaffable"] == ["un", "##aff", "##able"]
-    assert r["pieces"]["playing played"] == ["play", "##ing", "play", "##ed"]
+    assert r["pieces"]["unaffable"] == ["[CLS]", "un", "##aff", "##able", "[SEP]"]
+    assert r["pieces"]["playing played"][1:-1] == ["play", "##ing", "play", "##ed"]
+    assert "[UNK]" in r["pieces"]["xylophone"]
     assert r["chars_per_s"] > 0
