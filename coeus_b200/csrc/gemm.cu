@@ -27,6 +27,7 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr int AG_PARTS = 8;   // row groups a pulled tile is split into
+constexpr int AG_UNROLL = 16; // 16-byte loads in flight per pull thread
 constexpr int MAX_TP = 8;
 enum : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
 
@@ -403,10 +404,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       char* dbase = reinterpret_cast<char*>(p.ag_dst) + static_cast<size_t>(row0) * p.ag_ld * 2;
       const int vec_per_row = static_cast<int>(row_bytes / 16);
       const int total_vec = rows * vec_per_row;
-      for (int v0 = ct; v0 < total_vec; v0 += 64 * 8) {
-        uint4 buf[8];
+      // AG_UNROLL 16-byte loads per thread are issued before the first store: with 64 pull threads
+      // per CTA that is 16 KB in flight per SM, enough to keep the NVLink ingress busy
+      for (int v0 = ct; v0 < total_vec; v0 += 64 * AG_UNROLL) {
+        uint4 buf[AG_UNROLL];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < AG_UNROLL; ++u) {
           const int v = v0 + u * 64;
           if (v < total_vec) {
             const size_t off = static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
@@ -417,7 +420,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < AG_UNROLL; ++u) {
           const int v = v0 + u * 64;
           if (v < total_vec) {
             const size_t off = static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
