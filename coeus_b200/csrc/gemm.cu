@@ -404,33 +404,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       char* dbase = reinterpret_cast<char*>(p.ag_dst) + static_cast<size_t>(row0) * p.ag_ld * 2;
       const int vec_per_row = static_cast<int>(row_bytes / 16);
       const int total_vec = rows * vec_per_row;
-      // AG_UNROLL 16-byte loads per thread are issued before the first store: with 64 pull threads
-      // per CTA that is 16 KB in flight per SM, enough to keep the NVLink ingress busy
-      for (int v0 = ct; v0 < total_vec; v0 += 64 * AG_UNROLL) {
-        uint4 buf[AG_UNROLL];
+      // Two register batches of AG_UNROLL / 2 loads each: while one batch is being stored the
+      // other one's loads (and the refill of the first) are still in flight, so the NVLink
+      // ingress never drains inside a unit.  64 pull threads x 16 x 16 B = 16 KB per SM.
+      constexpr int HB = AG_UNROLL / 2;
+      auto offset_of = [&](int v) {
+        return static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
+               static_cast<size_t>(v % vec_per_row) * 16;
+      };
+      auto load_batch = [&](uint4 (&b)[HB], int vb) {
 #pragma unroll
-        for (int u = 0; u < AG_UNROLL; ++u) {
-          const int v = v0 + u * 64;
-          if (v < total_vec) {
-            const size_t off = static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
-                               static_cast<size_t>(v % vec_per_row) * 16;
+        for (int u = 0; u < HB; ++u) {
+          const int v = vb + u * 64;
+          if (v < total_vec)
             asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(buf[u].x), "=r"(buf[u].y), "=r"(buf[u].z), "=r"(buf[u].w)
-                         : "l"(sbase + off) : "memory");
-          }
+                         : "=r"(b[u].x), "=r"(b[u].y), "=r"(b[u].z), "=r"(b[u].w)
+                         : "l"(sbase + offset_of(v)) : "memory");
         }
+      };
+      auto store_batch = [&](const uint4 (&b)[HB], int vb) {
 #pragma unroll
-        for (int u = 0; u < AG_UNROLL; ++u) {
-          const int v = v0 + u * 64;
-          if (v < total_vec) {
-            const size_t off = static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
-                               static_cast<size_t>(v % vec_per_row) * 16;
-            *reinterpret_cast<uint4*>(dbase + off) = buf[u];
-          }
+        for (int u = 0; u < HB; ++u) {
+          const int v = vb + u * 64;
+          if (v < total_vec) *reinterpret_cast<uint4*>(dbase + offset_of(v)) = b[u];
         }
+      };
+      uint4 ba[HB], bb[HB];
+      constexpr int STEP = 64 * HB;
+      load_batch(ba, ct);
+      for (int v0 = ct; v0 < total_vec; v0 += 2 * STEP) {
+        load_batch(bb, v0 + STEP);
+        store_batch(ba, v0);
+        load_batch(ba, v0 + 2 * STEP);
+        store_batch(bb, v0 + STEP);
       }
-      __threadfence();
-      asm volatile("fence.proxy.async.global;" ::: "memory");
+      // The release below is cumulative over what the barrier orders before it, and the consumer
+      // issues the generic->async proxy fence after its acquire.
       asm volatile("bar.sync 2, 64;" ::: "memory");
       if (ct == 0)
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + m_blk) : "memory");
