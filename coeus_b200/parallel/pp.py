@@ -6,9 +6,9 @@ one backward, then drains the remaining backwards; at most ``P - s`` micro-batch
 stage at a time, which bounds the activation stash.  Activations and their gradients travel with
 point-to-point sends (NCCL on GPUs, Gloo on CPU ranks).  The forward and the backward direction
 use separate process groups, so a receive that was posted early never blocks a send of the other
-direction; receives for the next micro-batch are posted before the current one is computed and
-sends are not waited for until their buffer is reused, which is what overlaps the transfers with
-the math.  The reference is a single process and has no pipeline (no send/recv anywhere in its
+direction; sends are not waited for until their buffer is reused and, on CPU ranks, receives for
+the next micro-batch are posted before the current one is computed (on GPUs a receive is posted
+when it is needed, see ``_Channel``), which is what overlaps the transfers with the math.  The reference is a single process and has no pipeline (no send/recv anywhere in its
 sources); this is one of the parallelism strategies the larger training configurations need.
 """
 from __future__ import annotations
@@ -58,14 +58,21 @@ class _Channel:
     """One direction between two neighbouring stages: posts receives ahead and keeps sends alive."""
 
     def __init__(self, group, peer_global: int, shape, dtype, device, count: int, recv: bool) -> None:
+        # Receives are posted ahead only on CPU ranks.  On a GPU an early NCCL receive is a kernel
+        # that spins on its SMs until the peer sends; the persistent GEMM kernels (one CTA per SM,
+        # static tile assignment) cannot place their CTAs there, and two neighbouring stages that
+        # both wait like this for each other's next tensor would never finish the GEMMs that
+        # produce them.  So on CUDA a receive is posted when its tensor is needed, sends stay
+        # asynchronous.
+        self.prefetch = torch.device(device).type != "cuda"
         self.group, self.peer, self.count = group, peer_global, count
         self.shape, self.dtype, self.device = shape, dtype, device
         self.posted = 0
         self.pending: List[Tuple[object, torch.Tensor]] = []
         self.recv = recv
 
-    def post_recv(self) -> None:
-        if self.posted >= self.count:
+    def post_recv(self, force: bool = False) -> None:
+        if self.posted >= self.count or not (self.prefetch or force):
             return
         buf = torch.empty(self.shape, dtype=self.dtype, device=self.device)
         self.pending.append((dist.irecv(buf, src=self.peer, group=self.group), buf))
@@ -73,7 +80,7 @@ class _Channel:
 
     def take(self) -> torch.Tensor:
         if not self.pending:
-            self.post_recv()
+            self.post_recv(force=True)
         req, buf = self.pending.pop(0)
         req.wait()
         self.post_recv()          # the next one travels while this one is computed on

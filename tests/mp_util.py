@@ -21,9 +21,11 @@ def _entry(fn, rank, world, port, args, q):
         raise
 
 
-def run_ranks(fn, world: int, args=(), results: int = 1, timeout: float = 600.0):
+def run_ranks(fn, world: int, args=(), results: int = 1, timeout: float = 240.0):
     """Start ``fn(rank, world, port, *args, queue)`` on ``world`` processes, collect ``results``
-    queue items, join.  Raises with the child's traceback if one fails."""
+    queue items, join.  Raises with the child's traceback if one fails.  Children should put
+    plain Python / numpy data (tensors travel as file descriptors and are lost if the child exits
+    first)."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
