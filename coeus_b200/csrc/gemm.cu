@@ -68,15 +68,21 @@ struct GemmArgs {
 
 constexpr int GEMM_STAGING_BYTES = 32768;   // two [128 rows x 64 bf16] swizzled store tiles
 
-template <int BN>
+constexpr int PULL_SLOT_BYTES = 16384;      // one bulk copy of the all-gather pull ring
+
+// The all-gather variant gives up one pipeline stage for a ring of bulk-copy slots through which
+// one thread streams the peers' rows (peer memory -> shared memory -> the local gather buffer).
+template <int BN, int COMM = 0>
 struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = ((BN == 256) ? 4 : 6) - (COMM == 1 ? 1 : 0);
+  static constexpr int PULL_SLOTS = COMM == 1 ? STAGE_BYTES / PULL_SLOT_BYTES : 0;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int OFF_STAGING = STAGES * STAGE_BYTES;
-  static constexpr int OFF_BAR = OFF_STAGING + GEMM_STAGING_BYTES;
+  static constexpr int OFF_PULL = OFF_STAGING + GEMM_STAGING_BYTES;
+  static constexpr int OFF_BAR = OFF_PULL + PULL_SLOTS * PULL_SLOT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -183,11 +189,11 @@ __device__ __forceinline__ uint64_t ld_acquire_sys_u64_g(const uint64_t* p) {
 // sums straight into the owner rank's receive slot (coalesced peer stores from the staging
 // tile); the owner adds the slots in its next kernel.
 template <int BN, bool A_MN, bool B_MN, int COMM>
-__global__ void __launch_bounds__(COMM == COMM_AG ? GEMM_THREADS + 64 : GEMM_THREADS, 1)
+__global__ void __launch_bounds__(COMM == COMM_AG ? GEMM_THREADS + 32 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux,
                  const GemmArgs p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, COMM>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -206,6 +212,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto empty_bar = [&](int s) { return smem_u32(bars + STAGES + s); };
   auto tfull_bar = [&](int a) { return smem_u32(bars + 2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return smem_u32(bars + 2 * STAGES + 2 + a); };
+  auto pull_bar = [&](int s) { return smem_u32(bars + 2 * STAGES + 6 + s); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -216,6 +223,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 128);
     }
+    for (int s = 0; s < Cfg::PULL_SLOTS; ++s) mbar_init(pull_bar(s), 1);
     *abort_flag = 0;
     *epi_ok = 1;
     *(epi_ok + 1) = 1;
@@ -367,82 +375,101 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
   } else if (COMM == COMM_AG && warp >= 6) {
-    // ------------------------------------------------------------------ all-gather pull warps
-    const int ct = threadIdx.x - GEMM_THREADS;  // 0..63
-    volatile int* comm_ok = epi_ok + 1;
-    const int n_remote = (p.tp - 1) * p.tiles_per_shard;
-    const size_t row_bytes = static_cast<size_t>(p.K) * 2;  // gathered rows are K elements wide
-    // unit of work: one of the AG_PARTS row groups of one remote tile, so that even a short
-    // operand keeps every CTA's pull warps (and with them enough bytes in flight) busy
-    for (int c = blockIdx.x; c < n_remote * AG_PARTS; c += gridDim.x) {
-      const int tile_c = c / AG_PARTS, part = c % AG_PARTS;
-      const int dist = tile_c / p.tiles_per_shard + 1;
-      const int src = (p.rank + dist) % p.tp;
-      const int m_blk = src * p.tiles_per_shard + tile_c % p.tiles_per_shard;
-      if (ct == 0) {
-        int good = 1;
-        const uint64_t t0 = globaltimer_ns();
-        uint32_t n = 0;
-        while (ld_acquire_sys_u64_g(p.peer_flags + src) < p.peer_expect) {
-          if ((++n & 15u) == 0u &&
-              (*abort_flag || globaltimer_ns() - t0 > p.wait_limit_ns)) {
-            *abort_flag = 1u;
-            record_status(p.status, ST_COMM_TIMEOUT, src);
-            good = 0;
+    // ------------------------------------------------------------------ all-gather pull
+    // One thread streams this CTA's share of the peers' rows through a ring of shared-memory
+    // slots with bulk copies: peer memory -> slot (completion on the slot's mbarrier), slot ->
+    // local gather buffer (bulk group).  No registers hold data, PULL_SLOTS - 1 loads are in
+    // flight per SM at all times, and nothing drains between row groups: a group's arrival
+    // counter is raised when the bulk group of its last chunk has completed.
+    if constexpr (COMM == COMM_AG) {
+      if (lane == 0) {
+        constexpr int NS = Cfg::PULL_SLOTS;
+        constexpr int PART_ROWS = GEMM_BM / AG_PARTS;
+        const uint32_t s_pull = smem_base + Cfg::OFF_PULL;
+        const int n_units = (p.tp - 1) * p.tiles_per_shard * AG_PARTS;
+        const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+        const bool contig = p.ag_ld == p.K;           // a row group is one contiguous run
+        const int runs = contig ? 1 : PART_ROWS;
+        const size_t run_bytes = contig ? PART_ROWS * row_bytes : row_bytes;
+        const int chunks_per_run = static_cast<int>((run_bytes + PULL_SLOT_BYTES - 1) / PULL_SLOT_BYTES);
+        const int chunks_per_unit = runs * chunks_per_run;
+        const int my_units = n_units > static_cast<int>(blockIdx.x)
+                                 ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const long total = static_cast<long>(my_units) * chunks_per_unit;
+        uint32_t ready = 1u << p.rank;                // peers whose buffers may be read
+        bool ok = true;
+        struct Chunk { const char* src; char* dst; uint32_t bytes; int m_blk; bool last; };
+        auto chunk_of = [&](long j) {
+          const int ui = static_cast<int>(j / chunks_per_unit), rem = static_cast<int>(j % chunks_per_unit);
+          const int c = blockIdx.x + ui * gridDim.x;
+          const int tile_c = c / AG_PARTS, part = c % AG_PARTS;
+          const int src = (p.rank + tile_c / p.tiles_per_shard + 1) % p.tp;
+          const int m_blk = src * p.tiles_per_shard + tile_c % p.tiles_per_shard;
+          const int run = rem / chunks_per_run, ch = rem % chunks_per_run;
+          const size_t row = static_cast<size_t>(m_blk) * GEMM_BM + part * PART_ROWS + (contig ? 0 : run);
+          const size_t off = row * p.ag_ld * 2 + static_cast<size_t>(ch) * PULL_SLOT_BYTES;
+          const size_t left = run_bytes - static_cast<size_t>(ch) * PULL_SLOT_BYTES;
+          Chunk k;
+          k.src = static_cast<const char*>(p.ag_src[src]) + off;
+          k.dst = reinterpret_cast<char*>(p.ag_dst) + off;
+          k.bytes = static_cast<uint32_t>(left < PULL_SLOT_BYTES ? left : PULL_SLOT_BYTES);
+          k.m_blk = m_blk;
+          k.last = rem == chunks_per_unit - 1;
+          if (!(ready >> src & 1u)) {                 // first touch of this peer: is its shard written?
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t n = 0;
+            while (ld_acquire_sys_u64_g(p.peer_flags + src) < p.peer_expect) {
+              if ((++n & 15u) == 0u && (*abort_flag || globaltimer_ns() - t0 > p.wait_limit_ns)) {
+                *abort_flag = 1u;
+                record_status(p.status, ST_COMM_TIMEOUT, src);
+                ok = false;
+                break;
+              }
+            }
+            ready |= 1u << src;
+          }
+          return k;
+        };
+        auto issue_load = [&](long j) {
+          const Chunk k = chunk_of(j);
+          if (!ok) return;
+          const int slot = static_cast<int>(j % NS);
+          mbar_arrive_expect_tx(pull_bar(slot), k.bytes);
+          bulk_load_g2s(s_pull + slot * PULL_SLOT_BYTES, k.src, k.bytes, pull_bar(slot));
+        };
+        int pend_blk[2] = {-1, -1};                    // counters to raise once older groups finish
+        auto raise = [&](int m_blk) {
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + m_blk) : "memory");
+        };
+        long loads = 0;
+        for (; loads < total && loads < NS && ok; ++loads) issue_load(loads);
+        for (long j = 0; j < total && ok; ++j) {
+          const int slot = static_cast<int>(j % NS);
+          if (!mbar_wait(pull_bar(slot), static_cast<uint32_t>(j / NS) & 1u, abort_flag)) {
+            record_status(p.status, ST_WAIT_TIMEOUT, 600);
+            ok = false;
             break;
           }
+          const Chunk k = chunk_of(j);
+          fence_proxy_async_smem();
+          bulk_store_s2g(k.dst, s_pull + slot * PULL_SLOT_BYTES, k.bytes);
+          tma_store_commit();
+          // groups older than the two most recent have completed: their rows are in place
+          asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
+          if (pend_blk[0] >= 0) raise(pend_blk[0]);
+          pend_blk[0] = pend_blk[1];
+          pend_blk[1] = k.last ? k.m_blk : -1;
+          // the store before this one has read its slot: refill it
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          if (j >= 1 && loads < total) { issue_load(loads); ++loads; }
         }
-        *comm_ok = good;
+        tma_store_wait_all();
+        if (ok) {
+          if (pend_blk[0] >= 0) raise(pend_blk[0]);
+          if (pend_blk[1] >= 0) raise(pend_blk[1]);
+        }
       }
-      asm volatile("bar.sync 2, 64;" ::: "memory");
-      if (*comm_ok == 0) break;
-      constexpr int PART_ROWS = GEMM_BM / AG_PARTS;
-      const int row0 = m_blk * GEMM_BM + part * PART_ROWS;
-      const int rows = max(0, min(PART_ROWS, p.M - row0));
-      const char* sbase = static_cast<const char*>(p.ag_src[src]) +
-                          static_cast<size_t>(row0) * p.ag_ld * 2;
-      char* dbase = reinterpret_cast<char*>(p.ag_dst) + static_cast<size_t>(row0) * p.ag_ld * 2;
-      const int vec_per_row = static_cast<int>(row_bytes / 16);
-      const int total_vec = rows * vec_per_row;
-      // Two register batches of AG_UNROLL / 2 loads each: while one batch is being stored the
-      // other one's loads (and the refill of the first) are still in flight, so the NVLink
-      // ingress never drains inside a unit.  64 pull threads x 16 x 16 B = 16 KB per SM.
-      constexpr int HB = AG_UNROLL / 2;
-      auto offset_of = [&](int v) {
-        return static_cast<size_t>(v / vec_per_row) * p.ag_ld * 2 +
-               static_cast<size_t>(v % vec_per_row) * 16;
-      };
-      auto load_batch = [&](uint4 (&b)[HB], int vb) {
-#pragma unroll
-        for (int u = 0; u < HB; ++u) {
-          const int v = vb + u * 64;
-          if (v < total_vec)
-            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(b[u].x), "=r"(b[u].y), "=r"(b[u].z), "=r"(b[u].w)
-                         : "l"(sbase + offset_of(v)) : "memory");
-        }
-      };
-      auto store_batch = [&](const uint4 (&b)[HB], int vb) {
-#pragma unroll
-        for (int u = 0; u < HB; ++u) {
-          const int v = vb + u * 64;
-          if (v < total_vec) *reinterpret_cast<uint4*>(dbase + offset_of(v)) = b[u];
-        }
-      };
-      uint4 ba[HB], bb[HB];
-      constexpr int STEP = 64 * HB;
-      load_batch(ba, ct);
-      for (int v0 = ct; v0 < total_vec; v0 += 2 * STEP) {
-        load_batch(bb, v0 + STEP);
-        store_batch(ba, v0);
-        load_batch(ba, v0 + 2 * STEP);
-        store_batch(bb, v0 + STEP);
-      }
-      // The release below is cumulative over what the barrier orders before it, and the consumer
-      // issues the generic->async proxy fence after its acquire.
-      asm volatile("bar.sync 2, 64;" ::: "memory");
-      if (ct == 0)
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + m_blk) : "memory");
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -640,7 +667,7 @@ template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                        const CUtensorMap& taux, const GemmArgs& args, int max_ctas,
                        cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, COMM>;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, COMM>;
   if (!configured) {
@@ -653,7 +680,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, COMM == COMM_AG ? GEMM_THREADS + 64 : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
+  kern<<<grid, COMM == COMM_AG ? GEMM_THREADS + 32 : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
       ta, tb, td, taux, args);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
