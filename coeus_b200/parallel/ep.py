@@ -314,8 +314,12 @@ class ExpertParallelTrainer:
     (their gradients are complete once the exchanged rows have been processed), all other
     gradients are summed over the group while backward is still running."""
 
-    def __init__(self, model, cfg=None) -> None:
+    def __init__(self, model, cfg=None, overlap: bool = True) -> None:
+        """``overlap=False`` runs the dense all-reduces after the backward pass instead of
+        concurrently with it (no collective kernel then shares the SMs with expert GEMMs that
+        wait on peers)."""
         from ..optim.adamw import AdamW
+        self.overlap = overlap
         from ..train.trainer import TrainConfig
         self.model, self.cfg = model, cfg or TrainConfig()
         self.epx: ExpertParallel = model.epx
@@ -344,6 +348,8 @@ class ExpertParallelTrainer:
             dist.all_reduce(g, group=self.epx.group)
 
     def _on_layer_done(self, l: int) -> None:
+        if not self.overlap:
+            return
         if l == -1:
             self._reduce(self._head)
         elif l >= 1:
@@ -356,6 +362,10 @@ class ExpertParallelTrainer:
         m.zero_grad()
         loss = m.forward_loss(ids, targets, grad_scale=1.0 / (T * ep))
         m.backward(on_layer_done=self._on_layer_done)
+        if not self.overlap:
+            self._reduce(self._head)
+            for span in self.spans[1:-1]:
+                self._reduce(span)
         self._reduce(self.spans[0])
         self._reduce(self._tail)
         if self._stream is not None:
