@@ -442,8 +442,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           asm volatile("fence.proxy.async.global;" ::: "memory");
           asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + m_blk) : "memory");
         };
-        long loads = 0;
+        long loads = 0, done_j = 0;               // loads issued / loads waited for
         for (; loads < total && loads < NS && ok; ++loads) issue_load(loads);
+        if (!ok && loads > 0) --loads;               // the load that found its peer missing was not issued
         for (long j = 0; j < total && ok; ++j) {
           const int slot = static_cast<int>(j % NS);
           if (!mbar_wait(pull_bar(slot), static_cast<uint32_t>(j / NS) & 1u, abort_flag)) {
@@ -451,6 +452,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = false;
             break;
           }
+          done_j = j + 1;
           const Chunk k = chunk_of(j);
           fence_proxy_async_smem();
           bulk_store_s2g(k.dst, s_pull + slot * PULL_SLOT_BYTES, k.bytes);
@@ -462,9 +464,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           pend_blk[1] = k.last ? k.m_blk : -1;
           // the store before this one has read its slot: refill it
           asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          if (j >= 1 && loads < total) { issue_load(loads); ++loads; }
+          if (j >= 1 && loads < total) {
+            issue_load(loads);
+            if (ok) ++loads;
+          }
         }
         tma_store_wait_all();
+        if (!ok) {
+          // let the loads that were issued but not consumed land before the shared memory goes away
+          for (long i2 = done_j; i2 < loads; ++i2) {
+            const uint64_t t0 = globaltimer_ns();
+            while (!mbar_try_wait(pull_bar(static_cast<int>(i2 % NS)),
+                                  static_cast<uint32_t>(i2 / NS) & 1u)) {
+              if (globaltimer_ns() - t0 > 200000000ull) break;
+            }
+          }
+        }
         if (ok) {
           if (pend_blk[0] >= 0) raise(pend_blk[0]);
           if (pend_blk[1] >= 0) raise(pend_blk[1]);
