@@ -27,7 +27,6 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr int AG_PARTS = 8;   // row groups a pulled tile is split into
-constexpr int AG_UNROLL = 16; // 16-byte loads in flight per pull thread
 constexpr int MAX_TP = 8;
 enum : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
 
@@ -72,12 +71,14 @@ constexpr int PULL_SLOT_BYTES = 16384;      // one bulk copy of the all-gather p
 
 // The all-gather variant gives up one pipeline stage for a ring of bulk-copy slots through which
 // one thread streams the peers' rows (peer memory -> shared memory -> the local gather buffer).
-template <int BN, int COMM = 0>
+// CTA2: two CTAs of a cluster share one 256 x BN tile; each stages its 128 rows of A and half of
+// the B rows, so a stage is 32 KB and six stages fit.
+template <int BN, int COMM = 0, bool CTA2 = false>
 struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int B_BYTES = (CTA2 ? BN / 2 : BN) * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = ((BN == 256) ? 4 : 6) - (COMM == 1 ? 1 : 0);
+  static constexpr int STAGES = CTA2 ? 6 : ((BN == 256) ? 4 : 6) - (COMM == 1 ? 1 : 0);
   static constexpr int PULL_SLOTS = COMM == 1 ? STAGE_BYTES / PULL_SLOT_BYTES : 0;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int OFF_STAGING = STAGES * STAGE_BYTES;
@@ -188,13 +189,18 @@ __device__ __forceinline__ uint64_t ld_acquire_sys_u64_g(const uint64_t* p) {
 // COMM_RS: the result is reduce-scattered by rows.  The epilogue pushes each tile of partial
 // sums straight into the owner rank's receive slot (coalesced peer stores from the staging
 // tile); the owner adds the slots in its next kernel.
-template <int BN, bool A_MN, bool B_MN, int COMM>
+template <int BN, bool A_MN, bool B_MN, int COMM, bool CTA2 = false>
 __global__ void __launch_bounds__(COMM == COMM_AG ? GEMM_THREADS + 32 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux,
                  const GemmArgs p) {
-  using Cfg = GemmCfg<BN, COMM>;
+  static_assert(!CTA2 || (COMM == COMM_NONE && BN == 256), "CTA pairs: plain 256-wide GEMM only");
+  using Cfg = GemmCfg<BN, COMM, CTA2>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int TILE_M = CTA2 ? 2 * GEMM_BM : GEMM_BM;     // rows of one (cluster) tile
+  const uint32_t cta_rank = CTA2 ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the MMAs
+  const int first_tile = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_step = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -221,7 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 128);
+      mbar_init(tempty_bar(a), CTA2 ? 256 : 128);   // pair: both CTAs' epilogues report to rank 0
     }
     for (int s = 0; s < Cfg::PULL_SLOTS; ++s) mbar_init(pull_bar(s), 1);
     *abort_flag = 0;
@@ -233,15 +239,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (p.tma_store) tma_prefetch_desc(&tmD);
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CTA2) {
+      tmem_alloc_cg2(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+      tmem_relinquish_cg2();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTA2) cluster_sync_all();   // the peer's barriers exist before anything targets them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_m = (p.M + TILE_M - 1) / TILE_M;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
   const int kb_per = (kblocks + p.ksplit - 1) / p.ksplit;
@@ -260,11 +272,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       uint32_t armed = 0;  // number of stage fills issued
       bool ok = true;
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      for (int w = first_tile; w < total && ok; w += tile_step) {
         const int split = w % p.ksplit;
         const int tile = w / p.ksplit;
         const int m_blk = m_block_of(tile);
-        const int m0 = m_blk * GEMM_BM;
+        const int m0 = m_blk * TILE_M + static_cast<int>(cta_rank) * GEMM_BM;
         const int n0 = (tile % tiles_n) * BN;
         const int kb0 = split * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
@@ -294,6 +306,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
+          if constexpr (CTA2) {
+            // both CTAs fill their own stage; all bytes are counted on rank 0's barrier, which
+            // rank 0 arms for the pair
+            const uint32_t fb = mapa_shared(full_bar(stage), 0u);
+            if (cta_rank == 0u) mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+            const int nb = n0 + static_cast<int>(cta_rank) * (BN / 2);   // this CTA's half of B
+            if constexpr (!A_MN) {
+              tma_load_2d_cg2(sA, &tmA, fb, kb * GEMM_BK, m0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < GEMM_BM / 64; ++c)
+                tma_load_2d_cg2(sA + c * 8192, &tmA, fb, m0 + c * 64, kb * GEMM_BK);
+            }
+            if constexpr (!B_MN) {
+              tma_load_2d_cg2(sB, &tmB, fb, kb * GEMM_BK, nb);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / 128; ++c)
+                tma_load_2d_cg2(sB + c * 8192, &tmB, fb, nb + c * 64, kb * GEMM_BK);
+            }
+          } else {
           const uint32_t fb = full_bar(stage);
           mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
           if constexpr (!A_MN) {
@@ -310,12 +343,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int c = 0; c < BN / 64; ++c)
               tma_load_2d(sB + c * 8192, &tmB, fb, n0 + c * 64, kb * GEMM_BK);
           }
+          }
           ++armed;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-      if (!ok) {
-        // Let copies that were already issued land before the CTA's shared memory goes away.
+      if (!ok && cta_rank == 0u) {
+        // Let copies that were already issued land before the CTA's shared memory goes away
+        // (rank 0's barriers also count the peer's bytes; both CTAs stay until the final
+        // cluster barrier).
         const uint32_t n_wait = armed < (uint32_t)STAGES ? armed : (uint32_t)STAGES;
         for (uint32_t i = 0; i < n_wait; ++i) {
           const uint32_t idx = armed - 1 - i;  // fill index
@@ -331,13 +367,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    if (lane == 0 && cta_rank == 0u) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+      for (int w = first_tile; w < total && ok; w += tile_step, ++it) {
         const int split = w % p.ksplit;
         const int kb0 = split * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
@@ -365,12 +401,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : umma_desc_sw128(sA + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? umma_desc_sw128(sB + k * 2048, 8192, 1024)
                                      : umma_desc_sw128(sB + k * 32, 16, 1024);
-            umma_bf16_ss(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if constexpr (CTA2) umma_bf16_ss_cg2(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_bf16_ss(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));
+          if constexpr (CTA2) umma_commit_cg2(empty_bar(stage), 3);   // frees the stage in both CTAs
+          else umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(tfull_bar(acc));
+        if (ok) {
+          if constexpr (CTA2) umma_commit_cg2(tfull_bar(acc), 3);     // both epilogues may drain
+          else umma_commit(tfull_bar(acc));
+        }
       }
     }
     __syncwarp();
@@ -493,10 +534,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool aux_staged = p.tma_store && p.epi == EPI_GELU && p.aux_out != nullptr;
     int it = 0;
     uint32_t step = 0;  // running count of staged 64-column steps (selects the store tile)
-    for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
+    for (int w = first_tile; w < total; w += tile_step, ++it) {
       const int tile = w / p.ksplit;
       const int m_blk = m_block_of(tile);
-      const int m0 = m_blk * GEMM_BM;
+      const int m0 = m_blk * TILE_M + static_cast<int>(cta_rank) * GEMM_BM;
       const int n0 = (tile % tiles_n) * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
@@ -566,7 +607,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             fence_proxy_async_smem();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (leader) {
+            if (leader && m0 < p.M) {     // a pair's second CTA may lie entirely below the matrix
               tma_store_2d(&tmD, s_out, colq, m0);
               if (aux_staged) tma_store_2d(&tmAux, s_aux, colq, m0);
               tma_store_commit();
@@ -623,7 +664,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
+      if constexpr (CTA2) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0u));
+      else mbar_arrive(tempty_bar(acc));
     }
     // every bulk store must have finished (reading shared memory and writing global memory)
     if (leader && p.tma_store) tma_store_wait_all();
@@ -631,9 +673,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTA2) cluster_sync_all();   // nothing of the peer targets this CTA any more
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if constexpr (CTA2) tmem_dealloc_cg2(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -700,7 +744,44 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// CTA-pair variant: clusters of two CTAs, 256 x 256 tiles.
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                            const CUtensorMap& taux, const GemmArgs& args, int max_ctas,
+                            cudaStream_t stream) {
+  using Cfg = GemmCfg<256, COMM_NONE, true>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<256, A_MN, B_MN, COMM_NONE, true>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  const int tiles = ((args.M + 255) / 256) * ((args.N + 255) / 256) * args.ksplit;
+  int pairs = sm_count() / 2;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, td, taux, args) == cudaSuccess ? 0 : -11;
+}
+
+static int g_use_pairs = 0;   // 1: plain 256-wide GEMMs run on CTA pairs
+
 }  // namespace cb
+
+extern "C" void cb_gemm_use_pairs(int on) { cb::g_use_pairs = on; }
 
 // D[M,N] = epilogue(alpha * A . B^T)
 //   A: logical [M,K]; a_mn == 0: memory [M,K] row-major (pitch lda); a_mn == 1: memory [K,M].
@@ -715,6 +796,9 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (M <= 0 || N <= 0 || K <= 0) return -20;
   if ((N % 8) != 0 || (K % 8) != 0 || (ldd % 4) != 0) return -21;
   if (out_mode == OUT_BF16 && (ldd % 8) != 0) return -21;
+  // bn = 512 selects the 256-wide tile on CTA pairs
+  const bool pairs = bn == 512 || (bn == 256 && cb::g_use_pairs);
+  if (bn == 512) bn = 256;
   if (bn != 128 && bn != 256) return -22;
   const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
   if (ksplit < 1) ksplit = 1;
@@ -733,7 +817,7 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
     rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, 64);
   if (rc != 0) return rc - 30;
   if (b_mn == 0)
-    rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, bn);
+    rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, (bn == 256 && pairs) ? 128 : bn);
   else
     rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, 64);
   if (rc != 0) return rc - 40;
@@ -771,6 +855,12 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
     if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(ta, tb, td, taux, g, max_ctas, st);   \
     return launch_gemm<BN_, true, true>(ta, tb, td, taux, g, max_ctas, st);                       \
   } while (0)
+  if (bn == 256 && pairs) {
+    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(ta, tb, td, taux, g, max_ctas, st);
+    if (!a_mn && b_mn) return launch_gemm_pair<false, true>(ta, tb, td, taux, g, max_ctas, st);
+    if (a_mn && !b_mn) return launch_gemm_pair<true, false>(ta, tb, td, taux, g, max_ctas, st);
+    return launch_gemm_pair<true, true>(ta, tb, td, taux, g, max_ctas, st);
+  }
   if (bn == 256) CB_DISPATCH(256);
   CB_DISPATCH(128);
 #undef CB_DISPATCH
