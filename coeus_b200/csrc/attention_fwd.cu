@@ -201,7 +201,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = quarter * 32 + lane;       // query row within the tile
     const int q_idx = q0 + r;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    float m_used = -INFINITY, l = 0.f;
+    float m_used = -INFINITY, l = 0.f, l1 = 0.f;   // the row sum is kept as two partial sums
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const bool got = mbar_wait(bar(7), j & 1u, abort_flag);
@@ -226,8 +226,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int e = 0; e < BKV; ++e)
           if (kv0 + e <= kv_limit) mx = fmaxf(mx, __uint_as_float(v[e]));
       } else {
+        float mx1 = -INFINITY;      // two chains of three-input maxima
 #pragma unroll
-        for (int e = 0; e < BKV; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        for (int e = 0; e < BKV; e += 4) {
+          mx = max3(mx, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+          mx1 = max3(mx1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+        }
+        mx = fmaxf(mx, mx1);
       }
       mx *= p.scale_log2;  // scale > 0, so max commutes with it
       const float m_new = fmaxf(m_used, mx);
@@ -254,6 +259,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           tmem_st_wait();
           l *= f;
+          l1 *= f;
         }
       }
       if (grow) m_used = (m_new == -INFINITY) ? 0.f : m_new;
@@ -263,13 +269,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e]), p.scale_log2, -m_used));
-          float p1 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e + 1]), p.scale_log2, -m_used));
+          float t0, t1;
+          fma2(t0, t1, __uint_as_float(v[c * 32 + e]), __uint_as_float(v[c * 32 + e + 1]),
+               p.scale_log2, p.scale_log2, -m_used, -m_used);
+          float p0 = fast_exp2(t0);
+          float p1 = fast_exp2(t1);
           if (need_mask) {
             if (kv0 + c * 32 + e > kv_limit) p0 = 0.f;
             if (kv0 + c * 32 + e + 1 > kv_limit) p1 = 0.f;
           }
-          l += p0 + p1;
+          add2(l, l1, l, l1, p0, p1);
           pk[e >> 1] = pack_bf16x2(p0, p1);
         }
         // columns [c*32, c*32+32) of row r: half = (c*32)/64, 16-byte chunks (c*4 % 8)..+3
@@ -296,6 +305,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     if (ok) {
       tc_fence_after();
+      l += l1;
       const float inv_l = l > 0.f ? 1.0f / l : 0.f;
       const bool row_ok = q_idx < p.S;
       __nv_bfloat16* orow =
