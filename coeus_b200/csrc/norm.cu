@@ -248,7 +248,10 @@ int launch_bwd(const __nv_bfloat16* DY, const __nv_bfloat16* X, const __nv_bfloa
                const float* mean, const float* rstd, const __nv_bfloat16* DR,
                __nv_bfloat16* DX, float* dgamma, float* dbeta, int T, int H, cudaStream_t st) {
   constexpr int RPB = 4 / WPR;
-  const int blocks = min((T + RPB - 1) / RPB, sm_count() * 3);
+  // persistent blocks: as many as can be resident (the register count falls with the share of a
+  // row that one thread holds)
+  const int per_sm = WPR == 1 ? 3 : (WPR == 2 ? 4 : 8);
+  const int blocks = min((T + RPB - 1) / RPB, sm_count() * per_sm);
   const size_t sh = RPB > 1 ? 2 * RPB * static_cast<size_t>(H) * sizeof(float) : 0;
   static bool configured = false;
   if (!configured && sh > 0) {
@@ -261,6 +264,9 @@ int launch_bwd(const __nv_bfloat16* DY, const __nv_bfloat16* X, const __nv_bfloa
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 }  // namespace
+
+static int g_norm_bwd_variant = 1;   // half a row per warp: 123 registers, four blocks per SM
+extern "C" void cb_norm_bwd_variant(int v) { g_norm_bwd_variant = v; }
 
 // rms == 0: LayerNorm (beta may be null); rms == 1: RMSNorm (mean may be null).
 extern "C" int cb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y,
@@ -291,7 +297,11 @@ extern "C" int cb_norm_bwd(const void* dy, const void* x, const void* gamma, con
 #define CB_BWD(WPR, NV)                                                                        \
   return rms ? launch_bwd<WPR, NV, true>(DY, X, G, mean, rstd, DR, DX, dgamma, dbeta, T, H, st) \
              : launch_bwd<WPR, NV, false>(DY, X, G, mean, rstd, DR, DX, dgamma, dbeta, T, H, st)
-  if (H <= 1024) { CB_BWD(1, 4); }
+  if (H <= 1024) {
+    if (g_norm_bwd_variant == 1) { CB_BWD(2, 2); }
+    if (g_norm_bwd_variant == 2) { CB_BWD(4, 1); }
+    CB_BWD(1, 4);
+  }
   if (H <= 4096) { CB_BWD(4, 4); }
   CB_BWD(4, 8);
 #undef CB_BWD
