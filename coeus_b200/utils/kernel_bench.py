@@ -50,7 +50,9 @@ def timeit(fn, warmup: int, iters: int, flush: bool):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm_fwd", "norm_bwd",
-                                       "cross_entropy", "adamw", "decode_attn"])
+                                       "cross_entropy", "adamw", "decode_attn", "rope", "softmax",
+                                       "swiglu", "gelu", "embed", "rmsnorm_fwd", "rmsnorm_bwd",
+                                       "moe_route", "allreduce_local"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -148,6 +150,74 @@ def main(argv=None) -> int:
             dg, db = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
             fn = lambda: N.norm_bwd(dy, x, g, mean, rstd, dg, db, dres)  # noqa: E731
             nbytes = 2.0 * 4 * T * H
+    elif a.kernel in ("rmsnorm_fwd", "rmsnorm_bwd"):
+        T, H = a.tokens, a.hidden
+        x = torch.randn(T, H, device=dev).to(bf)
+        g = torch.ones(H, device=dev, dtype=bf)
+        y, _, rstd = N.norm_fwd(x, g, None, 1e-6, True)
+        if a.kernel == "rmsnorm_fwd":
+            fn = lambda: N.norm_fwd(x, g, None, 1e-6, True)  # noqa: E731
+            nbytes = 2.0 * 2 * T * H
+        else:
+            dy = torch.randn(T, H, device=dev).to(bf)
+            dres = torch.randn(T, H, device=dev).to(bf)
+            dg = torch.zeros(H, device=dev)
+            fn = lambda: N.norm_bwd(dy, x, g, None, rstd, dg, None, dres, True)  # noqa: E731
+            nbytes = 2.0 * 4 * T * H
+    elif a.kernel == "rope":
+        T, nh, dh = a.tokens, a.heads, a.dh
+        x = torch.randn(T, 3 * nh * dh, device=dev).to(bf)
+        fn = lambda: E.rope_(x, 2 * nh, dh, a.seq)  # noqa: E731
+        nbytes = 2.0 * 2 * T * 2 * nh * dh
+    elif a.kernel == "softmax":
+        T, V = a.tokens, a.vocab
+        x = torch.randn(T, V, device=dev)
+        fn = lambda: E.softmax_rows(x)  # noqa: E731
+        nbytes = 4.0 * 2 * T * V
+    elif a.kernel in ("swiglu", "gelu"):
+        T, I = a.tokens, a.n
+        if a.kernel == "swiglu":
+            gu = torch.randn(T, 2 * I, device=dev).to(bf)
+            fn = lambda: E.swiglu_fwd(gu)  # noqa: E731
+            nbytes = 2.0 * 3 * T * I
+        else:
+            u = torch.randn(T, I, device=dev).to(bf)
+            fn = lambda: E.gelu_fwd(u)  # noqa: E731
+            nbytes = 2.0 * 2 * T * I
+    elif a.kernel == "embed":
+        T, H, V = a.tokens, a.hidden, a.vocab
+        table = torch.randn(V, H, device=dev).to(bf)
+        ids = torch.randint(0, V, (T,), device=dev)
+        pe = E.sinusoid_table(a.seq, H, dev)
+        fn = lambda: E.embed_fwd(ids, table, pe, a.seq)  # noqa: E731
+        nbytes = 2.0 * 2 * T * H + 4.0 * T * H
+    elif a.kernel == "moe_route":
+        from ..ops import moe as M
+        T = a.tokens
+        logits = torch.randn(T, 8, device=dev)
+        fn = lambda: M.route(logits, 2, 1280 * (T // 4096 or 1))  # noqa: E731
+        nbytes = 4.0 * T * 8 * 2
+    elif a.kernel == "allreduce_local":
+        # the one-shot all-reduce (+ residual + RMSNorm) with both "ranks" on this GPU
+        import ctypes
+        from ..ops import _lib
+        B, H = a.batch, a.hidden
+        parts = [torch.randn(B, H, device=dev).to(bf) for _ in range(2)]
+        resid = torch.randn(B, H, device=dev).to(bf)
+        scale = torch.ones(H, device=dev, dtype=bf)
+        flags = [torch.full((2,), 1 << 40, dtype=torch.int64, device=dev) for _ in range(2)]
+        state = torch.zeros(2, dtype=torch.int64, device=dev)
+        xo, no = torch.empty(B, H, device=dev, dtype=bf), torch.empty(B, H, device=dev, dtype=bf)
+        pp = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in parts])
+        fp = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in flags])
+        st = _lib.status_buffer(torch.device(dev))
+
+        def fn():
+            _lib.lib().cb_ar_resid_norm(pp, fp, _lib.ptr(flags[0]), _lib.ptr(state), _lib.ptr(resid),
+                                        _lib.ptr(xo), _lib.ptr(scale), _lib.ptr(None), _lib.ptr(no),
+                                        2, 0, B, H, 1, ctypes.c_float(1e-6),
+                                        ctypes.c_ulonglong(int(1e9)), _lib.ptr(st), _lib.stream_ptr())
+        nbytes = 2.0 * 5 * B * H
     elif a.kernel == "cross_entropy":
         T, V = a.tokens, a.vocab
         logits = torch.randn(T, V, device=dev).to(bf)
