@@ -332,6 +332,45 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, int T, int nheads, in
   }
 }
 
+// Same rotation with the trigonometry hoisted out of the head loop: one thread owns eight
+// adjacent frequencies of one token, computes their sines and cosines once and applies them to
+// every head with 16-byte loads and stores (the head count no longer multiplies the sincos work,
+// which made the element-per-thread kernel compute-bound).  Needs dh % 16 == 0 and ld % 8 == 0.
+__global__ void rope_vec_kernel(__nv_bfloat16* __restrict__ x, int T, int nheads, int dh, int ld,
+                                int S, int pos_offset, const int* __restrict__ pos_dev,
+                                float theta, int inverse) {
+  const int half = dh >> 1;
+  const int vecs = half >> 3;
+  const float l2t = __log2f(theta);
+  const size_t total = static_cast<size_t>(T) * vecs;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % vecs);
+    const size_t t = i / vecs;
+    const int pos = static_cast<int>(t % S) + (pos_dev != nullptr ? pos_dev[t / S] : pos_offset);
+    float sn[8], cs[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float inv_freq = exp2f(-2.0f * (v * 8 + e) / dh * l2t);
+      sincosf(pos * inv_freq, &sn[e], &cs[e]);
+      if (inverse) sn[e] = -sn[e];
+    }
+    __nv_bfloat16* p = x + t * ld + v * 8;
+    for (int h = 0; h < nheads; ++h, p += dh) {
+      float a[8], b[8], oa[8], ob[8];
+      load8(p, a);
+      load8(p + half, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        oa[e] = a[e] * cs[e] - b[e] * sn[e];
+        ob[e] = a[e] * sn[e] + b[e] * cs[e];
+      }
+      store8(p, oa);
+      store8(p + half, ob);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ column sums
 // out[c] += sum_t x[t, c]   (x bf16 [T, C] with pitch ld; out fp32) — bias gradients.
 constexpr int COLSUM_THREADS = 256;
@@ -488,6 +527,11 @@ extern "C" int cb_softmax_rows(const float* x, float* y, int R, int C, void* str
 extern "C" int cb_rope(void* x, int T, int nheads, int dh, int ld, int S, int pos_offset,
                        float theta, int inverse, void* stream) {
   if (dh % 2 != 0) return -1;
+  if (dh % 16 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    rope_vec_kernel<<<grid_for(static_cast<size_t>(T) * (dh / 16), 128), 128, 0, CB_ST(stream)>>>(
+        static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S, pos_offset, nullptr, theta, inverse);
+    CB_RET();
+  }
   rope_kernel<<<grid_for(static_cast<size_t>(T) * nheads * (dh / 2), 256), 256, 0,
                 CB_ST(stream)>>>(static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S,
                                  pos_offset, nullptr, theta, inverse);
@@ -496,6 +540,11 @@ extern "C" int cb_rope(void* x, int T, int nheads, int dh, int ld, int S, int po
 extern "C" int cb_rope_dev(void* x, int T, int nheads, int dh, int ld, int S, const int* pos_dev,
                            float theta, int inverse, void* stream) {
   if (dh % 2 != 0 || pos_dev == nullptr) return -1;
+  if (dh % 16 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    rope_vec_kernel<<<grid_for(static_cast<size_t>(T) * (dh / 16), 128), 128, 0, CB_ST(stream)>>>(
+        static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S, 0, pos_dev, theta, inverse);
+    CB_RET();
+  }
   rope_kernel<<<grid_for(static_cast<size_t>(T) * nheads * (dh / 2), 256), 256, 0,
                 CB_ST(stream)>>>(static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S, 0, pos_dev,
                                  theta, inverse);

@@ -215,9 +215,14 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
       const int vec = tid_in_row + j * 32 * WPR;
       if (vec < nv) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          atomicAdd(dgamma + vec * 8 + e, accg[j][e]);
-          if (!RMS && dbeta != nullptr) atomicAdd(dbeta + vec * 8 + e, accb[j][e]);
+        for (int e = 0; e < 8; e += 4) {   // four columns per reduction instruction
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                       ::"l"(dgamma + vec * 8 + e), "f"(accg[j][e]), "f"(accg[j][e + 1]),
+                         "f"(accg[j][e + 2]), "f"(accg[j][e + 3]) : "memory");
+          if (!RMS && dbeta != nullptr)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                         ::"l"(dbeta + vec * 8 + e), "f"(accb[j][e]), "f"(accb[j][e + 1]),
+                           "f"(accb[j][e + 2]), "f"(accb[j][e + 3]) : "memory");
         }
       }
     }
@@ -250,7 +255,7 @@ int launch_bwd(const __nv_bfloat16* DY, const __nv_bfloat16* X, const __nv_bfloa
   constexpr int RPB = 4 / WPR;
   // persistent blocks: as many as can be resident (the register count falls with the share of a
   // row that one thread holds)
-  const int per_sm = WPR == 1 ? 3 : (WPR == 2 ? 4 : 8);
+  const int per_sm = WPR == 1 ? 3 : (WPR == 2 ? 4 : 3);   // every block ends with H column reductions
   const int blocks = min((T + RPB - 1) / RPB, sm_count() * per_sm);
   const size_t sh = RPB > 1 ? 2 * RPB * static_cast<size_t>(H) * sizeof(float) : 0;
   static bool configured = false;
