@@ -42,6 +42,12 @@ struct AttnBwdArgs {
   int* status;
 };
 
+// Optional timeline of block 0 (a debugging aid; off unless a trace buffer is registered):
+// [it][0..7] = clock64 at: softmax S^T/dP^T ready, after the first TMEM load, after the maths of
+// both chunks, after the fence+arrive; MMA thread: stage ready, S^T/dP^T issued, P^T ready,
+// dV/dK/dQ issued.
+__device__ long long* g_attn_bwd_trace = nullptr;
+
 template <int DH>
 struct AttnBwdCfg {
   static constexpr int BQ = (DH == 64) ? 128 : 64;
@@ -51,11 +57,14 @@ struct AttnBwdCfg {
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = KV_BYTES;
   static constexpr int OFF_Q = 2 * KV_BYTES;                    // 2 stages of (Q_i | dO_i)
-  static constexpr int OFF_PT = OFF_Q + 2 * 2 * Q_BYTES;
-  static constexpr int OFF_DST = OFF_PT + PT_BYTES;
-  static constexpr int OFF_STAT = OFF_DST + PT_BYTES;           // [2 stages][2][BQ] floats
+  static constexpr int OFF_PT = OFF_Q + 2 * 2 * Q_BYTES;        // two buffers of P^T ...
+  static constexpr int OFF_DST = OFF_PT + 2 * PT_BYTES;         // ... and of dS^T: the softmax of
+                                                                // tile i+1 writes one pair while
+                                                                // the MMAs of tile i read the other
+  static constexpr int OFF_STAT = OFF_DST + 2 * PT_BYTES;       // [2 stages][2][BQ] floats
   static constexpr int OFF_BAR = OFF_STAT + 2 * 2 * BQ * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static_assert(SMEM_BYTES <= 232448, "attention backward: shared memory budget");
   static constexpr int ST_COL = 0;
   static constexpr int DPT_COL = BQ;
   static constexpr int DV_COL = 2 * BQ;
@@ -123,9 +132,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5 s_full | 6 pds_full | 7 pds_empty | 8 dq_full |
-  // 9 dq_empty | 10 done | 11 stat_full
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 12);
+  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5 s_full | 6 pds_full | 7 pds_empty (even tiles) |
+  // 8 dq_full | 9 dq_empty | 10 done | 11 stat_full | 12 pds_empty (odd tiles)
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 13);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   auto bar = [&](int i) { return smem_u32(bars + i); };
   float* s_stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
@@ -158,6 +167,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar(9), 128);
     mbar_init(bar(10), 1);
     mbar_init(bar(11), 256);
+    mbar_init(bar(12), 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -174,7 +184,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t sK = sbase + Cfg::OFF_K, sV = sbase + Cfg::OFF_V;
-  const uint32_t sPT = sbase + Cfg::OFF_PT, sDST = sbase + Cfg::OFF_DST;
+  auto sPTb = [&](int buf) { return sbase + Cfg::OFF_PT + buf * Cfg::PT_BYTES; };
+  auto sDSTb = [&](int buf) { return sbase + Cfg::OFF_DST + buf * Cfg::PT_BYTES; };
   auto sQ = [&](int st) { return sbase + Cfg::OFF_Q + st * 2 * Cfg::Q_BYTES; };
   auto sDO = [&](int st) { return sQ(st) + Cfg::Q_BYTES; };
   const int row0 = b * p.S;
@@ -227,48 +238,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           (DH == 64) ? umma_idesc_bf16(BQ, DH, 1, 1) : umma_idesc_bf16(DH, BQ, 1, 1);
       bool ok = mbar_wait(bar(0), 0, abort_flag);
       if (!ok) record_status(p.status, ST_WAIT_TIMEOUT, 1020);
-      for (int it = 0; it < n_it && ok; ++it) {
+      long long* trace = blockIdx.x == 0 ? g_attn_bwd_trace : nullptr;
+      // S^T and dP^T of query tile `it` (needs its Q/dO stage and the S^T/dP^T columns free)
+      auto issue_scores = [&](int it) {
         const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1u;
-        if (!mbar_wait(bar(1 + st), ph, abort_flag)) {
+        if (!mbar_wait(bar(1 + st), (it >> 1) & 1u, abort_flag)) {
           record_status(p.status, ST_WAIT_TIMEOUT, 1021);
-          ok = false;
-          break;
+          return false;
         }
         tc_fence_after();
+        if (trace && it < 32) trace[it * 8 + 4] = clock64();
+        // the two products are independent: alternating them keeps two accumulation chains in
+        // flight instead of paying the dependent-MMA latency on each step
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(sK + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
           const uint64_t bd = umma_desc_sw128(sQ(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
           umma_bf16_ss(tmem_base + Cfg::ST_COL, ad, bd, idesc_st, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < DH / 16; ++kk) {
-          const uint64_t ad = umma_desc_sw128(sV + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sDO(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
-          umma_bf16_ss(tmem_base + Cfg::DPT_COL, ad, bd, idesc_st, kk > 0 ? 1u : 0u);
+          const uint64_t ad2 = umma_desc_sw128(sV + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd2 = umma_desc_sw128(sDO(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
+          umma_bf16_ss(tmem_base + Cfg::DPT_COL, ad2, bd2, idesc_st, kk > 0 ? 1u : 0u);
         }
         umma_commit(bar(5));
+        if (trace && it < 32) trace[it * 8 + 5] = clock64();
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1, buf = it & 1;
+        // P^T / dS^T of this tile are in shared memory and its S^T / dP^T columns have been read
         if (!mbar_wait(bar(6), it & 1u, abort_flag)) {
           record_status(p.status, ST_WAIT_TIMEOUT, 1022);
           ok = false;
           break;
         }
         tc_fence_after();
-        // dV += P^T . dO_i     dK += dS^T . Q_i      (contraction over the BQ query rows)
-#pragma unroll
-        for (int kk = 0; kk < BQ / 16; ++kk) {
-          const uint64_t ad = umma_desc_sw128(sPT + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sDO(st) + kk * 2048, BQ * 128, 1024);
-          umma_bf16_ss(tmem_base + Cfg::DV_COL, ad, bd, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
+        if (trace && it < 32) trace[it * 8 + 6] = clock64();
+        // The next tile's scores go first: its softmax then runs while the three products below
+        // execute (they read the other P^T / dS^T buffer).
+        if (it + 1 < n_it && !issue_scores(it + 1)) {
+          ok = false;
+          break;
         }
-#pragma unroll
-        for (int kk = 0; kk < BQ / 16; ++kk) {
-          const uint64_t ad = umma_desc_sw128(sDST + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sQ(st) + kk * 2048, BQ * 128, 1024);
-          umma_bf16_ss(tmem_base + Cfg::DK_COL, ad, bd, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
-        }
-        if (it > 0) {
+        const uint32_t sPT = sPTb(buf), sDST = sDSTb(buf);
+        if (it > 0) {     // the previous tile's dQ must have left tensor memory
           if (!mbar_wait(bar(9), (it - 1) & 1u, abort_flag)) {
             record_status(p.status, ST_WAIT_TIMEOUT, 1023);
             ok = false;
@@ -276,24 +289,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           tc_fence_after();
         }
-        // contraction over the 128 K/V rows
+        // dV += P^T . dO_i, dK += dS^T . Q_i (contraction over the BQ query rows) and
+        // dQ_i = dS . K_j (contraction over the 128 K/V rows): three independent accumulation
+        // chains, issued round-robin
+        constexpr int NK = (BQ > BKV ? BQ : BKV) / 16;
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          if constexpr (DH == 64) {
-            // dQ_i[q, d] = sum_kv dS^T[kv, q] K_j[kv, d]
-            const uint64_t ad = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
-            const uint64_t bd = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
-            umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
-          } else {
-            // dQ_i^T[d, q] = sum_kv K_j[kv, d] dS^T[kv, q]
-            const uint64_t ad = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
-            const uint64_t bd = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
-            umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < NK; ++kk) {
+          if (kk < BQ / 16) {
+            const uint64_t ad = umma_desc_sw128(sPT + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+            const uint64_t bd = umma_desc_sw128(sDO(st) + kk * 2048, BQ * 128, 1024);
+            umma_bf16_ss(tmem_base + Cfg::DV_COL, ad, bd, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
+            const uint64_t ad2 = umma_desc_sw128(sDST + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
+            const uint64_t bd2 = umma_desc_sw128(sQ(st) + kk * 2048, BQ * 128, 1024);
+            umma_bf16_ss(tmem_base + Cfg::DK_COL, ad2, bd2, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+          if (kk < BKV / 16) {
+            if constexpr (DH == 64) {
+              // dQ_i[q, d] = sum_kv dS^T[kv, q] K_j[kv, d]
+              const uint64_t ad = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
+              const uint64_t bd = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
+              umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
+            } else {
+              // dQ_i^T[d, q] = sum_kv K_j[kv, d] dS^T[kv, q]
+              const uint64_t ad = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
+              const uint64_t bd = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
+              umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
+            }
           }
         }
-        umma_commit(bar(8));       // dQ ready to drain
-        umma_commit(bar(3 + st));  // Q_i / dO_i stage free
-        umma_commit(bar(7));       // P^T / dS^T buffers free
+        if (trace && it < 32) trace[it * 8 + 7] = clock64();
+        umma_commit(bar(8));                 // dQ ready to drain
+        umma_commit(bar(3 + st));            // Q_i / dO_i stage free
+        umma_commit(bar(buf ? 12 : 7));      // this P^T / dS^T buffer free
       }
       if (ok) umma_commit(bar(10));
     }
@@ -320,13 +347,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(bar(11));
       bool got = mbar_wait(bar(11), it & 1u, abort_flag);
       if (got) got = mbar_wait(bar(5), it & 1u, abort_flag);
-      if (got && it > 0) got = mbar_wait(bar(7), (it - 1) & 1u, abort_flag);
+      // the buffer pair of this parity was last read by the products of tile it - 2
+      if (got && it > 1) got = mbar_wait(bar((it & 1) ? 12 : 7), ((it >> 1) - 1) & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1030);
         ok = false;
         break;
       }
       tc_fence_after();
+      long long* tr = (blockIdx.x == 0 && it < 32 && warp == 2 && lane == 0) ? g_attn_bwd_trace : nullptr;
+      if (tr) tr[it * 8 + 0] = clock64();
+      const uint32_t sPT = sPTb(it & 1), sDST = sDSTb(it & 1);
       const bool diag = p.causal && (kv0 + BKV - 1 > q0);
       const bool row_dead = kv_idx >= p.S;
 #pragma unroll 1
@@ -335,6 +366,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(lane_addr + Cfg::ST_COL + c * 32, sv);
         tmem_ld_32x32b_x32(lane_addr + Cfg::DPT_COL + c * 32, dv);
         tmem_ld_wait();
+        if (tr && c == half * (BQ / 64)) tr[it * 8 + 1] = clock64();
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -361,9 +393,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                        : "memory");
         }
       }
+      if (tr) tr[it * 8 + 2] = clock64();
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar(6));
+      if (tr) tr[it * 8 + 3] = clock64();
     }
     // ---- epilogue: dV and dK of this K/V tile
     if (ok) {
@@ -482,6 +516,10 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 
 // dqkv: bf16 [B*S, 3*nh*dh] (pitch ldd) receiving dQ | dK | dV.  dq_acc: zeroed fp32
 // [B*S, nh*dh] scratch; delta: fp32 [B, nh, S] scratch.
+extern "C" int cb_attn_bwd_set_trace(long long* device_buffer) {
+  return cudaMemcpyToSymbol(cb::g_attn_bwd_trace, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? 0 : -1;
+}
+
 extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const void* v,
                            const void* o, const float* lse, float* delta, float* dq_acc,
                            void* dqkv, int B, int S, int nh, int dh, int lddo, int ldq, int ldk,
