@@ -496,6 +496,9 @@ class DecoderLM:
             on_layer_done(-1)
         dx = self.backward_blocks(dx, sv, on_layer_done)
         E.embed_bwd(sv["ids"], dx, self.g["token_embed"])
+        if on_layer_done is not None:
+            on_layer_done(-2)
+        self._saved = None
 
     def backward_head(self, sv: dict) -> torch.Tensor:
         """Gradients of the LM head and final norm; returns d loss / d (last block output)."""
@@ -572,6 +575,3 @@ class DecoderLM:
             if on_layer_done is not None:
                 on_layer_done(l)
         return dx
-        if on_layer_done is not None:
-            on_layer_done(-2)
-        self._saved = None
