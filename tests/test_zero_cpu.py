@@ -91,3 +91,29 @@ def test_two_ranks_match_one_rank():
             assert d.max() < 2e-3, (s.name, d.max())
             assert (p16[sl] - ref.p16[sl].float()).abs().max() < 2e-2, s.name
     assert losses[2] < losses[0] and ref_losses[2] < ref_losses[0]
+
+
+def test_backward_reports_every_bucket_trigger_in_order():
+    """The data-parallel buckets hang on these callbacks: head (-1), the layers from last to
+    first, then -2 once the embedding gradient is complete."""
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    cfg = DecoderConfig(hidden_dim=32, num_layers=3, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    m = DecoderLM(cfg, "cpu", dtype=torch.float32)
+    ids = torch.randint(0, 64, (2, 16))
+    m.zero_grad()
+    m.forward_loss(ids, ids)
+    seen = []
+    embed_done_at_minus2 = []
+
+    def hook(t):
+        seen.append(t)
+        if t == -2:
+            embed_done_at_minus2.append(float(m.g["token_embed"].abs().sum()) > 0)
+
+    m.backward(on_layer_done=hook)
+    assert seen == [-1, 2, 1, 0, -2]
+    assert embed_done_at_minus2 == [True]
+    assert m._saved is None
