@@ -36,7 +36,7 @@ def reference_arm(args) -> int:
     installed or run here (no cargo/rustc in the image, pip finds no setup.py/pyproject)."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     why = ("reference is a pure-Rust CPU library (no setup.py/pyproject, no cargo/rustc in the "
-           "image, no GPU or training path): pip install of /root/reference fails and nothing "
+           "image, no GPU or training path): pip install of the reference tree fails and nothing "
            "of it can run the train-tokens/s benchmark")
     if os.path.isdir(ref_dir) and os.listdir(ref_dir):
         why = "baseline/_ref holds no runnable package: " + why

@@ -30,19 +30,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA / integer pipes instead of the special-function unit: round-to-nearest split
-// x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on [-0.5, 0.5] (relative error 8e-5, well
-// below bf16 resolution), and n added into the exponent field.  The softmax loops alternate it
-// with ex2.approx so the exponentials are spread over both pipes.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -125.0f);
-  const float r = x + 12582912.0f;
-  const float f = x - (r - 12582912.0f);
-  float p = fmaf(0.055088725f, f, 0.24260436f);
-  p = fmaf(p, f, 0.69327629f);
-  p = fmaf(p, f, 0.99992895f);
-  return __int_as_float(__float_as_int(p) + ((__float_as_int(r) - 0x4B400000) << 23));
-}
 // Three-input maximum and packed two-wide fp32 arithmetic (one instruction for two lanes of work;
 // the softmax loops are bound by instruction issue, not by the exponential unit alone).
 __device__ __forceinline__ float max3(float a, float b, float c) {
