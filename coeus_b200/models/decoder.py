@@ -143,8 +143,12 @@ class DecoderLM:
                  pad_multiple: int = 8 * 1024, training: bool = True,
                  dtype: torch.dtype = torch.bfloat16, epx=None,
                  layers: Optional[Tuple[int, int]] = None, embed: bool = True,
-                 head: bool = True, cp=None) -> None:
-        """``cp`` is a :class:`coeus_b200.parallel.cp.ContextParallel` (token ids then come as this
+                 head: bool = True, cp=None, recompute: bool = False) -> None:
+        """``recompute=True`` keeps only each block's input for the backward pass and runs the
+        block's forward again there (activation checkpointing: about one third more compute for
+        a per-layer activation footprint of one ``[T, H]`` tensor instead of roughly
+        ``[T, 14 H]``).
+        ``cp`` is a :class:`coeus_b200.parallel.cp.ContextParallel` (token ids then come as this
         rank's two zig-zag chunks ``[2, B, Sc]`` and attention runs as ring attention over the
         group) or a :class:`coeus_b200.parallel.ulysses.UlyssesParallel` (ids ``[1, B, S/sp]``,
         all-to-all between sequence and head sharding around attention); ``cp.shard(ids)`` makes
@@ -157,6 +161,7 @@ class DecoderLM:
         self.cfg = cfg
         self.device = torch.device(device)
         self.cp = cp
+        self.recompute = bool(recompute)
         self.epx = None
         self.moe: List = []
         if cfg.num_experts:
@@ -352,7 +357,8 @@ class DecoderLM:
         mc = self.max_ctas
         n1, mean1, rstd1 = self._norm(x, p + n1n)
         qkv = G.linear_fwd(n1, self.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"),
-                           out=self._buf(f"qkv{l}" if save is not None else "qkv", (T, 3 * H)),
+                           out=self._buf(f"qkv{l}" if save is not None and not self.recompute else "qkv",
+                                         (T, 3 * H)),
                            max_ctas=mc)
         if cfg.pos == "rope":
             self._rope(qkv, B, S, False)
@@ -421,7 +427,11 @@ class DecoderLM:
     def forward_blocks(self, x: torch.Tensor, B: int, S: int, save: Optional[dict]) -> torch.Tensor:
         """This model's blocks applied to ``x [B*S, H]``."""
         for l in self.layer_ids:
-            x = self._block_fwd(l, x, B, S, save)
+            if save is not None and self.recompute:
+                save[l] = dict(x=x)      # the block runs again in backward_blocks
+                x = self._block_fwd(l, x, B, S, None)
+            else:
+                x = self._block_fwd(l, x, B, S, save)
         return x
 
     def forward_final_norm(self, x: torch.Tensor, save: Optional[dict]) -> torch.Tensor:
@@ -530,6 +540,10 @@ class DecoderLM:
         mc = self.max_ctas
         for l in reversed(self.layer_ids):
             a = sv[l]
+            if "n1" not in a:            # activation checkpointing: rebuild the block's tensors
+                again: dict = {}
+                self._block_fwd(l, a["x"], B, S, again)
+                a = again[l]
             p = f"layers.{l}."
             if self.moe:
                 dn2 = self.moe[l - self.layer_ids[0]].backward(dx, aux_grad_scale=sv["aux_scale"])

@@ -39,12 +39,16 @@ class TrainConfig:
 
 
 class Trainer:
-    def __init__(self, model: DecoderLM, cfg: Optional[TrainConfig] = None, dp=None) -> None:
+    def __init__(self, model: DecoderLM, cfg: Optional[TrainConfig] = None, dp=None,
+                 schedule=None) -> None:
         """``dp`` is a :class:`coeus_b200.parallel.zero.ShardedDataParallel` (or ``None`` for a
-        single replica)."""
+        single replica); ``schedule`` an object with ``at(step) -> lr``
+        (:mod:`coeus_b200.optim.lr`) applied before every optimizer step."""
         self.model = model
         self.cfg = cfg or TrainConfig()
         self.dp = dp
+        self.schedule = schedule
+        self._micro = 0
         self._training = True
         self.step_index = 0
         self.listeners: List[Callable[[dict], None]] = []
@@ -72,19 +76,36 @@ class Trainer:
         else:
             self.dp.reduce_and_step(grad_scale)
 
+    def _set_lr(self, lr: float) -> None:
+        if self.dp is None:
+            self.opt.set_learning_rate(lr)
+        else:
+            self.dp.opt_cfg.lr = lr
+
     def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        """Forward, backward and optimizer update for one (micro-)batch per rank; returns the
-        rank-local mean loss as a device scalar."""
+        """Forward and backward for one micro-batch per rank and, on every ``grad_accum``-th call,
+        the optimizer update (gradients of the calls in between are summed, each scaled by
+        ``1 / grad_accum``); returns the rank-local mean loss as a device scalar."""
         m = self.model
         world = 1 if self.dp is None else self.dp.world
-        if self.dp is not None:
-            self.dp.set_grad_scale(1.0 / world)
-            self.dp.begin_step()
-        m.zero_grad()
-        loss = m.forward_loss(ids, targets)
-        m.backward(on_layer_done=None if self.dp is None else self.dp.on_layer_done)
-        self.update_parameters(1.0 / world)
-        self.step_index += 1
+        accum = max(1, self.cfg.grad_accum)
+        first, last = self._micro == 0, self._micro == accum - 1
+        if first:
+            if self.schedule is not None:
+                self._set_lr(self.schedule.at(self.step_index))
+            if self.dp is not None:
+                self.dp.set_grad_scale(1.0 / world)
+                self.dp.begin_step()
+            m.zero_grad()
+        T = ids.numel()
+        loss = m.forward_loss(ids, targets, grad_scale=1.0 / (T * accum))
+        # the bucket reductions of the data-parallel plan start only in the last micro-step
+        hook = self.dp.on_layer_done if (self.dp is not None and last) else None
+        m.backward(on_layer_done=hook)
+        self._micro = (self._micro + 1) % accum
+        if last:
+            self.update_parameters(1.0 / world)
+            self.step_index += 1
         return loss
 
     # ---- Checkpoint trait (src/core/traits.rs:181-189)

@@ -64,3 +64,33 @@ def test_logits_last_only_matches_full():
     full = m.forward_logits(ids)
     last = m.forward_logits(ids, last_only=True)
     assert (full[:, -1].float() - last.float()).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama"])
+def test_recompute_and_accumulation_match_the_plain_step(kind):
+    """Activation recomputation reproduces the gradients; two accumulated micro-batches equal one
+    step on their union (up to the order of fp32 sums)."""
+    cfg = CFGS[kind]
+    torch.manual_seed(1)
+    batch = torch.randint(0, cfg.vocab_size, (4, 129), device="cuda")
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    grads = []
+    for rc in (False, True):
+        m = DecoderLM(cfg, device="cuda", seed=5, recompute=rc)
+        m.zero_grad()
+        m.forward_loss(x, y)
+        m.backward()
+        grads.append(m.g32.clone())
+    scale = grads[0].abs().max()
+    assert (grads[0] - grads[1]).abs().max() <= 2e-3 * scale
+    a = Trainer(DecoderLM(cfg, device="cuda", seed=5), TrainConfig(learning_rate=1e-3, eps=1e-3))
+    b = Trainer(DecoderLM(cfg, device="cuda", seed=5),
+                TrainConfig(learning_rate=1e-3, eps=1e-3, grad_accum=2))
+    a.train_step(x, y)
+    b.train_step(x[:2].contiguous(), y[:2].contiguous())
+    b.train_step(x[2:].contiguous(), y[2:].contiguous())
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
+    assert b.step_index == 1
+    d = (a.model.p32 - b.model.p32).abs()
+    assert (d > 2e-4).float().mean() < 0.01

@@ -161,3 +161,64 @@ def test_llama_style_config_on_cpu():
     for _ in range(5):
         seq.append(int(np.argmax(m.forward(seq))))
     assert out == seq
+
+
+def test_gradient_accumulation_and_schedule():
+    """Two micro-batches with grad_accum=2 equal one step on their union; the schedule drives the
+    optimizer's learning rate."""
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.optim.lr import WarmupCosine
+    from coeus_b200.train.trainer import TrainConfig, Trainer
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (4, 16))
+    tgt = torch.randint(0, 64, (4, 16))
+    a = Trainer(DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32),
+                TrainConfig(learning_rate=1e-2, eps=1.0, weight_decay=0.0))
+    a.train_step(ids, tgt)
+    b = Trainer(DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32),
+                TrainConfig(learning_rate=1e-2, eps=1.0, weight_decay=0.0, grad_accum=2))
+    b.train_step(ids[:2], tgt[:2])
+    assert b.step_index == 0 and torch.equal(b.model.p32, DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32).p32)
+    b.train_step(ids[2:], tgt[2:])
+    assert b.step_index == 1
+    assert (a.model.p32 - b.model.p32).abs().max() < 1e-6
+    sched = WarmupCosine(peak=1e-2, warmup=2, total=10, floor=1e-3)
+    assert sched.at(0) == 5e-3 and sched.at(1) == 1e-2 and abs(sched.at(10) - 1e-3) < 1e-12
+    assert sched.at(5) < sched.at(3) < sched.at(2)
+    c = Trainer(DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32), TrainConfig(), schedule=sched)
+    c.train_step(ids, tgt)
+    assert c.opt.learning_rate() == 5e-3
+    c.train_step(ids, tgt)
+    assert c.opt.learning_rate() == 1e-2
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama", "moe"])
+def test_activation_recompute_gives_the_same_gradients(kind):
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    kw = dict(hidden_dim=32, num_layers=3, num_heads=2, intermediate_dim=64, vocab_size=64,
+              max_seq_len=16)
+    if kind != "gpt":
+        kw.update(use_bias=False, activation="swiglu", norm="rmsnorm", pos="rope")
+    if kind == "moe":
+        kw.update(num_experts=4, top_k=2, capacity_factor=2.0)
+    cfg = DecoderConfig(**kw)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (2, 16))
+    tgt = torch.randint(0, 64, (2, 16))
+    grads = []
+    for rc in (False, True):
+        m = DecoderLM(cfg, "cpu", seed=3, dtype=torch.float32, recompute=rc)
+        m.zero_grad()
+        loss = m.forward_loss(ids, tgt)
+        if rc:
+            assert all(set(m._saved[l]) == {"x"} for l in m.layer_ids)
+        m.backward()
+        grads.append((float(loss), m.g32.clone()))
+    assert grads[0][0] == grads[1][0]
+    assert torch.equal(grads[0][1], grads[1][1])
