@@ -414,6 +414,48 @@ __global__ void sin_init_kernel(float* __restrict__ p, size_t n, size_t index_of
     p[i] = fminf(0.1f, fmaxf(-0.1f, v));
   }
 }
+// Counter-based normal init: Philox4x32-10 keyed by the seed, counter = group index; each group
+// of four consecutive elements takes the four outputs of one block through two Box-Muller pairs.
+// The value of element i depends on (seed, i + index_offset) only, so any shard of a tensor can
+// be drawn by itself.
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+  const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+  const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+  c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+}
+__device__ __forceinline__ float u01(uint32_t x) {   // (0, 1), exact in fp32
+  return static_cast<float>(x >> 8) * 5.9604644775390625e-8f + 2.98023223876953125e-8f;
+}
+__global__ void normal_init_kernel(float* __restrict__ p, size_t n, size_t index_offset,
+                                   uint32_t seed_lo, uint32_t seed_hi, float mean, float std) {
+  const size_t g_first = index_offset / 4, g_last = (index_offset + n + 3) / 4;
+  for (size_t g = g_first + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+       g < g_last; g += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    uint32_t c[4] = {static_cast<uint32_t>(g), static_cast<uint32_t>(g >> 32), 0u, 0u};
+    uint32_t k0 = seed_lo, k1 = seed_hi;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+      philox_round(c, k0, k1);
+      k0 += 0x9E3779B9u;
+      k1 += 0xBB67AE85u;
+    }
+    float z[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float r = sqrtf(-2.0f * logf(u01(c[2 * h])));
+      float sn, cs;
+      sincosf(6.283185307179586f * u01(c[2 * h + 1]), &sn, &cs);
+      z[2 * h] = r * cs;
+      z[2 * h + 1] = r * sn;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t i = g * 4 + j;
+      if (i >= index_offset && i < index_offset + n) p[i - index_offset] = mean + std * z[j];
+    }
+  }
+}
 __global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                    size_t n) {
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
@@ -564,6 +606,12 @@ extern "C" int cb_colsum(const void* x, float* out, int T, int C, int ld, void* 
 }
 extern "C" int cb_sin_init(float* p, size_t n, size_t index_offset, float scale, void* stream) {
   sin_init_kernel<<<grid_for(n, 256), 256, 0, CB_ST(stream)>>>(p, n, index_offset, scale);
+  CB_RET();
+}
+extern "C" int cb_normal_init(float* p, size_t n, size_t index_offset, unsigned long long seed,
+                              float mean, float std, void* stream) {
+  normal_init_kernel<<<grid_for((n + 3) / 4 + 1, 256), 256, 0, CB_ST(stream)>>>(
+      p, n, index_offset, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32), mean, std);
   CB_RET();
 }
 extern "C" int cb_f32_to_bf16(const float* x, void* y, size_t n, void* stream) {

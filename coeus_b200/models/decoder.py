@@ -233,7 +233,9 @@ class DecoderLM:
         self._bind_views()
 
     def init_parameters(self, init: str = "normal", seed: int = 0) -> None:
-        """``normal``: weights N(0, init_std), scales 1, biases 0.  ``reference``: the
+        """``normal``: weights N(0, init_std) from the PyTorch generator, scales 1, biases 0;
+        ``philox``: the same distribution from the counter-based kernel
+        (:func:`coeus_b200.ops.elementwise.normal_init_`).  ``reference``: the
         reference's deterministic ``clamp(sin(i * 0.1234567) * sqrt(2/H), ±0.1)`` for every
         element, norm scales and biases included (plugins/model-transformer/src/lib.rs:604-611);
         ``i`` is the element's index in the reference's flat layout."""
@@ -264,6 +266,21 @@ class DecoderLM:
                     del full
                 elif s.kind in ("weight", "embed"):
                     t.normal_(0.0, cfg.init_std, generator=gen)
+                elif s.kind == "scale":
+                    t.fill_(1.0)
+                else:
+                    t.zero_()
+        elif init == "philox":
+            # counter-based N(0, init_std) drawn by the framework's own kernel: one key per tensor
+            # name, the element index as counter, so every shard (expert slice, pipeline stage,
+            # CPU or GPU) holds the values of the whole tensor at its place
+            import zlib
+            for s in self.layout.specs:
+                t = self.master[s.name]
+                if s.kind in ("weight", "embed"):
+                    off = self.epx.rank * t.numel() if (s.expert and self.layout.ep > 1) else 0
+                    E.normal_init_(t, (seed << 32) ^ zlib.crc32(s.name.encode()), 0.0,
+                                   cfg.init_std, index_offset=off)
                 elif s.kind == "scale":
                     t.fill_(1.0)
                 else:

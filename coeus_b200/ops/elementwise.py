@@ -314,6 +314,57 @@ def colsum_into(x: torch.Tensor, out: torch.Tensor) -> None:
     _lib.check_rc(rc, "cb_colsum")
 
 
+def _philox4x32(counter_lo, counter_hi, seed: int):
+    """Philox4x32-10 on numpy uint64 lanes holding 32-bit values; returns the four output words."""
+    import numpy as np
+    m32 = np.uint64(0xFFFFFFFF)
+    c = [counter_lo & m32, counter_hi & m32, np.zeros_like(counter_lo), np.zeros_like(counter_lo)]
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c[0]
+        p1 = np.uint64(0xCD9E8D57) * c[2]
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & m32, p1 >> np.uint64(32), p1 & m32
+        c = [hi1 ^ c[1] ^ np.uint64(k0), lo1, hi0 ^ c[3] ^ np.uint64(k1), lo0]
+        k0 = (k0 + 0x9E3779B9) & 0xFFFFFFFF
+        k1 = (k1 + 0xBB67AE85) & 0xFFFFFFFF
+    return c
+
+
+def normal_init_(p: torch.Tensor, seed: int, mean: float = 0.0, std: float = 0.02,
+                 index_offset: int = 0) -> torch.Tensor:
+    """Fill a contiguous fp32 tensor with N(mean, std) from a counter-based generator
+    (Philox4x32-10 + Box-Muller): element ``i`` depends on ``(seed, index_offset + i)`` only, so
+    a shard of a tensor draws the values the whole tensor would have there, on CPU and GPU alike
+    (the two agree to the precision of ``logf`` / ``sincosf``).  The reference has the
+    deterministic sine init only (plugins/model-transformer/src/lib.rs:604-611)."""
+    n = p.numel()
+    seed &= (1 << 64) - 1
+    if n == 0:
+        return p
+    if not p.is_cuda:
+        import numpy as np
+        g = np.arange(index_offset // 4, (index_offset + n + 3) // 4, dtype=np.uint64)
+        w = _philox4x32(g & np.uint64(0xFFFFFFFF), g >> np.uint64(32), seed)
+        u = [((x >> np.uint64(8)).astype(np.float32) * np.float32(2.0 ** -24) + np.float32(2.0 ** -25))
+             for x in w]
+        z = np.empty((g.size, 4), dtype=np.float32)
+        for h in range(2):
+            r = np.sqrt(np.float32(-2.0) * np.log(u[2 * h]))
+            th = np.float32(6.283185307179586) * u[2 * h + 1]
+            z[:, 2 * h] = r * np.cos(th)
+            z[:, 2 * h + 1] = r * np.sin(th)
+        lo = index_offset - (index_offset // 4) * 4
+        vals = np.float32(mean) + np.float32(std) * z.reshape(-1)[lo:lo + n]
+        p.copy_(torch.from_numpy(vals).reshape(p.shape))
+        return p
+    assert p.dtype == torch.float32 and p.is_contiguous()
+    rc = _lib.lib().cb_normal_init(_lib.ptr(p), c_size_t(n), c_size_t(index_offset),
+                                   ctypes.c_uint64(seed), c_float(mean), c_float(std),
+                                   _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_normal_init")
+    return p
+
+
 def sin_init_(p: torch.Tensor, hidden: int, index_offset: int = 0) -> torch.Tensor:
     """The reference's deterministic init ``clamp(sin(f32(i) * 0.1234567) * sqrt(2/H), ±0.1)``
     (plugins/model-transformer/src/lib.rs:604-611) on a flat fp32 tensor."""

@@ -224,3 +224,15 @@ def test_attention_fwd_bwd(dh, causal, S):
     for got, ref, name in ((dq, dqr, "dq"), (dk, dkr, "dk"), (dv, dvr, "dv")):
         err = (got.float().cpu() - ref.float()).abs().max().item()
         assert err < 0.02 * ref.float().abs().max().item() + 0.03, (name, err)
+
+
+def test_normal_init_matches_cpu_generator():
+    from coeus_b200.ops import elementwise as E
+    n = 1_000_003
+    ref = E.normal_init_(torch.empty(n), seed=(7 << 32) | 99, std=0.02)
+    got = E.normal_init_(torch.empty(n, device="cuda"), seed=(7 << 32) | 99, std=0.02)
+    torch.cuda.synchronize()
+    assert (got.cpu() - ref).abs().max() < 2e-6
+    part = E.normal_init_(torch.empty(4097, device="cuda"), seed=(7 << 32) | 99, std=0.02,
+                          index_offset=333_333)
+    assert torch.equal(part, got[333_333:333_333 + 4097])

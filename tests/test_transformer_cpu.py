@@ -222,3 +222,38 @@ def test_activation_recompute_gives_the_same_gradients(kind):
         grads.append((float(loss), m.g32.clone()))
     assert grads[0][0] == grads[1][0]
     assert torch.equal(grads[0][1], grads[1][1])
+
+
+def test_counter_based_normal_init():
+    import numpy as np
+    import torch
+    from coeus_b200.ops import elementwise as E
+    full = E.normal_init_(torch.empty(40_001), seed=1234, std=0.02)
+    assert abs(float(full.mean())) < 5e-4 and abs(float(full.std()) - 0.02) < 5e-4
+    # kurtosis of a normal distribution, and no repeated values
+    z = (full / 0.02).double()
+    assert abs(float((z ** 4).mean()) - 3.0) < 0.15
+    assert np.unique(full.numpy()).size > 39_900
+    # any slice draws what the whole tensor has there
+    for off, n in ((0, 7), (5, 1), (6, 1031), (4096, 4)):
+        part = E.normal_init_(torch.empty(n), seed=1234, std=0.02, index_offset=off)
+        assert torch.equal(part, full[off:off + n])
+    assert not torch.equal(E.normal_init_(torch.empty(64), seed=1235), full[:64])
+    # known-answer test of the generator: Philox4x32-10, counter 0, key 0 (Random123 vectors)
+    w = E._philox4x32(np.zeros(1, np.uint64), np.zeros(1, np.uint64), 0)
+    assert [int(x[0]) for x in w] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+
+
+def test_philox_model_init_is_shard_invariant():
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    cfg = DecoderConfig(hidden_dim=32, num_layers=4, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    whole = DecoderLM(cfg, "cpu", init="philox", seed=2, dtype=torch.float32)
+    stage = DecoderLM(cfg, "cpu", init="philox", seed=2, dtype=torch.float32, layers=(2, 4),
+                      embed=False)
+    for name, t in stage.named_parameters():
+        assert torch.equal(t, whole.master[name]), name
+    w = whole.master["layers.0.attn.qkv_weights"]
+    assert abs(float(w.std()) - cfg.init_std) < 0.1 * cfg.init_std
