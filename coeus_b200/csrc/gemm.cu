@@ -49,6 +49,10 @@ struct GemmArgs {
   int ksplit;
   int tma_store;                // bf16 outputs leave through shared memory and TMA stores
   int* status;
+  // ---- grouped GEMM (experts stacked along the row dimension of every operand's memory)
+  int group_m;                  // output rows per group; 0 = one group.  Group g of a tile adds
+  int g_am, g_ak;               // g * g_am to A's m coordinate, g * g_ak to its k coordinate,
+  int g_bn, g_bk;               // g * g_bn to B's n coordinate, g * g_bk to its k coordinate
   // ---- fused collectives over peer memory (COMM template parameter)
   int tp, rank;                 // ranks of the tensor-parallel group, this rank
   int tiles_per_shard;          // 128-row tiles per rank's sequence shard
@@ -280,6 +284,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int n0 = (tile % tiles_n) * BN;
         const int kb0 = split * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
+        // grouped GEMM: the tile's group shifts where its operands start
+        const int grp = p.group_m > 0 ? (m_blk * TILE_M) / p.group_m : 0;
+        const int am0 = m0 + grp * p.g_am, ak0 = grp * p.g_ak;
+        const int bn_off = grp * p.g_bn, bk0 = grp * p.g_bk;
         if constexpr (COMM == COMM_AG) {
           if (m_blk / p.tiles_per_shard != p.rank) {  // rows that come from a peer
             const uint64_t t0 = globaltimer_ns();
@@ -311,37 +319,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // rank 0 arms for the pair
             const uint32_t fb = mapa_shared(full_bar(stage), 0u);
             if (cta_rank == 0u) mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
-            const int nb = n0 + static_cast<int>(cta_rank) * (BN / 2);   // this CTA's half of B
+            // this CTA's half of B
+            const int nb = n0 + bn_off + static_cast<int>(cta_rank) * (BN / 2);
             if constexpr (!A_MN) {
-              tma_load_2d_cg2(sA, &tmA, fb, kb * GEMM_BK, m0);
+              tma_load_2d_cg2(sA, &tmA, fb, kb * GEMM_BK + ak0, am0);
             } else {
 #pragma unroll
               for (int c = 0; c < GEMM_BM / 64; ++c)
-                tma_load_2d_cg2(sA + c * 8192, &tmA, fb, m0 + c * 64, kb * GEMM_BK);
+                tma_load_2d_cg2(sA + c * 8192, &tmA, fb, am0 + c * 64, kb * GEMM_BK + ak0);
             }
             if constexpr (!B_MN) {
-              tma_load_2d_cg2(sB, &tmB, fb, kb * GEMM_BK, nb);
+              tma_load_2d_cg2(sB, &tmB, fb, kb * GEMM_BK + bk0, nb);
             } else {
 #pragma unroll
               for (int c = 0; c < BN / 128; ++c)
-                tma_load_2d_cg2(sB + c * 8192, &tmB, fb, nb + c * 64, kb * GEMM_BK);
+                tma_load_2d_cg2(sB + c * 8192, &tmB, fb, nb + c * 64, kb * GEMM_BK + bk0);
             }
           } else {
           const uint32_t fb = full_bar(stage);
           mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
           if constexpr (!A_MN) {
-            tma_load_2d(sA, &tmA, fb, kb * GEMM_BK, m0);
+            tma_load_2d(sA, &tmA, fb, kb * GEMM_BK + ak0, am0);
           } else {
 #pragma unroll
             for (int c = 0; c < GEMM_BM / 64; ++c)
-              tma_load_2d(sA + c * 8192, &tmA, fb, m0 + c * 64, kb * GEMM_BK);
+              tma_load_2d(sA + c * 8192, &tmA, fb, am0 + c * 64, kb * GEMM_BK + ak0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sB, &tmB, fb, kb * GEMM_BK, n0);
+            tma_load_2d(sB, &tmB, fb, kb * GEMM_BK + bk0, n0 + bn_off);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + c * 8192, &tmB, fb, n0 + c * 64, kb * GEMM_BK);
+              tma_load_2d(sB + c * 8192, &tmB, fb, n0 + bn_off + c * 64, kb * GEMM_BK + bk0);
           }
           }
           ++armed;
@@ -787,19 +796,34 @@ extern "C" void cb_gemm_use_pairs(int on) { cb::g_use_pairs = on; }
 //   A: logical [M,K]; a_mn == 0: memory [M,K] row-major (pitch lda); a_mn == 1: memory [K,M].
 //   B: logical [N,K]; b_mn == 0: memory [N,K] row-major (pitch ldb); b_mn == 1: memory [K,N].
 // Requirements: K, N (and M when a_mn) multiples of 8; 16-byte aligned pointers and pitches.
-extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
-                            int ldb, int ldd, int a_mn, int b_mn, const void* bias,
-                            const void* resid, int ldr, const void* aux_in, void* aux_out,
-                            int ldaux, int epi, int out_mode, float alpha, int ksplit, int bn,
-                            int* status, int max_ctas, void* stream) {
+//
+// groups > 1 (grouped GEMM, e.g. the experts of a mixture-of-experts layer): M, N and K are the
+// sizes of ONE group and every operand holds the groups stacked along the row dimension of its
+// memory: A is [groups*M, K] (a_mn == 0) or [groups*K, M] (a_mn == 1); B is [groups*N, K]
+// (b_mn == 0) or [groups*K, N] (b_mn == 1); D, resid and aux are [groups*M, N].  Group g's output
+// rows are produced from group g's slices.  Needs M a multiple of the tile height (128; CTA pairs
+// are used when it is a multiple of 256) and K a multiple of 64, so that no tile or k-block
+// straddles two groups.
+static int gemm_bf16_impl(const void* A, const void* B, void* D, int M, int N, int K, int lda,
+                          int ldb, int ldd, int a_mn, int b_mn, const void* bias,
+                          const void* resid, int ldr, const void* aux_in, void* aux_out,
+                          int ldaux, int epi, int out_mode, float alpha, int ksplit, int bn,
+                          int* status, int max_ctas, void* stream, int groups) {
   using namespace cb;
-  if (M <= 0 || N <= 0 || K <= 0) return -20;
+  if (M <= 0 || N <= 0 || K <= 0 || groups < 1) return -20;
   if ((N % 8) != 0 || (K % 8) != 0 || (ldd % 4) != 0) return -21;
   if (out_mode == OUT_BF16 && (ldd % 8) != 0) return -21;
   // bn = 512 selects the 256-wide tile on CTA pairs
-  const bool pairs = bn == 512 || (bn == 256 && cb::g_use_pairs);
+  bool pairs = bn == 512 || (bn == 256 && cb::g_use_pairs);
   if (bn == 512) bn = 256;
   if (bn != 128 && bn != 256) return -22;
+  const int Mg = M, Kg = K;       // per-group sizes; M becomes the stacked row count below
+  if (groups > 1) {
+    if ((Mg % GEMM_BM) != 0 || (Kg % GEMM_BK) != 0) return -24;
+    if ((Mg % (2 * GEMM_BM)) != 0) pairs = false;
+    if (static_cast<long long>(Mg) * groups > 0x7fffffffLL) return -24;
+    M = Mg * groups;
+  }
   const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
   if (ksplit < 1) ksplit = 1;
   if (ksplit > kblocks) ksplit = kblocks;
@@ -811,15 +835,16 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (ksplit > 1 && out_mode != OUT_F32_ATOMIC) return -23;
   CUtensorMap ta, tb;
   int rc;
+  const uint64_t G64 = static_cast<uint64_t>(groups);
   if (a_mn == 0)
     rc = make_tmap_bf16_2d(&ta, A, K, M, lda, 64, GEMM_BM);
   else
-    rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, 64);
+    rc = make_tmap_bf16_2d(&ta, A, Mg, G64 * Kg, lda, 64, 64);
   if (rc != 0) return rc - 30;
   if (b_mn == 0)
-    rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, 64, (bn == 256 && pairs) ? 128 : bn);
+    rc = make_tmap_bf16_2d(&tb, B, K, G64 * N, ldb, 64, (bn == 256 && pairs) ? 128 : bn);
   else
-    rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, 64);
+    rc = make_tmap_bf16_2d(&tb, B, N, G64 * Kg, ldb, 64, 64);
   if (rc != 0) return rc - 40;
   // bf16 results (and the kept pre-activation) go out through swizzled shared memory and TMA
   // stores whenever the output rows are 16-byte aligned; fp32 / atomic outputs are stored directly
@@ -847,6 +872,13 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   g.aux_out = static_cast<__nv_bfloat16*>(aux_out);
   g.ldaux = ldaux;
   g.epi = epi; g.out_mode = out_mode; g.alpha = alpha; g.ksplit = ksplit; g.status = status;
+  if (groups > 1) {
+    g.group_m = Mg;
+    g.g_am = a_mn ? -Mg : 0;
+    g.g_ak = a_mn ? Kg : 0;
+    g.g_bn = b_mn ? 0 : N;
+    g.g_bk = b_mn ? Kg : 0;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define CB_DISPATCH(BN_)                                                            \
   do {                                                                              \
@@ -864,6 +896,25 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (bn == 256) CB_DISPATCH(256);
   CB_DISPATCH(128);
 #undef CB_DISPATCH
+}
+
+extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
+                            int ldb, int ldd, int a_mn, int b_mn, const void* bias,
+                            const void* resid, int ldr, const void* aux_in, void* aux_out,
+                            int ldaux, int epi, int out_mode, float alpha, int ksplit, int bn,
+                            int* status, int max_ctas, void* stream) {
+  return gemm_bf16_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, bias, resid, ldr, aux_in,
+                        aux_out, ldaux, epi, out_mode, alpha, ksplit, bn, status, max_ctas, stream,
+                        1);
+}
+
+extern "C" int cb_gemm_bf16_grouped(const void* A, const void* B, void* D, int groups, int M, int N,
+                                    int K, int lda, int ldb, int ldd, int a_mn, int b_mn,
+                                    int out_mode, float alpha, int ksplit, int bn, int* status,
+                                    int max_ctas, void* stream) {
+  return gemm_bf16_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, nullptr, nullptr, 0, nullptr,
+                        nullptr, 0, cb::EPI_NONE, out_mode, alpha, ksplit, bn, status, max_ctas,
+                        stream, groups);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -141,6 +141,65 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def gemm_grouped(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+                 out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+                 accumulate: bool = False, alpha: float = 1.0, ksplit: int = 1,
+                 max_ctas: int = 0) -> torch.Tensor:
+    """``out[g] = alpha * A[g] @ B[g]^T`` for every group ``g`` in ONE launch (the experts of a
+    mixture-of-experts layer).  ``a`` is ``[G, M, K]`` (``a_mn``: ``[G, K, M]``), ``b`` is
+    ``[G, N, K]`` (``b_mn``: ``[G, K, N]``), ``out`` ``[G, M, N]``; groups must lie one after the
+    other in memory (``stride(0) == shape[1] * stride(1)``).  The kernel is the persistent
+    tcgen05 GEMM with a per-tile group offset on the operand coordinates; it needs ``M`` to be
+    a multiple of 128 and ``K`` of 64 so that no tile straddles two groups -- other shapes run
+    one launch per group."""
+    assert a.dim() == 3 and b.dim() == 3 and a.shape[0] == b.shape[0]
+    Gn = a.shape[0]
+    M, K = (a.shape[2], a.shape[1]) if a_mn else (a.shape[1], a.shape[2])
+    N, Kb = (b.shape[2], b.shape[1]) if b_mn else (b.shape[1], b.shape[2])
+    if K != Kb:
+        raise ValueError(f"gemm_grouped: contraction mismatch {K} vs {Kb}")
+    if accumulate:
+        out_dtype = torch.float32
+        if out is None:
+            raise ValueError("gemm_grouped: accumulate=True needs an fp32 `out`")
+    if out is None:
+        if not a.is_cuda and a.dtype != torch.bfloat16 and out_dtype == torch.bfloat16:
+            out_dtype = a.dtype
+        out = torch.empty((Gn, M, N), dtype=out_dtype, device=a.device)
+    stacked = all(t.stride(2) == 1 and t.stride(0) == t.shape[1] * t.stride(1)
+                  for t in (a, b, out))
+    if not a.is_cuda or not stacked or M % 128 or K % 64 or Gn == 1:
+        for g in range(Gn):
+            gemm(a[g], b[g], a_mn=a_mn, b_mn=b_mn, out=out[g], out_dtype=out_dtype,
+                 accumulate=accumulate, alpha=alpha, ksplit=ksplit, max_ctas=max_ctas)
+        return out
+    for t in (a, b):
+        if t.dtype != torch.bfloat16:
+            raise ValueError("gemm_grouped: operands must be bf16")
+    out_mode = _OUT_F32_ATOMIC if accumulate else (
+        _OUT_F32 if out.dtype == torch.float32 else _OUT_BF16)
+    bn = _pick_bn(M, N, ksplit)
+    st = _lib.status_buffer(a.device)
+    rc = _lib.lib().cb_gemm_bf16_grouped(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), Gn, M, N, K, a.stride(1), b.stride(1),
+        out.stride(1), int(a_mn), int(b_mn), out_mode, ctypes.c_float(alpha), ksplit, bn,
+        _lib.ptr(st), max_ctas, _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_gemm_bf16_grouped")
+    return out
+
+
+def linear_wgrad_grouped(x: torch.Tensor, dy: torch.Tensor, grad_w: torch.Tensor, *,
+                         max_ctas: int = 0) -> torch.Tensor:
+    """``grad_w[g][in,out] += x[g][T,in]^T @ dy[g][T,out]`` for all groups in one launch."""
+    Gn, T, Min, Nout = x.shape[0], x.shape[1], x.shape[2], dy.shape[2]
+    if _pick_bn(Min, Nout, 1) == 512 and Min % 256 == 0:     # CTA pairs: 256-row tiles, 74 units
+        ksplit = _pick_ksplit(Gn * (Min // 256) * ((Nout + 255) // 256), (T + 63) // 64, sms=74)
+    else:
+        ksplit = _pick_ksplit(Gn * ((Min + 127) // 128) * ((Nout + 255) // 256), (T + 63) // 64)
+    return gemm_grouped(x, dy, a_mn=True, b_mn=True, out=grad_w, accumulate=True, ksplit=ksplit,
+                        max_ctas=max_ctas)
+
+
 def linear_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
                resid: Optional[torch.Tensor] = None, epi: str = "none",
                aux_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,

@@ -134,24 +134,38 @@ class ExpertParallel:
             self.pad.signal(s0 + 2, epoch)                         # results are in your buffers
             self.pad.wait(s0 + 2, epoch)                           # ... and theirs are in mine
             return
-        # collective / single-rank path
+        raise ProcessingError.invalid_input(
+            "run_experts is the fused transport; use run_experts_grouped with this backend")
+
+    @property
+    def fused(self) -> bool:
+        return self.backend == "fused" and self.ep > 1
+
+    def run_experts_grouped(self, b: dict, C: int, El: int, first_all, second_all) -> None:
+        """The same two-GEMM pass with a library all-to-all (or none on one rank) around grouped
+        GEMMs: ``first_all(xg)`` maps the exchanged rows ``[El, ep*C, H]`` of all local experts to
+        the input ``[El, ep*C, K2]`` of the second GEMM; ``second_all()`` returns the stacked
+        weights ``(w2, b_mn)`` of the GEMM whose result rows go back."""
+        ep = self.ep
+        send, ret = b["send"], b["ret"]
+        H = send.shape[1]
+        b["epoch"] += 1
         if ep > 1:
             recv = torch.empty_like(send)
             dist.all_to_all_single(recv, send, group=self.group)    # [ep(src), El, C, H]
-            rv = recv.view(ep, El, C, H)
-        outs = []
-        for j in range(El):
-            # a private copy: the send buffer is reused by the next layer while backward needs these rows
-            xg = rv[:, j].reshape(ep * C, H).contiguous() if ep > 1 else send[j * C:(j + 1) * C].clone()
-            a2 = first(j, xg, None)
-            w2, b_mn = second(j, a2)
-            outs.append(G.gemm(a2, w2, b_mn=b_mn))
+            xg = recv.view(ep, El, C, H).permute(1, 0, 2, 3).reshape(El, ep * C, H)
+        else:
+            # a private copy: the send buffer is reused by the next layer while backward needs
+            # these rows
+            xg = send.view(El, C, H).clone()
+        a2 = first_all(xg)
+        w2, b_mn = second_all()
         if ep > 1:
-            back = torch.stack([o.view(ep, C, -1) for o in outs], 1).contiguous()  # [ep, El, C, H]
+            out = G.gemm_grouped(a2, w2, b_mn=b_mn)                 # [El, ep*C, H]
+            back = out.view(El, ep, C, -1).permute(1, 0, 2, 3).contiguous()
             dist.all_to_all_single(ret.view(ep, El, C, -1), back, group=self.group)
         else:
-            for j, o in enumerate(outs):
-                ret[j * C:(j + 1) * C].copy_(o)
+            G.gemm_grouped(a2, w2, b_mn=b_mn, out=ret.view(El, C, -1))
 
     def before_send_write(self, b: dict) -> None:
         if self.backend == "fused" and self.ep > 1 and b["epoch"] > 0:
@@ -232,7 +246,16 @@ class MoEFFN:
             kept[j] = (xg, gu, act)
             return act
 
-        epx.run_experts("f", b, C, self.El, first, lambda j, a2: (self.w["down"][j], True))
+        def first_all(xg):      # all local experts in one grouped launch per GEMM
+            gu = G.gemm_grouped(xg, self.w["gate_up"], b_mn=True)
+            act = E.swiglu_fwd(gu.view(-1, 2 * self.I)).view(self.El, -1, self.I)
+            kept["all"] = (xg, gu, act)
+            return act
+
+        if epx.fused:
+            epx.run_experts("f", b, C, self.El, first, lambda j, a2: (self.w["down"][j], True))
+        else:
+            epx.run_experts_grouped(b, C, self.El, first_all, lambda: (self.w["down"], True))
         out = M.combine_rows(b["ret"], expert, slot, C, w, resid)
         # load-balancing auxiliary loss: E * sum_e f_e * P_e
         frac = torch.zeros(self.E, dtype=torch.float32, device=x.device)
@@ -271,7 +294,21 @@ class MoEFFN:
             G.linear_wgrad(xg, dgu, self.g["gate_up"][j])
             return dgu
 
-        epx.run_experts("b", b, C, self.El, first, lambda j, a2: (self.w["gate_up"][j], False))
+        def first_all(dyg):
+            xg, gu, act = kept["all"]
+            dact = G.gemm_grouped(dyg, self.w["down"], b_mn=False)
+            G.linear_wgrad_grouped(act, dyg, self.g["down"])
+            dgu = E.swiglu_bwd(gu.view(-1, 2 * self.I), dact.view(-1, self.I)).view(
+                self.El, -1, 2 * self.I)
+            G.linear_wgrad_grouped(xg, dgu, self.g["gate_up"])
+            return dgu
+
+        if epx.fused:
+            epx.run_experts("b", b, C, self.El, first,
+                            lambda j, a2: (self.w["gate_up"][j], False))
+        else:
+            epx.run_experts_grouped(b, C, self.El, first_all,
+                                    lambda: (self.w["gate_up"], False))
         dx = M.combine_rows(b["ret"], expert, slot, C, None, None)
         epx.after_combine(b)
         # router: w_k = p_k / sum_j p_j over the chosen experts, plus the auxiliary loss

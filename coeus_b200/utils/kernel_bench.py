@@ -59,6 +59,9 @@ def main(argv=None) -> int:
     ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
     ap.add_argument("--epi", default="none", choices=["none", "gelu", "bias"])
     ap.add_argument("--ksplit", type=int, default=0)
+    ap.add_argument("--groups", type=int, default=1,
+                    help="gemm: number of stacked groups (experts); m, n, k are per group and "
+                         "--compare-torch then times one launch per group instead")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
@@ -86,7 +89,28 @@ def main(argv=None) -> int:
     hbm, tf, src = peaks()
     flops = nbytes = 0.0
     torch_fn = None
-    if a.kernel == "gemm":
+    if a.kernel == "gemm" and a.groups > 1:
+        Gn, M, Nn, K = a.groups, a.m, a.n, a.k
+        w = torch.randn(Gn, K, Nn, device=dev).to(bf)
+        if a.layout == "fwd":
+            x = torch.randn(Gn, M, K, device=dev).to(bf)
+            obuf = torch.empty(Gn, M, Nn, device=dev, dtype=bf)
+            fn = lambda: G.gemm_grouped(x, w, b_mn=True, out=obuf)  # noqa: E731
+            torch_fn = lambda: [G.gemm(x[g], w[g], b_mn=True, out=obuf[g]) for g in range(Gn)]  # noqa: E731
+        elif a.layout == "dgrad":
+            dy = torch.randn(Gn, M, Nn, device=dev).to(bf)
+            obuf = torch.empty(Gn, M, K, device=dev, dtype=bf)
+            fn = lambda: G.gemm_grouped(dy, w, out=obuf)  # noqa: E731
+            torch_fn = lambda: [G.gemm(dy[g], w[g], out=obuf[g]) for g in range(Gn)]  # noqa: E731
+        else:
+            x = torch.randn(Gn, M, K, device=dev).to(bf)
+            dy = torch.randn(Gn, M, Nn, device=dev).to(bf)
+            gw = torch.zeros(Gn, K, Nn, device=dev)
+            fn = lambda: G.linear_wgrad_grouped(x, dy, gw)  # noqa: E731
+            torch_fn = lambda: [G.linear_wgrad(x[g], dy[g], gw[g]) for g in range(Gn)]  # noqa: E731
+        flops = 2.0 * Gn * M * Nn * K
+        nbytes = 2.0 * Gn * (M * K + K * Nn + M * Nn)
+    elif a.kernel == "gemm":
         M, Nn, K = a.m, a.n, a.k
         if a.layout == "fwd":      # y[M,N] = x[M,K] @ w[K,N]
             x = torch.randn(M, K, device=dev).to(bf)
