@@ -83,7 +83,7 @@ __global__ void sinusoid_pe_kernel(float* __restrict__ pe, int S, int H) {
 // With vocab-parallel shards (vocab_start, partial stats) the fwd/bwd halves are split:
 //   mode 0: fused fwd+bwd;  mode 1: stats only (max, sumexp, target logit);  mode 2: bwd from lse.
 constexpr int CE_THREADS = 512;
-__global__ void __launch_bounds__(CE_THREADS)
+__global__ void __launch_bounds__(CE_THREADS, 4)
 ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
           float* __restrict__ loss, float* __restrict__ stats, const float* __restrict__ lse_in,
           int T, int V, int ld, int vocab_start, float grad_scale, int mode) {
@@ -94,6 +94,8 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
     const int64_t tgt = targets[t];
     const int local_tgt = (tgt >= vocab_start && tgt < vocab_start + V)
                               ? static_cast<int>(tgt - vocab_start) : -1;
+    // exponentials run as ex2(v * log2(e) - c * log2(e)): one FMA and one special-function op
+    constexpr float L2E = 1.4426950408889634f;
     float lse;
     if (mode != 2) {
       float m = -INFINITY, s = 0.f;
@@ -105,18 +107,21 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
           for (int e = 0; e < 8; ++e)
             if (vec * 8 + e >= V) v[e] = -INFINITY;
         }
-        float lm = v[0];
-#pragma unroll
-        for (int e = 1; e < 8; ++e) lm = fmaxf(lm, v[e]);
+        const float lm = fmaxf(max3(v[0], v[1], v[2]), fmaxf(max3(v[3], v[4], v[5]),
+                                                              fmaxf(v[6], v[7])));
         const float nm = fmaxf(m, lm);
-        float add = 0.f;
+        const float nb = -nm * L2E;
+        float add0 = 0.f, add1 = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) add += __expf(v[e] - nm);
-        s = s * __expf(m - nm) + add;
+        for (int e = 0; e < 8; e += 2) {
+          add0 += fast_exp2(fmaf(v[e], L2E, nb));
+          add1 += fast_exp2(fmaf(v[e + 1], L2E, nb));
+        }
+        s = s * fast_exp2((m - nm) * L2E) + (add0 + add1);
         m = nm;
       }
       const float gm = block_max(m, red);
-      s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+      s = (m == -INFINITY) ? 0.f : s * fast_exp2((m - gm) * L2E);
       const float gs = block_sum(s, red);
       lse = gm + __logf(gs);
       const float tl = local_tgt >= 0 ? __bfloat162float(row[local_tgt]) : 0.f;
@@ -133,15 +138,26 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
     } else {
       lse = lse_in[t];
     }
+    // d logit = (softmax - onehot) * scale; exp(v - lse) * scale = ex2(v * log2(e) + c) with the
+    // scale folded into the exponent would lose the exact zero of an ignored token, so the
+    // product stays a separate multiply
     const float scale = tgt < 0 ? 0.f : grad_scale;
+    const float nl = -lse * L2E;
+    const int tvec = local_tgt >> 3;          // -1 when the target lies in another shard
     for (int vec = threadIdx.x; vec < nv; vec += CE_THREADS) {
       float v[8];
       load8(row + vec * 8, v);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float p = __expf(v[e] - lse);
-        if (vec * 8 + e == local_tgt) p -= 1.0f;
-        v[e] = (vec * 8 + e < V) ? p * scale : 0.f;
+      for (int e = 0; e < 8; ++e) v[e] = fast_exp2(fmaf(v[e], L2E, nl)) * scale;
+      if (vec == tvec) {                       // one vector per row
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (e == (local_tgt & 7)) v[e] -= scale;
+      }
+      if (vec * 8 + 8 > V) {                   // padding columns of the last vector
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (vec * 8 + e >= V) v[e] = 0.f;
       }
       store8(row + vec * 8, v);
     }

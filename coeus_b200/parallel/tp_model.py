@@ -28,8 +28,11 @@ from .tp import TensorParallel
 
 class TPDecoderLM:
     def __init__(self, cfg: DecoderConfig, tp: TensorParallel, device, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16, full=None) -> None:
+                 dtype: torch.dtype = torch.bfloat16, full=None, recompute: bool = False) -> None:
+        """``recompute=True`` keeps only each block's (sequence-sharded) input and runs the
+        block's forward, collectives included, again in the backward pass."""
         cfg.validate()
+        self.recompute = bool(recompute)
         if cfg.use_bias or cfg.num_experts or cfg.tie_embeddings:
             raise ProcessingError.unsupported(
                 "tensor-parallel decoder with biases, experts or tied embeddings",
@@ -159,6 +162,32 @@ class TPDecoderLM:
         return self._pe
 
     # ------------------------------------------------------------------ forward
+    def _layer_fwd(self, l: int, x: torch.Tensor, B: int, S: int):
+        """One block on this rank's ``[T/tp, H]`` rows; returns the block output and the tensors
+        its backward needs."""
+        cfg, tp = self.cfg, self.tp
+        T = B * S
+        H, dh, nh, Hl = cfg.hidden_dim, cfg.head_dim, self.nh_l, self.Hl
+        p = f"layers.{l}."
+        n1, mean1, rstd1 = self._norm(x, p + "norm1")
+        tp.own_rows("ag_attn", T, H).copy_(n1)
+        qkv, n1_full = tp.ag_gemm("ag_attn", self.w[p + "attn.qkv_weights"])
+        n1_full = n1_full.clone()
+        if cfg.pos == "rope":
+            E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)
+        q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+        attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+        x_mid = tp.gemm_rs("rs_attn", attn, self.w[p + "attn.o_weights"], resid=x)
+        n2, mean2, rstd2 = self._norm(x_mid, p + "norm2")
+        tp.own_rows("ag_mlp", T, H).copy_(n2)
+        u, n2_full = tp.ag_gemm("ag_mlp", self.w[p + "ff.up_weights"])
+        n2_full = n2_full.clone()
+        act = E.swiglu_fwd(u) if self.swiglu else E.gelu_fwd(u)
+        x_out = tp.gemm_rs("rs_mlp", act, self.w[p + "ff.down_weights"], resid=x_mid)
+        return x_out, dict(x=x, mean1=mean1, rstd1=rstd1, n1_full=n1_full, qkv=qkv, attn=attn,
+                           lse=lse, x_mid=x_mid, mean2=mean2, rstd2=rstd2, n2_full=n2_full, u=u,
+                           act=act)
+
     def forward_loss(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """``ids``, ``targets``: the SAME ``[B, S]`` batch on every rank of the group.  Returns the
         mean loss (identical on all ranks) and keeps what :meth:`backward` needs."""
@@ -178,25 +207,8 @@ class TPDecoderLM:
         x = E.embed_fwd(my_ids, self.w["token_embed"], self._positions(S), S, pos_offset=pos_off)
         sv: dict = {"ids": my_ids, "B": B, "S": S, "T": T, "Ts": Ts, "layers": []}
         for l in range(cfg.num_layers):
-            p = f"layers.{l}."
-            n1, mean1, rstd1 = self._norm(x, p + "norm1")
-            tp.own_rows("ag_attn", T, H).copy_(n1)
-            qkv, n1_full = tp.ag_gemm("ag_attn", self.w[p + "attn.qkv_weights"])
-            n1_full = n1_full.clone()
-            if cfg.pos == "rope":
-                E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)
-            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
-            attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
-            x_mid = tp.gemm_rs("rs_attn", attn, self.w[p + "attn.o_weights"], resid=x)
-            n2, mean2, rstd2 = self._norm(x_mid, p + "norm2")
-            tp.own_rows("ag_mlp", T, H).copy_(n2)
-            u, n2_full = tp.ag_gemm("ag_mlp", self.w[p + "ff.up_weights"])
-            n2_full = n2_full.clone()
-            act = E.swiglu_fwd(u) if self.swiglu else E.gelu_fwd(u)
-            x_out = tp.gemm_rs("rs_mlp", act, self.w[p + "ff.down_weights"], resid=x_mid)
-            sv["layers"].append(dict(x=x, mean1=mean1, rstd1=rstd1, n1_full=n1_full, qkv=qkv,
-                                     attn=attn, lse=lse, x_mid=x_mid, mean2=mean2, rstd2=rstd2,
-                                     n2_full=n2_full, u=u, act=act))
+            x_out, kept = self._layer_fwd(l, x, B, S)
+            sv["layers"].append(dict(x=x) if self.recompute else kept)
             x = x_out
         xf, meanf, rstdf = self._norm(x, "final_norm")
         tp.own_rows("ag_head", T, H).copy_(xf)
@@ -246,6 +258,8 @@ class TPDecoderLM:
         dx = self._norm_bwd(dxf, sv["x_last"], "final_norm", sv["meanf"], sv["rstdf"], None)
         for l in reversed(range(cfg.num_layers)):
             a = sv["layers"][l]
+            if "qkv" not in a:          # activation checkpointing
+                a = self._layer_fwd(l, a["x"], B, S)[1]
             p = f"layers.{l}."
             # ---- feed-forward
             tp.own_rows("ag_mlp_b", T, H).copy_(dx)

@@ -34,6 +34,13 @@ def _worker(rank, world, port, batch, out):
     m.zero_grad()
     loss = m.forward_loss(x, y)
     m.backward()
+    # activation recomputation must reproduce the same gradients bit for bit
+    m2 = TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, full=full, recompute=True)
+    m2.zero_grad()
+    loss2 = m2.forward_loss(x, y)
+    assert all(set(a) == {"x"} for a in m2._saved["layers"])
+    m2.backward()
+    assert float(loss2) == float(loss) and torch.equal(m2.g32, m.g32)
     out.put((rank, float(loss), {k: v.numpy().copy() for k, v in m.g.items()}))
     dist.barrier()
     dist.destroy_process_group()
