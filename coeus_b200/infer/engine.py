@@ -19,6 +19,7 @@ from ..ops import decode as D
 from ..ops import elementwise as E
 from ..ops import gemm as G
 from ..ops import norm as N
+from ..ops import ring as R
 from .kv_cache import PagedKVCache
 from .sampler import select
 
@@ -74,9 +75,14 @@ class InferenceEngine:
         return G.linear_fwd(act, m.w[p + "ff.down_weights"], bias("ff.down_bias"), resid=resid)
 
     def _layers(self, x: torch.Tensor, B: int, S: int, pos0: torch.Tensor, pos0_host: int,
-                cache: PagedKVCache, prefill: bool, pos_dev: Optional[torch.Tensor] = None
-                ) -> torch.Tensor:
+                cache: PagedKVCache, prefill: bool, pos_dev: Optional[torch.Tensor] = None,
+                page_table: Optional[torch.Tensor] = None,
+                earlier: Optional[List[list]] = None) -> torch.Tensor:
+        """``earlier[l]`` (chunked prefill) lists the ``(k, v)`` of the sequence chunks that came
+        before this one; this chunk attends to them without a mask, to itself causally, and the
+        partial results are merged by their log-sum-exp."""
         m, cfg = self.m, self.cfg
+        page_table = cache.page_table if page_table is None else page_table
         H, nh, dh = cfg.hidden_dim, cfg.num_heads, cfg.head_dim
         n1n, n2n, _ = m.layout.norm_names
         for l in range(cfg.num_layers):
@@ -88,9 +94,19 @@ class InferenceEngine:
                 E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos0_host, theta=cfg.rope_theta,
                         pos_dev=pos_dev)
             q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
-            D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, nh, dh)
+            D.kv_write(k, v, cache.k[l], cache.v[l], page_table, pos0, S, nh, dh)
             if prefill:
-                attn, _ = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+                attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+                if earlier is not None:
+                    if earlier[l]:
+                        acc = torch.empty((B * S, H), dtype=torch.float32, device=x.device)
+                        lse_acc = torch.empty_like(lse)
+                        R.merge_partial(acc, lse_acc, attn, lse, B, S, nh, dh, True)
+                        for kj, vj in earlier[l]:
+                            o_p, lse_p = A.attention_fwd(q, kj, vj, B, S, nh, dh, causal=False)
+                            R.merge_partial(acc, lse_acc, o_p, lse_p, B, S, nh, dh, False)
+                        R.cast_rows(acc, attn)
+                    earlier[l].append((k, v))
             else:
                 attn = D.decode_attention(q, cache.k[l], cache.v[l], cache.page_table,
                                           self._ctx, nh, dh, splits=self.decode_splits)
@@ -105,18 +121,38 @@ class InferenceEngine:
         return G.gemm(xf, w, b_mn=b_mn)
 
     # ------------------------------------------------------------------ public API
-    def prefill(self, ids: torch.Tensor, total_len: int) -> torch.Tensor:
+    def prefill(self, ids: torch.Tensor, total_len: int, seq_chunk: Optional[int] = None,
+                token_chunk: Optional[int] = None) -> torch.Tensor:
         """Runs the prompt ``ids [B, S]`` through the model, fills the cache, returns the logits
-        of the last position ``[B, V]``."""
+        of the last position ``[B, V]``.
+
+        Chunking bounds the activation memory of a large prompt batch: ``seq_chunk`` sequences
+        are taken at a time, and within them ``token_chunk`` positions at a time (rounded down to
+        a divisor of ``S``; every chunk attends to the keys and values of the chunks before it,
+        which are kept until the group of sequences is done)."""
         B, S = ids.shape
-        cache = self._ensure_cache(B, total_len)
-        m, cfg = self.m, self.cfg
-        pos0 = torch.zeros(B, dtype=torch.int32, device=m.device)
-        x = E.embed_fwd(ids.reshape(-1), m.w["token_embed"], m._positions(max(S, total_len)), S)
-        x = self._layers(x, B, S, pos0, 0, cache, prefill=True)
-        last = x.view(B, S, -1)[:, -1, :].contiguous()
         if B > self.max_batch:
             raise ProcessingError.limit_exceeded("batch size", self.max_batch, B)
+        cache = self._ensure_cache(B, total_len)
+        m, cfg = self.m, self.cfg
+        nb = B if not seq_chunk else max(1, min(B, int(seq_chunk)))
+        Sc = S
+        if token_chunk and token_chunk < S:
+            Sc = max(d for d in range(1, int(token_chunk) + 1) if S % d == 0)
+        pe = m._positions(max(S, total_len))
+        last = torch.empty((B, cfg.hidden_dim), dtype=m.p16.dtype, device=m.device)
+        for b0 in range(0, B, nb):
+            b1 = min(B, b0 + nb)
+            Bg = b1 - b0
+            table = cache.page_table[b0:b1]
+            earlier = [[] for _ in range(cfg.num_layers)] if Sc < S else None
+            for c0 in range(0, S, Sc):
+                pos0 = torch.full((Bg,), c0, dtype=torch.int32, device=m.device)
+                x = E.embed_fwd(ids[b0:b1, c0:c0 + Sc].reshape(-1), m.w["token_embed"], pe, Sc,
+                                pos_offset=c0)
+                x = self._layers(x, Bg, Sc, pos0, c0, cache, prefill=True, page_table=table,
+                                 earlier=earlier)
+            last[b0:b1] = x.view(Bg, Sc, -1)[:, -1, :]
         self._pos = S
         self._pos0, self._ctx = self._pos_buf[:B], self._ctx_buf[:B]
         self._pos0.fill_(S)

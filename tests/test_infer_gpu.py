@@ -68,3 +68,23 @@ def test_engine_matches_full_forward(kind):
     assert out.shape == (3, 158) and torch.equal(out[:, :150], ids)
     torch.cuda.synchronize()
     _lib.check_status(torch.device("cuda", 0))
+
+
+def test_chunked_prefill_matches_one_pass():
+    torch.manual_seed(0)
+    cfg = DecoderConfig(hidden_dim=256, num_layers=2, num_heads=2, intermediate_dim=512,
+                        vocab_size=1000, max_seq_len=512, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope")
+    m = DecoderLM(cfg, device=DEV, training=False)
+    ids = torch.randint(0, cfg.vocab_size, (3, 384), device=DEV)
+    ref_eng = InferenceEngine(m)
+    ref = ref_eng.prefill(ids, 400).float()
+    ref_next = ref_eng.decode_step(ref.argmax(-1)).float()
+    for seq_chunk, token_chunk in ((2, None), (None, 128), (1, 192)):
+        eng = InferenceEngine(m)
+        got = eng.prefill(ids, 400, seq_chunk=seq_chunk, token_chunk=token_chunk).float()
+        assert (got - ref).abs().max() < 0.05, (seq_chunk, token_chunk)
+        nxt = eng.decode_step(ref.argmax(-1)).float()
+        assert (nxt - ref_next).abs().max() < 0.08, (seq_chunk, token_chunk)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
