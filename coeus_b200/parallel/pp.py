@@ -54,6 +54,37 @@ def schedule_1f1b(stage: int, stages: int, micro_batches: int) -> List[Tuple[str
     return steps
 
 
+def schedule_interleaved(stage: int, stages: int, micro_batches: int, chunks: int
+                         ) -> List[Tuple[str, int, int]]:
+    """Interleaved 1F1B: every rank holds ``chunks`` model chunks (chunk ``c`` of rank ``s`` is
+    virtual stage ``c * stages + s``), which shortens the pipeline bubble by the factor ``chunks``.
+    Returns ``("F" | "B", chunk, micro_batch)`` steps.  Forward units advance in groups of
+    ``stages`` micro-batches through chunk 0, 1, ...; backward units through the chunks in
+    reverse; ``micro_batches`` must be a multiple of ``stages``."""
+    P, M, v = stages, micro_batches, chunks
+    if M % P:
+        raise ProcessingError.invalid_input(
+            "the interleaved schedule needs micro_batches to be a multiple of the stage count")
+    total = M * v
+
+    def unit(n: int, backward: bool) -> Tuple[int, int]:
+        c = (n // P) % v
+        return (v - 1 - c if backward else c), (n // (P * v)) * P + n % P
+
+    warm = min((P - stage - 1) * 2 + (v - 1) * P, total)
+    steps: List[Tuple[str, int, int]] = [("F",) + unit(n, False) for n in range(warm)]
+    f, b = warm, 0
+    while f < total:
+        steps.append(("F",) + unit(f, False))
+        steps.append(("B",) + unit(b, True))
+        f += 1
+        b += 1
+    while b < total:
+        steps.append(("B",) + unit(b, True))
+        b += 1
+    return steps
+
+
 class _Channel:
     """One direction between two neighbouring stages: posts receives ahead and keeps sends alive."""
 
@@ -191,5 +222,138 @@ class PipelineStage:
             c.drain()
         m._ws_tag = ""
         self.opt.step(m.p32, m.g32, m.p16, 1.0)
+        self.step_index += 1
+        return loss_sum
+
+
+class InterleavedPipelineStage:
+    """One rank of a pipeline whose ranks each hold ``chunks`` non-adjacent groups of blocks
+    (virtual stages), run in the interleaved 1F1B order of :func:`schedule_interleaved`.
+
+    Activations travel round the ring of ranks: from rank ``s`` to ``s + 1`` inside one chunk and
+    from the last rank back to the first between chunks; gradients go the other way.  The four
+    kinds of transfer (forward / backward, inside a chunk / between chunks) use four process
+    groups, so each is a first-in-first-out stream whose order is the same on its two ends (both
+    follow the order of the schedule's units) and a transfer of one kind never queues behind one
+    of another kind.  On GPUs receives are posted when needed (see ``_Channel``)."""
+
+    def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, chunks: int = 2,
+                 seed: int = 0, dtype: torch.dtype = torch.bfloat16, train_cfg=None) -> None:
+        from ..optim.adamw import AdamW
+        from ..train.trainer import TrainConfig
+        self.group = group
+        self.stage = dist.get_rank(group)
+        self.stages = dist.get_world_size(group)
+        if self.stages < 2 or chunks < 2:
+            raise ProcessingError.invalid_input(
+                "the interleaved pipeline needs at least two ranks and two chunks per rank")
+        self.M, self.v, self.cfg = micro_batches, chunks, cfg
+        self.device = torch.device(device)
+        P, V = self.stages, self.stages * chunks
+        spans = split_layers(cfg.num_layers, V)
+        self.models: List[DecoderLM] = []
+        self.opts = []
+        self.train_cfg = train_cfg or TrainConfig()
+        for c in range(chunks):
+            k = c * P + self.stage
+            m = DecoderLM(cfg, self.device, seed=seed, dtype=dtype, layers=spans[k],
+                          embed=(k == 0), head=(k == V - 1))
+            self.models.append(m)
+            self.opts.append(AdamW(self.train_cfg.adamw(), 0, m.n_flat, m.layout.decay_end,
+                                   self.device))
+        ranks = dist.get_process_group_ranks(group)
+        self._ranks = ranks
+        self._groups = {k: dist.new_group(ranks) for k in ("f", "fw", "b", "bw")}
+        self.steps = schedule_interleaved(self.stage, P, micro_batches, chunks)
+        # workspace slots: micro-batches of one chunk that are alive together never share one
+        self._slot: Dict[Tuple[int, int], int] = {}
+        free = [list() for _ in range(chunks)]
+        used = [0] * chunks
+        for kind, c, i in self.steps:
+            if kind == "F":
+                if free[c]:
+                    self._slot[(c, i)] = free[c].pop()
+                else:
+                    self._slot[(c, i)] = used[c]
+                    used[c] += 1
+            else:
+                free[c].append(self._slot[(c, i)])
+        self.step_index = 0
+
+    def load_from_full(self, full: DecoderLM) -> None:
+        for m in self.models:
+            for name, t in m.master.items():
+                t.copy_(full.master[name])
+            m.sync_working_copy()
+
+    def _virtual(self, c: int) -> int:
+        return c * self.stages + self.stage
+
+    def train_step(self, ids: Optional[torch.Tensor], targets: Optional[torch.Tensor]) -> torch.Tensor:
+        """One optimizer step over ``M`` micro-batches; ``ids [M, b, S]`` is read on the first
+        rank, ``targets`` on the last.  Returns the mean loss on the last rank."""
+        P, v, M, s = self.stages, self.v, self.M, self.stage
+        V = P * v
+        ref = ids if ids is not None else targets
+        b, S = ref.shape[1], ref.shape[2]
+        T, H = b * S, self.cfg.hidden_dim
+        dt = self.models[0].p16.dtype
+        nxt, prv = self._ranks[(s + 1) % P], self._ranks[(s - 1) % P]
+        n_wrap = M * (v - 1)
+
+        def chan(key, peer, count, recv):
+            return _Channel(self._groups[key], peer, (T, H), dt, self.device, count, recv)
+
+        ch: Dict[str, _Channel] = {}
+        if s > 0:                       # inside a chunk: s-1 -> s forward, s -> s-1 backward
+            ch["rf"] = chan("f", prv, M * v, True)
+            ch["sb"] = chan("b", prv, M * v, False)
+        if s < P - 1:
+            ch["sf"] = chan("f", nxt, M * v, False)
+            ch["rb"] = chan("b", nxt, M * v, True)
+        if s == P - 1:                  # between chunks: last -> first forward, first -> last backward
+            ch["sfw"] = chan("fw", nxt, n_wrap, False)
+            ch["rbw"] = chan("bw", nxt, n_wrap, True)
+        if s == 0:
+            ch["rfw"] = chan("fw", prv, n_wrap, True)
+            ch["sbw"] = chan("bw", prv, n_wrap, False)
+        for m in self.models:
+            m.zero_grad()
+        saves: Dict[Tuple[int, int], dict] = {}
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for kind, c, i in self.steps:
+            m, k = self.models[c], self._virtual(c)
+            m._ws_tag = f"mb{self._slot[(c, i)]}:"
+            if kind == "F":
+                save: dict = {"B": b, "S": S}
+                if k == 0:
+                    save["ids"] = ids[i].reshape(-1)
+                    x = m.embed(ids[i], b, S)
+                else:
+                    x = ch["rf" if s > 0 else "rfw"].take()
+                x = m.forward_blocks(x, b, S, save)
+                if k == V - 1:
+                    xf = m.forward_final_norm(x, save)
+                    loss = m.loss_from_hidden(xf, targets[i], save, grad_scale=1.0 / (T * M))
+                    loss_sum += loss / M
+                else:
+                    ch["sf" if s < P - 1 else "sfw"].send(x)
+                saves[(c, i)] = save
+            else:
+                save = saves.pop((c, i))
+                if k == V - 1:
+                    dx = m.backward_head(save)
+                else:
+                    dx = ch["rb" if s < P - 1 else "rbw"].take()
+                dx = m.backward_blocks(dx, save)
+                if k == 0:
+                    E.embed_bwd(save["ids"], dx, m.g["token_embed"])
+                else:
+                    ch["sb" if s > 0 else "sbw"].send(dx)
+        for c_ in ch.values():
+            c_.drain()
+        for m, opt in zip(self.models, self.opts):
+            m._ws_tag = ""
+            opt.step(m.p32, m.g32, m.p16, 1.0)
         self.step_index += 1
         return loss_sum

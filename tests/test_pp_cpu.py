@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from coeus_b200.parallel.pp import schedule_1f1b, split_layers
+from coeus_b200.parallel.pp import schedule_1f1b, schedule_interleaved, split_layers
 
 
 def test_split_layers():
@@ -104,3 +104,99 @@ def test_pipeline_training_matches_single_rank(world):
             assert (torch.from_numpy(got) - full.master[name]).abs().max() < 1e-5, name
             seen.add(name)
     assert seen == set(full.master)     # every tensor lives on exactly the stages that need it
+
+
+@pytest.mark.parametrize("P,M,v", [(2, 2, 2), (2, 4, 2), (4, 8, 2), (3, 6, 3), (4, 4, 4)])
+def test_interleaved_schedule_runs_without_deadlock_and_in_fifo_order(P, M, v):
+    """All ranks' step lists executed against first-in-first-out channels: every unit finds its
+    input at the head of its channel (the order of sends equals the order of receives) and the
+    whole step finishes (no rank waits for a message that is never sent)."""
+    V = P * v
+    steps = [schedule_interleaved(s, P, M, v) for s in range(P)]
+    for s in range(P):
+        fs = [(c, i) for k, c, i in steps[s] if k == "F"]
+        bs = [(c, i) for k, c, i in steps[s] if k == "B"]
+        assert sorted(fs) == sorted(bs) == [(c, i) for c in range(v) for i in range(M)]
+    chans = {}                      # (kind, src, dst) -> list of (virtual stage of consumer, mb)
+    pc = [0] * P
+    done_f, done_b = set(), set()
+    progress = True
+    while progress:
+        progress = False
+        for s in range(P):
+            while pc[s] < len(steps[s]):
+                kind, c, i = steps[s][pc[s]]
+                k = c * P + s
+                if kind == "F":
+                    if k > 0:
+                        q = chans.get(("f", (s - 1) % P, s), [])
+                        if not q:
+                            break
+                        assert q.pop(0) == (k, i)
+                    if k < V - 1:
+                        chans.setdefault(("f", s, (s + 1) % P), []).append((k + 1, i))
+                    done_f.add((k, i))
+                else:
+                    assert (k, i) in done_f
+                    if k < V - 1:
+                        q = chans.get(("b", (s + 1) % P, s), [])
+                        if not q:
+                            break
+                        assert q.pop(0) == (k, i)
+                    if k > 0:
+                        chans.setdefault(("b", s, (s - 1) % P), []).append((k - 1, i))
+                    done_b.add((k, i))
+                pc[s] += 1
+                progress = True
+    assert all(pc[s] == len(steps[s]) for s in range(P)), "deadlock"
+    assert len(done_b) == V * M
+
+
+def _worker_interleaved(rank, world, port, ids, tgt, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.parallel.pp import InterleavedPipelineStage
+    cfg = _cfg()
+    cfg.num_layers = 5
+    st = InterleavedPipelineStage(cfg, dist.group.WORLD, "cpu", micro_batches=ids.shape[0],
+                                  chunks=2, seed=4, dtype=torch.float32, train_cfg=_train_cfg())
+    losses = [float(st.train_step(ids, tgt)) for _ in range(2)]
+    params = {}
+    for m in st.models:
+        params.update({k: v.numpy().copy() for k, v in m.master.items()})
+    out.put((rank, losses, params))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_interleaved_pipeline_training_matches_single_rank():
+    from mp_util import run_ranks
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.optim.adamw import AdamW
+    torch.manual_seed(0)
+    M, b, S, world = 4, 2, 16, 2
+    ids = torch.randint(0, 96, (M, b, S))
+    tgt = torch.randint(0, 96, (M, b, S))
+    cfg = _cfg()
+    cfg.num_layers = 5
+    full = DecoderLM(cfg, "cpu", seed=4, dtype=torch.float32)
+    opt = AdamW(_train_cfg().adamw(), 0, full.n_flat, full.layout.decay_end, "cpu")
+    ref_losses = []
+    for _ in range(2):
+        full.zero_grad()
+        tot = 0.0
+        for i in range(M):
+            tot += float(full.forward_loss(ids[i], tgt[i], grad_scale=1.0 / (b * S * M))) / M
+            full.backward()
+        opt.step(full.p32, full.g32, full.p16, 1.0)
+        ref_losses.append(tot)
+    res = {r[0]: r for r in run_ranks(_worker_interleaved, world, (ids, tgt), results=world)}
+    for step in range(2):
+        assert abs(res[world - 1][1][step] - ref_losses[step]) < 1e-5
+    seen = set()
+    for rank in range(world):
+        for name, got in res[rank][2].items():
+            assert (torch.from_numpy(got) - full.master[name]).abs().max() < 1e-5, name
+            seen.add(name)
+    assert seen == set(full.master)
