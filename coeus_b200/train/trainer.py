@@ -14,6 +14,7 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
+from ..foundation.error import ProcessingError
 from ..models.decoder import DecoderLM
 from ..optim.adamw import AdamW, AdamWConfig
 
@@ -111,6 +112,42 @@ class Trainer:
     # ---- Checkpoint trait (src/core/traits.rs:181-189)
     def state_dict(self) -> Dict[str, object]:
         return {"p32": self.model.p32, "opt": self.opt.state_dict(), "step": self.step_index}
+
+    def checkpoint(self) -> bytes:
+        """Single-replica training state as one byte string: a JSON header line, then the fp32
+        master weights and the two Adam moments (``Checkpoint::checkpoint``,
+        src/core/traits.rs:181-189).  Sharded runs use :meth:`save_checkpoint`."""
+        import json
+        if self.dp is not None:
+            raise ProcessingError.unsupported(
+                "Trainer.checkpoint() under data parallelism", "use save_checkpoint(directory)")
+        m = self.model
+        head = {"n_flat": m.n_flat, "opt_step": self.opt.step_count, "train_step": self.step_index,
+                "micro": self._micro, "config": m.cfg.to_dict()}
+        parts = [json.dumps(head).encode() + b"\n"]
+        for t in (m.p32, self.opt.m, self.opt.v):
+            parts.append(t.detach().cpu().numpy().tobytes())
+        return b"".join(parts)
+
+    def restore(self, checkpoint: bytes) -> None:
+        """Inverse of :meth:`checkpoint` (``Checkpoint::restore``)."""
+        import json
+
+        import numpy as np
+        m = self.model
+        nl = checkpoint.index(b"\n")
+        head = json.loads(checkpoint[:nl].decode())
+        n = int(head["n_flat"])
+        if n != m.n_flat or len(checkpoint) != nl + 1 + 12 * n:
+            raise ProcessingError.invalid_input(
+                f"checkpoint holds {n} parameters, the model {m.n_flat}")
+        body = np.frombuffer(checkpoint, dtype=np.float32, count=3 * n, offset=nl + 1)
+        for j, t in enumerate((m.p32, self.opt.m, self.opt.v)):
+            t.copy_(torch.from_numpy(body[j * n:(j + 1) * n].copy()))
+        m.sync_working_copy()
+        self.opt.step_count = int(head["opt_step"])
+        self.step_index = int(head["train_step"])
+        self._micro = int(head.get("micro", 0))
 
     # ---- sharded checkpoints (resume on any number of ranks)
     def _owned_segments(self):

@@ -257,3 +257,25 @@ def test_philox_model_init_is_shard_invariant():
         assert torch.equal(t, whole.master[name]), name
     w = whole.master["layers.0.attn.qkv_weights"]
     assert abs(float(w.std()) - cfg.init_std) < 0.1 * cfg.init_std
+
+
+def test_trainer_checkpoint_bytes_round_trip():
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.train.trainer import TrainConfig, Trainer
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (2, 16))
+    tgt = torch.randint(0, 64, (2, 16))
+    a = Trainer(DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32), TrainConfig(learning_rate=1e-2))
+    a.train_step(ids, tgt)
+    blob = a.checkpoint()
+    b = Trainer(DecoderLM(cfg, "cpu", seed=9, dtype=torch.float32), TrainConfig(learning_rate=1e-2))
+    b.restore(blob)
+    assert b.step_index == 1 and torch.equal(a.model.p32, b.model.p32)
+    la, lb = a.train_step(ids, tgt), b.train_step(ids, tgt)
+    assert float(la) == float(lb) and torch.equal(a.model.p32, b.model.p32)
+    with pytest.raises(Exception):
+        b.restore(blob[:-4])
