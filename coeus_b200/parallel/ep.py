@@ -108,8 +108,8 @@ class ExpertParallel:
         """Generic two-GEMM expert pass over exchanged rows.
 
         ``first(j, xg, fused_ag)`` must return the ``[ep*C, K2]`` input of the second GEMM given
-        the gathered rows ``xg`` of local expert ``j`` (``fused_ag(w, b_mn)`` performs the GEMM
-        that pulls the rows when the fused backend is active, else ``None``);
+        the gathered rows ``xg`` of local expert ``j`` (``fused_ag(w, b_mn, out)`` performs the
+        GEMM that pulls the rows from the peers);
         ``second(j, a2)`` returns ``(w2, b_mn)`` for the GEMM whose result rows go back."""
         ep, r = self.ep, self.rank
         send, ret = b["send"], b["ret"]
@@ -236,12 +236,9 @@ class MoEFFN:
         M.gather_rows(x, expert, slot, b["send"], C)
         kept = {}
 
-        def first(j, xg, fused_ag):
-            if fused_ag is not None:
-                gu = torch.empty((xg.shape[0], 2 * self.I), dtype=xg.dtype, device=xg.device)
-                fused_ag(self.w["gate_up"][j], True, gu)
-            else:
-                gu = G.gemm(xg, self.w["gate_up"][j], b_mn=True)
+        def first(j, xg, fused_ag):     # fused transport: the GEMM pulls the rows of expert j
+            gu = torch.empty((xg.shape[0], 2 * self.I), dtype=xg.dtype, device=xg.device)
+            fused_ag(self.w["gate_up"][j], True, gu)
             act = E.swiglu_fwd(gu)
             kept[j] = (xg, gu, act)
             return act
@@ -284,11 +281,8 @@ class MoEFFN:
 
         def first(j, dyg, fused_ag):
             xg, gu, act = kept[j]
-            if fused_ag is not None:
-                dact = torch.empty((dyg.shape[0], self.I), dtype=dyg.dtype, device=dyg.device)
-                fused_ag(self.w["down"][j], False, dact)
-            else:
-                dact = G.gemm(dyg, self.w["down"][j], b_mn=False)
+            dact = torch.empty((dyg.shape[0], self.I), dtype=dyg.dtype, device=dyg.device)
+            fused_ag(self.w["down"][j], False, dact)
             G.linear_wgrad(act, dyg, self.g["down"][j])
             dgu = E.swiglu_bwd(gu, dact)
             G.linear_wgrad(xg, dgu, self.g["gate_up"][j])

@@ -262,3 +262,34 @@ def test_grouped_gemm_matches_per_group_reference(Gn, M, N, K):
     assert (gw - ref).abs().max() <= 0.01 * ref.abs().max()
     torch.cuda.synchronize()
     _lib.check_status(torch.device("cuda", 0))
+
+
+def test_kernels_without_atomics_are_bitwise_repeatable():
+    """A cheap race detector: kernels whose reduction order is fixed must give the same bits on
+    every run (GEMM without split-K, grouped GEMM, attention forward, norm forward, cross-entropy,
+    AdamW)."""
+    torch.manual_seed(3)
+    x = torch.randn(1000, 512, device="cuda").bfloat16()
+    w = torch.randn(512, 768, device="cuda").bfloat16()
+    xg = torch.randn(4, 256, 128, device="cuda").bfloat16()
+    wg = torch.randn(4, 128, 320, device="cuda").bfloat16()
+    qkv = torch.randn(2 * 300, 3 * 256, device="cuda").bfloat16()
+    scale = torch.randn(512, device="cuda").bfloat16()
+    logits = torch.randn(333, 1000, device="cuda").bfloat16()
+    tgt = torch.randint(0, 1000, (333,), device="cuda")
+
+    def run():
+        y = G.linear_fwd(x, w, epi="gelu")
+        yg = G.gemm_grouped(xg, wg, b_mn=True)
+        o, lse = A.attention_fwd(qkv[:, :256], qkv[:, 256:512], qkv[:, 512:], 2, 300, 4, 64)
+        n, mean, rstd = N.norm_fwd(x, scale, None, 1e-5, True)
+        lg = logits.clone()
+        loss = E.cross_entropy_fwd_bwd(lg, tgt, 1.0 / 333, vocab=1000)
+        return [y, yg, o, lse, n, rstd, lg, loss]
+
+    first = run()
+    for _ in range(5):
+        for a, b in zip(first, run()):
+            assert torch.equal(a, b)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
