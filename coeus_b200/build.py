@@ -98,7 +98,8 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
 def build_host(force: bool = False) -> Path:
     LIB.mkdir(exist_ok=True)
     out = host_lib_path()
-    srcs = sorted(HOST.glob("*.cpp"))
+    # selftest.cpp is a stand-alone program (sanitizer builds), not part of the module
+    srcs = sorted(p for p in HOST.glob("*.cpp") if p.name != "selftest.cpp")
     hdrs = sorted(HOST.glob("*.hpp"))
     if not srcs:
         return out
