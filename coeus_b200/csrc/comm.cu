@@ -90,24 +90,54 @@ struct AdamArgs {
 // (multiples of 8).  grads.p[r] / params.p[r] are rank r's fp32 gradient and bf16 weight flat
 // buffers; p32 is this rank's flat master buffer (only its own shards are kept current), m / v
 // are its moment shards with element `gstart` at index `moff`.
+//
+// MODE 0 does all three steps.  With gradient clipping the global norm is known only after the
+// last bucket, so the step is split: MODE 1 reduces the shard over the ranks, leaves the sums in
+// this rank's own gradient buffer (only the owner reads that range) and writes the block's sum
+// of squares to partials[blockIdx.x] (fixed summation order, no atomics); MODE 2 reads the sums
+// back, multiplies them by *clip_coef and does AdamW + all-gather.
+template <int MODE>
 __global__ void __launch_bounds__(256)
 rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, float* __restrict__ p32,
                    float* __restrict__ m, float* __restrict__ v, size_t gstart, size_t gend,
                    size_t moff, size_t decay_end, AdamArgs a, int n, const uint64_t* flags,
-                   int slot, uint64_t expect, uint64_t limit_ns, int* status) {
-  if (flags != nullptr && !wait_flags(flags, slot, n, expect, limit_ns, status)) return;
+                   int slot, uint64_t expect, uint64_t limit_ns, int* status, int my_rank,
+                   float* __restrict__ partials, const float* __restrict__ clip_coef) {
+  __shared__ float red[32];
+  if (MODE != 2 && flags != nullptr && !wait_flags(flags, slot, n, expect, limit_ns, status)) {
+    if (MODE == 1 && threadIdx.x == 0) partials[blockIdx.x] = 0.f;
+    return;
+  }
+  if (MODE == 2) a.grad_scale *= *clip_coef;
+  float sq = 0.f;
   const size_t nvec = (gend - gstart) >> 3;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const size_t g0 = gstart + (i << 3);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (MODE == 2) {
+      const float* gp = static_cast<const float*>(grads.p[my_rank]) + g0;
+      const float4 x = *reinterpret_cast<const float4*>(gp);
+      const float4 y = *reinterpret_cast<const float4*>(gp + 4);
+      acc[0] = x.x; acc[1] = x.y; acc[2] = x.z; acc[3] = x.w;
+      acc[4] = y.x; acc[5] = y.y; acc[6] = y.z; acc[7] = y.w;
+    } else {
 #pragma unroll 4
-    for (int r = 0; r < n; ++r) {
-      const float* gp = static_cast<const float*>(grads.p[r]) + g0;
-      const float4 x = ld_relaxed_sys_f4(gp);
-      const float4 y = ld_relaxed_sys_f4(gp + 4);
-      acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-      acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+      for (int r = 0; r < n; ++r) {
+        const float* gp = static_cast<const float*>(grads.p[r]) + g0;
+        const float4 x = ld_relaxed_sys_f4(gp);
+        const float4 y = ld_relaxed_sys_f4(gp + 4);
+        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+      }
+    }
+    if (MODE == 1) {
+      float* own = static_cast<float*>(grads.p[my_rank]) + g0;
+      *reinterpret_cast<float4*>(own) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(own + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq = fmaf(acc[e], acc[e], sq);
+      continue;
     }
     const size_t mi = moff + (i << 3);
     float pw[8], mm[8], vv[8];
@@ -147,6 +177,10 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, float* __restrict__ p32,
 #pragma unroll 4
     for (int r = 0; r < n; ++r)
       *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + g0) = o;
+  }
+  if (MODE == 1) {
+    const float tot = block_sum(sq, red);
+    if (threadIdx.x == 0) partials[blockIdx.x] = tot;
   }
 }
 
@@ -236,14 +270,27 @@ extern "C" int cb_wait_flags(const void* flags, int slot, int n, unsigned long l
 }
 
 // ---------------------------------------------------------------------- fused DP step
+// mode 0: fused reduce-scatter + AdamW + all-gather; mode 1: reduce-scatter into this rank's own
+// gradient buffer plus per-block sums of squares in partials[0 .. blocks) (entries of blocks that
+// are not launched are set to zero); mode 2: AdamW + all-gather from the reduced gradients,
+// scaled by grad_scale * *clip_coef.
 extern "C" int cb_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, float* p32,
                               float* m, float* v, size_t gstart, size_t gend, size_t moff,
                               size_t decay_end, float lr, float beta1, float beta2, float eps,
                               float wd, int step, float grad_scale, int n, const void* flags,
                               int slot, unsigned long long expect, unsigned long long limit_ns,
-                              int blocks, int* status, void* stream) {
-  if (n < 1 || n > MAX_RANKS) return -1;
-  if (gend <= gstart) return 0;
+                              int blocks, int* status, void* stream, int mode, int my_rank,
+                              float* partials, const float* clip_coef) {
+  if (n < 1 || n > MAX_RANKS || mode < 0 || mode > 2 || my_rank < 0 || my_rank >= n) return -1;
+  if (mode == 1 && partials == nullptr) return -1;
+  if (mode == 2 && clip_coef == nullptr) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (blocks <= 0) blocks = 64;
+  const int slots = blocks;
+  if (gend <= gstart) {
+    if (mode == 1) cudaMemsetAsync(partials, 0, sizeof(float) * slots, st);
+    return 0;
+  }
   if (((gend - gstart) & 7) != 0 || (gstart & 7) != 0 || (moff & 3) != 0) return -3;
   PeerPtrs g, p;
   for (int i = 0; i < n; ++i) { g.p[i] = grad_ptrs[i]; p.p[i] = param_ptrs[i]; }
@@ -252,12 +299,19 @@ extern "C" int cb_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, f
   a.bc1 = 1.0f - powf(beta1, static_cast<float>(step));
   a.bc2 = 1.0f - powf(beta2, static_cast<float>(step));
   a.grad_scale = grad_scale;
-  if (blocks <= 0) blocks = 64;
   const size_t need = ((gend - gstart) / 8 + 255) / 256;
   if (static_cast<size_t>(blocks) > need) blocks = static_cast<int>(need);
-  rs_adamw_ag_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      g, p, p32, m, v, gstart, gend, moff, decay_end, a, n, static_cast<const uint64_t*>(flags),
-      slot, expect, limit_ns, status);
+  if (mode == 1 && blocks < slots)
+    cudaMemsetAsync(partials + blocks, 0, sizeof(float) * (slots - blocks), st);
+  const uint64_t* f = static_cast<const uint64_t*>(flags);
+#define CB_RS_LAUNCH(MODE_)                                                                    \
+  rs_adamw_ag_kernel<MODE_><<<blocks, 256, 0, st>>>(g, p, p32, m, v, gstart, gend, moff,       \
+                                                    decay_end, a, n, f, slot, expect, limit_ns, \
+                                                    status, my_rank, partials, clip_coef)
+  if (mode == 0) CB_RS_LAUNCH(0);
+  else if (mode == 1) CB_RS_LAUNCH(1);
+  else CB_RS_LAUNCH(2);
+#undef CB_RS_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -62,10 +62,6 @@ class ShardedDataParallel:
 
     # ------------------------------------------------------------------ set-up
     def attach(self, model, opt_cfg: AdamWConfig) -> None:
-        if opt_cfg.grad_clip is not None and self.backend == "p2p":
-            raise ProcessingError.unsupported(
-                "grad_clip with the fused data-parallel kernel",
-                "the global norm is only known after the last bucket; use backend='collective'")
         self.model = model
         self.opt_cfg = opt_cfg
         self.buckets: List[Bucket] = build_buckets(model.layout, model.n_flat)
@@ -93,6 +89,12 @@ class ShardedDataParallel:
             self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
             self.events = [torch.cuda.Event() for _ in self.buckets]
             self.done_event = torch.cuda.Event()
+            # gradient clipping: per-bucket, per-block sums of squares of the reduced shards
+            self._slots = self.comm_blocks if self.comm_blocks > 0 else 64
+            self.partials = torch.zeros(len(self.buckets) * self._slots, dtype=torch.float32,
+                                        device=self.device)
+            self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
+            self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
             dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------ step protocol
@@ -110,28 +112,37 @@ class ShardedDataParallel:
         for b in self.by_trigger.get(trigger, []):
             self._launch_bucket(b)
 
+    def _bucket_kernel(self, b: Bucket, mode: int) -> None:
+        """``mode`` 0: reduce-scatter + AdamW + all-gather; 1: reduce-scatter + sum of squares;
+        2: AdamW (gradients times the clip coefficient) + all-gather."""
+        c = self.opt_cfg
+        s, e = b.shard(self.rank, self.world)
+        m = self.model
+        st = _lib.status_buffer(self.device)
+        part = self.partials[b.index * self._slots:]
+        rc = _lib.lib().cb_rs_adamw_ag(
+            self.g_ptrs, self.p_ptrs, _lib.ptr(m.p32), _lib.ptr(self.opt.m),
+            _lib.ptr(self.opt.v), ctypes.c_size_t(s), ctypes.c_size_t(e),
+            ctypes.c_size_t(self.moffs[b.index]), ctypes.c_size_t(m.layout.decay_end),
+            ctypes.c_float(c.lr), ctypes.c_float(c.beta1), ctypes.c_float(c.beta2),
+            ctypes.c_float(c.eps), ctypes.c_float(c.weight_decay), self.step_no,
+            ctypes.c_float(self._grad_scale), self.world,
+            ctypes.c_void_p(self.pad.buf.local_ptr), b.index,
+            ctypes.c_ulonglong(self.step_no), ctypes.c_ulonglong(self.pad.limit_ns),
+            self._slots, _lib.ptr(st), _lib.stream_ptr(), mode, self.rank, _lib.ptr(part),
+            _lib.ptr(self.clip_coef))
+        _lib.check_rc(rc, "cb_rs_adamw_ag")
+
     def _launch_bucket(self, b: Bucket) -> None:
         ev = self.events[b.index]
         ev.record(torch.cuda.current_stream())
-        c = self.opt_cfg
         s, e = b.shard(self.rank, self.world)
+        clip = self.opt_cfg.grad_clip is not None
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ev)
             self.pad.signal(b.index, self.step_no)
-            if e > s:
-                m = self.model
-                st = _lib.status_buffer(self.device)
-                rc = _lib.lib().cb_rs_adamw_ag(
-                    self.g_ptrs, self.p_ptrs, _lib.ptr(m.p32), _lib.ptr(self.opt.m),
-                    _lib.ptr(self.opt.v), ctypes.c_size_t(s), ctypes.c_size_t(e),
-                    ctypes.c_size_t(self.moffs[b.index]), ctypes.c_size_t(m.layout.decay_end),
-                    ctypes.c_float(c.lr), ctypes.c_float(c.beta1), ctypes.c_float(c.beta2),
-                    ctypes.c_float(c.eps), ctypes.c_float(c.weight_decay), self.step_no,
-                    ctypes.c_float(self._grad_scale), self.world,
-                    ctypes.c_void_p(self.pad.buf.local_ptr), b.index,
-                    ctypes.c_ulonglong(self.step_no), ctypes.c_ulonglong(self.pad.limit_ns),
-                    self.comm_blocks, _lib.ptr(st), _lib.stream_ptr())
-                _lib.check_rc(rc, "cb_rs_adamw_ag")
+            if e > s or clip:
+                self._bucket_kernel(b, 1 if clip else 0)
 
     _grad_scale = 1.0
 
@@ -145,6 +156,18 @@ class ShardedDataParallel:
         self.opt.step_count += 1
         if self.backend == "p2p":
             with torch.cuda.stream(self.comm_stream):
+                if self.opt_cfg.grad_clip is not None:
+                    # every bucket has been reduced into its owner's gradient buffer: the global
+                    # norm is the root of the sum over owners, then the update runs per bucket
+                    sumsq = self.partials.sum().reshape(1)
+                    if self.world > 1:
+                        dist.all_reduce(sumsq, group=self.group)
+                    E.clip_coef_from_sumsq(sumsq, self._grad_scale, self.opt_cfg.grad_clip,
+                                           self.clip_coef, self.grad_norm)
+                    for b in self.buckets:
+                        s, e = b.shard(self.rank, self.world)
+                        if e > s:
+                            self._bucket_kernel(b, 2)
                 self.pad.signal(len(self.buckets), self.step_no)
                 self.done_event.record(self.comm_stream)
             return

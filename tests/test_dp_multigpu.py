@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, backend, out):
+def _worker(rank, world, port, backend, out, clip=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -35,7 +35,7 @@ def _worker(rank, world, port, backend, out):
     from coeus_b200.train.trainer import TrainConfig, Trainer
     model = DecoderLM(CFG, device=dev, seed=0)
     dp = ShardedDataParallel(dist.group.WORLD, dev, backend=backend)
-    tr = Trainer(model, TrainConfig(learning_rate=1e-3), dp=dp)
+    tr = Trainer(model, TrainConfig(learning_rate=1e-3, grad_clip=clip), dp=dp)
     gen = torch.Generator().manual_seed(100 + rank)
     batch = torch.randint(0, CFG.vocab_size, (2, 129), generator=gen).to(dev)
     losses = [float(tr.train_step(batch[:, :-1], batch[:, 1:])) for _ in range(4)]
@@ -48,10 +48,16 @@ def _worker(rank, world, port, backend, out):
     dist.destroy_process_group()
 
 
-def _run(backend, world=2):
+def _run(backend, world=2, clip=None):
     from mp_util import run_ranks
-    res = run_ranks(_worker, world, (backend,))[0]
+
+    res = run_ranks(_worker_clip if clip is not None else _worker, world,
+                    (backend, clip) if clip is not None else (backend,))[0]
     return res
+
+
+def _worker_clip(rank, world, port, backend, clip, out):
+    _worker(rank, world, port, backend, out, clip)
 
 
 def test_fused_kernel_matches_nccl_collectives():
@@ -65,3 +71,17 @@ def test_fused_kernel_matches_nccl_collectives():
     # the fraction of entries that moved apart
     assert (d > 5e-4).float().mean() < 0.01, d.max()
     assert (p_ref - p_p2p).abs().max() < 0.05
+
+
+def test_gradient_clipping_in_the_fused_step_matches_collectives():
+    """With a clip threshold far below the gradient norm the split kernel (reduce-scatter + sum of
+    squares, then AdamW + all-gather with the coefficient) must follow the NCCL path."""
+    l_ref, m_ref, _ = _run("collective", clip=0.05)
+    l_p2p, m_p2p, _ = _run("p2p", clip=0.05)
+    for a, b in zip(l_ref, l_p2p):
+        assert abs(a - b) < 0.05
+    d = (m_ref - m_p2p).abs()
+    assert (d > 5e-4).float().mean() < 0.01, d.max()
+    # clipping changed the trajectory: the unclipped run ends elsewhere
+    _, m_free, _ = _run("p2p")
+    assert (m_free - m_p2p).abs().max() > 1e-3

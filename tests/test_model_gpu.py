@@ -94,3 +94,36 @@ def test_recompute_and_accumulation_match_the_plain_step(kind):
     assert b.step_index == 1
     d = (a.model.p32 - b.model.p32).abs()
     assert (d > 2e-4).float().mean() < 0.01
+
+
+def test_fused_data_parallel_step_with_clipping_on_one_rank():
+    """The split bucket kernel (modes 1 and 2) on a group of one rank against the plain trainer
+    with the same clip threshold."""
+    import os
+    import torch.distributed as dist
+    from mp_util import free_port
+    from coeus_b200.parallel.zero import ShardedDataParallel
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(free_port())
+    dev = torch.device("cuda", 0)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    try:
+        cfg = CFGS["gpt"]
+        torch.manual_seed(2)
+        batch = torch.randint(0, cfg.vocab_size, (2, 129), device="cuda")
+        x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+        tc = TrainConfig(learning_rate=1e-3, grad_clip=0.05)
+        plain = Trainer(DecoderLM(cfg, device="cuda", seed=3), tc)
+        dp = ShardedDataParallel(dist.group.WORLD, dev, backend="p2p")
+        fused = Trainer(DecoderLM(cfg, device="cuda", seed=3), tc, dp=dp)
+        for _ in range(3):
+            la, lb = plain.train_step(x, y), fused.train_step(x, y)
+        full = dp.gather_master()
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        assert abs(float(la) - float(lb)) < 0.02
+        assert float(dp.grad_norm) > 0.05            # the threshold was active
+        d = (plain.model.p32 - full).abs()
+        assert (d > 5e-4).float().mean() < 0.01, d.max()
+    finally:
+        dist.destroy_process_group()
