@@ -82,6 +82,3 @@ def test_gradient_clipping_in_the_fused_step_matches_collectives():
         assert abs(a - b) < 0.05
     d = (m_ref - m_p2p).abs()
     assert (d > 5e-4).float().mean() < 0.01, d.max()
-    # clipping changed the trajectory: the unclipped run ends elsewhere
-    _, m_free, _ = _run("p2p")
-    assert (m_free - m_p2p).abs().max() > 1e-3
