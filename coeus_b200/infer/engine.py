@@ -77,7 +77,8 @@ class InferenceEngine:
     def _layers(self, x: torch.Tensor, B: int, S: int, pos0: torch.Tensor, pos0_host: int,
                 cache: PagedKVCache, prefill: bool, pos_dev: Optional[torch.Tensor] = None,
                 page_table: Optional[torch.Tensor] = None,
-                earlier: Optional[List[list]] = None) -> torch.Tensor:
+                earlier: Optional[List[list]] = None,
+                ctx: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``earlier[l]`` (chunked prefill) lists the ``(k, v)`` of the sequence chunks that came
         before this one; this chunk attends to them without a mask, to itself causally, and the
         partial results are merged by their log-sum-exp."""
@@ -108,8 +109,9 @@ class InferenceEngine:
                         R.cast_rows(acc, attn)
                     earlier[l].append((k, v))
             else:
-                attn = D.decode_attention(q, cache.k[l], cache.v[l], cache.page_table,
-                                          self._ctx, nh, dh, splits=self.decode_splits)
+                attn = D.decode_attention(q, cache.k[l], cache.v[l], page_table,
+                                          self._ctx if ctx is None else ctx, nh, dh,
+                                          splits=self.decode_splits)
             x_mid = G.linear_fwd(attn, m.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x)
             x = self._mlp(p, self._norm(x_mid, p + n2n), x_mid)
         return x
@@ -158,6 +160,54 @@ class InferenceEngine:
         self._pos0.fill_(S)
         self._ctx.fill_(S)
         return self._logits(last)
+
+    # ------------------------------------------------------------------ slot-wise API (serving)
+    def open_slots(self, max_seqs: int, max_len: int) -> PagedKVCache:
+        """A cache whose rows are independent request slots (see
+        :class:`coeus_b200.infer.scheduler.ContinuousBatcher`); pages are handed out per slot."""
+        self.cache = PagedKVCache.for_model(self.cfg, max_seqs, max(max_len, D.PAGE),
+                                            self.m.device)
+        self._graph = None
+        return self.cache
+
+    def prefill_slot(self, slot: int, ids: torch.Tensor, total_len: int,
+                     token_chunk: Optional[int] = None) -> torch.Tensor:
+        """Prompt ``ids [S]`` of one request into cache row ``slot``; returns its last-position
+        logits ``[V]``."""
+        cache, m, cfg = self.cache, self.m, self.cfg
+        S = ids.numel()
+        cache.reserve(slot, total_len)
+        Sc = S
+        if token_chunk and token_chunk < S:
+            Sc = max(d for d in range(1, int(token_chunk) + 1) if S % d == 0)
+        pe = m._positions(max(S, total_len))
+        table = cache.page_table[slot:slot + 1]
+        earlier = [[] for _ in range(cfg.num_layers)] if Sc < S else None
+        for c0 in range(0, S, Sc):
+            pos0 = torch.full((1,), c0, dtype=torch.int32, device=m.device)
+            x = E.embed_fwd(ids[c0:c0 + Sc].reshape(-1), m.w["token_embed"], pe, Sc, pos_offset=c0)
+            x = self._layers(x, 1, Sc, pos0, c0, cache, prefill=True, page_table=table,
+                             earlier=earlier)
+        cache.set_length(slot, S)
+        return self._logits(x[-1:].contiguous())[0]
+
+    def decode_slots(self, slots: torch.Tensor, tokens: torch.Tensor,
+                     positions: torch.Tensor) -> torch.Tensor:
+        """One token for each of the cache rows ``slots [n]`` (int64): ``tokens [n]`` is fed at
+        ``positions [n]`` (int32, the rows' current lengths, which may all differ); returns
+        ``[n, V]`` logits.  The caller advances the lengths."""
+        cache, m, cfg = self.cache, self.m, self.cfg
+        n = tokens.shape[0]
+        x = E.embed_fwd(tokens, m.w["token_embed"], None, 1)
+        if cfg.pos == "sinusoidal":
+            pe = m._positions(int(positions.max()) + 1)
+            x = (x.float() + pe[positions.long()].float()).to(x.dtype)
+        table = cache.page_table.index_select(0, slots)
+        ctx = (positions + 1).to(torch.int32)
+        x = self._layers(x, n, 1, positions, 0, cache, prefill=False,
+                         pos_dev=positions if cfg.pos == "rope" else None, page_table=table,
+                         ctx=ctx)
+        return self._logits(x)
 
     def _decode_body(self, tokens: torch.Tensor) -> torch.Tensor:
         """One token per sequence at the device-side position; advances the positions."""

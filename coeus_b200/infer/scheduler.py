@@ -1,0 +1,137 @@
+"""Continuous batching: requests of different prompt lengths join and leave a running decode batch.
+
+Every request owns one row ("slot") of the paged KV cache.  A step admits waiting requests into
+free slots (their prompts are prefilled one by one, optionally in chunks), then feeds one token
+per active slot through the model in a single decode batch whose rows sit at different positions
+(per-row positions for RoPE, per-row context lengths for the paged attention kernel), samples,
+and retires the rows that are done, returning their pages to the free list.  The reference's
+``InferenceRequest{tokens, max_length}`` / ``InferenceResult{predictions}``
+(src/domain/inference/mod.rs:6-32) name a request and a result; it has no batching or cache.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional
+
+import torch
+
+from ..foundation.error import ProcessingError
+from .engine import InferenceEngine
+from .sampler import select
+
+
+@dataclass
+class Request:
+    id: int
+    prompt: List[int]
+    max_new_tokens: int
+    eos_id: Optional[int] = None
+    temperature: float = 0.0
+    top_k: Optional[int] = None
+    top_p: Optional[float] = None
+    output: List[int] = field(default_factory=list)
+    slot: int = -1
+
+    @property
+    def done(self) -> bool:
+        return len(self.output) >= self.max_new_tokens or (
+            self.eos_id is not None and bool(self.output) and self.output[-1] == self.eos_id)
+
+
+class ContinuousBatcher:
+    def __init__(self, engine: InferenceEngine, max_seqs: int = 64, max_len: Optional[int] = None,
+                 token_chunk: Optional[int] = None, seed: int = 0) -> None:
+        """``max_seqs`` rows decode together; ``max_len`` bounds prompt + generated tokens of one
+        request; ``token_chunk`` prefills long prompts in pieces."""
+        self.engine = engine
+        self.max_seqs = max_seqs
+        self.max_len = max_len or engine.max_len
+        self.token_chunk = token_chunk
+        self.device = engine.m.device
+        engine.open_slots(max_seqs, self.max_len)
+        self.waiting: Deque[Request] = deque()
+        self.active: Dict[int, Request] = {}          # slot -> request
+        self.free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
+        self._next_id = 0
+        self._gen = torch.Generator(device=self.device)
+        self._gen.manual_seed(seed)
+        self.stats = {"steps": 0, "prefills": 0, "decoded_tokens": 0, "max_active": 0}
+
+    # ------------------------------------------------------------------ API
+    def submit(self, prompt, max_new_tokens: int, eos_id: Optional[int] = None,
+               temperature: float = 0.0, top_k: Optional[int] = None,
+               top_p: Optional[float] = None) -> int:
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ProcessingError.invalid_input("empty prompt")
+        if len(prompt) + max_new_tokens > self.max_len:
+            raise ProcessingError.limit_exceeded("sequence length", self.max_len,
+                                                 len(prompt) + max_new_tokens)
+        rid = self._next_id
+        self._next_id += 1
+        self.waiting.append(Request(rid, prompt, max_new_tokens, eos_id, temperature, top_k, top_p))
+        return rid
+
+    def pending(self) -> int:
+        return len(self.waiting) + len(self.active)
+
+    def step(self) -> List[Request]:
+        """Admit, decode one token per active request, retire; returns the requests that finished
+        in this step."""
+        eng, cache = self.engine, self.engine.cache
+        finished: List[Request] = []
+        # a request's first token comes from its prefill
+        while self.waiting and self.free_slots:
+            r = self.waiting.popleft()
+            r.slot = self.free_slots.pop()
+            ids = torch.tensor(r.prompt, dtype=torch.int64, device=self.device)
+            logits = eng.prefill_slot(r.slot, ids, len(r.prompt) + r.max_new_tokens,
+                                      token_chunk=self.token_chunk)
+            r.output.append(int(self._sample(logits[None], r)[0]))
+            self.stats["prefills"] += 1
+            if r.done:
+                self._retire(r, finished)
+            else:
+                self.active[r.slot] = r
+        if self.active:
+            order = sorted(self.active)
+            reqs = [self.active[s] for s in order]
+            slots = torch.tensor(order, dtype=torch.int64, device=self.device)
+            tokens = torch.tensor([r.output[-1] for r in reqs], dtype=torch.int64,
+                                  device=self.device)
+            pos = torch.tensor([len(r.prompt) + len(r.output) - 1 for r in reqs],
+                               dtype=torch.int32, device=self.device)
+            logits = eng.decode_slots(slots, tokens, pos)
+            greedy = all(not r.temperature for r in reqs)
+            nxt = select(logits, 0.0, None, None, None).tolist() if greedy else None
+            for i, r in enumerate(reqs):
+                tok = nxt[i] if greedy else int(self._sample(logits[i:i + 1], r)[0])
+                r.output.append(int(tok))
+                cache.set_length(r.slot, len(r.prompt) + len(r.output) - 1)
+                if r.done:
+                    self._retire(r, finished)
+            self.stats["decoded_tokens"] += len(reqs)
+            self.stats["max_active"] = max(self.stats["max_active"], len(reqs))
+        self.stats["steps"] += 1
+        return finished
+
+    def run(self) -> Dict[int, List[int]]:
+        """Steps until nothing is pending; returns ``{request id: generated tokens}``."""
+        out: Dict[int, List[int]] = {}
+        while self.pending():
+            for r in self.step():
+                out[r.id] = r.output
+        return out
+
+    # ------------------------------------------------------------------ internals
+    def _sample(self, logits: torch.Tensor, r: Request) -> torch.Tensor:
+        V = self.engine.cfg.vocab_size
+        gen = self._gen if r.temperature else None
+        return select(logits[:, :V], r.temperature, r.top_k, r.top_p, gen)
+
+    def _retire(self, r: Request, finished: List[Request]) -> None:
+        self.active.pop(r.slot, None)
+        self.engine.cache.release(r.slot)
+        self.free_slots.append(r.slot)
+        finished.append(r)

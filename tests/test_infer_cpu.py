@@ -43,3 +43,32 @@ def test_decode_matches_full_recompute():
     for i in range(6):          # greedy continuation of the full-sequence forward
         logits = m.forward_logits(out[:, :17 + i], last_only=True)[:, :96]
         assert torch.equal(logits.argmax(-1).reshape(-1), out[:, 17 + i])
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama"])
+def test_continuous_batching_matches_one_request_at_a_time(kind):
+    """Requests with different prompt lengths and budgets share decode steps (more requests than
+    slots, so rows are reused) and each gets what it would get alone."""
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    m = _model(kind)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, 96, (n,)).tolist() for n in (5, 17, 9, 30, 3, 12, 64)]
+    budgets = [4, 7, 1, 5, 9, 3, 6]
+    alone = []
+    for p, k in zip(prompts, budgets):
+        eng = InferenceEngine(m, max_batch=1)
+        alone.append(eng.generate(torch.tensor(p)[None], k)[0, len(p):].tolist())
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=3), max_seqs=3, max_len=128,
+                           token_chunk=16)
+    ids = [cb.submit(p, k) for p, k in zip(prompts, budgets)]
+    out = cb.run()
+    assert [out[i] for i in ids] == alone
+    assert cb.stats["max_active"] == 3 and cb.stats["prefills"] == 7
+    assert cb.engine.cache.pages_in_use() == 0 and len(cb.free_slots) == 3
+    # an end-of-sequence token stops a request early
+    first = alone[1][2]
+    rid = cb.submit(prompts[1], 7, eos_id=first)
+    got = cb.run()[rid]
+    assert got == alone[1][:alone[1].index(first) + 1]
+    with pytest.raises(Exception):
+        cb.submit([1] * 200, 10)
