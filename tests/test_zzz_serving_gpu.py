@@ -20,8 +20,10 @@ def test_continuous_batching_matches_single_requests():
     torch.manual_seed(5)
     prompts = [torch.randint(0, 1000, (n,)).tolist() for n in (7, 130, 33, 64, 200)]
     budgets = [6, 4, 9, 3, 5]
-    cb = ContinuousBatcher(InferenceEngine(m, max_batch=3), max_seqs=3, max_len=256,
-                           token_chunk=64)
+    # one context split in both engines, so that a row is computed by the same arithmetic alone
+    # and in a batch
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=3, decode_splits=1), max_seqs=3,
+                           max_len=256)
     ids = [cb.submit(p, k) for p, k in zip(prompts, budgets)]
     out = cb.run()
     torch.cuda.synchronize()
@@ -29,7 +31,7 @@ def test_continuous_batching_matches_single_requests():
     assert cb.engine.cache.pages_in_use() == 0
     agree = total = 0
     for rid, p, k in zip(ids, prompts, budgets):
-        eng = InferenceEngine(m, max_batch=1, use_graph=False)
+        eng = InferenceEngine(m, max_batch=1, use_graph=False, decode_splits=1)
         alone = eng.generate(torch.tensor(p, device="cuda")[None], k)[0, len(p):].tolist()
         assert len(out[rid]) == k
         # bf16 near-ties may flip an arg-max; the first token of every request must agree and
