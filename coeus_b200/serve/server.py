@@ -1,0 +1,171 @@
+"""A small completion server: one worker thread drives the continuous batcher, HTTP handlers
+hand it requests and wait for their results.
+
+``ServingLoop`` is usable without HTTP (``submit`` returns a ``concurrent.futures.Future``);
+``create_app`` wraps it in a FastAPI application with ``POST /v1/completions``,
+``GET /health`` and ``GET /metrics`` (Prometheus text).  The reference names an
+``InferenceService`` with ``InferenceRequest{tokens, max_length}`` and ``HealthCheck`` /
+``Metrics`` traits (src/domain/inference/mod.rs:6-32, src/core/traits.rs:197-221) and has no
+server; this is the deployment surface those names imply.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from concurrent.futures import Future
+from typing import Dict, List, Optional
+
+from ..foundation.error import ProcessingError
+from ..infer.engine import InferenceEngine
+from ..infer.scheduler import ContinuousBatcher
+
+try:        # the request schema lives at module level so that FastAPI can resolve its annotation
+    from pydantic import BaseModel, Field
+
+    class CompletionRequest(BaseModel):
+        prompt: Optional[str] = None
+        prompt_ids: Optional[List[int]] = None
+        max_tokens: int = Field(16, ge=1)
+        temperature: float = 0.0
+        top_k: Optional[int] = None
+        top_p: Optional[float] = None
+        eos_id: Optional[int] = None
+except ImportError:      # ServingLoop works without the HTTP stack
+    CompletionRequest = None
+
+
+class ServingLoop:
+    """Owns the batcher; all model work happens on its thread."""
+
+    def __init__(self, model, max_seqs: int = 16, max_len: Optional[int] = None,
+                 token_chunk: Optional[int] = None, idle_sleep_s: float = 0.002) -> None:
+        self.engine = InferenceEngine(model, max_batch=max_seqs, use_graph=False)
+        self.batcher = ContinuousBatcher(self.engine, max_seqs=max_seqs, max_len=max_len,
+                                         token_chunk=token_chunk)
+        self._lock = threading.Lock()
+        self._inbox: List[tuple] = []
+        self._futures: Dict[int, Future] = {}
+        self._t0: Dict[int, float] = {}
+        self._stop = threading.Event()
+        self._idle = idle_sleep_s
+        self.counters = {"requests": 0, "completed": 0, "failed": 0, "generated_tokens": 0,
+                         "latency_s_sum": 0.0}
+        self._thread = threading.Thread(target=self._run, name="coeus-serving", daemon=True)
+        self._thread.start()
+
+    def submit(self, prompt: List[int], max_new_tokens: int, **sampling) -> Future:
+        """Thread-safe; the future resolves to the list of generated token ids."""
+        fut: Future = Future()
+        with self._lock:
+            self._inbox.append((prompt, max_new_tokens, sampling, fut, time.perf_counter()))
+            self.counters["requests"] += 1
+        return fut
+
+    def healthy(self) -> bool:
+        return self._thread.is_alive() and not self._stop.is_set()
+
+    def close(self) -> None:
+        self._stop.set()
+        self._thread.join(timeout=30)
+
+    def _run(self) -> None:
+        device = self.engine.m.device
+        if device.type == "cuda":
+            import torch
+            torch.cuda.set_device(device)
+        while not self._stop.is_set():
+            with self._lock:
+                inbox, self._inbox = self._inbox, []
+            for prompt, n, sampling, fut, t0 in inbox:
+                try:
+                    rid = self.batcher.submit(prompt, n, **sampling)
+                    self._futures[rid] = fut
+                    self._t0[rid] = t0
+                except Exception as e:          # a bad request fails alone
+                    self.counters["failed"] += 1
+                    fut.set_exception(e)
+            if not self.batcher.pending():
+                time.sleep(self._idle)
+                continue
+            try:
+                done = self.batcher.step()
+            except Exception as e:              # a model failure fails everything in flight
+                for rid, fut in self._futures.items():
+                    fut.set_exception(e)
+                self.counters["failed"] += len(self._futures)
+                self._futures.clear()
+                self._stop.set()
+                return
+            for r in done:
+                fut = self._futures.pop(r.id)
+                self.counters["completed"] += 1
+                self.counters["generated_tokens"] += len(r.output)
+                self.counters["latency_s_sum"] += time.perf_counter() - self._t0.pop(r.id)
+                fut.set_result(list(r.output))
+
+
+def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int] = None,
+               token_chunk: Optional[int] = None, request_timeout_s: float = 120.0):
+    """FastAPI application.  ``tokenizer`` (anything with ``encode(str) -> ids`` and
+    ``decode_ids(ids) -> str`` or ``decode(ids) -> str``) enables text prompts; without it requests carry ``prompt_ids``."""
+    import asyncio
+
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import PlainTextResponse
+
+    from contextlib import asynccontextmanager
+
+    loop = ServingLoop(model, max_seqs=max_seqs, max_len=max_len, token_chunk=token_chunk)
+
+    @asynccontextmanager
+    async def lifespan(_app):
+        yield
+        loop.close()
+
+    app = FastAPI(title="coeus_b200", lifespan=lifespan)
+    app.state.loop = loop
+
+    @app.post("/v1/completions")
+    async def completions(req: CompletionRequest):
+        if req.prompt_ids is not None:
+            ids = list(req.prompt_ids)
+        elif req.prompt is not None and tokenizer is not None:
+            ids = [int(t) for t in tokenizer.encode(req.prompt)]
+        else:
+            raise HTTPException(422, "give prompt_ids, or prompt when the server has a tokenizer")
+        V = model.cfg.vocab_size
+        if not ids or any(t < 0 or t >= V for t in ids):
+            raise HTTPException(422, f"token ids must lie in [0, {V}) and the prompt be non-empty")
+        fut = loop.submit(ids, req.max_tokens, eos_id=req.eos_id, temperature=req.temperature,
+                          top_k=req.top_k, top_p=req.top_p)
+        try:
+            out = await asyncio.wait_for(asyncio.wrap_future(fut), request_timeout_s)
+        except asyncio.TimeoutError:
+            raise HTTPException(504, "generation timed out")
+        except ProcessingError as e:
+            raise HTTPException(422, str(e))
+        body = {"token_ids": out, "usage": {"prompt_tokens": len(ids),
+                                            "completion_tokens": len(out)}}
+        if tokenizer is not None:
+            decode = getattr(tokenizer, "decode_ids", None) or tokenizer.decode
+            body["text"] = decode(out)
+        return body
+
+    @app.get("/health")
+    async def health():
+        if not loop.healthy():
+            raise HTTPException(503, "serving loop stopped")
+        return {"status": "ok", "active": len(loop.batcher.active),
+                "waiting": len(loop.batcher.waiting)}
+
+    @app.get("/metrics", response_class=PlainTextResponse)
+    async def metrics():
+        c, b = loop.counters, loop.batcher
+        lines = [f"coeus_{k} {v}" for k, v in c.items()]
+        lines += [f"coeus_active_requests {len(b.active)}",
+                  f"coeus_waiting_requests {len(b.waiting)}",
+                  f"coeus_kv_pages_in_use {loop.engine.cache.pages_in_use()}",
+                  f"coeus_decode_steps {b.stats['steps']}"]
+        return "\n".join(lines) + "\n"
+
+    return app

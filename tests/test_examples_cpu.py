@@ -55,3 +55,7 @@ def test_wordpiece_example():
     assert r["pieces"]["playing played"][1:-1] == ["play", "##ing", "play", "##ed"]
     assert "[UNK]" in r["pieces"]["xylophone"]
     assert r["chars_per_s"] > 0
+
+
+def test_serve_completions_dry_run():
+    assert _load("serve_completions").main(["--device", "cpu", "--dry-run"]) == 0

@@ -1,0 +1,70 @@
+"""The completion server on CPU: concurrent HTTP requests through the continuous batcher."""
+import concurrent.futures as cf
+
+import pytest
+import torch
+
+from coeus_b200.infer.engine import InferenceEngine
+from coeus_b200.models.config import DecoderConfig
+from coeus_b200.models.decoder import DecoderLM
+
+
+class _ByteTok:
+    def encode(self, s):
+        return list(s.encode())
+
+    def decode(self, ids):
+        return bytes(int(i) % 256 for i in ids).decode("latin-1")
+
+
+@pytest.fixture(scope="module")
+def model():
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+                        vocab_size=256, max_seq_len=96, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope")
+    return DecoderLM(cfg, "cpu", seed=4, dtype=torch.float32, training=False)
+
+
+def test_serving_loop_futures(model):
+    from coeus_b200.serve import ServingLoop
+    loop = ServingLoop(model, max_seqs=2, max_len=96)
+    try:
+        prompts = [[1, 2, 3], [9] * 20, [7, 7], [100, 3, 5, 8]]
+        futs = [loop.submit(p, 5) for p in prompts]
+        outs = [f.result(timeout=120) for f in futs]
+        for p, o in zip(prompts, outs):
+            alone = InferenceEngine(model, max_batch=1).generate(torch.tensor(p)[None], 5)
+            assert o == alone[0, len(p):].tolist()
+        bad = loop.submit([1] * 95, 10)           # too long: fails alone
+        with pytest.raises(Exception):
+            bad.result(timeout=60)
+        assert loop.healthy() and loop.counters["completed"] == 4 and loop.counters["failed"] == 1
+    finally:
+        loop.close()
+    assert not loop.healthy()
+
+
+def test_http_completions(model):
+    from fastapi.testclient import TestClient
+    from coeus_b200.serve import create_app
+    app = create_app(model, tokenizer=_ByteTok(), max_seqs=3, max_len=96)
+    with TestClient(app) as client:
+        assert client.get("/health").json()["status"] == "ok"
+
+        def ask(i):
+            return client.post("/v1/completions", json={"prompt": "hello " * (i + 1),
+                                                        "max_tokens": 3 + i}).json()
+        with cf.ThreadPoolExecutor(4) as ex:
+            res = list(ex.map(ask, range(5)))
+        for i, r in enumerate(res):
+            assert len(r["token_ids"]) == 3 + i and isinstance(r["text"], str)
+            assert r["usage"]["prompt_tokens"] == 6 * (i + 1)
+        ids = client.post("/v1/completions", json={"prompt_ids": [1, 2, 3], "max_tokens": 2})
+        assert ids.status_code == 200 and len(ids.json()["token_ids"]) == 2
+        assert client.post("/v1/completions", json={"max_tokens": 2}).status_code == 422
+        assert client.post("/v1/completions",
+                           json={"prompt_ids": [999], "max_tokens": 2}).status_code == 422
+        assert client.post("/v1/completions",
+                           json={"prompt_ids": [1] * 95, "max_tokens": 9}).status_code == 422
+        text = client.get("/metrics").text
+        assert "coeus_completed 6" in text and "coeus_kv_pages_in_use 0" in text
