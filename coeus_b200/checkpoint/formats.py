@@ -18,7 +18,6 @@ dimension before the copy.
 """
 from __future__ import annotations
 
-import json
 import os
 from typing import Callable, Dict, Optional, Tuple
 
@@ -29,7 +28,7 @@ from ..core.serialization import ModelMetadata, read_rustllm, write_rustllm
 from ..foundation.error import ProcessingError, invalid_input
 from ..models.config import DecoderConfig, Transformer250MConfig
 from ..models.layout_ref import (from_reference_flat, load_named_into_model, named_from_model,
-                                 reference_buffer_len, reference_offsets, to_reference_flat)
+                                 reference_offsets, to_reference_flat)
 from ..utils import native
 
 _NP = {"F32": np.float32, "F16": np.float16, "I64": np.int64, "I32": np.int32, "U8": np.uint8,

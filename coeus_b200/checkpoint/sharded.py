@@ -17,7 +17,7 @@ from __future__ import annotations
 import json
 import os
 import threading
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, Optional, Sequence, Tuple
 
 import numpy as np
 import torch

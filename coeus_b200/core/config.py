@@ -11,10 +11,9 @@ import json
 import os
 import threading
 from dataclasses import dataclass
-from typing import Any, Dict, Iterable, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence
 
 from ..foundation.error import ConfigError
-from ..foundation.types import PluginName
 
 
 class ConfigValue:

@@ -17,7 +17,7 @@ import io
 import os
 import struct
 from dataclasses import dataclass, field
-from typing import BinaryIO, Callable, List, Optional, Sequence, Tuple
+from typing import BinaryIO, Callable, List, Optional, Tuple
 
 import numpy as np
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import abc
 from dataclasses import dataclass
-from typing import Any, Generic, Iterable, Iterator, List, Optional, Sequence, TypeVar
+from typing import Any, Generic, Iterable, Iterator, List, Sequence, TypeVar
 
 from ..foundation.types import Version
 

@@ -3,7 +3,7 @@ generation engine consumes and produces, sessions and events."""
 from __future__ import annotations
 
 import itertools
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, List, Optional
 
 

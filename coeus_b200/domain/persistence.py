@@ -6,7 +6,7 @@ from __future__ import annotations
 import enum
 import os
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict, List
 
 
 @dataclass(frozen=True)

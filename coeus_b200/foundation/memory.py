@@ -15,7 +15,7 @@ import mmap
 import os
 import threading
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Generic, List, Optional, Sequence, TypeVar
 
 T = TypeVar("T")

@@ -6,7 +6,6 @@ src/domain/inference/mod.rs:6-32); the reference itself recomputes the full sequ
 token and returns one position."""
 from __future__ import annotations
 
-import math
 import time
 from typing import Dict, List, Optional
 

@@ -6,8 +6,7 @@ It shares the parameter names and ``[in, out]`` weight layout of :mod:`.decoder`
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 import torch.nn.functional as F

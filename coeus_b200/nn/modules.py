@@ -4,7 +4,6 @@ follow the reference's transformer structs (``MultiHeadAttention`` with q/k/v/o 
 with q, k and v fused into one matrix."""
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -12,7 +12,7 @@ O / down along ``in``, the embedding table is replicated.
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 import torch.distributed as dist

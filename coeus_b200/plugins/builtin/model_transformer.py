@@ -13,8 +13,7 @@ from __future__ import annotations
 
 import io
 import os
-import tempfile
-from typing import Any, BinaryIO, List, Optional, Sequence, Union
+from typing import BinaryIO, List, Optional, Sequence, Union
 
 import torch
 

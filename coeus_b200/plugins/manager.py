@@ -8,7 +8,7 @@ from __future__ import annotations
 import sys
 import threading
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Sequence, Type
+from typing import Any, Callable, Dict, List, Sequence, Type
 
 from ..core.plugin import Plugin, PluginCapabilities, PluginEntry, PluginState
 from ..foundation.error import PluginError

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import contextlib
 import time
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 
