@@ -150,15 +150,20 @@ class Trainer:
         self._micro = int(head.get("micro", 0))
 
     # ---- sharded checkpoints (resume on any number of ranks)
+    def _sharded(self) -> bool:
+        """Whether optimizer state is split over the data-parallel ranks (else every rank holds
+        all of it and rank 0 writes the checkpoint of a single replica)."""
+        return self.dp is not None and getattr(self.dp, "sharded", True)
+
     def _owned_segments(self):
         m = self.model
-        if self.dp is None:
+        if not self._sharded():
             return [(0, m.n_flat)]
         return [b.shard(self.dp.rank, self.dp.world) for b in self.dp.buckets]
 
     def _moment_view(self, name: str, s: int, e: int) -> torch.Tensor:
         """The ``[s, e)`` slice of Adam's ``m`` or ``v`` (flat coordinates)."""
-        if self.dp is None:
+        if not self._sharded():
             return getattr(self.opt, name)[s:e]
         for b, off in zip(self.dp.buckets, self.dp.moffs):
             bs, be = b.shard(self.dp.rank, self.dp.world)
@@ -176,10 +181,17 @@ class Trainer:
 
         from ..checkpoint import sharded as S
         m = self.model
-        rank = 0 if self.dp is None else self.dp.rank
-        world = 1 if self.dp is None else self.dp.world
         if self.dp is not None:
             self.dp.finish()
+        if self.dp is not None and not self._sharded():
+            # replicated state: rank 0 writes the checkpoint of one replica, the others wait
+            if self.dp.rank != 0:
+                dist.barrier(group=self.dp.group)
+                return
+            rank, world = 0, 1
+        else:
+            rank = 0 if self.dp is None else self.dp.rank
+            world = 1 if self.dp is None else self.dp.world
 
         def fetch(name, s, e):
             return m.p32[s:e] if name == "p32" else self._moment_view(name, s, e)
@@ -187,7 +199,9 @@ class Trainer:
         meta = {"config": m.cfg.to_dict(), "n_flat": m.n_flat, "data_cursor": data_cursor,
                 "opt_step": self.opt.step_count, "train_step": self.step_index,
                 "python_rng": repr(random.getstate()[1][:4])}
-        barrier = (lambda: dist.barrier(group=self.dp.group)) if self.dp is not None else None
+        barrier = (lambda: dist.barrier(group=self.dp.group)) if self._sharded() else None
+        if background and self.dp is not None and not self._sharded():
+            background = False       # one writer; the other ranks are already at the barrier
         if background:
             if not hasattr(self, "_ckpt_writer"):
                 self._ckpt_writer = S.AsyncWriter()
@@ -197,6 +211,8 @@ class Trainer:
         else:
             S.save_shard(directory, rank, world, self._owned_segments(), fetch, self.step_index,
                          meta, barrier=barrier)
+        if self.dp is not None and not self._sharded():
+            dist.barrier(group=self.dp.group)
         for fn in self.listeners:
             fn({"event": "PersistenceEvent::Saved", "path": directory, "step": self.step_index})
 
