@@ -113,3 +113,80 @@ class SignalPad:
     def barrier(self, slot: int, value: int) -> None:
         self.signal(slot, value)
         self.wait(slot, value)
+
+
+class OffsetAllocator:
+    """First-fit allocator over ``[0, size)`` with coalescing free list: the bookkeeping of a
+    symmetric heap.  Pure host logic; all ranks that make the same sequence of calls get the same
+    offsets, which is what makes "the same offset on rank r" meaningful."""
+
+    def __init__(self, size: int, alignment: int = 256) -> None:
+        self.size, self.alignment = size, alignment
+        self.free: List[List[int]] = [[0, size]]          # sorted [start, end) holes
+        self.live = {}                                     # start -> end
+        self.peak = 0
+
+    def alloc(self, nbytes: int) -> int:
+        a = self.alignment
+        need = max(a, (nbytes + a - 1) // a * a)
+        for hole in self.free:
+            if hole[1] - hole[0] >= need:
+                start = hole[0]
+                hole[0] += need
+                if hole[0] == hole[1]:
+                    self.free.remove(hole)
+                self.live[start] = start + need
+                self.peak = max(self.peak, self.used())
+                return start
+        raise ResourceError.exhausted("symmetric heap", self.size - self.used(), need)
+
+    def release(self, start: int) -> None:
+        end = self.live.pop(start)
+        holes = sorted(self.free + [[start, end]])
+        merged: List[List[int]] = []
+        for h in holes:
+            if merged and merged[-1][1] == h[0]:
+                merged[-1][1] = h[1]
+            else:
+                merged.append(h)
+        self.free = merged
+
+    def used(self) -> int:
+        return sum(e - s for s, e in self.live.items())
+
+
+class SymmetricRegion:
+    """A piece of a :class:`SymmetricHeap`: ``local`` bytes of this rank, ``ptrs[r]`` by rank."""
+
+    def __init__(self, heap: "SymmetricHeap", offset: int, nbytes: int) -> None:
+        self.heap, self.offset, self.nbytes = heap, offset, nbytes
+        self.local = heap.buf.local[offset:offset + nbytes]
+        self.local_ptr = heap.buf.local_ptr + offset
+        self.ptrs = [p + offset for p in heap.buf.ptrs]
+
+    def ptr_array(self, byte_offset: int = 0):
+        return self.heap.buf.ptr_array(self.offset + byte_offset)
+
+    def view(self, dtype: torch.dtype, numel: Optional[int] = None) -> torch.Tensor:
+        return self.heap.buf.view(dtype, self.offset,
+                                  numel if numel is not None else
+                                  self.nbytes // torch.empty((), dtype=dtype).element_size())
+
+    def free(self) -> None:
+        self.heap.alloc_state.release(self.offset)
+
+
+class SymmetricHeap:
+    """One peer-mapped allocation per rank, sub-allocated on the host: many symmetric tensors
+    cost one IPC exchange, and every region's offset is the same on all ranks because all ranks
+    allocate in the same order (a collective convention, like the order of collectives)."""
+
+    def __init__(self, nbytes: int, group, device: torch.device, alignment: int = 256) -> None:
+        self.buf = SymmetricBuffer(nbytes, group, device)
+        self.alloc_state = OffsetAllocator(self.buf.nbytes, alignment)
+
+    def alloc(self, nbytes: int) -> SymmetricRegion:
+        return SymmetricRegion(self, self.alloc_state.alloc(nbytes), nbytes)
+
+    def close(self) -> None:
+        self.buf.close()

@@ -156,3 +156,26 @@ def test_replicated_data_parallel_matches_one_rank(tmp_path):
     assert int(meta["train_step"]) == 3
     assert torch.equal(other.model.p32, torch.from_numpy(full))
     assert len(ref_losses) == 3
+
+
+def test_symmetric_heap_offset_allocator():
+    from coeus_b200.parallel.symm import OffsetAllocator
+    a = OffsetAllocator(4096, alignment=256)
+    x, y, z = a.alloc(100), a.alloc(300), a.alloc(256)
+    assert (x, y, z) == (0, 256, 768) and a.used() == 1024
+    a.release(y)
+    assert a.alloc(512) == 256                      # first fit reuses the hole exactly
+    a.release(x)
+    a.release(256)
+    assert a.free[0] == [0, 768]                    # neighbours coalesce
+    w = a.alloc(3072)
+    assert w == 1024 and a.peak == 3072 + 256
+    with pytest.raises(Exception):
+        a.alloc(1024)
+    a.release(z)
+    a.release(w)
+    assert a.free == [[0, 4096]] and a.used() == 0
+    # the same call sequence gives the same offsets on every "rank"
+    b, c = OffsetAllocator(1 << 20), OffsetAllocator(1 << 20)
+    seq = [1000, 70000, 5, 4096]
+    assert [b.alloc(n) for n in seq] == [c.alloc(n) for n in seq]
