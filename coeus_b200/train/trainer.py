@@ -70,6 +70,25 @@ class Trainer:
     def compute_loss(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         return self.model.forward_loss(ids, targets)
 
+    def evaluate(self, batches) -> Dict[str, float]:
+        """Mean next-token loss and perplexity over ``(ids, targets)`` batches without touching
+        gradients or optimizer state (token-weighted; averaged over the data-parallel group when
+        there is one)."""
+        import math
+        m = self.model
+        tot = torch.zeros(2, dtype=torch.float64, device=m.device)
+        for ids, targets in batches:
+            n = int((targets >= 0).sum())
+            loss = m.forward_loss(ids, targets)
+            m._saved = None                       # nothing is kept for a backward pass
+            tot[0] += float(loss) * targets.numel()
+            tot[1] += n
+        if self.dp is not None and self.dp.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(tot, group=self.dp.group)
+        mean = float(tot[0] / tot[1].clamp_min(1))
+        return {"loss": mean, "perplexity": math.exp(min(mean, 80.0)), "tokens": int(tot[1])}
+
     def update_parameters(self, grad_scale: float = 1.0) -> None:
         m = self.model
         if self.dp is None:

@@ -279,3 +279,26 @@ def test_trainer_checkpoint_bytes_round_trip():
     assert float(la) == float(lb) and torch.equal(a.model.p32, b.model.p32)
     with pytest.raises(Exception):
         b.restore(blob[:-4])
+
+
+def test_trainer_evaluate_reports_loss_and_perplexity():
+    import math
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.train.trainer import TrainConfig, Trainer
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    torch.manual_seed(0)
+    data = [(torch.randint(0, 64, (2, 16)), torch.randint(0, 64, (2, 16))) for _ in range(3)]
+    tr = Trainer(DecoderLM(cfg, "cpu", seed=1, dtype=torch.float32), TrainConfig(learning_rate=1e-2))
+    before = tr.model.p32.clone()
+    ev = tr.evaluate(data)
+    assert torch.equal(before, tr.model.p32) and ev["tokens"] == 96
+    want = sum(float(tr.model.forward_loss(i, t)) for i, t in data) / 3
+    assert abs(ev["loss"] - want) < 1e-5 and abs(ev["perplexity"] - math.exp(want)) < 1e-2
+    # an untrained model is near the uniform distribution
+    assert abs(ev["loss"] - math.log(64)) < 0.2
+    for _ in range(30):
+        tr.train_step(*data[0])
+    assert tr.evaluate(data[:1])["loss"] < ev["loss"] - 0.5
