@@ -413,6 +413,52 @@ IteratorExt = Iter
 AdvancedIteratorExt = Iter
 
 
+class IteratorAdapter:
+    """An iterator that wraps a source iterator (iterator.rs:37-46)."""
+
+    def source(self):
+        return self._it
+
+    def source_mut(self):
+        return self._it
+
+
+class StatefulIterator:
+    """An iterator with an inspectable, resettable state (iterator.rs:49-58)."""
+
+    def state(self):
+        raise NotImplementedError
+
+    def reset_state(self) -> None:
+        raise NotImplementedError
+
+
+class PreciseSizeHint:
+    """``exact_size`` / ``is_empty`` on top of a size hint (iterator.rs:63-79; the reference
+    implements it for every iterator).  ``size_hint`` returns ``(lower, upper or None)``."""
+
+    def __init__(self, it: Iterable) -> None:
+        self._it = it
+
+    def __iter__(self):
+        return iter(self._it)
+
+    def size_hint(self) -> Tuple[int, Optional[int]]:
+        try:
+            n = len(self._it)              # type: ignore[arg-type]
+            return n, n
+        except TypeError:
+            import operator
+            return operator.length_hint(self._it, 0), None
+
+    def exact_size(self) -> Optional[int]:
+        lo, hi = self.size_hint()
+        return lo if hi == lo else None
+
+    def is_empty(self) -> bool:
+        return self.size_hint()[1] == 0
+
+
 # ------------------------------------------------------------------------------ literature
 class RopeNode:
     """``Leaf(str)`` or ``Branch{left,right}`` (public constructors, unlike the reference's

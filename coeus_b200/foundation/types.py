@@ -154,3 +154,7 @@ class markers:
 
     class Untrained:
         pass
+
+
+# ``dyn core::error::Error + Send + Sync`` (src/foundation/types.rs:112): any exception object.
+DynError = Exception

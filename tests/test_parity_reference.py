@@ -488,3 +488,38 @@ def test_concurrent_plugin_access():
     [t.start() for t in ts]
     [t.join() for t in ts]
     assert out == ["basic_tokenizer"] * 4
+
+
+def test_prelude_exports_every_name_of_the_reference_prelude():
+    """src/lib.rs:113-157: the named re-exports plus the public items behind the three glob
+    re-exports (``traits::*``, ``iterator::*``, ``types::*``)."""
+    import coeus_b200.prelude as P
+    named = """ConfigBuilder ConfigStore ConfigValue Configurable PluginConfigManager
+        BasicGenerationConfig BasicModelConfig DiffusionSampler ForwardModel GenerationConfig
+        GenerativeModel Loss Model ModelBuilder ModelConfig NoiseSchedule OptimizerState
+        TrainableModel Transformer250MConfig Plugin calculate_checksum ModelHeader ModelMetadata
+        ModelSerializable ParameterSerializer Token Tokenizer Error Arena CowStr LazyAlloc SliceView
+        ZeroCopyStringBuilder PluginManager InferenceEvent InferenceRequest InferenceResult
+        InferenceService InferenceSession Architecture DomainModelAggregate ModelRepository
+        ModelingEvent ModelingService DomainCheckpoint PersistenceEvent PersistenceService
+        SerializationFormat StorageBackend DomainToken TokenizationEvent TokenizationService
+        TokenizerAggregate TokenizerRepository Optimizer DomainTrainingConfig TrainingEvent
+        TrainingService TrainingSession""".split()
+    traits = """Identity Versioned Metadata Lifecycle AsyncLifecycle Process StreamProcess
+        BatchProcess Serialize Checkpoint HealthCheck Metrics Validate Constraint Builder Factory
+        Adapter Strategy Pipeline Piped Component ComponentInfo""".split()
+    iterators = """IteratorAdapter StatefulIterator PreciseSizeHint Windows SliceWindows
+        StreamFusion CacheOblivious Zipper Chunks Stride BatchIterator Scan Prefetch
+        ZeroCopyTokenizer ZeroCopySplit IteratorExt AdvancedIteratorExt RopeIterator
+        OwnedRopeIterator BTreeIterator SuffixArrayIterator WaveletTreeIterator TrieNode
+        TrieIterator BloomFilterBitIterator slice_windows slice_windows_step""".split()
+    types = """Version TokenId VocabSize SequenceLength BatchSize ModelDim HeadCount LayerCount
+        ModelFloat ModelDouble DynError PluginName ConfigKey Shape DType""".split()
+    missing = [n for n in named + traits + iterators + types if not hasattr(P, n)]
+    assert not missing, missing
+    # the framework's own entry points travel with it
+    for n in ("Trainer", "TrainConfig", "InferenceEngine", "ContinuousBatcher", "ParallelConfig",
+              "DecoderConfig"):
+        assert hasattr(P, n)
+    assert P.PreciseSizeHint([1, 2, 3]).exact_size() == 3
+    assert P.PreciseSizeHint(iter([1])).exact_size() is None and P.PreciseSizeHint([]).is_empty()
