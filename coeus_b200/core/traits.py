@@ -212,3 +212,21 @@ class Constraint(abc.ABC, Generic[T]):
 
     @abc.abstractmethod
     def description(self) -> str: ...
+
+
+class IntoIterator(Identity):
+    """A component that produces an iterator (traits.rs:386-395)."""
+
+    @abc.abstractmethod
+    def into_iter(self) -> Iterator[Any]: ...
+
+    def __iter__(self) -> Iterator[Any]:
+        return self.into_iter()
+
+
+class FromIterator(Identity):
+    """A component that can be built from an iterator (traits.rs:399-402)."""
+
+    @classmethod
+    @abc.abstractmethod
+    def from_iter(cls, iter: Iterable[Any]) -> "FromIterator": ...

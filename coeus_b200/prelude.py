@@ -17,7 +17,7 @@ from .core.traits import (Checkpoint, Component, ComponentInfo, HealthCheck, Ide
                           Versioned)
 from .core.tokenizer import NormalizingTokenizer, SpecialTokenizer  # noqa: F401
 from .core.traits import (Adapter, AsyncLifecycle, BatchProcess, Builder, Constraint, Factory,  # noqa: F401
-                          Strategy, StreamProcess)
+                          FromIterator, IntoIterator, Strategy, StreamProcess)
 from .domain.inference import (InferenceEvent, InferenceRequest, InferenceResult,  # noqa: F401
                                InferenceService, InferenceSession)
 from .domain.modeling import (Architecture, ModelingEvent, ModelingService,  # noqa: F401

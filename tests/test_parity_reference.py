@@ -507,7 +507,7 @@ def test_prelude_exports_every_name_of_the_reference_prelude():
         TrainingService TrainingSession""".split()
     traits = """Identity Versioned Metadata Lifecycle AsyncLifecycle Process StreamProcess
         BatchProcess Serialize Checkpoint HealthCheck Metrics Validate Constraint Builder Factory
-        Adapter Strategy Pipeline Piped Component ComponentInfo""".split()
+        Adapter Strategy Pipeline Piped Component ComponentInfo IntoIterator FromIterator""".split()
     iterators = """IteratorAdapter StatefulIterator PreciseSizeHint Windows SliceWindows
         StreamFusion CacheOblivious Zipper Chunks Stride BatchIterator Scan Prefetch
         ZeroCopyTokenizer ZeroCopySplit IteratorExt AdvancedIteratorExt RopeIterator
