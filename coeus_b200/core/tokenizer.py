@@ -11,6 +11,9 @@ from dataclasses import dataclass
 from typing import Iterable, Iterator, List, Optional, Sequence
 
 
+# ``Box<dyn Iterator<Item = T>>`` (src/core/tokenizer.rs:14): any iterator of tokens.
+TokenIterator = Iterator
+
 class Token(abc.ABC):
     @abc.abstractmethod
     def id(self) -> int: ...

@@ -45,8 +45,8 @@ class Error(Exception):
 
     def with_context(self, f) -> "ContextualError":
         """``f`` is an operation name, an ``ErrorContext`` or a callable returning one."""
-        if isinstance(f, str):
-            return ContextualError(self, ErrorContext(f))
+        if isinstance(f, str):      # error.rs:368-370: operation "operation", the text as details
+            return ContextualError(self, ErrorContext("operation").with_details(f))
         if isinstance(f, ErrorContext):
             return ContextualError(self, f)
         return ContextualError(self, f())
@@ -313,6 +313,19 @@ class ContextualError(Error, Generic[T]):
 def with_context(value: Any, ctx: ErrorContext) -> ContextualError:
     """``ErrorExt::context`` for arbitrary values."""
     return ContextualError(value, ctx)
+
+
+class ErrorExt:
+    """``ErrorExt`` (error.rs:352-371), which the reference implements for every type: wrap any
+    value with a context.  :class:`Error` carries the same two methods itself."""
+
+    @staticmethod
+    def context(value: Any, ctx: ErrorContext) -> ContextualError:
+        return ContextualError(value, ctx)
+
+    @staticmethod
+    def with_context(value: Any, context: str) -> ContextualError:
+        return ContextualError(value, ErrorContext("operation").with_details(context))
 
 
 # -------------------------------------------------------------------------------- helpers

@@ -36,7 +36,7 @@ from .foundation.error import (CommError, CompositeError, ConfigError, DeviceErr
                                ErrorContext, IoError, PluginError, ProcessingError, ResourceError,
                                error_context, internal_error, invalid_input, limit_exceeded,
                                not_initialized)
-from .foundation.error import ContextualError  # noqa: F401
+from .foundation.error import ContextualError, ErrorExt  # noqa: F401
 from .foundation.iterator import (AdvancedIteratorExt, BatchIterator, BloomFilterBitIterator,  # noqa: F401
                                   BTreeIterator, CacheOblivious, Chunks, Iter, IteratorAdapter,
                                   IteratorExt, OwnedRopeIterator, PreciseSizeHint, Prefetch,
