@@ -36,6 +36,8 @@ def _default_device(device: str = "auto") -> torch.device:
         else torch.device("cpu")
 
 
+from . import transformer_math as math  # noqa: E402  (the plugin's `mod math`)
+
 class TransformerModel(GenerativeModel, BatchedModel, ModelSerializable):
     def __init__(self, config: Union[Transformer250MConfig, DecoderConfig], lm: DecoderLM,
                  tail: Optional[torch.Tensor] = None, init: str = "reference") -> None:

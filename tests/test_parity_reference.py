@@ -523,3 +523,26 @@ def test_prelude_exports_every_name_of_the_reference_prelude():
         assert hasattr(P, n)
     assert P.PreciseSizeHint([1, 2, 3]).exact_size() == 3
     assert P.PreciseSizeHint(iter([1])).exact_size() is None and P.PreciseSizeHint([]).is_empty()
+
+
+def test_transformer_plugin_math_helpers():
+    """plugins/model-transformer/src/lib.rs:50-128 with the values its own unit tests use
+    (matmul of a 2x3 by a 3x2, softmax summing to one, gelu(0) = 0, layer_norm of 1..4)."""
+    import math as pymath
+    import torch
+    from coeus_b200.plugins.builtin import model_transformer as MT
+    m = MT.math
+    assert m.matmul([1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12], 2, 2, 3).tolist() == [58, 64, 139, 154]
+    p = m.softmax([1.0, 2.0, 3.0])
+    assert abs(float(p.sum()) - 1.0) < 1e-6 and p[2] > p[1] > p[0]
+    assert m.gelu(0.0) == 0.0 and abs(m.gelu(1.0) - 0.8411919906) < 1e-6
+    assert abs(m.gelu(-1.0) + 0.1588080094) < 1e-6
+    y = m.layer_norm([1.0, 2.0, 3.0, 4.0], [1.0] * 4, [0.0] * 4, 1e-5)
+    assert abs(float(y.mean())) < 1e-6 and abs(float((y * y).mean()) - 1.0) < 1e-4
+    # statistics span the whole buffer; scale and bias repeat with their own length
+    x = torch.arange(12.0)
+    z = m.layer_norm(x, [1.0, 2.0], [0.5], 1e-5)
+    mean, var = x.mean(), ((x - x.mean()) ** 2).mean()
+    want = torch.tensor([1.0, 2.0]).repeat(6) * (x - mean) / torch.sqrt(var + 1e-5) + 0.5
+    assert torch.allclose(z, want, atol=1e-6)
+    assert pymath.isclose(float(m.gelu(torch.tensor([2.0]))), m.gelu(2.0), rel_tol=1e-6)
