@@ -52,6 +52,7 @@ from .foundation.types import (BatchSize, ConfigKey, DType, DynError, HeadCount,
                                TokenId, Version, VocabSize)
 from .infer.engine import InferenceEngine  # noqa: F401
 from .infer.scheduler import ContinuousBatcher  # noqa: F401
+from .train.launch import ParallelRun, build_trainer  # noqa: F401
 from .train.trainer import TrainConfig, Trainer  # noqa: F401
 from .plugins import PluginEvent, PluginInfo, PluginManager, PluginRegistry, PluginRegistryBuilder  # noqa: F401
 from .plugins.builtin import (BasicLoaderPlugin, BasicModelPlugin, BasicTokenizerPlugin,  # noqa: F401

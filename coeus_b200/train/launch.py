@@ -1,0 +1,127 @@
+"""One entry point from a :class:`coeus_b200.core.config.ParallelConfig` to a ready trainer.
+
+``build_trainer`` reads which strategy the configuration asks for, builds the communication state
+and the (sharded) model of that strategy over the given process group, and returns a
+:class:`ParallelRun` whose ``step(ids, targets)`` takes the *global* batch on every rank and feeds
+each rank the part its strategy wants (a slice of sequences for data and expert parallelism, the
+whole batch for tensor parallelism, micro-batches for a pipeline, zig-zag chunks of every sequence
+for context parallelism).  One strategy at a time spans the group; products of strategies (e.g.
+dp x tp) are rejected with a configuration error rather than half-supported.  The reference is a
+single process (no parallelism of any kind in its sources).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..core.config import ParallelConfig
+from ..foundation.error import ConfigError
+from ..models.config import DecoderConfig
+from ..models.decoder import DecoderLM
+from .trainer import TrainConfig, Trainer
+
+
+@dataclass
+class ParallelRun:
+    strategy: str                       # single | dp | tp | pp | ep | cp
+    trainer: Any
+    model: Any
+    rank: int
+    world: int
+    _feed: Callable
+
+    def step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """``ids`` / ``targets``: the global ``[B, S]`` batch, identical on every rank.  Returns
+        this rank's loss (pipeline: the last stage holds it, the others return zeros)."""
+        return self._feed(ids, targets)
+
+
+def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
+                  train_cfg: Optional[TrainConfig] = None, group=None, micro_batches: int = 1,
+                  seed: int = 0, dtype: torch.dtype = torch.bfloat16,
+                  recompute: bool = False) -> ParallelRun:
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    parallel.validate()
+    active = [k for k in ("dp", "tp", "pp", "ep", "cp") if getattr(parallel, k) > 1]
+    if parallel.ep > 1 and parallel.dp == parallel.ep:
+        active = [k for k in active if k != "dp"]    # the expert group is the data group
+    if len(active) > 1:
+        raise ConfigError.conflict(active[0], active[1],
+                                   "one parallelism strategy spans the process group at a time")
+    strategy = active[0] if active else "single"
+    if strategy != "single" and getattr(parallel, strategy) != world:
+        raise ConfigError.invalid(strategy, getattr(parallel, strategy),
+                                  f"must equal the size of the process group ({world})")
+    if strategy != "single" and group is None:
+        group = dist.group.WORLD
+    device = torch.device(device)
+    tc = train_cfg or TrainConfig()
+    cpu = device.type != "cuda"
+
+    if strategy == "single":
+        model = DecoderLM(cfg, device, seed=seed, dtype=dtype, recompute=recompute)
+        tr = Trainer(model, tc)
+        return ParallelRun(strategy, tr, model, rank, world, tr.train_step)
+
+    if strategy == "dp":
+        from ..parallel.zero import ShardedDataParallel
+        backend = "collective" if cpu else parallel.dp_backend
+        model = DecoderLM(cfg, device, seed=seed, dtype=dtype, recompute=recompute)
+        tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend))
+
+        def feed(ids, targets):
+            per = ids.shape[0] // world
+            sl = slice(rank * per, (rank + 1) * per)
+            return tr.train_step(ids[sl].contiguous(), targets[sl].contiguous())
+        return ParallelRun(strategy, tr, model, rank, world, feed)
+
+    if strategy == "tp":
+        from ..parallel.tp import TensorParallel
+        from ..parallel.tp_model import TPDecoderLM, TPTrainer
+        tp = TensorParallel(group, device)
+        model = TPDecoderLM(cfg, tp, device, seed=seed, dtype=dtype, recompute=recompute)
+        tr = TPTrainer(model, tc.adamw())
+        return ParallelRun(strategy, tr, model, rank, world, tr.train_step)
+
+    if strategy == "pp":
+        from ..parallel.pp import PipelineStage
+        st = PipelineStage(cfg, group, device, micro_batches, seed=seed, dtype=dtype, train_cfg=tc)
+
+        def feed(ids, targets):
+            M = micro_batches
+            b = ids.shape[0] // M
+            return st.train_step(ids.reshape(M, b, -1), targets.reshape(M, b, -1))
+        return ParallelRun(strategy, st, st.model, rank, world, feed)
+
+    if strategy == "ep":
+        from ..parallel.ep import ExpertParallel, ExpertParallelTrainer
+        epx = ExpertParallel(group, device)
+        model = DecoderLM(cfg, device, seed=seed, dtype=dtype, epx=epx, recompute=recompute)
+        tr = ExpertParallelTrainer(model, tc)
+
+        def feed(ids, targets):
+            per = ids.shape[0] // world
+            sl = slice(rank * per, (rank + 1) * per)
+            return tr.train_step(ids[sl].contiguous(), targets[sl].contiguous())
+        return ParallelRun(strategy, tr, model, rank, world, feed)
+
+    # context parallelism: every rank sees its chunks of every sequence; gradients are summed over
+    # the group exactly like data-parallel replicas
+    from ..parallel.zero import ShardedDataParallel
+    if parallel.ulysses:
+        from ..parallel.ulysses import UlyssesParallel
+        cp = UlyssesParallel(group, device)
+    else:
+        from ..parallel.cp import ContextParallel
+        cp = ContextParallel(group, device)
+    model = DecoderLM(cfg, device, seed=seed, dtype=dtype, cp=cp, recompute=recompute)
+    backend = "collective" if cpu else parallel.dp_backend
+    tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend))
+
+    def feed_cp(ids, targets):
+        return tr.train_step(cp.shard(ids), cp.shard(targets))
+    return ParallelRun("cp", tr, model, rank, world, feed_cp)
