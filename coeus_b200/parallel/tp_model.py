@@ -93,51 +93,68 @@ class TPDecoderLM:
         if full is not None:
             self.load_from_full(full)
         else:
-            gen = torch.Generator(device=self.device)
-            gen.manual_seed(seed * 1000 + 17)
-            for name, shape, decay in specs:
-                t = self.master[name]
-                if decay:
-                    # replicated tensors must agree across ranks; shards get rank-specific seeds
-                    g2 = torch.Generator(device=self.device)
-                    import zlib
-                    g2.manual_seed(zlib.crc32(f"{seed}/{name}/"
-                                              f"{0 if name == 'token_embed' else self.rank}".encode()))
-                    t.normal_(0.0, cfg.init_std, generator=g2)
-                elif name.endswith("_scale"):
-                    t.fill_(1.0)
-            self.p16.copy_(self.p32)
+            self._init_like_unsharded(seed)
 
     # ------------------------------------------------------------------ parameters
     def load_from_full(self, full) -> None:
         """Take this rank's shards out of an unsharded :class:`DecoderLM` with the same config."""
+        self._take_shards(lambda name: full.master[name], full.layout.norm_names)
+
+    def _init_like_unsharded(self, seed: int) -> None:
+        """Random init that does not depend on the tensor-parallel degree: every tensor is drawn
+        whole, with the stream the unsharded model uses for it (one generator seed per tensor
+        name), and this rank keeps its slice.  One full tensor lives at a time."""
+        import zlib
+
+        from ..models.decoder import ParamLayout
+        cfg = self.cfg
+        layout = ParamLayout(cfg)
+        gen = torch.Generator(device=self.device)
+
+        def draw(name: str) -> torch.Tensor:
+            s = layout.by_name[name]
+            t = torch.zeros(tuple(s.shape), dtype=torch.float32, device=self.device)
+            if s.kind in ("weight", "embed"):
+                gen.manual_seed(seed * 1000003 + zlib.crc32(name.encode()))
+                t.normal_(0.0, cfg.init_std, generator=gen)
+                if name == "output_proj":          # padding columns of the vocabulary stay zero
+                    t[:, cfg.vocab_size:].zero_()
+            elif s.kind == "scale":
+                t.fill_(1.0)
+            return t
+
+        self._take_shards(draw, layout.norm_names)
+
+    def _take_shards(self, get, norm_names) -> None:
+        """``get(name)`` returns the unsharded fp32 tensor ``name`` (DecoderLM naming)."""
         cfg, r = self.cfg, self.rank
         H, I = cfg.hidden_dim, cfg.intermediate_dim
         Hl, Il, Vl = self.Hl, self.Il, self.Vl
-        fm = full.master
-        n1, n2, fn = full.layout.norm_names
-        self.master["token_embed"].copy_(fm["token_embed"][:cfg.vocab_size])
+        n1, n2, fn = norm_names
+        self.master["token_embed"].copy_(get("token_embed")[:cfg.vocab_size])
         for l in range(cfg.num_layers):
             p = f"layers.{l}."
-            wq = fm[p + "attn.qkv_weights"]
+            wq = get(p + "attn.qkv_weights")
             parts = [wq[:, i * H + r * Hl:i * H + (r + 1) * Hl] for i in range(3)]
             self.master[p + "attn.qkv_weights"].copy_(torch.cat(parts, 1))
-            self.master[p + "attn.o_weights"].copy_(fm[p + "attn.o_weights"][r * Hl:(r + 1) * Hl])
+            self.master[p + "attn.o_weights"].copy_(get(p + "attn.o_weights")[r * Hl:(r + 1) * Hl])
             if self.swiglu:
-                wg = fm[p + "ff.gate_up_weights"]
+                wg = get(p + "ff.gate_up_weights")
                 self.master[p + "ff.up_weights"].copy_(torch.cat(
                     [wg[:, r * Il:(r + 1) * Il], wg[:, I + r * Il:I + (r + 1) * Il]], 1))
             else:
-                self.master[p + "ff.up_weights"].copy_(fm[p + "ff.up_weights"][:, r * Il:(r + 1) * Il])
-            self.master[p + "ff.down_weights"].copy_(fm[p + "ff.down_weights"][r * Il:(r + 1) * Il])
+                self.master[p + "ff.up_weights"].copy_(
+                    get(p + "ff.up_weights")[:, r * Il:(r + 1) * Il])
+            self.master[p + "ff.down_weights"].copy_(
+                get(p + "ff.down_weights")[r * Il:(r + 1) * Il])
             for mine, theirs in (("norm1", n1), ("norm2", n2)):
-                self.master[p + mine + "_scale"].copy_(fm[p + theirs + "_scale"])
+                self.master[p + mine + "_scale"].copy_(get(p + theirs + "_scale"))
                 if not self.rms:
-                    self.master[p + mine + "_bias"].copy_(fm[p + theirs + "_bias"])
-        self.master["output_proj"].copy_(fm["output_proj"][:, r * Vl:(r + 1) * Vl])
-        self.master["final_norm_scale"].copy_(fm[fn + "_scale"])
+                    self.master[p + mine + "_bias"].copy_(get(p + theirs + "_bias"))
+        self.master["output_proj"].copy_(get("output_proj")[:, r * Vl:(r + 1) * Vl])
+        self.master["final_norm_scale"].copy_(get(fn + "_scale"))
         if not self.rms:
-            self.master["final_norm_bias"].copy_(fm[fn + "_bias"])
+            self.master["final_norm_bias"].copy_(get(fn + "_bias"))
         self.p16.copy_(self.p32)
 
     def num_parameters_local(self) -> int:

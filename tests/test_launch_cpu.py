@@ -61,12 +61,10 @@ def test_every_strategy_through_the_launcher(kind):
     want = "cp" if kind == "ulysses" else kind
     assert res[0][1] == want
     got = res[1][2]          # rank 1 is the last pipeline stage; the others agree on all ranks
-    # capacity slots differ between 1 and 2 expert-parallel ranks; the tensor-parallel model
-    # draws its shards with rank-specific streams (same distribution, other values)
-    tol = {"ep": 2e-2, "tp": 5e-2}.get(kind, 1e-4)
+    tol = 2e-2 if kind == "ep" else 1e-4     # capacity slots differ between 1 and 2 ranks
     assert abs(got[0] - ref[0]) < tol, (got, ref)
     assert got[-1] < got[0]
-    if kind not in ("ep", "tp"):
+    if kind != "ep":
         assert abs(got[-1] - ref[-1]) < 5e-3
 
 

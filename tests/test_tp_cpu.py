@@ -30,6 +30,9 @@ def _worker(rank, world, port, batch, out):
     full = DecoderLM(CFG, device="cpu", seed=0, dtype=torch.float32)
     tp = TensorParallel(dist.group.WORLD, "cpu")
     m = TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, full=full)
+    # the seed-based init draws what the unsharded model with that seed holds at this rank's place
+    seeded = TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, seed=0)
+    assert torch.equal(seeded.p32, m.p32)
     x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
     m.zero_grad()
     loss = m.forward_loss(x, y)
