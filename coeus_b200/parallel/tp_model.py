@@ -12,7 +12,7 @@ O / down along ``in``, the embedding table is replicated.
 from __future__ import annotations
 
 import math
-from typing import List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -156,6 +156,68 @@ class TPDecoderLM:
         if not self.rms:
             self.master["final_norm_bias"].copy_(get(fn + "_bias"))
         self.p16.copy_(self.p32)
+
+    def gather_full(self) -> Dict[str, torch.Tensor]:
+        """The unsharded fp32 tensors under the names of :class:`DecoderLM` (``attn.qkv_weights``
+        fused, ``ff.gate_up_weights`` for SwiGLU), assembled from all ranks' shards; every rank
+        gets the full set.  The inverse of :meth:`load_from_full`."""
+        cfg, n = self.cfg, self.n
+        H, Hl, Il = cfg.hidden_dim, self.Hl, self.Il
+        group = self.tp.group
+
+        def gather(t: torch.Tensor):
+            if n == 1:
+                return [t]
+            parts = [torch.empty_like(t) for _ in range(n)]
+            dist.all_gather(parts, t.contiguous(), group=group)
+            return parts
+
+        from ..models.decoder import ParamLayout
+        n1, n2, fn = ParamLayout(cfg).norm_names
+        out: Dict[str, torch.Tensor] = {}
+        emb = torch.zeros((cfg.vocab_padded, H), dtype=torch.float32, device=self.device)
+        emb[:cfg.vocab_size] = self.master["token_embed"]
+        out["token_embed"] = emb
+        for l in range(cfg.num_layers):
+            p = f"layers.{l}."
+            qkv = gather(self.master[p + "attn.qkv_weights"])
+            out[p + "attn.qkv_weights"] = torch.cat(
+                [torch.cat([s[:, i * Hl:(i + 1) * Hl] for s in qkv], 1) for i in range(3)], 1)
+            out[p + "attn.o_weights"] = torch.cat(gather(self.master[p + "attn.o_weights"]), 0)
+            up = gather(self.master[p + "ff.up_weights"])
+            if self.swiglu:
+                out[p + "ff.gate_up_weights"] = torch.cat(
+                    [torch.cat([s[:, :Il] for s in up], 1), torch.cat([s[:, Il:] for s in up], 1)], 1)
+            else:
+                out[p + "ff.up_weights"] = torch.cat(up, 1)
+            out[p + "ff.down_weights"] = torch.cat(gather(self.master[p + "ff.down_weights"]), 0)
+            for mine, theirs in (("norm1", n1), ("norm2", n2)):
+                out[p + theirs + "_scale"] = self.master[p + mine + "_scale"].clone()
+                if not self.rms:
+                    out[p + theirs + "_bias"] = self.master[p + mine + "_bias"].clone()
+        out["output_proj"] = torch.cat(gather(self.master["output_proj"]), 1)
+        out[fn + "_scale"] = self.master["final_norm_scale"].clone()
+        if not self.rms:
+            out[fn + "_bias"] = self.master["final_norm_bias"].clone()
+        return out
+
+    def save(self, path: str, fmt: Optional[str] = None) -> None:
+        """Write the whole model (``.safetensors`` / ``.gguf`` / ``.rustllm``) from rank 0; the
+        file loads into an unsharded model or, through :meth:`load_from_full` or the
+        tensor-parallel slicer of the checkpoint module, into any tensor-parallel degree."""
+        full = self.gather_full()
+        if self.rank == 0:
+            from ..checkpoint.formats import save_model
+
+            class _View:
+                cfg = self.cfg
+
+                @staticmethod
+                def named_parameters():
+                    return full.items()
+            save_model(_View, path, fmt)
+        if self.n > 1:
+            dist.barrier(group=self.tp.group)
 
     def num_parameters_local(self) -> int:
         return sum(math.prod(s) for _, s, _ in self.specs)
@@ -316,6 +378,7 @@ class TPTrainer:
         from ..optim.adamw import AdamW, AdamWConfig
         self.model = model
         self.opt = AdamW(opt_cfg or AdamWConfig(), 0, model.n_flat, model.decay_end, model.device)
+        self.step_index = 0
 
     def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         m = self.model
@@ -323,4 +386,54 @@ class TPTrainer:
         loss = m.forward_loss(ids, targets)
         m.backward()
         self.opt.step(m.p32, m.g32, m.p16)
+        self.step_index += 1
         return loss
+
+    # ---- training checkpoints: one file per rank (its shards of the weights and moments)
+    def save_checkpoint(self, directory: str) -> None:
+        """Every rank writes ``tp<rank>.safetensors`` (fp32 master weights and Adam moments of
+        its shards); rank 0 adds ``manifest.json``.  Resuming needs the same tensor-parallel
+        degree; to change it, :meth:`TPDecoderLM.save` the weights and load them elsewhere."""
+        import json
+        import os
+
+        from ..checkpoint.formats import save_safetensors
+        m = self.model
+        os.makedirs(directory, exist_ok=True)
+        if m.n > 1:
+            dist.barrier(group=m.tp.group)
+        save_safetensors(os.path.join(directory, f"tp{m.rank}.safetensors"),
+                         {"p32": m.p32, "m": self.opt.m, "v": self.opt.v},
+                         {"rank": str(m.rank), "tp": str(m.n)})
+        if m.n > 1:
+            dist.barrier(group=m.tp.group)
+        if m.rank == 0:
+            with open(os.path.join(directory, "manifest.json"), "w") as f:
+                json.dump({"kind": "tensor-parallel", "tp": m.n, "n_flat": m.n_flat,
+                           "opt_step": self.opt.step_count, "train_step": self.step_index,
+                           "config": m.cfg.to_dict()}, f)
+        if m.n > 1:
+            dist.barrier(group=m.tp.group)
+
+    def load_checkpoint(self, directory: str) -> dict:
+        import json
+        import os
+
+        from ..checkpoint.formats import load_safetensors
+        m = self.model
+        with open(os.path.join(directory, "manifest.json")) as f:
+            man = json.load(f)
+        if man.get("kind") != "tensor-parallel" or int(man["tp"]) != m.n \
+                or int(man["n_flat"]) != m.n_flat:
+            raise ProcessingError.invalid_input(
+                f"checkpoint was written at tensor-parallel degree {man.get('tp')} "
+                f"({man.get('n_flat')} local elements); this run has degree {m.n} "
+                f"({m.n_flat})")
+        t, _ = load_safetensors(os.path.join(directory, f"tp{m.rank}.safetensors"))
+        m.p32.copy_(t["p32"].to(m.device))
+        m.p16.copy_(m.p32)
+        self.opt.m.copy_(t["m"].to(m.device))
+        self.opt.v.copy_(t["v"].to(m.device))
+        self.opt.step_count = int(man["opt_step"])
+        self.step_index = int(man["train_step"])
+        return man

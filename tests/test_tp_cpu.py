@@ -21,6 +21,58 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _worker_ckpt(rank, world, port, batch, tmp, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.checkpoint.formats import load_model
+    from coeus_b200.optim.adamw import AdamWConfig
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM, TPTrainer
+    tp = TensorParallel(dist.group.WORLD, "cpu")
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    oc = AdamWConfig(lr=1e-2)
+    a = TPTrainer(TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, seed=0), oc)
+    for _ in range(2):
+        a.train_step(x, y)
+    a.save_checkpoint(tmp + "/ckpt")
+    a.model.save(tmp + "/full.safetensors")
+    # resume into a differently initialised trainer: the next step is the same step
+    b = TPTrainer(TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, seed=9), AdamWConfig(lr=1e-2))
+    man = b.load_checkpoint(tmp + "/ckpt")
+    assert man["train_step"] == 2 and torch.equal(a.model.p32, b.model.p32)
+    la, lb = float(a.train_step(x, y)), float(b.train_step(x, y))
+    assert la == lb and torch.equal(a.model.p32, b.model.p32)
+    # the exported whole model gives the loss the shards gave before that step
+    full, _ = load_model(tmp + "/full.safetensors", device="cpu")
+    c = TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, full=full)
+    b2 = TPTrainer(TPDecoderLM(CFG, tp, "cpu", dtype=torch.float32, seed=9), AdamWConfig(lr=1e-2))
+    b2.load_checkpoint(tmp + "/ckpt")
+    assert torch.equal(c.p32, b2.model.p32)
+    out.put((rank, la, float(full.forward_loss(x, y))))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_checkpoint_resume_and_whole_model_export(tmp_path):
+    from mp_util import run_ranks
+    torch.manual_seed(0)
+    batch = torch.randint(0, CFG.vocab_size, (2, 17))
+    res = run_ranks(_worker_ckpt, 2, (batch, str(tmp_path)), results=2)
+    ref = DecoderLM(CFG, device="cpu", seed=0, dtype=torch.float32)
+    from coeus_b200.optim.adamw import AdamW, AdamWConfig
+    opt = AdamW(AdamWConfig(lr=1e-2), 0, ref.n_flat, ref.layout.decay_end, "cpu")
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    for _ in range(2):
+        ref.zero_grad()
+        ref.forward_loss(x, y)
+        ref.backward()
+        opt.step(ref.p32, ref.g32, ref.p16)
+    want = float(ref.forward_loss(x, y))
+    for _, la, lfull in res:
+        assert abs(la - want) < 1e-4 and abs(lfull - want) < 1e-4
+
+
 def _worker(rank, world, port, batch, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
