@@ -387,6 +387,26 @@ class ExpertParallelTrainer:
             self._reduce(self.spans[l])     # attention + router weights of layer l
         # l == 0 and l == -2: the first span also holds the embedding; it goes last
 
+    def save_checkpoint(self, directory: str) -> None:
+        """Name-keyed training checkpoint: rank 0's file holds the replicated tensors and its
+        experts, the other ranks' files their experts (with the replicated tensors again, which
+        a loader takes from the first file that has them); loads into any expert-parallel
+        degree."""
+        from ..checkpoint.named import model_state, save_named
+        barrier = (lambda: dist.barrier(group=self.epx.group)) if self.epx.ep > 1 else None
+        save_named(directory, self.epx.rank, model_state(self.model, self.opt),
+                   {"ep": self.epx.ep, "opt_step": self.opt.step_count,
+                    "train_step": getattr(self, "step_index", 0),
+                    "config": self.model.cfg.to_dict()}, barrier)
+
+    def load_checkpoint(self, directory: str) -> dict:
+        from ..checkpoint.named import load_named, model_state
+        man = load_named(directory, model_state(self.model, self.opt))
+        self.model.sync_working_copy()
+        self.opt.step_count = int(man["opt_step"])
+        self.step_index = int(man["train_step"])
+        return man
+
     def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         m, ep = self.model, self.epx.ep
         T = ids.numel()

@@ -164,6 +164,23 @@ class PipelineStage:
             t.copy_(full.master[name])
         self.model.sync_working_copy()
 
+    def save_checkpoint(self, directory: str) -> None:
+        """Name-keyed training checkpoint (weights and Adam moments of this stage's tensors);
+        loads into any number of stages."""
+        from ..checkpoint.named import model_state, save_named
+        barrier = (lambda: dist.barrier(group=self.group)) if self.stages > 1 else None
+        save_named(directory, self.stage, model_state(self.model, self.opt),
+                   {"stages": self.stages, "opt_step": self.opt.step_count,
+                    "train_step": self.step_index, "config": self.cfg.to_dict()}, barrier)
+
+    def load_checkpoint(self, directory: str) -> dict:
+        from ..checkpoint.named import load_named, model_state
+        man = load_named(directory, model_state(self.model, self.opt))
+        self.model.sync_working_copy()
+        self.opt.step_count = int(man["opt_step"])
+        self.step_index = int(man["train_step"])
+        return man
+
     def train_step(self, ids: Optional[torch.Tensor], targets: Optional[torch.Tensor]) -> torch.Tensor:
         """One optimizer step over ``M`` micro-batches.  ``ids [M, b, S]`` is needed on the first
         stage, ``targets [M, b, S]`` on the last; both may be given everywhere.  Returns the mean

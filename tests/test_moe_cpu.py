@@ -203,3 +203,57 @@ def test_expert_parallel_training_matches_single_rank():
             if ".experts." in name:
                 ref = ref[rank * 2:(rank + 1) * 2]
             assert (got - ref).abs().max() < 1e-5, name
+
+
+def _worker_ep_ckpt(rank, world, port, tmp, out):
+    import os
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.parallel.ep import ExpertParallel, ExpertParallelTrainer
+    from coeus_b200.train.trainer import TrainConfig
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=48,
+                        vocab_size=96, max_seq_len=16, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope", num_experts=4, top_k=2, capacity_factor=2.0)
+    epx = ExpertParallel(dist.group.WORLD, "cpu")
+    tr = ExpertParallelTrainer(DecoderLM(cfg, "cpu", seed=2, dtype=torch.float32, epx=epx),
+                               TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0))
+    g = torch.Generator().manual_seed(rank)
+    ids = torch.randint(0, 96, (2, 16), generator=g)
+    tgt = torch.randint(0, 96, (2, 16), generator=g)
+    for _ in range(2):
+        tr.train_step(ids, tgt)
+    tr.save_checkpoint(tmp)
+    out.put((rank, {k: v.numpy().copy() for k, v in tr.model.master.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_checkpoint_loads_into_one_rank(tmp_path):
+    """Saved by two expert-parallel ranks (two experts each), loaded by a single rank holding all
+    four: replicated tensors equal either rank's, expert rows are the ranks' rows in order."""
+    import torch
+    from mp_util import run_ranks
+    from coeus_b200.checkpoint.named import load_named, model_state
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.optim.adamw import AdamW, AdamWConfig
+    res = {r[0]: r[1] for r in run_ranks(_worker_ep_ckpt, 2, (str(tmp_path),), results=2)}
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=48,
+                        vocab_size=96, max_seq_len=16, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope", num_experts=4, top_k=2, capacity_factor=2.0)
+    one = DecoderLM(cfg, "cpu", seed=7, dtype=torch.float32)
+    opt = AdamW(AdamWConfig(), 0, one.n_flat, one.layout.decay_end, "cpu")
+    man = load_named(str(tmp_path), model_state(one, opt))
+    assert man["ep"] == 2 and man["opt_step"] == 2
+    for name, t in one.master.items():
+        spec = one.layout.by_name[name]
+        if spec.expert:
+            want = torch.cat([torch.from_numpy(res[0][name]), torch.from_numpy(res[1][name])], 0)
+        else:
+            want = torch.from_numpy(res[0][name])
+        assert torch.equal(t, want), name
+    assert float(opt.v.abs().sum()) > 0

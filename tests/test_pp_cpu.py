@@ -200,3 +200,64 @@ def test_interleaved_pipeline_training_matches_single_rank():
             assert (torch.from_numpy(got) - full.master[name]).abs().max() < 1e-5, name
             seen.add(name)
     assert seen == set(full.master)
+
+
+def _worker_ckpt(rank, world, port, ids, tgt, tmp, mode, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.parallel.pp import PipelineStage
+    st = PipelineStage(_cfg(), dist.group.WORLD, "cpu", micro_batches=ids.shape[0],
+                       seed=4 if mode == "save" else 11, dtype=torch.float32, train_cfg=_train_cfg())
+    if mode == "save":
+        for _ in range(2):
+            st.train_step(ids, tgt)
+        st.save_checkpoint(tmp)
+        loss = 0.0
+    else:
+        man = st.load_checkpoint(tmp)
+        assert man["train_step"] == 2 and man["stages"] == 2
+        loss = float(st.train_step(ids, tgt))
+    out.put((rank, loss))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_pipeline_checkpoint_resumes_on_another_number_of_stages(tmp_path):
+    """Saved by two stages, resumed by three stages and by a single process: the third step is
+    the third step of the single-rank run."""
+    from mp_util import run_ranks
+    from coeus_b200.checkpoint.named import load_named, model_state
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.optim.adamw import AdamW
+    torch.manual_seed(0)
+    M, b, S = 4, 2, 16
+    ids = torch.randint(0, 96, (M, b, S))
+    tgt = torch.randint(0, 96, (M, b, S))
+    full = DecoderLM(_cfg(), "cpu", seed=4, dtype=torch.float32)
+    opt = AdamW(_train_cfg().adamw(), 0, full.n_flat, full.layout.decay_end, "cpu")
+
+    def ref_step(model, o):
+        model.zero_grad()
+        tot = 0.0
+        for i in range(M):
+            tot += float(model.forward_loss(ids[i], tgt[i], grad_scale=1.0 / (b * S * M))) / M
+            model.backward()
+        o.step(model.p32, model.g32, model.p16, 1.0)
+        return tot
+    for _ in range(2):
+        ref_step(full, opt)
+    run_ranks(_worker_ckpt, 2, (ids, tgt, str(tmp_path), "save"), results=2)
+    # single process
+    one = DecoderLM(_cfg(), "cpu", seed=11, dtype=torch.float32)
+    o1 = AdamW(_train_cfg().adamw(), 0, one.n_flat, one.layout.decay_end, "cpu")
+    man = load_named(str(tmp_path), model_state(one, o1))
+    one.sync_working_copy()
+    o1.step_count = int(man["opt_step"])
+    assert (one.p32 - full.p32).abs().max() < 1e-5 and (o1.v - opt.v).abs().max() < 1e-6
+    want = ref_step(full, opt)
+    assert abs(ref_step(one, o1) - want) < 1e-5
+    # three stages
+    res = {r[0]: r[1] for r in run_ranks(_worker_ckpt, 3, (ids, tgt, str(tmp_path), "load"),
+                                         results=3)}
+    assert abs(res[2] - want) < 1e-5
