@@ -35,6 +35,7 @@ class TPInferenceEngine:
         self.m, self.cfg, self.tp = model, model.cfg, model.tp
         self.device = model.device
         self.max_batch = max_batch
+        self.max_len = self.cfg.max_seq_len
         self.decode_splits = decode_splits
         cuda = self.device.type == "cuda"
         self.use_graph = (cuda and self.cfg.pos != "sinusoidal") if use_graph is None else use_graph
@@ -129,6 +130,104 @@ class TPInferenceEngine:
         self._pos_host = S
         xf = self._norm(last, "final_norm")
         return G.gemm(xf, m.w["output_proj"], b_mn=True)
+
+    # ------------------------------------------------------------------ slot-wise API (serving)
+    def open_slots(self, max_seqs: int, max_len: int) -> PagedKVCache:
+        """A cache whose rows are independent request slots (this rank's heads of each)."""
+        c = PagedKVCache.for_model(self.cfg, max_seqs, max(max_len, D.PAGE), self.device,
+                                   heads=self.m.nh_l)
+        if self.m.p16.dtype != torch.bfloat16:
+            c.k = [t.to(self.m.p16.dtype) for t in c.k]
+            c.v = [t.to(self.m.p16.dtype) for t in c.v]
+        self.cache, self._graph = c, None
+        return c
+
+    def _replicated_layers(self, x: torch.Tensor, n_seq: int, S: int, pos0: torch.Tensor,
+                           pos_host: int, table: torch.Tensor, ctx: Optional[torch.Tensor],
+                           pos_dev: Optional[torch.Tensor]) -> torch.Tensor:
+        """All layers on replicated activations ``[n_seq * S, H]``: column-parallel GEMMs give
+        this rank's heads / FFN columns, row-parallel GEMMs give partial sums that are added over
+        the group.  Prompts of any length go through here (``ctx is None``: causal attention over
+        the ``S`` new tokens; else one token per sequence against the paged cache).  Rows beyond
+        what the fused all-reduce buffers hold are summed with the library collective."""
+        m, cfg, ar, cache = self.m, self.cfg, self.ar, self.cache
+        dh, nh, Hl = cfg.head_dim, m.nh_l, m.Hl
+        T = x.shape[0]
+        fused = T <= self.max_batch
+
+        def reduce(partial_of, resid, norm_prefix):
+            if fused:
+                partial_of(ar.next_part(T))
+                return ar.reduce(T, resid, *self._norm_params(norm_prefix), m.rms, cfg.norm_eps)
+            part = torch.empty((T, cfg.hidden_dim), dtype=x.dtype, device=self.device)
+            partial_of(part)
+            if m.n > 1:
+                dist.all_reduce(part, group=self.tp.group)
+            y = (part.float() + resid.float()).to(x.dtype)
+            return y, self._norm(y, norm_prefix)
+
+        n1 = self._norm(x, "layers.0.norm1")
+        L = cfg.num_layers
+        for l in range(L):
+            p = f"layers.{l}."
+            qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
+            if cfg.pos == "rope":
+                E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos_host, theta=cfg.rope_theta,
+                        pos_dev=pos_dev)
+            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+            D.kv_write(k, v, cache.k[l], cache.v[l], table, pos0, S, nh, dh)
+            if ctx is None:
+                attn, _ = A.attention_fwd(q, k, v, n_seq, S, nh, dh, causal=True)
+            else:
+                attn = D.decode_attention(q, cache.k[l], cache.v[l], table, ctx, nh, dh,
+                                          splits=self.decode_splits)
+            x, n2 = reduce(lambda out: G.gemm(attn, m.w[p + "attn.o_weights"], b_mn=True, out=out),
+                           x, p + "norm2")
+            u = G.gemm(n2, m.w[p + "ff.up_weights"], b_mn=True)
+            act = E.swiglu_fwd(u) if m.swiglu else E.gelu_fwd(u)
+            nxt = f"layers.{l + 1}.norm1" if l + 1 < L else "final_norm"
+            x, n1 = reduce(lambda out: G.gemm(act, m.w[p + "ff.down_weights"], b_mn=True, out=out),
+                           x, nxt)
+        return n1            # final-norm output
+
+    def _full_logits(self, xf: torch.Tensor) -> torch.Tensor:
+        """``[T, V]`` logits on every rank from the vocabulary-parallel head."""
+        m = self.m
+        loc = G.gemm(xf, m.w["output_proj"], b_mn=True)            # [T, V/tp]
+        if m.n == 1:
+            return loc[:, :self.cfg.vocab_size]
+        parts = [torch.empty_like(loc) for _ in range(m.n)]
+        dist.all_gather(parts, loc.contiguous(), group=self.tp.group)
+        return torch.cat(parts, 1)[:, :self.cfg.vocab_size]
+
+    def prefill_slot(self, slot: int, ids: torch.Tensor, total_len: int,
+                     token_chunk: Optional[int] = None) -> torch.Tensor:
+        """Prompt ``ids [S]`` (any length, the same on every rank) into cache row ``slot``;
+        returns the last position's logits ``[V]``.  ``token_chunk`` is accepted for interface
+        parity with the single-GPU engine and ignored (the prompt runs in one pass)."""
+        m, cfg, cache = self.m, self.cfg, self.cache
+        S = ids.numel()
+        cache.reserve(slot, total_len)
+        x = E.embed_fwd(ids.reshape(-1), m.w["token_embed"], m._positions(max(S, total_len)), S)
+        pos0 = torch.zeros(1, dtype=torch.int32, device=self.device)
+        xf = self._replicated_layers(x, 1, S, pos0, 0, cache.page_table[slot:slot + 1], None, None)
+        cache.set_length(slot, S)
+        return self._full_logits(xf[-1:].contiguous())[0]
+
+    def decode_slots(self, slots: torch.Tensor, tokens: torch.Tensor,
+                     positions: torch.Tensor) -> torch.Tensor:
+        """One token for each cache row in ``slots [n]`` at ``positions [n]`` (int32); returns the
+        full ``[n, V]`` logits on every rank."""
+        m, cfg, cache = self.m, self.cfg, self.cache
+        x = E.embed_fwd(tokens, m.w["token_embed"], None, 1)
+        if cfg.pos == "sinusoidal":
+            pe = m._positions(int(positions.max()) + 1)
+            x = (x.float() + pe[positions.long()].float()).to(x.dtype)
+        table = cache.page_table.index_select(0, slots)
+        ctx = (positions + 1).to(torch.int32)
+        xf = self._replicated_layers(x, tokens.shape[0], 1, positions, 0, table, ctx,
+                                     positions if cfg.pos == "rope" else None)
+        return self._full_logits(xf)
 
     # ------------------------------------------------------------------ decode
     def _decode_body(self, tokens: torch.Tensor) -> torch.Tensor:

@@ -57,3 +57,41 @@ def test_tp_generation_matches_single_rank_engine():
         assert p.exitcode == 0
     for rank, toks in res:
         assert torch.equal(torch.from_numpy(toks), want), rank
+
+
+def _worker_serving(rank, world, port, prompts, budgets, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    from coeus_b200.infer.tp_engine import TPInferenceEngine
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM
+    full = DecoderLM(_cfg(), "cpu", seed=5, dtype=torch.float32, training=False)
+    tp = TensorParallel(dist.group.WORLD, "cpu", backend="nccl")
+    m = TPDecoderLM(_cfg(), tp, "cpu", dtype=torch.float32, full=full)
+    # max_batch 2 < longest prompt: prompts take the library all-reduce, decode rows the
+    # engine's all-reduce buffers
+    cb = ContinuousBatcher(TPInferenceEngine(m, max_batch=2), max_seqs=2, max_len=64)
+    ids = [cb.submit(p, k) for p, k in zip(prompts, budgets)]
+    res = cb.run()
+    out.put((rank, [res[i] for i in ids]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_continuous_batching_matches_single_rank_engine():
+    """Requests of different lengths through the batcher on two tensor-parallel ranks: every rank
+    produces the tokens the single-rank engine produces for each request alone."""
+    from mp_util import run_ranks
+    from coeus_b200.infer.engine import InferenceEngine
+    from coeus_b200.models.decoder import DecoderLM
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, 96, (n,)).tolist() for n in (5, 11, 3, 20)]
+    budgets = [4, 6, 2, 5]
+    full = DecoderLM(_cfg(), "cpu", seed=5, dtype=torch.float32, training=False)
+    want = [InferenceEngine(full, max_batch=1).generate(torch.tensor(p)[None], k)[0, len(p):].tolist()
+            for p, k in zip(prompts, budgets)]
+    for rank, got in run_ranks(_worker_serving, 2, (prompts, budgets), results=2):
+        assert got == want, rank
