@@ -374,18 +374,28 @@ class TPTrainer:
     """Training step of a tensor-parallel model: every rank applies AdamW to its own shards (the
     replicated tensors receive identical summed gradients, so they stay identical)."""
 
-    def __init__(self, model: TPDecoderLM, opt_cfg=None) -> None:
+    def __init__(self, model: TPDecoderLM, opt_cfg=None, dp_group=None) -> None:
+        """``dp_group``: ranks that hold the SAME shards in other tensor-parallel groups (data
+        parallelism across replicas of the tensor-parallel model); their gradients are averaged
+        with one all-reduce of the flat local gradient buffer before the optimizer step."""
         from ..optim.adamw import AdamW, AdamWConfig
         self.model = model
         self.opt = AdamW(opt_cfg or AdamWConfig(), 0, model.n_flat, model.decay_end, model.device)
         self.step_index = 0
+        self.dp_group = dp_group
+        self.dp = dist.get_world_size(dp_group) if dp_group is not None else 1
+        if self.dp > 1:      # replicas start from the same weights
+            dist.broadcast(model.p32, src=dist.get_global_rank(dp_group, 0), group=dp_group)
+            model.p16.copy_(model.p32)
 
     def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         m = self.model
         m.zero_grad()
         loss = m.forward_loss(ids, targets)
         m.backward()
-        self.opt.step(m.p32, m.g32, m.p16)
+        if self.dp > 1:
+            dist.all_reduce(m.g32, group=self.dp_group)
+        self.opt.step(m.p32, m.g32, m.p16, 1.0 / self.dp)
         self.step_index += 1
         return loss
 

@@ -5,8 +5,9 @@ and the (sharded) model of that strategy over the given process group, and retur
 :class:`ParallelRun` whose ``step(ids, targets)`` takes the *global* batch on every rank and feeds
 each rank the part its strategy wants (a slice of sequences for data and expert parallelism, the
 whole batch for tensor parallelism, micro-batches for a pipeline, zig-zag chunks of every sequence
-for context parallelism).  One strategy at a time spans the group; products of strategies (e.g.
-dp x tp) are rejected with a configuration error rather than half-supported.  The reference is a
+for context parallelism).  One strategy spans the group, with one product: data parallelism over replicas of a
+tensor-parallel model (``dp x tp``, ranks ``[d * tp, (d + 1) * tp)`` forming replica ``d``);
+other products are rejected with a configuration error rather than half-supported.  The reference is a
 single process (no parallelism of any kind in its sources).
 """
 from __future__ import annotations
@@ -49,6 +50,9 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
     active = [k for k in ("dp", "tp", "pp", "ep", "cp") if getattr(parallel, k) > 1]
     if parallel.ep > 1 and parallel.dp == parallel.ep:
         active = [k for k in active if k != "dp"]    # the expert group is the data group
+    if active == ["dp", "tp"]:
+        return _build_dp_tp(cfg, parallel, device, train_cfg or TrainConfig(), group, world, rank,
+                            seed, dtype, recompute)
     if len(active) > 1:
         raise ConfigError.conflict(active[0], active[1],
                                    "one parallelism strategy spans the process group at a time")
@@ -125,3 +129,35 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
     def feed_cp(ids, targets):
         return tr.train_step(cp.shard(ids), cp.shard(targets))
     return ParallelRun("cp", tr, model, rank, world, feed_cp)
+
+
+def _build_dp_tp(cfg, parallel, device, tc, group, world, rank, seed, dtype, recompute):
+    """Replicas of a tensor-parallel model: ``tp`` consecutive ranks share a model, ranks with the
+    same position in their replica average gradients."""
+    from ..parallel.tp import TensorParallel
+    from ..parallel.tp_model import TPDecoderLM, TPTrainer
+    dp, tp = parallel.dp, parallel.tp
+    if dp * tp != world:
+        raise ConfigError.invalid("dp*tp", dp * tp, f"must equal the size of the process group ({world})")
+    ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+    d_idx, t_idx = rank // tp, rank % tp
+    tp_group = dp_group = None
+    # every rank creates every group, in the same order
+    for d in range(dp):
+        g = dist.new_group([ranks[d * tp + t] for t in range(tp)])
+        if d == d_idx:
+            tp_group = g
+    for t in range(tp):
+        g = dist.new_group([ranks[d * tp + t] for d in range(dp)])
+        if t == t_idx:
+            dp_group = g
+    device = torch.device(device)
+    model = TPDecoderLM(cfg, TensorParallel(tp_group, device), device, seed=seed, dtype=dtype,
+                        recompute=recompute)
+    tr = TPTrainer(model, tc.adamw(), dp_group=dp_group)
+
+    def feed(ids, targets):
+        per = ids.shape[0] // dp
+        sl = slice(d_idx * per, (d_idx + 1) * per)
+        return tr.train_step(ids[sl].contiguous(), targets[sl].contiguous())
+    return ParallelRun("dp+tp", tr, model, rank, world, feed)

@@ -68,8 +68,33 @@ def test_every_strategy_through_the_launcher(kind):
         assert abs(got[-1] - ref[-1]) < 5e-3
 
 
+def _worker_2d(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    run = build_trainer(_cfg(), ParallelConfig(dp=2, tp=2), "cpu", _tc(), seed=3,
+                        dtype=torch.float32)
+    ids, tgt = _batch()
+    t = torch.tensor([float(run.step(ids, tgt)) for _ in range(4)])
+    dist.all_reduce(t)               # two replicas x two ranks, each reporting its replica's loss
+    out.put((rank, run.strategy, (t / world).tolist()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_data_parallel_replicas_of_a_tensor_parallel_model():
+    from mp_util import run_ranks
+    ids, tgt = _batch()
+    single = build_trainer(_cfg(), ParallelConfig(), "cpu", _tc(), seed=3, dtype=torch.float32)
+    ref = [float(single.step(ids, tgt)) for _ in range(4)]
+    res = run_ranks(_worker_2d, 4, (), results=4)
+    for _, strategy, got in res:
+        assert strategy == "dp+tp"
+        assert abs(got[0] - ref[0]) < 1e-4 and abs(got[-1] - ref[-1]) < 5e-3, (got, ref)
+
+
 def test_launcher_rejects_products_and_wrong_sizes():
     with pytest.raises(Exception):
-        build_trainer(_cfg(), ParallelConfig(dp=2, tp=2), "cpu")
+        build_trainer(_cfg(), ParallelConfig(pp=2, tp=2), "cpu")
     with pytest.raises(Exception):
         build_trainer(_cfg(), ParallelConfig(tp=2), "cpu")      # no process group of 2 here
