@@ -68,3 +68,24 @@ def test_flops_model_and_memory_stats_shape():
     assert f > 6 * n_matrix and f < 8 * n_matrix
     st = device_memory_stats("cpu")
     assert st.used_bytes == 0 and st.fragmentation_ratio() == 0.0
+
+
+def test_rank_prefixed_logging():
+    import io
+    import logging
+    from coeus_b200.utils.logging import get_logger, log_sink, setup_logging
+    buf = io.StringIO()
+    setup_logging(logging.INFO, rank=0, world=8, stream=buf)
+    get_logger("train").info("step %d", 3)
+    log_sink({"event": "TrainingEvent::Started"})
+    out = buf.getvalue()
+    assert "[rank 0/8] INFO coeus_b200.train: step 3" in out and "TrainingEvent::Started" in out
+    buf = io.StringIO()
+    setup_logging(logging.INFO, rank=5, world=8, stream=buf)       # other ranks: problems only
+    get_logger("train").info("quiet")
+    get_logger("train").warning("loud")
+    assert "quiet" not in buf.getvalue() and "[rank 5/8] WARNING" in buf.getvalue()
+    buf = io.StringIO()
+    setup_logging(logging.INFO, rank=5, world=8, all_ranks=True, stream=buf)
+    get_logger().info("everyone")
+    assert "everyone" in buf.getvalue()
