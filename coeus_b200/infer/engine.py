@@ -254,8 +254,10 @@ class InferenceEngine:
 
     def generate(self, ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
                  top_k: Optional[int] = None, top_p: Optional[float] = None, seed: int = 0,
-                 eos_id: Optional[int] = None) -> torch.Tensor:
-        """Returns ``[B, S + max_new_tokens]`` token ids (prompt included)."""
+                 eos_id: Optional[int] = None, seq_chunk: Optional[int] = None,
+                 token_chunk: Optional[int] = None) -> torch.Tensor:
+        """Returns ``[B, S + max_new_tokens]`` token ids (prompt included).  ``seq_chunk`` /
+        ``token_chunk`` bound the memory of the prompt pass (see :meth:`prefill`)."""
         if ids.dim() == 1:
             ids = ids[None]
         B, S = ids.shape
@@ -271,7 +273,7 @@ class InferenceEngine:
         if max_new_tokens == 0:
             return out
         t0 = time.perf_counter()
-        logits = self.prefill(ids, total)
+        logits = self.prefill(ids, total, seq_chunk=seq_chunk, token_chunk=token_chunk)
         if ids.is_cuda:
             torch.cuda.synchronize(ids.device)
         t1 = time.perf_counter()
