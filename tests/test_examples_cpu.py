@@ -59,3 +59,14 @@ def test_wordpiece_example():
 
 def test_serve_completions_dry_run():
     assert _load("serve_completions").main(["--device", "cpu", "--dry-run"]) == 0
+
+
+def test_serving_benchmark_runs_small():
+    spec = importlib.util.spec_from_file_location(
+        "bench_serving", os.path.join(os.path.dirname(ROOT), "benchmarks", "serving.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    r = mod.main(["--device", "cpu", "--requests", "5", "--max-seqs", "2", "--hidden", "64",
+                  "--layers", "2", "--heads", "2", "--prompt-max", "24", "--new-max", "6"])
+    assert r["generated_tokens"] > 0 and r["batched_tokens_per_s"] > 0
+    assert r["latency_s"]["p50"] <= r["latency_s"]["max"]
