@@ -17,7 +17,8 @@ from typing import BinaryIO, List, Optional, Sequence, Union
 
 import torch
 
-from ...core.model import (BasicGenerationConfig, BatchedModel, GenerativeModel, ModelBuilder)
+from ...core.model import (BasicGenerationConfig, BatchedModel, GenerativeModel, ModelBuilder,
+                           QuantizableModel)
 from ...core.plugin import ModelBuilderPlugin, PluginCapabilities
 from ...core.serialization import (ModelMetadata, ModelSerializable, read_rustllm_stream,
                                    write_rustllm_stream)
@@ -38,7 +39,7 @@ def _default_device(device: str = "auto") -> torch.device:
 
 from . import transformer_math as math  # noqa: E402  (the plugin's `mod math`)
 
-class TransformerModel(GenerativeModel, BatchedModel, ModelSerializable):
+class TransformerModel(GenerativeModel, BatchedModel, ModelSerializable, QuantizableModel):
     def __init__(self, config: Union[Transformer250MConfig, DecoderConfig], lm: DecoderLM,
                  tail: Optional[torch.Tensor] = None, init: str = "reference") -> None:
         self._config = config
@@ -46,6 +47,7 @@ class TransformerModel(GenerativeModel, BatchedModel, ModelSerializable):
         self._tail = tail
         self._init = init
         self._engine = None
+        self._quant = None
 
     # ---- Model / ForwardModel
     def config(self):
@@ -56,6 +58,19 @@ class TransformerModel(GenerativeModel, BatchedModel, ModelSerializable):
 
     def decoder_config(self) -> DecoderConfig:
         return self.lm.cfg
+
+    # ---- QuantizableModel (src/core/model.rs:191-200)
+    def quantize(self, config=None) -> None:
+        """Weight-only quantisation in place (see :mod:`coeus_b200.models.quant`); the codes and
+        scales stay available as ``quantized_tensors``."""
+        from ...models.quant import QuantConfig, quantize_model_
+        cfg = config or QuantConfig()
+        self.quantized_tensors = quantize_model_(self.lm, cfg)
+        self._quant = cfg
+        self._engine = None
+
+    def is_quantized(self) -> bool:
+        return self._quant is not None
 
     def num_parameters(self) -> int:
         return reference_buffer_len(self.lm.cfg)

@@ -302,3 +302,38 @@ def test_trainer_evaluate_reports_loss_and_perplexity():
     for _ in range(30):
         tr.train_step(*data[0])
     assert tr.evaluate(data[:1])["loss"] < ev["loss"] - 0.5
+
+
+def test_weight_only_quantisation():
+    import torch
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.quant import QuantConfig, dequantize_matrix, quantize_matrix
+    from coeus_b200.prelude import TransformerModelPlugin
+    torch.manual_seed(0)
+    w = torch.randn(64, 48) * 0.02
+    for bits, group in ((8, 0), (4, 16), (8, 20)):
+        codes, scales = quantize_matrix(w, bits, group)
+        assert codes.dtype == torch.int8 and int(codes.abs().max()) <= 2 ** (bits - 1) - 1
+        back = dequantize_matrix(codes, scales, group)
+        # round to nearest: at most half a step per element
+        g = 64 if group == 0 else group
+        step = scales[torch.arange(64) // g]
+        assert bool(((back - w).abs() <= 0.5 * step + 1e-9).all())
+        # a matrix on the grid is a fixed point
+        c2, s2 = quantize_matrix(back, bits, group)
+        assert torch.allclose(dequantize_matrix(c2, s2, group), back, atol=1e-8)
+    cfg = DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16)
+    model = TransformerModelPlugin().create_builder(device="cpu", init="normal").build(cfg)
+    ids = [1, 5, 9, 33]
+    before = torch.tensor(model.forward(ids))
+    assert not model.is_quantized()
+    model.quantize(QuantConfig(bits=8))
+    assert model.is_quantized()
+    after = torch.tensor(model.forward(ids))
+    assert (before - after).abs().max() < 0.02 * before.abs().max() + 1e-3
+    names = set(model.quantized_tensors)
+    assert "layers.0.attn.qkv_weights" in names and "token_embed" not in names
+    assert all(c.dtype == torch.int8 for c, _ in model.quantized_tensors.values())
+    with pytest.raises(Exception):
+        model.quantize(QuantConfig(bits=1))
