@@ -15,6 +15,7 @@ import time
 from concurrent.futures import Future
 from typing import Dict, List, Optional
 
+from ..core.traits import HealthCheck, Metrics
 from ..foundation.error import ProcessingError
 from ..infer.engine import InferenceEngine
 from ..infer.scheduler import ContinuousBatcher
@@ -34,8 +35,9 @@ except ImportError:      # ServingLoop works without the HTTP stack
     CompletionRequest = None
 
 
-class ServingLoop:
-    """Owns the batcher; all model work happens on its thread."""
+class ServingLoop(Metrics, HealthCheck):
+    """Owns the batcher; all model work happens on its thread.  Implements the reference's
+    ``Metrics`` and ``HealthCheck`` traits (src/core/traits.rs:197-221)."""
 
     def __init__(self, model, max_seqs: int = 16, max_len: Optional[int] = None,
                  token_chunk: Optional[int] = None, idle_sleep_s: float = 0.002) -> None:
@@ -63,6 +65,28 @@ class ServingLoop:
 
     def healthy(self) -> bool:
         return self._thread.is_alive() and not self._stop.is_set()
+
+    def id(self) -> str:
+        return "serving-loop"
+
+    def health(self):
+        from ..utils.metrics import Health
+        return Health(self.healthy(), {"active": len(self.batcher.active),
+                                       "waiting": len(self.batcher.waiting),
+                                       "kv_pages_in_use": self.engine.cache.pages_in_use()})
+
+    def metrics(self):
+        from ..utils.metrics import Metric
+        c = self.counters
+        done = max(1, c["completed"])
+        return [Metric("requests", c["requests"]), Metric("completed", c["completed"]),
+                Metric("failed", c["failed"]), Metric("generated_tokens", c["generated_tokens"]),
+                Metric("mean_latency_s", c["latency_s_sum"] / done, "s"),
+                Metric("decode_steps", self.batcher.stats["steps"])]
+
+    def reset_metrics(self) -> None:
+        for k in self.counters:
+            self.counters[k] = 0.0 if k == "latency_s_sum" else 0
 
     def close(self) -> None:
         self._stop.set()

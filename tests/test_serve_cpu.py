@@ -39,6 +39,9 @@ def test_serving_loop_futures(model):
         with pytest.raises(Exception):
             bad.result(timeout=60)
         assert loop.healthy() and loop.counters["completed"] == 4 and loop.counters["failed"] == 1
+        assert loop.health().healthy and loop.health().details["kv_pages_in_use"] == 0
+        ms = {m.name: m.value for m in loop.metrics()}
+        assert ms["completed"] == 4 and ms["generated_tokens"] == 20 and ms["mean_latency_s"] > 0
     finally:
         loop.close()
     assert not loop.healthy()
