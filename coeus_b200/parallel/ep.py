@@ -345,12 +345,13 @@ class ExpertParallelTrainer:
     (their gradients are complete once the exchanged rows have been processed), all other
     gradients are summed over the group while backward is still running."""
 
-    def __init__(self, model, cfg=None, overlap: bool = True) -> None:
+    def __init__(self, model, cfg=None, overlap: bool = True, schedule=None) -> None:
         """``overlap=False`` runs the dense all-reduces after the backward pass instead of
         concurrently with it (no collective kernel then shares the SMs with expert GEMMs that
         wait on peers)."""
         from ..optim.adamw import AdamW
         self.overlap = overlap
+        self.schedule = schedule          # object with at(step) -> learning rate
         from ..train.trainer import TrainConfig
         self.model, self.cfg = model, cfg or TrainConfig()
         self.epx: ExpertParallel = model.epx
@@ -410,6 +411,8 @@ class ExpertParallelTrainer:
     def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         m, ep = self.model, self.epx.ep
         T = ids.numel()
+        if self.schedule is not None:
+            self.opt.set_learning_rate(self.schedule.at(self.step_index))
         m.zero_grad()
         loss = m.forward_loss(ids, targets, grad_scale=1.0 / (T * ep))
         m.backward(on_layer_done=self._on_layer_done)

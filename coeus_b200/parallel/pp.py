@@ -134,9 +134,10 @@ class PipelineStage:
     """One rank's share of a pipelined decoder plus the 1F1B step loop."""
 
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16, train_cfg=None) -> None:
+                 dtype: torch.dtype = torch.bfloat16, train_cfg=None, schedule=None) -> None:
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
+        self.schedule = schedule          # object with at(step) -> learning rate
         self.group = group
         self.stage = dist.get_rank(group) if group is not None else 0
         self.stages = dist.get_world_size(group) if group is not None else 1
@@ -238,6 +239,8 @@ class PipelineStage:
         for c in chans.values():
             c.drain()
         m._ws_tag = ""
+        if self.schedule is not None:
+            self.opt.set_learning_rate(self.schedule.at(self.step_index))
         self.opt.step(m.p32, m.g32, m.p16, 1.0)
         self.step_index += 1
         return loss_sum
@@ -255,9 +258,11 @@ class InterleavedPipelineStage:
     of another kind.  On GPUs receives are posted when needed (see ``_Channel``)."""
 
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, chunks: int = 2,
-                 seed: int = 0, dtype: torch.dtype = torch.bfloat16, train_cfg=None) -> None:
+                 seed: int = 0, dtype: torch.dtype = torch.bfloat16, train_cfg=None,
+                 schedule=None) -> None:
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
+        self.schedule = schedule
         self.group = group
         self.stage = dist.get_rank(group)
         self.stages = dist.get_world_size(group)
@@ -371,6 +376,8 @@ class InterleavedPipelineStage:
             c_.drain()
         for m, opt in zip(self.models, self.opts):
             m._ws_tag = ""
+            if self.schedule is not None:
+                opt.set_learning_rate(self.schedule.at(self.step_index))
             opt.step(m.p32, m.g32, m.p16, 1.0)
         self.step_index += 1
         return loss_sum

@@ -374,7 +374,7 @@ class TPTrainer:
     """Training step of a tensor-parallel model: every rank applies AdamW to its own shards (the
     replicated tensors receive identical summed gradients, so they stay identical)."""
 
-    def __init__(self, model: TPDecoderLM, opt_cfg=None, dp_group=None) -> None:
+    def __init__(self, model: TPDecoderLM, opt_cfg=None, dp_group=None, schedule=None) -> None:
         """``dp_group``: ranks that hold the SAME shards in other tensor-parallel groups (data
         parallelism across replicas of the tensor-parallel model); their gradients are averaged
         with one all-reduce of the flat local gradient buffer before the optimizer step."""
@@ -382,6 +382,7 @@ class TPTrainer:
         self.model = model
         self.opt = AdamW(opt_cfg or AdamWConfig(), 0, model.n_flat, model.decay_end, model.device)
         self.step_index = 0
+        self.schedule = schedule          # object with at(step) -> learning rate
         self.dp_group = dp_group
         self.dp = dist.get_world_size(dp_group) if dp_group is not None else 1
         if self.dp > 1:      # replicas start from the same weights
@@ -390,6 +391,8 @@ class TPTrainer:
 
     def train_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         m = self.model
+        if self.schedule is not None:
+            self.opt.set_learning_rate(self.schedule.at(self.step_index))
         m.zero_grad()
         loss = m.forward_loss(ids, targets)
         m.backward()

@@ -43,7 +43,9 @@ class ParallelRun:
 def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
                   train_cfg: Optional[TrainConfig] = None, group=None, micro_batches: int = 1,
                   seed: int = 0, dtype: torch.dtype = torch.bfloat16,
-                  recompute: bool = False) -> ParallelRun:
+                  recompute: bool = False, schedule=None) -> ParallelRun:
+    """``schedule`` (an object with ``at(step) -> lr``, :mod:`coeus_b200.optim.lr`) drives the
+    learning rate of whichever trainer is built."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     parallel.validate()
@@ -52,7 +54,7 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
         active = [k for k in active if k != "dp"]    # the expert group is the data group
     if active == ["dp", "tp"]:
         return _build_dp_tp(cfg, parallel, device, train_cfg or TrainConfig(), group, world, rank,
-                            seed, dtype, recompute)
+                            seed, dtype, recompute, schedule)
     if len(active) > 1:
         raise ConfigError.conflict(active[0], active[1],
                                    "one parallelism strategy spans the process group at a time")
@@ -68,14 +70,15 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
 
     if strategy == "single":
         model = DecoderLM(cfg, device, seed=seed, dtype=dtype, recompute=recompute)
-        tr = Trainer(model, tc)
+        tr = Trainer(model, tc, schedule=schedule)
         return ParallelRun(strategy, tr, model, rank, world, tr.train_step)
 
     if strategy == "dp":
         from ..parallel.zero import ShardedDataParallel
         backend = "collective" if cpu else parallel.dp_backend
         model = DecoderLM(cfg, device, seed=seed, dtype=dtype, recompute=recompute)
-        tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend))
+        tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend),
+                     schedule=schedule)
 
         def feed(ids, targets):
             per = ids.shape[0] // world
@@ -88,12 +91,13 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
         from ..parallel.tp_model import TPDecoderLM, TPTrainer
         tp = TensorParallel(group, device)
         model = TPDecoderLM(cfg, tp, device, seed=seed, dtype=dtype, recompute=recompute)
-        tr = TPTrainer(model, tc.adamw())
+        tr = TPTrainer(model, tc.adamw(), schedule=schedule)
         return ParallelRun(strategy, tr, model, rank, world, tr.train_step)
 
     if strategy == "pp":
         from ..parallel.pp import PipelineStage
-        st = PipelineStage(cfg, group, device, micro_batches, seed=seed, dtype=dtype, train_cfg=tc)
+        st = PipelineStage(cfg, group, device, micro_batches, seed=seed, dtype=dtype, train_cfg=tc,
+                           schedule=schedule)
 
         def feed(ids, targets):
             M = micro_batches
@@ -105,7 +109,7 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
         from ..parallel.ep import ExpertParallel, ExpertParallelTrainer
         epx = ExpertParallel(group, device)
         model = DecoderLM(cfg, device, seed=seed, dtype=dtype, epx=epx, recompute=recompute)
-        tr = ExpertParallelTrainer(model, tc)
+        tr = ExpertParallelTrainer(model, tc, schedule=schedule)
 
         def feed(ids, targets):
             per = ids.shape[0] // world
@@ -124,14 +128,15 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
         cp = ContextParallel(group, device)
     model = DecoderLM(cfg, device, seed=seed, dtype=dtype, cp=cp, recompute=recompute)
     backend = "collective" if cpu else parallel.dp_backend
-    tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend))
+    tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend),
+                 schedule=schedule)
 
     def feed_cp(ids, targets):
         return tr.train_step(cp.shard(ids), cp.shard(targets))
     return ParallelRun("cp", tr, model, rank, world, feed_cp)
 
 
-def _build_dp_tp(cfg, parallel, device, tc, group, world, rank, seed, dtype, recompute):
+def _build_dp_tp(cfg, parallel, device, tc, group, world, rank, seed, dtype, recompute, schedule):
     """Replicas of a tensor-parallel model: ``tp`` consecutive ranks share a model, ranks with the
     same position in their replica average gradients."""
     from ..parallel.tp import TensorParallel
@@ -154,7 +159,7 @@ def _build_dp_tp(cfg, parallel, device, tc, group, world, rank, seed, dtype, rec
     device = torch.device(device)
     model = TPDecoderLM(cfg, TensorParallel(tp_group, device), device, seed=seed, dtype=dtype,
                         recompute=recompute)
-    tr = TPTrainer(model, tc.adamw(), dp_group=dp_group)
+    tr = TPTrainer(model, tc.adamw(), dp_group=dp_group, schedule=schedule)
 
     def feed(ids, targets):
         per = ids.shape[0] // dp

@@ -36,10 +36,14 @@ def _worker(rank, world, port, kind, out):
     par = ParallelConfig(**{kind: world}) if kind != "ulysses" else ParallelConfig(cp=world, ulysses=True)
     if kind == "ep":
         par = ParallelConfig(dp=world, ep=world)
+    from coeus_b200.optim.lr import Constant
     run = build_trainer(_cfg(moe=(kind == "ep")), par, "cpu", _tc(), micro_batches=2, seed=3,
-                        dtype=torch.float32)
+                        dtype=torch.float32, schedule=Constant(0.05))
     ids, tgt = _batch()
     losses = [float(run.step(ids, tgt)) for _ in range(4)]
+    opt = run.trainer.opt
+    assert abs((opt.learning_rate() if hasattr(opt, "learning_rate") else
+                run.trainer.dp.opt_cfg.lr) - 0.05) < 1e-12
     t = torch.tensor(losses)
     if kind in ("dp", "ep", "cp", "ulysses"):       # each rank reports the loss of its own part
         dist.all_reduce(t)
