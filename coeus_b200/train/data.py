@@ -27,6 +27,22 @@ class TokenDataset:
                                                         batch, prefetch, shuffle, seed, drop_last)
         self._buf = np.empty((batch, seq_len + 1), dtype=np.int64)
 
+    # ---- sources
+    @classmethod
+    def from_binary(cls, path: str, seq_len: int, batch: int, dtype=np.uint16, **kw
+                    ) -> "TokenDataset":
+        """A flat file of token ids (``uint16`` / ``uint32`` / ``int32``), memory-mapped while it
+        is converted; the usual layout of pre-tokenised corpora."""
+        return cls(np.memmap(path, dtype=dtype, mode="r"), seq_len, batch, **kw)
+
+    @classmethod
+    def from_text_files(cls, paths, tokenizer, seq_len: int, batch: int,
+                        eos_id: Optional[int] = None, **kw) -> "TokenDataset":
+        """Tokenise text files line by line (``tokenizer.encode_batch`` when the tokenizer has
+        it -- the native tokenizers encode a batch of lines on a thread pool -- else
+        ``encode``) into one stream, ``eos_id`` after every line when given."""
+        return cls(tokenize_files(paths, tokenizer, eos_id), seq_len, batch, **kw)
+
     def num_windows(self) -> int:
         return self._loader.num_windows()
 
@@ -54,6 +70,48 @@ class TokenDataset:
                 continue
             t = torch.from_numpy(self._buf[:n].copy())
             yield t[:, :-1].contiguous(), t[:, 1:].contiguous()
+
+
+def tokenize_files(paths, tokenizer, eos_id: Optional[int] = None, lines_per_call: int = 4096
+                   ) -> np.ndarray:
+    """All lines of ``paths`` as one ``int32`` token stream."""
+    if isinstance(paths, (str, bytes)):
+        paths = [paths]
+    chunks = []
+
+    def flush(lines):
+        if not lines:
+            return
+        if hasattr(tokenizer, "encode_batch"):
+            rows = tokenizer.encode_batch(lines)
+        else:
+            rows = [tokenizer.encode(t) for t in lines]
+        for r in rows:
+            chunks.append(np.asarray(r, dtype=np.int32).reshape(-1))
+            if eos_id is not None:
+                chunks.append(np.array([eos_id], dtype=np.int32))
+
+    for path in paths:
+        pending = []
+        with open(path, "r", encoding="utf-8", errors="replace") as f:
+            for line in f:
+                line = line.rstrip("\n")
+                if not line:
+                    continue
+                pending.append(line)
+                if len(pending) >= lines_per_call:
+                    flush(pending)
+                    pending = []
+        flush(pending)
+    return np.concatenate(chunks) if chunks else np.zeros(0, dtype=np.int32)
+
+
+def save_tokens(path: str, tokens, dtype=np.uint16) -> None:
+    """Write a token stream as the flat binary file :meth:`TokenDataset.from_binary` reads."""
+    arr = np.asarray(tokens)
+    if arr.size and int(arr.max()) > np.iinfo(dtype).max:
+        raise ValueError(f"token id {int(arr.max())} does not fit {np.dtype(dtype).name}")
+    arr.astype(dtype).tofile(path)
 
 
 class DevicePrefetcher:

@@ -1,5 +1,6 @@
 """Token dataset over the native batch loader and the prefetcher (CPU path)."""
 import numpy as np
+import pytest
 import torch
 
 from coeus_b200.train.data import DevicePrefetcher, TokenDataset
@@ -43,3 +44,32 @@ def test_prefetcher_passes_batches_through_on_cpu():
     want = [b[0] for b in TokenDataset(toks, 9, 2)]
     got = [b[0] for b in DevicePrefetcher(TokenDataset(toks, 9, 2), "cpu")]
     assert len(want) == len(got) and all(torch.equal(a, b) for a, b in zip(want, got))
+
+
+def test_dataset_from_text_files_and_binary(tmp_path):
+    import numpy as np
+    from coeus_b200.prelude import BpeTokenizerPlugin
+    from coeus_b200.train.data import TokenDataset, save_tokens, tokenize_files
+    tok = BpeTokenizerPlugin().create_tokenizer()
+    lines = ["the cat sat on the mat", "", "the dog sat on the log", "a cat and a dog"] * 20
+    tok.train([l for l in lines if l], 30)
+    a, b = tmp_path / "a.txt", tmp_path / "b.txt"
+    a.write_text("\n".join(lines[:40]) + "\n")
+    b.write_text("\n".join(lines[40:]))
+    stream = tokenize_files([str(a), str(b)], tok, eos_id=3)
+    want = []
+    for l in lines:
+        if l:
+            want += [int(t) for t in tok.encode(l)] + [3]
+    assert stream.dtype == np.int32 and stream.tolist() == want
+    ds = TokenDataset.from_text_files([str(a), str(b)], tok, seq_len=16, batch=4, eos_id=3)
+    ids, tgt = next(iter(ds))
+    assert ids.shape == (4, 16) and torch.equal(ids[:, 1:], tgt[:, :-1])
+    assert ids[0].tolist() == want[:16]
+    path = tmp_path / "tokens.bin"
+    save_tokens(str(path), stream)
+    ds2 = TokenDataset.from_binary(str(path), seq_len=16, batch=4)
+    ids2, _ = next(iter(ds2))
+    assert torch.equal(ids, ids2) and ds2.num_windows() == ds.num_windows()
+    with pytest.raises(ValueError):
+        save_tokens(str(path), [70000], dtype=np.uint16)
