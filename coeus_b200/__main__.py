@@ -1,0 +1,259 @@
+"""Command line: ``python -m coeus_b200 <command> [config files] [--key=value ...]``.
+
+Commands
+    train      build a model and a trainer from the layered configuration and train it
+    generate   load a model file and continue a prompt
+    serve      load a model file (or build a random one) and serve completions over HTTP
+    info       print the resolved configuration and the parameter count
+
+Configuration comes, lowest priority first, from the built-in defaults, the given ``.yaml`` /
+``.json`` files, ``COEUS_*`` environment variables (``COEUS_TRAIN__LR=1e-4`` sets ``train.lr``)
+and ``--key=value`` arguments (``--train.lr=1e-4``).  Under ``torchrun`` the process group is
+initialised from the environment (NCCL on GPUs, Gloo on CPU) and ``parallel.*`` selects the
+strategy.  The reference stops at a config store with no file, environment or command-line
+front end ("Implement configuration system" is unchecked in its CHECKLIST.md:64).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from typing import Any, Dict, List, Optional
+
+DEFAULTS: Dict[str, Any] = {
+    "model": {"preset": "", "hidden_dim": 256, "num_layers": 4, "num_heads": 4,
+              "intermediate_dim": 1024, "vocab_size": 512, "max_seq_len": 256, "use_bias": False,
+              "activation": "swiglu", "norm": "rmsnorm", "pos": "rope", "recompute": False},
+    "parallel": {"dp": 1, "tp": 1, "pp": 1, "ep": 1, "cp": 1, "ulysses": False,
+                 "micro_batches": 1},
+    "train": {"steps": 20, "batch": 4, "seq_len": 128, "lr": 3e-4, "warmup": 0, "grad_clip": 0.0,
+              "weight_decay": 0.01, "seed": 0, "log_every": 5, "checkpoint_dir": "",
+              "checkpoint_every": 0, "save": ""},
+    "data": {"files": "", "binary": "", "binary_dtype": "uint16"},
+    "device": "auto",
+}
+
+
+def _resolve(argv: List[str]):
+    from .core.config import ConfigStore
+    store = ConfigStore()
+    store.load_mapping(DEFAULTS)
+    rest = []
+    for a in argv:
+        if a.endswith((".yaml", ".yml", ".json")) and not a.startswith("--"):
+            store.load_file(a)
+        else:
+            rest.append(a)
+    store.load_env()
+    rest = store.load_args(rest)
+    return store, rest
+
+
+def _get(store, key: str):
+    v = store.get(key)
+    if v is None:
+        return None
+    for conv in (v.as_bool, v.as_integer, v.as_float, v.as_string):
+        try:
+            out = conv()
+        except Exception:
+            out = None
+        if out is not None:
+            return out
+    return None
+
+
+def _model_config(store):
+    from .models.config import DecoderConfig
+    preset = _get(store, "model.preset") or ""
+    if preset:
+        make = {"250m": DecoderConfig.transformer_250m, "1.3b": DecoderConfig.decoder_1p3b,
+                "moe": DecoderConfig.moe_8x}.get(str(preset).lower())
+        if make is None:
+            raise SystemExit(f"unknown model.preset '{preset}' (250m, 1.3b, moe)")
+        return make()
+    keys = ("hidden_dim", "num_layers", "num_heads", "intermediate_dim", "vocab_size",
+            "max_seq_len", "use_bias", "activation", "norm", "pos")
+    return DecoderConfig(**{k: _get(store, f"model.{k}") for k in keys})
+
+
+def _device(store) -> str:
+    import torch
+    d = _get(store, "device")
+    if d in (None, "auto"):
+        return "cuda" if torch.cuda.is_available() else "cpu"
+    return str(d)
+
+
+def _init_distributed(device: str):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world == 1:
+        return 0, 1, device
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if device.startswith("cuda"):
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        device = f"cuda:{local}"
+        dist.init_process_group("nccl", device_id=torch.device(device))
+    else:
+        dist.init_process_group("gloo")
+    return dist.get_rank(), world, device
+
+
+def cmd_train(store) -> dict:
+    import numpy as np
+    import torch
+
+    from .core.config import ParallelConfig
+    from .optim.lr import Constant, WarmupCosine
+    from .train.data import TokenDataset
+    from .train.launch import build_trainer
+    from .train.trainer import TrainConfig
+    from .utils.logging import setup_logging
+    device = _device(store)
+    rank, world, device = _init_distributed(device)
+    log = setup_logging(rank=rank, world=world)
+    cfg = _model_config(store)
+    par = ParallelConfig(**{k: _get(store, f"parallel.{k}") for k in ("dp", "tp", "pp", "ep", "cp")},
+                         ulysses=bool(_get(store, "parallel.ulysses")))
+    steps, B, S = (_get(store, f"train.{k}") for k in ("steps", "batch", "seq_len"))
+    lr, warm = _get(store, "train.lr"), _get(store, "train.warmup")
+    clip = _get(store, "train.grad_clip") or None
+    tc = TrainConfig(learning_rate=lr, weight_decay=_get(store, "train.weight_decay"),
+                     grad_clip=clip)
+    sched = WarmupCosine(lr, warm, steps, floor=0.1 * lr) if warm else Constant(lr)
+    dtype = torch.bfloat16 if device.startswith("cuda") else torch.float32
+    run = build_trainer(cfg, par, device, tc, micro_batches=_get(store, "parallel.micro_batches"),
+                        seed=_get(store, "train.seed"), dtype=dtype,
+                        recompute=bool(_get(store, "model.recompute")), schedule=sched)
+    # data: text files through a byte-level BPE tokenizer, a binary token file, or random ids
+    files, binary = _get(store, "data.files"), _get(store, "data.binary")
+    if binary:
+        ds = TokenDataset.from_binary(binary, S, B, dtype=np.dtype(_get(store, "data.binary_dtype")))
+    elif files:
+        from .prelude import BpeTokenizerPlugin
+        tok = BpeTokenizerPlugin().create_tokenizer()
+        paths = [p for p in str(files).split(",") if p]
+        with open(paths[0], encoding="utf-8", errors="replace") as f:
+            tok.train(f.read(1 << 20).splitlines(), max(0, cfg.vocab_size - 300))
+        ds = TokenDataset.from_text_files(paths, tok, S, B)
+    else:
+        g = np.random.default_rng(_get(store, "train.seed"))
+        ds = TokenDataset(g.integers(0, cfg.vocab_size, size=(steps + 1) * B * S + 1), S, B)
+    ckpt_dir, every = _get(store, "train.checkpoint_dir"), _get(store, "train.checkpoint_every")
+    losses, step, epoch = [], 0, 0
+    while step < steps:
+        ds.reset(epoch)
+        got = False
+        for ids, tgt in ds:
+            got = True
+            ids, tgt = ids.to(device), tgt.to(device)
+            loss = float(run.step(ids, tgt))
+            losses.append(loss)
+            step += 1
+            if step % max(1, _get(store, "train.log_every")) == 0:
+                log.info("step %d loss %.4f", step, loss)
+            if ckpt_dir and every and step % every == 0 and hasattr(run.trainer, "save_checkpoint"):
+                run.trainer.save_checkpoint(ckpt_dir)
+            if step >= steps:
+                break
+        if not got:
+            raise SystemExit("the data source yields no full batch")
+        epoch += 1
+    save = _get(store, "train.save")
+    if save and run.strategy in ("single", "dp", "cp"):
+        dp = getattr(run.trainer, "dp", None)
+        if dp is not None:
+            run.model.p32.copy_(dp.gather_master())
+        if rank == 0:
+            from .checkpoint.formats import save_model
+            save_model(run.model, save)
+    elif save and run.strategy in ("tp", "dp+tp"):
+        run.model.save(save)
+    out = {"strategy": run.strategy, "steps": step, "first_loss": losses[0],
+           "last_loss": losses[-1], "world": world}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def cmd_generate(store, rest: List[str]) -> dict:
+    import torch
+
+    from .checkpoint.formats import load_model
+    from .infer.engine import InferenceEngine
+    device = _device(store)
+    weights = _get(store, "weights")
+    if not weights:
+        raise SystemExit("generate needs --weights=<file.safetensors|.gguf|.rustllm>")
+    model, _ = load_model(str(weights), device=device)
+    ids_arg = _get(store, "prompt_ids")
+    if ids_arg is None:
+        raise SystemExit("generate needs --prompt_ids=1,2,3")
+    ids = [int(t) for t in str(ids_arg).split(",")]
+    n = int(_get(store, "max_tokens") or 16)
+    out = InferenceEngine(model, max_batch=1).generate(
+        torch.tensor(ids, device=device)[None], n,
+        temperature=float(_get(store, "temperature") or 0.0))
+    res = {"prompt_ids": ids, "token_ids": out[0, len(ids):].tolist()}
+    print(json.dumps(res))
+    return res
+
+
+def cmd_serve(store) -> int:
+    import uvicorn
+
+    from .checkpoint.formats import load_model
+    from .models.decoder import DecoderLM
+    from .serve import create_app
+    import torch
+    device = _device(store)
+    weights = _get(store, "weights")
+    if weights:
+        model, _ = load_model(str(weights), device=device)
+    else:
+        dtype = torch.bfloat16 if device.startswith("cuda") else torch.float32
+        model = DecoderLM(_model_config(store), device, dtype=dtype, training=False)
+    app = create_app(model, max_seqs=int(_get(store, "max_seqs") or 16),
+                     max_len=model.cfg.max_seq_len)
+    uvicorn.run(app, host=str(_get(store, "host") or "127.0.0.1"),
+                port=int(_get(store, "port") or 8000))
+    return 0
+
+
+def cmd_info(store) -> dict:
+    from .models.decoder import ParamLayout
+    cfg = _model_config(store)
+    out = {"model": cfg.to_dict(), "parameters": ParamLayout(cfg).num_parameters(),
+           "config": {k: _get(store, k) for k in sorted(store.keys())}}
+    print(json.dumps(out))
+    return out
+
+
+def main(argv: Optional[List[str]] = None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] in ("-h", "--help"):
+        print(__doc__)
+        return 0
+    cmd, store_rest = argv[0], _resolve(argv[1:])
+    store, rest = store_rest
+    if cmd == "train":
+        return cmd_train(store)
+    if cmd == "generate":
+        return cmd_generate(store, rest)
+    if cmd == "serve":
+        return cmd_serve(store)
+    if cmd == "info":
+        return cmd_info(store)
+    raise SystemExit(f"unknown command '{cmd}' (train, generate, serve, info)")
+
+
+if __name__ == "__main__":
+    r = main()
+    sys.exit(r if isinstance(r, int) else 0)
