@@ -249,14 +249,18 @@ class ParallelConfig:
     cp: int = 1
     sp: bool = True            # sequence-parallel activations inside a tensor-parallel group
     ulysses: bool = False      # context parallelism by head all-to-all instead of a K/V ring
-    zero_stage: int = 1
-    bucket_mb: int = 50
+    zero_stage: int = 2        # 0: replicated optimizer state (all-reduce comparator);
+                               # 1 / 2: optimizer state sharded, gradients reduce-scattered
     dp_backend: str = "p2p"    # "p2p" (fused kernel over NVLink peer memory) | "collective"
 
     def world_size(self) -> int:
         return self.dp * self.tp * self.pp * self.cp
 
     def validate(self, world: Optional[int] = None) -> None:
+        if self.zero_stage not in (0, 1, 2):
+            raise ConfigError.invalid("zero_stage", self.zero_stage,
+                                      "Stages 0 (replicated) and 1/2 (sharded state) are built; "
+                                      "parameter sharding (3) is not")
         for k in ("dp", "tp", "pp", "ep", "cp"):
             if getattr(self, k) < 1:
                 raise ConfigError.invalid(k, getattr(self, k), "Parallel degree must be >= 1")

@@ -74,11 +74,15 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
         return ParallelRun(strategy, tr, model, rank, world, tr.train_step)
 
     if strategy == "dp":
-        from ..parallel.zero import ShardedDataParallel
-        backend = "collective" if cpu else parallel.dp_backend
         model = DecoderLM(cfg, device, seed=seed, dtype=dtype, recompute=recompute)
-        tr = Trainer(model, tc, dp=ShardedDataParallel(group, device, backend=backend),
-                     schedule=schedule)
+        if parallel.zero_stage == 0:
+            from ..parallel.dp import ReplicatedDataParallel
+            dp_obj = ReplicatedDataParallel(group, device)
+        else:
+            from ..parallel.zero import ShardedDataParallel
+            dp_obj = ShardedDataParallel(group, device,
+                                         backend="collective" if cpu else parallel.dp_backend)
+        tr = Trainer(model, tc, dp=dp_obj, schedule=schedule)
 
         def feed(ids, targets):
             per = ids.shape[0] // world

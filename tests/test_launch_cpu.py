@@ -33,7 +33,12 @@ def _worker(rank, world, port, kind, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    par = ParallelConfig(**{kind: world}) if kind != "ulysses" else ParallelConfig(cp=world, ulysses=True)
+    if kind == "dp0":
+        par = ParallelConfig(dp=world, zero_stage=0)
+    elif kind == "ulysses":
+        par = ParallelConfig(cp=world, ulysses=True)
+    else:
+        par = ParallelConfig(**{kind: world})
     if kind == "ep":
         par = ParallelConfig(dp=world, ep=world)
     from coeus_b200.optim.lr import Constant
@@ -42,10 +47,11 @@ def _worker(rank, world, port, kind, out):
     ids, tgt = _batch()
     losses = [float(run.step(ids, tgt)) for _ in range(4)]
     opt = run.trainer.opt
-    assert abs((opt.learning_rate() if hasattr(opt, "learning_rate") else
-                run.trainer.dp.opt_cfg.lr) - 0.05) < 1e-12
+    dp = getattr(run.trainer, "dp", None)
+    lr_now = dp.opt_cfg.lr if dp is not None else opt.learning_rate()
+    assert abs(lr_now - 0.05) < 1e-12
     t = torch.tensor(losses)
-    if kind in ("dp", "ep", "cp", "ulysses"):       # each rank reports the loss of its own part
+    if kind in ("dp", "dp0", "ep", "cp", "ulysses"):       # each rank reports the loss of its own part
         dist.all_reduce(t)
         t /= world
     out.put((rank, run.strategy, t.tolist()))
@@ -53,7 +59,7 @@ def _worker(rank, world, port, kind, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind", ["dp", "tp", "pp", "ep", "cp", "ulysses"])
+@pytest.mark.parametrize("kind", ["dp", "dp0", "tp", "pp", "ep", "cp", "ulysses"])
 def test_every_strategy_through_the_launcher(kind):
     from mp_util import run_ranks
     ids, tgt = _batch()
@@ -62,7 +68,7 @@ def test_every_strategy_through_the_launcher(kind):
     assert single.strategy == "single"
     ref = [float(single.step(ids, tgt)) for _ in range(4)]
     res = {r[0]: r for r in run_ranks(_worker, 2, (kind,), results=2)}
-    want = "cp" if kind == "ulysses" else kind
+    want = {"ulysses": "cp", "dp0": "dp"}.get(kind, kind)
     assert res[0][1] == want
     got = res[1][2]          # rank 1 is the last pipeline stage; the others agree on all ranks
     tol = 2e-2 if kind == "ep" else 1e-4     # capacity slots differ between 1 and 2 ranks
@@ -102,3 +108,5 @@ def test_launcher_rejects_products_and_wrong_sizes():
         build_trainer(_cfg(), ParallelConfig(pp=2, tp=2), "cpu")
     with pytest.raises(Exception):
         build_trainer(_cfg(), ParallelConfig(tp=2), "cpu")      # no process group of 2 here
+    with pytest.raises(Exception):
+        build_trainer(_cfg(), ParallelConfig(zero_stage=3), "cpu")
