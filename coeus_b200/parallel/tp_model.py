@@ -384,8 +384,8 @@ class TPTrainer:
         self.step_index = 0
         self.schedule = schedule          # object with at(step) -> learning rate
         self.dp_group = dp_group
-        self.dp = dist.get_world_size(dp_group) if dp_group is not None else 1
-        if self.dp > 1:      # replicas start from the same weights
+        self.dp_degree = dist.get_world_size(dp_group) if dp_group is not None else 1
+        if self.dp_degree > 1:      # replicas start from the same weights
             dist.broadcast(model.p32, src=dist.get_global_rank(dp_group, 0), group=dp_group)
             model.p16.copy_(model.p32)
 
@@ -396,9 +396,9 @@ class TPTrainer:
         m.zero_grad()
         loss = m.forward_loss(ids, targets)
         m.backward()
-        if self.dp > 1:
+        if self.dp_degree > 1:
             dist.all_reduce(m.g32, group=self.dp_group)
-        self.opt.step(m.p32, m.g32, m.p16, 1.0 / self.dp)
+        self.opt.step(m.p32, m.g32, m.p16, 1.0 / self.dp_degree)
         self.step_index += 1
         return loss
 
