@@ -12,7 +12,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional
+from typing import Callable, Deque, Dict, List, Optional
 
 import torch
 
@@ -32,6 +32,12 @@ class Request:
     top_p: Optional[float] = None
     output: List[int] = field(default_factory=list)
     slot: int = -1
+    on_token: Optional[Callable[[int], None]] = None      # called with every new token
+
+    def push(self, tok: int) -> None:
+        self.output.append(tok)
+        if self.on_token is not None:
+            self.on_token(tok)
 
     @property
     def done(self) -> bool:
@@ -61,7 +67,8 @@ class ContinuousBatcher:
     # ------------------------------------------------------------------ API
     def submit(self, prompt, max_new_tokens: int, eos_id: Optional[int] = None,
                temperature: float = 0.0, top_k: Optional[int] = None,
-               top_p: Optional[float] = None) -> int:
+               top_p: Optional[float] = None,
+               on_token: Optional[Callable[[int], None]] = None) -> int:
         prompt = [int(t) for t in prompt]
         if not prompt:
             raise ProcessingError.invalid_input("empty prompt")
@@ -70,7 +77,8 @@ class ContinuousBatcher:
                                                  len(prompt) + max_new_tokens)
         rid = self._next_id
         self._next_id += 1
-        self.waiting.append(Request(rid, prompt, max_new_tokens, eos_id, temperature, top_k, top_p))
+        self.waiting.append(Request(rid, prompt, max_new_tokens, eos_id, temperature, top_k, top_p,
+                                    on_token=on_token))
         return rid
 
     def pending(self) -> int:
@@ -88,7 +96,7 @@ class ContinuousBatcher:
             ids = torch.tensor(r.prompt, dtype=torch.int64, device=self.device)
             logits = eng.prefill_slot(r.slot, ids, len(r.prompt) + r.max_new_tokens,
                                       token_chunk=self.token_chunk)
-            r.output.append(int(self._sample(logits[None], r)[0]))
+            r.push(int(self._sample(logits[None], r)[0]))
             self.stats["prefills"] += 1
             if r.done:
                 self._retire(r, finished)
@@ -107,7 +115,7 @@ class ContinuousBatcher:
             nxt = select(logits, 0.0, None, None, None).tolist() if greedy else None
             for i, r in enumerate(reqs):
                 tok = nxt[i] if greedy else int(self._sample(logits[i:i + 1], r)[0])
-                r.output.append(int(tok))
+                r.push(int(tok))
                 cache.set_length(r.slot, len(r.prompt) + len(r.output) - 1)
                 if r.done:
                     self._retire(r, finished)

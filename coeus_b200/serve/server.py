@@ -31,6 +31,7 @@ try:        # the request schema lives at module level so that FastAPI can resol
         top_k: Optional[int] = None
         top_p: Optional[float] = None
         eos_id: Optional[int] = None
+        stream: bool = False
 except ImportError:      # ServingLoop works without the HTTP stack
     CompletionRequest = None
 
@@ -56,7 +57,8 @@ class ServingLoop(Metrics, HealthCheck):
         self._thread.start()
 
     def submit(self, prompt: List[int], max_new_tokens: int, **sampling) -> Future:
-        """Thread-safe; the future resolves to the list of generated token ids."""
+        """Thread-safe; the future resolves to the list of generated token ids.  ``on_token``
+        (keyword) is called on the worker thread with every token as it is produced."""
         fut: Future = Future()
         with self._lock:
             self._inbox.append((prompt, max_new_tokens, sampling, fut, time.perf_counter()))
@@ -135,7 +137,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
     import asyncio
 
     from fastapi import FastAPI, HTTPException
-    from fastapi.responses import PlainTextResponse
+    from fastapi.responses import PlainTextResponse, StreamingResponse
 
     from contextlib import asynccontextmanager
 
@@ -149,6 +151,32 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
     app = FastAPI(title="coeus_b200", lifespan=lifespan)
     app.state.loop = loop
 
+    async def _stream(ids, max_tokens, sampling):
+        """Server-sent events: one ``data: {"token_id": ...}`` line per token, then
+        ``data: [DONE]``.  Tokens cross from the worker thread through the event loop's queue."""
+        import json as _json
+        aloop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        fut = loop.submit(ids, max_tokens,
+                          on_token=lambda t: aloop.call_soon_threadsafe(q.put_nowait, t),
+                          **sampling)
+        fut.add_done_callback(lambda f: aloop.call_soon_threadsafe(q.put_nowait, None))
+        decode = None
+        if tokenizer is not None:
+            decode = getattr(tokenizer, "decode_ids", None) or tokenizer.decode
+        while True:
+            tok = await asyncio.wait_for(q.get(), request_timeout_s)
+            if tok is None:
+                break
+            ev = {"token_id": tok}
+            if decode is not None:
+                ev["text"] = decode([tok])
+            yield f"data: {_json.dumps(ev)}\n\n"
+        err = fut.exception()
+        if err is not None:
+            yield f"data: {_json.dumps({'error': str(err)})}\n\n"
+        yield "data: [DONE]\n\n"
+
     @app.post("/v1/completions")
     async def completions(req: CompletionRequest):
         if req.prompt_ids is not None:
@@ -160,8 +188,12 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
         V = model.cfg.vocab_size
         if not ids or any(t < 0 or t >= V for t in ids):
             raise HTTPException(422, f"token ids must lie in [0, {V}) and the prompt be non-empty")
-        fut = loop.submit(ids, req.max_tokens, eos_id=req.eos_id, temperature=req.temperature,
-                          top_k=req.top_k, top_p=req.top_p)
+        sampling = dict(eos_id=req.eos_id, temperature=req.temperature, top_k=req.top_k,
+                        top_p=req.top_p)
+        if req.stream:
+            return StreamingResponse(_stream(ids, req.max_tokens, sampling),
+                                     media_type="text/event-stream")
+        fut = loop.submit(ids, req.max_tokens, **sampling)
         try:
             out = await asyncio.wait_for(asyncio.wrap_future(fut), request_timeout_s)
         except asyncio.TimeoutError:

@@ -69,5 +69,14 @@ def test_http_completions(model):
                            json={"prompt_ids": [999], "max_tokens": 2}).status_code == 422
         assert client.post("/v1/completions",
                            json={"prompt_ids": [1] * 95, "max_tokens": 9}).status_code == 422
+        # streaming: one event per token, in order, then the end marker
+        plain = client.post("/v1/completions", json={"prompt_ids": [4, 5, 6], "max_tokens": 5})
+        with client.stream("POST", "/v1/completions",
+                           json={"prompt_ids": [4, 5, 6], "max_tokens": 5, "stream": True}) as r:
+            assert r.status_code == 200
+            events = [l[6:] for l in r.iter_lines() if l.startswith("data: ")]
+        assert events[-1] == "[DONE]" and len(events) == 6
+        import json
+        assert [json.loads(e)["token_id"] for e in events[:-1]] == plain.json()["token_ids"]
         text = client.get("/metrics").text
-        assert "coeus_completed 6" in text and "coeus_kv_pages_in_use 0" in text
+        assert "coeus_completed 8" in text and "coeus_kv_pages_in_use 0" in text
