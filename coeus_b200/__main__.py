@@ -25,7 +25,7 @@ DEFAULTS: Dict[str, Any] = {
               "intermediate_dim": 1024, "vocab_size": 512, "max_seq_len": 256, "use_bias": False,
               "activation": "swiglu", "norm": "rmsnorm", "pos": "rope", "recompute": False},
     "parallel": {"dp": 1, "tp": 1, "pp": 1, "ep": 1, "cp": 1, "ulysses": False,
-                 "micro_batches": 1},
+                 "micro_batches": 1, "pp_chunks": 1, "zero_stage": 2},
     "train": {"steps": 20, "batch": 4, "seq_len": 128, "lr": 3e-4, "warmup": 0, "grad_clip": 0.0,
               "weight_decay": 0.01, "seed": 0, "log_every": 5, "checkpoint_dir": "",
               "checkpoint_every": 0, "save": ""},
@@ -116,7 +116,8 @@ def cmd_train(store) -> dict:
     rank, world, device = _init_distributed(device)
     log = setup_logging(rank=rank, world=world)
     cfg = _model_config(store)
-    par = ParallelConfig(**{k: _get(store, f"parallel.{k}") for k in ("dp", "tp", "pp", "ep", "cp")},
+    par = ParallelConfig(**{k: _get(store, f"parallel.{k}")
+                            for k in ("dp", "tp", "pp", "ep", "cp", "pp_chunks", "zero_stage")},
                          ulysses=bool(_get(store, "parallel.ulysses")))
     steps, B, S = (_get(store, f"train.{k}") for k in ("steps", "batch", "seq_len"))
     lr, warm = _get(store, "train.lr"), _get(store, "train.warmup")

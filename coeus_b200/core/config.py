@@ -247,6 +247,7 @@ class ParallelConfig:
     pp: int = 1
     ep: int = 1
     cp: int = 1
+    pp_chunks: int = 1         # > 1: interleaved 1F1B with this many model chunks per rank
     sp: bool = True            # sequence-parallel activations inside a tensor-parallel group
     ulysses: bool = False      # context parallelism by head all-to-all instead of a K/V ring
     zero_stage: int = 2        # 0: replicated optimizer state (all-reduce comparator);

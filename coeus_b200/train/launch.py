@@ -99,15 +99,21 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
         return ParallelRun(strategy, tr, model, rank, world, tr.train_step)
 
     if strategy == "pp":
-        from ..parallel.pp import PipelineStage
-        st = PipelineStage(cfg, group, device, micro_batches, seed=seed, dtype=dtype, train_cfg=tc,
-                           schedule=schedule)
+        from ..parallel.pp import InterleavedPipelineStage, PipelineStage
+        if parallel.pp_chunks > 1:
+            st = InterleavedPipelineStage(cfg, group, device, micro_batches,
+                                          chunks=parallel.pp_chunks, seed=seed, dtype=dtype,
+                                          train_cfg=tc, schedule=schedule)
+        else:
+            st = PipelineStage(cfg, group, device, micro_batches, seed=seed, dtype=dtype,
+                               train_cfg=tc, schedule=schedule)
 
         def feed(ids, targets):
             M = micro_batches
             b = ids.shape[0] // M
             return st.train_step(ids.reshape(M, b, -1), targets.reshape(M, b, -1))
-        return ParallelRun(strategy, st, st.model, rank, world, feed)
+        return ParallelRun(strategy, st, getattr(st, "model", None) or st.models[0], rank, world,
+                           feed)
 
     if strategy == "ep":
         from ..parallel.ep import ExpertParallel, ExpertParallelTrainer

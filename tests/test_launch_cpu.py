@@ -13,9 +13,9 @@ from coeus_b200.train.launch import build_trainer
 from coeus_b200.train.trainer import TrainConfig
 
 
-def _cfg(moe=False):
+def _cfg(moe=False, layers=2):
     kw = dict(num_experts=4, top_k=2, capacity_factor=4.0, aux_loss_coef=0.0) if moe else {}
-    return DecoderConfig(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64,
+    return DecoderConfig(hidden_dim=32, num_layers=layers, num_heads=2, intermediate_dim=64,
                          vocab_size=96, max_seq_len=16, use_bias=False, activation="swiglu",
                          norm="rmsnorm", pos="rope", **kw)
 
@@ -35,6 +35,8 @@ def _worker(rank, world, port, kind, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     if kind == "dp0":
         par = ParallelConfig(dp=world, zero_stage=0)
+    elif kind == "pp_interleaved":
+        par = ParallelConfig(pp=world, pp_chunks=2)
     elif kind == "ulysses":
         par = ParallelConfig(cp=world, ulysses=True)
     else:
@@ -42,11 +44,12 @@ def _worker(rank, world, port, kind, out):
     if kind == "ep":
         par = ParallelConfig(dp=world, ep=world)
     from coeus_b200.optim.lr import Constant
-    run = build_trainer(_cfg(moe=(kind == "ep")), par, "cpu", _tc(), micro_batches=2, seed=3,
+    run = build_trainer(_cfg(moe=(kind == "ep"), layers=4 if kind == "pp_interleaved" else 2),
+                        par, "cpu", _tc(), micro_batches=2, seed=3,
                         dtype=torch.float32, schedule=Constant(0.05))
     ids, tgt = _batch()
     losses = [float(run.step(ids, tgt)) for _ in range(4)]
-    opt = run.trainer.opt
+    opt = run.trainer.opt if hasattr(run.trainer, "opt") else run.trainer.opts[0]
     dp = getattr(run.trainer, "dp", None)
     lr_now = dp.opt_cfg.lr if dp is not None else opt.learning_rate()
     assert abs(lr_now - 0.05) < 1e-12
@@ -59,16 +62,16 @@ def _worker(rank, world, port, kind, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind", ["dp", "dp0", "tp", "pp", "ep", "cp", "ulysses"])
+@pytest.mark.parametrize("kind", ["dp", "dp0", "tp", "pp", "pp_interleaved", "ep", "cp", "ulysses"])
 def test_every_strategy_through_the_launcher(kind):
     from mp_util import run_ranks
     ids, tgt = _batch()
-    single = build_trainer(_cfg(moe=(kind == "ep")), ParallelConfig(), "cpu", _tc(), seed=3,
-                           dtype=torch.float32)
+    single = build_trainer(_cfg(moe=(kind == "ep"), layers=4 if kind == "pp_interleaved" else 2),
+                           ParallelConfig(), "cpu", _tc(), seed=3, dtype=torch.float32)
     assert single.strategy == "single"
     ref = [float(single.step(ids, tgt)) for _ in range(4)]
     res = {r[0]: r for r in run_ranks(_worker, 2, (kind,), results=2)}
-    want = {"ulysses": "cp", "dp0": "dp"}.get(kind, kind)
+    want = {"ulysses": "cp", "dp0": "dp", "pp_interleaved": "pp"}.get(kind, kind)
     assert res[0][1] == want
     got = res[1][2]          # rank 1 is the last pipeline stage; the others agree on all ranks
     tol = 2e-2 if kind == "ep" else 1e-4     # capacity slots differ between 1 and 2 ranks
