@@ -38,6 +38,9 @@ class AdamW:
         self.m = torch.zeros(n, dtype=torch.float32, device=device)
         self.v = torch.zeros(n, dtype=torch.float32, device=device)
         self.step_count = 0
+        # ``norm_hook(g32, sumsq)``: turns this rank's sum of squared gradients into the global one
+        # in place (tensor / pipeline / expert parallelism, where ranks hold different tensors)
+        self.norm_hook = None
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=device)
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=device)
@@ -72,6 +75,8 @@ class AdamW:
         """Global-norm clipping coefficient from this range's gradients (single rank)."""
         self.sumsq.zero_()
         E.sumsq_into(g32[self.start:self.end], self.sumsq)
+        if self.norm_hook is not None:      # model-parallel trainers complete the sum over ranks
+            self.norm_hook(g32, self.sumsq)
         E.clip_coef_from_sumsq(self.sumsq, grad_scale, self.cfg.grad_clip, self.clip_coef,
                                self.grad_norm)
 

@@ -367,6 +367,18 @@ class ExpertParallelTrainer:
         self._head, self._tail = (lo, d), (d, hi)
         self.step_index = 0
         self._stream = torch.cuda.Stream(model.device) if model.device.type == "cuda" else None
+        if self.epx.ep > 1:
+            # global gradient norm: the dense gradients are already summed over the group and equal
+            # on every rank, the expert gradients exist on one rank each
+            def norm_hook(g32, sumsq):
+                dense = torch.zeros_like(sumsq)
+                for lo_, hi_ in self.spans:
+                    if hi_ > lo_:
+                        E.sumsq_into(g32[lo_:hi_], dense)
+                experts = sumsq - dense
+                dist.all_reduce(experts, group=self.epx.group)
+                sumsq.copy_(experts + dense)
+            self.opt.norm_hook = norm_hook
 
     def _reduce(self, span: Tuple[int, int]) -> None:
         if self.epx.ep == 1 or span[1] <= span[0]:

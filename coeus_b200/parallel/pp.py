@@ -157,6 +157,8 @@ class PipelineStage:
             self.fwd_group = dist.new_group(ranks)
             self.bwd_group = dist.new_group(ranks)
             self._ranks = ranks
+            # global gradient norm: every stage holds its own tensors
+            self.opt.norm_hook = lambda g32, sumsq: dist.all_reduce(sumsq, group=self.group)
         self.step_index = 0
 
     def load_from_full(self, full: DecoderLM) -> None:
@@ -374,6 +376,14 @@ class InterleavedPipelineStage:
                     ch["sb" if s > 0 else "sbw"].send(dx)
         for c_ in ch.values():
             c_.drain()
+        if self.train_cfg.grad_clip is not None:
+            # one norm over all chunks of all ranks, handed to every chunk's optimizer
+            total = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for m in self.models:
+                E.sumsq_into(m.g32, total)
+            dist.all_reduce(total, group=self.group)
+            for opt in self.opts:
+                opt.norm_hook = lambda g32, sumsq, t=total: sumsq.copy_(t)
         for m, opt in zip(self.models, self.opts):
             m._ws_tag = ""
             if self.schedule is not None:

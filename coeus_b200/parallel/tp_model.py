@@ -385,6 +385,18 @@ class TPTrainer:
         self.schedule = schedule          # object with at(step) -> learning rate
         self.dp_group = dp_group
         self.dp_degree = dist.get_world_size(dp_group) if dp_group is not None else 1
+        if model.n > 1:
+            # global gradient norm: replicated tensors (embedding, norms) have the same gradient
+            # on every rank of the group, the sharded matrices one slice each
+            def norm_hook(g32, sumsq):
+                rep = torch.zeros_like(sumsq)
+                for name in model.replicated:
+                    o, shape = model.offsets[name]
+                    E.sumsq_into(g32[o:o + math.prod(shape)], rep)
+                shards = sumsq - rep
+                dist.all_reduce(shards, group=model.tp.group)
+                sumsq.copy_(shards + rep)
+            self.opt.norm_hook = norm_hook
         if self.dp_degree > 1:      # replicas start from the same weights
             dist.broadcast(model.p32, src=dist.get_global_rank(dp_group, 0), group=dp_group)
             model.p16.copy_(model.p32)

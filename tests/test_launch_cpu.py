@@ -20,8 +20,8 @@ def _cfg(moe=False, layers=2):
                          norm="rmsnorm", pos="rope", **kw)
 
 
-def _tc():
-    return TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0)
+def _tc(clip=None):
+    return TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0, grad_clip=clip)
 
 
 def _batch():
@@ -29,7 +29,7 @@ def _batch():
     return torch.randint(0, 96, (4, 16)), torch.randint(0, 96, (4, 16))
 
 
-def _worker(rank, world, port, kind, out):
+def _worker(rank, world, port, kind, out, clip=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -45,7 +45,7 @@ def _worker(rank, world, port, kind, out):
         par = ParallelConfig(dp=world, ep=world)
     from coeus_b200.optim.lr import Constant
     run = build_trainer(_cfg(moe=(kind == "ep"), layers=4 if kind == "pp_interleaved" else 2),
-                        par, "cpu", _tc(), micro_batches=2, seed=3,
+                        par, "cpu", _tc(clip), micro_batches=2, seed=3,
                         dtype=torch.float32, schedule=Constant(0.05))
     ids, tgt = _batch()
     losses = [float(run.step(ids, tgt)) for _ in range(4)]
@@ -79,6 +79,29 @@ def test_every_strategy_through_the_launcher(kind):
     assert got[-1] < got[0]
     if kind != "ep":
         assert abs(got[-1] - ref[-1]) < 5e-3
+
+
+def _worker_clip(rank, world, port, kind, clip, out):
+    _worker(rank, world, port, kind, out, clip)
+
+
+@pytest.mark.parametrize("kind", ["dp", "tp", "pp", "pp_interleaved", "cp"])
+def test_gradient_clipping_uses_the_global_norm_in_every_strategy(kind):
+    """With eps = 1 the AdamW update depends on the gradient scale, so a run clipped at a small
+    threshold only follows the clipped single-rank run if every rank clips by the norm of ALL
+    gradients (sharded, staged or replicated)."""
+    from mp_util import run_ranks
+    ids, tgt = _batch()
+    layers = 4 if kind == "pp_interleaved" else 2
+    ref, free = [], []
+    for clip, dst in ((0.02, ref), (None, free)):
+        single = build_trainer(_cfg(layers=layers), ParallelConfig(), "cpu", _tc(clip), seed=3,
+                               dtype=torch.float32)
+        dst += [float(single.step(ids, tgt)) for _ in range(4)]
+    assert abs(ref[-1] - free[-1]) > 0.02          # the threshold is active
+    res = {r[0]: r for r in run_ranks(_worker_clip, 2, (kind, 0.02), results=2)}
+    got = res[1][2]
+    assert abs(got[-1] - ref[-1]) < 3e-3, (got, ref, free)
 
 
 def _worker_2d(rank, world, port, out):
