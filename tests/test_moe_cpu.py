@@ -220,12 +220,26 @@ def _worker_ep_ckpt(rank, world, port, tmp, out):
                         norm="rmsnorm", pos="rope", num_experts=4, top_k=2, capacity_factor=2.0)
     epx = ExpertParallel(dist.group.WORLD, "cpu")
     tr = ExpertParallelTrainer(DecoderLM(cfg, "cpu", seed=2, dtype=torch.float32, epx=epx),
-                               TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0))
+                               TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0,
+                                           grad_clip=1e9))
     g = torch.Generator().manual_seed(rank)
     ids = torch.randint(0, 96, (2, 16), generator=g)
     tgt = torch.randint(0, 96, (2, 16), generator=g)
     for _ in range(2):
         tr.train_step(ids, tgt)
+    # the norm the optimizer clipped by is the norm of all gradients of all ranks: expert
+    # gradients live on one rank each, the rest is identical everywhere
+    m = tr.model
+    experts = torch.zeros(1)
+    dense = torch.zeros(1)
+    for sp in m.layout.specs:
+        sq = (m.g32[sp.offset:sp.offset + sp.numel].double() ** 2).sum().float()
+        if sp.expert:
+            experts += sq
+        else:
+            dense += sq
+    dist.all_reduce(experts)
+    assert abs(float(tr.opt.grad_norm) - float(torch.sqrt(experts + dense))) < 1e-4 * float(tr.opt.grad_norm)
     tr.save_checkpoint(tmp)
     out.put((rank, {k: v.numpy().copy() for k, v in tr.model.master.items()}))
     dist.barrier()
