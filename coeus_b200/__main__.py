@@ -28,7 +28,7 @@ DEFAULTS: Dict[str, Any] = {
                  "micro_batches": 1, "pp_chunks": 1, "zero_stage": 2},
     "train": {"steps": 20, "batch": 4, "seq_len": 128, "lr": 3e-4, "warmup": 0, "grad_clip": 0.0,
               "weight_decay": 0.01, "seed": 0, "log_every": 5, "checkpoint_dir": "",
-              "checkpoint_every": 0, "save": ""},
+              "checkpoint_every": 0, "save": "", "resume": False},
     "data": {"files": "", "binary": "", "binary_dtype": "uint16"},
     "device": "auto",
 }
@@ -145,8 +145,21 @@ def cmd_train(store) -> dict:
         ds = TokenDataset(g.integers(0, cfg.vocab_size, size=(steps + 1) * B * S + 1), S, B)
     ckpt_dir, every = _get(store, "train.checkpoint_dir"), _get(store, "train.checkpoint_every")
     losses, step, epoch = [], 0, 0
+    skip = 0
+    if _get(store, "train.resume") and ckpt_dir and hasattr(run.trainer, "load_checkpoint") \
+            and os.path.exists(os.path.join(ckpt_dir, "manifest.json")):
+        meta = run.trainer.load_checkpoint(ckpt_dir)
+        meta = meta.get("meta", meta)
+        step = int(meta.get("train_step", 0))
+        per_epoch = max(1, ds.num_windows() // B)
+        epoch, skip = divmod(step, per_epoch)       # continue inside the epoch that was running
+        log.info("resumed from %s at step %d (epoch %d, batch %d)", ckpt_dir, step, epoch, skip)
+    resumed_at = step
     while step < steps:
         ds.reset(epoch)
+        if skip:
+            ds.seek(skip)
+            skip = 0
         got = False
         for ids, tgt in ds:
             got = True
@@ -173,8 +186,9 @@ def cmd_train(store) -> dict:
             save_model(run.model, save)
     elif save and run.strategy in ("tp", "dp+tp"):
         run.model.save(save)
-    out = {"strategy": run.strategy, "steps": step, "first_loss": losses[0],
-           "last_loss": losses[-1], "world": world}
+    out = {"strategy": run.strategy, "steps": step, "resumed_at": resumed_at,
+           "first_loss": losses[0] if losses else None,
+           "last_loss": losses[-1] if losses else None, "world": world}
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

@@ -52,3 +52,16 @@ def test_train_two_ranks_under_torchrun(tmp_path):
                                     "--train.checkpoint_every=6"], launcher=launcher)
     assert out["strategy"] == "dp" and out["world"] == 2 and out["last_loss"] < out["first_loss"]
     assert os.path.exists(tmp_path / "ck" / "manifest.json")
+
+
+def test_resume_continues_the_interrupted_run(tmp_path):
+    text = tmp_path / "corpus.txt"
+    text.write_text("\n".join(["the cat sat on the mat", "the dog sat on the log",
+                               "a cat and a dog and a mat"] * 80))
+    common = SMALL + [f"--data.files={text}", "--train.checkpoint_every=5"]
+    whole = _run(["train"] + common + ["--train.steps=10", f"--train.checkpoint_dir={tmp_path}/a"])
+    _run(["train"] + common + ["--train.steps=5", f"--train.checkpoint_dir={tmp_path}/b"])
+    rest = _run(["train"] + common + ["--train.steps=10", f"--train.checkpoint_dir={tmp_path}/b",
+                                      "--train.resume=true"])
+    assert rest["resumed_at"] == 5 and rest["steps"] == 10
+    assert abs(rest["last_loss"] - whole["last_loss"]) < 1e-5
