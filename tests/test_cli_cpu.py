@@ -43,8 +43,12 @@ def test_train_on_text_save_and_generate(tmp_path):
 
 
 def test_train_two_ranks_under_torchrun(tmp_path):
+    import socket
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     launcher = ["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                "--master-addr=127.0.0.1", "--master-port=29731"]
+                "--master-addr=127.0.0.1", f"--master-port={port}"]
     text = tmp_path / "corpus.txt"
     text.write_text("\n".join(["the cat sat on the mat", "the dog sat on the log"] * 60))
     out = _run(["train"] + SMALL + ["--train.steps=12", "--parallel.dp=2", f"--data.files={text}",
