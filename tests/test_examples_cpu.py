@@ -70,3 +70,8 @@ def test_serving_benchmark_runs_small():
                   "--layers", "2", "--heads", "2", "--prompt-max", "24", "--new-max", "6"])
     assert r["generated_tokens"] > 0 and r["batched_tokens_per_s"] > 0
     assert r["latency_s"]["p50"] <= r["latency_s"]["max"]
+
+
+def test_parallel_training_example_single_process():
+    r = _load("parallel_training").main(["--device", "cpu", "--steps", "6"])
+    assert r["strategy"] == "single" and r["last"] < r["first"]
