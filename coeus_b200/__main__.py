@@ -140,6 +140,8 @@ def cmd_train(store) -> dict:
         with open(paths[0], encoding="utf-8", errors="replace") as f:
             tok.train(f.read(1 << 20).splitlines(), max(0, cfg.vocab_size - 300))
         ds = TokenDataset.from_text_files(paths, tok, S, B)
+        if _get(store, "train.save") and rank == 0:     # the tokenizer travels with the model
+            tok.save(str(_get(store, "train.save")) + ".tokenizer.json")
     else:
         g = np.random.default_rng(_get(store, "train.seed"))
         ds = TokenDataset(g.integers(0, cfg.vocab_size, size=(steps + 1) * B * S + 1), S, B)
@@ -198,6 +200,15 @@ def cmd_train(store) -> dict:
     return out
 
 
+def _load_tokenizer(store, weights: str):
+    """``--tokenizer=file`` or the file the training command wrote beside the weights."""
+    path = _get(store, "tokenizer") or (weights + ".tokenizer.json" if weights else None)
+    if not path or not os.path.exists(str(path)):
+        return None
+    from .plugins.builtin.tokenizer_bpe import BpeTokenizer
+    return BpeTokenizer.load(str(path))
+
+
 def cmd_generate(store, rest: List[str]) -> dict:
     import torch
 
@@ -208,15 +219,22 @@ def cmd_generate(store, rest: List[str]) -> dict:
     if not weights:
         raise SystemExit("generate needs --weights=<file.safetensors|.gguf|.rustllm>")
     model, _ = load_model(str(weights), device=device)
-    ids_arg = _get(store, "prompt_ids")
-    if ids_arg is None:
-        raise SystemExit("generate needs --prompt_ids=1,2,3")
-    ids = [int(t) for t in str(ids_arg).split(",")]
+    tok = _load_tokenizer(store, str(weights))
+    ids_arg, text = _get(store, "prompt_ids"), _get(store, "prompt")
+    if ids_arg is not None:
+        ids = [int(t) for t in str(ids_arg).split(",")]
+    elif text is not None and tok is not None:
+        ids = [int(t) for t in tok.encode(str(text))]
+    else:
+        raise SystemExit("generate needs --prompt_ids=1,2,3, or --prompt=text with a tokenizer "
+                         "file (<weights>.tokenizer.json or --tokenizer=...)")
     n = int(_get(store, "max_tokens") or 16)
     out = InferenceEngine(model, max_batch=1).generate(
         torch.tensor(ids, device=device)[None], n,
         temperature=float(_get(store, "temperature") or 0.0))
     res = {"prompt_ids": ids, "token_ids": out[0, len(ids):].tolist()}
+    if tok is not None:
+        res["text"] = tok.decode_ids(res["token_ids"])
     print(json.dumps(res))
     return res
 
@@ -235,7 +253,8 @@ def cmd_serve(store) -> int:
     else:
         dtype = torch.bfloat16 if device.startswith("cuda") else torch.float32
         model = DecoderLM(_model_config(store), device, dtype=dtype, training=False)
-    app = create_app(model, max_seqs=int(_get(store, "max_seqs") or 16),
+    app = create_app(model, tokenizer=_load_tokenizer(store, str(weights) if weights else ""),
+                     max_seqs=int(_get(store, "max_seqs") or 16),
                      max_len=model.cfg.max_seq_len)
     uvicorn.run(app, host=str(_get(store, "host") or "127.0.0.1"),
                 port=int(_get(store, "port") or 8000))

@@ -65,6 +65,7 @@ PYBIND11_MODULE(_coeus_host, m) {
   py::class_<BpeTokenizer>(m, "BpeTokenizer")
       .def(py::init<>())
       .def("train", &BpeTokenizer::train, py::call_guard<py::gil_scoped_release>())
+      .def("load_merges", &BpeTokenizer::load_merges)
       .def("encode", [](BpeTokenizer& t, const std::string& text) {
         std::vector<uint32_t> ids;
         { py::gil_scoped_release r; t.encode(text, ids); }
@@ -100,7 +101,11 @@ PYBIND11_MODULE(_coeus_host, m) {
         return py::int_(id);
       })
       .def("num_merges", &BpeTokenizer::num_merges)
-      .def("merge_at", &BpeTokenizer::merge_at);
+      .def("merge_at", &BpeTokenizer::merge_at)
+      .def("merge_at_bytes", [](const BpeTokenizer& t, size_t i) {
+        auto pr = t.merge_at(i);
+        return py::make_tuple(py::bytes(pr.first), py::bytes(pr.second));
+      });
 
   py::class_<WordPieceTokenizer>(m, "WordPieceTokenizer")
       .def(py::init<>())

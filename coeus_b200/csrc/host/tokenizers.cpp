@@ -227,6 +227,18 @@ void BpeTokenizer::train(const std::vector<std::string>& corpus, size_t num_merg
   cache_.clear();
 }
 
+void BpeTokenizer::load_merges(const std::vector<std::pair<std::string, std::string>>& pairs) {
+  for (const auto& pr : pairs) {
+    const uint32_t a = intern(pr.first), b = intern(pr.second);
+    const std::string merged_str = pr.first + pr.second;
+    const uint32_t merged = intern(merged_str);
+    merges_.push_back({a, b, merged});
+    merge_rank_.emplace(std::make_pair(a, b), static_cast<uint32_t>(merges_.size() - 1));
+    add_token(merged_str);
+  }
+  cache_.clear();
+}
+
 void BpeTokenizer::encode(std::string_view text, std::vector<uint32_t>& ids,
                           std::vector<std::string>* strings) {
   bool first = true;

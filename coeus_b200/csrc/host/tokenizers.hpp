@@ -40,6 +40,9 @@ class BpeTokenizer {
   // equally frequent pairs go to the pair with the smallest (first string, second string); the
   // reference leaves ties to hash-map iteration order.
   void train(const std::vector<std::string>& corpus, size_t num_merges);
+  // Replays merges learned elsewhere, in order, on a fresh tokenizer: the vocabulary ids come
+  // out as training assigned them (persistence of a trained tokenizer).
+  void load_merges(const std::vector<std::pair<std::string, std::string>>& pairs);
   // ids with a space token (id 32) between words; `strings` (optional) receives the token text.
   void encode(std::string_view text, std::vector<uint32_t>& ids,
               std::vector<std::string>* strings = nullptr);

@@ -81,6 +81,27 @@ class BpeTokenizer(VocabularyTokenizer, SpecialTokenizer):
     def merges(self) -> List[tuple]:
         return [self._t.merge_at(i) for i in range(self._t.num_merges())]
 
+    # ---- persistence (the reference's tokenizer lives and dies with its process)
+    def save(self, path: str) -> None:
+        """The learned merges, in order, as JSON (token bytes in hex): enough to rebuild the
+        tokenizer with the same ids."""
+        import json
+        pairs = [self._t.merge_at_bytes(i) for i in range(self._t.num_merges())]
+        with open(path, "w", encoding="utf-8") as f:
+            json.dump({"type": "bpe_tokenizer", "version": 1,
+                       "merges": [[a.hex(), b.hex()] for a, b in pairs]}, f)
+
+    @classmethod
+    def load(cls, path: str) -> "BpeTokenizer":
+        import json
+        with open(path, "r", encoding="utf-8") as f:
+            d = json.load(f)
+        if d.get("type") != "bpe_tokenizer":
+            raise ProcessingError.invalid_input(f"{path} is not a saved BPE tokenizer")
+        t = cls()
+        t._t.load_merges([(bytes.fromhex(a), bytes.fromhex(b)) for a, b in d["merges"]])
+        return t
+
     # ---- SpecialTokenizer
     def pad_token(self) -> Token:
         return StringToken.with_id("<PAD>", 0)

@@ -40,6 +40,11 @@ def test_train_on_text_save_and_generate(tmp_path):
     gen = _run(["generate", "--device=cpu", f"--weights={weights}", "--prompt_ids=5,6,7",
                 "--max_tokens=4"])
     assert gen["prompt_ids"] == [5, 6, 7] and len(gen["token_ids"]) == 4
+    # the tokenizer was saved beside the weights: text in, text out
+    assert os.path.exists(str(weights) + ".tokenizer.json")
+    gen = _run(["generate", "--device=cpu", f"--weights={weights}", "--prompt=the cat",
+                "--max_tokens=3"])
+    assert len(gen["prompt_ids"]) >= 1 and isinstance(gen["text"], str)
 
 
 def test_train_two_ranks_under_torchrun(tmp_path):

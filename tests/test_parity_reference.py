@@ -546,3 +546,16 @@ def test_transformer_plugin_math_helpers():
     want = torch.tensor([1.0, 2.0]).repeat(6) * (x - mean) / torch.sqrt(var + 1e-5) + 0.5
     assert torch.allclose(z, want, atol=1e-6)
     assert pymath.isclose(float(m.gelu(torch.tensor([2.0]))), m.gelu(2.0), rel_tol=1e-6)
+
+
+def test_bpe_tokenizer_save_and_load(tmp_path):
+    from coeus_b200.plugins.builtin.tokenizer_bpe import BpeTokenizer
+    t = BpeTokenizer()
+    t.train(["the cat sat on the mat", "naïve café 日本語", "the dog"], 50)
+    path = str(tmp_path / "tok.json")
+    t.save(path)
+    u = BpeTokenizer.load(path)
+    assert u.vocab_size() == t.vocab_size() and u.merges() == t.merges()
+    for s in ("the cat sat", "café 日本 xyz", "  spaced   out "):
+        assert u.encode(s).tolist() == t.encode(s).tolist()
+        assert u.decode_ids(u.encode(s)) == t.decode_ids(t.encode(s))
