@@ -70,6 +70,17 @@ static void test_tokenizers() {
   CHECK(!bpe.token_from_id(0xFFFFFFF0u, back));
   if (bpe.num_merges() > 0) (void)bpe.merge_at(bpe.num_merges() - 1);
   bpe.clear_cache();
+  {
+    // replaying the merges on a fresh tokenizer reproduces the ids
+    std::vector<std::pair<std::string, std::string>> pairs;
+    for (size_t i = 0; i < bpe.num_merges(); ++i) pairs.push_back(bpe.merge_at(i));
+    BpeTokenizer again;
+    again.load_merges(pairs);
+    std::vector<uint32_t> x, y;
+    bpe.encode("the cat sat on the caf\xc3\xa9", x);
+    again.encode("the cat sat on the caf\xc3\xa9", y);
+    CHECK(x == y && again.vocab_size() == bpe.vocab_size());
+  }
 
   WordPieceTokenizer wp;
   uint32_t next = 100;
