@@ -3,6 +3,7 @@
 Commands
     train      build a model and a trainer from the layered configuration and train it
     generate   load a model file and continue a prompt
+    eval       load a model file and report loss / perplexity on text or token files
     serve      load a model file (or build a random one) and serve completions over HTTP
     info       print the resolved configuration and the parameter count
 
@@ -239,6 +240,43 @@ def cmd_generate(store, rest: List[str]) -> dict:
     return res
 
 
+def cmd_eval(store) -> dict:
+    import numpy as np
+
+    from .checkpoint.formats import load_model
+    from .train.data import TokenDataset
+    from .train.trainer import Trainer
+    device = _device(store)
+    weights = _get(store, "weights")
+    if not weights:
+        raise SystemExit("eval needs --weights=<file>")
+    model, _ = load_model(str(weights), device=device, training=True)
+    S = min(int(_get(store, "train.seq_len")), model.cfg.max_seq_len)
+    B = int(_get(store, "train.batch"))
+    files, binary = _get(store, "data.files"), _get(store, "data.binary")
+    if binary:
+        ds = TokenDataset.from_binary(str(binary), S, B,
+                                      dtype=np.dtype(_get(store, "data.binary_dtype")))
+    elif files:
+        tok = _load_tokenizer(store, str(weights))
+        if tok is None:
+            raise SystemExit("eval on text needs the tokenizer (<weights>.tokenizer.json or "
+                             "--tokenizer=...)")
+        ds = TokenDataset.from_text_files([p for p in str(files).split(",") if p], tok, S, B)
+    else:
+        raise SystemExit("eval needs --data.files=... or --data.binary=...")
+    limit = int(_get(store, "max_batches") or 0)
+
+    def batches():
+        for i, (ids, tgt) in enumerate(ds):
+            if limit and i >= limit:
+                return
+            yield ids.to(device), tgt.to(device)
+    out = Trainer(model).evaluate(batches())
+    print(json.dumps(out))
+    return out
+
+
 def cmd_serve(store) -> int:
     import uvicorn
 
@@ -281,11 +319,13 @@ def main(argv: Optional[List[str]] = None):
         return cmd_train(store)
     if cmd == "generate":
         return cmd_generate(store, rest)
+    if cmd == "eval":
+        return cmd_eval(store)
     if cmd == "serve":
         return cmd_serve(store)
     if cmd == "info":
         return cmd_info(store)
-    raise SystemExit(f"unknown command '{cmd}' (train, generate, serve, info)")
+    raise SystemExit(f"unknown command '{cmd}' (train, generate, eval, serve, info)")
 
 
 if __name__ == "__main__":

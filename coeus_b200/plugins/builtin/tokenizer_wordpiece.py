@@ -49,6 +49,38 @@ class WordPieceTokenizer(NormalizingTokenizer, SpecialTokenizer):
     def add_token(self, token: str, id: int) -> None:
         self._t.add_token(token, int(id))
 
+    # ---- persistence
+    def vocabulary(self, max_id: int = 1 << 22) -> List[tuple]:
+        """``(token, id)`` for every entry, by id."""
+        out, want = [], self._t.vocab_size()
+        i = 0
+        while len(out) < want and i < max_id:
+            t = self._t.id_to_token(i)
+            if t is not None:
+                out.append((t, i))
+            i += 1
+        return out
+
+    def save(self, path: str) -> None:
+        import json
+        with open(path, "w", encoding="utf-8") as f:
+            json.dump({"type": "wordpiece_tokenizer", "version": 1,
+                       "vocab": self.vocabulary()}, f, ensure_ascii=False)
+
+    @classmethod
+    def load(cls, path: str, config: Optional[TokenizerConfig] = None) -> "WordPieceTokenizer":
+        import json
+        with open(path, "r", encoding="utf-8") as f:
+            d = json.load(f)
+        if d.get("type") != "wordpiece_tokenizer":
+            raise ValueError(f"{path} is not a saved WordPiece tokenizer")
+        t = cls(config)
+        have = dict(t.vocabulary())
+        for tok, i in d["vocab"]:
+            if have.get(tok) != i:
+                t.add_token(tok, int(i))
+        return t
+
     def longest_match(self, text: str):
         return self._t.longest_match(text)
 

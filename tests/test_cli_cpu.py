@@ -45,6 +45,10 @@ def test_train_on_text_save_and_generate(tmp_path):
     gen = _run(["generate", "--device=cpu", f"--weights={weights}", "--prompt=the cat",
                 "--max_tokens=3"])
     assert len(gen["prompt_ids"]) >= 1 and isinstance(gen["text"], str)
+    ev = _run(["eval", "--device=cpu", f"--weights={weights}", f"--data.files={text}",
+               "--train.seq_len=16", "--train.batch=4", "--max_batches=5"])
+    assert ev["tokens"] == 5 * 4 * 16 and ev["loss"] < out["first_loss"]
+    assert abs(ev["perplexity"] - __import__("math").exp(ev["loss"])) < 1e-3 * ev["perplexity"]
 
 
 def test_train_two_ranks_under_torchrun(tmp_path):

@@ -559,3 +559,16 @@ def test_bpe_tokenizer_save_and_load(tmp_path):
     for s in ("the cat sat", "café 日本 xyz", "  spaced   out "):
         assert u.encode(s).tolist() == t.encode(s).tolist()
         assert u.decode_ids(u.encode(s)) == t.decode_ids(t.encode(s))
+
+
+def test_wordpiece_tokenizer_save_and_load(tmp_path):
+    from coeus_b200.plugins.builtin.tokenizer_wordpiece import WordPieceTokenizer
+    t = WordPieceTokenizer()
+    for i, tok in enumerate(["un", "##aff", "##able", "caf", "##é", "日本"]):
+        t.add_token(tok, 5000 + i)
+    path = str(tmp_path / "wp.json")
+    t.save(path)
+    u = WordPieceTokenizer.load(path)
+    assert u.vocab_size() == t.vocab_size() and u.vocabulary() == t.vocabulary()
+    for s in ("unaffable café", "hello 日本 world"):
+        assert u.encode(s) == t.encode(s)
