@@ -30,6 +30,8 @@ class Request:
     temperature: float = 0.0
     top_k: Optional[int] = None
     top_p: Optional[float] = None
+    min_p: Optional[float] = None
+    repetition_penalty: float = 1.0
     output: List[int] = field(default_factory=list)
     slot: int = -1
     on_token: Optional[Callable[[int], None]] = None      # called with every new token
@@ -68,7 +70,8 @@ class ContinuousBatcher:
     def submit(self, prompt, max_new_tokens: int, eos_id: Optional[int] = None,
                temperature: float = 0.0, top_k: Optional[int] = None,
                top_p: Optional[float] = None,
-               on_token: Optional[Callable[[int], None]] = None) -> int:
+               on_token: Optional[Callable[[int], None]] = None, min_p: Optional[float] = None,
+               repetition_penalty: float = 1.0) -> int:
         prompt = [int(t) for t in prompt]
         if not prompt:
             raise ProcessingError.invalid_input("empty prompt")
@@ -78,6 +81,7 @@ class ContinuousBatcher:
         rid = self._next_id
         self._next_id += 1
         self.waiting.append(Request(rid, prompt, max_new_tokens, eos_id, temperature, top_k, top_p,
+                                    min_p=min_p, repetition_penalty=repetition_penalty,
                                     on_token=on_token))
         return rid
 
@@ -111,7 +115,7 @@ class ContinuousBatcher:
             pos = torch.tensor([len(r.prompt) + len(r.output) - 1 for r in reqs],
                                dtype=torch.int32, device=self.device)
             logits = eng.decode_slots(slots, tokens, pos)
-            greedy = all(not r.temperature for r in reqs)
+            greedy = all(not r.temperature and r.repetition_penalty == 1.0 for r in reqs)
             nxt = select(logits, 0.0, None, None, None).tolist() if greedy else None
             for i, r in enumerate(reqs):
                 tok = nxt[i] if greedy else int(self._sample(logits[i:i + 1], r)[0])
@@ -136,7 +140,11 @@ class ContinuousBatcher:
     def _sample(self, logits: torch.Tensor, r: Request) -> torch.Tensor:
         V = self.engine.cfg.vocab_size
         gen = self._gen if r.temperature else None
-        return select(logits[:, :V], r.temperature, r.top_k, r.top_p, gen)
+        hist = None
+        if r.repetition_penalty != 1.0:
+            hist = torch.tensor([r.prompt + r.output], dtype=torch.int64, device=logits.device)
+        return select(logits[:, :V], r.temperature, r.top_k, r.top_p, gen, min_p=r.min_p,
+                      history=hist, repetition_penalty=r.repetition_penalty)
 
     def _retire(self, r: Request, finished: List[Request]) -> None:
         self.active.pop(r.slot, None)

@@ -31,6 +31,8 @@ try:        # the request schema lives at module level so that FastAPI can resol
         top_k: Optional[int] = None
         top_p: Optional[float] = None
         eos_id: Optional[int] = None
+        min_p: Optional[float] = None
+        repetition_penalty: float = 1.0
         stream: bool = False
 except ImportError:      # ServingLoop works without the HTTP stack
     CompletionRequest = None
@@ -189,7 +191,8 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
         if not ids or any(t < 0 or t >= V for t in ids):
             raise HTTPException(422, f"token ids must lie in [0, {V}) and the prompt be non-empty")
         sampling = dict(eos_id=req.eos_id, temperature=req.temperature, top_k=req.top_k,
-                        top_p=req.top_p)
+                        top_p=req.top_p, min_p=req.min_p,
+                        repetition_penalty=req.repetition_penalty)
         if req.stream:
             return StreamingResponse(_stream(ids, req.max_tokens, sampling),
                                      media_type="text/event-stream")

@@ -72,3 +72,25 @@ def test_continuous_batching_matches_one_request_at_a_time(kind):
     assert got == alone[1][:alone[1].index(first) + 1]
     with pytest.raises(Exception):
         cb.submit([1] * 200, 10)
+    # a strong repetition penalty: no token is produced twice while unseen ones remain
+    rid = cb.submit(prompts[0], 12, repetition_penalty=1e6)
+    got = cb.run()[rid]
+    assert len(set(got)) == len(got) and not set(got) & set(prompts[0])
+
+
+def test_sampler_filters():
+    from coeus_b200.infer.sampler import apply_repetition_penalty, select
+    logits = torch.tensor([[4.0, 3.9, 1.0, -2.0, 0.0]])
+    assert int(select(logits)) == 0
+    # a penalised favourite loses to the runner-up; negative logits move further down
+    hist = torch.tensor([[0, 3, -1]])
+    pen = apply_repetition_penalty(logits, hist, 2.0)
+    assert pen[0].tolist() == [2.0, 3.9000000953674316, 1.0, -4.0, 0.0]
+    assert int(select(logits, history=hist, repetition_penalty=2.0)) == 1
+    g = torch.Generator().manual_seed(0)
+    draws = {int(select(logits, 1.0, min_p=0.5, generator=g)) for _ in range(200)}
+    assert draws == {0, 1}                       # everything below half the top probability is cut
+    draws = {int(select(logits, 1.0, top_k=3, generator=g)) for _ in range(300)}
+    assert draws <= {0, 1, 2} and {0, 1} <= draws
+    draws = {int(select(logits, 1.0, top_p=0.6, generator=g)) for _ in range(200)}
+    assert draws == {0, 1}
