@@ -256,7 +256,8 @@ class InferenceEngine:
                  top_k: Optional[int] = None, top_p: Optional[float] = None, seed: int = 0,
                  eos_id: Optional[int] = None, seq_chunk: Optional[int] = None,
                  token_chunk: Optional[int] = None) -> torch.Tensor:
-        """Returns ``[B, S + max_new_tokens]`` token ids (prompt included).  ``seq_chunk`` /
+        """Returns ``[B, S + max_new_tokens]`` token ids (prompt included); after ``eos_id`` a
+        sequence is padded with ``eos_id`` and decoding stops once all have ended.  ``seq_chunk`` /
         ``token_chunk`` bound the memory of the prompt pass (see :meth:`prefill`)."""
         if ids.dim() == 1:
             ids = ids[None]
@@ -279,9 +280,16 @@ class InferenceEngine:
         t1 = time.perf_counter()
         nxt = select(logits, temperature, top_k, top_p, gen)
         out[:, S] = nxt
+        done = (nxt == eos_id) if eos_id is not None else None
         for i in range(1, max_new_tokens):
+            if done is not None and bool(done.all()):      # every sequence has ended
+                out[:, S + i:] = eos_id
+                break
             logits = self.decode_step(nxt)
             nxt = select(logits, temperature, top_k, top_p, gen)
+            if done is not None:                           # a finished sequence stays finished
+                nxt = torch.where(done, torch.full_like(nxt, eos_id), nxt)
+                done = done | (nxt == eos_id)
             out[:, S + i] = nxt
         if ids.is_cuda:
             torch.cuda.synchronize(ids.device)

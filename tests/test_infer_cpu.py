@@ -40,6 +40,14 @@ def test_decode_matches_full_recompute():
     eng = InferenceEngine(m, max_batch=2)
     out = eng.generate(ids, 6)
     assert out.shape == (2, 23) and torch.equal(out[:, :17], ids)
+    # an end-of-sequence token freezes its sequence; the other keeps decoding
+    eos = int(out[0, 19])
+    stopped = InferenceEngine(m, max_batch=2).generate(ids, 6, eos_id=eos)
+    first = out[0, 17:].tolist().index(eos)
+    assert stopped[0, 17:17 + first + 1].tolist() == out[0, 17:17 + first + 1].tolist()
+    assert set(stopped[0, 17 + first:].tolist()) == {eos}
+    if eos not in out[1, 17:].tolist():
+        assert torch.equal(stopped[1], out[1])
     for i in range(6):          # greedy continuation of the full-sequence forward
         logits = m.forward_logits(out[:, :17 + i], last_only=True)[:, :96]
         assert torch.equal(logits.argmax(-1).reshape(-1), out[:, 17 + i])
