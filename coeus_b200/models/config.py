@@ -201,6 +201,13 @@ class DecoderConfig:
             raise ConfigError.invalid("hidden_dim", self.hidden_dim,
                                       "hidden_dim and intermediate_dim must be multiples of 8 "
                                       "(16-byte rows)")
+        if self.dropout or self.attention_dropout:
+            # the reference declares dropout rates and never applies them (its forward pass is
+            # inference only, plugins/model-transformer/src/lib.rs:863-921); the kernels here
+            # have no dropout either, so a non-zero rate is refused rather than ignored
+            raise ConfigError.invalid("dropout", self.dropout or self.attention_dropout,
+                                      "Dropout is not implemented; set dropout and "
+                                      "attention_dropout to 0")
         if self.num_experts and not (0 < self.top_k <= self.num_experts):
             raise ConfigError.invalid("top_k", self.top_k, "top_k must be in [1, num_experts]")
 

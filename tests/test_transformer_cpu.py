@@ -337,3 +337,12 @@ def test_weight_only_quantisation():
     assert all(c.dtype == torch.int8 for c, _ in model.quantized_tensors.values())
     with pytest.raises(Exception):
         model.quantize(QuantConfig(bits=1))
+
+
+def test_nonzero_dropout_is_refused_not_ignored():
+    from coeus_b200.models.config import DecoderConfig
+    cfg = DecoderConfig(hidden_dim=32, num_layers=1, num_heads=2, intermediate_dim=64,
+                        vocab_size=64, max_seq_len=16, dropout=0.1)
+    with pytest.raises(Exception) as e:
+        cfg.validate()
+    assert "Dropout" in str(e.value)
