@@ -262,6 +262,11 @@ class ParallelConfig:
             raise ConfigError.invalid("zero_stage", self.zero_stage,
                                       "Stages 0 (replicated) and 1/2 (sharded state) are built; "
                                       "parameter sharding (3) is not")
+        if self.tp > 1 and not self.sp:
+            raise ConfigError.invalid("sp", self.sp, "Tensor parallelism here always keeps the "
+                                      "activations between blocks sequence-sharded")
+        if self.pp_chunks < 1:
+            raise ConfigError.invalid("pp_chunks", self.pp_chunks, "Must be >= 1")
         for k in ("dp", "tp", "pp", "ep", "cp"):
             if getattr(self, k) < 1:
                 raise ConfigError.invalid(k, getattr(self, k), "Parallel degree must be >= 1")

@@ -67,6 +67,11 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
     device = torch.device(device)
     tc = train_cfg or TrainConfig()
     cpu = device.type != "cuda"
+    if tc.grad_accum > 1 and strategy in ("tp", "pp", "ep"):
+        raise ConfigError.invalid("grad_accum", tc.grad_accum,
+                                  "Gradient accumulation is built into the plain and "
+                                  "data-parallel trainers; a pipeline accumulates over its "
+                                  "micro_batches")
 
     if strategy == "single":
         model = DecoderLM(cfg, device, seed=seed, dtype=dtype, recompute=recompute)
@@ -152,6 +157,9 @@ def _build_dp_tp(cfg, parallel, device, tc, group, world, rank, seed, dtype, rec
     from ..parallel.tp import TensorParallel
     from ..parallel.tp_model import TPDecoderLM, TPTrainer
     dp, tp = parallel.dp, parallel.tp
+    if tc.grad_accum > 1:
+        raise ConfigError.invalid("grad_accum", tc.grad_accum,
+                                  "Not built for replicas of a tensor-parallel model")
     if dp * tp != world:
         raise ConfigError.invalid("dp*tp", dp * tp, f"must equal the size of the process group ({world})")
     ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
