@@ -164,10 +164,14 @@ class InferenceEngine:
     def open_slots(self, max_seqs: int, max_len: int) -> PagedKVCache:
         """A cache whose rows are independent request slots (see
         :class:`coeus_b200.infer.scheduler.ContinuousBatcher`); pages are handed out per slot."""
-        self.cache = PagedKVCache.for_model(self.cfg, max_seqs, max(max_len, D.PAGE),
-                                            self.m.device)
+        c = PagedKVCache.for_model(self.cfg, max_seqs, max(max_len, D.PAGE) + D.PAGE,
+                                   self.m.device)
+        if self.m.p16.dtype != torch.bfloat16:       # CPU oracle runs keep their precision
+            c.k = [t.to(self.m.p16.dtype) for t in c.k]
+            c.v = [t.to(self.m.p16.dtype) for t in c.v]
+        self.cache = c
         self._graph = None
-        return self.cache
+        return c
 
     def prefill_slot(self, slot: int, ids: torch.Tensor, total_len: int,
                      token_chunk: Optional[int] = None) -> torch.Tensor:
@@ -189,6 +193,40 @@ class InferenceEngine:
                              earlier=earlier)
         cache.set_length(slot, S)
         return self._logits(x[-1:].contiguous())[0]
+
+    def prefill_slot_paged(self, slot: int, ids: torch.Tensor, total_len: int,
+                           prefix_pages: List[int]) -> torch.Tensor:
+        """Like :meth:`prefill_slot`, but the first ``len(prefix_pages) * 64`` prompt tokens are
+        not computed: their keys and values already sit in ``prefix_pages`` (filled by an earlier
+        request with the same prefix), which the slot adopts.  The rest of the prompt runs in
+        page-sized chunks, each attending to the pages before it and causally to itself; the last
+        chunk is padded to a full page (rows past the prompt are computed and thrown away, their
+        cache entries are overwritten by the decode steps before anything reads them)."""
+        cache, m, cfg = self.cache, self.m, self.cfg
+        PG = D.PAGE
+        S = ids.numel()
+        P = len(prefix_pages) * PG
+        if not 0 <= P < S:
+            raise ProcessingError.invalid_input("the cached prefix must be shorter than the prompt")
+        H = cfg.hidden_dim
+        cache.adopt(slot, list(prefix_pages))
+        padded = P + (S - P + PG - 1) // PG * PG
+        cache.reserve(slot, max(total_len, padded))
+        pe = m._positions(max(padded, total_len))
+        table = cache.page_table[slot:slot + 1]
+        earlier = [[(cache.k[l][pg].view(PG, H), cache.v[l][pg].view(PG, H))
+                    for pg in prefix_pages] for l in range(cfg.num_layers)]
+        pad = torch.zeros(padded - S, dtype=ids.dtype, device=ids.device)
+        toks = torch.cat([ids, pad])
+        for c0 in range(P, padded, PG):
+            pos0 = torch.full((1,), c0, dtype=torch.int32, device=m.device)
+            x = E.embed_fwd(toks[c0:c0 + PG].reshape(-1), m.w["token_embed"], pe, PG,
+                            pos_offset=c0)
+            x = self._layers(x, 1, PG, pos0, c0, cache, prefill=True, page_table=table,
+                             earlier=earlier)
+        cache.set_length(slot, S)
+        last = (S - 1) - (padded - PG)
+        return self._logits(x[last:last + 1].contiguous())[0]
 
     def decode_slots(self, slots: torch.Tensor, tokens: torch.Tensor,
                      positions: torch.Tensor) -> torch.Tensor:

@@ -24,6 +24,9 @@ class PagedKVCache:
                                       device=self.device)
         self.free: List[int] = list(range(num_pages - 1, -1, -1))
         self.owned: Dict[int, List[int]] = {}
+        # pages can be shared (a cached prompt prefix used by several sequences): a page returns
+        # to the free list when its last holder lets go
+        self.refs: List[int] = [0] * num_pages
         self.lengths = torch.zeros(max_seqs, dtype=torch.int32, device=self.device)
         self._host_len = [0] * max_seqs
 
@@ -42,17 +45,41 @@ class PagedKVCache:
         new = []
         while len(have) + len(new) < need:
             if not self.free:
-                raise ResourceError.exhausted("KV cache pages", 0, need - len(have))
+                self.free.extend(reversed(new))       # nothing is taken when not all can be
+                raise ResourceError.exhausted("KV cache pages", len(new), need - len(have))
             new.append(self.free.pop())
+        for p in new:
+            self.refs[p] = 1
         if new:
             idx = torch.tensor(new, dtype=torch.int32, device=self.device)
             self.page_table[seq, len(have):len(have) + len(new)] = idx
             have.extend(new)
 
     def release(self, seq: int) -> None:
-        self.free.extend(reversed(self.owned.pop(seq, [])))
+        for p in reversed(self.owned.pop(seq, [])):
+            self.drop(p)
         self._host_len[seq] = 0
         self.lengths[seq] = 0
+
+    def retain(self, page: int) -> None:
+        """One more holder of ``page`` (e.g. a prefix cache entry)."""
+        self.refs[page] += 1
+
+    def drop(self, page: int) -> None:
+        self.refs[page] -= 1
+        if self.refs[page] == 0:
+            self.free.append(page)
+
+    def adopt(self, seq: int, pages: List[int]) -> None:
+        """Start sequence ``seq`` (which owns nothing yet) on existing, already filled pages."""
+        if self.owned.get(seq):
+            raise ResourceError.exhausted("KV slot", 0, 1)
+        for p in pages:
+            self.refs[p] += 1
+        self.owned[seq] = list(pages)
+        if pages:
+            idx = torch.tensor(pages, dtype=torch.int32, device=self.device)
+            self.page_table[seq, :len(pages)] = idx
 
     def set_length(self, seq: int, n: int) -> None:
         self._host_len[seq] = n

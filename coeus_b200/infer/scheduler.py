@@ -47,17 +47,92 @@ class Request:
             self.eos_id is not None and bool(self.output) and self.output[-1] == self.eos_id)
 
 
+class PrefixCache:
+    """Prompt prefixes whose keys and values are already in cache pages, by page: entry ``j`` of a
+    prompt is keyed by all of its first ``64 * (j + 1)`` tokens, so two prompts share exactly the
+    pages of their common page-aligned prefix.  The cache holds one reference on every page it
+    knows; pages nobody else uses are given back, least recently used first, when the pool runs
+    dry."""
+
+    def __init__(self, kv) -> None:
+        self.kv = kv
+        # (parent entry id, the page's 64 tokens) -> [entry id, page]; the chain through the
+        # parents spells the whole prefix, so a key is exact without storing the prefix again.
+        # Dict order = recency (entries are re-inserted when touched).
+        self.entries: "Dict[tuple, list]" = {}
+        self._next = 1
+        self.hits = self.lookups = 0
+
+    def _walk(self, prompt: List[int], page: int):
+        parent = 0
+        for j in range(len(prompt) // page):
+            yield j, (parent, tuple(prompt[page * j:page * (j + 1)]))
+            e = self.entries.get((parent, tuple(prompt[page * j:page * (j + 1)])))
+            if e is None:
+                return
+            parent = e[0]
+
+    def match(self, prompt: List[int], page: int) -> List[int]:
+        """Pages of the longest cached prefix that still leaves one prompt token to compute."""
+        out = []
+        for j, key in self._walk(prompt, page):
+            e = self.entries.get(key)
+            if e is None or page * (j + 1) >= len(prompt):
+                break
+            out.append(e[1])
+            self.entries[key] = self.entries.pop(key)      # touch
+        self.lookups += 1
+        self.hits += bool(out)
+        return out
+
+    def insert(self, prompt: List[int], page: int, owned: List[int]) -> None:
+        """Remember the full prompt pages of a sequence that owns ``owned`` (its pages in order)."""
+        parent = 0
+        for j in range(min(len(prompt) // page, len(owned))):
+            key = (parent, tuple(prompt[page * j:page * (j + 1)]))
+            e = self.entries.get(key)
+            if e is None:
+                e = [self._next, owned[j]]
+                self._next += 1
+                self.entries[key] = e
+                self.kv.retain(owned[j])
+            parent = e[0]
+
+    def evict(self, want: int) -> int:
+        """Give back up to ``want`` pages that only the cache still holds (least recently used
+        first; an entry whose page goes away takes its descendants' reachability with it, they
+        age out the same way); returns how many."""
+        freed = 0
+        for key in list(self.entries):
+            if freed >= want:
+                break
+            pg = self.entries[key][1]
+            if self.kv.refs[pg] == 1:
+                del self.entries[key]
+                self.kv.drop(pg)
+                freed += 1
+        return freed
+
+    def __len__(self) -> int:
+        return len(self.entries)
+
+
 class ContinuousBatcher:
     def __init__(self, engine: InferenceEngine, max_seqs: int = 64, max_len: Optional[int] = None,
-                 token_chunk: Optional[int] = None, seed: int = 0) -> None:
+                 token_chunk: Optional[int] = None, seed: int = 0,
+                 prefix_cache: bool = False) -> None:
         """``max_seqs`` rows decode together; ``max_len`` bounds prompt + generated tokens of one
-        request; ``token_chunk`` prefills long prompts in pieces."""
+        request; ``token_chunk`` prefills long prompts in pieces; ``prefix_cache`` reuses the
+        cache pages of prompt prefixes that earlier requests already computed (shared system
+        prompts), in units of whole pages."""
         self.engine = engine
         self.max_seqs = max_seqs
         self.max_len = max_len or engine.max_len
         self.token_chunk = token_chunk
         self.device = engine.m.device
         engine.open_slots(max_seqs, self.max_len)
+        self.prefix = PrefixCache(engine.cache) if prefix_cache and hasattr(
+            engine, "prefill_slot_paged") else None
         self.waiting: Deque[Request] = deque()
         self.active: Dict[int, Request] = {}          # slot -> request
         self.free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
@@ -98,8 +173,7 @@ class ContinuousBatcher:
             r = self.waiting.popleft()
             r.slot = self.free_slots.pop()
             ids = torch.tensor(r.prompt, dtype=torch.int64, device=self.device)
-            logits = eng.prefill_slot(r.slot, ids, len(r.prompt) + r.max_new_tokens,
-                                      token_chunk=self.token_chunk)
+            logits = self._prefill(r, ids)
             r.push(int(self._sample(logits[None], r)[0]))
             self.stats["prefills"] += 1
             if r.done:
@@ -137,6 +211,25 @@ class ContinuousBatcher:
         return out
 
     # ------------------------------------------------------------------ internals
+    def _prefill(self, r: Request, ids: torch.Tensor) -> torch.Tensor:
+        eng, total = self.engine, len(r.prompt) + r.max_new_tokens
+        if self.prefix is None:
+            return eng.prefill_slot(r.slot, ids, total, token_chunk=self.token_chunk)
+        from ..ops.decode import PAGE
+        from ..foundation.error import ResourceError
+        for attempt in range(2):
+            pages = self.prefix.match(r.prompt, PAGE)
+            try:
+                logits = eng.prefill_slot_paged(r.slot, ids, total, pages)
+                break
+            except ResourceError:
+                # the pool is full of cached prefixes nobody uses right now: drop some, retry
+                eng.cache.release(r.slot)
+                if attempt or not self.prefix.evict(total // PAGE + 2):
+                    raise
+        self.prefix.insert(r.prompt, PAGE, eng.cache.owned[r.slot])
+        return logits
+
     def _sample(self, logits: torch.Tensor, r: Request) -> torch.Tensor:
         V = self.engine.cfg.vocab_size
         gen = self._gen if r.temperature else None

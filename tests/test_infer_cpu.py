@@ -102,3 +102,54 @@ def test_sampler_filters():
     assert draws <= {0, 1, 2} and {0, 1} <= draws
     draws = {int(select(logits, 1.0, top_p=0.6, generator=g)) for _ in range(200)}
     assert draws == {0, 1}
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama"])
+def test_prefix_cache_reuses_pages_and_changes_nothing(kind):
+    """Requests that share a long system prompt: with the prefix cache the shared pages are
+    computed once and every request still gets exactly the tokens it gets without it."""
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    m = _model(kind)
+    torch.manual_seed(4)
+    system = torch.randint(0, 96, (130,)).tolist()           # two full pages + 2 tokens
+    prompts = [system + torch.randint(0, 96, (n,)).tolist() for n in (3, 9, 1)] + \
+              [system[:64] + [5, 6, 7], torch.randint(0, 96, (70,)).tolist(), system[:128]]
+    budgets = [3, 2, 4, 2, 3, 2]
+
+    def run(prefix_cache):
+        cb = ContinuousBatcher(InferenceEngine(m, max_batch=2), max_seqs=2, max_len=160,
+                               prefix_cache=prefix_cache)
+        ids = [cb.submit(p, k) for p, k in zip(prompts, budgets)]
+        out = cb.run()
+        return [out[i] for i in ids], cb
+
+    plain, _ = run(False)
+    cached, cb = run(True)
+    assert cached == plain
+    assert cb.prefix.hits >= 4 and len(cb.prefix) >= 3
+    kv = cb.engine.cache
+    # nothing is active: every page in use is held by the prefix cache alone
+    assert kv.pages_in_use() == len(cb.prefix) and all(kv.refs[e[1]] == 1
+                                                       for e in cb.prefix.entries.values())
+    assert cb.prefix.evict(100) == len(kv.refs) - len(kv.free) or kv.pages_in_use() == 0
+    assert kv.pages_in_use() == 0
+
+
+def test_prefix_cache_gives_pages_back_under_pressure():
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    m = _model("llama")
+    torch.manual_seed(6)
+    prompts = [torch.randint(0, 96, (140,)).tolist() for _ in range(4)]     # nothing in common
+    alone = [InferenceEngine(m, max_batch=1).generate(torch.tensor(p)[None], 3)[0, 140:].tolist()
+             for p in prompts]
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=1), max_seqs=1, max_len=160,
+                           prefix_cache=True)
+    assert cb.engine.cache.num_pages == 4            # one sequence's worth of pages
+    got = []
+    for p in prompts:                                # each request finds the pool full of the
+        rid = cb.submit(p, 3)                        # previous prompt's cached pages
+        got.append(cb.run()[rid])
+    assert got == alone and cb.prefix.hits == 0
+    rid = cb.submit(prompts[-1] + [1, 2], 2)         # the most recent prompt is still cached
+    cb.run()
+    assert cb.prefix.hits == 1
