@@ -293,6 +293,7 @@ def cmd_serve(store) -> int:
         model = DecoderLM(_model_config(store), device, dtype=dtype, training=False)
     app = create_app(model, tokenizer=_load_tokenizer(store, str(weights) if weights else ""),
                      max_seqs=int(_get(store, "max_seqs") or 16),
+                     prefix_cache=bool(_get(store, "prefix_cache")),
                      max_len=model.cfg.max_seq_len)
     uvicorn.run(app, host=str(_get(store, "host") or "127.0.0.1"),
                 port=int(_get(store, "port") or 8000))

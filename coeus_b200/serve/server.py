@@ -43,10 +43,11 @@ class ServingLoop(Metrics, HealthCheck):
     ``Metrics`` and ``HealthCheck`` traits (src/core/traits.rs:197-221)."""
 
     def __init__(self, model, max_seqs: int = 16, max_len: Optional[int] = None,
-                 token_chunk: Optional[int] = None, idle_sleep_s: float = 0.002) -> None:
+                 token_chunk: Optional[int] = None, idle_sleep_s: float = 0.002,
+                 prefix_cache: bool = False) -> None:
         self.engine = InferenceEngine(model, max_batch=max_seqs, use_graph=False)
         self.batcher = ContinuousBatcher(self.engine, max_seqs=max_seqs, max_len=max_len,
-                                         token_chunk=token_chunk)
+                                         token_chunk=token_chunk, prefix_cache=prefix_cache)
         self._lock = threading.Lock()
         self._inbox: List[tuple] = []
         self._futures: Dict[int, Future] = {}
@@ -133,7 +134,8 @@ class ServingLoop(Metrics, HealthCheck):
 
 
 def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int] = None,
-               token_chunk: Optional[int] = None, request_timeout_s: float = 120.0):
+               token_chunk: Optional[int] = None, request_timeout_s: float = 120.0,
+               prefix_cache: bool = False):
     """FastAPI application.  ``tokenizer`` (anything with ``encode(str) -> ids`` and
     ``decode_ids(ids) -> str`` or ``decode(ids) -> str``) enables text prompts; without it requests carry ``prompt_ids``."""
     import asyncio
@@ -143,7 +145,8 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
 
     from contextlib import asynccontextmanager
 
-    loop = ServingLoop(model, max_seqs=max_seqs, max_len=max_len, token_chunk=token_chunk)
+    loop = ServingLoop(model, max_seqs=max_seqs, max_len=max_len, token_chunk=token_chunk,
+                       prefix_cache=prefix_cache)
 
     @asynccontextmanager
     async def lifespan(_app):
@@ -225,6 +228,10 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
                   f"coeus_waiting_requests {len(b.waiting)}",
                   f"coeus_kv_pages_in_use {loop.engine.cache.pages_in_use()}",
                   f"coeus_decode_steps {b.stats['steps']}"]
+        if b.prefix is not None:
+            lines += [f"coeus_prefix_cache_lookups {b.prefix.lookups}",
+                      f"coeus_prefix_cache_hits {b.prefix.hits}",
+                      f"coeus_prefix_cache_pages {len(b.prefix)}"]
         return "\n".join(lines) + "\n"
 
     return app

@@ -80,3 +80,16 @@ def test_http_completions(model):
         assert [json.loads(e)["token_id"] for e in events[:-1]] == plain.json()["token_ids"]
         text = client.get("/metrics").text
         assert "coeus_completed 8" in text and "coeus_kv_pages_in_use 0" in text
+
+
+def test_http_prefix_cache_metrics(model):
+    from fastapi.testclient import TestClient
+    from coeus_b200.serve import create_app
+    app = create_app(model, max_seqs=2, max_len=96, prefix_cache=True)
+    system = list(range(1, 66))                       # one full page + 1 token
+    with TestClient(app) as client:
+        a = client.post("/v1/completions", json={"prompt_ids": system + [7], "max_tokens": 2})
+        b = client.post("/v1/completions", json={"prompt_ids": system + [9, 9], "max_tokens": 2})
+        assert a.status_code == 200 and b.status_code == 200
+        text = client.get("/metrics").text
+        assert "coeus_prefix_cache_hits 1" in text and "coeus_prefix_cache_lookups 2" in text
