@@ -40,3 +40,22 @@ def test_continuous_batching_matches_single_requests():
         agree += sum(a == b for a, b in zip(out[rid], alone))
         total += k
     assert agree >= total - 3
+
+
+def test_prefix_cache_warm_equals_cold():
+    """The same prompt twice through the prefix-caching batcher: the second run adopts the first
+    run's pages (same bf16 keys and values the first run attended to) and must produce the same
+    tokens."""
+    cfg = DecoderConfig(hidden_dim=256, num_layers=2, num_heads=2, intermediate_dim=512,
+                        vocab_size=1000, max_seq_len=512, use_bias=False, activation="swiglu",
+                        norm="rmsnorm", pos="rope")
+    m = DecoderLM(cfg, device="cuda", training=False, seed=12)
+    torch.manual_seed(8)
+    prompt = torch.randint(0, 1000, (200,)).tolist()
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=2, decode_splits=1), max_seqs=2,
+                           max_len=256, prefix_cache=True)
+    cold = cb.run()[cb.submit(prompt, 6)]
+    warm = cb.run()[cb.submit(prompt, 6)]
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
+    assert cb.prefix.hits == 1 and warm == cold
