@@ -31,6 +31,10 @@ def main(argv=None) -> dict:
     ap.add_argument("--prompt-max", type=int, default=512)
     ap.add_argument("--new-max", type=int, default=64)
     ap.add_argument("--skip-sequential", action="store_true")
+    ap.add_argument("--system-prompt", type=int, default=0,
+                    help="tokens of a prompt prefix shared by every request")
+    ap.add_argument("--prefix-cache", action="store_true",
+                    help="reuse the cache pages of the shared prefix")
     a = ap.parse_args(argv)
     from coeus_b200.infer.engine import InferenceEngine
     from coeus_b200.infer.scheduler import ContinuousBatcher
@@ -45,10 +49,11 @@ def main(argv=None) -> dict:
     model = DecoderLM(cfg, dev, dtype=dtype, training=False)
     g = torch.Generator().manual_seed(0)
     reqs = []
+    system = torch.randint(0, cfg.vocab_size, (a.system_prompt,), generator=g).tolist()
     for _ in range(a.requests):
-        n = int(torch.randint(4, a.prompt_max + 1, (1,), generator=g))
+        n = int(torch.randint(4, max(5, a.prompt_max - a.system_prompt) + 1, (1,), generator=g))
         k = int(torch.randint(1, a.new_max + 1, (1,), generator=g))
-        reqs.append((torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), k))
+        reqs.append((system + torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), k))
     total_new = sum(k for _, k in reqs)
 
     def sync():
@@ -56,7 +61,8 @@ def main(argv=None) -> dict:
             torch.cuda.synchronize(dev)
 
     cb = ContinuousBatcher(InferenceEngine(model, max_batch=a.max_seqs, use_graph=False),
-                           max_seqs=a.max_seqs, max_len=cfg.max_seq_len)
+                           max_seqs=a.max_seqs, max_len=cfg.max_seq_len,
+                           prefix_cache=a.prefix_cache)
     # warm-up: one short request end to end
     cb.submit(reqs[0][0][:8], 2)
     cb.run()
@@ -74,7 +80,8 @@ def main(argv=None) -> dict:
     out = {"requests": a.requests, "max_seqs": a.max_seqs, "generated_tokens": total_new,
            "batched_tokens_per_s": total_new / t_batch,
            "latency_s": {"p50": ls[len(ls) // 2], "p90": ls[int(len(ls) * 0.9)], "max": ls[-1]},
-           "decode_steps": cb.stats["steps"], "device": str(dev), "data": "synthetic"}
+           "decode_steps": cb.stats["steps"], "device": str(dev), "data": "synthetic",
+           "prefix_cache_hits": cb.prefix.hits if cb.prefix is not None else None}
     if not a.skip_sequential:
         eng = InferenceEngine(model, max_batch=1, use_graph=False)
         eng.generate(torch.tensor(reqs[0][0][:8], device=dev)[None], 2)
