@@ -160,6 +160,21 @@ class ContinuousBatcher:
                                     on_token=on_token))
         return rid
 
+    def cancel(self, rid: int) -> bool:
+        """Drop request ``rid`` wherever it is (waiting or decoding); its pages go back to the
+        pool.  Returns whether it was found."""
+        for r in list(self.waiting):
+            if r.id == rid:
+                self.waiting.remove(r)
+                return True
+        for r in list(self.active.values()):
+            if r.id == rid:
+                self.active.pop(r.slot, None)
+                self.engine.cache.release(r.slot)
+                self.free_slots.append(r.slot)
+                return True
+        return False
+
     def pending(self) -> int:
         return len(self.waiting) + len(self.active)
 

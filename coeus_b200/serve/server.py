@@ -50,6 +50,7 @@ class ServingLoop(Metrics, HealthCheck):
                                          token_chunk=token_chunk, prefix_cache=prefix_cache)
         self._lock = threading.Lock()
         self._inbox: List[tuple] = []
+        self._cancel: List[Future] = []
         self._futures: Dict[int, Future] = {}
         self._t0: Dict[int, float] = {}
         self._stop = threading.Event()
@@ -67,6 +68,12 @@ class ServingLoop(Metrics, HealthCheck):
             self._inbox.append((prompt, max_new_tokens, sampling, fut, time.perf_counter()))
             self.counters["requests"] += 1
         return fut
+
+    def cancel(self, fut: Future) -> None:
+        """Stop working on the request behind ``fut`` (a client that went away or timed out);
+        the future is cancelled and its cache pages are freed at the next step."""
+        with self._lock:
+            self._cancel.append(fut)
 
     def healthy(self) -> bool:
         return self._thread.is_alive() and not self._stop.is_set()
@@ -105,6 +112,16 @@ class ServingLoop(Metrics, HealthCheck):
         while not self._stop.is_set():
             with self._lock:
                 inbox, self._inbox = self._inbox, []
+                cancels, self._cancel = self._cancel, []
+            for fut in cancels:
+                inbox = [it for it in inbox if it[3] is not fut]
+                for rid, f in list(self._futures.items()):
+                    if f is fut:
+                        self.batcher.cancel(rid)
+                        self._futures.pop(rid)
+                        self._t0.pop(rid, None)
+                if not fut.done():
+                    fut.cancel()
             for prompt, n, sampling, fut, t0 in inbox:
                 try:
                     rid = self.batcher.submit(prompt, n, **sampling)
@@ -203,6 +220,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
         try:
             out = await asyncio.wait_for(asyncio.wrap_future(fut), request_timeout_s)
         except asyncio.TimeoutError:
+            loop.cancel(fut)
             raise HTTPException(504, "generation timed out")
         except ProcessingError as e:
             raise HTTPException(422, str(e))

@@ -35,13 +35,25 @@ def test_serving_loop_futures(model):
         for p, o in zip(prompts, outs):
             alone = InferenceEngine(model, max_batch=1).generate(torch.tensor(p)[None], 5)
             assert o == alone[0, len(p):].tolist()
+        # a cancelled request stops and gives its slot and pages back
+        slow = loop.submit([3, 4, 5], 80)
+        import time
+        time.sleep(0.05)
+        loop.cancel(slow)
+        for _ in range(200):
+            if slow.cancelled():
+                break
+            time.sleep(0.01)
+        assert slow.cancelled()
+        assert loop.submit([3, 4, 5], 2).result(timeout=60) is not None
+        assert loop.engine.cache.pages_in_use() == 0 and len(loop.batcher.free_slots) == 2
         bad = loop.submit([1] * 95, 10)           # too long: fails alone
         with pytest.raises(Exception):
             bad.result(timeout=60)
-        assert loop.healthy() and loop.counters["completed"] == 4 and loop.counters["failed"] == 1
+        assert loop.healthy() and loop.counters["completed"] == 5 and loop.counters["failed"] == 1
         assert loop.health().healthy and loop.health().details["kv_pages_in_use"] == 0
         ms = {m.name: m.value for m in loop.metrics()}
-        assert ms["completed"] == 4 and ms["generated_tokens"] == 20 and ms["mean_latency_s"] > 0
+        assert ms["completed"] == 5 and ms["generated_tokens"] == 22 and ms["mean_latency_s"] > 0
     finally:
         loop.close()
     assert not loop.healthy()
