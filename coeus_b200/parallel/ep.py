@@ -206,6 +206,14 @@ class MoEFFN:
         self.w = {k: v.to(dtype) for k, v in self.master.items()}
         self.g = {k: torch.zeros_like(v) for k, v in self.master.items()}
 
+    def routing_stats(self) -> dict:
+        """Load per expert and dropped share of the last forward pass (host numbers)."""
+        if getattr(self, "last_load", None) is None:
+            return {}
+        load = self.last_load.detach().float().cpu()
+        return {"load": load.tolist(), "max_over_mean": float(load.max() * self.E),
+                "dropped": float(self.last_dropped)}
+
     def bind(self, w: dict, g: dict, master: dict) -> None:
         """Use externally owned tensors (keys ``router``, ``gate_up``, ``down``)."""
         self.w, self.g, self.master = w, g, master
@@ -259,6 +267,10 @@ class MoEFFN:
         frac.index_add_(0, expert.reshape(-1).long(), torch.ones(T * self.k, device=x.device))
         frac /= float(T * self.k)
         self.last_aux = self.aux_coef * self.E * (frac * probs.mean(0)).sum()
+        # monitoring (device tensors, read on demand): share of the assignments each expert got
+        # and share that found no capacity slot
+        self.last_load = frac
+        self.last_dropped = (slot < 0).float().mean()
         if save:
             self._saved = dict(x=x, expert=expert, w=w, probs=probs, slot=slot, C=C, frac=frac,
                                ret=b["ret"].clone(), kept=kept)

@@ -271,3 +271,19 @@ def test_expert_parallel_checkpoint_loads_into_one_rank(tmp_path):
             want = torch.from_numpy(res[0][name])
         assert torch.equal(t, want), name
     assert float(opt.v.abs().sum()) > 0
+
+
+def test_routing_stats_report_load_and_drops():
+    import torch
+    from coeus_b200.parallel.ep import ExpertParallel, MoEFFN
+    torch.manual_seed(0)
+    epx = ExpertParallel(None, "cpu")
+    layer = MoEFFN(32, 48, 4, 2, 0.5, epx, dtype=torch.float32)      # capacity well below demand
+    x = torch.randn(256, 32)
+    layer.forward(x, torch.zeros_like(x), save=False)
+    st = layer.routing_stats()
+    assert abs(sum(st["load"]) - 1.0) < 1e-5 and st["max_over_mean"] >= 1.0
+    assert 0.0 < st["dropped"] < 1.0
+    roomy = MoEFFN(32, 48, 4, 2, 8.0, epx, dtype=torch.float32)
+    roomy.forward(x, torch.zeros_like(x), save=False)
+    assert roomy.routing_stats()["dropped"] == 0.0
