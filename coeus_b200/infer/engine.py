@@ -316,7 +316,8 @@ class InferenceEngine:
         if ids.is_cuda:
             torch.cuda.synchronize(ids.device)
         t1 = time.perf_counter()
-        nxt = select(logits, temperature, top_k, top_p, gen)
+        V = self.cfg.vocab_size      # the padding columns of the vocabulary never compete
+        nxt = select(logits[:, :V], temperature, top_k, top_p, gen)
         out[:, S] = nxt
         done = (nxt == eos_id) if eos_id is not None else None
         for i in range(1, max_new_tokens):
@@ -324,7 +325,7 @@ class InferenceEngine:
                 out[:, S + i:] = eos_id
                 break
             logits = self.decode_step(nxt)
-            nxt = select(logits, temperature, top_k, top_p, gen)
+            nxt = select(logits[:, :V], temperature, top_k, top_p, gen)
             if done is not None:                           # a finished sequence stays finished
                 nxt = torch.where(done, torch.full_like(nxt, eos_id), nxt)
                 done = done | (nxt == eos_id)

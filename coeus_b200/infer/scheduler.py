@@ -205,7 +205,8 @@ class ContinuousBatcher:
                                dtype=torch.int32, device=self.device)
             logits = eng.decode_slots(slots, tokens, pos)
             greedy = all(not r.temperature and r.repetition_penalty == 1.0 for r in reqs)
-            nxt = select(logits, 0.0, None, None, None).tolist() if greedy else None
+            V = eng.cfg.vocab_size   # the padding columns of the vocabulary never compete
+            nxt = select(logits[:, :V], 0.0, None, None, None).tolist() if greedy else None
             for i, r in enumerate(reqs):
                 tok = nxt[i] if greedy else int(self._sample(logits[i:i + 1], r)[0])
                 r.push(int(tok))

@@ -153,3 +153,31 @@ def test_prefix_cache_gives_pages_back_under_pressure():
     rid = cb.submit(prompts[-1] + [1, 2], 2)         # the most recent prompt is still cached
     cb.run()
     assert cb.prefix.hits == 1
+
+
+def test_generation_never_picks_a_vocabulary_padding_column():
+    """Vocabulary 90 is padded to 96 columns whose logits are exactly zero; with every real logit
+    pushed below zero the arg-max must still be a real token."""
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    cfg = DecoderConfig(hidden_dim=32, num_layers=1, num_heads=2, intermediate_dim=64,
+                        vocab_size=90, max_seq_len=32)
+    m = DecoderLM(cfg, "cpu", seed=2, dtype=torch.float32, training=False)
+    assert cfg.vocab_padded > cfg.vocab_size
+    name = "token_embed" if cfg.tie_embeddings else "output_proj"
+    fn = m.layout.norm_names[2]
+    u = torch.linspace(0.1, 1.0, 32)
+    if name == "output_proj":                              # every real column is the vector u
+        m.master[name][:, :90] = u[:, None]
+    else:
+        m.master[name][:90] = u[None, :]
+    m.master[fn + "_scale"].zero_()                        # final hidden state = the bias = -u
+    m.master[fn + "_bias"].copy_(-u)                       # so every real logit is -|u|^2 < 0
+    m.sync_working_copy()
+    ids = torch.randint(0, 90, (2, 5))
+    logits = m.forward_logits(ids, last_only=True)
+    assert bool((logits[:, :90] < 0).all()) and bool((logits[:, 90:] == 0).all())
+    out = InferenceEngine(m, max_batch=2).generate(ids, 3)
+    assert int(out.max()) < 90
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=2), max_seqs=2, max_len=32)
+    rid = cb.submit(ids[0].tolist(), 3)
+    assert max(cb.run()[rid]) < 90
