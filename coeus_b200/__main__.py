@@ -235,7 +235,7 @@ def cmd_generate(store, rest: List[str]) -> dict:
         temperature=float(_get(store, "temperature") or 0.0))
     res = {"prompt_ids": ids, "token_ids": out[0, len(ids):].tolist()}
     if tok is not None:
-        res["text"] = tok.decode_ids(res["token_ids"])
+        res["text"] = tok.decode_ids(res["token_ids"], ref_compat=False)
     print(json.dumps(res))
     return res
 

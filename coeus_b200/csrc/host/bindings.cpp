@@ -86,6 +86,9 @@ PYBIND11_MODULE(_coeus_host, m) {
       })
       .def("decode_strings", &BpeTokenizer::decode_strings)
       .def("decode_ids", &BpeTokenizer::decode_ids, py::call_guard<py::gil_scoped_release>())
+      .def("decode_ids_bytes", [](const BpeTokenizer& t, const std::vector<uint32_t>& ids) {
+        return py::bytes(t.decode_ids_bytes(ids));
+      })
       .def("vocab_size", &BpeTokenizer::vocab_size)
       .def("add_token", &BpeTokenizer::add_token)
       .def("remove_token", &BpeTokenizer::remove_token)

@@ -288,6 +288,39 @@ static void decode_one(const std::string& s, std::string& out) {
   out += s;
 }
 
+// The same walk keeping every byte token as its byte, so that a multi-byte character whose bytes
+// were never merged comes back whole (the caller validates the UTF-8 once, at the end).
+std::string BpeTokenizer::decode_ids_bytes(const std::vector<uint32_t>& ids) const {
+  std::string out;
+  for (uint32_t id : ids) {
+    if (id < 4) {   // the special tokens share the ids of the control bytes 0..3: bytes here
+      out.push_back(static_cast<char>(id));
+      continue;
+    }
+    auto it = reverse_vocab_.find(id);
+    if (it == reverse_vocab_.end()) continue;
+    const std::string& s = it->second;
+    // a merged token is the concatenation of its parts' strings: every "<0xNN>" with NN >= 0x80
+    // inside it is a byte token (bytes below 0x80 are stored as themselves, so a lower NN can
+    // only be literal text)
+    for (size_t i = 0; i < s.size();) {
+      if (i + 6 <= s.size() && s.compare(i, 3, "<0x") == 0 && s[i + 5] == '>') {
+        // byte tokens are written with upper-case digits; anything else is literal text
+        auto up = [](char c) { return (c >= '0' && c <= '9') || (c >= 'A' && c <= 'F'); };
+        const int hi = up(s[i + 3]) ? hex_val(s[i + 3]) : -1;
+        const int lo = up(s[i + 4]) ? hex_val(s[i + 4]) : -1;
+        if (hi >= 8 && lo >= 0) {
+          out.push_back(static_cast<char>(hi * 16 + lo));
+          i += 6;
+          continue;
+        }
+      }
+      out.push_back(s[i++]);
+    }
+  }
+  return out;
+}
+
 std::string BpeTokenizer::decode_strings(const std::vector<std::string>& tokens) const {
   std::string out;
   for (const std::string& s : tokens) decode_one(s, out);

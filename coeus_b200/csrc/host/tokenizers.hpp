@@ -48,6 +48,8 @@ class BpeTokenizer {
               std::vector<std::string>* strings = nullptr);
   std::string decode_strings(const std::vector<std::string>& tokens) const;
   std::string decode_ids(const std::vector<uint32_t>& ids) const;
+  // Raw bytes: byte tokens stay bytes (no per-byte lossy conversion); may be invalid UTF-8.
+  std::string decode_ids_bytes(const std::vector<uint32_t>& ids) const;
   size_t vocab_size() const { return vocab_.size(); }
   uint32_t add_token(const std::string& token);
   bool remove_token(const std::string& token);

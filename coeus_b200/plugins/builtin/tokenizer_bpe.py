@@ -58,8 +58,17 @@ class BpeTokenizer(VocabularyTokenizer, SpecialTokenizer):
             out[i, :len(r)] = torch.tensor(r, dtype=torch.int32)
         return out
 
-    def decode_ids(self, ids) -> str:
-        return self._t.decode_ids([int(i) for i in ids])
+    def decode_ids(self, ids, ref_compat: bool = True) -> str:
+        """``ref_compat=True`` is the reference's decoding: a byte token above 0x7F becomes
+        U+FFFD on its own (``String::from_utf8_lossy`` of one byte,
+        plugins/tokenizer-bpe/src/lib.rs:319-342), so characters whose bytes were never merged
+        do not survive, and ids 0..3 print as ``<PAD>`` .. ``<EOS>``.  ``ref_compat=False`` joins
+        the bytes first (ids 0..3 as the control bytes they also are) and decodes once: any text
+        round-trips."""
+        ids = [int(i) for i in ids]
+        if ref_compat:
+            return self._t.decode_ids(ids)
+        return self._t.decode_ids_bytes(ids).decode("utf-8", errors="replace")
 
     # ---- VocabularyTokenizer
     def add_token(self, token: str) -> int:

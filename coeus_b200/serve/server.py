@@ -150,6 +150,19 @@ class ServingLoop(Metrics, HealthCheck):
                 fut.set_result(list(r.output))
 
 
+def _decoder(tokenizer):
+    """ids -> text with the tokenizer's most faithful decoding (the BPE tokenizer's default
+    reproduces the reference's lossy per-byte decoding; serving wants the text back)."""
+    fn = getattr(tokenizer, "decode_ids", None)
+    if fn is None:
+        return tokenizer.decode
+    try:
+        fn([], ref_compat=False)
+        return lambda ids: fn(ids, ref_compat=False)
+    except TypeError:
+        return fn
+
+
 def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int] = None,
                token_chunk: Optional[int] = None, request_timeout_s: float = 120.0,
                prefix_cache: bool = False):
@@ -183,9 +196,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
                           on_token=lambda t: aloop.call_soon_threadsafe(q.put_nowait, t),
                           **sampling)
         fut.add_done_callback(lambda f: aloop.call_soon_threadsafe(q.put_nowait, None))
-        decode = None
-        if tokenizer is not None:
-            decode = getattr(tokenizer, "decode_ids", None) or tokenizer.decode
+        decode = _decoder(tokenizer) if tokenizer is not None else None
         while True:
             tok = await asyncio.wait_for(q.get(), request_timeout_s)
             if tok is None:
@@ -227,8 +238,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
         body = {"token_ids": out, "usage": {"prompt_tokens": len(ids),
                                             "completion_tokens": len(out)}}
         if tokenizer is not None:
-            decode = getattr(tokenizer, "decode_ids", None) or tokenizer.decode
-            body["text"] = decode(out)
+            body["text"] = _decoder(tokenizer)(out)
         return body
 
     @app.get("/health")
