@@ -32,6 +32,7 @@ class Request:
     top_p: Optional[float] = None
     min_p: Optional[float] = None
     repetition_penalty: float = 1.0
+    stop_ids: tuple = ()                 # further token ids that end the request like eos_id
     output: List[int] = field(default_factory=list)
     slot: int = -1
     on_token: Optional[Callable[[int], None]] = None      # called with every new token
@@ -43,8 +44,12 @@ class Request:
 
     @property
     def done(self) -> bool:
-        return len(self.output) >= self.max_new_tokens or (
-            self.eos_id is not None and bool(self.output) and self.output[-1] == self.eos_id)
+        if len(self.output) >= self.max_new_tokens:
+            return True
+        if not self.output:
+            return False
+        last = self.output[-1]
+        return (self.eos_id is not None and last == self.eos_id) or last in self.stop_ids
 
 
 class PrefixCache:
@@ -146,7 +151,7 @@ class ContinuousBatcher:
                temperature: float = 0.0, top_k: Optional[int] = None,
                top_p: Optional[float] = None,
                on_token: Optional[Callable[[int], None]] = None, min_p: Optional[float] = None,
-               repetition_penalty: float = 1.0) -> int:
+               repetition_penalty: float = 1.0, stop_ids=()) -> int:
         prompt = [int(t) for t in prompt]
         if not prompt:
             raise ProcessingError.invalid_input("empty prompt")
@@ -157,6 +162,7 @@ class ContinuousBatcher:
         self._next_id += 1
         self.waiting.append(Request(rid, prompt, max_new_tokens, eos_id, temperature, top_k, top_p,
                                     min_p=min_p, repetition_penalty=repetition_penalty,
+                                    stop_ids=tuple(int(t) for t in (stop_ids or ())),
                                     on_token=on_token))
         return rid
 

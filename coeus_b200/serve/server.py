@@ -33,6 +33,7 @@ try:        # the request schema lives at module level so that FastAPI can resol
         eos_id: Optional[int] = None
         min_p: Optional[float] = None
         repetition_penalty: float = 1.0
+        stop_ids: Optional[List[int]] = None
         stream: bool = False
 except ImportError:      # ServingLoop works without the HTTP stack
     CompletionRequest = None
@@ -223,7 +224,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
             raise HTTPException(422, f"token ids must lie in [0, {V}) and the prompt be non-empty")
         sampling = dict(eos_id=req.eos_id, temperature=req.temperature, top_k=req.top_k,
                         top_p=req.top_p, min_p=req.min_p,
-                        repetition_penalty=req.repetition_penalty)
+                        repetition_penalty=req.repetition_penalty, stop_ids=req.stop_ids or ())
         if req.stream:
             return StreamingResponse(_stream(ids, req.max_tokens, sampling),
                                      media_type="text/event-stream")

@@ -78,6 +78,10 @@ def test_continuous_batching_matches_one_request_at_a_time(kind):
     rid = cb.submit(prompts[1], 7, eos_id=first)
     got = cb.run()[rid]
     assert got == alone[1][:alone[1].index(first) + 1]
+    rid = cb.submit(prompts[1], 7, stop_ids=[alone[1][3], alone[1][1]])
+    got = cb.run()[rid]
+    cut = min(alone[1].index(alone[1][3]), alone[1].index(alone[1][1]))
+    assert got == alone[1][:cut + 1]
     with pytest.raises(Exception):
         cb.submit([1] * 200, 10)
     # a strong repetition penalty: no token is produced twice while unseen ones remain
