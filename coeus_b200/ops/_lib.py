@@ -7,6 +7,7 @@ PyTorch implementation on a GPU box.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional
 
@@ -36,7 +37,56 @@ def lib() -> ctypes.CDLL:
                             f"CUDA kernel library {path} is missing and could not be built: {e}"
                         ) from e
                 _lib = ctypes.CDLL(str(path))
-    return _lib
+    return _traced if _traced is not None else _lib
+
+
+class _TracedLib:
+    """The kernel library with an NVTX range around every ``cb_*`` call, named after the entry
+    point, so that a timeline shows each op of a step (host-side launch ranges; off unless
+    ``COEUS_NVTX=1`` or :func:`set_op_ranges`)."""
+
+    def __init__(self, get_cdll, push, pop) -> None:
+        self._get, self._push, self._pop = get_cdll, push, pop
+
+    def __getattr__(self, name: str):
+        fn = getattr(self._get(), name)
+        if not name.startswith("cb_"):
+            return fn
+        push, pop = self._push, self._pop
+
+        def traced(*args):
+            push(name)
+            try:
+                return fn(*args)
+            finally:
+                pop()
+        self.__dict__[name] = traced        # resolved once per entry point
+        return traced
+
+
+_traced: Optional[_TracedLib] = None
+
+
+def set_op_ranges(on: bool, push=None, pop=None) -> None:
+    """Turn the per-op NVTX ranges on or off.  ``push(name)`` / ``pop()`` default to
+    ``torch.cuda.nvtx.range_push`` / ``range_pop`` (tests pass recorders)."""
+    global _traced
+    if not on:
+        _traced = None
+        return
+
+    def cdll():
+        global _traced
+        keep, _traced = _traced, None       # lib() must hand out the real library here
+        try:
+            return lib()
+        finally:
+            _traced = keep
+    _traced = _TracedLib(cdll, push or torch.cuda.nvtx.range_push, pop or torch.cuda.nvtx.range_pop)
+
+
+if os.environ.get("COEUS_NVTX") == "1" and torch.cuda.is_available():
+    set_op_ranges(True)
 
 
 def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:

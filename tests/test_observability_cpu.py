@@ -89,3 +89,38 @@ def test_rank_prefixed_logging():
     setup_logging(logging.INFO, rank=5, world=8, all_ranks=True, stream=buf)
     get_logger().info("everyone")
     assert "everyone" in buf.getvalue()
+
+
+def test_per_op_ranges_wrap_every_kernel_entry_point(monkeypatch):
+    from coeus_b200.ops import _lib
+
+    class Fake:
+        def __init__(self):
+            self.calls = []
+
+        def cb_gemm(self, a, b):
+            self.calls.append(("gemm", a, b))
+            return 0
+
+        def cb_fails(self):
+            raise RuntimeError("boom")
+
+        other = staticmethod(lambda: 7)
+
+    fake = Fake()
+    monkeypatch.setattr(_lib, "_lib", fake)
+    log = []
+    _lib.set_op_ranges(True, push=lambda n: log.append(("push", n)), pop=lambda: log.append(("pop",)))
+    try:
+        assert _lib.lib().cb_gemm(1, 2) == 0 and _lib.lib().cb_gemm(3, 4) == 0
+        assert _lib.lib().other() == 7                       # not an op: not wrapped
+        try:
+            _lib.lib().cb_fails()
+        except RuntimeError:
+            pass
+        assert log == [("push", "cb_gemm"), ("pop",), ("push", "cb_gemm"), ("pop",),
+                       ("push", "cb_fails"), ("pop",)]       # the range closes on errors too
+        assert fake.calls == [("gemm", 1, 2), ("gemm", 3, 4)]
+    finally:
+        _lib.set_op_ranges(False)
+    assert _lib.lib() is fake
