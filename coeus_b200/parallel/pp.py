@@ -313,6 +313,30 @@ class InterleavedPipelineStage:
     def _virtual(self, c: int) -> int:
         return c * self.stages + self.stage
 
+    def _state(self) -> dict:
+        from ..checkpoint.named import model_state
+        st: dict = {}
+        for m, opt in zip(self.models, self.opts):
+            st.update(model_state(m, opt))
+        return st
+
+    def save_checkpoint(self, directory: str) -> None:
+        """Name-keyed checkpoint of all chunks of this rank; loads into any pipeline shape."""
+        from ..checkpoint.named import save_named
+        save_named(directory, self.stage, self._state(),
+                   {"stages": self.stages, "chunks": self.v, "opt_step": self.opts[0].step_count,
+                    "train_step": self.step_index, "config": self.cfg.to_dict()},
+                   lambda: dist.barrier(group=self.group))
+
+    def load_checkpoint(self, directory: str) -> dict:
+        from ..checkpoint.named import load_named
+        man = load_named(directory, self._state())
+        for m, opt in zip(self.models, self.opts):
+            m.sync_working_copy()
+            opt.step_count = int(man["opt_step"])
+        self.step_index = int(man["train_step"])
+        return man
+
     def train_step(self, ids: Optional[torch.Tensor], targets: Optional[torch.Tensor]) -> torch.Tensor:
         """One optimizer step over ``M`` micro-batches; ``ids [M, b, S]`` is read on the first
         rank, ``targets`` on the last.  Returns the mean loss on the last rank."""

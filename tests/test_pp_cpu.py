@@ -162,6 +162,15 @@ def _worker_interleaved(rank, world, port, ids, tgt, out):
     st = InterleavedPipelineStage(cfg, dist.group.WORLD, "cpu", micro_batches=ids.shape[0],
                                   chunks=2, seed=4, dtype=torch.float32, train_cfg=_train_cfg())
     losses = [float(st.train_step(ids, tgt)) for _ in range(2)]
+    # checkpoint of an interleaved stage: reload into a differently seeded copy, same next step
+    import tempfile
+    tmp = os.path.join(tempfile.gettempdir(), f"coeus_ipp_{port}")
+    st.save_checkpoint(tmp)
+    other = InterleavedPipelineStage(cfg, dist.group.WORLD, "cpu", micro_batches=ids.shape[0],
+                                     chunks=2, seed=99, dtype=torch.float32, train_cfg=_train_cfg())
+    assert other.load_checkpoint(tmp)["train_step"] == 2
+    for a_, b_ in zip(st.models, other.models):
+        assert torch.equal(a_.p32, b_.p32)
     params = {}
     for m in st.models:
         params.update({k: v.numpy().copy() for k, v in m.master.items()})
