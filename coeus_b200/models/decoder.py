@@ -64,6 +64,10 @@ class ParamLayout:
         """``layers=(lo, hi)``, ``embed`` and ``head`` restrict the list to one pipeline stage:
         blocks ``lo..hi-1`` (named by their index in the whole model), with or without the
         embedding, and with or without the final norm and LM head."""
+        if tp != 1:
+            raise ProcessingError.unsupported(
+                "a tensor-parallel ParamLayout",
+                "tensor-parallel shards are laid out by parallel.tp_model.TPDecoderLM")
         self.cfg = cfg
         self.ep = ep
         self.layer_ids = list(range(*(layers if layers is not None else (0, cfg.num_layers))))

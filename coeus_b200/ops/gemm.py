@@ -46,7 +46,7 @@ def use_cta_pairs(on: bool) -> None:
     _PAIRS = bool(on)
 
 
-def _pick_bn(M: int, N: int, ksplit: int, sms: int = 148) -> int:
+def _pick_bn(M: int, N: int) -> int:
     """N tile of the GEMM: 256 whenever N allows it (a 128-wide tile halves the arithmetic
     intensity per shared-memory byte and measured ~30 % slower per FLOP, which outweighs the
     better wave quantisation it sometimes gives).  The value 512 stands for "256 wide on CTA
@@ -128,7 +128,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if _discard:   # profiling aid: run the main loop, drop the result
         out_mode = 3
     if bn is None:
-        bn = _pick_bn(M, N, ksplit)
+        bn = _pick_bn(M, N)
     aux = aux_in if aux_in is not None else aux_out
     st = _lib.status_buffer(a.device)
     rc = _lib.lib().cb_gemm_bf16(
@@ -178,7 +178,7 @@ def gemm_grouped(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: 
             raise ValueError("gemm_grouped: operands must be bf16")
     out_mode = _OUT_F32_ATOMIC if accumulate else (
         _OUT_F32 if out.dtype == torch.float32 else _OUT_BF16)
-    bn = _pick_bn(M, N, ksplit)
+    bn = _pick_bn(M, N)
     st = _lib.status_buffer(a.device)
     rc = _lib.lib().cb_gemm_bf16_grouped(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), Gn, M, N, K, a.stride(1), b.stride(1),
@@ -192,7 +192,7 @@ def linear_wgrad_grouped(x: torch.Tensor, dy: torch.Tensor, grad_w: torch.Tensor
                          max_ctas: int = 0) -> torch.Tensor:
     """``grad_w[g][in,out] += x[g][T,in]^T @ dy[g][T,out]`` for all groups in one launch."""
     Gn, T, Min, Nout = x.shape[0], x.shape[1], x.shape[2], dy.shape[2]
-    if _pick_bn(Min, Nout, 1) == 512 and Min % 256 == 0:     # CTA pairs: 256-row tiles, 74 units
+    if _pick_bn(Min, Nout) == 512 and Min % 256 == 0:     # CTA pairs: 256-row tiles, 74 units
         ksplit = _pick_ksplit(Gn * (Min // 256) * ((Nout + 255) // 256), (T + 63) // 64, sms=74)
     else:
         ksplit = _pick_ksplit(Gn * ((Min + 127) // 128) * ((Nout + 255) // 256), (T + 63) // 64)
@@ -221,7 +221,7 @@ def linear_wgrad(x: torch.Tensor, dy: torch.Tensor, grad_w: torch.Tensor, *,
     """``grad_w[in,out] += x[T,in]^T @ dy[T,out]`` accumulated in fp32."""
     T = x.shape[0]
     if ksplit is None:
-        bn = _pick_bn(x.shape[1], dy.shape[1], 1)
+        bn = _pick_bn(x.shape[1], dy.shape[1])
         if bn == 512:     # CTA pairs: 256-row tiles scheduled over half as many units
             tiles = ((x.shape[1] + 255) // 256) * ((dy.shape[1] + 255) // 256)
             ksplit = _pick_ksplit(tiles, (T + 63) // 64, sms=74)
