@@ -29,7 +29,8 @@ DEFAULTS: Dict[str, Any] = {
                  "micro_batches": 1, "pp_chunks": 1, "zero_stage": 2},
     "train": {"steps": 20, "batch": 4, "seq_len": 128, "lr": 3e-4, "warmup": 0, "grad_clip": 0.0,
               "weight_decay": 0.01, "seed": 0, "log_every": 5, "checkpoint_dir": "",
-              "checkpoint_every": 0, "save": "", "resume": False},
+              "checkpoint_every": 0, "save": "", "resume": False, "watchdog": True,
+              "fault": ""},
     "data": {"files": "", "binary": "", "binary_dtype": "uint16"},
     "device": "auto",
 }
@@ -158,6 +159,12 @@ def cmd_train(store) -> dict:
         epoch, skip = divmod(step, per_epoch)       # continue inside the epoch that was running
         log.info("resumed from %s at step %d (epoch %d, batch %d)", ckpt_dir, step, epoch, skip)
     resumed_at = step
+    from .parallel.health import FaultInjector, StepWatchdog
+    import time as _time
+    watchdog = StepWatchdog() if _get(store, "train.watchdog") else None
+    # host-side fault injection for resume drills: --train.fault=after_step:7 raises there
+    injector = FaultInjector(str(_get(store, "train.fault") or "") or None)
+    slow = 0
     while step < steps:
         ds.reset(epoch)
         if skip:
@@ -167,9 +174,15 @@ def cmd_train(store) -> dict:
         for ids, tgt in ds:
             got = True
             ids, tgt = ids.to(device), tgt.to(device)
+            t_step = _time.perf_counter()
             loss = float(run.step(ids, tgt))
             losses.append(loss)
             step += 1
+            if watchdog is not None and watchdog.observe(_time.perf_counter() - t_step):
+                slow += 1
+                log.warning("step %d took %.3f s, far above the recent median", step,
+                            _time.perf_counter() - t_step)
+            injector.reach("after_step")
             if step % max(1, _get(store, "train.log_every")) == 0:
                 log.info("step %d loss %.4f", step, loss)
             if ckpt_dir and every and step % every == 0 and hasattr(run.trainer, "save_checkpoint"):
@@ -191,7 +204,7 @@ def cmd_train(store) -> dict:
         run.model.save(save)
     out = {"strategy": run.strategy, "steps": step, "resumed_at": resumed_at,
            "first_loss": losses[0] if losses else None,
-           "last_loss": losses[-1] if losses else None, "world": world}
+           "last_loss": losses[-1] if losses else None, "world": world, "slow_steps": slow}
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

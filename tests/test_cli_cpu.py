@@ -67,14 +67,19 @@ def test_train_two_ranks_under_torchrun(tmp_path):
     assert os.path.exists(tmp_path / "ck" / "manifest.json")
 
 
-def test_resume_continues_the_interrupted_run(tmp_path):
+def test_injected_fault_then_resume_matches_the_uninterrupted_run(tmp_path):
+    """A host-side fault after step 7 kills the run; the restart picks up the step-5 checkpoint
+    and ends where the uninterrupted run ends."""
     text = tmp_path / "corpus.txt"
     text.write_text("\n".join(["the cat sat on the mat", "the dog sat on the log",
                                "a cat and a dog and a mat"] * 80))
-    common = SMALL + [f"--data.files={text}", "--train.checkpoint_every=5"]
-    whole = _run(["train"] + common + ["--train.steps=10", f"--train.checkpoint_dir={tmp_path}/a"])
-    _run(["train"] + common + ["--train.steps=5", f"--train.checkpoint_dir={tmp_path}/b"])
-    rest = _run(["train"] + common + ["--train.steps=10", f"--train.checkpoint_dir={tmp_path}/b",
+    common = SMALL + [f"--data.files={text}", "--train.checkpoint_every=5", "--train.steps=10"]
+    whole = _run(["train"] + common + [f"--train.checkpoint_dir={tmp_path}/a"])
+    env = {**os.environ, "PYTHONPATH": ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")}
+    crash = subprocess.run([sys.executable, "-m", "coeus_b200", "train"] + common +
+                           [f"--train.checkpoint_dir={tmp_path}/b", "--train.fault=after_step:7"],
+                           capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    assert crash.returncode != 0 and "after_step" in crash.stderr
+    rest = _run(["train"] + common + [f"--train.checkpoint_dir={tmp_path}/b",
                                       "--train.resume=true"])
-    assert rest["resumed_at"] == 5 and rest["steps"] == 10
-    assert abs(rest["last_loss"] - whole["last_loss"]) < 1e-5
+    assert rest["resumed_at"] == 5 and abs(rest["last_loss"] - whole["last_loss"]) < 1e-5
