@@ -165,6 +165,10 @@ def cmd_train(store) -> dict:
     # host-side fault injection for resume drills: --train.fault=after_step:7 raises there
     injector = FaultInjector(str(_get(store, "train.fault") or "") or None)
     slow = 0
+    from .utils.metrics import model_flops_per_token
+    flops_tok = model_flops_per_token(cfg, S, True)
+    t_run, tok_run = _time.perf_counter(), 0
+    t_log, tok_log = t_run, 0
     while step < steps:
         ds.reset(epoch)
         if skip:
@@ -183,8 +187,14 @@ def cmd_train(store) -> dict:
                 log.warning("step %d took %.3f s, far above the recent median", step,
                             _time.perf_counter() - t_step)
             injector.reach("after_step")
+            tok_run += ids.numel()
+            tok_log += ids.numel()
             if step % max(1, _get(store, "train.log_every")) == 0:
-                log.info("step %d loss %.4f", step, loss)
+                now = _time.perf_counter()      # float(loss) above already waited for the device
+                tps = tok_log / max(now - t_log, 1e-9)
+                log.info("step %d loss %.4f  %.0f tokens/s  %.2f TFLOP/s", step, loss, tps,
+                         tps * flops_tok / 1e12)
+                t_log, tok_log = now, 0
             if ckpt_dir and every and step % every == 0 and hasattr(run.trainer, "save_checkpoint"):
                 run.trainer.save_checkpoint(ckpt_dir)
             if step >= steps:
@@ -204,7 +214,8 @@ def cmd_train(store) -> dict:
         run.model.save(save)
     out = {"strategy": run.strategy, "steps": step, "resumed_at": resumed_at,
            "first_loss": losses[0] if losses else None,
-           "last_loss": losses[-1] if losses else None, "world": world, "slow_steps": slow}
+           "last_loss": losses[-1] if losses else None, "world": world, "slow_steps": slow,
+           "tokens_per_s": tok_run / max(_time.perf_counter() - t_run, 1e-9)}
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
