@@ -302,23 +302,43 @@ def cmd_eval(store) -> dict:
 
 
 def cmd_serve(store) -> int:
-    import uvicorn
+    """One process: a single-GPU engine behind HTTP.  Under ``torchrun`` the ranks form one
+    tensor-parallel group: every rank holds its shards and runs the serving loop, rank 0 also
+    runs the HTTP server and feeds the others."""
+    import torch
 
     from .checkpoint.formats import load_model
     from .models.decoder import DecoderLM
-    from .serve import create_app
-    import torch
+    from .serve import ServingLoop, create_app
     device = _device(store)
+    rank, world, device = _init_distributed(device)
     weights = _get(store, "weights")
+    dtype = torch.bfloat16 if device.startswith("cuda") else torch.float32
     if weights:
-        model, _ = load_model(str(weights), device=device)
+        model, _ = load_model(str(weights), device=device if world == 1 else "cpu")
     else:
-        dtype = torch.bfloat16 if device.startswith("cuda") else torch.float32
-        model = DecoderLM(_model_config(store), device, dtype=dtype, training=False)
+        model = DecoderLM(_model_config(store), device if world == 1 else "cpu",
+                          dtype=dtype if world == 1 else torch.float32, training=False)
+    max_seqs = int(_get(store, "max_seqs") or 16)
+    kw = dict(max_seqs=max_seqs, max_len=model.cfg.max_seq_len)
+    engine = group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        from .infer.tp_engine import TPInferenceEngine
+        from .parallel.tp import TensorParallel
+        from .parallel.tp_model import TPDecoderLM
+        group = dist.group.WORLD
+        tpm = TPDecoderLM(model.cfg, TensorParallel(group, device), device, dtype=dtype, full=model)
+        engine = TPInferenceEngine(tpm, max_batch=max_seqs, use_graph=False)
+        if rank != 0:
+            loop = ServingLoop(None, engine=engine, group=group, **kw)
+            loop.join()
+            return 0
+    import uvicorn
     app = create_app(model, tokenizer=_load_tokenizer(store, str(weights) if weights else ""),
-                     max_seqs=int(_get(store, "max_seqs") or 16),
-                     prefix_cache=bool(_get(store, "prefix_cache")),
-                     max_len=model.cfg.max_seq_len)
+                     prefix_cache=bool(_get(store, "prefix_cache")), engine=engine, group=group,
+                     **kw)
     uvicorn.run(app, host=str(_get(store, "host") or "127.0.0.1"),
                 port=int(_get(store, "port") or 8000))
     return 0

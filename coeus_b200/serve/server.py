@@ -45,8 +45,20 @@ class ServingLoop(Metrics, HealthCheck):
 
     def __init__(self, model, max_seqs: int = 16, max_len: Optional[int] = None,
                  token_chunk: Optional[int] = None, idle_sleep_s: float = 0.002,
-                 prefix_cache: bool = False) -> None:
-        self.engine = InferenceEngine(model, max_batch=max_seqs, use_graph=False)
+                 prefix_cache: bool = False, engine=None, group=None) -> None:
+        """``engine``: a ready engine instead of a single-GPU one built from ``model`` (e.g. a
+        :class:`coeus_b200.infer.tp_engine.TPInferenceEngine`).  ``group``: the process group of a
+        tensor-parallel engine; every rank of it runs a loop, rank 0 of the group takes the
+        requests and sends each iteration's submissions and cancellations to the others, so all
+        ranks feed their batcher the same events in the same order and step together."""
+        self.engine = engine if engine is not None else InferenceEngine(
+            model, max_batch=max_seqs, use_graph=False)
+        self.group = group
+        self.leader = True
+        if group is not None:
+            import torch.distributed as dist
+            self.leader = dist.get_rank(group) == 0
+            self._src = dist.get_global_rank(group, 0)
         self.batcher = ContinuousBatcher(self.engine, max_seqs=max_seqs, max_len=max_len,
                                          token_chunk=token_chunk, prefix_cache=prefix_cache)
         self._lock = threading.Lock()
@@ -102,35 +114,73 @@ class ServingLoop(Metrics, HealthCheck):
             self.counters[k] = 0.0 if k == "latency_s_sum" else 0
 
     def close(self) -> None:
+        """Leader: ends the loop on every rank (the stop travels with the next exchange)."""
         self._stop.set()
         self._thread.join(timeout=30)
+
+    def join(self, timeout: Optional[float] = None) -> None:
+        """Block until the loop ends (what the follower ranks of a tensor-parallel group do)."""
+        self._thread.join(timeout)
+
+    def _exchange(self, events: list) -> list:
+        """Tensor-parallel groups: the leader's events of this iteration, on every rank."""
+        if self.group is None:
+            return events
+        import torch.distributed as dist
+        box = [events if self.leader else None]
+        dist.broadcast_object_list(box, src=self._src, group=self.group)
+        return box[0]
 
     def _run(self) -> None:
         device = self.engine.m.device
         if device.type == "cuda":
             import torch
             torch.cuda.set_device(device)
-        while not self._stop.is_set():
-            with self._lock:
-                inbox, self._inbox = self._inbox, []
-                cancels, self._cancel = self._cancel, []
-            for fut in cancels:
-                inbox = [it for it in inbox if it[3] is not fut]
-                for rid, f in list(self._futures.items()):
-                    if f is fut:
-                        self.batcher.cancel(rid)
-                        self._futures.pop(rid)
-                        self._t0.pop(rid, None)
-                if not fut.done():
-                    fut.cancel()
-            for prompt, n, sampling, fut, t0 in inbox:
-                try:
-                    rid = self.batcher.submit(prompt, n, **sampling)
-                    self._futures[rid] = fut
-                    self._t0[rid] = t0
-                except Exception as e:          # a bad request fails alone
-                    self.counters["failed"] += 1
-                    fut.set_exception(e)
+        pending_futs: List[tuple] = []          # leader: futures of this iteration's submits
+        while True:
+            events: list = []
+            if self.leader:
+                with self._lock:
+                    inbox, self._inbox = self._inbox, []
+                    cancels, self._cancel = self._cancel, []
+                for fut in cancels:
+                    inbox = [it for it in inbox if it[3] is not fut]
+                    for rid, f in list(self._futures.items()):
+                        if f is fut:
+                            events.append(("cancel", rid))
+                            self._futures.pop(rid)
+                            self._t0.pop(rid, None)
+                    if not fut.done():
+                        fut.cancel()
+                pending_futs = []
+                for prompt, n, sampling, fut, t0 in inbox:
+                    cb = sampling.pop("on_token", None)
+                    events.append(("submit", list(prompt), int(n), dict(sampling)))
+                    pending_futs.append((fut, t0, cb))
+                if self._stop.is_set():
+                    events.append(("stop",))
+            events = self._exchange(events)
+            stop, k = False, 0
+            for ev in events:
+                if ev[0] == "stop":
+                    stop = True
+                elif ev[0] == "cancel":
+                    self.batcher.cancel(ev[1])
+                else:
+                    fut, t0, cb = pending_futs[k] if self.leader else (None, 0.0, None)
+                    k += 1
+                    try:
+                        rid = self.batcher.submit(ev[1], ev[2], on_token=cb, **ev[3])
+                        if self.leader:
+                            self._futures[rid] = fut
+                            self._t0[rid] = t0
+                    except Exception as e:      # a bad request fails alone (on every rank alike)
+                        if self.leader:
+                            self.counters["failed"] += 1
+                            fut.set_exception(e)
+            if stop:
+                self._stop.set()
+                return
             if not self.batcher.pending():
                 time.sleep(self._idle)
                 continue
@@ -143,6 +193,8 @@ class ServingLoop(Metrics, HealthCheck):
                 self._futures.clear()
                 self._stop.set()
                 return
+            if not self.leader:
+                continue
             for r in done:
                 fut = self._futures.pop(r.id)
                 self.counters["completed"] += 1
@@ -166,7 +218,7 @@ def _decoder(tokenizer):
 
 def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int] = None,
                token_chunk: Optional[int] = None, request_timeout_s: float = 120.0,
-               prefix_cache: bool = False):
+               prefix_cache: bool = False, engine=None, group=None):
     """FastAPI application.  ``tokenizer`` (anything with ``encode(str) -> ids`` and
     ``decode_ids(ids) -> str`` or ``decode(ids) -> str``) enables text prompts; without it requests carry ``prompt_ids``."""
     import asyncio
@@ -177,7 +229,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
     from contextlib import asynccontextmanager
 
     loop = ServingLoop(model, max_seqs=max_seqs, max_len=max_len, token_chunk=token_chunk,
-                       prefix_cache=prefix_cache)
+                       prefix_cache=prefix_cache, engine=engine, group=group)
 
     @asynccontextmanager
     async def lifespan(_app):
@@ -219,7 +271,7 @@ def create_app(model, tokenizer=None, max_seqs: int = 16, max_len: Optional[int]
             ids = [int(t) for t in tokenizer.encode(req.prompt)]
         else:
             raise HTTPException(422, "give prompt_ids, or prompt when the server has a tokenizer")
-        V = model.cfg.vocab_size
+        V = loop.engine.cfg.vocab_size
         if not ids or any(t < 0 or t >= V for t in ids):
             raise HTTPException(422, f"token ids must lie in [0, {V}) and the prompt be non-empty")
         sampling = dict(eos_id=req.eos_id, temperature=req.temperature, top_k=req.top_k,

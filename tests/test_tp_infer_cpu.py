@@ -95,3 +95,47 @@ def test_tp_continuous_batching_matches_single_rank_engine():
             for p, k in zip(prompts, budgets)]
     for rank, got in run_ranks(_worker_serving, 2, (prompts, budgets), results=2):
         assert got == want, rank
+
+
+def _worker_tp_serving(rank, world, port, prompts, budgets, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.infer.tp_engine import TPInferenceEngine
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM
+    from coeus_b200.serve import ServingLoop
+    full = DecoderLM(_cfg(), "cpu", seed=5, dtype=torch.float32, training=False)
+    tp = TensorParallel(dist.group.WORLD, "cpu", backend="nccl")
+    m = TPDecoderLM(_cfg(), tp, "cpu", dtype=torch.float32, full=full)
+    loop = ServingLoop(None, max_seqs=2, max_len=64, engine=TPInferenceEngine(m, max_batch=2),
+                       group=dist.group.WORLD)
+    if rank == 0:                       # the leader takes the requests ...
+        futs = [loop.submit(p, k) for p, k in zip(prompts, budgets)]
+        res = [f.result(timeout=120) for f in futs]
+        slow = loop.submit(prompts[0], 40)
+        loop.cancel(slow)               # ... and cancellations and the stop reach the followers
+        late = loop.submit(prompts[1], 2).result(timeout=120)
+        loop.close()
+        out.put((rank, res, late, loop.counters["completed"]))
+    else:
+        loop.join(timeout=200)          # followers step along until the leader stops the loop
+        assert not loop.healthy()
+        out.put((rank, None, None, 0))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_serving_loop_leader_and_follower():
+    from mp_util import run_ranks
+    from coeus_b200.infer.engine import InferenceEngine
+    from coeus_b200.models.decoder import DecoderLM
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, 96, (n,)).tolist() for n in (5, 11, 3)]
+    budgets = [4, 6, 2]
+    full = DecoderLM(_cfg(), "cpu", seed=5, dtype=torch.float32, training=False)
+    want = [InferenceEngine(full, max_batch=1).generate(torch.tensor(p)[None], k)[0, len(p):].tolist()
+            for p, k in zip(prompts, budgets)]
+    res = {r[0]: r for r in run_ranks(_worker_tp_serving, 2, (prompts, budgets), results=2)}
+    assert res[0][1] == want and res[0][2] == want[1][:2] and res[0][3] == 4
