@@ -30,7 +30,7 @@ DEFAULTS: Dict[str, Any] = {
     "train": {"steps": 20, "batch": 4, "seq_len": 128, "lr": 3e-4, "warmup": 0, "grad_clip": 0.0,
               "weight_decay": 0.01, "seed": 0, "log_every": 5, "checkpoint_dir": "",
               "checkpoint_every": 0, "save": "", "resume": False, "watchdog": True,
-              "fault": ""},
+              "fault": "", "metrics_file": ""},
     "data": {"files": "", "binary": "", "binary_dtype": "uint16"},
     "device": "auto",
 }
@@ -165,7 +165,11 @@ def cmd_train(store) -> dict:
     # host-side fault injection for resume drills: --train.fault=after_step:7 raises there
     injector = FaultInjector(str(_get(store, "train.fault") or "") or None)
     slow = 0
-    from .utils.metrics import model_flops_per_token
+    from .utils.metrics import EventBus, JsonlSink, model_flops_per_token
+    bus = EventBus()
+    if _get(store, "train.metrics_file") and rank == 0:      # one JSON line per step
+        bus.subscribe(JsonlSink(str(_get(store, "train.metrics_file"))))
+    bus.emit("TrainingEvent::Started", strategy=run.strategy, world=world, resumed_at=step)
     flops_tok = model_flops_per_token(cfg, S, True)
     t_run, tok_run = _time.perf_counter(), 0
     t_log, tok_log = t_run, 0
@@ -189,6 +193,8 @@ def cmd_train(store) -> dict:
             injector.reach("after_step")
             tok_run += ids.numel()
             tok_log += ids.numel()
+            bus.emit("TrainingEvent::StepCompleted", step=step, loss=loss,
+                     seconds=_time.perf_counter() - t_step, tokens=ids.numel())
             if step % max(1, _get(store, "train.log_every")) == 0:
                 now = _time.perf_counter()      # float(loss) above already waited for the device
                 tps = tok_log / max(now - t_log, 1e-9)

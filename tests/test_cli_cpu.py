@@ -33,9 +33,15 @@ def test_train_on_text_save_and_generate(tmp_path):
     text = tmp_path / "corpus.txt"
     text.write_text("\n".join(["the cat sat on the mat", "the dog sat on the log"] * 60))
     weights = tmp_path / "m.safetensors"
+    metrics = tmp_path / "metrics.jsonl"
     out = _run(["train"] + SMALL + ["--train.steps=12", f"--data.files={text}",
-                                    f"--train.save={weights}", "--train.warmup=2"])
+                                    f"--train.save={weights}", "--train.warmup=2",
+                                    f"--train.metrics_file={metrics}"])
     assert out["strategy"] == "single" and out["steps"] == 12
+    events = [json.loads(l) for l in metrics.read_text().splitlines()]
+    assert events[0]["event"] == "TrainingEvent::Started"
+    steps_logged = [e for e in events if e["event"] == "TrainingEvent::StepCompleted"]
+    assert [e["step"] for e in steps_logged] == list(range(1, 13)) and steps_logged[0]["tokens"] == 64
     assert out["last_loss"] < out["first_loss"]
     gen = _run(["generate", "--device=cpu", f"--weights={weights}", "--prompt_ids=5,6,7",
                 "--max_tokens=4"])
