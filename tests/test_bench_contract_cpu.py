@@ -42,3 +42,15 @@ def test_multi_gpu_request_without_launcher_is_refused_cleanly():
                        capture_output=True, text=True, timeout=300, env=env)
     # either the clean refusal (no launcher) or, on a box without CUDA, a CUDA error before it
     assert r.returncode != 0
+
+
+def test_packaging_metadata_points_at_real_files():
+    import glob
+    import tomllib
+    with open(os.path.join(ROOT, "pyproject.toml"), "rb") as f:
+        meta = tomllib.load(f)
+    assert meta["project"]["name"] == "coeus_b200"
+    mod, fn = meta["project"]["scripts"]["coeus"].split(":")
+    assert callable(getattr(__import__(mod, fromlist=[fn]), fn))
+    for pattern in meta["tool"]["setuptools"]["package-data"]["coeus_b200"]:
+        assert glob.glob(os.path.join(ROOT, "coeus_b200", pattern)), pattern
