@@ -16,7 +16,7 @@ from typing import Callable, Deque, Dict, List, Optional
 
 import torch
 
-from ..foundation.error import ProcessingError
+from ..foundation.error import Error, ProcessingError
 from .engine import InferenceEngine
 from .sampler import select
 
@@ -36,6 +36,7 @@ class Request:
     output: List[int] = field(default_factory=list)
     slot: int = -1
     on_token: Optional[Callable[[int], None]] = None      # called with every new token
+    error: Optional[BaseException] = None                  # set when the request failed alone
 
     def push(self, tok: int) -> None:
         self.output.append(tok)
@@ -194,7 +195,14 @@ class ContinuousBatcher:
             r = self.waiting.popleft()
             r.slot = self.free_slots.pop()
             ids = torch.tensor(r.prompt, dtype=torch.int64, device=self.device)
-            logits = self._prefill(r, ids)
+            try:
+                logits = self._prefill(r, ids)
+            except Error as e:           # a framework error (e.g. no pages): this request only
+                eng.cache.release(r.slot)
+                self.free_slots.append(r.slot)
+                r.slot, r.error = -1, e
+                finished.append(r)
+                continue
             r.push(int(self._sample(logits[None], r)[0]))
             self.stats["prefills"] += 1
             if r.done:
@@ -229,6 +237,8 @@ class ContinuousBatcher:
         out: Dict[int, List[int]] = {}
         while self.pending():
             for r in self.step():
+                if r.error is not None:
+                    raise r.error
                 out[r.id] = r.output
         return out
 

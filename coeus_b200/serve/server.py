@@ -197,6 +197,11 @@ class ServingLoop(Metrics, HealthCheck):
                 continue
             for r in done:
                 fut = self._futures.pop(r.id)
+                if r.error is not None:
+                    self._t0.pop(r.id, None)
+                    self.counters["failed"] += 1
+                    fut.set_exception(r.error)
+                    continue
                 self.counters["completed"] += 1
                 self.counters["generated_tokens"] += len(r.output)
                 self.counters["latency_s_sum"] += time.perf_counter() - self._t0.pop(r.id)

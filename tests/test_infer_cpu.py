@@ -185,3 +185,26 @@ def test_generation_never_picks_a_vocabulary_padding_column():
     cb = ContinuousBatcher(InferenceEngine(m, max_batch=2), max_seqs=2, max_len=32)
     rid = cb.submit(ids[0].tolist(), 3)
     assert max(cb.run()[rid]) < 90
+
+
+def test_a_request_that_cannot_be_admitted_fails_alone():
+    """The page pool is made too small for the second request's prompt: it fails with a resource
+    error, its slot comes back, the others are served."""
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    m = _model("llama")
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=2), max_seqs=2, max_len=160)
+    kv = cb.engine.cache
+    while len(kv.free) > 2:              # leave two pages in the pool
+        kv.free.pop()
+    ok1 = cb.submit([1, 2, 3], 2)
+    big = cb.submit(list(range(1, 91)) + [5] * 60, 2)        # needs three pages
+    done = {}
+    errors = {}
+    while cb.pending():
+        for r in cb.step():
+            (errors if r.error is not None else done)[r.id] = r
+    assert list(done) == [ok1] and list(errors) == [big]
+    assert "exhausted" in str(errors[big].error)
+    assert len(cb.free_slots) == 2 and kv.pages_in_use() == kv.num_pages - 2
+    ok2 = cb.submit([4, 5, 6], 2)
+    assert len(cb.run()[ok2]) == 2
