@@ -117,3 +117,82 @@ class Block(nn.Module):
 class CrossEntropyLoss(nn.Module):
     def forward(self, logits, targets):
         return F.cross_entropy(logits, targets)
+
+
+class TransformerLM(nn.Module):
+    """The decoder-only language model of :class:`coeus_b200.models.config.DecoderConfig` as an
+    autograd module over the same kernels (dense feed-forward; the explicit
+    :class:`coeus_b200.models.decoder.DecoderLM` is the path the trainers and the parallel
+    strategies use and also covers mixtures of experts).  ``forward(ids [B, S])`` returns the
+    logits ``[B*S, V]``, or the mean next-token loss when ``targets`` is given."""
+
+    def __init__(self, cfg, device="cuda") -> None:
+        super().__init__()
+        if cfg.num_experts:
+            raise ValueError("TransformerLM covers dense models; use DecoderLM for experts")
+        self.cfg = cfg
+        H = cfg.hidden_dim
+        rms, swiglu, rope = cfg.norm == "rmsnorm", cfg.activation == "swiglu", cfg.pos == "rope"
+        self.embed = Embedding(cfg.vocab_size, H, device=device, init_std=cfg.init_std)
+        self.blocks = nn.ModuleList([
+            Block(H, cfg.num_heads, cfg.intermediate_dim, rms=rms, bias=cfg.use_bias,
+                  swiglu=swiglu, rope=rope, device=device) for _ in range(cfg.num_layers)])
+        for b in self.blocks:
+            b.norm1.eps = b.norm2.eps = cfg.norm_eps
+            b.attn.theta = cfg.rope_theta
+        Norm = RMSNorm if rms else LayerNorm
+        self.final_norm = Norm(H, eps=cfg.norm_eps, device=device)
+        self.head = None if cfg.tie_embeddings else Linear(H, cfg.vocab_size, bias=False,
+                                                           device=device, init_std=cfg.init_std)
+        self._pe = None
+
+    def _positions(self, S: int, device):
+        if self.cfg.pos != "sinusoidal":
+            return None
+        if self._pe is None or self._pe.shape[0] < S:
+            from ..ops.elementwise import sinusoid_table
+            self._pe = sinusoid_table(max(S, self.cfg.max_seq_len), self.cfg.hidden_dim, device)
+        return self._pe
+
+    def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None):
+        B, S = ids.shape
+        x = F.embedding(ids, self.embed.weight, self._positions(S, ids.device), S)
+        for blk in self.blocks:
+            x = blk(x, B, S)
+        x = self.final_norm(x)
+        logits = self.head(x) if self.head is not None else F.linear(
+            x, self.embed.weight.t().contiguous())
+        if targets is None:
+            return logits
+        return F.cross_entropy(logits, targets.reshape(-1))
+
+    @torch.no_grad()
+    def load_from(self, lm) -> None:
+        """Copy the weights of a :class:`DecoderLM` with the same configuration."""
+        V = self.cfg.vocab_size
+        n1, n2, fn = lm.layout.norm_names
+        self.embed.weight.copy_(lm.master["token_embed"][:V])
+
+        def norm(dst, prefix):
+            dst.scale.copy_(lm.master[prefix + "_scale"])
+            if hasattr(dst, "bias") and dst.bias is not None and (prefix + "_bias") in lm.master:
+                dst.bias.copy_(lm.master[prefix + "_bias"])
+
+        for l, b in enumerate(self.blocks):
+            p = f"layers.{l}."
+            norm(b.norm1, p + n1)
+            norm(b.norm2, p + n2)
+            b.attn.qkv.weight.copy_(lm.master[p + "attn.qkv_weights"])
+            b.attn.o.weight.copy_(lm.master[p + "attn.o_weights"])
+            up = "ff.gate_up_weights" if self.cfg.activation == "swiglu" else "ff.up_weights"
+            b.mlp.up.weight.copy_(lm.master[p + up])
+            b.mlp.down.weight.copy_(lm.master[p + "ff.down_weights"])
+            if self.cfg.use_bias:
+                b.attn.qkv.bias.copy_(lm.master[p + "attn.qkv_bias"])
+                b.attn.o.bias.copy_(lm.master[p + "attn.o_bias"])
+                if b.mlp.up.bias is not None:
+                    b.mlp.up.bias.copy_(lm.master[p + "ff.up_bias"])
+                    b.mlp.down.bias.copy_(lm.master[p + "ff.down_bias"])
+        norm(self.final_norm, fn)
+        if self.head is not None:
+            self.head.weight.copy_(lm.master["output_proj"][:, :V])

@@ -1,5 +1,6 @@
 """Autograd wrappers: gradients of every layer against plain PyTorch autograd on the same math
 (CPU restatement of the kernels; the GPU kernels themselves are covered by the kernel tests)."""
+import pytest
 import torch
 
 from coeus_b200 import nn as cnn
@@ -73,3 +74,42 @@ def test_functional_softmax_and_gelu_values():
     assert abs(float(s.sum()) - 1.0) < 1e-6 and s[0, 2] > s[0, 1] > s[0, 0]
     assert abs(float(F.gelu(torch.tensor([[0.0]])))) < 1e-6
     assert float(F.gelu(torch.tensor([[1.0]]))) > 0 > float(F.gelu(torch.tensor([[-1.0]])))
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama", "tied"])
+def test_autograd_transformer_matches_the_explicit_decoder(kind):
+    """The nn.Module model with the explicit decoder's weights: same loss, and autograd's
+    gradients equal the hand-written backward pass."""
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.nn import TransformerLM
+    kw = dict(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64, vocab_size=64,
+              max_seq_len=16)
+    if kind == "llama":
+        kw.update(use_bias=False, activation="swiglu", norm="rmsnorm", pos="rope")
+    if kind == "tied":
+        kw.update(tie_embeddings=True)
+    cfg = DecoderConfig(**kw)
+    lm = DecoderLM(cfg, "cpu", seed=3, dtype=torch.float32)
+    for s in lm.layout.specs:                       # non-trivial norm scales and biases
+        if s.kind in ("bias", "scale"):
+            lm.master[s.name].normal_(1.0 if s.kind == "scale" else 0.0, 0.1)
+    lm.sync_working_copy()
+    net = TransformerLM(cfg, device="cpu")
+    net.load_from(lm)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (2, 16))
+    tgt = torch.randint(0, 64, (2, 16))
+    lm.zero_grad()
+    want = lm.forward_loss(ids, tgt)
+    lm.backward()
+    loss = net(ids, tgt)
+    loss.backward()
+    assert abs(float(loss.detach()) - float(want)) < 1e-5
+    blk = net.blocks[1]
+    assert torch.allclose(blk.attn.qkv.weight.grad, lm.g["layers.1.attn.qkv_weights"], atol=1e-5)
+    assert torch.allclose(blk.mlp.down.weight.grad, lm.g["layers.1.ff.down_weights"], atol=1e-5)
+    assert torch.allclose(net.embed.weight.grad, lm.g["token_embed"][:64], atol=1e-5)
+    n1 = lm.layout.norm_names[0]
+    assert torch.allclose(net.blocks[0].norm1.scale.grad, lm.g[f"layers.0.{n1}_scale"], atol=1e-5)
+    assert net(ids).shape == (32, 64)
