@@ -113,3 +113,31 @@ def test_autograd_transformer_matches_the_explicit_decoder(kind):
     n1 = lm.layout.norm_names[0]
     assert torch.allclose(net.blocks[0].norm1.scale.grad, lm.g[f"layers.0.{n1}_scale"], atol=1e-5)
     assert net(ids).shape == (32, 64)
+
+
+def test_module_adamw_matches_torch_adamw():
+    from coeus_b200.nn import Block
+    from coeus_b200.optim.adamw import AdamWConfig
+    from coeus_b200.optim.module import ModuleAdamW
+    torch.manual_seed(0)
+    a = Block(32, 2, 64, device="cpu")
+    b = Block(32, 2, 64, device="cpu")
+    b.load_state_dict(a.state_dict())
+    decay = [p for n, p in b.named_parameters() if p.dim() >= 2]
+    plain = [p for n, p in b.named_parameters() if p.dim() < 2]
+    ref = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1},
+                             {"params": plain, "weight_decay": 0.0}],
+                            lr=1e-2, betas=(0.9, 0.95), eps=1e-3)
+    # eps well above rounding noise: the key bias has a mathematically zero gradient, and Adam
+    # with a tiny eps turns its rounding noise into full-size steps of random sign
+    mine = ModuleAdamW(a, AdamWConfig(1e-2, 0.9, 0.95, 1e-3, 0.1, None))
+    x = torch.randn(2 * 8, 32)
+    for _ in range(4):
+        for net, opt in ((a, mine), (b, ref)):
+            opt.zero_grad()
+            net(x, 2, 8).pow(2).mean().backward()
+            opt.step()
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.allclose(p, q, atol=2e-6), n
+    # the parameters are views of one flat buffer
+    assert all(p.data_ptr() >= mine.p16.data_ptr() for _, p, _ in mine.params)
