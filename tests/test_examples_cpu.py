@@ -75,3 +75,8 @@ def test_serving_benchmark_runs_small():
 def test_parallel_training_example_single_process():
     r = _load("parallel_training").main(["--device", "cpu", "--steps", "6"])
     assert r["strategy"] == "single" and r["last"] < r["first"]
+
+
+def test_autograd_training_example():
+    r = _load("autograd_training").main(["--device", "cpu", "--steps", "25"])
+    assert r["last"] < 0.6 * r["first"] and r["grad_norm"] > 0
