@@ -15,9 +15,12 @@ from .adamw import AdamW, AdamWConfig
 
 class ModuleAdamW:
     def __init__(self, module: torch.nn.Module, cfg: Optional[AdamWConfig] = None,
-                 no_decay: Optional[Callable[[str, torch.nn.Parameter], bool]] = None) -> None:
+                 no_decay: Optional[Callable[[str, torch.nn.Parameter], bool]] = None,
+                 group=None) -> None:
         """``no_decay(name, param)`` selects parameters without weight decay (default: vectors,
-        i.e. biases and norm scales)."""
+        i.e. biases and norm scales).  ``group``: data-parallel process group; the flat gradient
+        buffer is averaged over it with one all-reduce per step and the replicas start from the
+        first rank's weights."""
         self.cfg = cfg or AdamWConfig()
         no_decay = no_decay or (lambda name, p: p.dim() < 2)
         named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
@@ -28,11 +31,11 @@ class ModuleAdamW:
         plain = [(n, p) for n, p in named if no_decay(n, p)]
         self.params: List[Tuple[str, torch.nn.Parameter, int]] = []
         off = 0
-        for group in (decay, plain):
-            for n, p in group:
+        for part in (decay, plain):
+            for n, p in part:
                 self.params.append((n, p, off))
                 off += (p.numel() + 7) // 8 * 8          # the kernel works on 16-byte groups
-            if group is decay:
+            if part is decay:
                 self.decay_end = off
         self.n = max(off, 8)
         self.p32 = torch.zeros(self.n, dtype=torch.float32, device=dev)
@@ -43,6 +46,13 @@ class ModuleAdamW:
             self.p16[o:o + p.numel()].copy_(p.detach().reshape(-1))
             p.data = self.p16[o:o + p.numel()].view(p.shape)   # the module now reads the flat copy
         self.opt = AdamW(self.cfg, 0, self.n, self.decay_end, dev)
+        self.group = group
+        self.world = 1
+        if group is not None:
+            import torch.distributed as dist
+            self.world = dist.get_world_size(group)
+            dist.broadcast(self.p32, src=dist.get_global_rank(group, 0), group=group)
+            self.p16.copy_(self.p32)
 
     def zero_grad(self) -> None:
         for _, p, _ in self.params:
@@ -57,7 +67,10 @@ class ModuleAdamW:
         for _, p, o in self.params:
             if p.grad is not None:
                 self.g32[o:o + p.numel()].copy_(p.grad.reshape(-1))
-        self.opt.step(self.p32, self.g32, self.p16, grad_scale)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(self.g32, group=self.group)
+        self.opt.step(self.p32, self.g32, self.p16, grad_scale / self.world)
 
     @property
     def grad_norm(self) -> torch.Tensor:

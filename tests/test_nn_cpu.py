@@ -141,3 +141,48 @@ def test_module_adamw_matches_torch_adamw():
         assert torch.allclose(p, q, atol=2e-6), n
     # the parameters are views of one flat buffer
     assert all(p.data_ptr() >= mine.p16.data_ptr() for _, p, _ in mine.params)
+
+
+def _worker_module_dp(rank, world, port, x, out):
+    import os
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.nn import Block
+    from coeus_b200.optim.adamw import AdamWConfig
+    from coeus_b200.optim.module import ModuleAdamW
+    torch.manual_seed(100 + rank)                 # replicas start differently; rank 0 wins
+    net = Block(32, 2, 64, device="cpu")
+    opt = ModuleAdamW(net, AdamWConfig(1e-2, 0.9, 0.95, 1e-3, 0.1, None), group=dist.group.WORLD)
+    mine = x[rank * 8:(rank + 1) * 8]             # one sequence of 8 tokens per rank
+    for _ in range(3):
+        opt.zero_grad()
+        net(mine, 1, 8).pow(2).mean().backward()
+        opt.step()
+    out.put((rank, opt.p32.numpy().copy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_module_adamw_data_parallel_matches_one_process():
+    import sys
+    import os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from mp_util import run_ranks
+    from coeus_b200.nn import Block
+    from coeus_b200.optim.adamw import AdamWConfig
+    from coeus_b200.optim.module import ModuleAdamW
+    torch.manual_seed(7)
+    x = torch.randn(16, 32)
+    res = {r[0]: torch.from_numpy(r[1]) for r in run_ranks(_worker_module_dp, 2, (x,), results=2)}
+    assert torch.equal(res[0], res[1])            # replicas stay identical
+    torch.manual_seed(100)                        # rank 0's initial weights
+    net = Block(32, 2, 64, device="cpu")
+    opt = ModuleAdamW(net, AdamWConfig(1e-2, 0.9, 0.95, 1e-3, 0.1, None))
+    for _ in range(3):
+        opt.zero_grad()
+        # the mean over both ranks' sequences
+        (0.5 * (net(x[:8], 1, 8).pow(2).mean() + net(x[8:], 1, 8).pow(2).mean())).backward()
+        opt.step()
+    assert torch.allclose(opt.p32, res[0], atol=2e-6)
