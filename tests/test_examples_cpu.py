@@ -80,3 +80,20 @@ def test_parallel_training_example_single_process():
 def test_autograd_training_example():
     r = _load("autograd_training").main(["--device", "cpu", "--steps", "25"])
     assert r["last"] < 0.6 * r["first"] and r["grad_norm"] > 0
+
+
+def _load_bench(name):
+    spec = importlib.util.spec_from_file_location(
+        f"bench_{name}", os.path.join(os.path.dirname(ROOT), "benchmarks", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_tokenizer_and_iterator_microbenchmarks_run():
+    """Counterparts of the reference's criterion benches (benches/tokenizer_bench.rs,
+    benches/iterator_bench.rs, benches/advanced_iterator_bench.rs, wordpiece_bench.rs)."""
+    t = _load_bench("tokenizer_bench").main()
+    assert t["bpe/tokenize/lorem"] > 0 and any(k.startswith("wordpiece/encode") for k in t)
+    it = _load_bench("iterator_bench").main()
+    assert it["windows/5"] > 0 and "prefetch/64" in it and "rolling_average" in it
