@@ -52,7 +52,8 @@ def main(argv=None) -> int:
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm_fwd", "norm_bwd",
                                        "cross_entropy", "adamw", "decode_attn", "rope", "softmax",
                                        "swiglu", "gelu", "embed", "rmsnorm_fwd", "rmsnorm_bwd",
-                                       "moe_route", "allreduce_local"])
+                                       "moe_route", "allreduce_local", "kv_write", "argmax",
+                                       "normal_init", "colsum", "moe_gather", "moe_combine"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -256,6 +257,46 @@ def main(argv=None) -> int:
         fn = lambda: E.adamw_step(p, m, v, g, pb, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,  # noqa: E731
                                   weight_decay=0.1, step=3)
         nbytes = n * (16.0 + 12.0 + 2.0)
+    elif a.kernel == "kv_write":        # prefill-sized append of K and V into the pages
+        B, nh, dh, S = a.batch, a.heads, a.dh, a.seq
+        pages = (S + D.PAGE - 1) // D.PAGE
+        kc = torch.zeros(B * pages, D.PAGE, nh, dh, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        pt = torch.arange(B * pages, device=dev, dtype=torch.int32).view(B, pages)
+        kv = torch.randn(B * S, 2 * nh * dh, device=dev).to(bf)
+        k, v = kv[:, :nh * dh], kv[:, nh * dh:]
+        pos0 = torch.zeros(B, device=dev, dtype=torch.int32)
+        fn = lambda: D.kv_write(k, v, kc, vc, pt, pos0, S, nh, dh)  # noqa: E731
+        nbytes = 2.0 * 2 * 2 * B * S * nh * dh
+    elif a.kernel == "argmax":
+        B, V = a.batch, a.vocab
+        logits = torch.randn(B, V, device=dev).to(bf)
+        fn = lambda: D.argmax_rows(logits)  # noqa: E731
+        nbytes = 2.0 * B * V
+    elif a.kernel == "normal_init":
+        p = torch.empty(a.numel, device=dev)
+        fn = lambda: E.normal_init_(p, seed=1234, std=0.02)  # noqa: E731
+        nbytes = 4.0 * a.numel
+    elif a.kernel == "colsum":           # bias gradient: column sums of a [tokens, n] matrix
+        T, C = a.tokens, a.n
+        x = torch.randn(T, C, device=dev).to(bf)
+        acc = torch.zeros(C, device=dev)
+        fn = lambda: E.colsum_into(x, acc)  # noqa: E731
+        nbytes = 2.0 * T * C
+    elif a.kernel in ("moe_gather", "moe_combine"):
+        from ..ops import moe as M
+        T, H, Ex, K = a.tokens, a.hidden, 8, 2
+        C = (int(1.25 * T * K / Ex) + 127) // 128 * 128
+        x = torch.randn(T, H, device=dev).to(bf)
+        expert, w, _, slot, _ = M.route(torch.randn(T, Ex, device=dev), K, C)
+        buf = torch.zeros(Ex * C, H, device=dev, dtype=bf)
+        if a.kernel == "moe_gather":
+            fn = lambda: M.gather_rows(x, expert, slot, buf, C)  # noqa: E731
+            nbytes = 2.0 * (T * H + T * K * H)
+        else:
+            M.gather_rows(x, expert, slot, buf, C)
+            fn = lambda: M.combine_rows(buf, expert, slot, C, w, x)  # noqa: E731
+            nbytes = 2.0 * (T * K * H + 2 * T * H)
     else:
         B, nh, dh, S = a.batch, a.heads, a.dh, a.seq
         pages = (S + D.PAGE - 1) // D.PAGE
