@@ -231,6 +231,16 @@ def cmd_train(store) -> dict:
     return out
 
 
+def _load_weights(weights: str, device: str, training: bool = False):
+    """A model file (``.safetensors`` / ``.gguf`` / ``.rustllm``) or a Hugging Face style
+    directory (``config.json`` + ``*.safetensors``, Llama naming)."""
+    if os.path.isdir(weights):
+        from .checkpoint.hf import load_hf_dir
+        return load_hf_dir(weights, device=device, training=training)
+    from .checkpoint.formats import load_model
+    return load_model(weights, device=device, training=training)[0]
+
+
 def _load_tokenizer(store, weights: str):
     """``--tokenizer=file`` or the file the training command wrote beside the weights."""
     path = _get(store, "tokenizer") or (weights + ".tokenizer.json" if weights else None)
@@ -243,13 +253,12 @@ def _load_tokenizer(store, weights: str):
 def cmd_generate(store, rest: List[str]) -> dict:
     import torch
 
-    from .checkpoint.formats import load_model
     from .infer.engine import InferenceEngine
     device = _device(store)
     weights = _get(store, "weights")
     if not weights:
         raise SystemExit("generate needs --weights=<file.safetensors|.gguf|.rustllm>")
-    model, _ = load_model(str(weights), device=device)
+    model = _load_weights(str(weights), device)
     tok = _load_tokenizer(store, str(weights))
     ids_arg, text = _get(store, "prompt_ids"), _get(store, "prompt")
     if ids_arg is not None:
@@ -273,14 +282,13 @@ def cmd_generate(store, rest: List[str]) -> dict:
 def cmd_eval(store) -> dict:
     import numpy as np
 
-    from .checkpoint.formats import load_model
     from .train.data import TokenDataset
     from .train.trainer import Trainer
     device = _device(store)
     weights = _get(store, "weights")
     if not weights:
         raise SystemExit("eval needs --weights=<file>")
-    model, _ = load_model(str(weights), device=device, training=True)
+    model = _load_weights(str(weights), device, training=True)
     S = min(int(_get(store, "train.seq_len")), model.cfg.max_seq_len)
     B = int(_get(store, "train.batch"))
     files, binary = _get(store, "data.files"), _get(store, "data.binary")
@@ -313,7 +321,6 @@ def cmd_serve(store) -> int:
     runs the HTTP server and feeds the others."""
     import torch
 
-    from .checkpoint.formats import load_model
     from .models.decoder import DecoderLM
     from .serve import ServingLoop, create_app
     device = _device(store)
@@ -321,7 +328,7 @@ def cmd_serve(store) -> int:
     weights = _get(store, "weights")
     dtype = torch.bfloat16 if device.startswith("cuda") else torch.float32
     if weights:
-        model, _ = load_model(str(weights), device=device if world == 1 else "cpu")
+        model = _load_weights(str(weights), device if world == 1 else "cpu")
     else:
         model = DecoderLM(_model_config(store), device if world == 1 else "cpu",
                           dtype=dtype if world == 1 else torch.float32, training=False)

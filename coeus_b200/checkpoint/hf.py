@@ -1,0 +1,151 @@
+"""Llama-style checkpoints in the Hugging Face tensor naming (``model.layers.N.self_attn.q_proj
+.weight`` ..., weights stored ``[out, in]``) to and from the decoder of this framework (weights
+``[in, out]``, q/k/v fused, gate and up fused).  Covers the multi-head-attention members of the
+family (``num_key_value_heads == num_attention_heads``); grouped-query checkpoints are refused.
+The reference has its own flat ``.rustllm`` layout only (src/core/serialization.rs) and names
+SafeTensors / GGUF as formats without reading them (src/domain/persistence/mod.rs:20-24)."""
+from __future__ import annotations
+
+from typing import Any, Dict, Mapping, Tuple
+
+import torch
+
+from ..foundation.error import ProcessingError
+from ..models.config import DecoderConfig
+
+
+def _get(cfg: Any, key: str, default=None):
+    return cfg.get(key, default) if isinstance(cfg, Mapping) else getattr(cfg, key, default)
+
+
+def config_from_hf(hf_config: Any) -> DecoderConfig:
+    """``hf_config``: a ``LlamaConfig``-like object or the dict of its ``config.json``."""
+    nh = _get(hf_config, "num_attention_heads")
+    nkv = _get(hf_config, "num_key_value_heads", nh) or nh
+    if nkv != nh:
+        raise ProcessingError.unsupported(
+            f"grouped-query attention ({nkv} key/value heads for {nh} heads)",
+            "the attention kernels here are multi-head")
+    if _get(hf_config, "attention_bias", False) or _get(hf_config, "mlp_bias", False):
+        raise ProcessingError.unsupported("biases in a Llama-style checkpoint",
+                                          "the SwiGLU / RMSNorm path has none")
+    scaling = _get(hf_config, "rope_scaling", None)
+    if scaling and (_get(scaling, "rope_type", _get(scaling, "type", "default")) != "default"):
+        raise ProcessingError.unsupported("scaled rotary embeddings", "plain RoPE only")
+    act = _get(hf_config, "hidden_act", "silu")
+    if act != "silu":
+        raise ProcessingError.unsupported(f"activation '{act}'", "SwiGLU uses SiLU")
+    theta = _get(hf_config, "rope_theta", None)
+    if theta is None and _get(hf_config, "rope_parameters", None):
+        theta = _get(_get(hf_config, "rope_parameters"), "rope_theta", 10000.0)
+    return DecoderConfig(
+        hidden_dim=_get(hf_config, "hidden_size"), num_layers=_get(hf_config, "num_hidden_layers"),
+        num_heads=nh, intermediate_dim=_get(hf_config, "intermediate_size"),
+        vocab_size=_get(hf_config, "vocab_size"),
+        max_seq_len=_get(hf_config, "max_position_embeddings", 2048),
+        norm_eps=float(_get(hf_config, "rms_norm_eps", 1e-6)), use_bias=False,
+        activation="swiglu", norm="rmsnorm", pos="rope", rope_theta=float(theta or 10000.0),
+        tie_embeddings=bool(_get(hf_config, "tie_word_embeddings", False)))
+
+
+def load_hf_llama(state: Mapping[str, torch.Tensor], hf_config: Any, device="cuda",
+                  training: bool = False):
+    """A :class:`coeus_b200.models.decoder.DecoderLM` holding the weights of ``state``."""
+    from ..models.decoder import DecoderLM
+    cfg = config_from_hf(hf_config)
+    dev = torch.device(device)
+    lm = DecoderLM(cfg, dev, init="zeros", training=training,
+                   dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    V = cfg.vocab_size
+    n1, n2, fn = lm.layout.norm_names
+
+    def t(name: str) -> torch.Tensor:
+        if name not in state:
+            raise ProcessingError.invalid_input(f"missing tensor '{name}'")
+        return state[name].to(torch.float32)
+
+    lm.master["token_embed"][:V] = t("model.embed_tokens.weight")
+    for l in range(cfg.num_layers):
+        h, p = f"model.layers.{l}.", f"layers.{l}."
+        lm.master[p + "attn.qkv_weights"].copy_(torch.cat(
+            [t(h + f"self_attn.{x}_proj.weight").t() for x in ("q", "k", "v")], 1))
+        lm.master[p + "attn.o_weights"].copy_(t(h + "self_attn.o_proj.weight").t())
+        lm.master[p + "ff.gate_up_weights"].copy_(torch.cat(
+            [t(h + "mlp.gate_proj.weight").t(), t(h + "mlp.up_proj.weight").t()], 1))
+        lm.master[p + "ff.down_weights"].copy_(t(h + "mlp.down_proj.weight").t())
+        lm.master[p + n1 + "_scale"].copy_(t(h + "input_layernorm.weight"))
+        lm.master[p + n2 + "_scale"].copy_(t(h + "post_attention_layernorm.weight"))
+    lm.master[fn + "_scale"].copy_(t("model.norm.weight"))
+    if not cfg.tie_embeddings:
+        lm.master["output_proj"][:, :V] = t("lm_head.weight").t()
+    lm.sync_working_copy()
+    return lm
+
+
+def to_hf_llama(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
+    """``(state dict in the Hugging Face naming, config.json fields)`` of a Llama-style
+    :class:`DecoderLM` (RMSNorm, SwiGLU, RoPE, no biases, dense)."""
+    cfg = lm.cfg
+    if not (cfg.norm == "rmsnorm" and cfg.activation == "swiglu" and cfg.pos == "rope"
+            and not cfg.use_bias and not cfg.num_experts):
+        raise ProcessingError.unsupported("export of a non-Llama-style decoder",
+                                          "needs RMSNorm, SwiGLU, RoPE, no biases, no experts")
+    H, I, V = cfg.hidden_dim, cfg.intermediate_dim, cfg.vocab_size
+    n1, n2, fn = lm.layout.norm_names
+    m = lm.master
+    out: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": m["token_embed"][:V].clone()}
+    for l in range(cfg.num_layers):
+        h, p = f"model.layers.{l}.", f"layers.{l}."
+        qkv = m[p + "attn.qkv_weights"]
+        for i, x in enumerate(("q", "k", "v")):
+            out[h + f"self_attn.{x}_proj.weight"] = qkv[:, i * H:(i + 1) * H].t().contiguous()
+        out[h + "self_attn.o_proj.weight"] = m[p + "attn.o_weights"].t().contiguous()
+        gu = m[p + "ff.gate_up_weights"]
+        out[h + "mlp.gate_proj.weight"] = gu[:, :I].t().contiguous()
+        out[h + "mlp.up_proj.weight"] = gu[:, I:].t().contiguous()
+        out[h + "mlp.down_proj.weight"] = m[p + "ff.down_weights"].t().contiguous()
+        out[h + "input_layernorm.weight"] = m[p + n1 + "_scale"].clone()
+        out[h + "post_attention_layernorm.weight"] = m[p + n2 + "_scale"].clone()
+    out["model.norm.weight"] = m[fn + "_scale"].clone()
+    if not cfg.tie_embeddings:
+        out["lm_head.weight"] = m["output_proj"][:, :V].t().contiguous()
+    hf = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": H,
+          "intermediate_size": I, "num_hidden_layers": cfg.num_layers,
+          "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_heads,
+          "vocab_size": V, "max_position_embeddings": cfg.max_seq_len,
+          "rms_norm_eps": cfg.norm_eps, "rope_theta": cfg.rope_theta, "hidden_act": "silu",
+          "tie_word_embeddings": cfg.tie_embeddings, "attention_bias": False, "mlp_bias": False}
+    return out, hf
+
+
+def load_hf_dir(path: str, device="cuda", training: bool = False):
+    """A model directory in the Hugging Face layout: ``config.json`` plus one ``.safetensors``
+    file or several with ``model.safetensors.index.json``."""
+    import glob
+    import json
+    import os
+
+    from .formats import load_safetensors
+    with open(os.path.join(path, "config.json")) as f:
+        hf_config = json.load(f)
+    files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    if not files:
+        raise ProcessingError.invalid_input(f"no .safetensors file in {path}")
+    state: Dict[str, torch.Tensor] = {}
+    for fpath in files:
+        tensors, _ = load_safetensors(fpath)
+        state.update(tensors)
+    return load_hf_llama(state, hf_config, device=device, training=training)
+
+
+def save_hf_dir(lm, path: str) -> None:
+    """Write ``config.json`` and ``model.safetensors`` in the Hugging Face naming."""
+    import json
+    import os
+
+    from .formats import save_safetensors
+    os.makedirs(path, exist_ok=True)
+    state, fields = to_hf_llama(lm)
+    save_safetensors(os.path.join(path, "model.safetensors"), state, {"format": "pt"})
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(fields, f, indent=1)

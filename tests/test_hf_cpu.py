@@ -1,0 +1,64 @@
+"""Hugging Face Llama naming: a randomly initialised ``LlamaForCausalLM`` (transformers) and the
+decoder of this framework must agree on the logits once the weights have been converted, which
+pins the rotary convention, the gate / up order, the norm epsilon and every transposition."""
+import pytest
+import torch
+
+from coeus_b200.checkpoint.hf import config_from_hf, load_hf_llama, to_hf_llama
+
+transformers = pytest.importorskip("transformers")
+
+
+def _tiny(tie=False):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64,
+                      rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=tie,
+                      attention_bias=False, mlp_bias=False)
+    torch.manual_seed(0)
+    return cfg, LlamaForCausalLM(cfg).eval()
+
+
+@pytest.mark.parametrize("tie", [False, True])
+def test_logits_match_transformers_llama(tie):
+    hf_cfg, hf = _tiny(tie)
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu")
+    assert lm.cfg.tie_embeddings == tie and lm.cfg.rope_theta == 10000.0
+    ids = torch.randint(0, 128, (2, 33))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1, 128)
+    got = lm.forward_logits(ids).reshape(66, -1)[:, :128]
+    assert (got - want).abs().max() < 2e-4
+    # and back: the exported state dict loads into transformers and gives the same logits
+    state, fields = to_hf_llama(lm)
+    from transformers import LlamaConfig, LlamaForCausalLM
+    keep = {k: v for k, v in fields.items() if k not in ("architectures", "model_type")}
+    again = LlamaForCausalLM(LlamaConfig(**keep)).eval()
+    missing = again.load_state_dict(state, strict=False)
+    assert not [k for k in missing.missing_keys if "rotary" not in k and k != "lm_head.weight"]
+    with torch.no_grad():
+        assert (again(ids).logits.reshape(-1, 128) - want).abs().max() < 2e-4
+
+
+def test_unsupported_variants_are_refused():
+    with pytest.raises(Exception) as e:
+        config_from_hf({"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 8,
+                        "num_key_value_heads": 2, "intermediate_size": 128, "vocab_size": 100})
+    assert "grouped-query" in str(e.value)
+    with pytest.raises(Exception):
+        config_from_hf({"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+                        "intermediate_size": 128, "vocab_size": 100, "attention_bias": True})
+
+
+def test_directory_round_trip_and_transformers_can_read_it(tmp_path):
+    from coeus_b200.checkpoint.hf import load_hf_dir, save_hf_dir
+    hf_cfg, hf = _tiny()
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu")
+    save_hf_dir(lm, str(tmp_path / "m"))
+    back = load_hf_dir(str(tmp_path / "m"), device="cpu")
+    assert torch.equal(back.p32, lm.p32)
+    from transformers import AutoModelForCausalLM
+    again = AutoModelForCausalLM.from_pretrained(str(tmp_path / "m")).eval()
+    ids = torch.randint(0, 128, (1, 20))
+    with torch.no_grad():
+        assert (again(ids).logits - hf(ids).logits).abs().max() < 2e-4
