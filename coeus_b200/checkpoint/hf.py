@@ -2,6 +2,8 @@
 .weight`` ..., weights stored ``[out, in]``) to and from the decoder of this framework (weights
 ``[in, out]``, q/k/v fused, gate and up fused).  Covers the multi-head-attention members of the
 family (``num_key_value_heads == num_attention_heads``); grouped-query checkpoints are refused.
+Mixtral-style mixtures of experts load too (router ``mlp.gate``, fused ``mlp.experts.gate_up_proj``
+/ ``down_proj``), with a capacity that never drops a token.
 The reference has its own flat ``.rustllm`` layout only (src/core/serialization.rs) and names
 SafeTensors / GGUF as formats without reading them (src/domain/persistence/mod.rs:20-24)."""
 from __future__ import annotations
@@ -38,7 +40,16 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
     theta = _get(hf_config, "rope_theta", None)
     if theta is None and _get(hf_config, "rope_parameters", None):
         theta = _get(_get(hf_config, "rope_parameters"), "rope_theta", 10000.0)
+    experts = int(_get(hf_config, "num_local_experts", 0) or 0)
+    moe = {}
+    if experts:
+        # Mixtral-style routing has no capacity limit; a capacity factor of E / k reserves room
+        # for every token at every expert, so nothing is ever dropped
+        k = int(_get(hf_config, "num_experts_per_tok", 2))
+        moe = dict(num_experts=experts, top_k=k, capacity_factor=float(experts) / k,
+                   aux_loss_coef=float(_get(hf_config, "router_aux_loss_coef", 0.0) or 0.0))
     return DecoderConfig(
+        **moe,
         hidden_dim=_get(hf_config, "hidden_size"), num_layers=_get(hf_config, "num_hidden_layers"),
         num_heads=nh, intermediate_dim=_get(hf_config, "intermediate_size"),
         vocab_size=_get(hf_config, "vocab_size"),
@@ -70,9 +81,17 @@ def load_hf_llama(state: Mapping[str, torch.Tensor], hf_config: Any, device="cud
         lm.master[p + "attn.qkv_weights"].copy_(torch.cat(
             [t(h + f"self_attn.{x}_proj.weight").t() for x in ("q", "k", "v")], 1))
         lm.master[p + "attn.o_weights"].copy_(t(h + "self_attn.o_proj.weight").t())
-        lm.master[p + "ff.gate_up_weights"].copy_(torch.cat(
-            [t(h + "mlp.gate_proj.weight").t(), t(h + "mlp.up_proj.weight").t()], 1))
-        lm.master[p + "ff.down_weights"].copy_(t(h + "mlp.down_proj.weight").t())
+        if cfg.num_experts:
+            # Mixtral naming: router [E, H]; experts fused as gate_up [E, 2I, H], down [E, H, I]
+            lm.master[p + "moe.router_weights"].copy_(t(h + "mlp.gate.weight").t())
+            lm.master[p + "moe.experts.gate_up_weights"].copy_(
+                t(h + "mlp.experts.gate_up_proj").transpose(1, 2))
+            lm.master[p + "moe.experts.down_weights"].copy_(
+                t(h + "mlp.experts.down_proj").transpose(1, 2))
+        else:
+            lm.master[p + "ff.gate_up_weights"].copy_(torch.cat(
+                [t(h + "mlp.gate_proj.weight").t(), t(h + "mlp.up_proj.weight").t()], 1))
+            lm.master[p + "ff.down_weights"].copy_(t(h + "mlp.down_proj.weight").t())
         lm.master[p + n1 + "_scale"].copy_(t(h + "input_layernorm.weight"))
         lm.master[p + n2 + "_scale"].copy_(t(h + "post_attention_layernorm.weight"))
     lm.master[fn + "_scale"].copy_(t("model.norm.weight"))

@@ -62,3 +62,25 @@ def test_directory_round_trip_and_transformers_can_read_it(tmp_path):
     ids = torch.randint(0, 128, (1, 20))
     with torch.no_grad():
         assert (again(ids).logits - hf(ids).logits).abs().max() < 2e-4
+
+
+def test_logits_match_transformers_mixtral():
+    """Mixture of experts: router softmax, top-2 renormalised weights and the fused expert
+    tensors against ``MixtralForCausalLM`` (capacity large enough that nothing is dropped)."""
+    from transformers import MixtralConfig, MixtralForCausalLM
+    hf_cfg = MixtralConfig(vocab_size=128, hidden_size=64, intermediate_size=96,
+                           num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
+                           max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0,
+                           num_local_experts=4, num_experts_per_tok=2, sliding_window=None,
+                           tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = MixtralForCausalLM(hf_cfg).eval()
+    if "model.layers.0.mlp.experts.gate_up_proj" not in hf.state_dict():
+        pytest.skip("this transformers version stores Mixtral experts under other names")
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu")
+    assert lm.cfg.num_experts == 4 and lm.cfg.top_k == 2
+    ids = torch.randint(0, 128, (2, 24))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1, 128)
+    got = lm.forward_logits(ids).reshape(48, -1)[:, :128]
+    assert (got - want).abs().max() < 3e-4
