@@ -84,3 +84,35 @@ def test_logits_match_transformers_mixtral():
         want = hf(ids).logits.reshape(-1, 128)
     got = lm.forward_logits(ids).reshape(48, -1)[:, :128]
     assert (got - want).abs().max() < 3e-4
+
+
+def test_loss_and_gradients_match_transformers_autograd():
+    """The hand-written backward pass against PyTorch autograd through an independent
+    implementation of the same architecture."""
+    hf_cfg, hf = _tiny()
+    hf.train()
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu", training=True)
+    torch.manual_seed(3)
+    ids = torch.randint(0, 128, (2, 25))
+    out = hf(input_ids=ids, labels=ids)            # predicts token t+1 from position t
+    out.loss.backward()
+    lm.zero_grad()
+    loss = lm.forward_loss(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+    lm.backward()
+    assert abs(float(loss) - float(out.loss.detach())) < 1e-5
+    sd = dict(hf.named_parameters())
+    H = 64
+    g_qkv = lm.g["layers.1.attn.qkv_weights"]
+    for i, x in enumerate(("q", "k", "v")):
+        want = sd[f"model.layers.1.self_attn.{x}_proj.weight"].grad.t()
+        assert torch.allclose(g_qkv[:, i * H:(i + 1) * H], want, atol=2e-6), x
+    assert torch.allclose(lm.g["layers.0.ff.down_weights"],
+                          sd["model.layers.0.mlp.down_proj.weight"].grad.t(), atol=2e-6)
+    gu = lm.g["layers.0.ff.gate_up_weights"]
+    assert torch.allclose(gu[:, :128], sd["model.layers.0.mlp.gate_proj.weight"].grad.t(), atol=2e-6)
+    assert torch.allclose(gu[:, 128:], sd["model.layers.0.mlp.up_proj.weight"].grad.t(), atol=2e-6)
+    assert torch.allclose(lm.g["token_embed"][:128], sd["model.embed_tokens.weight"].grad, atol=2e-6)
+    n1 = lm.layout.norm_names[0]
+    assert torch.allclose(lm.g[f"layers.0.{n1}_scale"],
+                          sd["model.layers.0.input_layernorm.weight"].grad, atol=2e-6)
+    assert torch.allclose(lm.g["output_proj"][:, :128], sd["lm_head.weight"].grad.t(), atol=2e-6)
