@@ -116,3 +116,18 @@ def test_loss_and_gradients_match_transformers_autograd():
     assert torch.allclose(lm.g[f"layers.0.{n1}_scale"],
                           sd["model.layers.0.input_layernorm.weight"].grad, atol=2e-6)
     assert torch.allclose(lm.g["output_proj"][:, :128], sd["lm_head.weight"].grad.t(), atol=2e-6)
+
+
+def test_greedy_generation_matches_transformers():
+    """Paged KV cache, decode-time rotary positions and the stop rule against
+    ``LlamaForCausalLM.generate``."""
+    from coeus_b200.infer.engine import InferenceEngine
+    hf_cfg, hf = _tiny()
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu")
+    torch.manual_seed(5)
+    ids = torch.randint(0, 128, (2, 9))
+    with torch.no_grad():
+        want = hf.generate(ids, max_new_tokens=12, do_sample=False, pad_token_id=0,
+                           eos_token_id=None)
+    got = InferenceEngine(lm, max_batch=2).generate(ids, 12)
+    assert torch.equal(got, want)
