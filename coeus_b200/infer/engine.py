@@ -49,6 +49,9 @@ class InferenceEngine:
         need_pages = (total + D.PAGE - 1) // D.PAGE
         if c is None or c.page_table.shape[0] < B or c.page_table.shape[1] < need_pages:
             c = PagedKVCache.for_model(self.cfg, max(B, 1), max(total, D.PAGE), self.m.device)
+            if self.m.p16.dtype != torch.bfloat16:       # CPU oracle runs keep their precision
+                c.k = [t.to(self.m.p16.dtype) for t in c.k]
+                c.v = [t.to(self.m.p16.dtype) for t in c.v]
             self.cache = c
             self._graph = None
         for b in list(c.owned):
