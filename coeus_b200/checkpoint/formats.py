@@ -44,7 +44,8 @@ def config_metadata(cfg: DecoderConfig) -> Dict[str, str]:
          "layer_norm_eps": cfg.norm_eps, "activation": cfg.activation, "dropout": cfg.dropout,
          "attention_dropout": cfg.attention_dropout, "norm": cfg.norm, "pos": cfg.pos,
          "rope_theta": cfg.rope_theta, "num_experts": cfg.num_experts, "top_k": cfg.top_k,
-         "capacity_factor": cfg.capacity_factor, "tie_embeddings": cfg.tie_embeddings}
+         "capacity_factor": cfg.capacity_factor, "tie_embeddings": cfg.tie_embeddings,
+         "num_kv_heads": cfg.num_kv_heads}
     return {k: (str(v).lower() if isinstance(v, bool) else str(v)) for k, v in d.items()}
 
 
@@ -71,7 +72,7 @@ def config_from_metadata(meta: Dict[str, str]) -> DecoderConfig:
         norm=meta.get("norm", "layernorm"), pos=meta.get("pos", "sinusoidal"),
         rope_theta=float(meta.get("rope_theta", 10000.0)), num_experts=geti("num_experts", 0),
         top_k=geti("top_k", 2), capacity_factor=float(meta.get("capacity_factor", 1.25)),
-        tie_embeddings=getb("tie_embeddings", False))
+        tie_embeddings=getb("tie_embeddings", False), num_kv_heads=geti("num_kv_heads", 0))
 
 
 # ------------------------------------------------------------------------------ named tensors
@@ -177,6 +178,10 @@ def save_model(model, path: str, fmt: Optional[str] = None,
     named = named_from_model(model)
     meta = config_metadata(model.cfg)
     if fmt == "rustllm":
+        if model.cfg.kv_heads != model.cfg.num_heads:
+            raise ProcessingError.unsupported(
+                "grouped-query attention in a .rustllm file",
+                "the reference's flat layout has square K and V projections")
         flat = to_reference_flat(named, model.cfg)
         if tail is not None:
             flat[flat.numel() - tail.numel():] = tail.to(torch.float32).cpu()

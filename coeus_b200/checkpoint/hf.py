@@ -1,7 +1,8 @@
 """Llama-style checkpoints in the Hugging Face tensor naming (``model.layers.N.self_attn.q_proj
 .weight`` ..., weights stored ``[out, in]``) to and from the decoder of this framework (weights
 ``[in, out]``, q/k/v fused, gate and up fused).  Covers the multi-head-attention members of the
-family (``num_key_value_heads == num_attention_heads``); grouped-query checkpoints are refused.
+family and the grouped-query ones (fewer key/value heads; the attention kernels are multi-head,
+so K and V are expanded per group before they run).
 Mixtral-style mixtures of experts load too (router ``mlp.gate``, fused ``mlp.experts.gate_up_proj``
 / ``down_proj``), with a capacity that never drops a token.
 The reference has its own flat ``.rustllm`` layout only (src/core/serialization.rs) and names
@@ -24,10 +25,8 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
     """``hf_config``: a ``LlamaConfig``-like object or the dict of its ``config.json``."""
     nh = _get(hf_config, "num_attention_heads")
     nkv = _get(hf_config, "num_key_value_heads", nh) or nh
-    if nkv != nh:
-        raise ProcessingError.unsupported(
-            f"grouped-query attention ({nkv} key/value heads for {nh} heads)",
-            "the attention kernels here are multi-head")
+    if nh % nkv:
+        raise ProcessingError.invalid_input(f"{nkv} key/value heads do not divide {nh} heads")
     if _get(hf_config, "attention_bias", False) or _get(hf_config, "mlp_bias", False):
         raise ProcessingError.unsupported("biases in a Llama-style checkpoint",
                                           "the SwiGLU / RMSNorm path has none")
@@ -51,7 +50,7 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
     return DecoderConfig(
         **moe,
         hidden_dim=_get(hf_config, "hidden_size"), num_layers=_get(hf_config, "num_hidden_layers"),
-        num_heads=nh, intermediate_dim=_get(hf_config, "intermediate_size"),
+        num_heads=nh, num_kv_heads=0 if nkv == nh else nkv, intermediate_dim=_get(hf_config, "intermediate_size"),
         vocab_size=_get(hf_config, "vocab_size"),
         max_seq_len=_get(hf_config, "max_position_embeddings", 2048),
         norm_eps=float(_get(hf_config, "rms_norm_eps", 1e-6)), use_bias=False,
@@ -116,8 +115,9 @@ def to_hf_llama(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
     for l in range(cfg.num_layers):
         h, p = f"model.layers.{l}.", f"layers.{l}."
         qkv = m[p + "attn.qkv_weights"]
-        for i, x in enumerate(("q", "k", "v")):
-            out[h + f"self_attn.{x}_proj.weight"] = qkv[:, i * H:(i + 1) * H].t().contiguous()
+        Hkv = cfg.kv_dim
+        for x, lo, hi in (("q", 0, H), ("k", H, H + Hkv), ("v", H + Hkv, H + 2 * Hkv)):
+            out[h + f"self_attn.{x}_proj.weight"] = qkv[:, lo:hi].t().contiguous()
         out[h + "self_attn.o_proj.weight"] = m[p + "attn.o_weights"].t().contiguous()
         gu = m[p + "ff.gate_up_weights"]
         out[h + "mlp.gate_proj.weight"] = gu[:, :I].t().contiguous()
@@ -130,7 +130,7 @@ def to_hf_llama(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
         out["lm_head.weight"] = m["output_proj"][:, :V].t().contiguous()
     hf = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": H,
           "intermediate_size": I, "num_hidden_layers": cfg.num_layers,
-          "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_heads,
+          "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.kv_heads,
           "vocab_size": V, "max_position_embeddings": cfg.max_seq_len,
           "rms_norm_eps": cfg.norm_eps, "rope_theta": cfg.rope_theta, "hidden_act": "silu",
           "tie_word_embeddings": cfg.tie_embeddings, "attention_bias": False, "mlp_bias": False}

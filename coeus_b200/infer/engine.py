@@ -94,9 +94,14 @@ class InferenceEngine:
             n1 = self._norm(x, p + n1n)
             qkv = G.linear_fwd(n1, m.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"))
             if cfg.pos == "rope":
-                E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos0_host, theta=cfg.rope_theta,
-                        pos_dev=pos_dev)
-            q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+                E.rope_(qkv, nh + cfg.kv_heads, dh, S, pos_offset=pos0_host,
+                        theta=cfg.rope_theta, pos_dev=pos_dev)
+            Hkv = cfg.kv_dim
+            q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+            if Hkv != H:
+                # grouped-query attention on multi-head kernels: K and V are expanded per group
+                # here, and the cache keeps the expanded heads
+                k, v = m._expand_kv(k), m._expand_kv(v)
             D.kv_write(k, v, cache.k[l], cache.v[l], page_table, pos0, S, nh, dh)
             if prefill:
                 attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)

@@ -144,6 +144,7 @@ class DecoderConfig:
     max_seq_len: int = 1024
     dropout: float = 0.0
     attention_dropout: float = 0.0
+    num_kv_heads: int = 0           # grouped-query attention; 0 = one K/V head per query head
     norm_eps: float = 1e-5
     use_bias: bool = True
     activation: str = "gelu"        # "gelu" (tanh approximation) | "swiglu"
@@ -161,6 +162,19 @@ class DecoderConfig:
     @property
     def head_dim(self) -> int:
         return self.hidden_dim // self.num_heads
+
+    @property
+    def kv_heads(self) -> int:
+        return self.num_kv_heads or self.num_heads
+
+    @property
+    def kv_dim(self) -> int:
+        """Width of the K (and of the V) projection."""
+        return self.kv_heads * self.head_dim
+
+    @property
+    def qkv_dim(self) -> int:
+        return self.hidden_dim + 2 * self.kv_dim
 
     @property
     def vocab_padded(self) -> int:
@@ -201,6 +215,12 @@ class DecoderConfig:
             raise ConfigError.invalid("hidden_dim", self.hidden_dim,
                                       "hidden_dim and intermediate_dim must be multiples of 8 "
                                       "(16-byte rows)")
+        if self.num_kv_heads and (self.num_kv_heads < 0 or self.num_heads % self.num_kv_heads):
+            raise ConfigError.invalid("num_kv_heads", self.num_kv_heads,
+                                      "Key/value heads must divide the number of heads")
+        if self.kv_dim % 8:
+            raise ConfigError.invalid("num_kv_heads", self.num_kv_heads,
+                                      "kv_heads * head_dim must be a multiple of 8 (16-byte rows)")
         if self.dropout or self.attention_dropout:
             # the reference declares dropout rates and never applies them (its forward pass is
             # inference only, plugins/model-transformer/src/lib.rs:863-921); the kernels here

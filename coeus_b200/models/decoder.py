@@ -84,7 +84,7 @@ class ParamLayout:
             specs.append(ParamSpec("token_embed", (Vp if cfg.tie_embeddings else V, H), True, "embed"))
         for l in self.layer_ids:
             p = f"layers.{l}."
-            specs.append(ParamSpec(p + "attn.qkv_weights", (H, 3 * H), True, "weight"))
+            specs.append(ParamSpec(p + "attn.qkv_weights", (H, cfg.qkv_dim), True, "weight"))
             specs.append(ParamSpec(p + "attn.o_weights", (H, H), True, "weight"))
             if cfg.num_experts:
                 E_ = cfg.num_experts
@@ -112,7 +112,7 @@ class ParamLayout:
             if ln:
                 vec.append(ParamSpec(p + s2 + "_bias", (H,), False, "bias"))
             if cfg.use_bias:
-                vec.append(ParamSpec(p + "attn.qkv_bias", (3 * H,), False, "bias"))
+                vec.append(ParamSpec(p + "attn.qkv_bias", (cfg.qkv_dim,), False, "bias"))
                 vec.append(ParamSpec(p + "attn.o_bias", (H,), False, "bias"))
                 if not cfg.num_experts and cfg.activation == "gelu":
                     vec.append(ParamSpec(p + "ff.up_bias", (I,), False, "bias"))
@@ -166,6 +166,11 @@ class DecoderLM:
         self.device = torch.device(device)
         self.cp = cp
         self.recompute = bool(recompute)
+        self.gqa = cfg.kv_heads != cfg.num_heads
+        if self.gqa and cp is not None:
+            raise ProcessingError.unsupported(
+                "grouped-query attention with context / Ulysses parallelism",
+                "the ring and all-to-all paths exchange one K/V head per query head")
         self.epx = None
         self.moe: List = []
         if cfg.num_experts:
@@ -303,15 +308,16 @@ class DecoderLM:
 
     def _assign_reference_tensor(self, name: str, value: torch.Tensor) -> None:
         """Store a tensor given under its reference name (q/k/v separate) into the fused layout."""
-        H = self.cfg.hidden_dim
-        for i, part in enumerate(("q", "k", "v")):
+        H, Hkv = self.cfg.hidden_dim, self.cfg.kv_dim
+        spans = {"q": (0, H), "k": (H, H + Hkv), "v": (H + Hkv, H + 2 * Hkv)}
+        for part, (lo, hi) in spans.items():
             if name.endswith(f"attn.{part}_weights"):
                 fused = name.replace(f"attn.{part}_weights", "attn.qkv_weights")
-                self.master[fused][:, i * H:(i + 1) * H] = value
+                self.master[fused][:, lo:hi] = value
                 return
             if name.endswith(f"attn.{part}_bias"):
                 fused = name.replace(f"attn.{part}_bias", "attn.qkv_bias")
-                self.master[fused][i * H:(i + 1) * H] = value
+                self.master[fused][lo:hi] = value
                 return
         dst = self.master[name]
         if tuple(dst.shape) != tuple(value.shape):   # vocabulary padding
@@ -361,12 +367,22 @@ class DecoderLM:
         cfg = self.cfg
         nh, dh = cfg.num_heads, cfg.head_dim
         if self.cp is None:
-            E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta, inverse=inverse)
+            # q heads and k heads sit next to each other in the fused buffer
+            E.rope_(qkv, nh + cfg.kv_heads, dh, S, theta=cfg.rope_theta, inverse=inverse)
             return
         Tc = B * S
         for c, off in enumerate(self.cp.position_offsets(S)):
             E.rope_(qkv[c * Tc:(c + 1) * Tc], 2 * nh, dh, S, pos_offset=off, theta=cfg.rope_theta,
                     inverse=inverse)
+
+    def _expand_kv(self, t: torch.Tensor) -> torch.Tensor:
+        """``[T, kv_heads * dh] -> [T, heads * dh]``: every K/V head repeated for the query heads
+        of its group (query head ``h`` reads K/V head ``h // group``).  The attention kernels are
+        multi-head, so grouped-query attention runs on the expanded copies."""
+        cfg = self.cfg
+        T, g = t.shape[0], cfg.num_heads // cfg.kv_heads
+        return t.reshape(T, cfg.kv_heads, 1, cfg.head_dim).expand(
+            T, cfg.kv_heads, g, cfg.head_dim).reshape(T, cfg.hidden_dim)
 
     def _block_fwd(self, l: int, x: torch.Tensor, B: int, S: int, save: Optional[dict]):
         cfg = self.cfg
@@ -379,14 +395,17 @@ class DecoderLM:
         n1, mean1, rstd1 = self._norm(x, p + n1n)
         qkv = G.linear_fwd(n1, self.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"),
                            out=self._buf(f"qkv{l}" if save is not None and not self.recompute else "qkv",
-                                         (T, 3 * H)),
+                                         (T, cfg.qkv_dim)),
                            max_ctas=mc)
         if cfg.pos == "rope":
             self._rope(qkv, B, S, False)
         if self.cp is not None:
             attn, lse = self.cp.attention_fwd(qkv, B, S, nh, dh)
         else:
-            q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+            Hkv = cfg.kv_dim
+            q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+            if self.gqa:
+                k, v = self._expand_kv(k), self._expand_kv(v)
             attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
         x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
                              max_ctas=mc)
@@ -591,10 +610,22 @@ class DecoderLM:
                 E.colsum_into(dx_mid, self.g[p + "attn.o_bias"])
             dattn = G.linear_dgrad(dx_mid, self.w[p + "attn.o_weights"], max_ctas=mc)
             qkv = a["qkv"]
-            q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+            Hkv = cfg.kv_dim
+            q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
             dqkv = self._buf("dqkv", (dattn.shape[0], 3 * H))
             if self.cp is not None:
                 self.cp.attention_bwd(dattn, qkv, a["attn"], a["lse"], B, S, nh, dh, dqkv=dqkv)
+            elif self.gqa:
+                A.attention_bwd(dattn, q, self._expand_kv(k), self._expand_kv(v), a["attn"],
+                                a["lse"], B, S, nh, dh, causal=True, dqkv=dqkv)
+                # the gradients of a K/V head are the sum over the query heads of its group
+                Tn, g = dqkv.shape[0], nh // cfg.kv_heads
+                narrow = self._buf("dqkv_gqa", (Tn, cfg.qkv_dim))
+                narrow[:, :H].copy_(dqkv[:, :H])
+                for j, lo in ((1, H), (2, H + Hkv)):
+                    part = dqkv[:, j * H:(j + 1) * H].reshape(Tn, cfg.kv_heads, g, dh)
+                    narrow[:, lo:lo + Hkv].copy_(part.float().sum(2).reshape(Tn, Hkv))
+                dqkv = narrow
             else:
                 A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, causal=True,
                                 dqkv=dqkv)

@@ -113,14 +113,16 @@ def named_from_model(model) -> Dict[str, torch.Tensor]:
     """Reference-named fp32 tensors (q/k/v split out of the fused matrix) of a DecoderLM."""
     cfg = model.cfg
     H = cfg.hidden_dim
+    Hkv = getattr(cfg, "kv_dim", H)
+    spans = (("q", 0, H), ("k", H, H + Hkv), ("v", H + Hkv, H + 2 * Hkv))
     out: Dict[str, torch.Tensor] = {}
     for name, t in model.named_parameters():
         if name.endswith("attn.qkv_weights"):
-            for i, part in enumerate(("q", "k", "v")):
-                out[name.replace("qkv_weights", f"{part}_weights")] = t[:, i * H:(i + 1) * H].contiguous()
+            for part, lo, hi in spans:
+                out[name.replace("qkv_weights", f"{part}_weights")] = t[:, lo:hi].contiguous()
         elif name.endswith("attn.qkv_bias"):
-            for i, part in enumerate(("q", "k", "v")):
-                out[name.replace("qkv_bias", f"{part}_bias")] = t[i * H:(i + 1) * H].contiguous()
+            for part, lo, hi in spans:
+                out[name.replace("qkv_bias", f"{part}_bias")] = t[lo:hi].contiguous()
         elif name == "output_proj":
             out[name] = t[:, :cfg.vocab_size].contiguous()
         elif name == "token_embed":

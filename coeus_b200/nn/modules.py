@@ -128,8 +128,9 @@ class TransformerLM(nn.Module):
 
     def __init__(self, cfg, device="cuda") -> None:
         super().__init__()
-        if cfg.num_experts:
-            raise ValueError("TransformerLM covers dense models; use DecoderLM for experts")
+        if cfg.num_experts or cfg.kv_heads != cfg.num_heads:
+            raise ValueError("TransformerLM covers dense multi-head models; use DecoderLM for "
+                             "experts and grouped-query attention")
         self.cfg = cfg
         H = cfg.hidden_dim
         rms, swiglu, rope = cfg.norm == "rmsnorm", cfg.activation == "swiglu", cfg.pos == "rope"

@@ -33,6 +33,10 @@ class TPDecoderLM:
         block's forward, collectives included, again in the backward pass."""
         cfg.validate()
         self.recompute = bool(recompute)
+        if cfg.kv_heads != cfg.num_heads:
+            raise ProcessingError.unsupported(
+                "grouped-query attention under tensor parallelism",
+                "the head sharding here assumes one K/V head per query head")
         if cfg.use_bias or cfg.num_experts or cfg.tie_embeddings:
             raise ProcessingError.unsupported(
                 "tensor-parallel decoder with biases, experts or tied embeddings",

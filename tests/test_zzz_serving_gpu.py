@@ -54,8 +54,10 @@ def test_prefix_cache_warm_equals_cold():
     prompt = torch.randint(0, 1000, (200,)).tolist()
     cb = ContinuousBatcher(InferenceEngine(m, max_batch=2, decode_splits=1), max_seqs=2,
                            max_len=256, prefix_cache=True)
-    cold = cb.run()[cb.submit(prompt, 6)]
-    warm = cb.run()[cb.submit(prompt, 6)]
+    rid = cb.submit(prompt, 6)
+    cold = cb.run()[rid]
+    rid = cb.submit(prompt, 6)
+    warm = cb.run()[rid]
     torch.cuda.synchronize()
     _lib.check_status(torch.device("cuda", 0))
     assert cb.prefix.hits == 1 and warm == cold
