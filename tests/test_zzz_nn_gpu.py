@@ -61,18 +61,19 @@ def test_module_adamw_trains_on_gpu():
     assert losses[-1] < losses[0]
 
 
-def test_gpu_decoder_matches_transformers_llama():
+@pytest.mark.parametrize("kv_heads", [4, 2])
+def test_gpu_decoder_matches_transformers_llama(kv_heads):
     """The bf16 kernel path against an independent fp32 implementation (transformers' Llama) of
-    the same weights."""
+    the same weights; with two key/value heads the grouped-query expansion is in the path."""
     transformers = pytest.importorskip("transformers")
     from coeus_b200.checkpoint.hf import load_hf_llama
     hf_cfg = transformers.LlamaConfig(
         vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-        num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=256,
+        num_attention_heads=4, num_key_value_heads=kv_heads, max_position_embeddings=256,
         rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
     torch.manual_seed(0)
     hf = transformers.LlamaForCausalLM(hf_cfg).eval()
-    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cuda")
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cuda", training=True)
     ids = torch.randint(0, 1024, (2, 150))
     with torch.no_grad():
         want = hf(ids).logits.reshape(-1, 1024)
@@ -80,3 +81,13 @@ def test_gpu_decoder_matches_transformers_llama():
     torch.cuda.synchronize()
     _lib.check_status(torch.device("cuda", 0))
     assert (got - want).abs().max() < 0.05 * want.abs().max() + 0.02
+    # one training step's loss against autograd through the independent implementation
+    hf.train()
+    out = hf(input_ids=ids, labels=ids)
+    dev_ids = ids.cuda()
+    lm.zero_grad()
+    loss = lm.forward_loss(dev_ids[:, :-1].contiguous(), dev_ids[:, 1:].contiguous())
+    lm.backward()
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
+    assert abs(float(loss) - float(out.loss.detach())) < 0.03
