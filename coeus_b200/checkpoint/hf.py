@@ -33,6 +33,10 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
     scaling = _get(hf_config, "rope_scaling", None)
     if scaling and (_get(scaling, "rope_type", _get(scaling, "type", "default")) != "default"):
         raise ProcessingError.unsupported("scaled rotary embeddings", "plain RoPE only")
+    window = _get(hf_config, "sliding_window", None)
+    if window and window < _get(hf_config, "max_position_embeddings", 0):
+        raise ProcessingError.unsupported(f"sliding-window attention (window {window})",
+                                          "the attention kernels are fully causal")
     act = _get(hf_config, "hidden_act", "silu")
     if act != "silu":
         raise ProcessingError.unsupported(f"activation '{act}'", "SwiGLU uses SiLU")

@@ -48,6 +48,11 @@ def test_unsupported_variants_are_refused():
     with pytest.raises(Exception):
         config_from_hf({"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
                         "intermediate_size": 128, "vocab_size": 100, "attention_bias": True})
+    with pytest.raises(Exception) as e:
+        config_from_hf({"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+                        "intermediate_size": 128, "vocab_size": 100, "sliding_window": 32,
+                        "max_position_embeddings": 128})
+    assert "sliding-window" in str(e.value)
 
 
 def test_directory_round_trip_and_transformers_can_read_it(tmp_path):
