@@ -27,13 +27,18 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
     nkv = _get(hf_config, "num_key_value_heads", nh) or nh
     if nh % nkv:
         raise ProcessingError.invalid_input(f"{nkv} key/value heads do not divide {nh} heads")
-    if _get(hf_config, "attention_bias", False) or _get(hf_config, "mlp_bias", False):
-        raise ProcessingError.unsupported("biases in a Llama-style checkpoint",
-                                          "the SwiGLU / RMSNorm path has none")
+    if _get(hf_config, "mlp_bias", False):
+        raise ProcessingError.unsupported("feed-forward biases in a Llama-style checkpoint",
+                                          "the SwiGLU path has none")
+    # Qwen2-style checkpoints carry q/k/v biases (and no output-projection bias)
+    attn_bias = bool(_get(hf_config, "attention_bias", False)) or \
+        _get(hf_config, "model_type", "") == "qwen2"
     scaling = _get(hf_config, "rope_scaling", None)
     if scaling and (_get(scaling, "rope_type", _get(scaling, "type", "default")) != "default"):
         raise ProcessingError.unsupported("scaled rotary embeddings", "plain RoPE only")
     window = _get(hf_config, "sliding_window", None)
+    if _get(hf_config, "use_sliding_window", True) is False:
+        window = None
     if window and window < _get(hf_config, "max_position_embeddings", 0):
         raise ProcessingError.unsupported(f"sliding-window attention (window {window})",
                                           "the attention kernels are fully causal")
@@ -57,7 +62,7 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
         num_heads=nh, num_kv_heads=0 if nkv == nh else nkv, intermediate_dim=_get(hf_config, "intermediate_size"),
         vocab_size=_get(hf_config, "vocab_size"),
         max_seq_len=_get(hf_config, "max_position_embeddings", 2048),
-        norm_eps=float(_get(hf_config, "rms_norm_eps", 1e-6)), use_bias=False,
+        norm_eps=float(_get(hf_config, "rms_norm_eps", 1e-6)), use_bias=attn_bias,
         activation="swiglu", norm="rmsnorm", pos="rope", rope_theta=float(theta or 10000.0),
         tie_embeddings=bool(_get(hf_config, "tie_word_embeddings", False)))
 
@@ -84,6 +89,11 @@ def load_hf_llama(state: Mapping[str, torch.Tensor], hf_config: Any, device="cud
         lm.master[p + "attn.qkv_weights"].copy_(torch.cat(
             [t(h + f"self_attn.{x}_proj.weight").t() for x in ("q", "k", "v")], 1))
         lm.master[p + "attn.o_weights"].copy_(t(h + "self_attn.o_proj.weight").t())
+        if cfg.use_bias:
+            lm.master[p + "attn.qkv_bias"].copy_(torch.cat(
+                [t(h + f"self_attn.{x}_proj.bias") for x in ("q", "k", "v")]))
+            if h + "self_attn.o_proj.bias" in state:
+                lm.master[p + "attn.o_bias"].copy_(t(h + "self_attn.o_proj.bias"))
         if cfg.num_experts:
             # Mixtral naming: router [E, H]; experts fused as gate_up [E, 2I, H], down [E, H, I]
             lm.master[p + "moe.router_weights"].copy_(t(h + "mlp.gate.weight").t())

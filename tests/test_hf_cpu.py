@@ -47,7 +47,7 @@ def test_unsupported_variants_are_refused():
                         "num_key_value_heads": 3, "intermediate_size": 128, "vocab_size": 100})
     with pytest.raises(Exception):
         config_from_hf({"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
-                        "intermediate_size": 128, "vocab_size": 100, "attention_bias": True})
+                        "intermediate_size": 128, "vocab_size": 100, "mlp_bias": True})
     with pytest.raises(Exception) as e:
         config_from_hf({"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
                         "intermediate_size": 128, "vocab_size": 100, "sliding_window": 32,
@@ -171,3 +171,25 @@ def test_grouped_query_attention_matches_transformers(kv_heads):
     assert fields["num_key_value_heads"] == kv_heads
     assert torch.equal(state["model.layers.0.self_attn.k_proj.weight"],
                        hf.state_dict()["model.layers.0.self_attn.k_proj.weight"])
+
+
+def test_logits_match_transformers_qwen2():
+    """Qwen2-style: q/k/v biases, no output-projection bias, grouped-query attention."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    hf_cfg = Qwen2Config(vocab_size=128, hidden_size=64, intermediate_size=128,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=64, rms_norm_eps=1e-6, rope_theta=10000.0,
+                         tie_word_embeddings=False, use_sliding_window=False)
+    torch.manual_seed(0)
+    hf = Qwen2ForCausalLM(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("_proj.bias"):
+                p.normal_(0, 0.1)
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu")
+    assert lm.cfg.use_bias and lm.cfg.kv_heads == 2
+    ids = torch.randint(0, 128, (2, 21))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1, 128)
+    got = lm.forward_logits(ids).reshape(42, -1)[:, :128]
+    assert (got - want).abs().max() < 3e-4
