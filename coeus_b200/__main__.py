@@ -244,6 +244,12 @@ def _load_weights(weights: str, device: str, training: bool = False):
 def _load_tokenizer(store, weights: str):
     """``--tokenizer=file`` or the file the training command wrote beside the weights."""
     path = _get(store, "tokenizer") or (weights + ".tokenizer.json" if weights else None)
+    # a Hugging Face model directory brings its own tokenizer files
+    hf_dir = str(_get(store, "tokenizer") or weights or "")
+    if os.path.isdir(hf_dir) and any(os.path.exists(os.path.join(hf_dir, f))
+                                     for f in ("tokenizer.json", "tokenizer.model")):
+        from transformers import AutoTokenizer
+        return AutoTokenizer.from_pretrained(hf_dir)
     if not path or not os.path.exists(str(path)):
         return None
     from .plugins.builtin.tokenizer_bpe import BpeTokenizer
@@ -274,7 +280,8 @@ def cmd_generate(store, rest: List[str]) -> dict:
         temperature=float(_get(store, "temperature") or 0.0))
     res = {"prompt_ids": ids, "token_ids": out[0, len(ids):].tolist()}
     if tok is not None:
-        res["text"] = tok.decode_ids(res["token_ids"], ref_compat=False)
+        from .serve.server import _decoder
+        res["text"] = _decoder(tok)(res["token_ids"])
     print(json.dumps(res))
     return res
 
