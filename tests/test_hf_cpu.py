@@ -193,3 +193,15 @@ def test_logits_match_transformers_qwen2():
         want = hf(ids).logits.reshape(-1, 128)
     got = lm.forward_logits(ids).reshape(42, -1)[:, :128]
     assert (got - want).abs().max() < 3e-4
+
+
+def test_reads_a_directory_written_by_transformers(tmp_path):
+    """``save_pretrained`` output (the official SafeTensors writer) through the native reader."""
+    from coeus_b200.checkpoint.hf import load_hf_dir
+    hf_cfg, hf = _tiny(kv_heads=2)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    lm = load_hf_dir(str(tmp_path / "hf"), device="cpu")
+    ids = torch.randint(0, 128, (1, 17))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1, 128)
+    assert (lm.forward_logits(ids).reshape(17, -1)[:, :128] - want).abs().max() < 2e-4
