@@ -22,7 +22,7 @@ import sys
 from typing import Any, Dict, List, Optional
 
 DEFAULTS: Dict[str, Any] = {
-    "model": {"preset": "", "hidden_dim": 256, "num_layers": 4, "num_heads": 4,
+    "model": {"preset": "", "hidden_dim": 256, "num_layers": 4, "num_heads": 4, "num_kv_heads": 0,
               "intermediate_dim": 1024, "vocab_size": 512, "max_seq_len": 256, "use_bias": False,
               "activation": "swiglu", "norm": "rmsnorm", "pos": "rope", "recompute": False},
     "parallel": {"dp": 1, "tp": 1, "pp": 1, "ep": 1, "cp": 1, "ulysses": False,
@@ -74,7 +74,7 @@ def _model_config(store):
         if make is None:
             raise SystemExit(f"unknown model.preset '{preset}' (250m, 1.3b, moe)")
         return make()
-    keys = ("hidden_dim", "num_layers", "num_heads", "intermediate_dim", "vocab_size",
+    keys = ("hidden_dim", "num_layers", "num_heads", "num_kv_heads", "intermediate_dim", "vocab_size",
             "max_seq_len", "use_bias", "activation", "norm", "pos")
     return DecoderConfig(**{k: _get(store, f"model.{k}") for k in keys})
 
