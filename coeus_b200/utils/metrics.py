@@ -74,7 +74,7 @@ def model_flops_per_token(cfg, seq_len: int, training: bool = True) -> float:
     ff = (3 if cfg.activation == "swiglu" else 2) * H * I
     if cfg.num_experts:
         ff = ff * cfg.top_k + H * cfg.num_experts
-    per_layer = 4 * H * H + ff
+    per_layer = H * getattr(cfg, "qkv_dim", 3 * H) + H * H + ff    # fused QKV (narrower with GQA) + O
     attn = 2 * seq_len * H          # QK^T and PV, causal half of 2 * 2 * S * H
     fwd = 2.0 * (L * per_layer + H * V) + 2.0 * L * attn
     return fwd * (3.0 if training else 1.0)
