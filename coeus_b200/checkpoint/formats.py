@@ -46,7 +46,16 @@ def config_metadata(cfg: DecoderConfig) -> Dict[str, str]:
          "rope_theta": cfg.rope_theta, "num_experts": cfg.num_experts, "top_k": cfg.top_k,
          "capacity_factor": cfg.capacity_factor, "tie_embeddings": cfg.tie_embeddings,
          "num_kv_heads": cfg.num_kv_heads}
+    if cfg.rope_llama3 is not None:
+        d["rope_llama3"] = ",".join(str(x) for x in cfg.rope_llama3)
     return {k: (str(v).lower() if isinstance(v, bool) else str(v)) for k, v in d.items()}
+
+
+def _parse_llama3(text):
+    if not text:
+        return None
+    f, lo, hi, orig = text.split(",")
+    return float(f), float(lo), float(hi), int(float(orig))
 
 
 def config_from_metadata(meta: Dict[str, str]) -> DecoderConfig:
@@ -72,7 +81,8 @@ def config_from_metadata(meta: Dict[str, str]) -> DecoderConfig:
         norm=meta.get("norm", "layernorm"), pos=meta.get("pos", "sinusoidal"),
         rope_theta=float(meta.get("rope_theta", 10000.0)), num_experts=geti("num_experts", 0),
         top_k=geti("top_k", 2), capacity_factor=float(meta.get("capacity_factor", 1.25)),
-        tie_embeddings=getb("tie_embeddings", False), num_kv_heads=geti("num_kv_heads", 0))
+        tie_embeddings=getb("tie_embeddings", False), num_kv_heads=geti("num_kv_heads", 0),
+        rope_llama3=_parse_llama3(meta.get("rope_llama3")))
 
 
 # ------------------------------------------------------------------------------ named tensors

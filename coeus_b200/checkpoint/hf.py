@@ -33,9 +33,15 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
     # Qwen2-style checkpoints carry q/k/v biases (and no output-projection bias)
     attn_bias = bool(_get(hf_config, "attention_bias", False)) or \
         _get(hf_config, "model_type", "") == "qwen2"
-    scaling = _get(hf_config, "rope_scaling", None)
-    if scaling and (_get(scaling, "rope_type", _get(scaling, "type", "default")) != "default"):
-        raise ProcessingError.unsupported("scaled rotary embeddings", "plain RoPE only")
+    scaling = _get(hf_config, "rope_scaling", None) or _get(hf_config, "rope_parameters", None)
+    kind = _get(scaling, "rope_type", _get(scaling, "type", "default")) if scaling else "default"
+    llama3 = None
+    if kind == "llama3":
+        llama3 = (float(_get(scaling, "factor")), float(_get(scaling, "low_freq_factor")),
+                  float(_get(scaling, "high_freq_factor")),
+                  int(_get(scaling, "original_max_position_embeddings")))
+    elif kind not in ("default", None):
+        raise ProcessingError.unsupported(f"rotary scaling '{kind}'", "plain and llama3 only")
     window = _get(hf_config, "sliding_window", None)
     if _get(hf_config, "use_sliding_window", True) is False:
         window = None
@@ -64,6 +70,7 @@ def config_from_hf(hf_config: Any) -> DecoderConfig:
         max_seq_len=_get(hf_config, "max_position_embeddings", 2048),
         norm_eps=float(_get(hf_config, "rms_norm_eps", 1e-6)), use_bias=attn_bias,
         activation="swiglu", norm="rmsnorm", pos="rope", rope_theta=float(theta or 10000.0),
+        rope_llama3=llama3,
         tie_embeddings=bool(_get(hf_config, "tie_word_embeddings", False)))
 
 
@@ -148,6 +155,10 @@ def to_hf_llama(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
           "vocab_size": V, "max_position_embeddings": cfg.max_seq_len,
           "rms_norm_eps": cfg.norm_eps, "rope_theta": cfg.rope_theta, "hidden_act": "silu",
           "tie_word_embeddings": cfg.tie_embeddings, "attention_bias": False, "mlp_bias": False}
+    if cfg.rope_llama3 is not None:
+        f, lo, hi, orig = cfg.rope_llama3
+        hf["rope_scaling"] = {"rope_type": "llama3", "factor": f, "low_freq_factor": lo,
+                              "high_freq_factor": hi, "original_max_position_embeddings": orig}
     return out, hf
 
 

@@ -93,7 +93,10 @@ class InferenceEngine:
             bias = (lambda n: m.w[p + n]) if cfg.use_bias else (lambda n: None)
             n1 = self._norm(x, p + n1n)
             qkv = G.linear_fwd(n1, m.w[p + "attn.qkv_weights"], bias("attn.qkv_bias"))
-            if cfg.pos == "rope":
+            if cfg.pos == "rope" and cfg.rope_llama3 is not None:
+                E.rope_freq_(qkv, nh + cfg.kv_heads, dh, S, m.rope_inv_freq(),
+                             pos_offset=pos0_host, pos_dev=pos_dev)
+            elif cfg.pos == "rope":
                 E.rope_(qkv, nh + cfg.kv_heads, dh, S, pos_offset=pos0_host,
                         theta=cfg.rope_theta, pos_dev=pos_dev)
             Hkv = cfg.kv_dim

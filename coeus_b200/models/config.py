@@ -9,7 +9,7 @@ values (LayerNorm, sinusoidal positions, tanh-GELU, biases) stay the defaults.
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass, field, replace
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
 from ..foundation.error import ConfigError
 
@@ -151,6 +151,9 @@ class DecoderConfig:
     norm: str = "layernorm"         # "layernorm" | "rmsnorm"
     pos: str = "sinusoidal"         # "sinusoidal" | "rope" | "none"
     rope_theta: float = 10000.0
+    # Llama-3.1 style frequency scaling of the rotary embedding, as a tuple
+    # (factor, low_freq_factor, high_freq_factor, original_max_position); None = plain RoPE
+    rope_llama3: Optional[Tuple[float, float, float, int]] = None
     num_experts: int = 0            # 0 = dense MLP
     top_k: int = 2
     capacity_factor: float = 1.25

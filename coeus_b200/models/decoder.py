@@ -361,11 +361,25 @@ class DecoderLM:
         return N.norm_fwd(x, self.w[prefix + "_scale"], None if rms else self.w[prefix + "_bias"],
                           cfg.norm_eps, rms)
 
+    def rope_inv_freq(self) -> torch.Tensor:
+        """Frequency table of a scaled rotary embedding (cached on the model's device)."""
+        if getattr(self, "_inv_freq", None) is None:
+            f, lo, hi, orig = self.cfg.rope_llama3
+            self._inv_freq = E.llama3_inv_freq(self.cfg.head_dim, self.cfg.rope_theta, f, lo, hi,
+                                               int(orig)).to(self.device)
+        return self._inv_freq
+
     def _rope(self, qkv: torch.Tensor, B: int, S: int, inverse: bool) -> None:
         """Rotary embedding of the q and k heads (adjacent in the fused buffer); under context
         parallelism each of the two chunks starts at its own position."""
         cfg = self.cfg
         nh, dh = cfg.num_heads, cfg.head_dim
+        if cfg.rope_llama3 is not None:
+            if self.cp is not None:
+                raise ProcessingError.unsupported("scaled rotary embeddings under context "
+                                                  "parallelism", "plain RoPE only there")
+            E.rope_freq_(qkv, nh + cfg.kv_heads, dh, S, self.rope_inv_freq(), inverse=inverse)
+            return
         if self.cp is None:
             # q heads and k heads sit next to each other in the fused buffer
             E.rope_(qkv, nh + cfg.kv_heads, dh, S, theta=cfg.rope_theta, inverse=inverse)

@@ -128,9 +128,9 @@ class TransformerLM(nn.Module):
 
     def __init__(self, cfg, device="cuda") -> None:
         super().__init__()
-        if cfg.num_experts or cfg.kv_heads != cfg.num_heads:
+        if cfg.num_experts or cfg.kv_heads != cfg.num_heads or cfg.rope_llama3 is not None:
             raise ValueError("TransformerLM covers dense multi-head models; use DecoderLM for "
-                             "experts and grouped-query attention")
+                             "experts, grouped-query attention and scaled rotary embeddings")
         self.cfg = cfg
         H = cfg.hidden_dim
         rms, swiglu, rope = cfg.norm == "rmsnorm", cfg.activation == "swiglu", cfg.pos == "rope"

@@ -304,6 +304,42 @@ def rope_(x: torch.Tensor, nheads: int, dh: int, S: int, pos_offset: int = 0,
     return x
 
 
+def llama3_inv_freq(dh: int, theta: float, factor: float, low: float, high: float,
+                    original_max: int) -> torch.Tensor:
+    """Rotary frequencies with the Llama-3.1 scaling: wavelengths longer than
+    ``original_max / low`` are divided by ``factor``, shorter than ``original_max / high`` kept,
+    in between interpolated."""
+    inv = theta ** (-2.0 * torch.arange(dh // 2).float() / dh)
+    wavelen = 2 * math.pi / inv
+    smooth = ((original_max / wavelen) - low) / (high - low)
+    mid = (1 - smooth) * inv / factor + smooth * inv
+    out = torch.where(wavelen > original_max / low, inv / factor, inv)
+    is_mid = (wavelen <= original_max / low) & (wavelen >= original_max / high)
+    return torch.where(is_mid, mid, out)
+
+
+def rope_freq_(x: torch.Tensor, nheads: int, dh: int, S: int, inv_freq: torch.Tensor,
+               pos_offset: int = 0, inverse: bool = False,
+               pos_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`rope_` with an explicit frequency table (scaled rotary embeddings), written with
+    tensor ops on whatever device ``x`` lives on: the hand-written kernel derives its
+    frequencies from ``theta`` alone, so models with scaled frequencies take this path."""
+    T = x.shape[0]
+    half = dh // 2
+    t = torch.arange(T, device=x.device)
+    base = pos_dev.long()[t // S] if pos_dev is not None else pos_offset
+    pos = ((t % S) + base).float()
+    ang = pos[:, None] * inv_freq.to(x.device)[None, :]
+    sn, cs = torch.sin(ang)[:, None, :], torch.cos(ang)[:, None, :]
+    if inverse:
+        sn = -sn
+    xv = x[:, :nheads * dh].reshape(T, nheads, dh).float()
+    a, b = xv[..., :half], xv[..., half:]
+    x[:, :nheads * dh] = torch.cat([a * cs - b * sn, a * sn + b * cs], -1).reshape(
+        T, nheads * dh).to(x.dtype)
+    return x
+
+
 def colsum_into(x: torch.Tensor, out: torch.Tensor) -> None:
     """``out[c] += sum_t x[t,c]`` with fp32 accumulation (bias gradients)."""
     T, C = x.shape

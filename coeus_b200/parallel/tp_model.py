@@ -37,6 +37,9 @@ class TPDecoderLM:
             raise ProcessingError.unsupported(
                 "grouped-query attention under tensor parallelism",
                 "the head sharding here assumes one K/V head per query head")
+        if cfg.rope_llama3 is not None:
+            raise ProcessingError.unsupported("scaled rotary embeddings under tensor parallelism",
+                                              "plain RoPE only there")
         if cfg.use_bias or cfg.num_experts or cfg.tie_embeddings:
             raise ProcessingError.unsupported(
                 "tensor-parallel decoder with biases, experts or tied embeddings",

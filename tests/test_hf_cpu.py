@@ -205,3 +205,46 @@ def test_reads_a_directory_written_by_transformers(tmp_path):
     with torch.no_grad():
         want = hf(ids).logits.reshape(-1, 128)
     assert (lm.forward_logits(ids).reshape(17, -1)[:, :128] - want).abs().max() < 2e-4
+
+
+def test_llama3_rope_scaling_matches_transformers():
+    """Llama-3.1 style frequency scaling: logits, loss and generation past the original context
+    length against transformers."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from coeus_b200.infer.engine import InferenceEngine
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+               "high_freq_factor": 4.0, "original_max_position_embeddings": 16,
+               "rope_theta": 10000.0}
+    try:
+        hf_cfg = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128,
+                             num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                             max_position_embeddings=64, rms_norm_eps=1e-5,
+                             tie_word_embeddings=False, rope_parameters=scaling)
+    except TypeError:
+        pytest.skip("this transformers version takes rope scaling under another name")
+    torch.manual_seed(0)
+    hf = LlamaForCausalLM(hf_cfg)
+    lm = load_hf_llama(hf.state_dict(), hf_cfg, device="cpu", training=True)
+    assert lm.cfg.rope_llama3 == (8.0, 1.0, 4.0, 16)
+    ids = torch.randint(0, 128, (2, 41))
+    out = hf(input_ids=ids, labels=ids)
+    lm.zero_grad()
+    loss = lm.forward_loss(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+    lm.backward()
+    assert abs(float(loss) - float(out.loss.detach())) < 1e-5
+    out.loss.backward()
+    want = dict(hf.named_parameters())["model.layers.0.self_attn.q_proj.weight"].grad.t()
+    assert torch.allclose(lm.g["layers.0.attn.qkv_weights"][:, :64], want, atol=2e-6)
+    hf.eval()
+    with torch.no_grad():
+        gen = hf.generate(ids[:, :30], attention_mask=torch.ones_like(ids[:, :30]),
+                          max_new_tokens=10, do_sample=False, pad_token_id=0, eos_token_id=None)
+    assert torch.equal(InferenceEngine(lm, max_batch=2).generate(ids[:, :30], 10), gen)
+    # the scaling survives this framework's own file format
+    import os
+    import tempfile
+    from coeus_b200.checkpoint.formats import load_model, save_model
+    path = os.path.join(tempfile.mkdtemp(), "l3.safetensors")
+    save_model(lm, path)
+    assert load_model(path, device="cpu")[0].cfg.rope_llama3 == (8.0, 1.0, 4.0, 16)
+    assert to_hf_llama(lm)[1]["rope_scaling"]["rope_type"] == "llama3"
