@@ -121,6 +121,63 @@ def load_hf_llama(state: Mapping[str, torch.Tensor], hf_config: Any, device="cud
     return lm
 
 
+def config_from_hf_gpt2(hf_config: Any) -> DecoderConfig:
+    """GPT-2 family: LayerNorm, tanh-GELU, biases everywhere, a trained position table, and the
+    output projection tied to the token embedding."""
+    act = _get(hf_config, "activation_function", "gelu_new")
+    if act not in ("gelu_new", "gelu_pytorch_tanh"):
+        raise ProcessingError.unsupported(f"activation '{act}'", "the GELU kernel is the tanh form")
+    if _get(hf_config, "scale_attn_by_inverse_layer_idx", False) or \
+            _get(hf_config, "reorder_and_upcast_attn", False):
+        raise ProcessingError.unsupported("per-layer attention scaling", "1/sqrt(head_dim) only")
+    H = _get(hf_config, "n_embd")
+    return DecoderConfig(
+        hidden_dim=H, num_layers=_get(hf_config, "n_layer"), num_heads=_get(hf_config, "n_head"),
+        intermediate_dim=_get(hf_config, "n_inner", None) or 4 * H,
+        vocab_size=_get(hf_config, "vocab_size"), max_seq_len=_get(hf_config, "n_positions", 1024),
+        norm_eps=float(_get(hf_config, "layer_norm_epsilon", 1e-5)), use_bias=True,
+        activation="gelu", norm="layernorm", pos="learned",
+        tie_embeddings=bool(_get(hf_config, "tie_word_embeddings", True)))
+
+
+def load_hf_gpt2(state: Mapping[str, torch.Tensor], hf_config: Any, device="cuda",
+                 training: bool = False):
+    """A :class:`coeus_b200.models.decoder.DecoderLM` holding a ``GPT2LMHeadModel`` state dict.
+    GPT-2 stores its projections as ``[in, out]`` already (its ``Conv1D``), which is the layout
+    used here, so nothing is transposed."""
+    from ..models.decoder import DecoderLM
+    cfg = config_from_hf_gpt2(hf_config)
+    dev = torch.device(device)
+    lm = DecoderLM(cfg, dev, init="zeros", training=training,
+                   dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    V = cfg.vocab_size
+    n1, n2, fn = lm.layout.norm_names
+
+    def t(name: str) -> torch.Tensor:
+        for k in (name, "transformer." + name):
+            if k in state:
+                return state[k].to(torch.float32)
+        raise ProcessingError.invalid_input(f"missing tensor '{name}'")
+
+    lm.master["token_embed"][:V] = t("wte.weight")
+    lm.master["pos_embed"].copy_(t("wpe.weight"))
+    for l in range(cfg.num_layers):
+        h, p = f"h.{l}.", f"layers.{l}."
+        for ours, theirs in (("attn.qkv", "attn.c_attn"), ("attn.o", "attn.c_proj"),
+                             ("ff.up", "mlp.c_fc"), ("ff.down", "mlp.c_proj")):
+            lm.master[p + ours + "_weights"].copy_(t(h + theirs + ".weight"))
+            lm.master[p + ours + "_bias"].copy_(t(h + theirs + ".bias"))
+        for ours, theirs in ((n1, "ln_1"), (n2, "ln_2")):
+            lm.master[p + ours + "_scale"].copy_(t(h + theirs + ".weight"))
+            lm.master[p + ours + "_bias"].copy_(t(h + theirs + ".bias"))
+    lm.master[fn + "_scale"].copy_(t("ln_f.weight"))
+    lm.master[fn + "_bias"].copy_(t("ln_f.bias"))
+    if not cfg.tie_embeddings:
+        lm.master["output_proj"][:, :V] = state["lm_head.weight"].to(torch.float32).t()
+    lm.sync_working_copy()
+    return lm
+
+
 def to_hf_llama(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
     """``(state dict in the Hugging Face naming, config.json fields)`` of a Llama-style
     :class:`DecoderLM` (RMSNorm, SwiGLU, RoPE, no biases, dense)."""
@@ -179,6 +236,8 @@ def load_hf_dir(path: str, device="cuda", training: bool = False):
     for fpath in files:
         tensors, _ = load_safetensors(fpath)
         state.update(tensors)
+    if hf_config.get("model_type") == "gpt2":
+        return load_hf_gpt2(state, hf_config, device=device, training=training)
     return load_hf_llama(state, hf_config, device=device, training=training)
 
 

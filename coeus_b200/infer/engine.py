@@ -37,7 +37,8 @@ class InferenceEngine:
         self.cache: Optional[PagedKVCache] = None
         self.stats: Dict[str, float] = {}
         cuda = model.device.type == "cuda"
-        self.use_graph = (cuda and self.cfg.pos != "sinusoidal") if use_graph is None else use_graph
+        self.use_graph = (cuda and self.cfg.pos not in ("sinusoidal", "learned")) \
+            if use_graph is None else use_graph
         self._pos_buf = torch.zeros(max_batch, dtype=torch.int32, device=model.device)
         self._ctx_buf = torch.zeros(max_batch, dtype=torch.int32, device=model.device)
         self._graph = None
@@ -247,7 +248,7 @@ class InferenceEngine:
         cache, m, cfg = self.cache, self.m, self.cfg
         n = tokens.shape[0]
         x = E.embed_fwd(tokens, m.w["token_embed"], None, 1)
-        if cfg.pos == "sinusoidal":
+        if cfg.pos in ("sinusoidal", "learned"):
             pe = m._positions(int(positions.max()) + 1)
             x = (x.float() + pe[positions.long()].float()).to(x.dtype)
         table = cache.page_table.index_select(0, slots)
@@ -262,7 +263,7 @@ class InferenceEngine:
         m, cfg = self.m, self.cfg
         B = tokens.shape[0]
         pos = self._pos
-        if cfg.pos == "sinusoidal":
+        if cfg.pos in ("sinusoidal", "learned"):
             x = E.embed_fwd(tokens, m.w["token_embed"], m._positions(pos + 1), 1, pos_offset=pos)
         else:
             x = E.embed_fwd(tokens, m.w["token_embed"], None, 1)

@@ -149,7 +149,7 @@ class DecoderConfig:
     use_bias: bool = True
     activation: str = "gelu"        # "gelu" (tanh approximation) | "swiglu"
     norm: str = "layernorm"         # "layernorm" | "rmsnorm"
-    pos: str = "sinusoidal"         # "sinusoidal" | "rope" | "none"
+    pos: str = "sinusoidal"         # "sinusoidal" | "rope" | "learned" (a trained table) | "none"
     rope_theta: float = 10000.0
     # Llama-3.1 style frequency scaling of the rotary embedding, as a tuple
     # (factor, low_freq_factor, high_freq_factor, original_max_position); None = plain RoPE
@@ -211,9 +211,9 @@ class DecoderConfig:
                                       "Activation must be 'gelu' or 'swiglu'")
         if self.norm not in ("layernorm", "rmsnorm"):
             raise ConfigError.invalid("norm", self.norm, "Norm must be 'layernorm' or 'rmsnorm'")
-        if self.pos not in ("sinusoidal", "rope", "none"):
+        if self.pos not in ("sinusoidal", "rope", "none", "learned"):
             raise ConfigError.invalid("pos", self.pos,
-                                      "Positions must be 'sinusoidal', 'rope' or 'none'")
+                                      "Positions must be 'sinusoidal', 'rope', 'learned' or 'none'")
         if self.hidden_dim % 8 or self.intermediate_dim % 8:
             raise ConfigError.invalid("hidden_dim", self.hidden_dim,
                                       "hidden_dim and intermediate_dim must be multiples of 8 "

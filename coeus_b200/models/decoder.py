@@ -82,6 +82,8 @@ class ParamLayout:
         specs: List[ParamSpec] = []
         if embed:
             specs.append(ParamSpec("token_embed", (Vp if cfg.tie_embeddings else V, H), True, "embed"))
+            if cfg.pos == "learned":     # trained absolute positions (GPT-2 style)
+                specs.append(ParamSpec("pos_embed", (cfg.max_seq_len, H), True, "embed"))
         for l in self.layer_ids:
             p = f"layers.{l}."
             specs.append(ParamSpec(p + "attn.qkv_weights", (H, cfg.qkv_dim), True, "weight"))
@@ -347,6 +349,11 @@ class DecoderLM:
         return t
 
     def _positions(self, S: int) -> Optional[torch.Tensor]:
+        if self.cfg.pos == "learned":
+            # the embedding kernel adds an fp32 table; the working copy is the one every
+            # data-parallel rank keeps current
+            w = self.w["pos_embed"]
+            return w if w.dtype == torch.float32 else w.float()
         if self.cfg.pos != "sinusoidal":
             return None
         if self._pe is None or self._pe.shape[0] < S:
@@ -560,9 +567,22 @@ class DecoderLM:
             on_layer_done(-1)
         dx = self.backward_blocks(dx, sv, on_layer_done)
         E.embed_bwd(sv["ids"], dx, self.g["token_embed"])
+        self.backward_positions(dx, sv)
         if on_layer_done is not None:
             on_layer_done(-2)
         self._saved = None
+
+    def backward_positions(self, dx: torch.Tensor, sv: dict) -> None:
+        """Gradient of a learned position table: row ``s`` collects ``dx`` of position ``s`` of
+        every sequence (the embedding-gradient kernel with the positions as ids)."""
+        if self.cfg.pos != "learned":
+            return
+        if self.cp is not None:
+            raise ProcessingError.unsupported("learned positions under context parallelism",
+                                              "use rotary or sinusoidal positions")
+        S = sv["S"]
+        pos_ids = torch.arange(dx.shape[0], device=dx.device, dtype=torch.int64) % S
+        E.embed_bwd(pos_ids, dx, self.g["pos_embed"])
 
     def backward_head(self, sv: dict) -> torch.Tensor:
         """Gradients of the LM head and final norm; returns d loss / d (last block output)."""

@@ -128,7 +128,8 @@ class TransformerLM(nn.Module):
 
     def __init__(self, cfg, device="cuda") -> None:
         super().__init__()
-        if cfg.num_experts or cfg.kv_heads != cfg.num_heads or cfg.rope_llama3 is not None:
+        if cfg.num_experts or cfg.kv_heads != cfg.num_heads or cfg.rope_llama3 is not None \
+                or cfg.pos == "learned":
             raise ValueError("TransformerLM covers dense multi-head models; use DecoderLM for "
                              "experts, grouped-query attention and scaled rotary embeddings")
         self.cfg = cfg

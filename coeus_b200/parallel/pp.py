@@ -236,6 +236,7 @@ class PipelineStage:
                 dx = m.backward_blocks(dx, save)
                 if self.first:
                     E.embed_bwd(save["ids"], dx, m.g["token_embed"])
+                    m.backward_positions(dx, save)
                 else:
                     chans["sb"].send(dx)
         for c in chans.values():
@@ -396,6 +397,7 @@ class InterleavedPipelineStage:
                 dx = m.backward_blocks(dx, save)
                 if k == 0:
                     E.embed_bwd(save["ids"], dx, m.g["token_embed"])
+                    m.backward_positions(dx, save)
                 else:
                     ch["sb" if s > 0 else "sbw"].send(dx)
         for c_ in ch.values():

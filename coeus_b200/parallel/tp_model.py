@@ -37,9 +37,10 @@ class TPDecoderLM:
             raise ProcessingError.unsupported(
                 "grouped-query attention under tensor parallelism",
                 "the head sharding here assumes one K/V head per query head")
-        if cfg.rope_llama3 is not None:
-            raise ProcessingError.unsupported("scaled rotary embeddings under tensor parallelism",
-                                              "plain RoPE only there")
+        if cfg.rope_llama3 is not None or cfg.pos == "learned":
+            raise ProcessingError.unsupported(
+                "scaled rotary embeddings / learned positions under tensor parallelism",
+                "plain RoPE or sinusoidal positions only there")
         if cfg.use_bias or cfg.num_experts or cfg.tie_embeddings:
             raise ProcessingError.unsupported(
                 "tensor-parallel decoder with biases, experts or tied embeddings",

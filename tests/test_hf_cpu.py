@@ -248,3 +248,73 @@ def test_llama3_rope_scaling_matches_transformers():
     save_model(lm, path)
     assert load_model(path, device="cpu")[0].cfg.rope_llama3 == (8.0, 1.0, 4.0, 16)
     assert to_hf_llama(lm)[1]["rope_scaling"]["rope_type"] == "llama3"
+
+
+def _tiny_gpt2():
+    cfg = transformers.GPT2Config(vocab_size=131, n_positions=48, n_embd=64, n_layer=2, n_head=4,
+                                  resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    torch.manual_seed(11)
+    hf = transformers.GPT2LMHeadModel(cfg).eval()
+    with torch.no_grad():                     # the default init leaves biases and norms trivial
+        for n, p in hf.named_parameters():
+            if n.endswith(".bias") or "ln_" in n:
+                p.add_(0.1 * torch.randn_like(p))
+    return cfg, hf
+
+
+def test_gpt2_logits_loss_and_gradients_match_transformers(tmp_path):
+    """The reference architecture (LayerNorm, tanh-GELU, biases, absolute positions) with a
+    trained position table and tied output projection, against ``GPT2LMHeadModel``."""
+    from coeus_b200.checkpoint.hf import load_hf_dir, load_hf_gpt2
+    hf_cfg, hf = _tiny_gpt2()
+    lm = load_hf_gpt2(hf.state_dict(), hf_cfg, device="cpu", training=True)
+    assert lm.cfg.pos == "learned" and lm.cfg.tie_embeddings
+    torch.manual_seed(2)
+    ids = torch.randint(0, 131, (2, 21))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1, 131)
+    assert (lm.forward_logits(ids).reshape(42, -1)[:, :131] - want).abs().max() < 2e-4
+    out = hf(input_ids=ids, labels=ids)
+    out.loss.backward()
+    lm.zero_grad()
+    loss = lm.forward_loss(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+    lm.backward()
+    assert abs(float(loss) - float(out.loss.detach())) < 1e-5
+    sd = dict(hf.named_parameters())
+    # position rows beyond the sequence get no gradient; the tied table gets both contributions
+    assert torch.allclose(lm.g["pos_embed"], sd["transformer.wpe.weight"].grad, atol=2e-6)
+    assert torch.allclose(lm.g["token_embed"][:131], sd["transformer.wte.weight"].grad, atol=2e-6)
+    assert torch.allclose(lm.g["layers.1.attn.qkv_weights"],
+                          sd["transformer.h.1.attn.c_attn.weight"].grad, atol=2e-6)
+    assert torch.allclose(lm.g["layers.0.ff.up_bias"],
+                          sd["transformer.h.0.mlp.c_fc.bias"].grad, atol=2e-6)
+    assert torch.allclose(lm.g["final_ln_bias"], sd["transformer.ln_f.bias"].grad, atol=2e-6)
+    # and through the directory reader (the writer de-duplicates the tied head)
+    hf.save_pretrained(str(tmp_path / "g"), safe_serialization=True)
+    lm2 = load_hf_dir(str(tmp_path / "g"), device="cpu")
+    assert (lm2.forward_logits(ids).reshape(42, -1)[:, :131] - want).abs().max() < 2e-4
+
+
+def test_gpt2_greedy_generation_matches_transformers():
+    from coeus_b200.infer.engine import InferenceEngine
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    from coeus_b200.checkpoint.hf import load_hf_gpt2
+    hf_cfg, hf = _tiny_gpt2()
+    lm = load_hf_gpt2(hf.state_dict(), hf_cfg, device="cpu")
+    torch.manual_seed(5)
+    ids = torch.randint(0, 131, (2, 9))
+    with torch.no_grad():
+        want = hf.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=12,
+                           do_sample=False, pad_token_id=0, eos_token_id=None)
+    eng = InferenceEngine(lm, max_batch=2)
+    assert torch.equal(eng.generate(ids, 12), want)
+    # rows at different positions in one decode batch (per-row position lookups)
+    cb = ContinuousBatcher(InferenceEngine(lm, max_batch=2), max_seqs=2, max_len=40)
+    a = cb.submit(ids[0].tolist(), 12)
+    b = cb.submit(ids[1, :5].tolist(), 6)
+    out = cb.run()
+    assert out[a] == want[0, 9:].tolist()
+    with torch.no_grad():
+        w2 = hf.generate(ids[1:2, :5], attention_mask=torch.ones(1, 5, dtype=torch.long),
+                         max_new_tokens=6, do_sample=False, pad_token_id=0, eos_token_id=None)
+    assert out[b] == w2[0, 5:].tolist()
