@@ -105,8 +105,8 @@ class TPInferenceEngine:
             tp.own_rows("ag_attn", T, H).copy_(self._norm(x, p + "norm1"))
             qkv, _ = tp.ag_gemm("ag_attn", m.w[p + "attn.qkv_weights"])
             if cfg.pos == "rope":
-                E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)
-            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+                E.rope_(qkv, nh + m.kvh_l, dh, S, theta=cfg.rope_theta)
+            q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
             D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, nh, dh)
             attn, _ = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
             x_mid = tp.gemm_rs("rs_attn", attn, m.w[p + "attn.o_weights"], resid=x)
@@ -172,9 +172,9 @@ class TPInferenceEngine:
             p = f"layers.{l}."
             qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
             if cfg.pos == "rope":
-                E.rope_(qkv, 2 * nh, dh, S, pos_offset=pos_host, theta=cfg.rope_theta,
+                E.rope_(qkv, nh + m.kvh_l, dh, S, pos_offset=pos_host, theta=cfg.rope_theta,
                         pos_dev=pos_dev)
-            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+            q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
             D.kv_write(k, v, cache.k[l], cache.v[l], table, pos0, S, nh, dh)
             if ctx is None:
                 attn, _ = A.attention_fwd(q, k, v, n_seq, S, nh, dh, causal=True)
@@ -249,8 +249,8 @@ class TPInferenceEngine:
             p = f"layers.{l}."
             qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
             if cfg.pos == "rope":
-                E.rope_(qkv, 2 * nh, dh, 1, theta=cfg.rope_theta, pos_dev=self._pos0)
-            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+                E.rope_(qkv, nh + m.kvh_l, dh, 1, theta=cfg.rope_theta, pos_dev=self._pos0)
+            q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
             D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, self._pos0, 1, nh, dh)
             attn = D.decode_attention(q, cache.k[l], cache.v[l], cache.page_table, self._ctx, nh,
                                       dh, splits=self.decode_splits)

@@ -33,10 +33,6 @@ class TPDecoderLM:
         block's forward, collectives included, again in the backward pass."""
         cfg.validate()
         self.recompute = bool(recompute)
-        if cfg.kv_heads != cfg.num_heads:
-            raise ProcessingError.unsupported(
-                "grouped-query attention under tensor parallelism",
-                "the head sharding here assumes one K/V head per query head")
         if cfg.rope_llama3 is not None or cfg.pos == "learned":
             raise ProcessingError.unsupported(
                 "scaled rotary embeddings / learned positions under tensor parallelism",
@@ -46,22 +42,28 @@ class TPDecoderLM:
                 "tensor-parallel decoder with biases, experts or tied embeddings",
                 "use use_bias=False, num_experts=0, tie_embeddings=False")
         n = tp.tp
-        if cfg.num_heads % n or cfg.intermediate_dim % (8 * n) or cfg.vocab_padded % (8 * n):
+        if cfg.num_heads % n or cfg.kv_heads % n or cfg.intermediate_dim % (8 * n) \
+                or cfg.vocab_padded % (8 * n):
             raise ProcessingError.invalid_input(
-                "heads, intermediate_dim/8 and padded vocab/8 must be divisible by the "
-                "tensor-parallel degree")
+                "heads, key/value heads, intermediate_dim/8 and padded vocab/8 must be divisible "
+                "by the tensor-parallel degree")
         self.cfg, self.tp, self.device = cfg, tp, torch.device(device)
         self.rank, self.n = tp.rank, n
         H, I, L = cfg.hidden_dim, cfg.intermediate_dim, cfg.num_layers
         self.Hl, self.Il, self.Vl = H // n, I // n, cfg.vocab_padded // n
         self.nh_l = cfg.num_heads // n
+        # grouped-query attention: a rank holds whole groups (its query heads and the K/V heads
+        # they read), so attention stays local to the rank
+        self.kvh_l = cfg.kv_heads // n
+        self.Kl = self.kvh_l * cfg.head_dim
+        self.gqa = cfg.kv_heads != cfg.num_heads
         self.swiglu = cfg.activation == "swiglu"
         self.rms = cfg.norm == "rmsnorm"
         up_w = 2 * self.Il if self.swiglu else self.Il
         specs: List[Tuple[str, Tuple[int, ...], bool]] = [("token_embed", (cfg.vocab_size, H), True)]
         for l in range(L):
             p = f"layers.{l}."
-            specs += [(p + "attn.qkv_weights", (H, 3 * self.Hl), True),
+            specs += [(p + "attn.qkv_weights", (H, self.Hl + 2 * self.Kl), True),
                       (p + "attn.o_weights", (self.Hl, H), True),
                       (p + "ff.up_weights", (H, up_w), True),
                       (p + "ff.down_weights", (self.Il, H), True)]
@@ -143,7 +145,9 @@ class TPDecoderLM:
         for l in range(cfg.num_layers):
             p = f"layers.{l}."
             wq = get(p + "attn.qkv_weights")
-            parts = [wq[:, i * H + r * Hl:i * H + (r + 1) * Hl] for i in range(3)]
+            Kl, Hkv = self.Kl, cfg.kv_dim
+            parts = [wq[:, r * Hl:(r + 1) * Hl], wq[:, H + r * Kl:H + (r + 1) * Kl],
+                     wq[:, H + Hkv + r * Kl:H + Hkv + (r + 1) * Kl]]
             self.master[p + "attn.qkv_weights"].copy_(torch.cat(parts, 1))
             self.master[p + "attn.o_weights"].copy_(get(p + "attn.o_weights")[r * Hl:(r + 1) * Hl])
             if self.swiglu:
@@ -189,8 +193,10 @@ class TPDecoderLM:
         for l in range(cfg.num_layers):
             p = f"layers.{l}."
             qkv = gather(self.master[p + "attn.qkv_weights"])
+            Kl = self.Kl
             out[p + "attn.qkv_weights"] = torch.cat(
-                [torch.cat([s[:, i * Hl:(i + 1) * Hl] for s in qkv], 1) for i in range(3)], 1)
+                [torch.cat([s[:, lo:hi] for s in qkv], 1)
+                 for lo, hi in ((0, Hl), (Hl, Hl + Kl), (Hl + Kl, Hl + 2 * Kl))], 1)
             out[p + "attn.o_weights"] = torch.cat(gather(self.master[p + "attn.o_weights"]), 0)
             up = gather(self.master[p + "ff.up_weights"])
             if self.swiglu:
@@ -249,6 +255,18 @@ class TPDecoderLM:
         return self._pe
 
     # ------------------------------------------------------------------ forward
+    def _split_qkv(self, qkv: torch.Tensor):
+        """``(q, k, v)`` of this rank's heads as ``[T, Hl]`` each; under grouped-query attention
+        the rank's K/V heads are repeated for the query heads of their groups (the attention
+        kernels are multi-head)."""
+        Hl, Kl = self.Hl, self.Kl
+        q, k, v = qkv[:, :Hl], qkv[:, Hl:Hl + Kl], qkv[:, Hl + Kl:]
+        if self.gqa:
+            T, dh, g_ = qkv.shape[0], self.cfg.head_dim, self.nh_l // self.kvh_l
+            k, v = (t.reshape(T, self.kvh_l, 1, dh).expand(T, self.kvh_l, g_, dh).reshape(T, Hl)
+                    for t in (k, v))
+        return q, k, v
+
     def _layer_fwd(self, l: int, x: torch.Tensor, B: int, S: int):
         """One block on this rank's ``[T/tp, H]`` rows; returns the block output and the tensors
         its backward needs."""
@@ -261,8 +279,8 @@ class TPDecoderLM:
         qkv, n1_full = tp.ag_gemm("ag_attn", self.w[p + "attn.qkv_weights"])
         n1_full = n1_full.clone()
         if cfg.pos == "rope":
-            E.rope_(qkv, 2 * nh, dh, S, theta=cfg.rope_theta)
-        q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+            E.rope_(qkv, nh + self.kvh_l, dh, S, theta=cfg.rope_theta)
+        q, k, v = self._split_qkv(qkv)
         attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
         x_mid = tp.gemm_rs("rs_attn", attn, self.w[p + "attn.o_weights"], resid=x)
         n2, mean2, rstd2 = self._norm(x_mid, p + "norm2")
@@ -361,12 +379,19 @@ class TPDecoderLM:
             dattn, dxm_full = tp.ag_gemm("ag_attn_b", self.w[p + "attn.o_weights"], b_mn=False)
             G.linear_wgrad(a["attn"], dxm_full, self.g[p + "attn.o_weights"])
             qkv = a["qkv"]
-            q, k, v = qkv[:, :Hl], qkv[:, Hl:2 * Hl], qkv[:, 2 * Hl:]
+            q, k, v = self._split_qkv(qkv)
             dq, dk, dv = A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh,
                                          causal=True)
-            dqkv = dq._base if dq._base is not None else torch.cat([dq, dk, dv], 1)
+            if self.gqa:
+                # a K/V head's gradient is the sum over the query heads of its group
+                g_, Tn = nh // self.kvh_l, dq.shape[0]
+                dk, dv = (t.reshape(Tn, self.kvh_l, g_, dh).float().sum(2).reshape(
+                    Tn, self.Kl).to(dq.dtype) for t in (dk, dv))
+                dqkv = torch.cat([dq, dk, dv], 1)
+            else:
+                dqkv = dq._base if dq._base is not None else torch.cat([dq, dk, dv], 1)
             if cfg.pos == "rope":
-                E.rope_(dqkv, 2 * nh, dh, S, theta=cfg.rope_theta, inverse=True)
+                E.rope_(dqkv, nh + self.kvh_l, dh, S, theta=cfg.rope_theta, inverse=True)
             G.linear_wgrad(a["n1_full"], dqkv, self.g[p + "attn.qkv_weights"])
             dn1 = tp.gemm_rs("rs_attn_b", dqkv, self.w[p + "attn.qkv_weights"], b_mn=False)
             dx = self._norm_bwd(dn1, a["x"], p + "norm1", a["mean1"], a["rstd1"], dx_mid)

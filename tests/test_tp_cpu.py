@@ -140,3 +140,68 @@ def test_tp2_matches_unsharded():
             assert (g[p + "norm1_scale"] - fg[p + "norm1_scale"]).abs().max() < 1e-5
             assert (g[p + "norm2_scale"] - fg[p + "norm2_scale"]).abs().max() < 1e-5
         assert (g["final_norm_scale"] - fg["final_norm_scale"]).abs().max() < 1e-5
+
+
+GQA = DecoderConfig(hidden_dim=64, num_layers=2, num_heads=8, num_kv_heads=4, intermediate_dim=96,
+                    vocab_size=250, max_seq_len=32, use_bias=False, activation="swiglu",
+                    norm="rmsnorm", pos="rope")
+
+
+def _worker_gqa(rank, world, port, batch, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coeus_b200.infer.tp_engine import TPInferenceEngine
+    from coeus_b200.parallel.tp import TensorParallel
+    from coeus_b200.parallel.tp_model import TPDecoderLM
+    full = DecoderLM(GQA, device="cpu", seed=0, dtype=torch.float32)
+    tp = TensorParallel(dist.group.WORLD, "cpu")
+    m = TPDecoderLM(GQA, tp, "cpu", dtype=torch.float32, full=full)
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    m.zero_grad()
+    loss = m.forward_loss(x, y)
+    m.backward()
+    whole = m.gather_full()        # shards put back together = the model they were cut from
+    same = all(torch.equal(whole[k], full.master[k]) for k in
+               ("layers.0.attn.qkv_weights", "layers.1.attn.o_weights", "output_proj"))
+    toks = TPInferenceEngine(m, max_batch=2).generate(x[:, :8].contiguous(), 5)
+    out.put((rank, float(loss), same, toks.numpy().copy(),
+             {k: v.numpy().copy() for k, v in m.g.items() if "attn" in k}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp2_grouped_query_attention_matches_unsharded():
+    """Every rank holds whole groups (4 query heads with their 2 K/V heads): loss, the narrow
+    fused-QKV gradient shard, the reassembled weights and generation equal the unsharded model."""
+    from coeus_b200.infer.engine import InferenceEngine
+    torch.manual_seed(0)
+    batch = torch.randint(0, GQA.vocab_size, (2, 17))
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    full = DecoderLM(GQA, device="cpu", seed=0, dtype=torch.float32)
+    full.zero_grad()
+    ref_loss = float(full.forward_loss(x, y))
+    full.backward()
+    want_toks = InferenceEngine(full, max_batch=2).generate(x[:, :8].contiguous(), 5)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_gqa, args=(r, 2, port, batch, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    H, Hkv = GQA.hidden_dim, GQA.kv_dim
+    Hl, Kl = H // 2, Hkv // 2
+    for rank, loss, same, toks, g in results:
+        assert same and abs(loss - ref_loss) < 1e-4
+        assert torch.equal(torch.from_numpy(toks), want_toks)
+        for l in range(GQA.num_layers):
+            p = f"layers.{l}."
+            fg = full.g[p + "attn.qkv_weights"]
+            want = torch.cat([fg[:, rank * Hl:(rank + 1) * Hl],
+                              fg[:, H + rank * Kl:H + (rank + 1) * Kl],
+                              fg[:, H + Hkv + rank * Kl:H + Hkv + (rank + 1) * Kl]], 1)
+            assert (torch.from_numpy(g[p + "attn.qkv_weights"]) - want).abs().max() < 1e-5
