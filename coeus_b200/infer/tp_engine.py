@@ -105,7 +105,7 @@ class TPInferenceEngine:
             tp.own_rows("ag_attn", T, H).copy_(self._norm(x, p + "norm1"))
             qkv, _ = tp.ag_gemm("ag_attn", m.w[p + "attn.qkv_weights"])
             if cfg.pos == "rope":
-                E.rope_(qkv, nh + m.kvh_l, dh, S, theta=cfg.rope_theta)
+                m._rope(qkv, S)
             q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
             D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, nh, dh)
             attn, _ = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
@@ -172,8 +172,7 @@ class TPInferenceEngine:
             p = f"layers.{l}."
             qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
             if cfg.pos == "rope":
-                E.rope_(qkv, nh + m.kvh_l, dh, S, pos_offset=pos_host, theta=cfg.rope_theta,
-                        pos_dev=pos_dev)
+                m._rope(qkv, S, pos_offset=pos_host, pos_dev=pos_dev)
             q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
             D.kv_write(k, v, cache.k[l], cache.v[l], table, pos0, S, nh, dh)
             if ctx is None:
@@ -249,7 +248,7 @@ class TPInferenceEngine:
             p = f"layers.{l}."
             qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
             if cfg.pos == "rope":
-                E.rope_(qkv, nh + m.kvh_l, dh, 1, theta=cfg.rope_theta, pos_dev=self._pos0)
+                m._rope(qkv, 1, pos_dev=self._pos0)
             q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
             D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, self._pos0, 1, nh, dh)
             attn = D.decode_attention(q, cache.k[l], cache.v[l], cache.page_table, self._ctx, nh,

@@ -33,10 +33,10 @@ class TPDecoderLM:
         block's forward, collectives included, again in the backward pass."""
         cfg.validate()
         self.recompute = bool(recompute)
-        if cfg.rope_llama3 is not None or cfg.pos == "learned":
+        if cfg.pos == "learned":
             raise ProcessingError.unsupported(
-                "scaled rotary embeddings / learned positions under tensor parallelism",
-                "plain RoPE or sinusoidal positions only there")
+                "learned positions under tensor parallelism",
+                "rotary or sinusoidal positions only there")
         if cfg.use_bias or cfg.num_experts or cfg.tie_embeddings:
             raise ProcessingError.unsupported(
                 "tensor-parallel decoder with biases, experts or tied embeddings",
@@ -255,6 +255,22 @@ class TPDecoderLM:
         return self._pe
 
     # ------------------------------------------------------------------ forward
+    def _rope(self, qkv: torch.Tensor, S: int, inverse: bool = False, pos_offset: int = 0,
+              pos_dev: Optional[torch.Tensor] = None) -> None:
+        """Rotary embedding of this rank's query and K/V heads (adjacent in the fused buffer);
+        Llama-3.1 style scaled frequencies go through the explicit frequency table."""
+        cfg, heads = self.cfg, self.nh_l + self.kvh_l
+        if cfg.rope_llama3 is not None:
+            if getattr(self, "_inv_freq", None) is None:
+                f, lo, hi, orig = cfg.rope_llama3
+                self._inv_freq = E.llama3_inv_freq(cfg.head_dim, cfg.rope_theta, f, lo, hi,
+                                                   int(orig)).to(self.device)
+            E.rope_freq_(qkv, heads, cfg.head_dim, S, self._inv_freq, pos_offset=pos_offset,
+                         inverse=inverse, pos_dev=pos_dev)
+        else:
+            E.rope_(qkv, heads, cfg.head_dim, S, pos_offset=pos_offset, theta=cfg.rope_theta,
+                    inverse=inverse, pos_dev=pos_dev)
+
     def _split_qkv(self, qkv: torch.Tensor):
         """``(q, k, v)`` of this rank's heads as ``[T, Hl]`` each; under grouped-query attention
         the rank's K/V heads are repeated for the query heads of their groups (the attention
@@ -279,7 +295,7 @@ class TPDecoderLM:
         qkv, n1_full = tp.ag_gemm("ag_attn", self.w[p + "attn.qkv_weights"])
         n1_full = n1_full.clone()
         if cfg.pos == "rope":
-            E.rope_(qkv, nh + self.kvh_l, dh, S, theta=cfg.rope_theta)
+            self._rope(qkv, S)
         q, k, v = self._split_qkv(qkv)
         attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
         x_mid = tp.gemm_rs("rs_attn", attn, self.w[p + "attn.o_weights"], resid=x)
@@ -391,7 +407,7 @@ class TPDecoderLM:
             else:
                 dqkv = dq._base if dq._base is not None else torch.cat([dq, dk, dv], 1)
             if cfg.pos == "rope":
-                E.rope_(dqkv, nh + self.kvh_l, dh, S, theta=cfg.rope_theta, inverse=True)
+                self._rope(dqkv, S, inverse=True)
             G.linear_wgrad(a["n1_full"], dqkv, self.g[p + "attn.qkv_weights"])
             dn1 = tp.gemm_rs("rs_attn_b", dqkv, self.w[p + "attn.qkv_weights"], b_mn=False)
             dx = self._norm_bwd(dn1, a["x"], p + "norm1", a["mean1"], a["rstd1"], dx_mid)

@@ -144,7 +144,7 @@ def test_tp2_matches_unsharded():
 
 GQA = DecoderConfig(hidden_dim=64, num_layers=2, num_heads=8, num_kv_heads=4, intermediate_dim=96,
                     vocab_size=250, max_seq_len=32, use_bias=False, activation="swiglu",
-                    norm="rmsnorm", pos="rope")
+                    norm="rmsnorm", pos="rope", rope_llama3=(8.0, 1.0, 4.0, 8))
 
 
 def _worker_gqa(rank, world, port, batch, out):
@@ -172,7 +172,8 @@ def _worker_gqa(rank, world, port, batch, out):
 
 
 def test_tp2_grouped_query_attention_matches_unsharded():
-    """Every rank holds whole groups (4 query heads with their 2 K/V heads): loss, the narrow
+    """Llama-3.1 style model (grouped-query attention, scaled rotary frequencies).  Every rank
+    holds whole groups (4 query heads with their 2 K/V heads): loss, the narrow
     fused-QKV gradient shard, the reassembled weights and generation equal the unsharded model."""
     from coeus_b200.infer.engine import InferenceEngine
     torch.manual_seed(0)
