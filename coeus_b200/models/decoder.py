@@ -353,6 +353,8 @@ class DecoderLM:
             # the embedding kernel adds an fp32 table; the working copy is the one every
             # data-parallel rank keeps current
             w = self.w["pos_embed"]
+            if S > w.shape[0]:           # the table has one row per trained position, no more
+                raise ProcessingError.limit_exceeded("sequence length", w.shape[0], S)
             return w if w.dtype == torch.float32 else w.float()
         if self.cfg.pos != "sinusoidal":
             return None

@@ -289,6 +289,8 @@ def test_gpt2_logits_loss_and_gradients_match_transformers(tmp_path):
     assert torch.allclose(lm.g["layers.0.ff.up_bias"],
                           sd["transformer.h.0.mlp.c_fc.bias"].grad, atol=2e-6)
     assert torch.allclose(lm.g["final_ln_bias"], sd["transformer.ln_f.bias"].grad, atol=2e-6)
+    with pytest.raises(Exception, match="[Ss]equence length"):       # 48 trained positions
+        lm.forward_logits(torch.zeros(1, 49, dtype=torch.long))
     # and through the directory reader (the writer de-duplicates the tied head)
     hf.save_pretrained(str(tmp_path / "g"), safe_serialization=True)
     lm2 = load_hf_dir(str(tmp_path / "g"), device="cpu")

@@ -91,3 +91,35 @@ def test_gpu_decoder_matches_transformers_llama(kv_heads):
     torch.cuda.synchronize()
     _lib.check_status(torch.device("cuda", 0))
     assert abs(float(loss) - float(out.loss.detach())) < 0.03
+
+
+def test_gpu_decoder_matches_transformers_gpt2():
+    """LayerNorm, tanh-GELU, biases, a trained position table and the tied head on the bf16 kernel
+    path against ``GPT2LMHeadModel`` in fp32."""
+    transformers = pytest.importorskip("transformers")
+    from coeus_b200.checkpoint.hf import load_hf_gpt2
+    hf_cfg = transformers.GPT2Config(vocab_size=1024, n_positions=256, n_embd=256, n_layer=2,
+                                     n_head=4, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    torch.manual_seed(0)
+    hf = transformers.GPT2LMHeadModel(hf_cfg).eval()
+    lm = load_hf_gpt2(hf.state_dict(), hf_cfg, device="cuda", training=True)
+    ids = torch.randint(0, 1024, (2, 150))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1, 1024)
+    got = lm.forward_logits(ids.cuda()).reshape(300, -1)[:, :1024].float().cpu()
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
+    assert (got - want).abs().max() < 0.05 * want.abs().max() + 0.02
+    hf.train()
+    out = hf(input_ids=ids, labels=ids)
+    out.loss.backward()
+    dev_ids = ids.cuda()
+    lm.zero_grad()
+    loss = lm.forward_loss(dev_ids[:, :-1].contiguous(), dev_ids[:, 1:].contiguous())
+    lm.backward()
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
+    assert abs(float(loss) - float(out.loss.detach())) < 0.03
+    g_want = hf.transformer.wpe.weight.grad
+    g_got = lm.g["pos_embed"].float().cpu()
+    assert (g_got - g_want).abs().max() <= 0.05 * g_want.abs().max() + 1e-4
