@@ -178,6 +178,41 @@ def load_hf_gpt2(state: Mapping[str, torch.Tensor], hf_config: Any, device="cuda
     return lm
 
 
+def to_hf_gpt2(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
+    """``(state dict, config.json fields)`` of a ``GPT2LMHeadModel`` for a model of that family
+    (LayerNorm, tanh-GELU, biases, learned positions, tied head)."""
+    cfg = lm.cfg
+    if not (cfg.pos == "learned" and cfg.norm == "layernorm" and cfg.activation == "gelu"
+            and cfg.use_bias and cfg.tie_embeddings and not cfg.num_experts
+            and cfg.kv_heads == cfg.num_heads):
+        raise ProcessingError.unsupported("export of this configuration in the GPT-2 naming",
+                                          "LayerNorm, GELU, biases, learned positions and a "
+                                          "tied head are that family")
+    V = cfg.vocab_size
+    n1, n2, fn = lm.layout.norm_names
+    m = lm.master
+    out: Dict[str, torch.Tensor] = {"transformer.wte.weight": m["token_embed"][:V].clone(),
+                                    "transformer.wpe.weight": m["pos_embed"].clone()}
+    for l in range(cfg.num_layers):
+        h, p = f"transformer.h.{l}.", f"layers.{l}."
+        for ours, theirs in (("attn.qkv", "attn.c_attn"), ("attn.o", "attn.c_proj"),
+                             ("ff.up", "mlp.c_fc"), ("ff.down", "mlp.c_proj")):
+            out[h + theirs + ".weight"] = m[p + ours + "_weights"].clone()
+            out[h + theirs + ".bias"] = m[p + ours + "_bias"].clone()
+        for ours, theirs in ((n1, "ln_1"), (n2, "ln_2")):
+            out[h + theirs + ".weight"] = m[p + ours + "_scale"].clone()
+            out[h + theirs + ".bias"] = m[p + ours + "_bias"].clone()
+    out["transformer.ln_f.weight"] = m[fn + "_scale"].clone()
+    out["transformer.ln_f.bias"] = m[fn + "_bias"].clone()
+    hf = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_embd": cfg.hidden_dim,
+          "n_layer": cfg.num_layers, "n_head": cfg.num_heads, "n_inner": cfg.intermediate_dim,
+          "n_positions": cfg.max_seq_len, "vocab_size": V,
+          "layer_norm_epsilon": cfg.norm_eps, "activation_function": "gelu_new",
+          "resid_pdrop": 0.0, "embd_pdrop": 0.0, "attn_pdrop": 0.0,
+          "tie_word_embeddings": True, "torch_dtype": "float32"}
+    return out, hf
+
+
 def to_hf_llama(lm) -> Tuple[Dict[str, torch.Tensor], Dict[str, Any]]:
     """``(state dict in the Hugging Face naming, config.json fields)`` of a Llama-style
     :class:`DecoderLM` (RMSNorm, SwiGLU, RoPE, no biases, dense)."""
@@ -248,7 +283,7 @@ def save_hf_dir(lm, path: str) -> None:
 
     from .formats import save_safetensors
     os.makedirs(path, exist_ok=True)
-    state, fields = to_hf_llama(lm)
+    state, fields = to_hf_gpt2(lm) if lm.cfg.pos == "learned" else to_hf_llama(lm)
     save_safetensors(os.path.join(path, "model.safetensors"), state, {"format": "pt"})
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(fields, f, indent=1)

@@ -297,6 +297,18 @@ def test_gpt2_logits_loss_and_gradients_match_transformers(tmp_path):
     assert (lm2.forward_logits(ids).reshape(42, -1)[:, :131] - want).abs().max() < 2e-4
 
 
+def test_gpt2_export_is_read_by_transformers(tmp_path):
+    from coeus_b200.checkpoint.hf import load_hf_dir, load_hf_gpt2, save_hf_dir
+    hf_cfg, hf = _tiny_gpt2()
+    lm = load_hf_gpt2(hf.state_dict(), hf_cfg, device="cpu")
+    save_hf_dir(lm, str(tmp_path / "m"))
+    assert torch.equal(load_hf_dir(str(tmp_path / "m"), device="cpu").p32, lm.p32)
+    again = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m")).eval()
+    ids = torch.randint(0, 131, (1, 20))
+    with torch.no_grad():
+        assert (again(ids).logits - hf(ids).logits).abs().max() < 2e-4
+
+
 def test_gpt2_greedy_generation_matches_transformers():
     from coeus_b200.infer.engine import InferenceEngine
     from coeus_b200.infer.scheduler import ContinuousBatcher

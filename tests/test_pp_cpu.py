@@ -35,12 +35,12 @@ def test_schedule_is_valid_1f1b(P, M):
         assert peak <= min(P - s, M)    # bounded activation stash
 
 
-def _cfg(moe=False):
+def _cfg(moe=False, pos="rope"):
     from coeus_b200.models.config import DecoderConfig
     kw = dict(num_experts=4, top_k=2, capacity_factor=2.0, aux_loss_coef=0.0) if moe else {}
     return DecoderConfig(hidden_dim=32, num_layers=3, num_heads=2, intermediate_dim=48,
                          vocab_size=96, max_seq_len=16, use_bias=False, activation="swiglu",
-                         norm="rmsnorm", pos="rope", **kw)
+                         norm="rmsnorm", pos=pos, **kw)
 
 
 def _train_cfg():
@@ -54,12 +54,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, ids, tgt, out):
+def _worker(rank, world, port, ids, tgt, out, pos="rope"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from coeus_b200.parallel.pp import PipelineStage
-    st = PipelineStage(_cfg(), dist.group.WORLD, "cpu", micro_batches=ids.shape[0], seed=4,
+    st = PipelineStage(_cfg(pos=pos), dist.group.WORLD, "cpu", micro_batches=ids.shape[0], seed=4,
                        dtype=torch.float32, train_cfg=_train_cfg())
     losses = [float(st.train_step(ids, tgt)) for _ in range(2)]
     out.put((rank, losses, {k: v.numpy().copy() for k, v in st.model.master.items()}))
@@ -75,7 +75,9 @@ def test_pipeline_training_matches_single_rank(world):
     M, b, S = 4, 2, 16
     ids = torch.randint(0, 96, (M, b, S))
     tgt = torch.randint(0, 96, (M, b, S))
-    full = DecoderLM(_cfg(), "cpu", seed=4, dtype=torch.float32)
+    # three stages run with a trained position table (its gradient is the first stage's)
+    pos = "learned" if world == 3 else "rope"
+    full = DecoderLM(_cfg(pos=pos), "cpu", seed=4, dtype=torch.float32)
     opt = AdamW(_train_cfg().adamw(), 0, full.n_flat, full.layout.decay_end, "cpu")
     ref_losses = []
     for _ in range(2):
@@ -89,7 +91,8 @@ def test_pipeline_training_matches_single_rank(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, ids, tgt, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ids, tgt, q, pos))
+             for r in range(world)]
     for p in procs:
         p.start()
     res = {r[0]: r for r in (q.get(timeout=300) for _ in range(world))}
