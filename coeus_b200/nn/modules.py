@@ -68,17 +68,29 @@ class CausalSelfAttention(nn.Module):
     """Fused QKV projection, optional RoPE, flash attention, output projection."""
 
     def __init__(self, dim: int, num_heads: int, bias: bool = False, rope: bool = False,
-                 rope_theta: float = 10000.0, device="cuda") -> None:
+                 rope_theta: float = 10000.0, device="cuda", num_kv_heads: int = 0) -> None:
+        """``num_kv_heads`` (0 = ``num_heads``): grouped-query attention, K and V projected to
+        that many heads and shared by the query heads of a group."""
         super().__init__()
         self.nh, self.dh = num_heads, dim // num_heads
+        self.kvh = num_kv_heads or num_heads
+        if num_heads % self.kvh:
+            raise ValueError("num_kv_heads must divide num_heads")
         self.rope, self.theta = rope, rope_theta
-        self.qkv = Linear(dim, 3 * dim, bias, device=device)
+        self.qkv = Linear(dim, dim + 2 * self.kvh * self.dh, bias, device=device)
         self.o = Linear(dim, dim, bias, device=device)
 
     def forward(self, x, B: int, S: int):
         qkv = self.qkv(x)
         if self.rope:
-            qkv = F.rope(qkv, 2 * self.nh, self.dh, S, 0, self.theta)
+            qkv = F.rope(qkv, self.nh + self.kvh, self.dh, S, 0, self.theta)
+        if self.kvh != self.nh:
+            # the attention kernels are multi-head: K/V heads are repeated for their groups
+            # (autograd sums the group's gradients back into the narrow projection)
+            T, H, Hkv, g = qkv.shape[0], self.nh * self.dh, self.kvh * self.dh, self.nh // self.kvh
+            wide = [t.reshape(T, self.kvh, 1, self.dh).expand(T, self.kvh, g, self.dh)
+                    .reshape(T, H) for t in (qkv[:, H:H + Hkv], qkv[:, H + Hkv:])]
+            qkv = torch.cat([qkv[:, :H]] + wide, 1)
         return self.o(F.attention(qkv, B, S, self.nh, self.dh, True))
 
 
@@ -102,11 +114,13 @@ class Block(nn.Module):
     """Pre-norm decoder block (the reference's ``TransformerLayer``, lib.rs:425-500)."""
 
     def __init__(self, dim: int, num_heads: int, inter: int, rms: bool = False, bias: bool = True,
-                 swiglu: bool = False, rope: bool = False, device="cuda") -> None:
+                 swiglu: bool = False, rope: bool = False, device="cuda",
+                 num_kv_heads: int = 0) -> None:
         super().__init__()
         Norm = RMSNorm if rms else LayerNorm
         self.norm1, self.norm2 = Norm(dim, device=device), Norm(dim, device=device)
-        self.attn = CausalSelfAttention(dim, num_heads, bias, rope, device=device)
+        self.attn = CausalSelfAttention(dim, num_heads, bias, rope, device=device,
+                                        num_kv_heads=num_kv_heads)
         self.mlp = MLP(dim, inter, bias, swiglu, device=device)
 
     def forward(self, x, B: int, S: int):
@@ -128,17 +142,18 @@ class TransformerLM(nn.Module):
 
     def __init__(self, cfg, device="cuda") -> None:
         super().__init__()
-        if cfg.num_experts or cfg.kv_heads != cfg.num_heads or cfg.rope_llama3 is not None \
-                or cfg.pos == "learned":
-            raise ValueError("TransformerLM covers dense multi-head models; use DecoderLM for "
-                             "experts, grouped-query attention and scaled rotary embeddings")
+        if cfg.num_experts or cfg.rope_llama3 is not None or cfg.pos == "learned":
+            raise ValueError("TransformerLM covers dense models with sinusoidal or plain rotary "
+                             "positions; use DecoderLM for experts, scaled rotary embeddings "
+                             "and learned positions")
         self.cfg = cfg
         H = cfg.hidden_dim
         rms, swiglu, rope = cfg.norm == "rmsnorm", cfg.activation == "swiglu", cfg.pos == "rope"
         self.embed = Embedding(cfg.vocab_size, H, device=device, init_std=cfg.init_std)
         self.blocks = nn.ModuleList([
             Block(H, cfg.num_heads, cfg.intermediate_dim, rms=rms, bias=cfg.use_bias,
-                  swiglu=swiglu, rope=rope, device=device) for _ in range(cfg.num_layers)])
+                  swiglu=swiglu, rope=rope, device=device, num_kv_heads=cfg.num_kv_heads)
+            for _ in range(cfg.num_layers)])
         for b in self.blocks:
             b.norm1.eps = b.norm2.eps = cfg.norm_eps
             b.attn.theta = cfg.rope_theta

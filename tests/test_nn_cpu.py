@@ -76,7 +76,7 @@ def test_functional_softmax_and_gelu_values():
     assert float(F.gelu(torch.tensor([[1.0]]))) > 0 > float(F.gelu(torch.tensor([[-1.0]])))
 
 
-@pytest.mark.parametrize("kind", ["gpt", "llama", "tied"])
+@pytest.mark.parametrize("kind", ["gpt", "llama", "tied", "gqa"])
 def test_autograd_transformer_matches_the_explicit_decoder(kind):
     """The nn.Module model with the explicit decoder's weights: same loss, and autograd's
     gradients equal the hand-written backward pass."""
@@ -85,8 +85,10 @@ def test_autograd_transformer_matches_the_explicit_decoder(kind):
     from coeus_b200.nn import TransformerLM
     kw = dict(hidden_dim=32, num_layers=2, num_heads=2, intermediate_dim=64, vocab_size=64,
               max_seq_len=16)
-    if kind == "llama":
+    if kind in ("llama", "gqa"):
         kw.update(use_bias=False, activation="swiglu", norm="rmsnorm", pos="rope")
+    if kind == "gqa":                  # 4 query heads reading 2 key/value heads
+        kw.update(num_heads=4, num_kv_heads=2)
     if kind == "tied":
         kw.update(tie_embeddings=True)
     cfg = DecoderConfig(**kw)
