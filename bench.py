@@ -31,16 +31,34 @@ SEQ_LEN = 2048
 SEQS_PER_GPU = 8
 
 
-def reference_arm(args) -> int:
-    """The reference is a Rust workspace with no Python packaging and no GPU path; it cannot be
-    installed or run here (no cargo/rustc in the image, pip finds no setup.py/pyproject)."""
+def probe_reference_toolchain() -> dict:
+    """What the reference would need in order to run here: a Rust compiler (it is a Rust
+    workspace; its core crate and the transformer plugin have no external dependencies, so
+    ``rustc`` alone would do) and, for the packaged arm, an installed copy under
+    ``baseline/_ref``."""
+    import shutil
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    why = ("reference is a pure-Rust CPU library (no setup.py/pyproject, no cargo/rustc in the "
-           "image, no GPU or training path): pip install of the reference tree fails and nothing "
-           "of it can run the train-tokens/s benchmark")
-    if os.path.isdir(ref_dir) and os.listdir(ref_dir):
-        why = "baseline/_ref holds no runnable package: " + why
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return {"rustc": shutil.which("rustc"), "cargo": shutil.which("cargo"),
+            "ref_installed": os.path.isdir(ref_dir) and bool(os.listdir(ref_dir))}
+
+
+def reference_arm(args) -> int:
+    """The reference is a Rust CPU library without a training step, a GPU path or Python
+    packaging.  The arm probes for a Rust toolchain at run time; without one (or with one: the
+    reference has no backward pass, optimizer or batching, so it cannot produce train tokens/s)
+    it answers with its one-line ``unavailable`` record."""
+    probe = probe_reference_toolchain()
+    if probe["rustc"] is None:
+        why = ("no Rust toolchain on this box (probe: rustc=None, cargo=%s) and pip cannot install "
+               "the reference (a Rust workspace with neither setup.py nor pyproject.toml); the "
+               "reference also has no training step (forward only, CPU only), so it cannot run "
+               "the train-tokens/s benchmark" % probe["cargo"])
+    else:
+        why = ("rustc found at %s, but the reference has no backward pass, optimizer, batching or "
+               "GPU path (forward of one sequence on the CPU only), so the train-tokens/s "
+               "benchmark cannot be run through its public API; its forward loops are timed by "
+               "benchmarks/cpu_baseline.py" % probe["rustc"])
+    print(json.dumps({"impl": "reference", "unavailable": why, "probe": probe}))
     return 0
 
 
@@ -97,6 +115,78 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def build_config(seq_len: int = SEQ_LEN):
+    """The model configuration every arm of the benchmark trains."""
+    from coeus_b200.models.config import DecoderConfig
+    return DecoderConfig.transformer_250m(max_seq_len=seq_len)
+
+
+def build_arm(impl: str, cfg, dev, world: int):
+    """``(step, parallelism, owner)`` of one arm: ``step(batch [B, S+1]) -> loss`` runs one whole
+    training step (forward, backward, gradient reduction, AdamW); ``owner`` keeps the arm's
+    state alive and is dropped to free it."""
+    if impl == "coeus":
+        import torch.distributed as dist
+        from coeus_b200.models.decoder import DecoderLM
+        from coeus_b200.train.trainer import TrainConfig, Trainer
+        model = DecoderLM(cfg, device=dev, init="normal", seed=0)
+        dp = None
+        if world > 1:
+            from coeus_b200.parallel.zero import ShardedDataParallel
+            dp = ShardedDataParallel(dist.group.WORLD, dev)
+        trainer = Trainer(model, TrainConfig(learning_rate=3e-4), dp=dp)
+
+        def step(batch):
+            return trainer.train_step(batch[:, :-1], batch[:, 1:])
+        par = (f"dp{world} (sharded AdamW state, fused RS+AdamW+AG over NVLink peer memory)"
+               if world > 1 else "single GPU")
+        return step, par, trainer
+    from coeus_b200.models import torch_baseline
+    runner = torch_baseline.TorchBaseline(cfg, dev, world)
+    return runner.step, f"ddp{world} (stock PyTorch: bf16 weights, cuBLAS + SDPA + NCCL)", runner
+
+
+def time_arm(step, dev_pool, host, args, dev, world, sync_all, lib=None, e2e=True):
+    """Warm-up, the device-timed region and the end-to-end region of one arm.  Returns a dict
+    of this rank's times (ms) plus clocks and launch count."""
+    import torch
+    n_pool = len(dev_pool)
+    for i in range(args.warmup):
+        loss = step(dev_pool[i % n_pool])
+    sync_all()
+    if lib is not None:
+        lib.check_status(dev)
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    launches0 = lib.launch_count if lib is not None else 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for i in range(args.steps):
+        loss = step(dev_pool[i % n_pool])
+    e1.record()
+    sync_all()
+    out = {"ms": e0.elapsed_time(e1), "clocks": sampler.stop(),
+           "launches": (lib.launch_count - launches0) if lib is not None else 0,
+           "loss": float(loss), "e2e_ms": 0.0}
+    if e2e:
+        # end to end through the public API: pinned host batch -> device, step, loss -> host
+        staging = torch.empty_like(dev_pool[0])
+        sync_all()
+        t0 = time.perf_counter()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(args.steps):
+            staging.copy_(host[i % n_pool], non_blocking=True)
+            float(step(staging))
+        f1.record()
+        sync_all()
+        out["e2e_ms"] = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3)
+    if lib is not None:
+        lib.check_status(dev)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -106,6 +196,9 @@ def main() -> int:
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-compare", action="store_true",
+                    help="skip the stock-PyTorch comparator that the coeus arm times afterwards "
+                         "in the same process to fill vs_baseline")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -128,10 +221,9 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    from coeus_b200.models.config import DecoderConfig
     from coeus_b200.ops import _lib
 
-    cfg = DecoderConfig.transformer_250m(max_seq_len=args.seq_len)
+    cfg = build_config(args.seq_len)
     B, S = args.seqs_per_gpu, args.seq_len
     tokens_per_step = B * S * world
 
@@ -142,78 +234,43 @@ def main() -> int:
             for _ in range(n_pool)]
     dev_pool = [h.to(dev) for h in host]
 
-    if args.impl == "coeus":
-        from coeus_b200.models.decoder import DecoderLM
-        from coeus_b200.train.trainer import TrainConfig, Trainer
-        model = DecoderLM(cfg, device=dev, init="normal", seed=0)
-        dp = None
-        if world > 1:
-            from coeus_b200.parallel.zero import ShardedDataParallel
-            dp = ShardedDataParallel(dist.group.WORLD, dev)
-        trainer = Trainer(model, TrainConfig(learning_rate=3e-4), dp=dp)
-
-        def step(batch):
-            return trainer.train_step(batch[:, :-1], batch[:, 1:])
-        parallelism = f"dp{world} (sharded AdamW state, fused RS+AdamW+AG over NVLink P2P)" \
-            if world > 1 else "single GPU"
-    else:
-        from coeus_b200.models import torch_baseline
-        runner = torch_baseline.TorchBaseline(cfg, dev, world)
-        step = runner.step
-        parallelism = f"ddp{world} (stock PyTorch: cuBLAS + SDPA + NCCL)"
-
     def sync_all():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up
-    for i in range(args.warmup):
-        loss = step(dev_pool[i % n_pool])
-    sync_all()
-    if args.impl == "coeus":
-        _lib.check_status(dev)
+    def max_over_ranks(*vals):
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
 
-    # ---- device-timed region
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    launches0 = _lib.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    for i in range(args.steps):
-        loss = step(dev_pool[i % n_pool])
-    e1.record()
-    sync_all()
-    ms = e0.elapsed_time(e1)
-    launches = _lib.launch_count - launches0
-    clocks = sampler.stop()
-    final_loss = float(loss)
+    # ---- the comparator (same model, config, steps and data on stock PyTorch) is timed first,
+    # in the same process, and its state released before this framework's arm is built
+    baseline = None
+    if args.impl == "coeus" and not args.no_compare:
+        try:
+            tstep, tpar, towner = build_arm("torch", cfg, dev, world)
+            theirs = time_arm(tstep, dev_pool, host, args, dev, world, sync_all, lib=None,
+                              e2e=not args.no_e2e)
+            t_ms, t_e2e = max_over_ranks(theirs["ms"], theirs["e2e_ms"])
+            baseline = {"impl": "torch", "parallelism": tpar,
+                        "ms_per_step": t_ms / args.steps,
+                        "value": tokens_per_step / (t_ms / args.steps / 1e3),
+                        "final_loss": theirs["loss"]}
+            if not args.no_e2e:
+                baseline["e2e_value"] = tokens_per_step / (t_e2e / args.steps / 1e3)
+        except Exception as exc:   # the comparator must never cost the headline its number
+            baseline = {"impl": "torch", "error": f"{type(exc).__name__}: {exc}"[:200]}
+        tstep = towner = theirs = None
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
 
-    # ---- end to end through the public API: pinned host batch -> device, step, loss -> host
-    e2e = None
-    if not args.no_e2e:
-        staging = torch.empty((B, S + 1), dtype=torch.int64, device=dev)
-        sync_all()
-        t0 = time.perf_counter()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for i in range(args.steps):
-            staging.copy_(host[i % n_pool], non_blocking=True)
-            loss_host = float(step(staging))
-        f1.record()
-        sync_all()
-        e2e_ms = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3)
-        e2e = {"ms": e2e_ms, "h2d": host[0].numel() * 8 * world, "d2h": 4 * world}
-
-    if args.impl == "coeus":
-        _lib.check_status(dev)
-
-    # ---- max over ranks
-    vals = torch.tensor([ms, e2e["ms"] if e2e else 0.0], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms_max, e2e_ms_max = vals.tolist()
+    step, parallelism, owner = build_arm(args.impl, cfg, dev, world)
+    mine = time_arm(step, dev_pool, host, args, dev, world, sync_all,
+                    lib=_lib if args.impl == "coeus" else None, e2e=not args.no_e2e)
+    ms_max, e2e_ms_max = max_over_ranks(mine["ms"], mine["e2e_ms"])
 
     if rank == 0:
         ms_per_step = ms_max / args.steps
@@ -221,7 +278,10 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / baseline["value"]) if baseline and "value" in baseline
+            else None,
+            "dtype": "bf16",
             "data": "synthetic (uniform random token ids, random-init weights)",
             "impl": args.impl,
             "config": {"model": "Transformer-250M (V32000 H1024 L16 nh16 FFN4096, "
@@ -229,13 +289,19 @@ def main() -> int:
                        "global_batch": B * world, "seq_len": S, "parallelism": parallelism,
                        "optimizer": "AdamW lr 3e-4 (fp32 master weights and moments)",
                        "l2": "no explicit flush: every step streams > 10 GB of weights, "
-                             "activations and optimizer state, far above the 126 MB L2"},
-            "clocks": clocks, "gpu_launches": launches, "final_loss": final_loss,
+                             "activations and optimizer state, far above the 126 MB L2",
+                       "baseline": "the reference publishes no number and cannot run here; "
+                                   "vs_baseline is against the stock-PyTorch arm timed in this "
+                                   "same process (see 'baseline')"},
+            "clocks": mine["clocks"], "gpu_launches": mine["launches"],
+            "final_loss": mine["loss"],
         }
-        if e2e:
+        if baseline is not None:
+            out["baseline"] = baseline
+        if not args.no_e2e:
             out["e2e"] = {"value": tokens_per_step / (e2e_ms_max / args.steps / 1e3),
-                          "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
-                          "d2h_bytes_per_step": e2e["d2h"]}
+                          "unit": "tokens/s", "h2d_bytes_per_step": host[0].numel() * 8 * world,
+                          "d2h_bytes_per_step": 4 * world}
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

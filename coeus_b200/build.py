@@ -5,8 +5,9 @@ Two shared objects are produced under ``coeus_b200/lib/``:
 * ``libcoeus_kernels.so`` – every ``.cu`` file of ``coeus_b200/csrc`` compiled by ``nvcc`` for
   ``sm_100a`` only (``-gencode arch=compute_100a,code=sm_100a``); plain ``extern "C"`` entry
   points that take raw device pointers and a stream, loaded through ``ctypes``.
-* ``_coeus_host*.so`` – the host-side C++ components (tokenizers, checkpoint IO, iterators,
-  text algorithms, CPU oracle) as a pybind11 module.
+* ``_coeus_host*.so`` – the host-side C++ components of ``csrc/host`` (``tokenizers.cpp``,
+  ``io.cpp`` checkpoint formats, ``pipeline.cpp`` data loader / suffix array / bloom filter /
+  arena, ``oracle.cpp`` CPU oracle) as a pybind11 module.
 
 ``python -m coeus_b200.build`` builds both; ``build_all(force=True)`` rebuilds from scratch.
 """
@@ -64,7 +65,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     OBJ.mkdir(exist_ok=True)
     out = kernels_lib_path()
     cus = sorted(CSRC.glob("*.cu"))
-    hdrs = sorted(CSRC.glob("*.cuh"))
+    hdrs = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
     stamp = LIB / "kernels.sha256"
     digest = _digest(cus + hdrs)
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:

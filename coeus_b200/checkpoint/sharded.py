@@ -9,6 +9,12 @@ assembles each from whichever files overlap it (memory-mapped reads).  Saving ca
 background: the pieces are copied to pinned host memory on a side stream and a writer thread
 does the file IO.  A file whose hash no longer matches the manifest is reported as corrupt.
 
+A save never touches the files of the previous checkpoint: every step's files carry the step in
+their name and are written under a temporary name first, the manifest is replaced atomically
+once all of them exist, and only then are the files that the new manifest no longer lists
+removed.  A crash at any point of a save leaves the previous manifest and its files intact, so
+a resume loads the last complete checkpoint.
+
 The reference has only whole-model ``.rustllm`` files without optimizer state, and names a
 ``Checkpoint{checkpoint(), restore()}`` trait that nothing implements (src/core/traits.rs:181-189,
 src/domain/persistence/mod.rs:10-29)."""
@@ -30,9 +36,19 @@ MANIFEST = "manifest.json"
 STATE_NAMES = ("p32", "m", "v")
 Segment = Tuple[int, int]
 
+# Host-side fault injection (coeus_b200.parallel.health.FaultInjector or None): the save path
+# reports the points "checkpoint.shard_written" and "checkpoint.before_manifest" to it, which is
+# how the crash-during-save drill interrupts a save between the shard files and the manifest.
+fault_injector = None
 
-def _shard_file(rank: int) -> str:
-    return f"shard_{rank:05d}.safetensors"
+
+def _reach(point: str) -> None:
+    if fault_injector is not None:
+        fault_injector.reach(point)
+
+
+def _shard_file(rank: int, step: int) -> str:
+    return f"shard_{rank:05d}.step{step:09d}.safetensors"
 
 
 def file_hash(path: str) -> str:
@@ -98,25 +114,29 @@ def save_shard(directory: str, rank: int, world: int, segments: Sequence[Segment
     if cuda_dev is not None:
         event = torch.cuda.Event()
         event.record(torch.cuda.current_stream(cuda_dev))
-    path = os.path.join(directory, _shard_file(rank))
+    path = os.path.join(directory, _shard_file(rank, step))
     side = {"rank": rank, "world": world, "step": step,
             "segments": [[int(s), int(e)] for s, e in segments if e > s]}
 
     def write():
         if event is not None:
             event.synchronize()
-        save_safetensors(path, host, {"step": str(step), "rank": str(rank)})
-        side["hash"] = file_hash(path)
-        with open(path + ".json", "w") as f:
+        save_safetensors(path + ".tmp", host, {"step": str(step), "rank": str(rank)})
+        side["hash"] = file_hash(path + ".tmp")
+        os.replace(path + ".tmp", path)
+        with open(path + ".json.tmp", "w") as f:
             json.dump(side, f)
+        os.replace(path + ".json.tmp", path + ".json")
 
     if writer is not None:
         writer.submit(write)
         return
     write()
+    _reach("checkpoint.shard_written")
     if barrier is not None:
         barrier()
     if rank == 0:
+        _reach("checkpoint.before_manifest")
         finalize_manifest(directory, world, step, meta or {})
     if barrier is not None:
         barrier()
@@ -126,7 +146,7 @@ def finalize_manifest(directory: str, world: int, step: int, meta: dict) -> None
     """Merge the per-rank side files into ``manifest.json`` (call once all files are written)."""
     files = []
     for r in range(world):
-        p = os.path.join(directory, _shard_file(r) + ".json")
+        p = os.path.join(directory, _shard_file(r, step) + ".json")
         if not os.path.exists(p):
             raise IoError.file_system(p, "open", "file not found")
         with open(p) as f:
@@ -134,12 +154,31 @@ def finalize_manifest(directory: str, world: int, step: int, meta: dict) -> None
         if side["step"] != step:
             raise ProcessingError.invalid_input(
                 f"shard {r} is from step {side['step']}, expected {step}")
-        files.append({"file": _shard_file(r), "segments": side["segments"], "hash": side["hash"]})
+        files.append({"file": _shard_file(r, step), "segments": side["segments"], "hash": side["hash"]})
     man = {"format": "coeus-sharded-1", "step": step, "world": world, "files": files, "meta": meta}
     tmp = os.path.join(directory, MANIFEST + ".tmp")
     with open(tmp, "w") as f:
         json.dump(man, f)
     os.replace(tmp, os.path.join(directory, MANIFEST))     # atomic: a manifest is never partial
+    _remove_stale_shards(directory, {e["file"] for e in files})
+
+
+def _remove_stale_shards(directory: str, keep: set) -> None:
+    """Delete shard files (and their side files, and left-over temporaries) that the current
+    manifest does not list: the previous checkpoint's, and the remains of an interrupted save."""
+    for name in os.listdir(directory):
+        if not name.startswith("shard_"):
+            continue
+        base = name
+        for suffix in (".json.tmp", ".tmp", ".json"):
+            if base.endswith(suffix):
+                base = base[: -len(suffix)]
+                break
+        if base not in keep:
+            try:
+                os.remove(os.path.join(directory, name))
+            except OSError:
+                pass
 
 
 def read_manifest(directory: str) -> dict:

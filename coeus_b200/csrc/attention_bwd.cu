@@ -531,6 +531,14 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int H = nh * dh;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
+  // every argument check (the tensor maps included) comes before the first launch, so that a
+  // refused call has enqueued nothing
+  const uint32_t bq = dh == 64 ? 128 : 64;
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_tmap_bf16_2d(&tq, q, H, rows, ldq, 64, bq) != 0) return -3;
+  if (make_tmap_bf16_2d(&tk, k, H, rows, ldk, 64, ATB_BKV) != 0) return -4;
+  if (make_tmap_bf16_2d(&tv, v, H, rows, ldv, 64, ATB_BKV) != 0) return -5;
+  if (make_tmap_bf16_2d(&tdo, dO, H, rows, lddo, 64, bq) != 0) return -6;
   {
     const size_t work = rows * nh * (dh / 8);
     const int blocks = static_cast<int>(std::min<size_t>((work + 255) / 256, sm_count() * 16));
@@ -538,12 +546,6 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
                                               static_cast<const __nv_bfloat16*>(o), delta, B, S,
                                               nh, dh, lddo, ldo);
   }
-  const uint32_t bq = dh == 64 ? 128 : 64;
-  CUtensorMap tq, tk, tv, tdo;
-  if (make_tmap_bf16_2d(&tq, q, H, rows, ldq, 64, bq) != 0) return -3;
-  if (make_tmap_bf16_2d(&tk, k, H, rows, ldk, 64, ATB_BKV) != 0) return -4;
-  if (make_tmap_bf16_2d(&tv, v, H, rows, ldv, 64, ATB_BKV) != 0) return -5;
-  if (make_tmap_bf16_2d(&tdo, dO, H, rows, lddo, 64, bq) != 0) return -6;
   AttnBwdArgs a;
   a.B = B; a.S = S; a.nh = nh;
   a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
@@ -573,9 +575,12 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
 
 static __device__ __align__(256) float g_noalloc_scratch[CB_NOALLOC_SCRATCH_FLOATS];
 
+#include <mutex>
+
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;   // guards the one-time fill of g_noalloc_ptr
 
 // Device address of the scratch array on the current device.  In host code the array's name is
 // only a handle for the runtime, not an address a kernel could use, so the address is asked for
@@ -584,6 +589,7 @@ int noalloc_scratch(float** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return CB_NOALLOC_ERR_SYMBOL;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (g_noalloc_ptr[dev] == nullptr) {
     float* p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess ||
@@ -600,7 +606,10 @@ extern "C" int cb_attn_bwd_noalloc(const void* dO, const void* q, const void* k,
                                    const void* o, const float* lse, void* dqkv, int B, int S,
                                    int nh, int dh, int lddo, int ldq, int ldk, int ldv, int ldo,
                                    int ldd, float scale, int causal, int* status, void* stream) {
-  if (B <= 0 || S <= 0 || nh <= 0 || dh <= 0) return -2;
+  // the checks cb_attn_bwd() would make on these arguments, made here before anything (the
+  // clearing of the scratch included) is enqueued
+  if (dh != 64 && dh != 128) return -1;
+  if (B <= 0 || S <= 0 || nh <= 0 || (ldd % 8) != 0) return -2;
   const size_t dq_floats = static_cast<size_t>(B) * S * nh * dh;
   const size_t delta_floats = static_cast<size_t>(B) * nh * S;
   if (dq_floats + delta_floats > CB_NOALLOC_SCRATCH_FLOATS) return CB_NOALLOC_ERR_TOO_LARGE;
@@ -623,6 +632,8 @@ extern "C" const char* cb_noalloc_strerror(int code) {
              "of CB_NOALLOC_SCRATCH_FLOATS (4 Mi floats, 16 MiB)";
     case CB_NOALLOC_ERR_SYMBOL:
       return "could not obtain the device address of the built-in scratch array";
+    case -1: return "unsupported head dimension (the kernels cover dh = 64 and dh = 128)";
+    case -2: return "bad sizes: B, S and nh must be positive and ldd a multiple of 8";
     case -102: return "clearing the scratch failed";
     default: return "attention backward failed (see cb_attn_bwd return codes)";
   }

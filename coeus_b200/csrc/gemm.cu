@@ -795,7 +795,9 @@ extern "C" void cb_gemm_use_pairs(int on) { cb::g_use_pairs = on; }
 // D[M,N] = epilogue(alpha * A . B^T)
 //   A: logical [M,K]; a_mn == 0: memory [M,K] row-major (pitch lda); a_mn == 1: memory [K,M].
 //   B: logical [N,K]; b_mn == 0: memory [N,K] row-major (pitch ldb); b_mn == 1: memory [K,N].
-// Requirements: K, N (and M when a_mn) multiples of 8; 16-byte aligned pointers and pitches.
+// Requirements: N a multiple of 8; K a multiple of 8 unless both operands are
+// MN-major (there K is the outer, strided dimension of both tensor maps and any length works: the
+// last k-block reads zero fill past the end); 16-byte aligned pointers and pitches.
 //
 // groups > 1 (grouped GEMM, e.g. the experts of a mixture-of-experts layer): M, N and K are the
 // sizes of ONE group and every operand holds the groups stacked along the row dimension of its
@@ -811,7 +813,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* D, int M, int N, i
                           int* status, int max_ctas, void* stream, int groups) {
   using namespace cb;
   if (M <= 0 || N <= 0 || K <= 0 || groups < 1) return -20;
-  if ((N % 8) != 0 || (K % 8) != 0 || (ldd % 4) != 0) return -21;
+  if ((N % 8) != 0 || (ldd % 4) != 0) return -21;
+  if ((K % 8) != 0 && !(a_mn && b_mn)) return -21;
   if (out_mode == OUT_BF16 && (ldd % 8) != 0) return -21;
   // bn = 512 selects the 256-wide tile on CTA pairs
   bool pairs = bn == 512 || (bn == 256 && cb::g_use_pairs);

@@ -10,7 +10,7 @@ carries the item that overflowed the limit into the next batch, where the refere
 (iterator.rs:617-624).  The "literature" iterators (rope, B-tree, suffix array, wavelet-tree
 placeholder, trie, Bloom-filter bits) follow.  The token-stream versions that feed training
 (windows / chunks / batch over int32 arrays with a pinned double-buffer prefetch) are native, in
-``csrc/host/iter.cpp``, and are reached through :mod:`coeus_b200.train.data`.
+``csrc/host/pipeline.cpp``, and are reached through :mod:`coeus_b200.train.data`.
 """
 from __future__ import annotations
 

@@ -197,10 +197,18 @@ class ContinuousBatcher:
             ids = torch.tensor(r.prompt, dtype=torch.int64, device=self.device)
             try:
                 logits = self._prefill(r, ids)
-            except Error as e:           # a framework error (e.g. no pages): this request only
+            except BaseException as e:
+                # whatever the prefill raised, the slot and the pages it reserved or adopted go
+                # back first; an ordinary exception (a framework error such as "no pages", a
+                # kernel-library or torch error) then ends this request only, anything else
+                # (KeyboardInterrupt, SystemExit) propagates
                 eng.cache.release(r.slot)
                 self.free_slots.append(r.slot)
-                r.slot, r.error = -1, e
+                r.slot = -1
+                if not isinstance(e, Exception):
+                    self.waiting.appendleft(r)
+                    raise
+                r.error = e
                 finished.append(r)
                 continue
             r.push(int(self._sample(logits[None], r)[0]))

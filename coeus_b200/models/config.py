@@ -187,7 +187,11 @@ class DecoderConfig:
 
     @classmethod
     def transformer_250m(cls, max_seq_len: int = 2048) -> "DecoderConfig":
-        return Transformer250MConfig.benchmark_250m(max_seq_len).to_decoder()
+        # the reference declares dropout = 0.1 in this preset and never applies it (its forward
+        # pass has no dropout, plugins/model-transformer/src/lib.rs:791-919); the throughput
+        # benchmark trains without dropout, callers that want it pass the rates explicitly
+        return Transformer250MConfig.benchmark_250m(max_seq_len).to_decoder(
+            dropout=0.0, attention_dropout=0.0)
 
     @classmethod
     def decoder_1p3b(cls, max_seq_len: int = 4096) -> "DecoderConfig":

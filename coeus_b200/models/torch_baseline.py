@@ -1,5 +1,8 @@
-"""Comparator arm: the same decoder on stock PyTorch (fp32 parameters under bf16 autocast, cuBLAS
-GEMMs, SDPA attention, fused torch AdamW, ``DistributedDataParallel`` over NCCL).  None of this
+"""Comparator arm: the same decoder on stock PyTorch (cuBLAS GEMMs, SDPA attention, fused torch
+AdamW, ``DistributedDataParallel`` over NCCL).  Parameters are resident in bf16 by default, so no
+step pays for casting weights (and the optimizer updates bf16 directly, without the fp32 master
+copy this framework keeps: the comparator does strictly less work per step);
+``resident="fp32"`` selects fp32 parameters under bf16 autocast instead.  None of this
 framework's kernels are used here; it exists to be measured against."""
 from __future__ import annotations
 
@@ -12,9 +15,10 @@ from .decoder import ParamLayout
 
 
 class TorchDecoder(nn.Module):
-    def __init__(self, cfg: DecoderConfig, device) -> None:
+    def __init__(self, cfg: DecoderConfig, device, resident: str = "bf16") -> None:
         super().__init__()
         self.cfg = cfg
+        self.resident = resident
         self.params = nn.ParameterDict()
         gen = torch.Generator(device=device)
         gen.manual_seed(0)
@@ -26,17 +30,21 @@ class TorchDecoder(nn.Module):
                 t.fill_(1.0)
             else:
                 t.zero_()
+            if resident == "bf16":
+                t = t.to(torch.bfloat16)
             self.params[s.name.replace(".", "__")] = nn.Parameter(t)
 
     def forward(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         named = {k.replace("__", "."): v for k, v in self.params.items()}
+        if self.resident == "bf16":
+            return R.forward_loss(named, self.cfg, ids, targets)
         with torch.autocast("cuda", dtype=torch.bfloat16):
             return R.forward_loss(named, self.cfg, ids, targets)
 
 
 class TorchBaseline:
-    def __init__(self, cfg: DecoderConfig, device, world: int) -> None:
-        self.module = TorchDecoder(cfg, device)
+    def __init__(self, cfg: DecoderConfig, device, world: int, resident: str = "bf16") -> None:
+        self.module = TorchDecoder(cfg, device, resident)
         self.model = self.module
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP

@@ -208,3 +208,28 @@ def test_a_request_that_cannot_be_admitted_fails_alone():
     assert len(cb.free_slots) == 2 and kv.pages_in_use() == kv.num_pages - 2
     ok2 = cb.submit([4, 5, 6], 2)
     assert len(cb.run()[ok2]) == 2
+
+
+def test_a_prefill_that_raises_a_foreign_error_gives_its_slot_and_pages_back():
+    """An exception that is not one of the framework's (a kernel-library or torch error is a
+    ``RuntimeError``) ends that request only: the slot and the pages return to their pools and
+    the batcher keeps serving."""
+    from coeus_b200.infer.scheduler import ContinuousBatcher
+    m = _model("llama")
+    cb = ContinuousBatcher(InferenceEngine(m, max_batch=2), max_seqs=2, max_len=160)
+    kv = cb.engine.cache
+    slots0, pages0 = len(cb.free_slots), kv.pages_in_use()
+    real = cb.engine.prefill_slot
+
+    def boom(slot, ids, total, **kw):
+        real(slot, ids, total, **kw)          # reserves pages and writes K/V first
+        raise RuntimeError("launch failed")
+    cb.engine.prefill_slot = boom
+    bad = cb.submit([1, 2, 3, 4], 3)
+    fin = cb.step()
+    assert [r.id for r in fin] == [bad] and isinstance(fin[0].error, RuntimeError)
+    assert len(cb.free_slots) == slots0 and kv.pages_in_use() == pages0
+    assert cb.pending() == 0
+    cb.engine.prefill_slot = real
+    ok = cb.submit([4, 5, 6], 2)
+    assert len(cb.run()[ok]) == 2

@@ -52,12 +52,37 @@ def test_single_rank_resume_is_exact(tmp_path):
 def test_corrupt_shard_is_refused(tmp_path):
     d = str(tmp_path / "ck")
     _single(2, ckpt_at=2, path=d)
-    f = os.path.join(d, "shard_00000.safetensors")
+    f = os.path.join(d, "shard_00000.step000000002.safetensors")
     raw = bytearray(open(f, "rb").read())
     raw[-5] ^= 0x40
     open(f, "wb").write(bytes(raw))
     with pytest.raises(IoError):
         _single(3, resume=d)
+
+
+def test_crash_during_a_save_keeps_the_previous_checkpoint(tmp_path, monkeypatch):
+    """A fault between the shard write and the manifest (the host-side injector raising where the
+    manifest would be written) must leave the previous complete checkpoint loadable; the next
+    complete save then removes the left-overs."""
+    from coeus_b200.checkpoint import sharded as S
+    from coeus_b200.parallel.health import FaultInjector, InjectedFault
+    d = str(tmp_path / "ck")
+    want, _ = _single(2)
+    _single(2, ckpt_at=2, path=d)                 # complete checkpoint of step 2
+    monkeypatch.setattr(S, "fault_injector", FaultInjector("checkpoint.before_manifest:1"))
+    with pytest.raises(InjectedFault):
+        _single(4, ckpt_at=4, path=d, resume=d)   # the save of step 4 dies before its manifest
+    monkeypatch.setattr(S, "fault_injector", None)
+    names = sorted(os.listdir(d))
+    assert "shard_00000.step000000002.safetensors" in names       # old files untouched
+    assert "shard_00000.step000000004.safetensors" in names       # new shard was written
+    assert S.read_manifest(d)["step"] == 2
+    got, tr = _single(2, resume=d)                # resume finds the checkpoint of step 2
+    assert torch.equal(want, got) and tr.step_index == 2
+    _single(3, ckpt_at=3, path=d, resume=d)       # a complete save cleans up
+    names = sorted(n for n in os.listdir(d) if n.startswith("shard_"))
+    assert names == ["shard_00000.step000000003.safetensors",
+                     "shard_00000.step000000003.safetensors.json"]
 
 
 def _free_port():

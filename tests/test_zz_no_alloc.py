@@ -67,3 +67,22 @@ def test_noalloc_rejects_oversize_problem():
     assert rc == -100
     assert b"maximum" in lib.cb_noalloc_strerror(rc)
     torch.cuda.synchronize()
+
+
+def test_noalloc_rejects_unsupported_head_dim_before_touching_anything():
+    """dh = 32 passes the size check but no kernel covers it: the call must return a negative
+    code with nothing enqueued (output untouched, status word clear)."""
+    lib = _lib.lib()
+    lib.cb_noalloc_strerror.restype = ctypes.c_char_p
+    dev = torch.device("cuda", 0)
+    B, S, nh, dh = 1, 128, 2, 32
+    H = nh * dh
+    t = torch.zeros(B * S, H, dtype=torch.bfloat16, device=dev)
+    lse = torch.zeros(B * nh * S, dtype=torch.float32, device=dev)
+    out = torch.full((B * S, 3 * H), 7.0, dtype=torch.bfloat16, device=dev)
+    rc = _call_noalloc(t, t, t, t, t, lse, out, B, S, nh, dh, True)
+    assert rc == -1
+    assert b"head dimension" in lib.cb_noalloc_strerror(rc)
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())
+    assert _lib.status_buffer(dev).tolist()[0] == 0
