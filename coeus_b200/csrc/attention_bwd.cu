@@ -231,35 +231,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the control flow (addresses and descriptors stay warp-uniform, which
+    // keeps the issue of one MMA near 35 clocks instead of ~100 from a divergent single lane);
+    // one elected lane issues.  Descriptors are built once; a product only adds constants to
+    // their address field.
+    {
       constexpr uint32_t idesc_st = umma_idesc_bf16(BKV, BQ, 0, 0);   // S^T, dP^T
       constexpr uint32_t idesc_dv = umma_idesc_bf16(BKV, DH, 0, 1);   // dV, dK
       constexpr uint32_t idesc_dq =
           (DH == 64) ? umma_idesc_bf16(BQ, DH, 1, 1) : umma_idesc_bf16(DH, BQ, 1, 1);
-      bool ok = mbar_wait(bar(0), 0, abort_flag);
-      if (!ok) record_status(p.status, ST_WAIT_TIMEOUT, 1020);
-      long long* trace = blockIdx.x == 0 ? g_attn_bwd_trace : nullptr;
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      // K-major forms (rows of 64 contraction elements) and MN-major forms (one row per
+      // contraction index, 64-element column groups lbo bytes apart)
+      const uint64_t dK_k = umma_desc_sw128(sK, 16, 1024), dV_k = umma_desc_sw128(sV, 16, 1024);
+      const uint64_t dK_mn = umma_desc_sw128(sK, BKV * 128, 1024);
+      const uint64_t dQ_k0 = umma_desc_sw128(sQ(0), 16, 1024), dDO_k0 = umma_desc_sw128(sDO(0), 16, 1024);
+      const uint64_t dQ_mn0 = umma_desc_sw128(sQ(0), BQ * 128, 1024);
+      const uint64_t dDO_mn0 = umma_desc_sw128(sDO(0), BQ * 128, 1024);
+      const uint64_t dPT_k0 = umma_desc_sw128(sPTb(0), 16, 1024);
+      const uint64_t dDST_k0 = umma_desc_sw128(sDSTb(0), 16, 1024);
+      const uint64_t dDST_mn0 = umma_desc_sw128(sDSTb(0), BKV * 128, 1024);
+      constexpr uint64_t ST_STEP = (2 * Cfg::Q_BYTES) >> 4;     // Q/dO stage pitch
+      constexpr uint64_t BUF_STEP = Cfg::PT_BYTES >> 4;         // P^T / dS^T buffer pitch
+      auto wait_all = [&](int b_idx, uint32_t parity, int where) {
+        const bool got = mbar_wait(bar(b_idx), parity, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
+          return false;
+        }
+        return true;
+      };
+      bool ok = wait_all(0, 0, 1020);
+      long long* trace = (blockIdx.x == 0 && lane == 0) ? g_attn_bwd_trace : nullptr;
       // S^T and dP^T of query tile `it` (needs its Q/dO stage and the S^T/dP^T columns free)
       auto issue_scores = [&](int it) {
         const int st = it & 1;
-        if (!mbar_wait(bar(1 + st), (it >> 1) & 1u, abort_flag)) {
-          record_status(p.status, ST_WAIT_TIMEOUT, 1021);
-          return false;
-        }
+        if (!wait_all(1 + st, (it >> 1) & 1u, 1021)) return false;
         tc_fence_after();
         if (trace && it < 32) trace[it * 8 + 4] = clock64();
-        // the two products are independent: alternating them keeps two accumulation chains in
-        // flight instead of paying the dependent-MMA latency on each step
+        const uint64_t bq = dQ_k0 + st * ST_STEP, bdo = dDO_k0 + st * ST_STEP;
+        if (elect_one()) {
+          // the two products are independent: alternating them keeps two accumulation chains
+          // in flight
 #pragma unroll
-        for (int kk = 0; kk < DH / 16; ++kk) {
-          const uint64_t ad = umma_desc_sw128(sK + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sQ(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
-          umma_bf16_ss(tmem_base + Cfg::ST_COL, ad, bd, idesc_st, kk > 0 ? 1u : 0u);
-          const uint64_t ad2 = umma_desc_sw128(sV + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd2 = umma_desc_sw128(sDO(st) + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16, 1024);
-          umma_bf16_ss(tmem_base + Cfg::DPT_COL, ad2, bd2, idesc_st, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < DH / 16; ++kk) {
+            constexpr int dummy = 0;
+            (void)dummy;
+            const uint64_t ko = static_cast<uint64_t>(((kk / 4) * (BKV * 128) + (kk % 4) * 32) >> 4);
+            const uint64_t qo = static_cast<uint64_t>(((kk / 4) * (BQ * 128) + (kk % 4) * 32) >> 4);
+            umma_bf16_ss(tmem_u + Cfg::ST_COL, dK_k + ko, bq + qo, idesc_st, kk > 0 ? 1u : 0u);
+            umma_bf16_ss(tmem_u + Cfg::DPT_COL, dV_k + ko, bdo + qo, idesc_st, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(bar(5));
         }
-        umma_commit(bar(5));
+        __syncwarp();
         if (trace && it < 32) trace[it * 8 + 5] = clock64();
         return true;
       };
@@ -267,64 +292,53 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1, buf = it & 1;
         // P^T / dS^T of this tile are in shared memory and its S^T / dP^T columns have been read
-        if (!mbar_wait(bar(6), it & 1u, abort_flag)) {
-          record_status(p.status, ST_WAIT_TIMEOUT, 1022);
-          ok = false;
-          break;
-        }
+        if (!wait_all(6, it & 1u, 1022)) { ok = false; break; }
         tc_fence_after();
         if (trace && it < 32) trace[it * 8 + 6] = clock64();
         // The next tile's scores go first: its softmax then runs while the three products below
         // execute (they read the other P^T / dS^T buffer).
-        if (it + 1 < n_it && !issue_scores(it + 1)) {
-          ok = false;
-          break;
-        }
-        const uint32_t sPT = sPTb(buf), sDST = sDSTb(buf);
+        if (it + 1 < n_it && !issue_scores(it + 1)) { ok = false; break; }
         if (it > 0) {     // the previous tile's dQ must have left tensor memory
-          if (!mbar_wait(bar(9), (it - 1) & 1u, abort_flag)) {
-            record_status(p.status, ST_WAIT_TIMEOUT, 1023);
-            ok = false;
-            break;
-          }
+          if (!wait_all(9, (it - 1) & 1u, 1023)) { ok = false; break; }
           tc_fence_after();
         }
         // dV += P^T . dO_i, dK += dS^T . Q_i (contraction over the BQ query rows) and
         // dQ_i = dS . K_j (contraction over the 128 K/V rows): three independent accumulation
         // chains, issued round-robin
-        constexpr int NK = (BQ > BKV ? BQ : BKV) / 16;
+        const uint64_t aPT = dPT_k0 + buf * BUF_STEP, aDST = dDST_k0 + buf * BUF_STEP;
+        const uint64_t mDST = dDST_mn0 + buf * BUF_STEP;
+        const uint64_t bDO = dDO_mn0 + st * ST_STEP, bQ = dQ_mn0 + st * ST_STEP;
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
+        if (elect_one()) {
+          constexpr int NK = (BQ > BKV ? BQ : BKV) / 16;
 #pragma unroll
-        for (int kk = 0; kk < NK; ++kk) {
-          if (kk < BQ / 16) {
-            const uint64_t ad = umma_desc_sw128(sPT + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-            const uint64_t bd = umma_desc_sw128(sDO(st) + kk * 2048, BQ * 128, 1024);
-            umma_bf16_ss(tmem_base + Cfg::DV_COL, ad, bd, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
-            const uint64_t ad2 = umma_desc_sw128(sDST + (kk / 4) * (BKV * 128) + (kk % 4) * 32, 16, 1024);
-            const uint64_t bd2 = umma_desc_sw128(sQ(st) + kk * 2048, BQ * 128, 1024);
-            umma_bf16_ss(tmem_base + Cfg::DK_COL, ad2, bd2, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
-          }
-          if (kk < BKV / 16) {
-            if constexpr (DH == 64) {
-              // dQ_i[q, d] = sum_kv dS^T[kv, q] K_j[kv, d]
-              const uint64_t ad = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
-              const uint64_t bd = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
-              umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
-            } else {
-              // dQ_i^T[d, q] = sum_kv K_j[kv, d] dS^T[kv, q]
-              const uint64_t ad = umma_desc_sw128(sK + kk * 2048, BKV * 128, 1024);
-              const uint64_t bd = umma_desc_sw128(sDST + kk * 2048, BKV * 128, 1024);
-              umma_bf16_ss(tmem_base + Cfg::DQ_COL, ad, bd, idesc_dq, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < NK; ++kk) {
+            const uint64_t ko = static_cast<uint64_t>(((kk / 4) * (BKV * 128) + (kk % 4) * 32) >> 4);
+            const uint64_t mo = static_cast<uint64_t>((kk * 2048) >> 4);
+            if (kk < BQ / 16) {
+              umma_bf16_ss(tmem_u + Cfg::DV_COL, aPT + ko, bDO + mo, idesc_dv, kk > 0 ? 1u : acc0);
+              umma_bf16_ss(tmem_u + Cfg::DK_COL, aDST + ko, bQ + mo, idesc_dv, kk > 0 ? 1u : acc0);
+            }
+            if (kk < BKV / 16) {
+              if constexpr (DH == 64) {
+                // dQ_i[q, d] = sum_kv dS^T[kv, q] K_j[kv, d]
+                umma_bf16_ss(tmem_u + Cfg::DQ_COL, mDST + mo, dK_mn + mo, idesc_dq, kk > 0 ? 1u : 0u);
+              } else {
+                // dQ_i^T[d, q] = sum_kv K_j[kv, d] dS^T[kv, q]
+                umma_bf16_ss(tmem_u + Cfg::DQ_COL, dK_mn + mo, mDST + mo, idesc_dq, kk > 0 ? 1u : 0u);
+              }
             }
           }
+          umma_commit(bar(8));                 // dQ ready to drain
+          umma_commit(bar(3 + st));            // Q_i / dO_i stage free
+          umma_commit(bar(buf ? 12 : 7));      // this P^T / dS^T buffer free
         }
+        __syncwarp();
         if (trace && it < 32) trace[it * 8 + 7] = clock64();
-        umma_commit(bar(8));                 // dQ ready to drain
-        umma_commit(bar(3 + st));            // Q_i / dO_i stage free
-        umma_commit(bar(buf ? 12 : 7));      // this P^T / dS^T buffer free
       }
-      if (ok) umma_commit(bar(10));
+      if (ok && elect_one()) umma_commit(bar(10));
+      __syncwarp();
     }
-    __syncwarp();
   } else if (warp < 10) {
     // ---------------------------------------------------------------- softmax / dS
     const int quarter = warp & 3;

@@ -376,50 +376,66 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && cta_rank == 0u) {
+    // The whole warp runs the control flow (addresses and descriptors stay warp-uniform, which
+    // makes the issue of an MMA markedly cheaper than from a divergent single lane); one elected
+    // lane issues.  The descriptors of stage 0 are built once; a k-step adds constants to them.
+    if (cta_rank == 0u) {
       constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint64_t dA0 = A_MN ? umma_desc_sw128(smem_base, 8192, 1024)
+                                : umma_desc_sw128(smem_base, 16, 1024);
+      const uint64_t dB0 = B_MN ? umma_desc_sw128(smem_base + Cfg::A_BYTES, 8192, 1024)
+                                : umma_desc_sw128(smem_base + Cfg::A_BYTES, 16, 1024);
+      constexpr uint64_t STAGE_STEP = Cfg::STAGE_BYTES >> 4;
+      constexpr uint64_t A_K_STEP = (A_MN ? 2048 : 32) >> 4, B_K_STEP = (B_MN ? 2048 : 32) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      auto wait_all = [&](uint32_t b_addr, uint32_t parity, int where) {
+        const bool got = mbar_wait(b_addr, parity, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
+          ok = false;
+        }
+        return ok;
+      };
       for (int w = first_tile; w < total && ok; w += tile_step, ++it) {
         const int split = w % p.ksplit;
         const int kb0 = split * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          record_status(p.status, ST_WAIT_TIMEOUT, 200);
-          ok = false;
-          break;
-        }
+        if (!wait_all(tempty_bar(acc), acc_phase ^ 1u, 200)) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_u + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            record_status(p.status, ST_WAIT_TIMEOUT, 201);
-            ok = false;
-            break;
-          }
+          if (!wait_all(full_bar(stage), phase, 201)) break;
           tc_fence_after();
-          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
-          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint64_t ad0 = dA0 + stage * STAGE_STEP, bd0 = dB0 + stage * STAGE_STEP;
+          const uint32_t acc_first = kb > kb0 ? 1u : 0u;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < GEMM_BK / 16; ++k) {
-            const uint64_t ad = A_MN ? umma_desc_sw128(sA + k * 2048, 8192, 1024)
-                                     : umma_desc_sw128(sA + k * 32, 16, 1024);
-            const uint64_t bd = B_MN ? umma_desc_sw128(sB + k * 2048, 8192, 1024)
-                                     : umma_desc_sw128(sB + k * 32, 16, 1024);
-            if constexpr (CTA2) umma_bf16_ss_cg2(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            else umma_bf16_ss(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < GEMM_BK / 16; ++k) {
+              if constexpr (CTA2)
+                umma_bf16_ss_cg2(tmem_d, ad0 + k * A_K_STEP, bd0 + k * B_K_STEP, idesc,
+                                 k > 0 ? 1u : acc_first);
+              else
+                umma_bf16_ss(tmem_d, ad0 + k * A_K_STEP, bd0 + k * B_K_STEP, idesc,
+                             k > 0 ? 1u : acc_first);
+            }
+            if constexpr (CTA2) umma_commit_cg2(empty_bar(stage), 3);   // frees the stage in both CTAs
+            else umma_commit(empty_bar(stage));
           }
-          if constexpr (CTA2) umma_commit_cg2(empty_bar(stage), 3);   // frees the stage in both CTAs
-          else umma_commit(empty_bar(stage));
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) {
-          if constexpr (CTA2) umma_commit_cg2(tfull_bar(acc), 3);     // both epilogues may drain
-          else umma_commit(tfull_bar(acc));
+          if (elect_one()) {
+            if constexpr (CTA2) umma_commit_cg2(tfull_bar(acc), 3);     // both epilogues may drain
+            else umma_commit(tfull_bar(acc));
+          }
+          __syncwarp();
         }
       }
     }

@@ -68,10 +68,24 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// Non-blocking test of the phase with the given parity (no suspension machinery: a plain
+// shared-memory read, noticeably cheaper than try_wait when the phase has already completed).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Wait for the phase with the given parity.  Returns false when the time limit passed or
 // when another thread of the CTA already raised *abort_flag (a shared-memory word).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t n = 0;

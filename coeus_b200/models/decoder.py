@@ -400,8 +400,9 @@ class DecoderLM:
 
     def _expand_kv(self, t: torch.Tensor) -> torch.Tensor:
         """``[T, kv_heads * dh] -> [T, heads * dh]``: every K/V head repeated for the query heads
-        of its group (query head ``h`` reads K/V head ``h // group``).  The attention kernels are
-        multi-head, so grouped-query attention runs on the expanded copies."""
+        of its group (query head ``h`` reads K/V head ``h // group``).  The forward kernel reads
+        the narrow K/V directly; the backward kernel is multi-head and runs on the expanded
+        copies, after which the gradients of a group are summed."""
         cfg = self.cfg
         T, g = t.shape[0], cfg.num_heads // cfg.kv_heads
         return t.reshape(T, cfg.kv_heads, 1, cfg.head_dim).expand(
@@ -427,8 +428,7 @@ class DecoderLM:
         else:
             Hkv = cfg.kv_dim
             q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
-            if self.gqa:
-                k, v = self._expand_kv(k), self._expand_kv(v)
+            # grouped-query attention: the forward kernel indexes K/V by head // group itself
             attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
         x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
                              max_ctas=mc)

@@ -1,4 +1,5 @@
-"""Flash-style attention on tcgen05 (``csrc/attention_fwd.cu``, ``csrc/attention_bwd.cu``).
+"""Flash-style attention on tcgen05 (``csrc/attention_fwd.cu``: two query tiles per CTA with the
+probabilities kept in tensor memory; ``csrc/attention_bwd.cu``).
 
 Tensors are token-major: ``q``, ``k``, ``v`` are ``[B*S, nh*dh]`` views (they may be column
 slices of one fused ``[B*S, 3*nh*dh]`` projection output), ``o`` is ``[B*S, nh*dh]``.  The
@@ -9,17 +10,27 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
 
 from . import _lib
 
+# ``COEUS_ATTN_POLY=1`` makes the forward kernel evaluate a quarter of its exponentials as a
+# polynomial on the FMA pipe instead of the special-function unit (measured slower on B200 at
+# dh 64 and 128 with the present instruction mix, hence off by default).
+FWD_POLY = int(os.environ.get("COEUS_ATTN_POLY", "0"))
+
 
 def _ref_fwd(q, k, v, B, S, nh, dh, scale, causal):
     qf = q.float().reshape(B, S, nh, dh).transpose(1, 2)
-    kf = k.float().reshape(B, S, nh, dh).transpose(1, 2)
-    vf = v.float().reshape(B, S, nh, dh).transpose(1, 2)
+    nkv = k.shape[1] // dh
+    kf = k.float().reshape(B, S, nkv, dh).transpose(1, 2)
+    vf = v.float().reshape(B, S, nkv, dh).transpose(1, 2)
+    if nkv != nh:          # grouped-query attention: query head h reads K/V head h // group
+        kf = kf.repeat_interleave(nh // nkv, 1)
+        vf = vf.repeat_interleave(nh // nkv, 1)
     s = (qf @ kf.transpose(-1, -2)) * scale
     if causal:
         mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
@@ -33,8 +44,11 @@ def _ref_fwd(q, k, v, B, S, nh, dh, scale, causal):
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: int, nh: int,
                   dh: int, *, causal: bool = True, scale: Optional[float] = None
                   ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns ``(o [B*S, nh*dh], lse [B, nh, S] fp32)``."""
+    """Returns ``(o [B*S, nh*dh], lse [B, nh, S] fp32)``.  ``k`` and ``v`` may hold fewer heads
+    than ``q`` (``[B*S, nkv*dh]``, ``nkv`` dividing ``nh``): grouped-query attention, query head
+    ``h`` reading K/V head ``h // (nh // nkv)`` inside the kernel."""
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    nkv = k.shape[1] // dh
     if not q.is_cuda:
         o, lse, _, _ = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
         return o.to(q.dtype), lse
@@ -43,10 +57,10 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: 
     o = torch.empty((B * S, nh * dh), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
     st = _lib.status_buffer(q.device)
-    rc = _lib.lib().cb_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse),
-                                B, S, nh, dh, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
-                                ctypes.c_float(scale), int(causal), _lib.ptr(st),
-                                _lib.stream_ptr())
+    rc = _lib.lib().cb_attn_fwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), B, S, nh, nkv, dh,
+        q.stride(0), k.stride(0), v.stride(0), o.stride(0), ctypes.c_float(scale),
+        int(causal), FWD_POLY, _lib.ptr(st), 0, _lib.stream_ptr())
     _lib.check_rc(rc, "cb_attn_fwd")
     return o, lse
 

@@ -67,6 +67,8 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--dh", type=int, default=64)
+    ap.add_argument("--attn-poly", type=int, default=None,
+                    help="0: every exponential on the special-function unit; 1: a share as polynomial")
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--vocab", type=int, default=32000)
@@ -143,6 +145,8 @@ def main(argv=None) -> int:
         H = nh * dh
         qkv = torch.randn(B * S, 3 * H, device=dev).to(bf)
         q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+        if a.attn_poly is not None:
+            A.FWD_POLY = a.attn_poly
         o, lse = A.attention_fwd(q, k, v, B, S, nh, dh)
         fwd_flops = 4.0 * B * nh * S * S * dh / 2
         if a.kernel == "attn_fwd":

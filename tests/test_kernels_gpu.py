@@ -226,6 +226,30 @@ def test_attention_fwd_bwd(dh, causal, S):
         assert err < 0.02 * ref.float().abs().max().item() + 0.03, (name, err)
 
 
+@pytest.mark.parametrize("dh,nh,nkv,B,S,causal", [
+    (64, 4, 4, 1, 384, True),       # three query tiles: the last pair has one tile only
+    (64, 16, 16, 4, 1024, True),    # 256 work items: persistent CTAs take several each
+    (64, 8, 2, 2, 1000, True),      # grouped-query attention, ragged last tile
+    (128, 4, 1, 2, 640, True),      # multi-query, dh 128, five query tiles
+    (128, 2, 2, 3, 512, False),
+    (64, 3, 3, 2, 77, False),
+])
+def test_attention_fwd_shapes_and_grouped_query(dh, nh, nkv, B, S, causal):
+    torch.manual_seed(9)
+    H, Hkv = nh * dh, nkv * dh
+    qkv = _bf(torch.randn(B * S, H + 2 * Hkv, device=DEV))
+    q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+    orf, lser = A.attention_fwd(q.cpu(), k.cpu(), v.cpu(), B, S, nh, dh, causal=causal)
+    for poly in (0, 1):
+        A.FWD_POLY = poly
+        o, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal)
+        torch.cuda.synchronize()
+        _status_clean()
+        assert (o.float().cpu() - orf.float()).abs().max() < 0.03, poly
+        assert (lse.cpu() - lser).abs().max() < 0.02, poly
+    A.FWD_POLY = 1
+
+
 def test_normal_init_matches_cpu_generator():
     from coeus_b200.ops import elementwise as E
     n = 1_000_003
