@@ -183,6 +183,215 @@ extern "C" int cb_ar_resid_norm(void* const* parts, void* const* peer_flags, con
 }
 
 // ------------------------------------------------------------------------------------------
+// The same collective through NVLink multicast (NVLS): every buffer below is symmetric memory
+// bound to one multicast object, so `mc + offset` names that offset on ALL ranks at once.
+//   1. arrive: one multimem.red adds 1 to the arrival counter on every rank; wait (bounded) until
+//      the local counter shows all ranks of this call,
+//   2. each rank takes the rows r with r % tp == rank: multimem.ld_reduce returns the sum of the
+//      row over all ranks' partial buffers (reduced in the switch, fp32 accumulation), the
+//      residual is added, the row is normalised, and x / n are written to EVERY rank's output
+//      buffers with multimem.st -- so all ranks hold bit-identical results,
+//   3. leave: a second counter (multimem.red by the last block of every rank) tells each rank
+//      that all rows have arrived before its kernel completes.
+// A rank moves 1/tp of the rows in and out instead of reading every rank's copy of all of them.
+// Outputs and partials alternate between two buffers (a rank can be at most one call ahead of a
+// peer), the call counter lives on the device, launch parameters never change (graph replay).
+namespace cb {
+
+struct ArMmArgs {
+  const __nv_bfloat16* part_mc;     // multicast address of the partial buffer of this call
+  __nv_bfloat16* x_mc;              // multicast addresses of the outputs of this call
+  __nv_bfloat16* n_mc;
+  const __nv_bfloat16* resid;       // local [rows, H] or null
+  unsigned int* flags_mc;           // multicast address of {arrive, leave} counters
+  const unsigned int* flags_local;  // the same counters through this rank's own mapping
+  unsigned long long* epoch;
+  unsigned int* done;
+  const __nv_bfloat16* scale;
+  const __nv_bfloat16* bias;
+  int tp, rank, rows, H, rms;
+  int one_shot;                     // 1: every rank reduces all rows for itself (x / n are local
+                                    // addresses, plain stores, no second counter)
+  float eps;
+  unsigned long long limit_ns;
+  int* status;
+};
+
+__device__ __forceinline__ void st_out(__nv_bfloat16* dst, const uint4& v, bool multicast) {
+  if (multicast) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(dst), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+                    "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+  } else {
+    *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+__device__ __forceinline__ bool wait_counter(const unsigned int* p, unsigned int target,
+                                             unsigned long long limit_ns, int* status, int where) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    // counters only grow; the comparison survives wrap-around of the 32-bit value
+    if (static_cast<int>(v - target) >= 0) return true;
+    if ((++it & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) {
+      record_status(status, ST_COMM_TIMEOUT, where);
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(AR_THREADS) ar_multimem_kernel(ArMmArgs a) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(a.epoch) + 1ull;
+  const unsigned int target = static_cast<unsigned int>(e) * static_cast<unsigned int>(a.tp);
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    if (blockIdx.x == 0) {
+      __threadfence_system();      // this rank's partial (written by the kernel before) is visible
+      asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;"
+                   :: "l"(a.flags_mc), "r"(1u) : "memory");
+    }
+    if (!wait_counter(a.flags_local, target, a.limit_ns, a.status, 0)) s_ok = 0;
+  }
+  __syncthreads();
+  const int row = a.one_shot ? static_cast<int>(blockIdx.x)
+                             : a.rank + static_cast<int>(blockIdx.x) * a.tp;
+  const bool mcast = a.one_shot == 0;
+  if (s_ok != 0 && row < a.rows) {
+    const int nv = a.H >> 3;
+    float x[AR_MAX_VEC][8];
+    float sum = 0.f, sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < AR_MAX_VEC; ++j) {
+      const int v = threadIdx.x + j * AR_THREADS;
+      if (v < nv) {
+        const size_t off = static_cast<size_t>(row) * a.H + v * 8;
+        uint4 raw;
+        asm volatile(
+            "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+            : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+            : "l"(a.part_mc + off) : "memory");
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float acc[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __bfloat1622float2(h[q]);
+          acc[2 * q] = f.x;
+          acc[2 * q + 1] = f.y;
+        }
+        if (a.resid != nullptr) {
+          float r[8];
+          load8(a.resid + off, r);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] += r[q];
+        }
+        uint4 out;
+        out.x = pack_bf16x2(acc[0], acc[1]);
+        out.y = pack_bf16x2(acc[2], acc[3]);
+        out.z = pack_bf16x2(acc[4], acc[5]);
+        out.w = pack_bf16x2(acc[6], acc[7]);
+        st_out(a.x_mc + off, out, mcast);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {   // normalise what was stored (bf16-rounded values)
+          x[j][q] = __bfloat162float(__float2bfloat16(acc[q]));
+          sum += x[j][q];
+          sq += x[j][q] * x[j][q];
+        }
+      }
+    }
+    if (a.n_mc != nullptr) {
+      float mean = 0.f, rstd;
+      if (a.rms) {
+        sq = block_sum(sq, red);
+        rstd = rsqrtf(sq / a.H + a.eps);
+      } else {
+        sum = block_sum(sum, red);
+        mean = sum / a.H;
+        float var = 0.f;
+#pragma unroll
+        for (int j = 0; j < AR_MAX_VEC; ++j)
+          if (threadIdx.x + j * AR_THREADS < nv)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) var += (x[j][q] - mean) * (x[j][q] - mean);
+        var = block_sum(var, red);
+        rstd = rsqrtf(var / a.H + a.eps);
+      }
+#pragma unroll
+      for (int j = 0; j < AR_MAX_VEC; ++j) {
+        const int v = threadIdx.x + j * AR_THREADS;
+        if (v < nv) {
+          float g[8], b[8], y[8];
+          load8(a.scale + v * 8, g);
+          if (a.bias != nullptr) load8(a.bias + v * 8, b);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            y[q] = (x[j][q] - mean) * rstd * g[q] + (a.bias != nullptr ? b[q] : 0.f);
+          uint4 yo;
+          yo.x = pack_bf16x2(y[0], y[1]);
+          yo.y = pack_bf16x2(y[2], y[3]);
+          yo.z = pack_bf16x2(y[4], y[5]);
+          yo.w = pack_bf16x2(y[6], y[7]);
+          st_out(a.n_mc + static_cast<size_t>(row) * a.H + v * 8, yo, mcast);
+        }
+      }
+    }
+  }
+  // the last block of this rank announces its rows everywhere and waits for everybody's
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(a.done, 1u);
+    if (prev == gridDim.x - 1) {
+      if (mcast) {
+        asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;"
+                     :: "l"(a.flags_mc + 1), "r"(1u) : "memory");
+        if (s_ok != 0) wait_counter(a.flags_local + 1, target, a.limit_ns, a.status, 1);
+      }
+      *a.done = 0u;
+      *reinterpret_cast<volatile unsigned long long*>(a.epoch) = e;
+      __threadfence();
+    }
+  }
+}
+}  // namespace cb
+
+// part_mc: multicast address of the [rows, H] bf16 partial buffer; x_mc / n_mc: multicast
+// addresses of the outputs (n_mc may be null) -- or, with one_shot != 0, local addresses: every
+// rank then reduces all rows for itself and nothing is broadcast;
+// flags_mc / flags_local: two 32-bit counters (arrive, leave), zero before the first call;
+// state as in cb_ar_resid_norm.
+extern "C" int cb_ar_multimem(const void* part_mc, void* x_mc, void* n_mc, const void* resid,
+                              void* flags_mc, const void* flags_local, void* state,
+                              const void* scale, const void* bias, int tp, int rank, int rows,
+                              int H, int rms, float eps, unsigned long long limit_ns, int* status,
+                              int one_shot, void* stream) {
+  using namespace cb;
+  if (tp < 1 || tp > AR_MAX_RANKS || H % 8 != 0 || H > AR_THREADS * AR_MAX_VEC * 8) return -1;
+  if (rows <= 0) return 0;
+  ArMmArgs a;
+  a.part_mc = static_cast<const __nv_bfloat16*>(part_mc);
+  a.x_mc = static_cast<__nv_bfloat16*>(x_mc);
+  a.n_mc = static_cast<__nv_bfloat16*>(n_mc);
+  a.resid = static_cast<const __nv_bfloat16*>(resid);
+  a.flags_mc = static_cast<unsigned int*>(flags_mc);
+  a.flags_local = static_cast<const unsigned int*>(flags_local);
+  a.epoch = static_cast<unsigned long long*>(state);
+  a.done = reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(state) + 1);
+  a.scale = static_cast<const __nv_bfloat16*>(scale);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.tp = tp; a.rank = rank; a.rows = rows; a.H = H; a.rms = rms; a.eps = eps;
+  a.one_shot = one_shot;
+  a.limit_ns = limit_ns; a.status = status;
+  const int grid = one_shot ? rows : (rows + tp - 1) / tp;   // the same on every rank
+  ar_multimem_kernel<<<grid, AR_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// ------------------------------------------------------------------------------------------
 // Greedy token selection over a vocabulary that is split across ranks, without a library
 // collective: block b finds the arg-max of row b of this rank's logits slice, stores the pair
 // (value, global index) into slot [rank][b] of EVERY rank's pair table, raises the slot's flag,

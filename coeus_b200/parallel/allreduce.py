@@ -1,12 +1,17 @@
 """One-shot all-reduce fused with the residual add and the next normalisation
-(``csrc/allreduce.cu``): the collective of tensor-parallel decoding.  ``backend="fused"`` reads
-every rank's partial result through NVLink peer mappings inside one kernel whose parameters never
-change between calls (so it can be replayed from a CUDA graph); ``backend="nccl"`` composes
+(``csrc/allreduce.cu``): the collective of tensor-parallel decoding.  ``backend="nvls"`` reduces
+in the NVLink switch: each rank pulls its share of the rows with ``multimem.ld_reduce`` from a
+multicast mapping of all ranks' partial buffers and writes the finished rows to every rank with
+``multimem.st``; ``backend="fused"`` reads every rank's partial result through plain NVLink peer
+mappings.  Both are one kernel whose parameters never change between calls (so it can be replayed
+from a CUDA graph).  ``backend=None`` picks ``nvls`` where the devices support multicast objects
+(``COEUS_NVLS=0`` switches that off), else ``fused``.  ``backend="nccl"`` composes
 ``all_reduce`` with the stand-alone kernels and is the baseline and the path of CPU ranks.  The
 reference has no collective of any kind."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -18,18 +23,45 @@ from ..ops import norm as N
 
 class FusedAllReduce:
     def __init__(self, group, device, max_rows: int, hidden: int, backend: Optional[str] = None,
-                 wait_limit_ms: float = 5000.0, dtype=torch.bfloat16) -> None:
+                 wait_limit_ms: float = 5000.0, dtype=torch.bfloat16,
+                 one_shot: Optional[bool] = None) -> None:
+        """``one_shot`` (``nvls`` only): every rank reduces all rows for itself with
+        ``multimem.ld_reduce`` and stores locally -- one counter round trip instead of two, at
+        ``tp`` times the switch traffic; the default (``COEUS_NVLS_ONESHOT``, else off) is the
+        two-phase form in which a rank handles ``1/tp`` of the rows and broadcasts them."""
         self.group = group
         self.device = torch.device(device)
         self.rank = dist.get_rank(group) if group is not None else 0
         self.tp = dist.get_world_size(group) if group is not None else 1
         if backend is None:
             backend = "fused" if self.device.type == "cuda" and self.tp > 1 else "nccl"
+            if backend == "fused" and os.environ.get("COEUS_NVLS", "1") != "0":
+                from .symm import multicast_supported
+                if multicast_supported(self.device):
+                    backend = "nvls"
         self.backend = backend
         self.max_rows, self.H = max_rows, hidden
         self.limit_ns = int(wait_limit_ms * 1e6)
         self._turn = 0
-        if backend == "fused":
+        if one_shot is None:
+            one_shot = os.environ.get("COEUS_NVLS_ONESHOT", "0") == "1"
+        self.one_shot = bool(one_shot)
+        if backend == "nvls":
+            from .symm import MulticastBuffer
+            n = max_rows * hidden * 2                 # bytes of one [max_rows, H] bf16 buffer
+            self._stride = (n + 255) // 256 * 256
+            # one allocation: 2 partial buffers, 2 x outputs, 2 n outputs, then the counters
+            self._mc = MulticastBuffer(6 * self._stride + 256, group, self.device)
+            self._mc.local.zero_()
+            view = lambda i: self._mc.view(torch.bfloat16, i * self._stride,   # noqa: E731
+                                           max_rows * hidden).view(max_rows, hidden)
+            self.parts = [view(0), view(1)]
+            self._x = [view(2), view(3)]
+            self._n = [view(4), view(5)]
+            self._state = torch.zeros(2, dtype=torch.int64, device=self.device)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=group)
+        elif backend == "fused":
             from .symm import SymmetricBuffer
             n = max_rows * hidden
             self._sym = [SymmetricBuffer(n * 2, group, self.device) for _ in range(2)]
@@ -57,6 +89,25 @@ class FusedAllReduce:
         turn = self._turn
         self._turn ^= 1
         part = self.parts[turn][:rows]
+        if self.backend == "nvls":
+            # results land in this rank's copy of the symmetric output buffers (every rank's
+            # rows are written by their owner through the multicast mapping); the views stay
+            # valid until the call after next
+            mc, sd = self._mc, self._stride
+            x = self._x[turn][:rows]
+            n = self._n[turn][:rows] if scale is not None else None
+            st = _lib.status_buffer(self.device)
+            out_base = mc.local_ptr if self.one_shot else mc.mc_ptr
+            rc = _lib.lib().cb_ar_multimem(
+                ctypes.c_void_p(mc.mc_ptr + turn * sd), ctypes.c_void_p(out_base + (2 + turn) * sd),
+                ctypes.c_void_p(out_base + (4 + turn) * sd) if scale is not None else None,
+                _lib.ptr(resid), ctypes.c_void_p(mc.mc_ptr + 6 * sd),
+                ctypes.c_void_p(mc.local_ptr + 6 * sd), _lib.ptr(self._state), _lib.ptr(scale),
+                _lib.ptr(bias), self.tp, self.rank, rows, self.H, int(rms), ctypes.c_float(eps),
+                ctypes.c_ulonglong(self.limit_ns), _lib.ptr(st), int(self.one_shot),
+                _lib.stream_ptr())
+            _lib.check_rc(rc, "cb_ar_multimem")
+            return x, n
         if self.backend != "fused":
             x = part.clone()
             if self.tp > 1:
@@ -77,6 +128,14 @@ class FusedAllReduce:
             ctypes.c_ulonglong(self.limit_ns), _lib.ptr(st), _lib.stream_ptr())
         _lib.check_rc(rc, "cb_ar_resid_norm")
         return x, n
+
+
+    def close(self) -> None:
+        """Release the symmetric memory (collective: no rank may still be using it)."""
+        if self.backend == "nvls" and getattr(self, "_mc", None) is not None:
+            self.parts, self._x, self._n = [], [], []
+            self._mc.close()
+            self._mc = None
 
 
 class GreedySelect:
