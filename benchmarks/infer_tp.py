@@ -27,7 +27,7 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--layers", type=int, default=24)
-    ap.add_argument("--ar", default=None, choices=["fused", "nccl"])
+    ap.add_argument("--ar", default=None, choices=["nvls", "fused", "nccl"])
     ap.add_argument("--tp-backend", default=None, choices=["fused", "nccl"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--weights", default=None, help="SafeTensors file (written if absent)")

@@ -1,6 +1,8 @@
 // Decode-time attention over a paged KV cache, and the kernel that appends K/V to the pages.
 //
-// Cache layout: k_cache / v_cache are [num_pages, PAGE, nh, dh] bf16 with PAGE = 64 tokens;
+// Cache layout: k_cache / v_cache are [num_pages, PAGE, nkv, dh] bf16 with PAGE = 64 tokens
+// (nkv key/value heads; with grouped-query attention query head h reads head h / (nh / nkv), so
+// the cache and the bytes streamed per step shrink by the group factor);
 // page_table[b, i] is the physical page of logical page i of sequence b.  One query token per
 // sequence attends to ctx_len[b] cached tokens.  The kernel is bandwidth bound (it streams the
 // whole K and V of the sequence once): one CTA per (head, sequence), 16-byte loads, 8 (dh = 64)
@@ -25,10 +27,11 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table,
                    int max_pages, const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out,
                    int ldo, float* __restrict__ part_o, float* __restrict__ part_ml, int nh,
-                   int splits, float scale_log2) {
+                   int nkv, int splits, float scale_log2) {
   constexpr int LPT = DH / 8;                 // lanes per token
   constexpr int GROUPS = DEC_THREADS / LPT;   // token groups per CTA
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int hk = h / (nh / nkv);              // the key/value head this query head reads
   const int g = threadIdx.x / LPT, part = threadIdx.x % LPT;
   const int n_ctx = ctx_len[b];
   const int per = (n_ctx + splits - 1) / splits;
@@ -54,7 +57,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
       if (act[u]) {
         const int page = pt[t / KV_PAGE];
         const size_t off =
-            ((static_cast<size_t>(page) * KV_PAGE + (t % KV_PAGE)) * nh + h) * DH + part * 8;
+            ((static_cast<size_t>(page) * KV_PAGE + (t % KV_PAGE)) * nkv + hk) * DH + part * 8;
         kr[u] = __ldg(reinterpret_cast<const uint4*>(k_cache + off));
         vr[u] = __ldg(reinterpret_cast<const uint4*>(v_cache + off));
       }
@@ -211,12 +214,13 @@ __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, 
 using namespace cb;
 
 // part_o: fp32 [B, nh, splits, dh] and part_ml: fp32 [B, nh, splits, 2] scratch, used when
-// splits > 1.
+// splits > 1.  nh query heads, nkv key/value heads in the cache (nkv divides nh).
 extern "C" int cb_decode_attn(const void* q, int ldq, const void* k_cache, const void* v_cache,
                               const int* page_table, int max_pages, const int* ctx_len, void* out,
-                              int ldo, float* part_o, float* part_ml, int B, int nh, int dh,
-                              int splits, float scale, void* stream) {
+                              int ldo, float* part_o, float* part_ml, int B, int nh, int nkv,
+                              int dh, int splits, float scale, void* stream) {
   if (dh != 64 && dh != 128) return -1;
+  if (nkv < 1 || nh % nkv != 0) return -1;
   if (splits < 1) splits = 1;
   if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return -2;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -227,9 +231,9 @@ extern "C" int cb_decode_attn(const void* q, int ldq, const void* k_cache, const
   auto V = static_cast<const __nv_bfloat16*>(v_cache);
   auto O = static_cast<__nv_bfloat16*>(out);
   if (dh == 64)
-    decode_attn_kernel<64><<<grid, DEC_THREADS, 0, st>>>(Q, ldq, K, V, page_table, max_pages, ctx_len, O, ldo, part_o, part_ml, nh, splits, sl2);
+    decode_attn_kernel<64><<<grid, DEC_THREADS, 0, st>>>(Q, ldq, K, V, page_table, max_pages, ctx_len, O, ldo, part_o, part_ml, nh, nkv, splits, sl2);
   else
-    decode_attn_kernel<128><<<grid, DEC_THREADS, 0, st>>>(Q, ldq, K, V, page_table, max_pages, ctx_len, O, ldo, part_o, part_ml, nh, splits, sl2);
+    decode_attn_kernel<128><<<grid, DEC_THREADS, 0, st>>>(Q, ldq, K, V, page_table, max_pages, ctx_len, O, ldo, part_o, part_ml, nh, nkv, splits, sl2);
   if (splits > 1) {
     dim3 g2(nh, B);
     if (dh == 64) decode_merge_kernel<64><<<g2, 64, 0, st>>>(part_o, part_ml, O, ldo, nh, splits);

@@ -102,11 +102,9 @@ class InferenceEngine:
                         theta=cfg.rope_theta, pos_dev=pos_dev)
             Hkv = cfg.kv_dim
             q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
-            if Hkv != H:
-                # grouped-query attention on multi-head kernels: K and V are expanded per group
-                # here, and the cache keeps the expanded heads
-                k, v = m._expand_kv(k), m._expand_kv(v)
-            D.kv_write(k, v, cache.k[l], cache.v[l], page_table, pos0, S, nh, dh)
+            # grouped-query attention: the cache keeps the key/value heads as they are, the
+            # prefill and decode kernels index them by query head // group
+            D.kv_write(k, v, cache.k[l], cache.v[l], page_table, pos0, S, cfg.kv_heads, dh)
             if prefill:
                 attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
                 if earlier is not None:
@@ -122,7 +120,7 @@ class InferenceEngine:
             else:
                 attn = D.decode_attention(q, cache.k[l], cache.v[l], page_table,
                                           self._ctx if ctx is None else ctx, nh, dh,
-                                          splits=self.decode_splits)
+                                          splits=self.decode_splits, nkv=cfg.kv_heads)
             x_mid = G.linear_fwd(attn, m.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x)
             x = self._mlp(p, self._norm(x_mid, p + n2n), x_mid)
         return x
@@ -226,7 +224,8 @@ class InferenceEngine:
         cache.reserve(slot, max(total_len, padded))
         pe = m._positions(max(padded, total_len))
         table = cache.page_table[slot:slot + 1]
-        earlier = [[(cache.k[l][pg].view(PG, H), cache.v[l][pg].view(PG, H))
+        Hkv = cfg.kv_dim        # the cache holds the key/value heads
+        earlier = [[(cache.k[l][pg].view(PG, Hkv), cache.v[l][pg].view(PG, Hkv))
                     for pg in prefix_pages] for l in range(cfg.num_layers)]
         pad = torch.zeros(padded - S, dtype=ids.dtype, device=ids.device)
         toks = torch.cat([ids, pad])

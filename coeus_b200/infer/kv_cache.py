@@ -33,7 +33,9 @@ class PagedKVCache:
     @classmethod
     def for_model(cls, cfg, batch: int, max_len: int, device, heads: int = None) -> "PagedKVCache":
         pages_per_seq = (max_len + PAGE - 1) // PAGE
-        return cls(cfg.num_layers, heads or cfg.num_heads, cfg.head_dim, batch * pages_per_seq,
+        # the cache holds the key/value heads (fewer than query heads under grouped-query
+        # attention; ``heads`` overrides with a tensor-parallel rank's share)
+        return cls(cfg.num_layers, heads or cfg.kv_heads, cfg.head_dim, batch * pages_per_seq,
                    batch, pages_per_seq, device)
 
     def reserve(self, seq: int, total_len: int) -> None:

@@ -42,7 +42,7 @@ class TPInferenceEngine:
         self.ar = FusedAllReduce(self.tp.group, self.device, max_batch, self.cfg.hidden_dim,
                                  backend=ar_backend, dtype=model.p16.dtype)
         self._select = None
-        if self.ar.backend == "fused":
+        if self.ar.backend in ("fused", "nvls"):
             from ..parallel.allreduce import GreedySelect
             self._select = GreedySelect(self.tp.group, self.device, max_batch)
         self.cache: Optional[PagedKVCache] = None
@@ -59,7 +59,7 @@ class TPInferenceEngine:
         need_pages = (total + D.PAGE - 1) // D.PAGE
         if c is None or c.page_table.shape[0] < B or c.page_table.shape[1] < need_pages:
             c = PagedKVCache.for_model(self.cfg, max(B, 1), max(total, D.PAGE), self.device,
-                                       heads=self.m.nh_l)
+                                       heads=self.m.kvh_l)
             if self.m.p16.dtype != torch.bfloat16:
                 c.k = [t.to(self.m.p16.dtype) for t in c.k]
                 c.v = [t.to(self.m.p16.dtype) for t in c.v]
@@ -106,8 +106,8 @@ class TPInferenceEngine:
             qkv, _ = tp.ag_gemm("ag_attn", m.w[p + "attn.qkv_weights"])
             if cfg.pos == "rope":
                 m._rope(qkv, S)
-            q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
-            D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, nh, dh)
+            q, k, v = m._split_qkv(qkv, expand=False)   # the cache keeps the rank's K/V heads
+            D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, pos0, S, m.kvh_l, dh)
             attn, _ = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
             x_mid = tp.gemm_rs("rs_attn", attn, m.w[p + "attn.o_weights"], resid=x)
             tp.own_rows("ag_mlp", T, H).copy_(self._norm(x_mid, p + "norm2"))
@@ -135,7 +135,7 @@ class TPInferenceEngine:
     def open_slots(self, max_seqs: int, max_len: int) -> PagedKVCache:
         """A cache whose rows are independent request slots (this rank's heads of each)."""
         c = PagedKVCache.for_model(self.cfg, max_seqs, max(max_len, D.PAGE), self.device,
-                                   heads=self.m.nh_l)
+                                   heads=self.m.kvh_l)
         if self.m.p16.dtype != torch.bfloat16:
             c.k = [t.to(self.m.p16.dtype) for t in c.k]
             c.v = [t.to(self.m.p16.dtype) for t in c.v]
@@ -173,13 +173,13 @@ class TPInferenceEngine:
             qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
             if cfg.pos == "rope":
                 m._rope(qkv, S, pos_offset=pos_host, pos_dev=pos_dev)
-            q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
-            D.kv_write(k, v, cache.k[l], cache.v[l], table, pos0, S, nh, dh)
+            q, k, v = m._split_qkv(qkv, expand=False)   # the cache keeps the rank's K/V heads
+            D.kv_write(k, v, cache.k[l], cache.v[l], table, pos0, S, m.kvh_l, dh)
             if ctx is None:
                 attn, _ = A.attention_fwd(q, k, v, n_seq, S, nh, dh, causal=True)
             else:
                 attn = D.decode_attention(q, cache.k[l], cache.v[l], table, ctx, nh, dh,
-                                          splits=self.decode_splits)
+                                          splits=self.decode_splits, nkv=m.kvh_l)
             x, n2 = reduce(lambda out: G.gemm(attn, m.w[p + "attn.o_weights"], b_mn=True, out=out),
                            x, p + "norm2")
             u = G.gemm(n2, m.w[p + "ff.up_weights"], b_mn=True)
@@ -249,10 +249,10 @@ class TPInferenceEngine:
             qkv = G.gemm(n1, m.w[p + "attn.qkv_weights"], b_mn=True)
             if cfg.pos == "rope":
                 m._rope(qkv, 1, pos_dev=self._pos0)
-            q, k, v = m._split_qkv(qkv)   # K/V heads expanded per group; the cache keeps them so
-            D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, self._pos0, 1, nh, dh)
+            q, k, v = m._split_qkv(qkv, expand=False)   # the cache keeps the rank's K/V heads
+            D.kv_write(k, v, cache.k[l], cache.v[l], cache.page_table, self._pos0, 1, m.kvh_l, dh)
             attn = D.decode_attention(q, cache.k[l], cache.v[l], cache.page_table, self._ctx, nh,
-                                      dh, splits=self.decode_splits)
+                                      dh, splits=self.decode_splits, nkv=m.kvh_l)
             G.gemm(attn, m.w[p + "attn.o_weights"], b_mn=True, out=ar.next_part(B))
             x, n2 = ar.reduce(B, x, *self._norm_params(p + "norm2"), m.rms, cfg.norm_eps)
             u = G.gemm(n2, m.w[p + "ff.up_weights"], b_mn=True)

@@ -40,8 +40,10 @@ def kv_write(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: t
 
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      page_table: torch.Tensor, ctx_len: torch.Tensor, nh: int, dh: int,
-                     scale: Optional[float] = None, splits: int = 0) -> torch.Tensor:
-    """``q`` is a ``[B, nh*dh]`` view; returns ``[B, nh*dh]``.  ``splits`` cuts every context
+                     scale: Optional[float] = None, splits: int = 0,
+                     nkv: Optional[int] = None) -> torch.Tensor:
+    """``q`` is a ``[B, nh*dh]`` view; returns ``[B, nh*dh]``.  The cache holds ``nkv`` heads
+    (default ``nh``); with fewer, query head ``h`` reads head ``h // (nh // nkv)``.  ``splits`` cuts every context
     into that many pieces handled by separate CTAs and merged afterwards; ``0`` picks the count
     that gives about four CTAs per SM (bounded so that a piece keeps at least 256 tokens of the
     longest context the page table allows)."""
@@ -51,15 +53,16 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         splits = max(1, min(16, (4 * 148 + ctas - 1) // ctas,
                             (page_table.shape[1] * PAGE) // 256 or 1))
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    nkv = nkv or nh
     if not q.is_cuda:
         out = torch.zeros((B, nh * dh), dtype=q.dtype)
-        kc = k_cache.view(-1, PAGE, nh, dh).float()
-        vc = v_cache.view(-1, PAGE, nh, dh).float()
+        kc = k_cache.view(-1, PAGE, nkv, dh).float()
+        vc = v_cache.view(-1, PAGE, nkv, dh).float()
         for b in range(B):
             n = int(ctx_len[b])
             pages = page_table[b, :(n + PAGE - 1) // PAGE].long()
-            K = kc[pages].reshape(-1, nh, dh)[:n]
-            V = vc[pages].reshape(-1, nh, dh)[:n]
+            K = kc[pages].reshape(-1, nkv, dh)[:n].repeat_interleave(nh // nkv, 1)
+            V = vc[pages].reshape(-1, nkv, dh)[:n].repeat_interleave(nh // nkv, 1)
             qq = q[b, :nh * dh].float().view(nh, dh)
             s = torch.einsum("hd,nhd->hn", qq, K) * scale
             p = torch.softmax(s, -1)
@@ -73,7 +76,7 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     rc = _lib.lib().cb_decode_attn(_lib.ptr(q), q.stride(0), _lib.ptr(k_cache), _lib.ptr(v_cache),
                                    _lib.ptr(page_table), page_table.shape[1], _lib.ptr(ctx_len),
                                    _lib.ptr(out), out.stride(0), _lib.ptr(part_o),
-                                   _lib.ptr(part_ml), B, nh, dh, splits, ctypes.c_float(scale),
+                                   _lib.ptr(part_ml), B, nh, nkv, dh, splits, ctypes.c_float(scale),
                                    _lib.stream_ptr())
     _lib.check_rc(rc, "cb_decode_attn", launches=2 if splits > 1 else 1)
     return out

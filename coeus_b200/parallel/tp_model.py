@@ -271,13 +271,14 @@ class TPDecoderLM:
             E.rope_(qkv, heads, cfg.head_dim, S, pos_offset=pos_offset, theta=cfg.rope_theta,
                     inverse=inverse, pos_dev=pos_dev)
 
-    def _split_qkv(self, qkv: torch.Tensor):
-        """``(q, k, v)`` of this rank's heads as ``[T, Hl]`` each; under grouped-query attention
-        the rank's K/V heads are repeated for the query heads of their groups (the attention
-        kernels are multi-head)."""
+    def _split_qkv(self, qkv: torch.Tensor, expand: bool = True):
+        """``(q, k, v)`` of this rank's heads; under grouped-query attention ``expand=True``
+        repeats the rank's K/V heads for the query heads of their groups (``[T, Hl]`` each: the
+        backward attention kernel is multi-head), ``expand=False`` leaves K/V ``[T, Kl]`` (the
+        forward, decode and cache-write kernels index them by query head // group)."""
         Hl, Kl = self.Hl, self.Kl
         q, k, v = qkv[:, :Hl], qkv[:, Hl:Hl + Kl], qkv[:, Hl + Kl:]
-        if self.gqa:
+        if self.gqa and expand:
             T, dh, g_ = qkv.shape[0], self.cfg.head_dim, self.nh_l // self.kvh_l
             k, v = (t.reshape(T, self.kvh_l, 1, dh).expand(T, self.kvh_l, g_, dh).reshape(T, Hl)
                     for t in (k, v))

@@ -13,9 +13,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.mark.parametrize("dh,nh", [(64, 4), (128, 2)])
+@pytest.mark.parametrize("dh,nq,nh", [(64, 4, 4), (128, 2, 2), (64, 8, 2), (128, 4, 1)])
 @pytest.mark.parametrize("splits", [1, 4])
-def test_paged_decode_attention(dh, nh, splits):
+def test_paged_decode_attention(dh, nq, nh, splits):
+    """``nq`` query heads over a cache of ``nh`` key/value heads (grouped-query when fewer)."""
     torch.manual_seed(0)
     B, n_pages, max_pages = 3, 40, 8
     kc = torch.zeros(n_pages, D.PAGE, nh, dh, device=DEV, dtype=torch.bfloat16)
@@ -28,9 +29,9 @@ def test_paged_decode_attention(dh, nh, splits):
         pos0 = torch.zeros(B, dtype=torch.int32, device=DEV)
         D.kv_write(k, v, kc, vc, perm[b:b + 1].contiguous(), pos0[:1], n, nh, dh)
     ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
-    q = torch.randn(B, nh * dh, device=DEV).bfloat16()
-    out = D.decode_attention(q, kc, vc, perm.contiguous(), ctx, nh, dh, splits=splits)
-    ref = D.decode_attention(q.cpu(), kc.cpu(), vc.cpu(), perm.cpu(), ctx.cpu(), nh, dh)
+    q = torch.randn(B, nq * dh, device=DEV).bfloat16()
+    out = D.decode_attention(q, kc, vc, perm.contiguous(), ctx, nq, dh, splits=splits, nkv=nh)
+    ref = D.decode_attention(q.cpu(), kc.cpu(), vc.cpu(), perm.cpu(), ctx.cpu(), nq, dh, nkv=nh)
     torch.cuda.synchronize()
     assert _lib.status_buffer(torch.device("cuda", 0)).tolist()[0] == 0
     assert (out.float().cpu() - ref.float()).abs().max() < 0.03
@@ -41,12 +42,16 @@ def test_argmax_rows():
     assert torch.equal(D.argmax_rows(x).cpu(), x.float().argmax(-1).cpu())
 
 
-@pytest.mark.parametrize("kind", ["gpt", "llama"])
+@pytest.mark.parametrize("kind", ["gpt", "llama", "gqa"])
 def test_engine_matches_full_forward(kind):
     torch.manual_seed(0)
     if kind == "gpt":
         cfg = DecoderConfig(hidden_dim=256, num_layers=2, num_heads=4, intermediate_dim=512,
                             vocab_size=1000, max_seq_len=512)
+    elif kind == "gqa":     # four query heads over one key/value head: the cache holds one head
+        cfg = DecoderConfig(hidden_dim=256, num_layers=2, num_heads=4, num_kv_heads=1,
+                            intermediate_dim=512, vocab_size=1000, max_seq_len=512,
+                            use_bias=False, activation="swiglu", norm="rmsnorm", pos="rope")
     else:
         cfg = DecoderConfig(hidden_dim=256, num_layers=2, num_heads=2, intermediate_dim=512,
                             vocab_size=1000, max_seq_len=512, use_bias=False, activation="swiglu",
