@@ -52,6 +52,22 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, f
       "mov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
+// Dropout masks are a pure function of (key, element index): one 32-bit hash per group of four
+// consecutive elements, one byte per element; an element is dropped when its byte is below
+// thr = round(p * 256), kept elements are scaled by 256 / (256 - thr).  The same function is
+// restated with tensor ops on the host (ops/elementwise.py dropout_mask), so the CPU path, the
+// forward pass and the recomputation in the backward pass agree bit for bit and no mask is stored.
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ uint32_t dropout_bits(unsigned long long group, uint32_t key) {
+  return mix32(static_cast<uint32_t>(group) ^ mix32(static_cast<uint32_t>(group >> 32) ^ key));
+}
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -635,3 +635,45 @@ extern "C" int cb_f32_to_bf16(const float* x, void* y, size_t n, void* stream) {
       x, static_cast<__nv_bfloat16*>(y), n);
   CB_RET();
 }
+
+// ------------------------------------------------------------------------------------------
+// Dropout applied to a [rows, cols] bf16 tensor (cols % 8 == 0): y = x * mask * scale with the
+// mask of common.cuh (dropout_bits) over the element index row * cols + col.  The forward pass
+// of the decoder applies it inside GEMM epilogues; this kernel recomputes the same mask on the
+// gradient in the backward pass and serves the stand-alone nn module.
+namespace cb {
+__global__ void dropout_apply_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                     __nv_bfloat16* __restrict__ y, int ldy, size_t rows, int cols,
+                                     int thr, uint32_t key, float scale) {
+  const int nv = cols / 8;
+  const size_t total = rows * nv;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = i / nv;
+    const int c = static_cast<int>(i % nv) * 8;
+    float v[8];
+    load8(x + r * ldx + c, v);
+    const unsigned long long g0 = (static_cast<unsigned long long>(r) * cols + c) >> 2;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const uint32_t h = dropout_bits(g0 + g, key);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        v[g * 4 + j] = static_cast<int>((h >> (8 * j)) & 255u) < thr ? 0.f : v[g * 4 + j] * scale;
+    }
+    store8(y + r * ldy + c, v);
+  }
+}
+}  // namespace cb
+
+extern "C" int cb_dropout_apply(const void* x, int ldx, void* y, int ldy, size_t rows, int cols,
+                                int thr, unsigned int key, void* stream) {
+  if (cols % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || thr < 0 || thr > 255) return -1;
+  if (rows == 0) return 0;
+  const size_t work = rows * (cols / 8);
+  const int blocks = static_cast<int>(std::min<size_t>((work + 255) / 256, cb::sm_count() * 16));
+  cb::dropout_apply_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy, rows, cols,
+      thr, key, 256.0f / static_cast<float>(256 - thr));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -48,6 +48,9 @@ struct GemmArgs {
   float alpha;
   int ksplit;
   int tma_store;                // bf16 outputs leave through shared memory and TMA stores
+  int drop_thr;                 // dropout on the value before the residual is added: bytes below
+  uint32_t drop_key;            // drop_thr (= round(p * 256)) drop the element; 0 = off
+  float drop_scale;             // 256 / (256 - drop_thr)
   int* status;
   // ---- grouped GEMM (experts stacked along the row dimension of every operand's memory)
   int group_m;                  // output rows per group; 0 = one group.  Group g of a tile adds
@@ -132,6 +135,19 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& p, float* v, float
           v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
         }
       }
+    }
+  }
+  if (p.drop_thr > 0) {
+    // the 32 columns start on a multiple of 32: eight hash groups of four elements
+    const unsigned long long g0 =
+        (static_cast<unsigned long long>(row) * static_cast<unsigned long long>(p.N) + col0) >> 2;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const uint32_t h = dropout_bits(g0 + g, p.drop_key);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        v[g * 4 + j] = static_cast<int>((h >> (8 * j)) & 255u) < p.drop_thr ? 0.f
+                                                                             : v[g * 4 + j] * p.drop_scale;
     }
   }
   if (p.resid != nullptr && row_ok) {
@@ -826,8 +842,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* D, int M, int N, i
                           int ldb, int ldd, int a_mn, int b_mn, const void* bias,
                           const void* resid, int ldr, const void* aux_in, void* aux_out,
                           int ldaux, int epi, int out_mode, float alpha, int ksplit, int bn,
-                          int* status, int max_ctas, void* stream, int groups) {
+                          int* status, int max_ctas, void* stream, int groups, int drop_thr = 0,
+                          unsigned int drop_key = 0) {
   using namespace cb;
+  if (drop_thr < 0 || drop_thr > 255 || (drop_thr > 0 && (N % 32) != 0)) return -25;
   if (M <= 0 || N <= 0 || K <= 0 || groups < 1) return -20;
   if ((N % 8) != 0 || (ldd % 4) != 0) return -21;
   if ((K % 8) != 0 && !(a_mn && b_mn)) return -21;
@@ -891,6 +909,9 @@ static int gemm_bf16_impl(const void* A, const void* B, void* D, int M, int N, i
   g.aux_out = static_cast<__nv_bfloat16*>(aux_out);
   g.ldaux = ldaux;
   g.epi = epi; g.out_mode = out_mode; g.alpha = alpha; g.ksplit = ksplit; g.status = status;
+  g.drop_thr = drop_thr;
+  g.drop_key = drop_key;
+  g.drop_scale = 256.0f / static_cast<float>(256 - drop_thr);
   if (groups > 1) {
     g.group_m = Mg;
     g.g_am = a_mn ? -Mg : 0;
@@ -925,6 +946,18 @@ extern "C" int cb_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   return gemm_bf16_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, bias, resid, ldr, aux_in,
                         aux_out, ldaux, epi, out_mode, alpha, ksplit, bn, status, max_ctas, stream,
                         1);
+}
+
+// cb_gemm_bf16 with dropout on the epilogue value (after bias / activation, before the residual):
+// drop_thr = round(p * 256) in 1..255, drop_key selects the mask (see dropout_bits); N % 32 == 0.
+extern "C" int cb_gemm_bf16_dropout(const void* A, const void* B, void* D, int M, int N, int K,
+                                    int lda, int ldb, int ldd, int a_mn, int b_mn,
+                                    const void* bias, const void* resid, int ldr, int epi,
+                                    float alpha, int bn, int drop_thr, unsigned int drop_key,
+                                    int* status, int max_ctas, void* stream) {
+  return gemm_bf16_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, bias, resid, ldr, nullptr,
+                        nullptr, 0, epi, cb::OUT_BF16, alpha, 1, bn, status, max_ctas, stream, 1,
+                        drop_thr, drop_key);
 }
 
 extern "C" int cb_gemm_bf16_grouped(const void* A, const void* B, void* D, int groups, int M, int N,

@@ -228,15 +228,22 @@ class DecoderConfig:
         if self.kv_dim % 8:
             raise ConfigError.invalid("num_kv_heads", self.num_kv_heads,
                                       "kv_heads * head_dim must be a multiple of 8 (16-byte rows)")
-        if self.dropout or self.attention_dropout:
-            # the reference declares dropout rates and never applies them (its forward pass is
-            # inference only, plugins/model-transformer/src/lib.rs:863-921); the kernels here
-            # have no dropout either, so a non-zero rate is refused rather than ignored
-            raise ConfigError.invalid("dropout", self.dropout or self.attention_dropout,
-                                      "Dropout is not implemented; set dropout and "
-                                      "attention_dropout to 0")
+        for name, rate in (("dropout", self.dropout), ("attention_dropout", self.attention_dropout)):
+            # the reference declares the two rates and never applies them (its forward pass is
+            # inference only, plugins/model-transformer/src/lib.rs:863-921); here they act in
+            # training passes of the decoder (rates are realised in steps of 1/256)
+            if not 0.0 <= rate < 1.0:
+                raise ConfigError.invalid(name, rate, "Dropout rates must lie in [0, 1)")
         if self.num_experts and not (0 < self.top_k <= self.num_experts):
             raise ConfigError.invalid("top_k", self.top_k, "top_k must be in [1, num_experts]")
+
+    def require_no_dropout(self, where: str) -> None:
+        """Dropout is implemented in the single-replica / data-parallel decoder; the other
+        execution plans refuse a non-zero rate instead of ignoring it."""
+        if self.dropout or self.attention_dropout:
+            raise ConfigError.invalid("dropout", self.dropout or self.attention_dropout,
+                                      f"Dropout is not implemented under {where}; set dropout "
+                                      "and attention_dropout to 0")
 
     def to_dict(self) -> Dict[str, Any]:
         return asdict(self)

@@ -173,6 +173,13 @@ class DecoderLM:
             raise ProcessingError.unsupported(
                 "grouped-query attention with context / Ulysses parallelism",
                 "the ring and all-to-all paths exchange one K/V head per query head")
+        # dropout (training passes only): masks are a function of (seed, step, call, rank, layer,
+        # site), nothing is stored; see _drop()
+        self.train_mode = True
+        self.dropout_seed, self.dropout_step, self.dropout_rank = seed, 0, 0
+        self._drop_call, self._drop_active = 0, False
+        if cfg.num_experts or cp is not None or layers is not None:
+            cfg.require_no_dropout("expert / context / pipeline parallelism")
         self.epx = None
         self.moe: List = []
         if cfg.num_experts:
@@ -398,6 +405,22 @@ class DecoderLM:
             E.rope_(qkv[c * Tc:(c + 1) * Tc], 2 * nh, dh, S, pos_offset=off, theta=cfg.rope_theta,
                     inverse=inverse)
 
+    def train(self, mode: bool = True) -> "DecoderLM":
+        """Training mode applies dropout in :meth:`forward_loss`; evaluation mode never does."""
+        self.train_mode = bool(mode)
+        return self
+
+    def _drop(self, rate: float, l: int, site: int):
+        """``(threshold, key)`` of one dropout site of the current training pass, or ``None``
+        when dropout does not apply (rate 0, evaluation mode, inference entry points)."""
+        if not self._drop_active or not rate:
+            return None
+        thr = E.dropout_threshold(rate)
+        if thr == 0:
+            return None
+        return thr, E.dropout_key(self.dropout_seed, self.dropout_step, self._drop_call,
+                                  self.dropout_rank, l, site)
+
     def _expand_kv(self, t: torch.Tensor) -> torch.Tensor:
         """``[T, kv_heads * dh] -> [T, heads * dh]``: every K/V head repeated for the query heads
         of its group (query head ``h`` reads K/V head ``h // group``).  The forward kernel reads
@@ -428,10 +451,15 @@ class DecoderLM:
         else:
             Hkv = cfg.kv_dim
             q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
-            # grouped-query attention: the forward kernel indexes K/V by head // group itself
-            attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+            da = self._drop(cfg.attention_dropout, l, 2)
+            if da is not None:   # dropout on the probabilities: the materialised path
+                attn, lse = A.attention_dropout_fwd(q, k, v, B, S, nh, dh, *da, causal=True)
+            else:
+                # grouped-query attention: the forward kernel indexes K/V by head // group itself
+                attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+        d0, d1 = self._drop(cfg.dropout, l, 0), self._drop(cfg.dropout, l, 1)
         x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
-                             max_ctas=mc)
+                             max_ctas=mc, dropout=d0)
         n2, mean2, rstd2 = self._norm(x_mid, p + n2n)
         if self.moe:
             u = act = None
@@ -440,17 +468,20 @@ class DecoderLM:
             gu = G.linear_fwd(n2, self.w[p + "ff.gate_up_weights"], None, max_ctas=mc)
             act = E.swiglu_fwd(gu)
             u = gu
-            x_out = G.linear_fwd(act, self.w[p + "ff.down_weights"], None, resid=x_mid, max_ctas=mc)
+            x_out = G.linear_fwd(act, self.w[p + "ff.down_weights"], None, resid=x_mid, max_ctas=mc,
+                                 dropout=d1)
         else:
             u = torch.empty((T, cfg.intermediate_dim), dtype=self.p16.dtype, device=x.device) \
                 if save is not None else None
             act = G.linear_fwd(n2, self.w[p + "ff.up_weights"], bias("ff.up_bias"), epi="gelu",
                                aux_out=u, max_ctas=mc)
             x_out = G.linear_fwd(act, self.w[p + "ff.down_weights"], bias("ff.down_bias"),
-                                 resid=x_mid, max_ctas=mc)
+                                 resid=x_mid, max_ctas=mc, dropout=d1)
         if save is not None:
             save[l] = dict(x=x, n1=n1, mean1=mean1, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse,
-                           x_mid=x_mid, n2=n2, mean2=mean2, rstd2=rstd2, u=u, act=act)
+                           x_mid=x_mid, n2=n2, mean2=mean2, rstd2=rstd2, u=u, act=act,
+                           drop=(d0, d1, self._drop(cfg.attention_dropout, l, 2)
+                                 if self.cp is None else None))
         return x_out
 
     def _check_ids(self, ids: torch.Tensor) -> Tuple[int, int]:
@@ -514,6 +545,7 @@ class DecoderLM:
         """Logits in bf16: ``[B, S, V]``, or ``[B, V]`` of the last position (the reference's
         ``forward`` returns the last position only, lib.rs:913-918)."""
         B, S = self._check_ids(ids)
+        self._drop_active = False          # inference entry point: never any dropout
         xf = self.forward_hidden(ids)
         V, Vp = self.cfg.vocab_size, self.cfg.vocab_padded
         if last_only:
@@ -528,6 +560,11 @@ class DecoderLM:
         ``targets [B,S]``; keeps what :meth:`backward` needs.  ``grad_scale`` is the factor the
         logit gradients are multiplied with (default ``1 / (B*S)``)."""
         B, S = self._check_ids(ids)
+        cfg = self.cfg
+        self._drop_active = bool(self.train_mode and self.g32 is not None
+                                 and (cfg.dropout or cfg.attention_dropout))
+        if self._drop_active:
+            self._drop_call += 1           # micro-steps of one optimizer step draw different masks
         save: dict = {"ids": ids.reshape(-1), "B": B, "S": S}
         xf = self.forward_hidden(ids, save)
         return self.loss_from_hidden(xf, targets, save, grad_scale)
@@ -621,36 +658,45 @@ class DecoderLM:
                 self._block_fwd(l, a["x"], B, S, again)
                 a = again[l]
             p = f"layers.{l}."
+            d0, d1, da = a.get("drop", (None, None, None))
+            # the gradient that enters the down projection is the residual gradient times the
+            # (recomputed) dropout mask; dx itself continues along the residual path
+            dxd = E.dropout_apply(dx, *d1) if d1 is not None else dx
             if self.moe:
                 dn2 = self.moe[l - self.layer_ids[0]].backward(dx, aux_grad_scale=sv["aux_scale"])
             elif cfg.activation == "swiglu":
-                G.linear_wgrad(a["act"], dx, self.g[p + "ff.down_weights"], max_ctas=mc)
-                dact = G.linear_dgrad(dx, self.w[p + "ff.down_weights"], max_ctas=mc)
+                G.linear_wgrad(a["act"], dxd, self.g[p + "ff.down_weights"], max_ctas=mc)
+                dact = G.linear_dgrad(dxd, self.w[p + "ff.down_weights"], max_ctas=mc)
                 du = E.swiglu_bwd(a["u"], dact)
                 G.linear_wgrad(a["n2"], du, self.g[p + "ff.gate_up_weights"], max_ctas=mc)
                 dn2 = G.linear_dgrad(du, self.w[p + "ff.gate_up_weights"], max_ctas=mc)
             else:
-                G.linear_wgrad(a["act"], dx, self.g[p + "ff.down_weights"], max_ctas=mc)
-                du = G.linear_dgrad(dx, self.w[p + "ff.down_weights"], epi="dgelu", aux_in=a["u"],
+                G.linear_wgrad(a["act"], dxd, self.g[p + "ff.down_weights"], max_ctas=mc)
+                du = G.linear_dgrad(dxd, self.w[p + "ff.down_weights"], epi="dgelu", aux_in=a["u"],
                                     max_ctas=mc)
                 G.linear_wgrad(a["n2"], du, self.g[p + "ff.up_weights"], max_ctas=mc)
                 if cfg.use_bias:
-                    E.colsum_into(dx, self.g[p + "ff.down_bias"])
+                    E.colsum_into(dxd, self.g[p + "ff.down_bias"])
                     E.colsum_into(du, self.g[p + "ff.up_bias"])
                 dn2 = G.linear_dgrad(du, self.w[p + "ff.up_weights"], max_ctas=mc)
             dx_mid = N.norm_bwd(dn2, a["x_mid"], self.w[p + n2n + "_scale"], a["mean2"], a["rstd2"],
                                 self.g[p + n2n + "_scale"],
                                 None if rms else self.g[p + n2n + "_bias"], dx, rms)
-            G.linear_wgrad(a["attn"], dx_mid, self.g[p + "attn.o_weights"], max_ctas=mc)
+            dxm = E.dropout_apply(dx_mid, *d0) if d0 is not None else dx_mid
+            G.linear_wgrad(a["attn"], dxm, self.g[p + "attn.o_weights"], max_ctas=mc)
             if cfg.use_bias:
-                E.colsum_into(dx_mid, self.g[p + "attn.o_bias"])
-            dattn = G.linear_dgrad(dx_mid, self.w[p + "attn.o_weights"], max_ctas=mc)
+                E.colsum_into(dxm, self.g[p + "attn.o_bias"])
+            dattn = G.linear_dgrad(dxm, self.w[p + "attn.o_weights"], max_ctas=mc)
             qkv = a["qkv"]
             Hkv = cfg.kv_dim
             q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
             dqkv = self._buf("dqkv", (dattn.shape[0], 3 * H))
             if self.cp is not None:
                 self.cp.attention_bwd(dattn, qkv, a["attn"], a["lse"], B, S, nh, dh, dqkv=dqkv)
+            elif da is not None:
+                dqkv = self._buf("dqkv_drop", (dattn.shape[0], cfg.qkv_dim))
+                A.attention_dropout_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, *da,
+                                        causal=True, dqkv=dqkv)
             elif self.gqa:
                 A.attention_bwd(dattn, q, self._expand_kv(k), self._expand_kv(v), a["attn"],
                                 a["lse"], B, S, nh, dh, causal=True, dqkv=dqkv)

@@ -103,3 +103,53 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
         _lib.ptr(st), _lib.stream_ptr())
     _lib.check_rc(rc, "cb_attn_bwd", launches=3)
     return out[:, :H], out[:, H:2 * H], out[:, 2 * H:]
+
+
+# ------------------------------------------------------------------------------ dropout path
+# Attention with dropout on the probabilities materialises the score matrix with tensor ops (on
+# either device): the flash kernels have no dropout, and a rate > 0 is a training-only option
+# that no benchmark of this framework uses.  The mask is the counter-based one of
+# :func:`coeus_b200.ops.elementwise.dropout_mask` over the ``[B*nh*S, S]`` probability matrix, so
+# nothing is stored between the passes and CPU and GPU agree.
+def attention_dropout_fwd(q, k, v, B, S, nh, dh, thr, key, *, causal=True, scale=None):
+    """``(o, lse)`` like :func:`attention_fwd`, with ``P`` dropped before ``P @ V``."""
+    from .elementwise import dropout_mask
+    scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    _, lse, p, (_, _, vf) = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
+    keep = dropout_mask(B * nh * S, S, thr, key, q.device).view(B, nh, S, S)
+    pd = torch.where(keep, p * (256.0 / (256 - thr)), torch.zeros((), device=q.device))
+    o = (pd @ vf).transpose(1, 2).reshape(B * S, nh * dh)
+    return o.to(q.dtype), lse
+
+
+def attention_dropout_bwd(do, q, k, v, o, lse, B, S, nh, dh, thr, key, *, causal=True, scale=None,
+                          dqkv=None):
+    """``(dq, dk, dv)`` of :func:`attention_dropout_fwd` (views of one ``[B*S, H + 2*Hkv]``
+    buffer)."""
+    from .elementwise import dropout_mask
+    scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    H, Hkv = nh * dh, k.shape[1]
+    nkv = Hkv // dh
+    _, _, p, (qf, kf, vf) = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
+    sc = 256.0 / (256 - thr)
+    keep = dropout_mask(B * nh * S, S, thr, key, q.device).view(B, nh, S, S)
+    zero = torch.zeros((), device=q.device)
+    pd = torch.where(keep, p * sc, zero)
+    dof = do.float().reshape(B, S, nh, dh).transpose(1, 2)
+    of = o.float().reshape(B, S, nh, dh).transpose(1, 2)
+    dv = pd.transpose(-1, -2) @ dof
+    dp = torch.where(keep, (dof @ vf.transpose(-1, -2)) * sc, zero)
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = ds @ kf
+    dk = ds.transpose(-1, -2) @ qf
+    if nkv != nh:        # gradients of a shared K/V head: the sum over its query heads
+        g = nh // nkv
+        dk = dk.reshape(B, nkv, g, S, dh).sum(2)
+        dv = dv.reshape(B, nkv, g, S, dh).sum(2)
+    out = dqkv if dqkv is not None else torch.empty((B * S, H + 2 * Hkv), dtype=q.dtype,
+                                                    device=q.device)
+    out[:, :H] = dq.transpose(1, 2).reshape(B * S, H).to(out.dtype)
+    out[:, H:H + Hkv] = dk.transpose(1, 2).reshape(B * S, Hkv).to(out.dtype)
+    out[:, H + Hkv:H + 2 * Hkv] = dv.transpose(1, 2).reshape(B * S, Hkv).to(out.dtype)
+    return out[:, :H], out[:, H:H + Hkv], out[:, H + Hkv:H + 2 * Hkv]

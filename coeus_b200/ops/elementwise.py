@@ -416,3 +416,69 @@ def sin_init_(p: torch.Tensor, hidden: int, index_offset: int = 0) -> torch.Tens
                                 _lib.stream_ptr())
     _lib.check_rc(rc, "cb_sin_init")
     return p
+
+
+# ------------------------------------------------------------------------------ dropout
+def dropout_threshold(p: float) -> int:
+    """Dropout rates are realised in steps of 1/256: the byte threshold of rate ``p``."""
+    thr = int(round(float(p) * 256.0))
+    if not 0 <= thr <= 255:
+        raise ValueError(f"dropout rate {p} out of range [0, 1)")
+    return thr
+
+
+def dropout_key(seed: int, *parts: int) -> int:
+    """32-bit key of one dropout site from the run's seed and integers that name the site (step,
+    layer, position in the layer, micro-batch, rank ...)."""
+    x = (int(seed) * 0x9E3779B1 + 0x7F4A7C15) & 0xFFFFFFFF
+    for v in parts:
+        x = ((x ^ (int(v) & 0xFFFFFFFF)) * 0x85EBCA6B + 0xC2B2AE35) & 0xFFFFFFFF
+        x ^= x >> 15
+    return x
+
+
+def _mix32(x: torch.Tensor) -> torch.Tensor:
+    m = 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    x = (x * 0x7FEB352D) & m
+    x = x ^ (x >> 15)
+    x = (x * 0x846CA68B) & m
+    return x ^ (x >> 16)
+
+
+def dropout_mask(rows: int, cols: int, thr: int, key: int, device="cpu",
+                 row_offset: int = 0) -> torch.Tensor:
+    """The keep-mask (bool ``[rows, cols]``) of the kernels' dropout function
+    (``csrc/common.cuh: dropout_bits``): element ``(r, c)`` has index ``(r + row_offset) * cols +
+    c``, groups of four consecutive indices share one 32-bit hash, one byte per element, dropped
+    when the byte is below ``thr``."""
+    r = torch.arange(row_offset, row_offset + rows, dtype=torch.int64, device=device)[:, None]
+    c = torch.arange(cols, dtype=torch.int64, device=device)[None, :]
+    idx = r * cols + c
+    group, lane = idx >> 2, idx & 3
+    h = _mix32((group & 0xFFFFFFFF) ^ _mix32(((group >> 32) & 0xFFFFFFFF) ^ (key & 0xFFFFFFFF)))
+    return ((h >> (8 * lane)) & 255) >= thr
+
+
+def dropout_apply(x: torch.Tensor, thr: int, key: int, out: Optional[torch.Tensor] = None
+                  ) -> torch.Tensor:
+    """``x * mask * 256 / (256 - thr)`` for a 2-D tensor with the mask of :func:`dropout_mask`;
+    ``thr == 0`` returns ``x`` itself."""
+    if thr == 0:
+        return x
+    rows, cols = x.shape
+    if not x.is_cuda:
+        keep = dropout_mask(rows, cols, thr, key, x.device)
+        y = torch.where(keep, x.float() * (256.0 / (256 - thr)), torch.zeros((), device=x.device))
+        y = y.to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty_like(x)
+    rc = _lib.lib().cb_dropout_apply(_lib.ptr(x), x.stride(0), _lib.ptr(out), out.stride(0),
+                                     c_size_t(rows), cols, thr, ctypes.c_uint(key & 0xFFFFFFFF),
+                                     _lib.stream_ptr())
+    _lib.check_rc(rc, "cb_dropout_apply")
+    return out

@@ -78,8 +78,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          aux_in: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, alpha: float = 1.0,
          ksplit: int = 1, bn: Optional[int] = None, max_ctas: int = 0,
-         _discard: bool = False) -> torch.Tensor:
+         _discard: bool = False, dropout: Optional[tuple] = None) -> torch.Tensor:
     """``out[M,N] = epilogue(alpha * A @ B^T)`` with A logical ``[M,K]`` and B logical ``[N,K]``.
+
+    ``dropout=(thr, key)`` drops elements of the epilogue value (after bias and activation,
+    before ``resid`` is added) with the mask of :func:`coeus_b200.ops.elementwise.dropout_mask`
+    and scales the kept ones by ``256 / (256 - thr)`` (bf16 output, ``N % 32 == 0``).
 
     ``a_mn`` / ``b_mn`` say that the tensor passed is the transpose in memory (``[K,M]`` /
     ``[K,N]`` row-major).  ``accumulate=True`` adds into an fp32 ``out`` with atomic adds,
@@ -110,6 +114,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             v = _gelu_ref(v)
         elif epi == "dgelu":
             v = v * _gelu_grad_ref(aux_in.float())
+        if dropout is not None and dropout[0] > 0:
+            from .elementwise import dropout_mask
+            keep = dropout_mask(M, N, dropout[0], dropout[1], v.device)
+            v = torch.where(keep, v * (256.0 / (256 - dropout[0])), torch.zeros((), device=v.device))
         if resid is not None:
             v = v + resid.float()
         if accumulate:
@@ -131,6 +139,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         bn = _pick_bn(M, N)
     aux = aux_in if aux_in is not None else aux_out
     st = _lib.status_buffer(a.device)
+    if dropout is not None and dropout[0] > 0:
+        if aux is not None or out_mode != _OUT_BF16 or ksplit != 1 or N % 32:
+            raise ValueError("gemm: dropout needs a plain bf16 output with N % 32 == 0")
+        rc = _lib.lib().cb_gemm_bf16_dropout(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
+            out.stride(0), int(a_mn), int(b_mn), _lib.ptr(bias), _lib.ptr(resid),
+            resid.stride(0) if resid is not None else 0, EPI[epi], ctypes.c_float(alpha), bn,
+            int(dropout[0]), ctypes.c_uint(dropout[1] & 0xFFFFFFFF), _lib.ptr(st), max_ctas,
+            _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_gemm_bf16_dropout")
+        return out
     rc = _lib.lib().cb_gemm_bf16(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
         out.stride(0), int(a_mn), int(b_mn), _lib.ptr(bias), _lib.ptr(resid),
@@ -203,10 +222,11 @@ def linear_wgrad_grouped(x: torch.Tensor, dy: torch.Tensor, grad_w: torch.Tensor
 def linear_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
                resid: Optional[torch.Tensor] = None, epi: str = "none",
                aux_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-               out_dtype: torch.dtype = torch.bfloat16, max_ctas: int = 0) -> torch.Tensor:
-    """``y[T,out] = epilogue(x[T,in] @ w[in,out] + bias) (+ resid)``."""
+               out_dtype: torch.dtype = torch.bfloat16, max_ctas: int = 0,
+               dropout: Optional[tuple] = None) -> torch.Tensor:
+    """``y[T,out] = dropout(epilogue(x[T,in] @ w[in,out] + bias)) (+ resid)``."""
     return gemm(x, w, b_mn=True, bias=bias, resid=resid, epi=epi, aux_out=aux_out, out=out,
-                out_dtype=out_dtype, max_ctas=max_ctas)
+                out_dtype=out_dtype, max_ctas=max_ctas, dropout=dropout)
 
 
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, *, epi: str = "none",

@@ -32,6 +32,7 @@ class TPDecoderLM:
         """``recompute=True`` keeps only each block's (sequence-sharded) input and runs the
         block's forward, collectives included, again in the backward pass."""
         cfg.validate()
+        cfg.require_no_dropout("tensor parallelism")
         self.recompute = bool(recompute)
         if cfg.pos == "learned":
             raise ProcessingError.unsupported(

@@ -63,6 +63,7 @@ class ShardedDataParallel:
     # ------------------------------------------------------------------ set-up
     def attach(self, model, opt_cfg: AdamWConfig) -> None:
         self.model = model
+        model.dropout_rank = self.rank      # replicas draw different dropout masks
         self.opt_cfg = opt_cfg
         self.buckets: List[Bucket] = build_buckets(model.layout, model.n_flat)
         self.moffs, mtotal = moment_offsets(self.buckets, self.rank, self.world)

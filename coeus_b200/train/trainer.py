@@ -77,6 +77,7 @@ class Trainer:
         import math
         m = self.model
         tot = torch.zeros(2, dtype=torch.float64, device=m.device)
+        was_training, m.train_mode = getattr(m, "train_mode", True), False   # no dropout
         for ids, targets in batches:
             n = int((targets >= 0).sum())
             loss = m.forward_loss(ids, targets)
@@ -86,6 +87,7 @@ class Trainer:
         if self.dp is not None and self.dp.world > 1:
             import torch.distributed as dist
             dist.all_reduce(tot, group=self.dp.group)
+        m.train_mode = was_training
         mean = float(tot[0] / tot[1].clamp_min(1))
         return {"loss": mean, "perplexity": math.exp(min(mean, 80.0)), "tokens": int(tot[1])}
 
@@ -126,6 +128,7 @@ class Trainer:
         if last:
             self.update_parameters(1.0 / world)
             self.step_index += 1
+            m.dropout_step = self.step_index      # the next step draws new dropout masks
         return loss
 
     # ---- Checkpoint trait (src/core/traits.rs:181-189)

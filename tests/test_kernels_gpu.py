@@ -250,6 +250,33 @@ def test_attention_fwd_shapes_and_grouped_query(dh, nh, nkv, B, S, causal):
     A.FWD_POLY = 1
 
 
+def test_dropout_mask_is_the_same_on_the_device_in_the_gemm_and_on_the_host():
+    """One mask function in three places: the stand-alone kernel, the GEMM epilogue (dropout on
+    the value before the residual is added) and the tensor-op restatement on the host."""
+    torch.manual_seed(3)
+    thr, key = E.dropout_threshold(0.3), E.dropout_key(11, 5, 1, 0, 2, 1)
+    x = _bf(torch.randn(300, 256, device=DEV))
+    got = E.dropout_apply(x, thr, key)
+    want = E.dropout_apply(x.cpu(), thr, key)
+    torch.cuda.synchronize()
+    _status_clean()
+    assert torch.equal(got.cpu(), want)
+    kept = float((got != 0).float().mean())
+    assert abs(kept - (1 - thr / 256)) < 0.02
+    a = _bf(torch.randn(384, 128, device=DEV))
+    w = _bf(torch.randn(128, 256, device=DEV) * 0.1)
+    bias = _bf(torch.randn(256, device=DEV))
+    resid = _bf(torch.randn(384, 256, device=DEV))
+    y = G.linear_fwd(a, w, bias, resid=resid, dropout=(thr, key))
+    yr = G.linear_fwd(a.cpu(), w.cpu(), bias.cpu(), resid=resid.cpu(), dropout=(thr, key))
+    torch.cuda.synchronize()
+    _status_clean()
+    assert (y.float().cpu() - yr.float()).abs().max() < 0.06
+    # where the mask dropped the value only the residual is left, exactly
+    keep = E.dropout_mask(384, 256, thr, key)
+    assert torch.equal(y.cpu()[~keep], resid.cpu()[~keep])
+
+
 def test_normal_init_matches_cpu_generator():
     from coeus_b200.ops import elementwise as E
     n = 1_000_003

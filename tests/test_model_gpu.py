@@ -47,6 +47,33 @@ def test_forward_backward_matches_autograd(kind):
         assert err <= tol, (n, err, tol)
 
 
+def test_dropout_on_the_kernel_path_matches_the_host_path():
+    """The same model, seed and step on the GPU (dropout in the GEMM epilogues, mask recomputed
+    by the kernel in the backward pass, materialised attention-dropout path) and on the CPU
+    restatement: equal masks, so loss and gradients agree to bf16 accuracy."""
+    import dataclasses
+    cfg = dataclasses.replace(CFGS["gpt"], dropout=0.2, attention_dropout=0.1)
+    dev_m = DecoderLM(cfg, device="cuda", seed=5)
+    cpu_m = DecoderLM(cfg, device="cpu", seed=5, dtype=torch.float32)
+    cpu_m.p32.copy_(dev_m.p16.float().cpu())      # the host model computes on the bf16 weights
+    cpu_m.sync_working_copy()
+    batch = torch.randint(0, cfg.vocab_size, (2, 129), device="cuda")
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    for m, xx, yy in ((dev_m, x, y), (cpu_m, x.cpu(), y.cpu())):
+        m.zero_grad()
+        m.loss_value = float(m.forward_loss(xx, yy))
+        m.backward()
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda", 0))
+    assert abs(dev_m.loss_value - cpu_m.loss_value) < 0.03
+    dev_m.train(False)
+    assert abs(float(dev_m.forward_loss(x, y)) - dev_m.loss_value) > 1e-3   # dropout acted
+    for n, _ in dev_m.named_parameters():
+        got, want = dev_m.g[n].cpu(), cpu_m.g[n]
+        err = (got - want).abs().max().item()
+        assert err <= 0.06 * want.abs().max().item() + 2e-4, (n, err)
+
+
 def test_training_reduces_loss():
     cfg = CFGS["gpt"]
     m = DecoderLM(cfg, device="cuda")

@@ -339,13 +339,115 @@ def test_weight_only_quantisation():
         model.quantize(QuantConfig(bits=1))
 
 
-def test_nonzero_dropout_is_refused_not_ignored():
+def test_dropout_rates_are_validated_and_other_plans_refuse_them():
     from coeus_b200.models.config import DecoderConfig
     cfg = DecoderConfig(hidden_dim=32, num_layers=1, num_heads=2, intermediate_dim=64,
-                        vocab_size=64, max_seq_len=16, dropout=0.1)
+                        vocab_size=64, max_seq_len=16, dropout=0.1, attention_dropout=0.2)
+    cfg.validate()
+    with pytest.raises(Exception):
+        DecoderConfig(hidden_dim=32, num_layers=1, num_heads=2, intermediate_dim=64,
+                      vocab_size=64, max_seq_len=16, dropout=1.0).validate()
     with pytest.raises(Exception) as e:
-        cfg.validate()
+        cfg.require_no_dropout("tensor parallelism")
     assert "Dropout" in str(e.value)
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama_gqa"])
+def test_dropout_trains_with_recomputed_masks_and_matches_autograd(kind):
+    """Hidden and attention dropout in a training pass: the loss and every gradient equal an
+    autograd pass through the fp32 restatement that applies the SAME masks (they are a function
+    of the key and the element index), evaluation passes see no dropout, and a new step draws
+    new masks."""
+    import torch
+    import torch.nn.functional as F
+    from coeus_b200.models.config import DecoderConfig
+    from coeus_b200.models.decoder import DecoderLM
+    from coeus_b200.ops import elementwise as E
+    kw = dict(hidden_dim=32, num_layers=2, num_heads=4, intermediate_dim=64, vocab_size=64,
+              max_seq_len=16, dropout=0.25, attention_dropout=0.125)
+    if kind == "llama_gqa":
+        kw.update(num_kv_heads=2, use_bias=False, activation="swiglu", norm="rmsnorm", pos="rope")
+    cfg = DecoderConfig(**kw)
+    m = DecoderLM(cfg, "cpu", seed=3, dtype=torch.float32)
+    ids = torch.randint(0, 64, (2, 9), generator=torch.Generator().manual_seed(0))
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    B, S, H, nh, dh = 2, 8, 32, 4, 8
+    m.zero_grad()
+    loss = m.forward_loss(x, y)
+    call = m._drop_call
+    m.backward()
+
+    # the same model under autograd, masks from the same keys
+    params = {n: t.clone().requires_grad_(True) for n, t in m.named_parameters()}
+    from coeus_b200.models import torch_reference as R
+    ln = cfg.norm == "layernorm"
+    n1n, n2n, fn = ("ln1", "ln2", "final_ln") if ln else ("norm1", "norm2", "final_norm")
+
+    def norm(t, prefix):
+        if ln:
+            return F.layer_norm(t, (H,), params[prefix + "_scale"], params[prefix + "_bias"],
+                                cfg.norm_eps)
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + cfg.norm_eps) * params[prefix + "_scale"]
+
+    def key(l, site):
+        return E.dropout_key(m.dropout_seed, 0, call, 0, l, site)
+
+    def drop(t2d, rate, l, site):
+        thr = E.dropout_threshold(rate)
+        keep = E.dropout_mask(t2d.shape[0], t2d.shape[1], thr, key(l, site))
+        return torch.where(keep, t2d * (256.0 / (256 - thr)), torch.zeros(()))
+
+    h = params["token_embed"][x.reshape(-1)]
+    if cfg.pos == "sinusoidal":
+        h = h + R.sinusoid(S, H, "cpu").repeat(B, 1)
+    Hkv = cfg.kv_dim
+    for l in range(cfg.num_layers):
+        p = f"layers.{l}."
+        qkv = norm(h, p + n1n) @ params[p + "attn.qkv_weights"]
+        if cfg.use_bias:
+            qkv = qkv + params[p + "attn.qkv_bias"]
+        q = qkv[:, :H].reshape(B, S, nh, dh)
+        k = qkv[:, H:H + Hkv].reshape(B, S, cfg.kv_heads, dh)
+        v = qkv[:, H + Hkv:].reshape(B, S, cfg.kv_heads, dh)
+        if cfg.pos == "rope":
+            q, k = R._rope(q, S, cfg.rope_theta), R._rope(k, S, cfg.rope_theta)
+        g = nh // cfg.kv_heads
+        k, v = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
+        sc = (q.transpose(1, 2) @ k.transpose(1, 2).transpose(-1, -2)) / dh ** 0.5
+        sc = sc.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+        pr = torch.softmax(sc, -1)
+        pr = drop(pr.reshape(B * nh * S, S), cfg.attention_dropout, l, 2).reshape(B, nh, S, S)
+        a = (pr @ v.transpose(1, 2)).transpose(1, 2).reshape(B * S, H)
+        o = a @ params[p + "attn.o_weights"]
+        if cfg.use_bias:
+            o = o + params[p + "attn.o_bias"]
+        h = h + drop(o, cfg.dropout, l, 0)
+        n2 = norm(h, p + n2n)
+        if cfg.activation == "swiglu":
+            gu = n2 @ params[p + "ff.gate_up_weights"]
+            f = (F.silu(gu[:, :64]) * gu[:, 64:]) @ params[p + "ff.down_weights"]
+        else:
+            u = n2 @ params[p + "ff.up_weights"] + params[p + "ff.up_bias"]
+            f = R.gelu_tanh(u) @ params[p + "ff.down_weights"] + params[p + "ff.down_bias"]
+        h = h + drop(f, cfg.dropout, l, 1)
+    logits = norm(h, fn) @ params["output_proj"]
+    want = F.cross_entropy(logits[:, :64], y.reshape(-1))
+    want.backward()
+    assert abs(float(loss) - float(want.detach())) < 1e-5
+    for n, t in params.items():
+        got = m.g[n]
+        assert (got - t.grad).abs().max() <= 1e-4 * max(1.0, float(t.grad.abs().max())), n
+
+    # dropout really acted, evaluation sees none, and the next step draws other masks
+    m.train(False)
+    plain = float(m.forward_loss(x, y))
+    m.train(True)
+    assert abs(plain - float(loss)) > 1e-4
+    again = float(m.forward_loss(x, y))          # same step, next call: other masks
+    assert abs(again - float(loss)) > 1e-6
+    lg1 = m.forward_logits(x)
+    lg2 = m.forward_logits(x)
+    assert torch.equal(lg1, lg2)                 # inference entry points: never any dropout
 
 
 def test_grouped_query_attention_trains_saves_and_serves():
