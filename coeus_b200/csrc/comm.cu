@@ -96,13 +96,25 @@ struct AdamArgs {
 // this rank's own gradient buffer (only the owner reads that range) and writes the block's sum
 // of squares to partials[blockIdx.x] (fixed summation order, no atomics); MODE 2 reads the sums
 // back, multiplies them by *clip_coef and does AdamW + all-gather.
-template <int MODE>
-__global__ void __launch_bounds__(256)
+// The kernel runs beside the backward pass and must share SMs with the persistent compute
+// kernels: a GEMM CTA takes about 42K of an SM's 64K registers and nearly all of its shared
+// memory, so a block here is small (128 threads, ~12-16K registers, no dynamic shared memory) and
+// the launch spreads about one block per SM.  Blocks of 256 threads, two of which can land on one
+// SM, kept the GEMM's CTA off that SM for the duration of the bucket (measured: the bucket time
+// was then added to the step instead of hidden).
+constexpr int RS_THREADS = 128;
+template <int MODE, bool NVLS>
+__global__ void __launch_bounds__(RS_THREADS)
 rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, float* __restrict__ p32,
                    float* __restrict__ m, float* __restrict__ v, size_t gstart, size_t gend,
                    size_t moff, size_t decay_end, AdamArgs a, int n, const uint64_t* flags,
                    int slot, uint64_t expect, uint64_t limit_ns, int* status, int my_rank,
-                   float* __restrict__ partials, const float* __restrict__ clip_coef) {
+                   float* __restrict__ partials, const float* __restrict__ clip_coef,
+                   const float* __restrict__ grads_mc, __nv_bfloat16* __restrict__ params_mc) {
+  // grads_mc / params_mc (both or neither): NVLink multicast mappings of the gradient and weight
+  // buffers.  With them the shard is read with multimem.ld_reduce (one load returns the sum over
+  // all ranks, added in the switch) and the new weights leave with one multimem.st instead of a
+  // store per rank.
   __shared__ float red[32];
   if (MODE != 2 && flags != nullptr && !wait_flags(flags, slot, n, expect, limit_ns, status)) {
     if (MODE == 1 && threadIdx.x == 0) partials[blockIdx.x] = 0.f;
@@ -111,33 +123,17 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, float* __restrict__ p32,
   if (MODE == 2) a.grad_scale *= *clip_coef;
   float sq = 0.f;
   const size_t nvec = (gend - gstart) >> 3;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+  // what happens to one vector of eight summed gradients: AdamW on the owner's master weights and
+  // moments and the broadcast of the new bf16 weights (MODE 0 / 2), or the store of the sums (1)
+  auto update = [&](size_t i, float (&acc)[8]) {
     const size_t g0 = gstart + (i << 3);
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (MODE == 2) {
-      const float* gp = static_cast<const float*>(grads.p[my_rank]) + g0;
-      const float4 x = *reinterpret_cast<const float4*>(gp);
-      const float4 y = *reinterpret_cast<const float4*>(gp + 4);
-      acc[0] = x.x; acc[1] = x.y; acc[2] = x.z; acc[3] = x.w;
-      acc[4] = y.x; acc[5] = y.y; acc[6] = y.z; acc[7] = y.w;
-    } else {
-#pragma unroll 4
-      for (int r = 0; r < n; ++r) {
-        const float* gp = static_cast<const float*>(grads.p[r]) + g0;
-        const float4 x = ld_relaxed_sys_f4(gp);
-        const float4 y = ld_relaxed_sys_f4(gp + 4);
-        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
-      }
-    }
     if (MODE == 1) {
       float* own = static_cast<float*>(grads.p[my_rank]) + g0;
       *reinterpret_cast<float4*>(own) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       *reinterpret_cast<float4*>(own + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) sq = fmaf(acc[e], acc[e], sq);
-      continue;
+      return;
     }
     const size_t mi = moff + (i << 3);
     float pw[8], mm[8], vv[8];
@@ -174,9 +170,78 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, float* __restrict__ p32,
     o.y = pack_bf16x2(pw[2], pw[3]);
     o.z = pack_bf16x2(pw[4], pw[5]);
     o.w = pack_bf16x2(pw[6], pw[7]);
-#pragma unroll 4
-    for (int r = 0; r < n; ++r)
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + g0) = o;
+    if (NVLS) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                   :: "l"(params_mc + g0), "f"(__uint_as_float(o.x)), "f"(__uint_as_float(o.y)),
+                      "f"(__uint_as_float(o.z)), "f"(__uint_as_float(o.w)) : "memory");
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < n) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + g0) = o;
+    }
+  };
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t first = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (NVLS && MODE != 2) {
+    // D vectors per thread are requested before the first is used: with few blocks beside the
+    // backward pass the loop lives on the bytes it keeps in flight through the switch
+    constexpr int D = 4;
+    for (size_t i0 = first; i0 < nvec; i0 += D * stride) {
+      float4 qx[D], qy[D];
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        const size_t i = i0 + d * stride;
+        if (i < nvec) {
+          const float* gp = grads_mc + gstart + (i << 3);
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(qx[d].x), "=f"(qx[d].y), "=f"(qx[d].z), "=f"(qx[d].w) : "l"(gp) : "memory");
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(qy[d].x), "=f"(qy[d].y), "=f"(qy[d].z), "=f"(qy[d].w) : "l"(gp + 4) : "memory");
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        const size_t i = i0 + d * stride;
+        if (i < nvec) {
+          float acc[8] = {qx[d].x, qx[d].y, qx[d].z, qx[d].w, qy[d].x, qy[d].y, qy[d].z, qy[d].w};
+          update(i, acc);
+        }
+      }
+    }
+  } else {
+  for (size_t i = first; i < nvec; i += stride) {
+    const size_t g0 = gstart + (i << 3);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (MODE == 2) {
+      const float* gp = static_cast<const float*>(grads.p[my_rank]) + g0;
+      const float4 x = *reinterpret_cast<const float4*>(gp);
+      const float4 y = *reinterpret_cast<const float4*>(gp + 4);
+      acc[0] = x.x; acc[1] = x.y; acc[2] = x.z; acc[3] = x.w;
+      acc[4] = y.x; acc[5] = y.y; acc[6] = y.z; acc[7] = y.w;
+    } else {
+      // every rank's vector of a group of four is requested before the first one is used
+      constexpr int U = 4;
+      for (int r0 = 0; r0 < n; r0 += U) {
+        float4 x[U], y[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (r0 + u < n) {
+            const float* gp = static_cast<const float*>(grads.p[r0 + u]) + g0;
+            x[u] = ld_relaxed_sys_f4(gp);
+            y[u] = ld_relaxed_sys_f4(gp + 4);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (r0 + u < n) {
+            acc[0] += x[u].x; acc[1] += x[u].y; acc[2] += x[u].z; acc[3] += x[u].w;
+            acc[4] += y[u].x; acc[5] += y[u].y; acc[6] += y[u].z; acc[7] += y[u].w;
+          }
+        }
+      }
+    }
+    update(i, acc);
+  }
   }
   if (MODE == 1) {
     const float tot = block_sum(sq, red);
@@ -280,7 +345,8 @@ extern "C" int cb_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, f
                               float wd, int step, float grad_scale, int n, const void* flags,
                               int slot, unsigned long long expect, unsigned long long limit_ns,
                               int blocks, int* status, void* stream, int mode, int my_rank,
-                              float* partials, const float* clip_coef) {
+                              float* partials, const float* clip_coef, const void* grads_mc,
+                              void* params_mc) {
   if (n < 1 || n > MAX_RANKS || mode < 0 || mode > 2 || my_rank < 0 || my_rank >= n) return -1;
   if (mode == 1 && partials == nullptr) return -1;
   if (mode == 2 && clip_coef == nullptr) return -1;
@@ -299,15 +365,25 @@ extern "C" int cb_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, f
   a.bc1 = 1.0f - powf(beta1, static_cast<float>(step));
   a.bc2 = 1.0f - powf(beta2, static_cast<float>(step));
   a.grad_scale = grad_scale;
-  const size_t need = ((gend - gstart) / 8 + 255) / 256;
+  const size_t need = ((gend - gstart) / 8 + RS_THREADS - 1) / RS_THREADS;
   if (static_cast<size_t>(blocks) > need) blocks = static_cast<int>(need);
   if (mode == 1 && blocks < slots)
     cudaMemsetAsync(partials + blocks, 0, sizeof(float) * (slots - blocks), st);
   const uint64_t* f = static_cast<const uint64_t*>(flags);
+  const bool nvls = grads_mc != nullptr && params_mc != nullptr;
 #define CB_RS_LAUNCH(MODE_)                                                                    \
-  rs_adamw_ag_kernel<MODE_><<<blocks, 256, 0, st>>>(g, p, p32, m, v, gstart, gend, moff,       \
+  if (nvls)                                                                                    \
+    rs_adamw_ag_kernel<MODE_, true><<<blocks, RS_THREADS, 0, st>>>(g, p, p32, m, v, gstart, gend, moff, \
                                                     decay_end, a, n, f, slot, expect, limit_ns, \
-                                                    status, my_rank, partials, clip_coef)
+                                                    status, my_rank, partials, clip_coef,     \
+                                                    static_cast<const float*>(grads_mc),      \
+                                                    static_cast<__nv_bfloat16*>(params_mc));  \
+  else                                                                                         \
+  rs_adamw_ag_kernel<MODE_, false><<<blocks, RS_THREADS, 0, st>>>(g, p, p32, m, v, gstart, gend, moff,       \
+                                                    decay_end, a, n, f, slot, expect, limit_ns, \
+                                                    status, my_rank, partials, clip_coef,     \
+                                                    static_cast<const float*>(grads_mc),      \
+                                                    static_cast<__nv_bfloat16*>(params_mc))
   if (mode == 0) CB_RS_LAUNCH(0);
   else if (mode == 1) CB_RS_LAUNCH(1);
   else CB_RS_LAUNCH(2);

@@ -5,9 +5,12 @@ The flat buffer is cut into buckets that follow the backward pass (``plans.build
 soon as a bucket's gradients are complete on a rank, that rank signals its peers, and the owner
 of each shard of the bucket runs ONE kernel (``csrc/comm.cu: rs_adamw_ag_kernel``) that
 
-* reads the shard from every rank's gradient buffer over NVLink (the reduce-scatter),
+* reads the shard from every rank's gradient buffer over NVLink (the reduce-scatter): with
+  ``multimem.ld_reduce`` through an NVLink multicast mapping where the devices have one (the sum
+  is formed in the switch), else with plain peer loads added in rank order,
 * scales it and applies AdamW to its fp32 master weights and moments,
-* writes the new bf16 weights into every rank's working copy (the all-gather),
+* writes the new bf16 weights into every rank's working copy (the all-gather): one
+  ``multimem.st``, or a store per rank,
 
 on a side stream, overlapped with the rest of the backward pass.  ``backend="collective"`` does
 the same arithmetic with ``torch.distributed`` collectives (reduce-scatter / all-gather on NCCL,
@@ -17,6 +20,7 @@ CPU ranks, and the fallback when peer mapping is unavailable.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -45,8 +49,13 @@ class _ShardedOptState:
 
 
 class ShardedDataParallel:
-    def __init__(self, group, device, backend: Optional[str] = None, comm_blocks: int = 64,
-                 wait_limit_ms: float = 5000.0) -> None:
+    def __init__(self, group, device, backend: Optional[str] = None,
+                 comm_blocks: Optional[int] = None, wait_limit_ms: float = 5000.0,
+                 tail_blocks: Optional[int] = None) -> None:
+        """``comm_blocks``: thread blocks (of 128 threads) of a bucket kernel that runs beside the
+        backward pass: about one per SM, small enough to share the SM with a persistent compute
+        CTA; ``tail_blocks``: blocks of the buckets that complete when the backward pass ends and
+        have nothing left to hide behind."""
         self.group = group
         self.device = torch.device(device)
         self.rank = dist.get_rank(group)
@@ -56,7 +65,11 @@ class ShardedDataParallel:
         if backend not in ("p2p", "collective"):
             raise ProcessingError.invalid_input(f"unknown data-parallel backend '{backend}'")
         self.backend = backend
-        self.comm_blocks = comm_blocks
+        if comm_blocks is None:
+            comm_blocks = int(os.environ.get("COEUS_DP_BLOCKS", "128"))
+        if tail_blocks is None:
+            tail_blocks = int(os.environ.get("COEUS_DP_TAIL_BLOCKS", "592"))
+        self.comm_blocks, self.tail_blocks = comm_blocks, tail_blocks
         self.wait_limit_ms = wait_limit_ms
         self.model = None
 
@@ -76,10 +89,33 @@ class ShardedDataParallel:
         dist.broadcast(model.p32, src=dist.get_global_rank(self.group, 0), group=self.group)
         model.sync_working_copy()
         if self.backend == "p2p":
-            from .symm import SignalPad, SymmetricBuffer
+            from .symm import MulticastBuffer, SignalPad, SymmetricBuffer, multicast_supported
             n = model.n_flat
-            self.sym_g = SymmetricBuffer(n * 4, self.group, self.device)
-            self.sym_p = SymmetricBuffer(n * 2, self.group, self.device)
+            # Gradient and weight buffers: symmetric memory bound to an NVLink multicast object
+            # where the devices support it (the bucket kernel then reduces in the switch with
+            # multimem.ld_reduce and broadcasts with multimem.st), plain peer mappings otherwise.
+            # All ranks must take the same branch, hence the agreement over the group.
+            self.g_mc = self.p_mc = None
+            want = self.world > 1 and os.environ.get("COEUS_NVLS", "1") != "0" and \
+                multicast_supported(self.device)
+            ok = torch.tensor([1 if want else 0], device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            if int(ok) == 1:
+                try:
+                    self.sym_g = MulticastBuffer(n * 4, self.group, self.device)
+                    self.sym_p = MulticastBuffer(n * 2, self.group, self.device)
+                    self.g_mc, self.p_mc = self.sym_g.mc_ptr, self.sym_p.mc_ptr
+                except Exception:
+                    ok.fill_(0)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+                if int(ok) == 0:        # some rank failed: everybody falls back together
+                    for b in (getattr(self, "sym_g", None), getattr(self, "sym_p", None)):
+                        if isinstance(b, MulticastBuffer):
+                            b.close()
+                    self.g_mc = self.p_mc = None
+            if self.g_mc is None:
+                self.sym_g = SymmetricBuffer(n * 4, self.group, self.device)
+                self.sym_p = SymmetricBuffer(n * 2, self.group, self.device)
             model.rebind(p16=self.sym_p.view(torch.bfloat16, 0, n),
                          g32=self.sym_g.view(torch.float32, 0, n))
             self.pad = SignalPad(len(self.buckets) + 1, self.group, self.device,
@@ -87,11 +123,12 @@ class ShardedDataParallel:
             self.g_ptrs = self.sym_g.ptr_array()
             self.p_ptrs = self.sym_p.ptr_array()
             self.flag_ptrs = self.pad.buf.ptr_array()
-            self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            self.comm_stream = torch.cuda.Stream(
+                device=self.device, priority=int(os.environ.get("COEUS_DP_PRIORITY", "-1")))
             self.events = [torch.cuda.Event() for _ in self.buckets]
             self.done_event = torch.cuda.Event()
             # gradient clipping: per-bucket, per-block sums of squares of the reduced shards
-            self._slots = self.comm_blocks if self.comm_blocks > 0 else 64
+            self._slots = max(self.comm_blocks, self.tail_blocks, 64)
             self.partials = torch.zeros(len(self.buckets) * self._slots, dtype=torch.float32,
                                         device=self.device)
             self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
@@ -117,6 +154,9 @@ class ShardedDataParallel:
         """``mode`` 0: reduce-scatter + AdamW + all-gather; 1: reduce-scatter + sum of squares;
         2: AdamW (gradients times the clip coefficient) + all-gather."""
         c = self.opt_cfg
+        # buckets completed by the end of the backward pass (and the second pass of a clipped
+        # step) run alone: they take the whole machine
+        blocks = self.tail_blocks if (b.trigger == -2 or mode == 2) else self.comm_blocks
         s, e = b.shard(self.rank, self.world)
         m = self.model
         st = _lib.status_buffer(self.device)
@@ -130,8 +170,8 @@ class ShardedDataParallel:
             ctypes.c_float(self._grad_scale), self.world,
             ctypes.c_void_p(self.pad.buf.local_ptr), b.index,
             ctypes.c_ulonglong(self.step_no), ctypes.c_ulonglong(self.pad.limit_ns),
-            self._slots, _lib.ptr(st), _lib.stream_ptr(), mode, self.rank, _lib.ptr(part),
-            _lib.ptr(self.clip_coef))
+            blocks, _lib.ptr(st), _lib.stream_ptr(), mode, self.rank, _lib.ptr(part),
+            _lib.ptr(self.clip_coef), ctypes.c_void_p(self.g_mc), ctypes.c_void_p(self.p_mc))
         _lib.check_rc(rc, "cb_rs_adamw_ag")
 
     def _launch_bucket(self, b: Bucket) -> None:
