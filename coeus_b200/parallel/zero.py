@@ -105,6 +105,9 @@ class ShardedDataParallel:
                     self.sym_g = MulticastBuffer(n * 4, self.group, self.device)
                     self.sym_p = MulticastBuffer(n * 2, self.group, self.device)
                     self.g_mc, self.p_mc = self.sym_g.mc_ptr, self.sym_p.mc_ptr
+                    if os.environ.get("COEUS_DP_MC_KERNEL", "1") == "0":
+                        # tuning aid: multicast-bound buffers, plain peer loads in the kernel
+                        self.g_mc = self.p_mc = 0
                 except Exception:
                     ok.fill_(0)
                 dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
@@ -113,7 +116,9 @@ class ShardedDataParallel:
                         if isinstance(b, MulticastBuffer):
                             b.close()
                     self.g_mc = self.p_mc = None
-            if self.g_mc is None:
+            if self.g_mc == 0:
+                self.g_mc = self.p_mc = None
+            elif self.g_mc is None:
                 self.sym_g = SymmetricBuffer(n * 4, self.group, self.device)
                 self.sym_p = SymmetricBuffer(n * 2, self.group, self.device)
             model.rebind(p16=self.sym_p.view(torch.bfloat16, 0, n),
