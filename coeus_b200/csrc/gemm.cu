@@ -80,16 +80,21 @@ constexpr int PULL_SLOT_BYTES = 16384;      // one bulk copy of the all-gather p
 // one thread streams the peers' rows (peer memory -> shared memory -> the local gather buffer).
 // CTA2: two CTAs of a cluster share one 256 x BN tile; each stages its 128 rows of A and half of
 // the B rows, so a stage is 32 KB and six stages fit.
-template <int BN, int COMM = 0, bool CTA2 = false>
+// AUX2 (CTA pairs only): the epilogue that stores two tensors per step (the activation and the
+// kept pre-activation of the fused GELU) gets two pairs of store tiles, paid for with one pipeline
+// stage, so that it no longer waits for its own stores after every 64 columns.
+template <int BN, int COMM = 0, bool CTA2 = false, bool AUX2 = false>
 struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = (CTA2 ? BN / 2 : BN) * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = CTA2 ? 6 : ((BN == 256) ? 4 : 6) - (COMM == 1 ? 1 : 0);
+  static constexpr int STAGES =
+      CTA2 ? (AUX2 ? 5 : 6) : ((BN == 256) ? 4 : 6) - (COMM == 1 ? 1 : 0);
   static constexpr int PULL_SLOTS = COMM == 1 ? STAGE_BYTES / PULL_SLOT_BYTES : 0;
   static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int STAGING_BYTES = AUX2 ? 2 * GEMM_STAGING_BYTES : GEMM_STAGING_BYTES;
   static constexpr int OFF_STAGING = STAGES * STAGE_BYTES;
-  static constexpr int OFF_PULL = OFF_STAGING + GEMM_STAGING_BYTES;
+  static constexpr int OFF_PULL = OFF_STAGING + STAGING_BYTES;
   static constexpr int OFF_BAR = OFF_PULL + PULL_SLOTS * PULL_SLOT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -209,13 +214,14 @@ __device__ __forceinline__ uint64_t ld_acquire_sys_u64_g(const uint64_t* p) {
 // COMM_RS: the result is reduce-scattered by rows.  The epilogue pushes each tile of partial
 // sums straight into the owner rank's receive slot (coalesced peer stores from the staging
 // tile); the owner adds the slots in its next kernel.
-template <int BN, bool A_MN, bool B_MN, int COMM, bool CTA2 = false>
+template <int BN, bool A_MN, bool B_MN, int COMM, bool CTA2 = false, bool AUX2 = false>
 __global__ void __launch_bounds__(COMM == COMM_AG ? GEMM_THREADS + 32 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux,
                  const GemmArgs p) {
   static_assert(!CTA2 || (COMM == COMM_NONE && BN == 256), "CTA pairs: plain 256-wide GEMM only");
-  using Cfg = GemmCfg<BN, COMM, CTA2>;
+  static_assert(!AUX2 || CTA2, "the doubled store tiles exist for CTA pairs");
+  using Cfg = GemmCfg<BN, COMM, CTA2, AUX2>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int TILE_M = CTA2 ? 2 * GEMM_BM : GEMM_BM;     // rows of one (cluster) tile
   const uint32_t cta_rank = CTA2 ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the MMAs
@@ -600,13 +606,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int qs = 0; qs < BN / 64; ++qs) {
           const int colq = n0 + qs * 64;
           if (colq >= p.N) break;
-          const uint32_t buf = aux_staged ? 0u : (step & 1u);
-          const uint32_t s_out = s_staging + buf * 16384;
-          const uint32_t s_aux = s_staging + 16384;
+          const uint32_t buf = AUX2 ? (step & 1u) : (aux_staged ? 0u : (step & 1u));
+          const uint32_t s_out = s_staging + buf * (AUX2 ? 32768 : 16384);
+          const uint32_t s_aux = AUX2 ? s_out + 16384 : s_staging + 16384;
           // the store that last read this tile must be done with it
           if constexpr (COMM != COMM_RS) {
             if (leader) {
-              if (aux_staged) tma_store_wait_read_all();
+              if (aux_staged && !AUX2) tma_store_wait_read_all();
               else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             }
           }
@@ -786,13 +792,13 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 }
 
 // CTA-pair variant: clusters of two CTAs, 256 x 256 tiles.
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool AUX2 = false>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                             const CUtensorMap& taux, const GemmArgs& args, int max_ctas,
                             cudaStream_t stream) {
-  using Cfg = GemmCfg<256, COMM_NONE, true>;
+  using Cfg = GemmCfg<256, COMM_NONE, true, AUX2>;
   static bool configured = false;
-  auto kern = gemm_bf16_kernel<256, A_MN, B_MN, COMM_NONE, true>;
+  auto kern = gemm_bf16_kernel<256, A_MN, B_MN, COMM_NONE, true, AUX2>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
@@ -928,6 +934,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* D, int M, int N, i
     return launch_gemm<BN_, true, true>(ta, tb, td, taux, g, max_ctas, st);                       \
   } while (0)
   if (bn == 256 && pairs) {
+    if (!a_mn && b_mn && tma_store && epi == EPI_GELU && aux_out != nullptr)
+      return launch_gemm_pair<false, true, true>(ta, tb, td, taux, g, max_ctas, st);
     if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(ta, tb, td, taux, g, max_ctas, st);
     if (!a_mn && b_mn) return launch_gemm_pair<false, true>(ta, tb, td, taux, g, max_ctas, st);
     if (a_mn && !b_mn) return launch_gemm_pair<true, false>(ta, tb, td, taux, g, max_ctas, st);
