@@ -30,6 +30,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--clip", type=float, default=None)
+    ap.add_argument("--nvls", action="store_true",
+                    help="reduce in the NVLink switch (multimem) instead of plain peer loads")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -59,7 +61,7 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
-    out = {"ranks": world, "layers": a.layers, "grad_clip": a.clip}
+    out = {"ranks": world, "layers": a.layers, "grad_clip": a.clip, "nvls": a.nvls}
     # ---- one replica without data parallelism
     m0 = DecoderLM(cfg, device=dev, seed=0)
     t0 = Trainer(m0, TrainConfig(learning_rate=3e-4, grad_clip=a.clip))
@@ -70,7 +72,7 @@ def main() -> int:
     torch.cuda.empty_cache()
     # ---- the data-parallel step
     m = DecoderLM(cfg, device=dev, seed=0)
-    dp = ShardedDataParallel(dist.group.WORLD, dev)
+    dp = ShardedDataParallel(dist.group.WORLD, dev, nvls=a.nvls)
     tr = Trainer(m, TrainConfig(learning_rate=3e-4, grad_clip=a.clip), dp=dp)
     for _ in range(3):
         tr.train_step(x, y)

@@ -161,12 +161,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(bar(3 + s), 1);
     }
     mbar_init(bar(5), 1);
-    mbar_init(bar(6), 256);
+    mbar_init(bar(6), 8);      // one arrival per softmax warp
     mbar_init(bar(7), 1);
     mbar_init(bar(8), 1);
-    mbar_init(bar(9), 128);
+    mbar_init(bar(9), 4);      // one arrival per dQ-drain warp
     mbar_init(bar(10), 1);
-    mbar_init(bar(11), 256);
+    mbar_init(bar(11), 8);
     mbar_init(bar(12), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -358,7 +358,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         s_lse[tid] = qi < p.S ? p.lse[stat_base + qi] * 1.4426950408889634f : INFINITY;
         s_dl[tid] = qi < p.S ? p.delta[stat_base + qi] : 0.f;
       }
-      mbar_arrive(bar(11));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(11));
       bool got = mbar_wait(bar(11), it & 1u, abort_flag);
       if (got) got = mbar_wait(bar(5), it & 1u, abort_flag);
       // the buffer pair of this parity was last read by the products of tile it - 2
@@ -410,7 +411,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (tr) tr[it * 8 + 2] = clock64();
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(bar(6));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(6));
       if (tr) tr[it * 8 + 3] = clock64();
     }
     // ---- epilogue: dV and dK of this K/V tile
@@ -497,7 +499,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(bar(9));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(9));
     }
   }
 

@@ -51,7 +51,7 @@ class _ShardedOptState:
 class ShardedDataParallel:
     def __init__(self, group, device, backend: Optional[str] = None,
                  comm_blocks: Optional[int] = None, wait_limit_ms: float = 5000.0,
-                 tail_blocks: Optional[int] = None) -> None:
+                 tail_blocks: Optional[int] = None, nvls: Optional[bool] = None) -> None:
         """``comm_blocks``: thread blocks (of 128 threads) of a bucket kernel that runs beside the
         backward pass: about one per SM, small enough to share the SM with a persistent compute
         CTA; ``tail_blocks``: blocks of the buckets that complete when the backward pass ends and
@@ -70,6 +70,7 @@ class ShardedDataParallel:
         if tail_blocks is None:
             tail_blocks = int(os.environ.get("COEUS_DP_TAIL_BLOCKS", "592"))
         self.comm_blocks, self.tail_blocks = comm_blocks, tail_blocks
+        self.nvls = (os.environ.get("COEUS_DP_NVLS", "0") == "1") if nvls is None else bool(nvls)
         self.wait_limit_ms = wait_limit_ms
         self.model = None
 
@@ -96,8 +97,10 @@ class ShardedDataParallel:
             # multimem.ld_reduce and broadcasts with multimem.st), plain peer mappings otherwise.
             # All ranks must take the same branch, hence the agreement over the group.
             self.g_mc = self.p_mc = None
-            want = self.world > 1 and os.environ.get("COEUS_NVLS", "1") != "0" and \
-                multicast_supported(self.device)
+            # (measured on 8 B200s the two paths are within noise of each other over a whole
+            # step -- 41.4 against 41.5 ms -- and at two ranks the plain path is ahead, so the
+            # multicast path is opt-in: nvls=True or COEUS_DP_NVLS=1)
+            want = self.world > 1 and self.nvls and multicast_supported(self.device)
             ok = torch.tensor([1 if want else 0], device=self.device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
             if int(ok) == 1:

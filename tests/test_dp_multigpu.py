@@ -34,7 +34,8 @@ def _worker(rank, world, port, backend, out, clip=None):
     from coeus_b200.parallel.zero import ShardedDataParallel
     from coeus_b200.train.trainer import TrainConfig, Trainer
     model = DecoderLM(CFG, device=dev, seed=0)
-    dp = ShardedDataParallel(dist.group.WORLD, dev, backend=backend)
+    nvls = backend == "p2p-nvls"      # the same kernel reading through the NVLink multicast mapping
+    dp = ShardedDataParallel(dist.group.WORLD, dev, backend="p2p" if nvls else backend, nvls=nvls)
     tr = Trainer(model, TrainConfig(learning_rate=1e-3, grad_clip=clip), dp=dp)
     gen = torch.Generator().manual_seed(100 + rank)
     batch = torch.randint(0, CFG.vocab_size, (2, 129), generator=gen).to(dev)
@@ -71,6 +72,18 @@ def test_fused_kernel_matches_nccl_collectives():
     # the fraction of entries that moved apart
     assert (d > 5e-4).float().mean() < 0.01, d.max()
     assert (p_ref - p_p2p).abs().max() < 0.05
+
+
+def test_switch_reduced_kernel_matches_nccl_collectives():
+    """The bucket kernel with multimem.ld_reduce / multimem.st (NVLink multicast) against the
+    collective path; falls back to plain peer loads by itself where multicast is unsupported."""
+    l_ref, m_ref, p_ref = _run("collective")
+    l_mc, m_mc, p_mc = _run("p2p-nvls")
+    for a, b in zip(l_ref, l_mc):
+        assert abs(a - b) < 0.05
+    d = (m_ref - m_mc).abs()
+    assert (d > 5e-4).float().mean() < 0.01, d.max()
+    assert (p_ref - p_mc).abs().max() < 0.05
 
 
 def test_gradient_clipping_in_the_fused_step_matches_collectives():
