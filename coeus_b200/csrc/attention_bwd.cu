@@ -16,6 +16,7 @@
 //   warps 10..13 dQ drain (TMEM -> red.global.add)
 #include <algorithm>
 
+#include "attention_bwd.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -23,30 +24,18 @@ namespace cb {
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t ld, uint32_t box_inner, uint32_t box_outer);
+int make_tmap_f32_3d(CUtensorMap* out, void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                     uint64_t ld1, uint64_t ld2, uint32_t box1);
 int sm_count();
 
 constexpr int ATB_BKV = 128;
 constexpr int ATB_THREADS = 448;
 
-struct AttnBwdArgs {
-  int B, S, nh;
-  const float* lse;     // [B, nh, S]
-  const float* delta;   // [B, nh, S]
-  float* dq_acc;        // fp32 [B*S, nh*dh], zero-initialised
-  __nv_bfloat16* dk;    // [B*S, ...] pitch ldd, already offset to the K slice
-  __nv_bfloat16* dv;
-  int ldd;
-  float scale;
-  float scale_log2;
-  int causal;
-  int* status;
-};
-
 // Optional timeline of block 0 (a debugging aid; off unless a trace buffer is registered):
-// [it][0..7] = clock64 at: softmax S^T/dP^T ready, after the first TMEM load, after the maths of
+// [it][0..11] = clock64 at: softmax S^T/dP^T ready, after the first TMEM load, after the maths of
 // both chunks, after the fence+arrive; MMA thread: stage ready, S^T/dP^T issued, P^T ready,
-// dV/dK/dQ issued.
-__device__ long long* g_attn_bwd_trace = nullptr;
+// dV/dK/dQ issued; dQ drain: start, end; MMA thread: previous dQ drained.
+static long long* g_attn_bwd_trace_host = nullptr;
 
 template <int DH>
 struct AttnBwdCfg {
@@ -262,13 +251,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         return true;
       };
       bool ok = wait_all(0, 0, 1020);
-      long long* trace = (blockIdx.x == 0 && lane == 0) ? g_attn_bwd_trace : nullptr;
+      long long* trace = (blockIdx.x == 0 && lane == 0) ? p.trace : nullptr;
       // S^T and dP^T of query tile `it` (needs its Q/dO stage and the S^T/dP^T columns free)
       auto issue_scores = [&](int it) {
         const int st = it & 1;
         if (!wait_all(1 + st, (it >> 1) & 1u, 1021)) return false;
         tc_fence_after();
-        if (trace && it < 32) trace[it * 8 + 4] = clock64();
+        if (trace && it < 32) trace[it * 12 + 4] = clock64();
         const uint64_t bq = dQ_k0 + st * ST_STEP, bdo = dDO_k0 + st * ST_STEP;
         if (elect_one()) {
           // the two products are independent: alternating them keeps two accumulation chains
@@ -285,7 +274,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_commit(bar(5));
         }
         __syncwarp();
-        if (trace && it < 32) trace[it * 8 + 5] = clock64();
+        if (trace && it < 32) trace[it * 12 + 5] = clock64();
         return true;
       };
       if (ok && n_it > 0) ok = issue_scores(0);
@@ -294,7 +283,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // P^T / dS^T of this tile are in shared memory and its S^T / dP^T columns have been read
         if (!wait_all(6, it & 1u, 1022)) { ok = false; break; }
         tc_fence_after();
-        if (trace && it < 32) trace[it * 8 + 6] = clock64();
+        if (trace && it < 32) trace[it * 12 + 6] = clock64();
         // The next tile's scores go first: its softmax then runs while the three products below
         // execute (they read the other P^T / dS^T buffer).
         if (it + 1 < n_it && !issue_scores(it + 1)) { ok = false; break; }
@@ -302,6 +291,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!wait_all(9, (it - 1) & 1u, 1023)) { ok = false; break; }
           tc_fence_after();
         }
+        if (trace && it < 32) trace[it * 12 + 10] = clock64();
         // dV += P^T . dO_i, dK += dS^T . Q_i (contraction over the BQ query rows) and
         // dQ_i = dS . K_j (contraction over the 128 K/V rows): three independent accumulation
         // chains, issued round-robin
@@ -334,7 +324,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_commit(bar(buf ? 12 : 7));      // this P^T / dS^T buffer free
         }
         __syncwarp();
-        if (trace && it < 32) trace[it * 8 + 7] = clock64();
+        if (trace && it < 32) trace[it * 12 + 7] = clock64();
       }
       if (ok && elect_one()) umma_commit(bar(10));
       __syncwarp();
@@ -370,8 +360,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after();
-      long long* tr = (blockIdx.x == 0 && it < 32 && warp == 2 && lane == 0) ? g_attn_bwd_trace : nullptr;
-      if (tr) tr[it * 8 + 0] = clock64();
+      long long* tr = (blockIdx.x == 0 && it < 32 && warp == 2 && lane == 0) ? p.trace : nullptr;
+      if (tr) tr[it * 12 + 0] = clock64();
       const uint32_t sPT = sPTb(it & 1), sDST = sDSTb(it & 1);
       const bool diag = p.causal && (kv0 + BKV - 1 > q0);
       const bool row_dead = kv_idx >= p.S;
@@ -381,7 +371,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(lane_addr + Cfg::ST_COL + c * 32, sv);
         tmem_ld_32x32b_x32(lane_addr + Cfg::DPT_COL + c * 32, dv);
         tmem_ld_wait();
-        if (tr && c == half * (BQ / 64)) tr[it * 8 + 1] = clock64();
+        if (tr && c == half * (BQ / 64)) tr[it * 12 + 1] = clock64();
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -408,12 +398,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                        : "memory");
         }
       }
-      if (tr) tr[it * 8 + 2] = clock64();
+      if (tr) tr[it * 12 + 2] = clock64();
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(6));
-      if (tr) tr[it * 8 + 3] = clock64();
+      if (tr) tr[it * 12 + 3] = clock64();
     }
     // ---- epilogue: dV and dK of this K/V tile
     if (ok) {
@@ -464,6 +454,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after();
+      long long* trq = (blockIdx.x == 0 && it < 32 && warp == 10 && lane == 0) ? p.trace : nullptr;
+      if (trq) trq[it * 12 + 8] = clock64();
       const int q0 = (i_start + it) * BQ;
       if constexpr (DH == 64) {
         const int qi = q0 + r;
@@ -500,6 +492,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before();
       __syncwarp();
+      if (trq) trq[it * 12 + 9] = clock64();
       if (lane == 0) mbar_arrive(bar(9));
     }
   }
@@ -534,7 +527,8 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 // dqkv: bf16 [B*S, 3*nh*dh] (pitch ldd) receiving dQ | dK | dV.  dq_acc: zeroed fp32
 // [B*S, nh*dh] scratch; delta: fp32 [B, nh, S] scratch.
 extern "C" int cb_attn_bwd_set_trace(long long* device_buffer) {
-  return cudaMemcpyToSymbol(cb::g_attn_bwd_trace, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? 0 : -1;
+  cb::g_attn_bwd_trace_host = device_buffer;
+  return 0;
 }
 
 extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const void* v,
@@ -556,6 +550,9 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   if (make_tmap_bf16_2d(&tk, k, H, rows, ldk, 64, ATB_BKV) != 0) return -4;
   if (make_tmap_bf16_2d(&tv, v, H, rows, ldv, 64, ATB_BKV) != 0) return -5;
   if (make_tmap_bf16_2d(&tdo, dO, H, rows, lddo, 64, bq) != 0) return -6;
+  CUtensorMap tdq;
+  if (dh == 64 && make_tmap_f32_3d(&tdq, dq_acc, H, S, B, H, static_cast<uint64_t>(S) * H, 32) != 0)
+    return -7;
   {
     const size_t work = rows * nh * (dh / 8);
     const int blocks = static_cast<int>(std::min<size_t>((work + 255) / 256, sm_count() * 16));
@@ -573,7 +570,8 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal;
   a.status = status;
-  int rc = dh == 64 ? launch_attn_bwd<64>(tq, tk, tv, tdo, a, st)
+  a.trace = g_attn_bwd_trace_host;
+  int rc = dh == 64 ? launch_attn_bwd_dh64(tq, tk, tv, tdo, tdq, a, st)
                     : launch_attn_bwd<128>(tq, tk, tv, tdo, a, st);
   if (rc != 0) return rc;
   {

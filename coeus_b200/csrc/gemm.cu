@@ -759,6 +759,25 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// 3-D fp32 tensor map (inner `d0` contiguous floats, then `d1` rows of pitch ld1 floats, then `d2`
+// slabs of pitch ld2 floats) with a box of 32 floats x box1 rows x 1 slab, 128-byte swizzle: the
+// target of bulk reduce-add stores of an fp32 tile.
+int make_tmap_f32_3d(CUtensorMap* out, void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                     uint64_t ld1, uint64_t ld2, uint32_t box1) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld1 * 4) % 16 != 0 || (ld2 * 4) % 16 != 0)
+    return -2;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {ld1 * 4, ld2 * 4};
+  cuuint32_t box[3] = {32, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {

@@ -148,6 +148,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src,
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+// 3-D tiled reduce-add shared -> global (the element type comes from the tensor map; bulk group
+// completion).  Coordinates must not be negative; rows beyond the tensor are dropped.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, uint32_t src, int x, int y,
+                                                  int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // Untiled bulk copies (addresses and size multiples of 16 bytes).  The source of the load may be
 // another GPU's memory (a peer mapping): this is a plain bulk load, no cluster multicast.
 __device__ __forceinline__ void bulk_load_g2s(uint32_t dst, const void* src, uint32_t bytes,

@@ -226,6 +226,28 @@ def test_attention_fwd_bwd(dh, causal, S):
         assert err < 0.02 * ref.float().abs().max().item() + 0.03, (name, err)
 
 
+@pytest.mark.parametrize("dh,S,causal", [(64, 1152, True), (64, 1100, True), (64, 640, False),
+                                          (128, 1152, True)])
+def test_attention_bwd_many_query_tiles(dh, S, causal):
+    """Nine query tiles per K/V tile: every ring (query stages, dS^T and dQ buffers) wraps around
+    several times, with a ragged last tile in one case."""
+    torch.manual_seed(18)
+    B, nh = 1, 2
+    H = nh * dh
+    qkv = _bf(torch.randn(B * S, 3 * H, device=DEV))
+    q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+    o, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal)
+    do = _bf(torch.randn(B * S, H, device=DEV))
+    dq, dk, dv = A.attention_bwd(do, q, k, v, o, lse, B, S, nh, dh, causal=causal)
+    dqr, dkr, dvr = A.attention_bwd(do.cpu(), q.cpu(), k.cpu(), v.cpu(), o.cpu(), lse.cpu(), B, S,
+                                    nh, dh, causal=causal)
+    torch.cuda.synchronize()
+    _status_clean()
+    for got, ref, name in ((dq, dqr, "dq"), (dk, dkr, "dk"), (dv, dvr, "dv")):
+        err = (got.float().cpu() - ref.float()).abs().max().item()
+        assert err < 0.02 * ref.float().abs().max().item() + 0.03, (name, err)
+
+
 @pytest.mark.parametrize("dh,nh,nkv,B,S,causal", [
     (64, 4, 4, 1, 384, True),       # three query tiles: the last pair has one tile only
     (64, 16, 16, 4, 1024, True),    # 256 work items: persistent CTAs take several each
