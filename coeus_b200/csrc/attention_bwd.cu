@@ -544,7 +544,7 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   const uint64_t rows = static_cast<uint64_t>(B) * S;
   // every argument check (the tensor maps included) comes before the first launch, so that a
   // refused call has enqueued nothing
-  const uint32_t bq = dh == 64 ? 128 : 64;
+  const uint32_t bq = 64;   // rows per query / dO box: a tile (dh 128) or half a tile (dh 64)
   CUtensorMap tq, tk, tv, tdo;
   if (make_tmap_bf16_2d(&tq, q, H, rows, ldq, 64, bq) != 0) return -3;
   if (make_tmap_bf16_2d(&tk, k, H, rows, ldk, 64, ATB_BKV) != 0) return -4;

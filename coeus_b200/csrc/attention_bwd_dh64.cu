@@ -1,25 +1,29 @@
-// Flash-style attention backward for head dimension 64, pipelined over the two halves of a query
-// tile.  One CTA owns one (batch, head, 128-row K/V tile) and streams the 128-row query tiles
-// that attend to it, in the transposed orientation (K/V rows on the tensor-memory lanes):
+// Flash-style attention backward for head dimension 64: persistent CTAs, pipelined over the two
+// halves of a query tile.  A work item is one (batch, head, 128-row K/V tile); a CTA takes items
+// from the list sorted by length (heavy and light ends alternate, see BwdWalk) and streams the
+// 128-row query tiles that attend to the item's K/V tile, in the transposed orientation (K/V rows
+// on the tensor-memory lanes):
 //   S^T  = K_j . Q_i^T          dP^T = V_j . dO_i^T
 //   P^T  = exp2(S^T * c - LSE_i)       dS^T = P^T o (dP^T - delta_i)
 //   dV_j += P^T . dO_i          dK_j += dS^T . Q_i          dQ_i = dS . K_j
 // What distinguishes it from the generic kernel (attention_bwd.cu):
 //  * a query tile is handled as two halves of 64 query columns, each with its own S^T / dP^T
-//    columns in tensor memory and its own softmax warpgroup; while one half's products and next
-//    scores run on the tensor cores the other half's softmax runs, so neither side idles for the
-//    whole length of the other;
+//    columns in tensor memory, its own softmax warpgroup and its own query / dO ring slots; while
+//    one half's products and next scores run on the tensor cores the other half's softmax runs;
 //  * P^T and dS^T are written back as packed bf16 over their own score columns in tensor memory
 //    and feed dV and dK as tensor-memory A operands: no shared-memory round trip for P^T at all,
 //    dS^T goes to shared memory only for dQ (where it is the transposed operand);
-//  * dQ is double-buffered in tensor memory, so its drain (bulk reduce-adds into the fp32
-//    accumulation buffer shared by all K/V tiles) overlaps the next tile;
+//  * dQ is double-buffered in tensor memory and leaves through a swizzled staging tile and bulk
+//    reduce-adds into the fp32 accumulation buffer shared by all K/V tiles;
 //  * the tensor pipe executes one thread's MMAs in issue order, which is what lets the scores of
-//    tile i+1 overwrite the columns P^T / dS^T of tile i were read from without a barrier.
-//   warp 0        TMA producer (K_j, V_j once; Q_i, dO_i through a 3-stage ring)
+//    the next step overwrite the columns P^T / dS^T of this step were read from without a barrier;
+//  * the steps of consecutive items form one stream: the next item's K/V tile is loaded (second
+//    buffer) and its first scores are issued while the current item finishes, and the dV / dK
+//    epilogue of an item runs after the softmax of the next item's first step.
+//   warp 0        TMA producer (K_j, V_j per item, two buffers; Q_i, dO_i per half, two stages)
 //   warp 1        MMA issuer          (warps 2, 3 idle: register donors)
-//   warps 4..7    softmax / dS of the first half; afterwards the dV epilogue
-//   warps 8..11   softmax / dS of the second half; afterwards the dK epilogue
+//   warps 4..7    softmax / dS of the first half; dV epilogue
+//   warps 8..11   softmax / dS of the second half; dK epilogue
 //   warps 12..15  dQ drain (TMEM -> shared memory -> bulk reduce-add into the fp32 accumulator)
 // delta_i = rowsum(dO_i o O_i) comes from a pre-kernel, a post-kernel scales and casts dQ (both in
 // attention_bwd.cu).  The reference (plugins/model-transformer/src/lib.rs:300-372) computes the
@@ -31,20 +35,23 @@
 #include "ptx.cuh"
 
 namespace cb {
+
+int sm_count();
+
 namespace {
 
 struct B64 {
   static constexpr int DH = 64, BQ = 128, BKV = 128, HQ = 64;
   static constexpr int THREADS = 512;
-  static constexpr int NST = 3;                           // Q_i / dO_i stages
+  static constexpr int NST = 2;                           // Q_i / dO_i stages
   static constexpr int KV_BYTES = BKV * DH * 2;           // K_j or V_j
   static constexpr int Q_BYTES = BQ * DH * 2;             // Q_i or dO_i
+  static constexpr int HALF_BYTES = HQ * DH * 2;          // 64 query rows of Q_i or dO_i
   static constexpr int ST_BYTES = 2 * Q_BYTES;            // one stage: Q_i | dO_i
   static constexpr int DST_BYTES = BKV * BQ * 2;          // dS^T of one tile
-  static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = KV_BYTES;
-  static constexpr int OFF_Q = 2 * KV_BYTES;
-  static constexpr int OFF_DST = OFF_Q + NST * ST_BYTES;  // two buffers (tile parity)
+  static constexpr int OFF_K = 0;                         // two buffers of (K_j | V_j)
+  static constexpr int OFF_Q = 2 * 2 * KV_BYTES;
+  static constexpr int OFF_DST = OFF_Q + NST * ST_BYTES;  // two buffers (step parity)
   static constexpr int OFF_DQS = OFF_DST + 2 * DST_BYTES;   // dQ staging: per drain warp two boxes
                                                             // of [32 rows][32 floats], swizzled
   static constexpr int DQS_BYTES = BQ * DH * 4;
@@ -57,29 +64,70 @@ struct B64 {
   static constexpr int DV_COL = 256, DK_COL = 320, DQ_COL = 384;
   static constexpr int TMEM_COLS = 512;
   enum {
-    B_KV = 0,
-    B_QF = 1,                // + stage: Q_i / dO_i landed
-    B_QE = B_QF + NST,       // + stage: stage free
-    B_SF = B_QE + NST,       // + half: S^T / dP^T of the half complete
+    B_KVF = 0,               // + buffer: K_j / V_j landed
+    B_KVE = 2,               // + buffer: buffer free (the item's last dQ product completed)
+    B_QF = 4,                // + 2 stage + half: the half's Q_i / dO_i rows landed
+    B_QE = B_QF + 2 * NST,   // + 2 stage + half: slot free
+    B_SF = B_QE + 2 * NST,   // + half: S^T / dP^T of the half complete
     B_PF = B_SF + 2,         // + half: P^T / dS^T of the half written (4 warps)
     B_STF = B_PF + 2,        // + half: the half's lse / delta in shared memory (4 warps)
     B_DF = B_STF + 2,        // + parity: dS^T buffer free (its dQ product completed)
     B_DQF = B_DF + 2,        // + parity: dQ complete in tensor memory
     B_DQE = B_DQF + 2,       // + parity: dQ drained (4 warps)
-    B_DONE = B_DQE + 2,
+    B_DONE = B_DQE + 2,      // the item's dV / dK are complete
+    B_EPI,                   // dV / dK of the item have left tensor memory (8 warps)
     N_BARS
   };
   static_assert(N_BARS * 8 + 8 <= 256, "barrier block");
 };
 
-// One 32-column chunk of a half: p = exp2(s c - lse), ds = p (dp - delta), both packed to bf16.
+// The items of one CTA in the order every role walks them.  Items are sorted by the number of
+// query tiles (K/V tile 0 sees all of them under a causal mask); CTA c takes one item of every
+// wave of gridDim.x items, counted from the front of even waves and from the back of odd ones.
+struct BwdWalk {
+  int wave;
+  int b, h, j, n_it;
+  bool valid;
+  __device__ int i_start(const AttnBwdArgs& p) const { return p.causal ? j : 0; }   // BQ == BKV
+  __device__ void init(const AttnBwdArgs& p) {
+    wave = -1;
+    valid = true;
+    next(p);
+  }
+  __device__ void next(const AttnBwdArgs& p) {
+    const int n_bh = p.B * p.nh;
+    const int n_items = n_bh * ((p.S + B64::BKV - 1) / B64::BKV);
+    while (true) {
+      ++wave;
+      if (wave * static_cast<int>(gridDim.x) >= n_items) { valid = false; return; }
+      const int c = (wave & 1) ? static_cast<int>(gridDim.x - 1 - blockIdx.x)
+                               : static_cast<int>(blockIdx.x);
+      const int i = wave * static_cast<int>(gridDim.x) + c;
+      if (i >= n_items) continue;
+      const int bh = i % n_bh;
+      j = i / n_bh;
+      b = bh / p.nh;
+      h = bh % p.nh;
+      n_it = (p.S + B64::BQ - 1) / B64::BQ - (p.causal ? j : 0);
+      return;
+    }
+  }
+  // the item after this one (a temporary: only the roles' last step of an item looks ahead)
+  __device__ BwdWalk peek(const AttnBwdArgs& p) const {
+    BwdWalk t = *this;
+    t.next(p);
+    return t;
+  }
+};
+
+// One 16-column chunk of a half: p = exp2(s c - lse), ds = p (dp - delta), both packed to bf16.
 // `lim` > query index hides the element (causal mask and rows beyond the sequence).
 template <bool MASK>
 __device__ __forceinline__ void bwd_chunk(const uint32_t* sv, const uint32_t* dv,
                                           const float* s_lse, const float* s_dl, float c, int lim,
                                           int q_first, uint32_t* pk, uint32_t* dk) {
 #pragma unroll
-  for (int e = 0; e < 32; e += 4) {
+  for (int e = 0; e < 16; e += 4) {
     const float4 L = *reinterpret_cast<const float4*>(s_lse + e);
     const float4 D = *reinterpret_cast<const float4*>(s_dl + e);
     float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c, -L.x));
@@ -103,6 +151,7 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* sv, const uint32_t* dv
   }
 }
 
+// tmQ / tmdO: boxes of 64 rows (one half of a query tile); tmK / tmV: boxes of 128 rows.
 __global__ void __launch_bounds__(B64::THREADS, 1)
 attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -118,25 +167,16 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* s_stat = reinterpret_cast<float*>(smem + C::OFF_STAT);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.trace) p.trace[14] = clock64();
   if ((sbase & 1023u) != 0u) {
     if (threadIdx.x == 0) record_status(p.status, ST_BAD_ARG, 1100);
     return;
   }
-  const int bh = blockIdx.x % (p.B * p.nh);
-  const int j = blockIdx.x / (p.B * p.nh);  // early K/V tiles see the most queries: first
-  const int b = bh / p.nh, h = bh % p.nh;
-  const int kv0 = j * BKV;
-  const int n_q_tiles = (p.S + BQ - 1) / BQ;
-  const int i_start = p.causal ? j : 0;      // BQ == BKV
-  const int n_it = n_q_tiles - i_start;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(C::B_KV), 1);
-    for (int s = 0; s < NST; ++s) {
-      mbar_init(bar(C::B_QF + s), 1);
-      mbar_init(bar(C::B_QE + s), 1);
-    }
     for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(C::B_KVF + s), 1);
+      mbar_init(bar(C::B_KVE + s), 1);
       mbar_init(bar(C::B_SF + s), 1);
       mbar_init(bar(C::B_PF + s), 4);      // one arrival per softmax warp of the half
       mbar_init(bar(C::B_STF + s), 4);
@@ -144,7 +184,12 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(bar(C::B_DQF + s), 1);
       mbar_init(bar(C::B_DQE + s), 4);     // one arrival per dQ-drain warp
     }
+    for (int s = 0; s < 2 * NST; ++s) {
+      mbar_init(bar(C::B_QF + s), 1);
+      mbar_init(bar(C::B_QE + s), 1);
+    }
     mbar_init(bar(C::B_DONE), 1);
+    mbar_init(bar(C::B_EPI), 8);           // one arrival per softmax warp
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -161,47 +206,72 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t sK = sbase + C::OFF_K, sV = sbase + C::OFF_V;
+  auto sK = [&](int kb) { return sbase + C::OFF_K + kb * 2 * C::KV_BYTES; };
+  auto sV = [&](int kb) { return sK(kb) + C::KV_BYTES; };
   auto sDST = [&](int buf) { return sbase + C::OFF_DST + buf * C::DST_BYTES; };
   auto sQ = [&](int st) { return sbase + C::OFF_Q + st * C::ST_BYTES; };
   auto sDO = [&](int st) { return sQ(st) + C::Q_BYTES; };
-  const int row0 = b * p.S;
 
   // 512 threads start with 128 registers each.  The first warpgroup (producer, MMA issue) and the
-  // dQ-drain warpgroup hand registers to the two softmax warpgroups, which keep both chunks of a
-  // half (S^T and dP^T, 128 values) in flight: 128 * (56 + 88 + 184 + 184) = 65536.
+  // dQ-drain warpgroup hand registers to the two softmax warpgroups: 128 * (104 + 104 + 152 + 152)
+  // = 65536.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
     if (warp == 0) {
       // -------------------------------------------------------------- producer
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar(C::B_KV), 2 * C::KV_BYTES);
-        tma_load_2d(sK, &tmK, bar(C::B_KV), h * DH, row0 + kv0);
-        tma_load_2d(sV, &tmV, bar(C::B_KV), h * DH, row0 + kv0);
-        int issued = 0;
-        for (int it = 0; it < n_it; ++it) {
-          const int st = it % NST;
-          if (!mbar_wait(bar(C::B_QE + st), ((it / NST) & 1u) ^ 1u, abort_flag)) {
+        uint32_t n = 0, g = 0;        // items and steps so far
+        uint32_t q_issued = 0;        // half-tile loads issued (two per step)
+        uint32_t kv_issued = 0;
+        bool ok = true;
+        BwdWalk w;
+        for (w.init(p); w.valid && ok; w.next(p), ++n) {
+          const int kb = n & 1;
+          const int row0 = w.b * p.S;
+          if (!mbar_wait(bar(C::B_KVE + kb), ((n >> 1) & 1u) ^ 1u, abort_flag)) {
             record_status(p.status, ST_WAIT_TIMEOUT, 1110);
             break;
           }
-          const int qrow = row0 + (i_start + it) * BQ;
-          mbar_arrive_expect_tx(bar(C::B_QF + st), C::ST_BYTES);
-          tma_load_2d(sQ(st), &tmQ, bar(C::B_QF + st), h * DH, qrow);
-          tma_load_2d(sDO(st), &tmdO, bar(C::B_QF + st), h * DH, qrow);
-          ++issued;
-        }
-        if (*abort_flag) {
-          // let the copies already in flight land before shared memory is released
-          const uint64_t t0 = globaltimer_ns();
-          for (int i = max(0, issued - NST); i < issued; ++i) {
-            while (!mbar_try_wait(bar(C::B_QF + i % NST), (i / NST) & 1u)) {
-              if (globaltimer_ns() - t0 > 200000000ull) break;
+          mbar_arrive_expect_tx(bar(C::B_KVF + kb), 2 * C::KV_BYTES);
+          tma_load_2d(sK(kb), &tmK, bar(C::B_KVF + kb), w.h * DH, row0 + w.j * BKV);
+          tma_load_2d(sV(kb), &tmV, bar(C::B_KVF + kb), w.h * DH, row0 + w.j * BKV);
+          ++kv_issued;
+          for (int it = 0; it < w.n_it && ok; ++it, ++g) {
+            const int st = g % NST;
+            const int qrow = row0 + (w.i_start(p) + it) * BQ;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const int slot = 2 * st + hf;
+              if (!mbar_wait(bar(C::B_QE + slot), ((g / NST) & 1u) ^ 1u, abort_flag)) {
+                record_status(p.status, ST_WAIT_TIMEOUT, 1111);
+                ok = false;
+                break;
+              }
+              mbar_arrive_expect_tx(bar(C::B_QF + slot), 2 * C::HALF_BYTES);
+              tma_load_2d(sQ(st) + hf * C::HALF_BYTES, &tmQ, bar(C::B_QF + slot), w.h * DH,
+                          qrow + hf * HQ);
+              tma_load_2d(sDO(st) + hf * C::HALF_BYTES, &tmdO, bar(C::B_QF + slot), w.h * DH,
+                          qrow + hf * HQ);
+              ++q_issued;
             }
           }
-          while (!mbar_try_wait(bar(C::B_KV), 0)) {
-            if (globaltimer_ns() - t0 > 200000000ull) break;
+        }
+        if (*abort_flag) {
+          // let the copies already in flight land before shared memory is released: the last use
+          // of every ring slot and of both K/V buffers
+          const uint64_t t0 = globaltimer_ns();
+          auto settle = [&](int b_idx, uint32_t parity) {
+            while (!mbar_try_wait(bar(b_idx), parity)) {
+              if (globaltimer_ns() - t0 > 200000000ull) return;
+            }
+          };
+          const uint32_t q_first = q_issued > 2u * NST ? q_issued - 2u * NST : 0u;
+          for (uint32_t u = q_first; u < q_issued; ++u) {
+            const uint32_t step = u >> 1;
+            settle(C::B_QF + 2 * (step % NST) + (u & 1u), (step / NST) & 1u);
           }
+          for (uint32_t u = kv_issued > 2u ? kv_issued - 2u : 0u; u < kv_issued; ++u)
+            settle(C::B_KVF + (u & 1u), (u >> 1) & 1u);
         }
       }
       __syncwarp();
@@ -209,38 +279,47 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // -------------------------------------------------------------- MMA issuer
       // The whole warp runs the control flow (addresses and descriptors stay warp-uniform); one
       // elected lane issues.  Descriptors are built once; a product only adds constants to their
-      // address field.
+      // address field.  The waits poll: this warp's reaction time is on the critical path.
       constexpr uint32_t idesc_sc = umma_idesc_bf16(BKV, HQ, 0, 0);   // S^T, dP^T of a half
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BKV, DH, 0, 1);   // dV, dK (A in tensor memory)
       constexpr uint32_t idesc_dq = umma_idesc_bf16(BQ, DH, 1, 1);    // dQ
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-      const uint64_t dK_k = umma_desc_sw128(sK, 16, 1024), dV_k = umma_desc_sw128(sV, 16, 1024);
-      const uint64_t dK_mn = umma_desc_sw128(sK, BKV * 128, 1024);
-      const uint64_t dQ_k0 = umma_desc_sw128(sQ(0), 16, 1024);
-      const uint64_t dDO_k0 = umma_desc_sw128(sDO(0), 16, 1024);
-      const uint64_t dQ_mn0 = umma_desc_sw128(sQ(0), BQ * 128, 1024);
-      const uint64_t dDO_mn0 = umma_desc_sw128(sDO(0), BQ * 128, 1024);
-      const uint64_t dDST_mn0 = umma_desc_sw128(sDST(0), BKV * 128, 1024);
-      constexpr uint64_t ST_STEP = C::ST_BYTES >> 4;       // stage pitch
-      constexpr uint64_t BUF_STEP = C::DST_BYTES >> 4;     // dS^T buffer pitch
-      constexpr uint64_t HALF_STEP = (HQ * 128) >> 4;      // 64 query rows further in a Q / dO tile
+      // every operand descriptor is this one plus compile-time constants (offset in the address
+      // field; the leading-dimension field switched from the K-major to the MN-major value)
+      const uint64_t d_base = umma_desc_sw128(sbase, 16, 1024);
+      constexpr uint64_t MN = static_cast<uint64_t>(((BKV * 128) >> 4) - 1) << 16;
+      static_assert(BKV == BQ, "one MN-major leading dimension for K, Q, dO and dS^T tiles");
+      const uint64_t dK_k0 = d_base + (C::OFF_K >> 4);
+      const uint64_t dV_k0 = d_base + ((C::OFF_K + C::KV_BYTES) >> 4);
+      const uint64_t dK_mn0 = dK_k0 + MN;
+      const uint64_t dQ_k0 = d_base + (C::OFF_Q >> 4);
+      const uint64_t dDO_k0 = d_base + ((C::OFF_Q + C::Q_BYTES) >> 4);
+      const uint64_t dQ_mn0 = dQ_k0 + MN;
+      const uint64_t dDO_mn0 = dDO_k0 + MN;
+      const uint64_t dDST_mn0 = d_base + (C::OFF_DST >> 4) + MN;
+      constexpr uint64_t KB_STEP = (2 * C::KV_BYTES) >> 4;  // K/V buffer pitch
+      constexpr uint64_t ST_STEP = C::ST_BYTES >> 4;        // stage pitch
+      constexpr uint64_t BUF_STEP = C::DST_BYTES >> 4;      // dS^T buffer pitch
+      constexpr uint64_t HALF_STEP = C::HALF_BYTES >> 4;    // 64 query rows further in a tile
       auto wait_all = [&](int b_idx, uint32_t parity, int where) {
-        const bool got = mbar_wait(bar(b_idx), parity, abort_flag);
+        const bool got = mbar_wait_poll(bar(b_idx), parity, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
           return false;
         }
         return true;
       };
-      // S^T and dP^T of half hf of the tile in stage st (K-major operands, contraction over dh)
-      auto scores = [&](int hf, int st) {
+      // S^T and dP^T of half hf of the tile in stage st against K/V buffer kb (K-major operands,
+      // contraction over dh)
+      auto scores = [&](int hf, int st, int kb) {
         const uint64_t bq = dQ_k0 + st * ST_STEP + hf * HALF_STEP;
         const uint64_t bdo = dDO_k0 + st * ST_STEP + hf * HALF_STEP;
+        const uint64_t ak = dK_k0 + kb * KB_STEP, av = dV_k0 + kb * KB_STEP;
         const uint32_t s_col = tmem_u + hf * 128, d_col = s_col + 64;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-          umma_bf16_ss(s_col, dK_k + 2 * kk, bq + 2 * kk, idesc_sc, kk > 0 ? 1u : 0u);
-          umma_bf16_ss(d_col, dV_k + 2 * kk, bdo + 2 * kk, idesc_sc, kk > 0 ? 1u : 0u);
+          umma_bf16_ss(s_col, ak + 2 * kk, bq + 2 * kk, idesc_sc, kk > 0 ? 1u : 0u);
+          umma_bf16_ss(d_col, av + 2 * kk, bdo + 2 * kk, idesc_sc, kk > 0 ? 1u : 0u);
         }
         umma_commit(bar(C::B_SF + hf));
       };
@@ -254,157 +333,118 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           umma_bf16_ts(tmem_u + C::DV_COL, pt + kk * 8, bdo + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
           umma_bf16_ts(tmem_u + C::DK_COL, dst + kk * 8, bq + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
         }
+        umma_commit(bar(C::B_QE + 2 * st + hf));       // the half's Q_i / dO_i rows are free
       };
       long long* trace = (blockIdx.x == 0 && lane == 0) ? p.trace : nullptr;
-      bool ok = wait_all(C::B_KV, 0, 1120);
-      if (ok) ok = wait_all(C::B_QF, 0, 1121);
+      uint32_t n = 0, g = 0;
+      BwdWalk w;
+      w.init(p);
+      bool ok = w.valid;
+      if (ok) ok = wait_all(C::B_KVF, 0, 1120);
+      if (ok) ok = wait_all(C::B_QF + 0, 0, 1121);
+      if (ok) ok = wait_all(C::B_QF + 1, 0, 1121);
       if (ok) {
         tc_fence_after();
+        if (trace) trace[16 + 14] = clock64();
         if (elect_one()) {
-          scores(0, 0);
-          scores(1, 0);
+          scores(0, 0, 0);
+          scores(1, 0, 0);
         }
         __syncwarp();
       }
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it % NST, buf = it & 1;
-        const int nst = (it + 1) % NST;
-        const bool more = it + 1 < n_it;
-        // ---- first half: its products, then the next tile's scores over the same columns
-        if (!wait_all(C::B_PF + 0, it & 1u, 1122)) { ok = false; break; }
-        if (more && !wait_all(C::B_QF + nst, ((it + 1) / NST) & 1u, 1123)) { ok = false; break; }
-        tc_fence_after();
-        if (trace && it < 16) trace[it * 16 + 6] = clock64();
-        if (elect_one()) {
-          products(0, st, it > 0 ? 1u : 0u);
-          if (more) scores(0, nst);
-        }
-        __syncwarp();
-        if (trace && it < 16) trace[it * 16 + 7] = clock64();
-        // ---- second half
-        if (!wait_all(C::B_PF + 1, it & 1u, 1124)) { ok = false; break; }
-        tc_fence_after();
-        if (trace && it < 16) trace[it * 16 + 8] = clock64();
-        if (elect_one()) {
-          products(1, st, 1u);
-          umma_commit(bar(C::B_QE + st));        // Q_i / dO_i stage free
-          if (more) scores(1, nst);
-        }
-        __syncwarp();
-        if (trace && it < 16) trace[it * 16 + 9] = clock64();
-        // ---- dQ_i = dS . K_j over the whole tile, into the dQ buffer of this parity
-        if (it >= 2) {
-          if (!wait_all(C::B_DQE + buf, ((it >> 1) - 1) & 1u, 1125)) { ok = false; break; }
+      while (ok && w.valid) {
+        const bool has_next = w.peek(p).valid;
+        const int kb = n & 1;
+        for (int it = 0; it < w.n_it && ok; ++it, ++g) {
+          const int st = g % NST, buf = g & 1;
+          const int nst = (g + 1) % NST;
+          const bool last = it + 1 == w.n_it;
+          const bool more = !last || has_next;
+          const int nkb = last ? (n + 1) & 1 : kb;
+          const uint32_t nq_par = ((g + 1) / NST) & 1u;
+          // ---- first half: its products, then the next step's scores over the same columns
+          if (!wait_all(C::B_PF + 0, g & 1u, 1122)) { ok = false; break; }
+          // the first products of an item overwrite dV / dK: the previous item's must have left
+          if (it == 0 && n > 0 && !wait_all(C::B_EPI, (n - 1) & 1u, 1126)) { ok = false; break; }
+          if (more) {
+            if (last && !wait_all(C::B_KVF + nkb, ((n + 1) >> 1) & 1u, 1127)) { ok = false; break; }
+            if (!wait_all(C::B_QF + 2 * nst, nq_par, 1123)) { ok = false; break; }
+          }
           tc_fence_after();
-        }
-        if (trace && it < 16) trace[it * 16 + 10] = clock64();
-        if (elect_one()) {
-          const uint64_t a = dDST_mn0 + buf * BUF_STEP;
-          const uint32_t d = tmem_u + C::DQ_COL + buf * DH;
+          if (trace && g < 16) trace[g * 16 + 6] = clock64();
+          if (elect_one()) {
+            products(0, st, it > 0 ? 1u : 0u);
+            if (more) scores(0, nst, nkb);
+          }
+          __syncwarp();
+          if (trace && g < 16) trace[g * 16 + 7] = clock64();
+          // ---- second half
+          if (!wait_all(C::B_PF + 1, g & 1u, 1124)) { ok = false; break; }
+          if (more && !wait_all(C::B_QF + 2 * nst + 1, nq_par, 1128)) { ok = false; break; }
+          tc_fence_after();
+          if (trace && g < 16) trace[g * 16 + 8] = clock64();
+          if (elect_one()) {
+            products(1, st, 1u);
+            if (more) scores(1, nst, nkb);
+          }
+          __syncwarp();
+          if (trace && g < 16) trace[g * 16 + 9] = clock64();
+          // ---- dQ_i = dS . K_j over the whole tile, into the dQ buffer of this parity
+          if (g >= 2) {
+            if (!wait_all(C::B_DQE + buf, ((g >> 1) - 1) & 1u, 1125)) { ok = false; break; }
+            tc_fence_after();
+          }
+          if (trace && g < 16) trace[g * 16 + 10] = clock64();
+          if (elect_one()) {
+            const uint64_t a = dDST_mn0 + buf * BUF_STEP;
+            const uint64_t bk = dK_mn0 + kb * KB_STEP;
+            const uint32_t d = tmem_u + C::DQ_COL + buf * DH;
 #pragma unroll
-          for (int kk = 0; kk < BKV / 16; ++kk)
-            umma_bf16_ss(d, a + 128 * kk, dK_mn + 128 * kk, idesc_dq, kk > 0 ? 1u : 0u);
-          umma_commit(bar(C::B_DQF + buf));
-          umma_commit(bar(C::B_DF + buf));
+            for (int kk = 0; kk < BKV / 16; ++kk)
+              umma_bf16_ss(d, a + 128 * kk, bk + 128 * kk, idesc_dq, kk > 0 ? 1u : 0u);
+            umma_commit(bar(C::B_DQF + buf));
+            umma_commit(bar(C::B_DF + buf));
+            if (last) {
+              umma_commit(bar(C::B_KVE + kb));   // nothing reads this K/V buffer any more
+              umma_commit(bar(C::B_DONE));       // dV / dK of the item are complete
+            }
+          }
+          __syncwarp();
+          if (trace && g < 16) trace[g * 16 + 11] = clock64();
         }
-        __syncwarp();
-        if (trace && it < 16) trace[it * 16 + 11] = clock64();
+        w.next(p);
+        ++n;
       }
-      if (ok && elect_one()) umma_commit(bar(C::B_DONE));
-      __syncwarp();
     }
   } else if (warp < 12) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;" ::: "memory");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 152;" ::: "memory");
     // ---------------------------------------------------------------- softmax / dS of one half
     const int hf = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;        // K/V row within the tile = tensor-memory lane
-    const int kv_idx = kv0 + r;
     const int gt = threadIdx.x - 128 - hf * 128;   // 0..127 within the half's warpgroup
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + hf * 128, d_addr = s_addr + 64;
-    const size_t stat_base = (static_cast<size_t>(b) * p.nh + h) * p.S;
     const float c = p.scale_log2;
     // the thread's share of a tile's statistics: lse (times log2 e) of one query column for the
     // first 64 threads, delta of one column for the others
-    auto load_stat = [&](int it) {
-      const int qi = (i_start + it) * BQ + hf * HQ + (gt & 63);
+    auto load_stat = [&](const BwdWalk& w, int it) {
+      const size_t stat_base = (static_cast<size_t>(w.b) * p.nh + w.h) * p.S;
+      const int qi = (w.i_start(p) + it) * BQ + hf * HQ + (gt & 63);
       if (gt < 64) return qi < p.S ? p.lse[stat_base + qi] * 1.4426950408889634f : INFINITY;
       return qi < p.S ? p.delta[stat_base + qi] : 0.f;
     };
-    float stat_next = load_stat(0);
-    bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int q0 = (i_start + it) * BQ;
-      float* s_lse = s_stat + (it & 1) * 2 * BQ + hf * HQ;
-      float* s_dl = s_lse + BQ;
-      (gt < 64 ? s_lse : s_dl)[gt & 63] = stat_next;
-      if (it + 1 < n_it) stat_next = load_stat(it + 1);   // lands during this tile's work
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::B_STF + hf));
-      bool got = mbar_wait(bar(C::B_STF + hf), it & 1u, abort_flag);
-      if (got) got = mbar_wait(bar(C::B_SF + hf), it & 1u, abort_flag);
-      // the dS^T buffer of this parity was last read by the dQ product of tile it - 2
-      if (got && it > 1) got = mbar_wait(bar(C::B_DF + (it & 1)), ((it >> 1) - 1) & 1u, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1130);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      long long* tr = (blockIdx.x == 0 && it < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
-      if (tr) tr[it * 16 + hf * 3] = clock64();
-      const bool mask = (p.causal && kv0 + BKV - 1 > q0) || (kv0 + BKV > p.S);
-      const int lim = kv_idx >= p.S ? INT_MAX : (p.causal ? kv_idx : INT_MIN);
-      // dS^T in shared memory: two groups of 64 query columns, each [128 K/V rows][128 bytes],
-      // 128-byte swizzled (the layout the dQ product reads as a transposed A operand)
-      const uint32_t srow = sDST(it & 1) + hf * (BKV * 128) + r * 128;
-      uint32_t s0[32], d0[32], s1[32], d1[32];
-      tmem_ld_32x32b_x32(s_addr, s0);
-      tmem_ld_32x32b_x32(d_addr, d0);
-      tmem_ld_wait();
-      tmem_ld_32x32b_x32(s_addr + 32, s1);     // in flight during the first chunk's arithmetic
-      tmem_ld_32x32b_x32(d_addr + 32, d1);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t pk[16], dk[16];
-        const uint32_t* sv = ch ? s1 : s0;
-        const uint32_t* dv = ch ? d1 : d0;
-        if (ch) tmem_ld_wait();
-        if (mask)
-          bwd_chunk<true>(sv, dv, s_lse + ch * 32, s_dl + ch * 32, c, lim, q0 + hf * HQ + ch * 32, pk, dk);
-        else
-          bwd_chunk<false>(sv, dv, s_lse + ch * 32, s_dl + ch * 32, c, lim, 0, pk, dk);
-        tmem_st_32x32b_x16(s_addr + ch * 16, pk);
-        tmem_st_32x32b_x16(d_addr + ch * 16, dk);
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t sw = static_cast<uint32_t>((ch * 4 + g) ^ (r & 7)) << 4;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw),
-                       "r"(dk[4 * g]), "r"(dk[4 * g + 1]), "r"(dk[4 * g + 2]), "r"(dk[4 * g + 3])
-                       : "memory");
-        }
-      }
-      if (tr) tr[it * 16 + hf * 3 + 1] = clock64();
-      tmem_st_wait();
-      fence_proxy_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::B_PF + hf));
-      if (tr) tr[it * 16 + hf * 3 + 2] = clock64();
-    }
-    // ---- epilogue: dV (first half's warps) and dK (second half's) of this K/V tile
-    if (ok) {
-      const bool got = mbar_wait(bar(C::B_DONE), 0, abort_flag);
+    // dV (first half's warps) or dK (second half's) of a finished item: tensor memory -> bf16 rows
+    auto epilogue = [&](int b, int h, int j, uint32_t n_done) {
+      const bool got = mbar_wait(bar(C::B_DONE), n_done & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1131);
-        ok = false;
+        return false;
       }
-    }
-    if (ok) {
       tc_fence_after();
+      const int kv_idx = j * BKV + r;
       const bool row_ok = kv_idx < p.S;
-      const size_t orow = (static_cast<size_t>(row0) + kv_idx) * p.ldd + static_cast<size_t>(h) * DH;
+      const size_t orow = (static_cast<size_t>(b) * p.S + kv_idx) * p.ldd + static_cast<size_t>(h) * DH;
       __nv_bfloat16* dst = (hf == 0 ? p.dv : p.dk) + orow;
       const float mul = hf == 0 ? 1.0f : p.scale;
       const int col = hf == 0 ? C::DV_COL : C::DK_COL;
@@ -415,19 +455,108 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[8 * g + 0]) * mul, __uint_as_float(o[8 * g + 1]) * mul);
-            w.y = pack_bf16x2(__uint_as_float(o[8 * g + 2]) * mul, __uint_as_float(o[8 * g + 3]) * mul);
-            w.z = pack_bf16x2(__uint_as_float(o[8 * g + 4]) * mul, __uint_as_float(o[8 * g + 5]) * mul);
-            w.w = pack_bf16x2(__uint_as_float(o[8 * g + 6]) * mul, __uint_as_float(o[8 * g + 7]) * mul);
-            *reinterpret_cast<uint4*>(dst + ch * 32 + g * 8) = w;
+          for (int gq = 0; gq < 4; ++gq) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * gq + 0]) * mul, __uint_as_float(o[8 * gq + 1]) * mul);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * gq + 2]) * mul, __uint_as_float(o[8 * gq + 3]) * mul);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * gq + 4]) * mul, __uint_as_float(o[8 * gq + 5]) * mul);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * gq + 6]) * mul, __uint_as_float(o[8 * gq + 7]) * mul);
+            *reinterpret_cast<uint4*>(dst + ch * 32 + gq * 8) = v;
           }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::B_EPI));
+      return true;
+    };
+    uint32_t n = 0, g = 0;
+    bool ok = true;
+    int pb = 0, ph = 0, pj = 0;               // the previous item, whose epilogue is still due
+    BwdWalk w;
+    w.init(p);
+    float stat_next = w.valid ? load_stat(w, 0) : 0.f;
+    while (ok && w.valid) {
+      const int kv0 = w.j * BKV;
+      const int kv_idx = kv0 + r;
+      const int lim = kv_idx >= p.S ? INT_MAX : (p.causal ? kv_idx : INT_MIN);
+      for (int it = 0; it < w.n_it; ++it, ++g) {
+        const int q0 = (w.i_start(p) + it) * BQ;
+        float* s_lse = s_stat + (g & 1) * 2 * BQ + hf * HQ;
+        float* s_dl = s_lse + BQ;
+        (gt < 64 ? s_lse : s_dl)[gt & 63] = stat_next;
+        // the next step's statistics land during this step's work
+        if (it + 1 < w.n_it) {
+          stat_next = load_stat(w, it + 1);
+        } else {
+          const BwdWalk t = w.peek(p);
+          if (t.valid) stat_next = load_stat(t, 0);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_STF + hf));
+        bool got = mbar_wait(bar(C::B_STF + hf), g & 1u, abort_flag);
+        if (got) got = mbar_wait(bar(C::B_SF + hf), g & 1u, abort_flag);
+        // the dS^T buffer of this parity was last read by the dQ product of step g - 2
+        if (got && g > 1) got = mbar_wait(bar(C::B_DF + (g & 1)), ((g >> 1) - 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1130);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        long long* tr = (blockIdx.x == 0 && g < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
+        if (tr) tr[g * 16 + hf * 3] = clock64();
+        const bool mask = (p.causal && kv0 + BKV - 1 > q0) || (kv0 + BKV > p.S);
+        // dS^T in shared memory: two groups of 64 query columns, each [128 K/V rows][128 bytes],
+        // 128-byte swizzled (the layout the dQ product reads as a transposed A operand)
+        const uint32_t srow = sDST(g & 1) + hf * (BKV * 128) + r * 128;
+        // four chunks of 16 query columns; the next chunk's loads are in flight during a chunk's
+        // arithmetic.  P^T / dS^T (packed, 8 columns) go over columns whose scores were read before.
+        uint32_t sc[2][16], dc[2][16];
+        tmem_ld_32x32b_x16(s_addr, sc[0]);
+        tmem_ld_32x32b_x16(d_addr, dc[0]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t pk[8], dk[8];
+          if (ch < 3) {
+            tmem_ld_32x32b_x16(s_addr + (ch + 1) * 16, sc[(ch + 1) & 1]);
+            tmem_ld_32x32b_x16(d_addr + (ch + 1) * 16, dc[(ch + 1) & 1]);
+          }
+          if (mask)
+            bwd_chunk<true>(sc[ch & 1], dc[ch & 1], s_lse + ch * 16, s_dl + ch * 16, c, lim,
+                            q0 + hf * HQ + ch * 16, pk, dk);
+          else
+            bwd_chunk<false>(sc[ch & 1], dc[ch & 1], s_lse + ch * 16, s_dl + ch * 16, c, lim, 0, pk, dk);
+          tmem_st_32x32b_x8(s_addr + ch * 8, pk);
+          tmem_st_32x32b_x8(d_addr + ch * 8, dk);
+#pragma unroll
+          for (int gq = 0; gq < 2; ++gq) {
+            const uint32_t sw = static_cast<uint32_t>((ch * 2 + gq) ^ (r & 7)) << 4;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw),
+                         "r"(dk[4 * gq]), "r"(dk[4 * gq + 1]), "r"(dk[4 * gq + 2]), "r"(dk[4 * gq + 3])
+                         : "memory");
+          }
+          if (ch < 3) tmem_ld_wait();
+        }
+        if (tr) tr[g * 16 + hf * 3 + 1] = clock64();
+        tmem_st_wait();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_PF + hf));
+        if (tr) tr[g * 16 + hf * 3 + 2] = clock64();
+        // the previous item's dV / dK leave after this item's first softmax, whose scores were
+        // issued while that item was finishing
+        if (it == 0 && n > 0 && !epilogue(pb, ph, pj, n - 1)) { ok = false; break; }
+      }
+      pb = w.b; ph = w.h; pj = w.j;
+      w.next(p);
+      ++n;
     }
+    if (ok && n > 0) epilogue(pb, ph, pj, n - 1);
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
     // ---------------------------------------------------------------- dQ drain
     // Each warp moves its 32 query rows on its own: tensor memory -> registers -> a swizzled
     // staging tile in shared memory -> bulk reduce-add into the fp32 accumulator (whole 128-byte
@@ -438,49 +567,54 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t stage = sbase + C::OFF_DQS + quarter * (C::DQS_BYTES / 4);
     const uint32_t srow = stage + lane * 128;
-    bool pending = false;
-    for (int it = 0; it < n_it; ++it) {
-      const int buf = it & 1;
-      const bool got = mbar_wait(bar(C::B_DQF + buf), (it >> 1) & 1u, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1140);
-        break;
-      }
-      tc_fence_after();
-      long long* trq = (blockIdx.x == 0 && it < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
-      if (trq) trq[it * 16 + 12] = clock64();
-      uint32_t o0[32], o1[32];
-      tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH, o0);
-      tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH + 32, o1);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(C::B_DQE + buf));               // the tensor-memory buffer is free again
-        if (pending) tma_store_wait_read_all();         // ... and so is the staging tile
-      }
-      __syncwarp();
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const uint32_t sw = static_cast<uint32_t>(g ^ (lane & 7)) << 4;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw), "r"(o0[4 * g]),
-                     "r"(o0[4 * g + 1]), "r"(o0[4 * g + 2]), "r"(o0[4 * g + 3]) : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + 4096 + sw),
-                     "r"(o1[4 * g]), "r"(o1[4 * g + 1]), "r"(o1[4 * g + 2]), "r"(o1[4 * g + 3])
-                     : "memory");
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        const int qrow = (i_start + it) * BQ + quarter * 32;
-        if (qrow < p.S) {
-          tma_reduce_add_3d(&tmDQ, stage, h * DH, qrow, b);
-          tma_reduce_add_3d(&tmDQ, stage + 4096, h * DH + 32, qrow, b);
-          tma_store_commit();
-          pending = true;
+    bool pending = false, ok = true;
+    uint32_t g = 0;
+    BwdWalk w;
+    for (w.init(p); w.valid && ok; w.next(p)) {
+      for (int it = 0; it < w.n_it; ++it, ++g) {
+        const int buf = g & 1;
+        const bool got = mbar_wait(bar(C::B_DQF + buf), (g >> 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1140);
+          ok = false;
+          break;
         }
+        tc_fence_after();
+        long long* trq = (blockIdx.x == 0 && g < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
+        if (trq) trq[g * 16 + 12] = clock64();
+        uint32_t o0[32], o1[32];
+        tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH, o0);
+        tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH + 32, o1);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(C::B_DQE + buf));               // the tensor-memory buffer is free again
+          if (pending) tma_store_wait_read_all();         // ... and so is the staging tile
+        }
+        __syncwarp();
+#pragma unroll
+        for (int gq = 0; gq < 8; ++gq) {
+          const uint32_t sw = static_cast<uint32_t>(gq ^ (lane & 7)) << 4;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw), "r"(o0[4 * gq]),
+                       "r"(o0[4 * gq + 1]), "r"(o0[4 * gq + 2]), "r"(o0[4 * gq + 3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + 4096 + sw),
+                       "r"(o1[4 * gq]), "r"(o1[4 * gq + 1]), "r"(o1[4 * gq + 2]), "r"(o1[4 * gq + 3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int qrow = (w.i_start(p) + it) * BQ + quarter * 32;
+          if (qrow < p.S) {
+            tma_reduce_add_3d(&tmDQ, stage, w.h * DH, qrow, w.b);
+            tma_reduce_add_3d(&tmDQ, stage + 4096, w.h * DH + 32, qrow, w.b);
+            tma_store_commit();
+            pending = true;
+          }
+        }
+        if (trq) trq[g * 16 + 13] = clock64();
       }
-      if (trq) trq[it * 16 + 13] = clock64();
     }
     if (lane == 0 && pending) tma_store_wait_all();
     __syncwarp();
@@ -492,6 +626,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.trace) p.trace[15] = clock64();
 }
 
 }  // namespace
@@ -506,9 +641,9 @@ int launch_attn_bwd_dh64(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
       return -10;
     configured = true;
   }
-  const int n_kv_tiles = (a.S + B64::BKV - 1) / B64::BKV;
-  attn_bwd_dh64_kernel<<<n_kv_tiles * a.B * a.nh, B64::THREADS, B64::SMEM_BYTES, st>>>(
-      tq, tk, tv, tdo, tdq, a);
+  const int n_items = ((a.S + B64::BKV - 1) / B64::BKV) * a.B * a.nh;
+  const int grid = n_items < sm_count() ? n_items : sm_count();
+  attn_bwd_dh64_kernel<<<grid, B64::THREADS, B64::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

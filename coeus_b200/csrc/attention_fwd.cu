@@ -166,6 +166,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + Cfg::N_BARS);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* seen = tmem_slot + 2;   // [t]: 1 + the last step whose scores tile t's warps saw
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -192,6 +193,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(bar(Cfg::B_VE + s), 1);
     }
     *abort_flag = 0;
+    seen[0] = 0;
+    seen[1] = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -414,7 +417,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = quarter * 32 + lane;         // query row within the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t o_addr = lane_addr + Cfg::O_COL0 + t * DH;
-    uint32_t g = 0, g_prev = 0, mine = 0;
+    uint32_t g = 0, g_prev = 0, mine = 0, own_seen = 0;
     bool ok = true;
     float m_used = -INFINITY;
     float l[4] = {0.f, 0.f, 0.f, 0.f};           // the row sum is kept as four partial sums
@@ -431,6 +434,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const uint32_t buf = g % NBUF;
       const uint32_t s_addr = lane_addr + Cfg::S_COL0 + buf * BKV;
+      // The parity wait below is only meaningful once the scores of step g - NBUF (the previous
+      // use of this barrier) are known to be complete: with that phase still open, the wait for
+      // the opposite parity would return at once.  A warpgroup's own recent steps imply it; after
+      // sitting out several steps (an item with a single query tile; key tiles that only tile B
+      // sees under a causal mask) the other warpgroup's published progress does: it owned all the
+      // steps in between, none of which depends on this warpgroup.
+      {
+        const uint32_t need = g >= NBUF ? g - NBUF + 1u : 0u;
+        if (own_seen < need) {
+          bool got = true;
+          if (seen[1 - t] < need) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t n = 0;
+            while (seen[1 - t] < need) {
+              if ((++n & 63u) == 0u) {
+                if (*abort_flag) { got = false; break; }
+                if (globaltimer_ns() - t0 > CB_WAIT_LIMIT_NS) {
+                  *abort_flag = 1u;
+                  got = false;
+                  break;
+                }
+              }
+            }
+          }
+          if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 973);
+            ok = false;
+            break;
+          }
+        }
+      }
       {
         const bool got = mbar_wait(bar(Cfg::B_SF + buf), (g / NBUF) & 1u, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
@@ -439,6 +473,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           break;
         }
       }
+      own_seen = g + 1u;
+      if (quarter == 0 && lane == 0) seen[t] = g + 1u;   // one writer per tile: monotonic
       long long* tr = (blockIdx.x == g_attn_fwd_trace_cta && mine < 120 && quarter == 0 && lane == 0)
                           ? g_attn_fwd_trace : nullptr;
       const uint32_t tri = t * 1024 + mine * 8;

@@ -101,6 +101,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// The same wait by plain polling (test_wait only, no suspension): for a warp with nothing else to
+// do whose reaction time is on the critical path -- a suspended try_wait wakes up some hundreds
+// of clocks after the phase completes.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t n = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((++n & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > CB_WAIT_LIMIT_NS) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -348,6 +368,13 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
         "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
         "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {

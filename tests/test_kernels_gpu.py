@@ -226,13 +226,17 @@ def test_attention_fwd_bwd(dh, causal, S):
         assert err < 0.02 * ref.float().abs().max().item() + 0.03, (name, err)
 
 
-@pytest.mark.parametrize("dh,S,causal", [(64, 1152, True), (64, 1100, True), (64, 640, False),
-                                          (128, 1152, True)])
-def test_attention_bwd_many_query_tiles(dh, S, causal):
-    """Nine query tiles per K/V tile: every ring (query stages, dS^T and dQ buffers) wraps around
-    several times, with a ragged last tile in one case."""
+@pytest.mark.parametrize("dh,B,nh,S,causal", [
+    (64, 1, 2, 1152, True), (64, 1, 2, 1100, True), (64, 1, 2, 640, False), (128, 1, 2, 1152, True),
+    (64, 4, 16, 512, True),      # 256 work items: persistent CTAs chain several, K/V buffers alternate
+    (64, 8, 16, 300, True),      # 384 items of one to three steps, ragged last tile
+    (64, 3, 20, 256, False),     # 120 + items of equal length
+    (64, 5, 32, 128, True),      # 160 single-step items
+])
+def test_attention_bwd_many_query_tiles(dh, B, nh, S, causal):
+    """Many query tiles per K/V tile (every ring -- query stages, dS^T and dQ buffers -- wraps
+    around several times, with a ragged last tile in one case) and more work items than CTAs."""
     torch.manual_seed(18)
-    B, nh = 1, 2
     H = nh * dh
     qkv = _bf(torch.randn(B * S, 3 * H, device=DEV))
     q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
@@ -255,6 +259,13 @@ def test_attention_bwd_many_query_tiles(dh, S, causal):
     (128, 4, 1, 2, 640, True),      # multi-query, dh 128, five query tiles
     (128, 2, 2, 3, 512, False),
     (64, 3, 3, 2, 77, False),
+    # odd numbers of query tiles with more work items than CTAs: a CTA's first item has a single
+    # query tile, so one softmax warpgroup sits that item out and joins at the next
+    (64, 16, 16, 8, 300, True),
+    (64, 16, 16, 8, 384, False),
+    (64, 16, 4, 8, 640, True),
+    (128, 8, 8, 8, 640, True),
+    (128, 8, 8, 6, 384, False),
 ])
 def test_attention_fwd_shapes_and_grouped_query(dh, nh, nkv, B, S, causal):
     torch.manual_seed(9)
@@ -262,14 +273,17 @@ def test_attention_fwd_shapes_and_grouped_query(dh, nh, nkv, B, S, causal):
     qkv = _bf(torch.randn(B * S, H + 2 * Hkv, device=DEV))
     q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
     orf, lser = A.attention_fwd(q.cpu(), k.cpu(), v.cpu(), B, S, nh, dh, causal=causal)
-    for poly in (0, 1):
-        A.FWD_POLY = poly
-        o, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal)
-        torch.cuda.synchronize()
-        _status_clean()
-        assert (o.float().cpu() - orf.float()).abs().max() < 0.03, poly
-        assert (lse.cpu() - lser).abs().max() < 0.02, poly
-    A.FWD_POLY = 1
+    before = A.FWD_POLY
+    try:
+        for poly in (0, 1):
+            A.FWD_POLY = poly
+            o, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal)
+            torch.cuda.synchronize()
+            _status_clean()
+            assert (o.float().cpu() - orf.float()).abs().max() < 0.03, poly
+            assert (lse.cpu() - lser).abs().max() < 0.02, poly
+    finally:
+        A.FWD_POLY = before
 
 
 def test_dropout_mask_is_the_same_on_the_device_in_the_gemm_and_on_the_host():
