@@ -20,8 +20,10 @@
 //  * the steps of consecutive items form one stream: the next item's K/V tile is loaded (second
 //    buffer) and its first scores are issued while the current item finishes, and the dV / dK
 //    epilogue of an item runs after the softmax of the next item's first step.
-//   warp 0        TMA producer (K_j, V_j per item, two buffers; Q_i, dO_i per half, two stages)
-//   warp 1        MMA issuer          (warps 2, 3 idle: register donors)
+//   warp 0        TMA producer (K_j, V_j per item, two buffers; Q_i, dO_i by halves through a ring
+//                 of five slots)
+//   warp 1        MMA issuer: products and scores      warp 2   MMA issuer: dQ
+//   warp 3        idle (register donor)
 //   warps 4..7    softmax / dS of the first half; dV epilogue
 //   warps 8..11   softmax / dS of the second half; dK epilogue
 //   warps 12..15  dQ drain (TMEM -> shared memory -> bulk reduce-add into the fp32 accumulator)
@@ -43,18 +45,17 @@ namespace {
 struct B64 {
   static constexpr int DH = 64, BQ = 128, BKV = 128, HQ = 64;
   static constexpr int THREADS = 512;
-  static constexpr int NST = 2;                           // Q_i / dO_i stages
+  static constexpr int NSLOT = 5;                         // ring of half-tile slots (2.5 steps)
   static constexpr int KV_BYTES = BKV * DH * 2;           // K_j or V_j
-  static constexpr int Q_BYTES = BQ * DH * 2;             // Q_i or dO_i
   static constexpr int HALF_BYTES = HQ * DH * 2;          // 64 query rows of Q_i or dO_i
-  static constexpr int ST_BYTES = 2 * Q_BYTES;            // one stage: Q_i | dO_i
+  static constexpr int SLOT_BYTES = 2 * HALF_BYTES;       // one slot: half of Q_i | half of dO_i
   static constexpr int DST_BYTES = BKV * BQ * 2;          // dS^T of one tile
   static constexpr int OFF_K = 0;                         // two buffers of (K_j | V_j)
   static constexpr int OFF_Q = 2 * 2 * KV_BYTES;
-  static constexpr int OFF_DST = OFF_Q + NST * ST_BYTES;  // two buffers (step parity)
-  static constexpr int OFF_DQS = OFF_DST + 2 * DST_BYTES;   // dQ staging: per drain warp two boxes
+  static constexpr int OFF_DST = OFF_Q + NSLOT * SLOT_BYTES;  // two buffers (step parity)
+  static constexpr int OFF_DQS = OFF_DST + 2 * DST_BYTES;   // dQ staging: per drain warp one box
                                                             // of [32 rows][32 floats], swizzled
-  static constexpr int DQS_BYTES = BQ * DH * 4;
+  static constexpr int DQS_BYTES = BQ * 32 * 4;
   static constexpr int OFF_STAT = OFF_DQS + DQS_BYTES;      // [2 parities][lse | delta][BQ] floats
   static constexpr int OFF_BAR = OFF_STAT + 2 * 2 * BQ * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
@@ -65,10 +66,10 @@ struct B64 {
   static constexpr int TMEM_COLS = 512;
   enum {
     B_KVF = 0,               // + buffer: K_j / V_j landed
-    B_KVE = 2,               // + buffer: buffer free (the item's last dQ product completed)
-    B_QF = 4,                // + 2 stage + half: the half's Q_i / dO_i rows landed
-    B_QE = B_QF + 2 * NST,   // + 2 stage + half: slot free
-    B_SF = B_QE + 2 * NST,   // + half: S^T / dP^T of the half complete
+    B_KVE = 2,               // + buffer: buffer free (both issuers are through with the item)
+    B_QF = 4,                // + slot: a half's Q_i / dO_i rows landed
+    B_QE = B_QF + NSLOT,     // + slot: slot free
+    B_SF = B_QE + NSLOT,     // + half: S^T / dP^T of the half complete
     B_PF = B_SF + 2,         // + half: P^T / dS^T of the half written (4 warps)
     B_STF = B_PF + 2,        // + half: the half's lse / delta in shared memory (4 warps)
     B_DF = B_STF + 2,        // + parity: dS^T buffer free (its dQ product completed)
@@ -157,7 +158,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                      const __grid_constant__ CUtensorMap tmDQ, const AttnBwdArgs p) {
   using C = B64;
-  constexpr int DH = C::DH, BQ = C::BQ, BKV = C::BKV, HQ = C::HQ, NST = C::NST;
+  constexpr int DH = C::DH, BQ = C::BQ, BKV = C::BKV, HQ = C::HQ, NSLOT = C::NSLOT;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
@@ -176,7 +177,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::B_KVF + s), 1);
-      mbar_init(bar(C::B_KVE + s), 1);
+      mbar_init(bar(C::B_KVE + s), 2);     // the product / score issuer and the dQ issuer
       mbar_init(bar(C::B_SF + s), 1);
       mbar_init(bar(C::B_PF + s), 4);      // one arrival per softmax warp of the half
       mbar_init(bar(C::B_STF + s), 4);
@@ -184,7 +185,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(bar(C::B_DQF + s), 1);
       mbar_init(bar(C::B_DQE + s), 4);     // one arrival per dQ-drain warp
     }
-    for (int s = 0; s < 2 * NST; ++s) {
+    for (int s = 0; s < NSLOT; ++s) {
       mbar_init(bar(C::B_QF + s), 1);
       mbar_init(bar(C::B_QE + s), 1);
     }
@@ -209,8 +210,8 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   auto sK = [&](int kb) { return sbase + C::OFF_K + kb * 2 * C::KV_BYTES; };
   auto sV = [&](int kb) { return sK(kb) + C::KV_BYTES; };
   auto sDST = [&](int buf) { return sbase + C::OFF_DST + buf * C::DST_BYTES; };
-  auto sQ = [&](int st) { return sbase + C::OFF_Q + st * C::ST_BYTES; };
-  auto sDO = [&](int st) { return sQ(st) + C::Q_BYTES; };
+  auto sQ = [&](int slot) { return sbase + C::OFF_Q + slot * C::SLOT_BYTES; };   // half of Q_i
+  auto sDO = [&](int slot) { return sQ(slot) + C::HALF_BYTES; };                  // half of dO_i
 
   // 512 threads start with 128 registers each.  The first warpgroup (producer, MMA issue) and the
   // dQ-drain warpgroup hand registers to the two softmax warpgroups: 128 * (104 + 104 + 152 + 152)
@@ -220,8 +221,8 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (warp == 0) {
       // -------------------------------------------------------------- producer
       if (lane == 0) {
-        uint32_t n = 0, g = 0;        // items and steps so far
-        uint32_t q_issued = 0;        // half-tile loads issued (two per step)
+        uint32_t n = 0;               // items so far
+        uint32_t q_issued = 0;        // half-tile loads issued (two per step): the ring position
         uint32_t kv_issued = 0;
         bool ok = true;
         BwdWalk w;
@@ -236,22 +237,19 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tma_load_2d(sK(kb), &tmK, bar(C::B_KVF + kb), w.h * DH, row0 + w.j * BKV);
           tma_load_2d(sV(kb), &tmV, bar(C::B_KVF + kb), w.h * DH, row0 + w.j * BKV);
           ++kv_issued;
-          for (int it = 0; it < w.n_it && ok; ++it, ++g) {
-            const int st = g % NST;
+          for (int it = 0; it < w.n_it && ok; ++it) {
             const int qrow = row0 + (w.i_start(p) + it) * BQ;
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
-              const int slot = 2 * st + hf;
-              if (!mbar_wait(bar(C::B_QE + slot), ((g / NST) & 1u) ^ 1u, abort_flag)) {
+              const int slot = q_issued % NSLOT;
+              if (!mbar_wait(bar(C::B_QE + slot), ((q_issued / NSLOT) & 1u) ^ 1u, abort_flag)) {
                 record_status(p.status, ST_WAIT_TIMEOUT, 1111);
                 ok = false;
                 break;
               }
-              mbar_arrive_expect_tx(bar(C::B_QF + slot), 2 * C::HALF_BYTES);
-              tma_load_2d(sQ(st) + hf * C::HALF_BYTES, &tmQ, bar(C::B_QF + slot), w.h * DH,
-                          qrow + hf * HQ);
-              tma_load_2d(sDO(st) + hf * C::HALF_BYTES, &tmdO, bar(C::B_QF + slot), w.h * DH,
-                          qrow + hf * HQ);
+              mbar_arrive_expect_tx(bar(C::B_QF + slot), C::SLOT_BYTES);
+              tma_load_2d(sQ(slot), &tmQ, bar(C::B_QF + slot), w.h * DH, qrow + hf * HQ);
+              tma_load_2d(sDO(slot), &tmdO, bar(C::B_QF + slot), w.h * DH, qrow + hf * HQ);
               ++q_issued;
             }
           }
@@ -265,55 +263,45 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               if (globaltimer_ns() - t0 > 200000000ull) return;
             }
           };
-          const uint32_t q_first = q_issued > 2u * NST ? q_issued - 2u * NST : 0u;
-          for (uint32_t u = q_first; u < q_issued; ++u) {
-            const uint32_t step = u >> 1;
-            settle(C::B_QF + 2 * (step % NST) + (u & 1u), (step / NST) & 1u);
-          }
+          const uint32_t q_first = q_issued > NSLOT ? q_issued - NSLOT : 0u;
+          for (uint32_t u = q_first; u < q_issued; ++u)
+            settle(C::B_QF + u % NSLOT, (u / NSLOT) & 1u);
           for (uint32_t u = kv_issued > 2u ? kv_issued - 2u : 0u; u < kv_issued; ++u)
             settle(C::B_KVF + (u & 1u), (u >> 1) & 1u);
         }
       }
       __syncwarp();
     } else if (warp == 1) {
-      // -------------------------------------------------------------- MMA issuer
+      // -------------------------------------------------------------- MMA issuer: products, scores
       // The whole warp runs the control flow (addresses and descriptors stay warp-uniform); one
-      // elected lane issues.  Descriptors are built once; a product only adds constants to their
-      // address field.  The waits poll: this warp's reaction time is on the critical path.
+      // elected lane issues.  Every operand descriptor is one base plus compile-time constants
+      // (offset in the address field; the leading-dimension field switched from the K-major to
+      // the MN-major value).  (Polling waits here were tried and cost more than they saved: the
+      // spinning warp takes issue slots from the softmax warps of its scheduler.)
+      // dQ has an issuer of its own (warp 2): it shares no accumulator with these products.
       constexpr uint32_t idesc_sc = umma_idesc_bf16(BKV, HQ, 0, 0);   // S^T, dP^T of a half
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BKV, DH, 0, 1);   // dV, dK (A in tensor memory)
-      constexpr uint32_t idesc_dq = umma_idesc_bf16(BQ, DH, 1, 1);    // dQ
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-      // every operand descriptor is this one plus compile-time constants (offset in the address
-      // field; the leading-dimension field switched from the K-major to the MN-major value)
       const uint64_t d_base = umma_desc_sw128(sbase, 16, 1024);
       constexpr uint64_t MN = static_cast<uint64_t>(((BKV * 128) >> 4) - 1) << 16;
-      static_assert(BKV == BQ, "one MN-major leading dimension for K, Q, dO and dS^T tiles");
       const uint64_t dK_k0 = d_base + (C::OFF_K >> 4);
       const uint64_t dV_k0 = d_base + ((C::OFF_K + C::KV_BYTES) >> 4);
-      const uint64_t dK_mn0 = dK_k0 + MN;
       const uint64_t dQ_k0 = d_base + (C::OFF_Q >> 4);
-      const uint64_t dDO_k0 = d_base + ((C::OFF_Q + C::Q_BYTES) >> 4);
-      const uint64_t dQ_mn0 = dQ_k0 + MN;
-      const uint64_t dDO_mn0 = dDO_k0 + MN;
-      const uint64_t dDST_mn0 = d_base + (C::OFF_DST >> 4) + MN;
       constexpr uint64_t KB_STEP = (2 * C::KV_BYTES) >> 4;  // K/V buffer pitch
-      constexpr uint64_t ST_STEP = C::ST_BYTES >> 4;        // stage pitch
-      constexpr uint64_t BUF_STEP = C::DST_BYTES >> 4;      // dS^T buffer pitch
-      constexpr uint64_t HALF_STEP = C::HALF_BYTES >> 4;    // 64 query rows further in a tile
+      constexpr uint64_t SLOT_STEP = C::SLOT_BYTES >> 4;    // ring slot pitch
+      constexpr uint64_t DO_STEP = C::HALF_BYTES >> 4;      // dO half after the Q half of a slot
       auto wait_all = [&](int b_idx, uint32_t parity, int where) {
-        const bool got = mbar_wait_poll(bar(b_idx), parity, abort_flag);
+        const bool got = mbar_wait(bar(b_idx), parity, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
           return false;
         }
         return true;
       };
-      // S^T and dP^T of half hf of the tile in stage st against K/V buffer kb (K-major operands,
+      // S^T and dP^T of half hf from ring slot `slot` against K/V buffer kb (K-major operands,
       // contraction over dh)
-      auto scores = [&](int hf, int st, int kb) {
-        const uint64_t bq = dQ_k0 + st * ST_STEP + hf * HALF_STEP;
-        const uint64_t bdo = dDO_k0 + st * ST_STEP + hf * HALF_STEP;
+      auto scores = [&](int hf, uint32_t slot, int kb) {
+        const uint64_t bq = dQ_k0 + slot * SLOT_STEP, bdo = bq + DO_STEP;
         const uint64_t ak = dK_k0 + kb * KB_STEP, av = dV_k0 + kb * KB_STEP;
         const uint32_t s_col = tmem_u + hf * 128, d_col = s_col + 64;
 #pragma unroll
@@ -323,17 +311,16 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(bar(C::B_SF + hf));
       };
-      // dV += P^T . dO and dK += dS^T . Q over the 64 query rows of half hf
-      auto products = [&](int hf, int st, uint32_t acc0) {
-        const uint64_t bdo = dDO_mn0 + st * ST_STEP + hf * HALF_STEP;
-        const uint64_t bq = dQ_mn0 + st * ST_STEP + hf * HALF_STEP;
+      // dV += P^T . dO and dK += dS^T . Q over the 64 query rows of half hf (ring slot `slot`)
+      auto products = [&](int hf, uint32_t slot, uint32_t acc0) {
+        const uint64_t bq = dQ_k0 + slot * SLOT_STEP + MN, bdo = bq + DO_STEP;
         const uint32_t pt = tmem_u + hf * 128, dst = pt + 64;
 #pragma unroll
         for (int kk = 0; kk < HQ / 16; ++kk) {
           umma_bf16_ts(tmem_u + C::DV_COL, pt + kk * 8, bdo + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
           umma_bf16_ts(tmem_u + C::DK_COL, dst + kk * 8, bq + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
         }
-        umma_commit(bar(C::B_QE + 2 * st + hf));       // the half's Q_i / dO_i rows are free
+        umma_commit(bar(C::B_QE + slot));       // the slot may be refilled
       };
       long long* trace = (blockIdx.x == 0 && lane == 0) ? p.trace : nullptr;
       uint32_t n = 0, g = 0;
@@ -348,7 +335,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (trace) trace[16 + 14] = clock64();
         if (elect_one()) {
           scores(0, 0, 0);
-          scores(1, 0, 0);
+          scores(1, 1, 0);
         }
         __syncwarp();
       }
@@ -356,44 +343,80 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const bool has_next = w.peek(p).valid;
         const int kb = n & 1;
         for (int it = 0; it < w.n_it && ok; ++it, ++g) {
-          const int st = g % NST, buf = g & 1;
-          const int nst = (g + 1) % NST;
           const bool last = it + 1 == w.n_it;
           const bool more = !last || has_next;
           const int nkb = last ? (n + 1) & 1 : kb;
-          const uint32_t nq_par = ((g + 1) / NST) & 1u;
+          const uint32_t u = 2 * g, un = u + 2;            // ring positions of this / the next step
+          const uint32_t slot0 = u % NSLOT, slot1 = (u + 1) % NSLOT;
+          const uint32_t nslot0 = un % NSLOT, nslot1 = (un + 1) % NSLOT;
           // ---- first half: its products, then the next step's scores over the same columns
           if (!wait_all(C::B_PF + 0, g & 1u, 1122)) { ok = false; break; }
           // the first products of an item overwrite dV / dK: the previous item's must have left
           if (it == 0 && n > 0 && !wait_all(C::B_EPI, (n - 1) & 1u, 1126)) { ok = false; break; }
           if (more) {
             if (last && !wait_all(C::B_KVF + nkb, ((n + 1) >> 1) & 1u, 1127)) { ok = false; break; }
-            if (!wait_all(C::B_QF + 2 * nst, nq_par, 1123)) { ok = false; break; }
+            if (!wait_all(C::B_QF + nslot0, (un / NSLOT) & 1u, 1123)) { ok = false; break; }
           }
           tc_fence_after();
           if (trace && g < 16) trace[g * 16 + 6] = clock64();
           if (elect_one()) {
-            products(0, st, it > 0 ? 1u : 0u);
-            if (more) scores(0, nst, nkb);
+            products(0, slot0, it > 0 ? 1u : 0u);
+            if (more) scores(0, nslot0, nkb);
           }
           __syncwarp();
           if (trace && g < 16) trace[g * 16 + 7] = clock64();
           // ---- second half
           if (!wait_all(C::B_PF + 1, g & 1u, 1124)) { ok = false; break; }
-          if (more && !wait_all(C::B_QF + 2 * nst + 1, nq_par, 1128)) { ok = false; break; }
+          if (more && !wait_all(C::B_QF + nslot1, ((un + 1) / NSLOT) & 1u, 1128)) { ok = false; break; }
           tc_fence_after();
           if (trace && g < 16) trace[g * 16 + 8] = clock64();
           if (elect_one()) {
-            products(1, st, 1u);
-            if (more) scores(1, nst, nkb);
+            products(1, slot1, 1u);
+            if (last) {
+              umma_commit(bar(C::B_KVE + kb));   // no score product reads this K/V buffer any more
+              umma_commit(bar(C::B_DONE));       // dV / dK of the item are complete
+            }
+            if (more) scores(1, nslot1, nkb);
           }
           __syncwarp();
           if (trace && g < 16) trace[g * 16 + 9] = clock64();
-          // ---- dQ_i = dS . K_j over the whole tile, into the dQ buffer of this parity
-          if (g >= 2) {
-            if (!wait_all(C::B_DQE + buf, ((g >> 1) - 1) & 1u, 1125)) { ok = false; break; }
-            tc_fence_after();
-          }
+        }
+        w.next(p);
+        ++n;
+      }
+    } else if (warp == 2) {
+      // -------------------------------------------------------------- MMA issuer: dQ
+      // dQ_i = dS . K_j over the whole tile (dS^T from shared memory as the transposed operand),
+      // into the dQ buffer of the step's parity, once both halves' dS^T are written.
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(BQ, DH, 1, 1);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      constexpr uint64_t MN = static_cast<uint64_t>(((BKV * 128) >> 4) - 1) << 16;
+      const uint64_t d_base = umma_desc_sw128(sbase, 16, 1024) + MN;
+      const uint64_t dK_mn0 = d_base + (C::OFF_K >> 4);
+      const uint64_t dDST_mn0 = d_base + (C::OFF_DST >> 4);
+      constexpr uint64_t KB_STEP = (2 * C::KV_BYTES) >> 4;
+      constexpr uint64_t BUF_STEP = C::DST_BYTES >> 4;
+      auto wait_all = [&](int b_idx, uint32_t parity, int where) {
+        const bool got = mbar_wait(bar(b_idx), parity, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
+          return false;
+        }
+        return true;
+      };
+      long long* trace = (blockIdx.x == 0 && lane == 0) ? p.trace : nullptr;
+      uint32_t n = 0, g = 0;
+      bool ok = true;
+      BwdWalk w;
+      for (w.init(p); w.valid && ok; w.next(p), ++n) {
+        const int kb = n & 1;
+        for (int it = 0; it < w.n_it; ++it, ++g) {
+          const int buf = g & 1;
+          ok = wait_all(C::B_PF + 0, g & 1u, 1150) && wait_all(C::B_PF + 1, g & 1u, 1151);
+          // the dQ of step g - 2 must have left this tensor-memory buffer
+          if (ok && g >= 2) ok = wait_all(C::B_DQE + buf, ((g >> 1) - 1) & 1u, 1152);
+          if (!ok) break;
+          tc_fence_after();
           if (trace && g < 16) trace[g * 16 + 10] = clock64();
           if (elect_one()) {
             const uint64_t a = dDST_mn0 + buf * BUF_STEP;
@@ -404,16 +427,11 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               umma_bf16_ss(d, a + 128 * kk, bk + 128 * kk, idesc_dq, kk > 0 ? 1u : 0u);
             umma_commit(bar(C::B_DQF + buf));
             umma_commit(bar(C::B_DF + buf));
-            if (last) {
-              umma_commit(bar(C::B_KVE + kb));   // nothing reads this K/V buffer any more
-              umma_commit(bar(C::B_DONE));       // dV / dK of the item are complete
-            }
+            if (it + 1 == w.n_it) umma_commit(bar(C::B_KVE + kb));   // K_j is not read any more
           }
           __syncwarp();
           if (trace && g < 16) trace[g * 16 + 11] = clock64();
         }
-        w.next(p);
-        ++n;
       }
     }
   } else if (warp < 12) {
@@ -565,7 +583,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // dropped by the tensor map's bounds.
     const int quarter = warp & 3;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t stage = sbase + C::OFF_DQS + quarter * (C::DQS_BYTES / 4);
+    const uint32_t stage = sbase + C::OFF_DQS + quarter * (C::DQS_BYTES / 4);   // 4 KB
     const uint32_t srow = stage + lane * 128;
     bool pending = false, ok = true;
     uint32_t g = 0;
@@ -582,34 +600,34 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_after();
         long long* trq = (blockIdx.x == 0 && g < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
         if (trq) trq[g * 16 + 12] = clock64();
-        uint32_t o0[32], o1[32];
-        tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH, o0);
-        tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH + 32, o1);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar(C::B_DQE + buf));               // the tensor-memory buffer is free again
-          if (pending) tma_store_wait_read_all();         // ... and so is the staging tile
-        }
-        __syncwarp();
+        const int qrow = (w.i_start(p) + it) * BQ + quarter * 32;
+#pragma unroll 1
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + C::DQ_COL + buf * DH + ch * 32, o);
+          tmem_ld_wait();
+          if (ch == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(C::B_DQE + buf));   // the tensor-memory buffer is free
+          }
+          if (pending) {
+            if (lane == 0) tma_store_wait_read_all();          // ... and so is the staging tile
+            __syncwarp();
+          }
 #pragma unroll
-        for (int gq = 0; gq < 8; ++gq) {
-          const uint32_t sw = static_cast<uint32_t>(gq ^ (lane & 7)) << 4;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw), "r"(o0[4 * gq]),
-                       "r"(o0[4 * gq + 1]), "r"(o0[4 * gq + 2]), "r"(o0[4 * gq + 3]) : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + 4096 + sw),
-                       "r"(o1[4 * gq]), "r"(o1[4 * gq + 1]), "r"(o1[4 * gq + 2]), "r"(o1[4 * gq + 3])
-                       : "memory");
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int qrow = (w.i_start(p) + it) * BQ + quarter * 32;
+          for (int gq = 0; gq < 8; ++gq) {
+            const uint32_t sw = static_cast<uint32_t>(gq ^ (lane & 7)) << 4;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw), "r"(o[4 * gq]),
+                         "r"(o[4 * gq + 1]), "r"(o[4 * gq + 2]), "r"(o[4 * gq + 3]) : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
           if (qrow < p.S) {
-            tma_reduce_add_3d(&tmDQ, stage, w.h * DH, qrow, w.b);
-            tma_reduce_add_3d(&tmDQ, stage + 4096, w.h * DH + 32, qrow, w.b);
-            tma_store_commit();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tmDQ, stage, w.h * DH + ch * 32, qrow, w.b);
+              tma_store_commit();
+            }
             pending = true;
           }
         }
