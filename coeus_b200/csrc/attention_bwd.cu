@@ -26,6 +26,8 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint64_t ld, uint32_t box_inner, uint32_t box_outer);
 int make_tmap_f32_3d(CUtensorMap* out, void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                      uint64_t ld1, uint64_t ld2, uint32_t box1);
+int make_tmap_bf16_3d(CUtensorMap* out, void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                      uint64_t ld1, uint64_t ld2, uint32_t box1);
 int sm_count();
 
 constexpr int ATB_BKV = 128;
@@ -550,9 +552,14 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   if (make_tmap_bf16_2d(&tk, k, H, rows, ldk, 64, ATB_BKV) != 0) return -4;
   if (make_tmap_bf16_2d(&tv, v, H, rows, ldv, 64, ATB_BKV) != 0) return -5;
   if (make_tmap_bf16_2d(&tdo, dO, H, rows, lddo, 64, bq) != 0) return -6;
-  CUtensorMap tdq;
-  if (dh == 64 && make_tmap_f32_3d(&tdq, dq_acc, H, S, B, H, static_cast<uint64_t>(S) * H, 32) != 0)
-    return -7;
+  CUtensorMap tdq, tdk, tdv;
+  if (dh == 64) {
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(dqkv);
+    const uint64_t slab = static_cast<uint64_t>(S) * ldd;
+    if (make_tmap_f32_3d(&tdq, dq_acc, H, S, B, H, static_cast<uint64_t>(S) * H, 32) != 0) return -7;
+    if (make_tmap_bf16_3d(&tdk, out + H, H, S, B, ldd, slab, 128) != 0) return -8;
+    if (make_tmap_bf16_3d(&tdv, out + 2 * H, H, S, B, ldd, slab, 128) != 0) return -9;
+  }
   {
     const size_t work = rows * nh * (dh / 8);
     const int blocks = static_cast<int>(std::min<size_t>((work + 255) / 256, sm_count() * 16));
@@ -571,7 +578,7 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   a.causal = causal;
   a.status = status;
   a.trace = g_attn_bwd_trace_host;
-  int rc = dh == 64 ? launch_attn_bwd_dh64(tq, tk, tv, tdo, tdq, a, st)
+  int rc = dh == 64 ? launch_attn_bwd_dh64(tq, tk, tv, tdo, tdq, tdk, tdv, a, st)
                     : launch_attn_bwd<128>(tq, tk, tv, tdo, a, st);
   if (rc != 0) return rc;
   {

@@ -23,9 +23,10 @@ struct AttnBwdArgs {
 };
 
 // Head dimension 64 (attention_bwd_dh64.cu).
-// `tdq`: fp32 map of the dQ accumulator as (nh*64, S, B), box 32 x 32 x 1.
+// `tdq`: fp32 map of the dQ accumulator as (nh*64, S, B), box 32 x 32 x 1; `tdk`, `tdv`: bf16 maps
+// of the dK / dV output slices as (nh*64, S, B), box 64 x 128 x 1.
 int launch_attn_bwd_dh64(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdArgs& a,
-                         cudaStream_t st);
+                         const CUtensorMap& tdo, const CUtensorMap& tdq, const CUtensorMap& tdk,
+                         const CUtensorMap& tdv, const AttnBwdArgs& a, cudaStream_t st);
 
 }  // namespace cb

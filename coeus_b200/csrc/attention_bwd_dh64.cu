@@ -23,9 +23,9 @@
 //   warp 0        TMA producer (K_j, V_j per item, two buffers; Q_i, dO_i by halves through a ring
 //                 of five slots)
 //   warp 1        MMA issuer: products and scores      warp 2   MMA issuer: dQ
-//   warp 3        idle (register donor)
-//   warps 4..7    softmax / dS of the first half; dV epilogue
-//   warps 8..11   softmax / dS of the second half; dK epilogue
+//   warp 3        stores the staged dV / dK tiles (bulk stores)
+//   warps 4..7    softmax / dS of the first half; dV epilogue (staged in the item's K tile)
+//   warps 8..11   softmax / dS of the second half; dK epilogue (staged in the item's V tile)
 //   warps 12..15  dQ drain (TMEM -> shared memory -> bulk reduce-add into the fp32 accumulator)
 // delta_i = rowsum(dO_i o O_i) comes from a pre-kernel, a post-kernel scales and casts dQ (both in
 // attention_bwd.cu).  The reference (plugins/model-transformer/src/lib.rs:300-372) computes the
@@ -66,7 +66,7 @@ struct B64 {
   static constexpr int TMEM_COLS = 512;
   enum {
     B_KVF = 0,               // + buffer: K_j / V_j landed
-    B_KVE = 2,               // + buffer: buffer free (both issuers are through with the item)
+    B_KVE = 2,               // + buffer: buffer free (issuers and epilogue through with the item)
     B_QF = 4,                // + slot: a half's Q_i / dO_i rows landed
     B_QE = B_QF + NSLOT,     // + slot: slot free
     B_SF = B_QE + NSLOT,     // + half: S^T / dP^T of the half complete
@@ -75,8 +75,9 @@ struct B64 {
     B_DF = B_STF + 2,        // + parity: dS^T buffer free (its dQ product completed)
     B_DQF = B_DF + 2,        // + parity: dQ complete in tensor memory
     B_DQE = B_DQF + 2,       // + parity: dQ drained (4 warps)
-    B_DONE = B_DQE + 2,      // the item's dV / dK are complete
+    B_DONE = B_DQE + 2,      // the item's dV / dK are complete and its K/V buffer is not read any more
     B_EPI,                   // dV / dK of the item have left tensor memory (8 warps)
+    B_STG,                   // dV / dK of the item are staged in shared memory (8 warps)
     N_BARS
   };
   static_assert(N_BARS * 8 + 8 <= 256, "barrier block");
@@ -156,7 +157,8 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* sv, const uint32_t* dv
 __global__ void __launch_bounds__(B64::THREADS, 1)
 attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                     const __grid_constant__ CUtensorMap tmDQ, const AttnBwdArgs p) {
+                     const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+                     const __grid_constant__ CUtensorMap tmDV, const AttnBwdArgs p) {
   using C = B64;
   constexpr int DH = C::DH, BQ = C::BQ, BKV = C::BKV, HQ = C::HQ, NSLOT = C::NSLOT;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -168,7 +170,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* s_stat = reinterpret_cast<float*>(smem + C::OFF_STAT);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (blockIdx.x == 0 && threadIdx.x == 0 && p.trace) p.trace[14] = clock64();
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.trace) p.trace[1088] = clock64();
   if ((sbase & 1023u) != 0u) {
     if (threadIdx.x == 0) record_status(p.status, ST_BAD_ARG, 1100);
     return;
@@ -177,7 +179,8 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::B_KVF + s), 1);
-      mbar_init(bar(C::B_KVE + s), 2);     // the product / score issuer and the dQ issuer
+      mbar_init(bar(C::B_KVE + s), 3);     // both MMA issuers, and the store warp once the dV / dK
+                                           // staged in the finished item's K/V buffer have left
       mbar_init(bar(C::B_SF + s), 1);
       mbar_init(bar(C::B_PF + s), 4);      // one arrival per softmax warp of the half
       mbar_init(bar(C::B_STF + s), 4);
@@ -189,8 +192,9 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(bar(C::B_QF + s), 1);
       mbar_init(bar(C::B_QE + s), 1);
     }
-    mbar_init(bar(C::B_DONE), 1);
+    mbar_init(bar(C::B_DONE), 2);          // both MMA issuers
     mbar_init(bar(C::B_EPI), 8);           // one arrival per softmax warp
+    mbar_init(bar(C::B_STG), 8);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -198,6 +202,8 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmdO);
     tma_prefetch_desc(&tmDQ);
+    tma_prefetch_desc(&tmDK);
+    tma_prefetch_desc(&tmDV);
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
@@ -214,10 +220,10 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   auto sDO = [&](int slot) { return sQ(slot) + C::HALF_BYTES; };                  // half of dO_i
 
   // 512 threads start with 128 registers each.  The first warpgroup (producer, MMA issue) and the
-  // dQ-drain warpgroup hand registers to the two softmax warpgroups: 128 * (104 + 104 + 152 + 152)
+  // dQ-drain warpgroup hand registers to the two softmax warpgroups: 128 * (72 + 72 + 184 + 184)
   // = 65536.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
     if (warp == 0) {
       // -------------------------------------------------------------- producer
       if (lane == 0) {
@@ -247,6 +253,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 ok = false;
                 break;
               }
+              if (blockIdx.x == 0 && p.trace && q_issued < 64) p.trace[1024 + q_issued] = clock64();
               mbar_arrive_expect_tx(bar(C::B_QF + slot), C::SLOT_BYTES);
               tma_load_2d(sQ(slot), &tmQ, bar(C::B_QF + slot), w.h * DH, qrow + hf * HQ);
               tma_load_2d(sDO(slot), &tmdO, bar(C::B_QF + slot), w.h * DH, qrow + hf * HQ);
@@ -291,7 +298,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       constexpr uint64_t SLOT_STEP = C::SLOT_BYTES >> 4;    // ring slot pitch
       constexpr uint64_t DO_STEP = C::HALF_BYTES >> 4;      // dO half after the Q half of a slot
       auto wait_all = [&](int b_idx, uint32_t parity, int where) {
-        const bool got = mbar_wait(bar(b_idx), parity, abort_flag);
+        const bool got = mbar_wait_poll(bar(b_idx), parity, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
           return false;
@@ -325,19 +332,33 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       long long* trace = (blockIdx.x == 0 && lane == 0) ? p.trace : nullptr;
       uint32_t n = 0, g = 0;
       BwdWalk w;
+      // A wait on an mbarrier costs a few hundred clocks even when its phase completed long ago,
+      // so the ring slots are waited for ahead of their use, while this warp has nothing to
+      // issue: qf_waited half-slots (in ring order) have been seen to land, of qf_total in all.
+      uint32_t qf_total = 0;
+      for (w.init(p); w.valid; w.next(p)) qf_total += 2u * static_cast<uint32_t>(w.n_it);
+      uint32_t qf_waited = 0;
+      auto wait_slots = [&](uint32_t upto) {     // ... until half-slots [0, upto) have landed
+        upto = min(upto, qf_total);
+        while (qf_waited < upto) {
+          if (!wait_all(C::B_QF + qf_waited % NSLOT, (qf_waited / NSLOT) & 1u, 1123)) return false;
+          ++qf_waited;
+        }
+        return true;
+      };
       w.init(p);
       bool ok = w.valid;
       if (ok) ok = wait_all(C::B_KVF, 0, 1120);
-      if (ok) ok = wait_all(C::B_QF + 0, 0, 1121);
-      if (ok) ok = wait_all(C::B_QF + 1, 0, 1121);
+      if (ok) ok = wait_slots(2);
       if (ok) {
         tc_fence_after();
-        if (trace) trace[16 + 14] = clock64();
+        if (trace) trace[1090] = clock64();
         if (elect_one()) {
           scores(0, 0, 0);
           scores(1, 1, 0);
         }
         __syncwarp();
+        ok = wait_slots(4);
       }
       while (ok && w.valid) {
         const bool has_next = w.peek(p).valid;
@@ -351,25 +372,27 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const uint32_t nslot0 = un % NSLOT, nslot1 = (un + 1) % NSLOT;
           // ---- first half: its products, then the next step's scores over the same columns
           if (!wait_all(C::B_PF + 0, g & 1u, 1122)) { ok = false; break; }
+          if (trace && g < 32) trace[512 + g * 8 + 0] = clock64();
           // the first products of an item overwrite dV / dK: the previous item's must have left
           if (it == 0 && n > 0 && !wait_all(C::B_EPI, (n - 1) & 1u, 1126)) { ok = false; break; }
           if (more) {
             if (last && !wait_all(C::B_KVF + nkb, ((n + 1) >> 1) & 1u, 1127)) { ok = false; break; }
-            if (!wait_all(C::B_QF + nslot0, (un / NSLOT) & 1u, 1123)) { ok = false; break; }
+            if (!wait_slots(un + 1)) { ok = false; break; }      // normally seen already
           }
           tc_fence_after();
-          if (trace && g < 16) trace[g * 16 + 6] = clock64();
+          if (trace && g < 32) trace[g * 16 + 6] = clock64();
           if (elect_one()) {
             products(0, slot0, it > 0 ? 1u : 0u);
             if (more) scores(0, nslot0, nkb);
           }
           __syncwarp();
-          if (trace && g < 16) trace[g * 16 + 7] = clock64();
+          if (trace && g < 32) trace[g * 16 + 7] = clock64();
           // ---- second half
           if (!wait_all(C::B_PF + 1, g & 1u, 1124)) { ok = false; break; }
-          if (more && !wait_all(C::B_QF + nslot1, ((un + 1) / NSLOT) & 1u, 1128)) { ok = false; break; }
+          if (trace && g < 32) trace[512 + g * 8 + 1] = clock64();
+          if (more && !wait_slots(un + 2)) { ok = false; break; }
           tc_fence_after();
-          if (trace && g < 16) trace[g * 16 + 8] = clock64();
+          if (trace && g < 32) trace[g * 16 + 8] = clock64();
           if (elect_one()) {
             products(1, slot1, 1u);
             if (last) {
@@ -379,11 +402,39 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (more) scores(1, nslot1, nkb);
           }
           __syncwarp();
-          if (trace && g < 16) trace[g * 16 + 9] = clock64();
+          if (trace && g < 32) trace[g * 16 + 9] = clock64();
+          // nothing to issue until the softmax of the next step is through: the slots of the step
+          // after it
+          if (!wait_slots(un + 4)) { ok = false; break; }
         }
         w.next(p);
         ++n;
       }
+    } else if (warp == 3) {
+      // -------------------------------------------------------------- dV / dK store
+      // The softmax warps stage an item's dV / dK in its K / V tiles; this warp (which has nothing
+      // else to do and whose waits hold nobody up) stores the two tiles in bulk and hands the
+      // K/V buffer back to the producer once the stores have read it.
+      if (lane == 0) {
+        uint32_t n = 0;
+        bool stored = false;
+        BwdWalk w;
+        for (w.init(p); w.valid; w.next(p), ++n) {
+          if (!mbar_wait(bar(C::B_STG), n & 1u, abort_flag)) {
+            record_status(p.status, ST_WAIT_TIMEOUT, 1160);
+            break;
+          }
+          const int kb = n & 1;
+          tma_store_3d(&tmDV, sK(kb), w.h * DH, w.j * BKV, w.b);
+          tma_store_3d(&tmDK, sV(kb), w.h * DH, w.j * BKV, w.b);
+          tma_store_commit();
+          tma_store_wait_read_all();
+          mbar_arrive(bar(C::B_KVE + kb));
+          stored = true;
+        }
+        if (stored) tma_store_wait_all();
+      }
+      __syncwarp();
     } else if (warp == 2) {
       // -------------------------------------------------------------- MMA issuer: dQ
       // dQ_i = dS . K_j over the whole tile (dS^T from shared memory as the transposed operand),
@@ -397,7 +448,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       constexpr uint64_t KB_STEP = (2 * C::KV_BYTES) >> 4;
       constexpr uint64_t BUF_STEP = C::DST_BYTES >> 4;
       auto wait_all = [&](int b_idx, uint32_t parity, int where) {
-        const bool got = mbar_wait(bar(b_idx), parity, abort_flag);
+        const bool got = mbar_wait_poll(bar(b_idx), parity, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, where);
           return false;
@@ -417,7 +468,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (ok && g >= 2) ok = wait_all(C::B_DQE + buf, ((g >> 1) - 1) & 1u, 1152);
           if (!ok) break;
           tc_fence_after();
-          if (trace && g < 16) trace[g * 16 + 10] = clock64();
+          if (trace && g < 32) trace[g * 16 + 10] = clock64();
           if (elect_one()) {
             const uint64_t a = dDST_mn0 + buf * BUF_STEP;
             const uint64_t bk = dK_mn0 + kb * KB_STEP;
@@ -427,15 +478,18 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               umma_bf16_ss(d, a + 128 * kk, bk + 128 * kk, idesc_dq, kk > 0 ? 1u : 0u);
             umma_commit(bar(C::B_DQF + buf));
             umma_commit(bar(C::B_DF + buf));
-            if (it + 1 == w.n_it) umma_commit(bar(C::B_KVE + kb));   // K_j is not read any more
+            if (it + 1 == w.n_it) {
+              umma_commit(bar(C::B_KVE + kb));   // K_j is not read any more
+              umma_commit(bar(C::B_DONE));
+            }
           }
           __syncwarp();
-          if (trace && g < 16) trace[g * 16 + 11] = clock64();
+          if (trace && g < 32) trace[g * 16 + 11] = clock64();
         }
       }
     }
   } else if (warp < 12) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 152;" ::: "memory");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;" ::: "memory");
     // ---------------------------------------------------------------- softmax / dS of one half
     const int hf = (warp - 4) >> 2;
     const int quarter = warp & 3;
@@ -452,45 +506,47 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (gt < 64) return qi < p.S ? p.lse[stat_base + qi] * 1.4426950408889634f : INFINITY;
       return qi < p.S ? p.delta[stat_base + qi] : 0.f;
     };
-    // dV (first half's warps) or dK (second half's) of a finished item: tensor memory -> bf16 rows
-    auto epilogue = [&](int b, int h, int j, uint32_t n_done) {
+    // dV (first half's warps) or dK (second half's) of a finished item: tensor memory -> bf16 ->
+    // the finished item's K (for dV) or V (for dK) tile in shared memory, which nothing reads any
+    // more and which has the very layout of a 64-column swizzled store tile; warp 3 stores it in
+    // bulk (a row per thread straight to global memory takes 32 separate 16-byte segments per
+    // instruction and kept the load/store pipe busy for ~2000 clocks per item).
+    auto epilogue = [&](uint32_t n_done) {
       const bool got = mbar_wait(bar(C::B_DONE), n_done & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1131);
         return false;
       }
       tc_fence_after();
-      const int kv_idx = j * BKV + r;
-      const bool row_ok = kv_idx < p.S;
-      const size_t orow = (static_cast<size_t>(b) * p.S + kv_idx) * p.ldd + static_cast<size_t>(h) * DH;
-      __nv_bfloat16* dst = (hf == 0 ? p.dv : p.dk) + orow;
       const float mul = hf == 0 ? 1.0f : p.scale;
       const int col = hf == 0 ? C::DV_COL : C::DK_COL;
-#pragma unroll 1
-      for (int ch = 0; ch < DH / 32; ++ch) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(lane_addr + col + ch * 32, o);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(o[8 * gq + 0]) * mul, __uint_as_float(o[8 * gq + 1]) * mul);
-            v.y = pack_bf16x2(__uint_as_float(o[8 * gq + 2]) * mul, __uint_as_float(o[8 * gq + 3]) * mul);
-            v.z = pack_bf16x2(__uint_as_float(o[8 * gq + 4]) * mul, __uint_as_float(o[8 * gq + 5]) * mul);
-            v.w = pack_bf16x2(__uint_as_float(o[8 * gq + 6]) * mul, __uint_as_float(o[8 * gq + 7]) * mul);
-            *reinterpret_cast<uint4*>(dst + ch * 32 + gq * 8) = v;
-          }
-        }
-      }
+      const uint32_t tile = (hf == 0 ? sK(n_done & 1) : sV(n_done & 1)) + quarter * 4096;
+      const uint32_t trow = tile + lane * 128;
+      uint32_t o0[32], o1[32];
+      tmem_ld_32x32b_x32(lane_addr + col, o0);
+      tmem_ld_32x32b_x32(lane_addr + col + 32, o1);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::B_EPI));
+      if (lane == 0) mbar_arrive(bar(C::B_EPI));       // dV / dK may be overwritten
+#pragma unroll
+      for (int gq = 0; gq < 8; ++gq) {
+        const uint32_t* o = gq < 4 ? o0 + 8 * gq : o1 + 8 * (gq - 4);
+        const uint32_t v0 = pack_bf16x2(__uint_as_float(o[0]) * mul, __uint_as_float(o[1]) * mul);
+        const uint32_t v1 = pack_bf16x2(__uint_as_float(o[2]) * mul, __uint_as_float(o[3]) * mul);
+        const uint32_t v2 = pack_bf16x2(__uint_as_float(o[4]) * mul, __uint_as_float(o[5]) * mul);
+        const uint32_t v3 = pack_bf16x2(__uint_as_float(o[6]) * mul, __uint_as_float(o[7]) * mul);
+        const uint32_t sw = static_cast<uint32_t>(gq ^ (lane & 7)) << 4;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(trow + sw), "r"(v0), "r"(v1),
+                     "r"(v2), "r"(v3) : "memory");
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::B_STG));       // warp 3 stores the tile
       return true;
     };
     uint32_t n = 0, g = 0;
     bool ok = true;
-    int pb = 0, ph = 0, pj = 0;               // the previous item, whose epilogue is still due
     BwdWalk w;
     w.init(p);
     float stat_next = w.valid ? load_stat(w, 0) : 0.f;
@@ -513,49 +569,56 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_STF + hf));
         bool got = mbar_wait(bar(C::B_STF + hf), g & 1u, abort_flag);
-        if (got) got = mbar_wait(bar(C::B_SF + hf), g & 1u, abort_flag);
         // the dS^T buffer of this parity was last read by the dQ product of step g - 2
         if (got && g > 1) got = mbar_wait(bar(C::B_DF + (g & 1)), ((g >> 1) - 1) & 1u, abort_flag);
+        // the scores last: they are what this step is really waiting for, and every wait costs a
+        // few hundred clocks even when its phase completed long ago
+        if (got) got = mbar_wait_poll(bar(C::B_SF + hf), g & 1u, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) record_status(p.status, ST_WAIT_TIMEOUT, 1130);
           ok = false;
           break;
         }
         tc_fence_after();
-        long long* tr = (blockIdx.x == 0 && g < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
+        long long* tr = (blockIdx.x == 0 && g < 32 && quarter == 0 && lane == 0) ? p.trace : nullptr;
         if (tr) tr[g * 16 + hf * 3] = clock64();
         const bool mask = (p.causal && kv0 + BKV - 1 > q0) || (kv0 + BKV > p.S);
         // dS^T in shared memory: two groups of 64 query columns, each [128 K/V rows][128 bytes],
         // 128-byte swizzled (the layout the dQ product reads as a transposed A operand)
         const uint32_t srow = sDST(g & 1) + hf * (BKV * 128) + r * 128;
-        // four chunks of 16 query columns; the next chunk's loads are in flight during a chunk's
-        // arithmetic.  P^T / dS^T (packed, 8 columns) go over columns whose scores were read before.
-        uint32_t sc[2][16], dc[2][16];
-        tmem_ld_32x32b_x16(s_addr, sc[0]);
-        tmem_ld_32x32b_x16(d_addr, dc[0]);
+        // two chunks of 32 query columns; the second chunk's loads are in flight during the first
+        // chunk's arithmetic.  P^T / dS^T (packed, 16 columns) go over columns read before.
+        uint32_t s0[32], d0[32], s1[32], d1[32];
+        tmem_ld_32x32b_x32(s_addr, s0);
+        tmem_ld_32x32b_x32(d_addr, d0);
         tmem_ld_wait();
+        tmem_ld_32x32b_x32(s_addr + 32, s1);
+        tmem_ld_32x32b_x32(d_addr + 32, d1);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t pk[8], dk[8];
-          if (ch < 3) {
-            tmem_ld_32x32b_x16(s_addr + (ch + 1) * 16, sc[(ch + 1) & 1]);
-            tmem_ld_32x32b_x16(d_addr + (ch + 1) * 16, dc[(ch + 1) & 1]);
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t pk[16], dk[16];
+          const uint32_t* sv = ch ? s1 : s0;
+          const uint32_t* dv = ch ? d1 : d0;
+          if (ch) tmem_ld_wait();
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            if (mask)
+              bwd_chunk<true>(sv + sub * 16, dv + sub * 16, s_lse + ch * 32 + sub * 16,
+                              s_dl + ch * 32 + sub * 16, c, lim, q0 + hf * HQ + ch * 32 + sub * 16,
+                              pk + sub * 8, dk + sub * 8);
+            else
+              bwd_chunk<false>(sv + sub * 16, dv + sub * 16, s_lse + ch * 32 + sub * 16,
+                               s_dl + ch * 32 + sub * 16, c, lim, 0, pk + sub * 8, dk + sub * 8);
           }
-          if (mask)
-            bwd_chunk<true>(sc[ch & 1], dc[ch & 1], s_lse + ch * 16, s_dl + ch * 16, c, lim,
-                            q0 + hf * HQ + ch * 16, pk, dk);
-          else
-            bwd_chunk<false>(sc[ch & 1], dc[ch & 1], s_lse + ch * 16, s_dl + ch * 16, c, lim, 0, pk, dk);
-          tmem_st_32x32b_x8(s_addr + ch * 8, pk);
-          tmem_st_32x32b_x8(d_addr + ch * 8, dk);
+          tmem_st_32x32b_x16(s_addr + ch * 16, pk);
+          tmem_st_32x32b_x16(d_addr + ch * 16, dk);
 #pragma unroll
-          for (int gq = 0; gq < 2; ++gq) {
-            const uint32_t sw = static_cast<uint32_t>((ch * 2 + gq) ^ (r & 7)) << 4;
+          for (int gq = 0; gq < 4; ++gq) {
+            const uint32_t sw = static_cast<uint32_t>((ch * 4 + gq) ^ (r & 7)) << 4;
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw),
                          "r"(dk[4 * gq]), "r"(dk[4 * gq + 1]), "r"(dk[4 * gq + 2]), "r"(dk[4 * gq + 3])
                          : "memory");
           }
-          if (ch < 3) tmem_ld_wait();
         }
         if (tr) tr[g * 16 + hf * 3 + 1] = clock64();
         tmem_st_wait();
@@ -564,17 +627,18 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_PF + hf));
         if (tr) tr[g * 16 + hf * 3 + 2] = clock64();
+        if (blockIdx.x == 0 && g < 32 && lane == 0 && p.trace)
+          p.trace[512 + 256 * hf + g * 8 + 2 + quarter] = clock64();
         // the previous item's dV / dK leave after this item's first softmax, whose scores were
         // issued while that item was finishing
-        if (it == 0 && n > 0 && !epilogue(pb, ph, pj, n - 1)) { ok = false; break; }
+        if (it == 0 && n > 0 && !epilogue(n - 1)) { ok = false; break; }
       }
-      pb = w.b; ph = w.h; pj = w.j;
       w.next(p);
       ++n;
     }
-    if (ok && n > 0) epilogue(pb, ph, pj, n - 1);
+    if (ok && n > 0) epilogue(n - 1);
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
     // ---------------------------------------------------------------- dQ drain
     // Each warp moves its 32 query rows on its own: tensor memory -> registers -> a swizzled
     // staging tile in shared memory -> bulk reduce-add into the fp32 accumulator (whole 128-byte
@@ -598,7 +662,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           break;
         }
         tc_fence_after();
-        long long* trq = (blockIdx.x == 0 && g < 16 && quarter == 0 && lane == 0) ? p.trace : nullptr;
+        long long* trq = (blockIdx.x == 0 && g < 32 && quarter == 0 && lane == 0) ? p.trace : nullptr;
         if (trq) trq[g * 16 + 12] = clock64();
         const int qrow = (w.i_start(p) + it) * BQ + quarter * 32;
 #pragma unroll 1
@@ -644,14 +708,14 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0 && p.trace) p.trace[15] = clock64();
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.trace) p.trace[1089] = clock64();
 }
 
 }  // namespace
 
 int launch_attn_bwd_dh64(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdArgs& a,
-                         cudaStream_t st) {
+                         const CUtensorMap& tdo, const CUtensorMap& tdq, const CUtensorMap& tdk,
+                         const CUtensorMap& tdv, const AttnBwdArgs& a, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_bwd_dh64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -661,7 +725,8 @@ int launch_attn_bwd_dh64(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   }
   const int n_items = ((a.S + B64::BKV - 1) / B64::BKV) * a.B * a.nh;
   const int grid = n_items < sm_count() ? n_items : sm_count();
-  attn_bwd_dh64_kernel<<<grid, B64::THREADS, B64::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, a);
+  attn_bwd_dh64_kernel<<<grid, B64::THREADS, B64::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv,
+                                                                    a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

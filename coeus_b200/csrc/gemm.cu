@@ -778,6 +778,25 @@ int make_tmap_f32_3d(CUtensorMap* out, void* base, uint64_t d0, uint64_t d1, uin
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// 3-D bf16 tensor map (inner `d0` contiguous elements, then `d1` rows of pitch ld1 elements, then
+// `d2` slabs of pitch ld2 elements) with a box of 64 x box1 x 1, 128-byte swizzle: tiles of one
+// sequence that must not run into the next one.
+int make_tmap_bf16_3d(CUtensorMap* out, void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                      uint64_t ld1, uint64_t ld2, uint32_t box1) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld1 * 2) % 16 != 0 || (ld2 * 2) % 16 != 0)
+    return -2;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {ld1 * 2, ld2 * 2};
+  cuuint32_t box[3] = {64, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {

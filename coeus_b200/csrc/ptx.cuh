@@ -101,15 +101,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
-// The same wait by plain polling (test_wait only, no suspension): for a warp with nothing else to
-// do whose reaction time is on the critical path -- a suspended try_wait wakes up some hundreds
-// of clocks after the phase completes.
+// The same wait by polling with a short sleep between polls (test_wait only, no suspension): for
+// waits whose reaction time is on the critical path -- a suspended try_wait was seen to resume
+// some hundreds of clocks after the phase completed, while a poll loop without the sleep takes
+// issue slots from the working warps of its scheduler.
 __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity,
                                                volatile uint32_t* abort_flag) {
   if (mbar_test_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t n = 0;
   while (true) {
+    asm volatile("nanosleep.u32 20;" ::: "memory");
     if (mbar_test_wait(bar, parity)) return true;
     if ((++n & 255u) == 0u) {
       if (*abort_flag) return false;
@@ -166,6 +168,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+// 3-D tiled store shared -> global (bulk group completion); rows beyond the tensor are dropped.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int x, int y,
+                                             int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
 // 3-D tiled reduce-add shared -> global (the element type comes from the tensor map; bulk group
