@@ -45,6 +45,7 @@ namespace {
 struct B64 {
   static constexpr int DH = 64, BQ = 128, BKV = 128, HQ = 64;
   static constexpr int THREADS = 512;
+  static constexpr bool DQ_OWN_WARP = true;               // dQ issued by warp 2 (else by warp 1)
   static constexpr int NSLOT = 5;                         // ring of half-tile slots (2.5 steps)
   static constexpr int KV_BYTES = BKV * DH * 2;           // K_j or V_j
   static constexpr int HALF_BYTES = HQ * DH * 2;          // 64 query rows of Q_i or dO_i
@@ -179,7 +180,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::B_KVF + s), 1);
-      mbar_init(bar(C::B_KVE + s), 3);     // both MMA issuers, and the store warp once the dV / dK
+      mbar_init(bar(C::B_KVE + s), C::DQ_OWN_WARP ? 3 : 2);     // both MMA issuers, and the store warp once the dV / dK
                                            // staged in the finished item's K/V buffer have left
       mbar_init(bar(C::B_SF + s), 1);
       mbar_init(bar(C::B_PF + s), 4);      // one arrival per softmax warp of the half
@@ -192,7 +193,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(bar(C::B_QF + s), 1);
       mbar_init(bar(C::B_QE + s), 1);
     }
-    mbar_init(bar(C::B_DONE), 2);          // both MMA issuers
+    mbar_init(bar(C::B_DONE), C::DQ_OWN_WARP ? 2 : 1);   // the MMA issuer(s)
     mbar_init(bar(C::B_EPI), 8);           // one arrival per softmax warp
     mbar_init(bar(C::B_STG), 8);
     *abort_flag = 0;
@@ -387,6 +388,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
           __syncwarp();
           if (trace && g < 32) trace[g * 16 + 7] = clock64();
+          if (more && !wait_slots(un + 2)) { ok = false; break; }   // ahead of its use just below
           // ---- second half
           if (!wait_all(C::B_PF + 1, g & 1u, 1124)) { ok = false; break; }
           if (trace && g < 32) trace[512 + g * 8 + 1] = clock64();
@@ -395,7 +397,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (trace && g < 32) trace[g * 16 + 8] = clock64();
           if (elect_one()) {
             products(1, slot1, 1u);
-            if (last) {
+            if (C::DQ_OWN_WARP && last) {
               umma_commit(bar(C::B_KVE + kb));   // no score product reads this K/V buffer any more
               umma_commit(bar(C::B_DONE));       // dV / dK of the item are complete
             }
@@ -403,9 +405,35 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
           __syncwarp();
           if (trace && g < 32) trace[g * 16 + 9] = clock64();
-          // nothing to issue until the softmax of the next step is through: the slots of the step
-          // after it
-          if (!wait_slots(un + 4)) { ok = false; break; }
+          if constexpr (!C::DQ_OWN_WARP) {
+            // ---- dQ_i = dS . K_j over the whole tile, into the dQ buffer of this parity
+            const int buf = g & 1;
+            if (g >= 2) {
+              if (!wait_all(C::B_DQE + buf, ((g >> 1) - 1) & 1u, 1125)) { ok = false; break; }
+              tc_fence_after();
+            }
+            if (trace && g < 32) trace[g * 16 + 10] = clock64();
+            if (elect_one()) {
+              const uint64_t a = d_base + MN + (C::OFF_DST >> 4) + buf * (C::DST_BYTES >> 4);
+              const uint64_t bk = dK_k0 + MN + kb * KB_STEP;
+              const uint32_t d = tmem_u + C::DQ_COL + buf * DH;
+              constexpr uint32_t idesc_dq = umma_idesc_bf16(BQ, DH, 1, 1);
+#pragma unroll
+              for (int kk = 0; kk < BKV / 16; ++kk)
+                umma_bf16_ss(d, a + 128 * kk, bk + 128 * kk, idesc_dq, kk > 0 ? 1u : 0u);
+              umma_commit(bar(C::B_DQF + buf));
+              umma_commit(bar(C::B_DF + buf));
+              if (last) {
+                umma_commit(bar(C::B_KVE + kb));
+                umma_commit(bar(C::B_DONE));
+              }
+            }
+            __syncwarp();
+            if (trace && g < 32) trace[g * 16 + 11] = clock64();
+          }
+          // nothing to issue until the softmax of the next step is through: the first slot of the
+          // step after it (the second one was freed just now and is still being refilled)
+          if (!wait_slots(un + 3)) { ok = false; break; }
         }
         w.next(p);
         ++n;
@@ -435,7 +463,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (stored) tma_store_wait_all();
       }
       __syncwarp();
-    } else if (warp == 2) {
+    } else if (warp == 2 && C::DQ_OWN_WARP) {
       // -------------------------------------------------------------- MMA issuer: dQ
       // dQ_i = dS . K_j over the whole tile (dS^T from shared memory as the transposed operand),
       // into the dQ buffer of the step's parity, once both halves' dS^T are written.
