@@ -418,6 +418,43 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int 
   if (blockIdx.x * 256 + c < C) atomicAdd(out + blockIdx.x * 256 + c, s);
 }
 
+// dx = dy * gelu'(x) and out[c] += sum_t dx[t, c] (the bf16 values that are stored) in one pass:
+// the bias gradient of the layer that produced x needs no second read of dx.  x, dy, dx are
+// [T, C] contiguous.
+__global__ void __launch_bounds__(COLSUM_THREADS)
+gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ out, int T, int C,
+                       int rows_per_block) {
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(T, r0 + rows_per_block);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col < C) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      const size_t off = static_cast<size_t>(r) * C + col;
+      float v[8], d[8];
+      load8(x + off, v);
+      load8(dy + off, d);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[e] = __bfloat162float(__float2bfloat16(d[e] * gelu_tanh_grad(v[e])));
+        acc[e] += v[e];
+      }
+      store8(dx + off, v);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[warp][lane * 8 + e] = acc[e];
+  __syncthreads();
+  const int c = threadIdx.x;
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) s += red[w][c];
+  if (blockIdx.x * 256 + c < C) atomicAdd(out + blockIdx.x * 256 + c, s);
+}
+
 // ------------------------------------------------------------------------------ init / casts
 // p[i] = clamp(sin(float(i) * 0.1234567) * sqrt(2/H), -0.1, 0.1)   (lib.rs:604-611); the index
 // is converted to fp32 first, exactly like the reference's `i as f32`.
@@ -606,6 +643,20 @@ extern "C" int cb_rope_dev(void* x, int T, int nheads, int dh, int ld, int S, co
   rope_kernel<<<grid_for(static_cast<size_t>(T) * nheads * (dh / 2), 256), 256, 0,
                 CB_ST(stream)>>>(static_cast<__nv_bfloat16*>(x), T, nheads, dh, ld, S, 0, pos_dev,
                                  theta, inverse);
+  CB_RET();
+}
+extern "C" int cb_gelu_bwd_colsum(const void* x, const void* dy, void* dx, float* out, int T, int C,
+                                  void* stream) {
+  if (C % 8 != 0 || T <= 0) return -1;
+  const int col_groups = (C + 255) / 256;
+  int row_chunks = (sm_count() * 4 + col_groups - 1) / col_groups;
+  if (row_chunks > (T + 63) / 64) row_chunks = (T + 63) / 64;
+  if (row_chunks < 1) row_chunks = 1;
+  const int rpb = (T + row_chunks - 1) / row_chunks;
+  dim3 grid(col_groups, (T + rpb - 1) / rpb);
+  gelu_bwd_colsum_kernel<<<grid, COLSUM_THREADS, 0, CB_ST(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
+      static_cast<__nv_bfloat16*>(dx), out, T, C, rpb);
   CB_RET();
 }
 extern "C" int cb_colsum(const void* x, float* out, int T, int C, int ld, void* stream) {

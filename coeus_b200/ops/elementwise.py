@@ -221,13 +221,27 @@ def gelu_fwd(x: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def gelu_bwd(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+def gelu_bwd(x: torch.Tensor, dy: torch.Tensor, colsum: Optional[torch.Tensor] = None
+             ) -> torch.Tensor:
+    """``dx = dy * gelu'(x)``.  With ``colsum`` (fp32 ``[C]``) the column sums of ``dx`` are added
+    to it in the same pass: the bias gradient of the projection that produced ``x``."""
     if not x.is_cuda:
-        return (dy.float() * _gelu_grad_ref(x.float())).to(x.dtype)
+        dx = (dy.float() * _gelu_grad_ref(x.float())).to(x.dtype)
+        if colsum is not None:
+            colsum.add_(dx.float().sum(0))
+        return dx
     dx = torch.empty_like(x)
+    if colsum is not None and x.dim() == 2 and x.is_contiguous() and dy.is_contiguous():
+        rc = _lib.lib().cb_gelu_bwd_colsum(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dx),
+                                           _lib.ptr(colsum), x.shape[0], x.shape[1],
+                                           _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_gelu_bwd_colsum")
+        return dx
     rc = _lib.lib().cb_gelu_bwd(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dx), c_size_t(x.numel()),
                                 _lib.stream_ptr())
     _lib.check_rc(rc, "cb_gelu_bwd")
+    if colsum is not None:
+        colsum_into(dx, colsum)
     return dx
 
 

@@ -179,6 +179,11 @@ def test_activations_softmax_rope_colsum_init():
     dy = _bf(torch.randn(333, 512, device=DEV))
     assert (E.gelu_fwd(x).float().cpu() - E.gelu_fwd(x.cpu()).float()).abs().max() < 0.02
     assert (E.gelu_bwd(x, dy).float().cpu() - E.gelu_bwd(x.cpu(), dy.cpu()).float()).abs().max() < 0.03
+    # the same with the column sums of the result (a bias gradient) added in the same pass
+    acc = torch.full((512,), 0.5, device=DEV)
+    dxf = E.gelu_bwd(x, dy, acc)
+    assert torch.equal(dxf, E.gelu_bwd(x, dy))
+    assert (acc.cpu() - 0.5 - dxf.float().cpu().sum(0)).abs().max() < 1e-2
     gu = _bf(torch.randn(100, 1024, device=DEV))
     d2 = _bf(torch.randn(100, 512, device=DEV))
     assert (E.swiglu_fwd(gu).float().cpu() - E.swiglu_fwd(gu.cpu()).float()).abs().max() < 0.03
