@@ -401,11 +401,24 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int 
   const int r1 = min(T, r0 + rows_per_block);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col < C) {
-    for (int r = r0 + warp; r < r1; r += 8) {
-      float v[8];
-      load8(x + static_cast<size_t>(r) * ld + col, v);
+    // four rows per warp and trip: four 16-byte loads in flight per thread
+    for (int r = r0 + warp; r < r1; r += 32) {
+      bf16x8 xv[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+      for (int k = 0; k < 4; ++k)
+        if (r + 8 * k < r1)
+          xv[k] = *reinterpret_cast<const bf16x8*>(x + static_cast<size_t>(r + 8 * k) * ld + col);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (r + 8 * k < r1) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 q = __bfloat1622float2(xv[k].v[e]);
+            acc[2 * e] += q.x;
+            acc[2 * e + 1] += q.y;
+          }
+        }
+      }
     }
   }
 #pragma unroll
@@ -420,39 +433,50 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int 
 
 // dx = dy * gelu'(x) and out[c] += sum_t dx[t, c] (the bf16 values that are stored) in one pass:
 // the bias gradient of the layer that produced x needs no second read of dx.  x, dy, dx are
-// [T, C] contiguous.
+// [T, C] contiguous.  A block covers 2048 adjacent columns of one row at a time (4 KB per
+// operand, in address order across the block) and strides over the rows, four rows per trip;
+// each thread keeps the sums of its eight columns and adds them to `out` at the end.
 __global__ void __launch_bounds__(COLSUM_THREADS)
 gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
-                       __nv_bfloat16* __restrict__ dx, float* __restrict__ out, int T, int C,
-                       int rows_per_block) {
-  __shared__ float red[8][256];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int col = blockIdx.x * 256 + lane * 8;
-  const int r0 = blockIdx.y * rows_per_block;
-  const int r1 = min(T, r0 + rows_per_block);
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ out, int T, int C) {
+  const int col = (blockIdx.x * COLSUM_THREADS + threadIdx.x) * 8;
+  if (col >= C) return;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (col < C) {
-    for (int r = r0 + warp; r < r1; r += 8) {
-      const size_t off = static_cast<size_t>(r) * C + col;
-      float v[8], d[8];
-      load8(x + off, v);
-      load8(dy + off, d);
+  const int stride = gridDim.y;
+  for (int r = blockIdx.y; r < T; r += 4 * stride) {
+    bf16x8 xv[4], dv[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        v[e] = __bfloat162float(__float2bfloat16(d[e] * gelu_tanh_grad(v[e])));
-        acc[e] += v[e];
+    for (int k = 0; k < 4; ++k) {
+      const int rr = r + k * stride;
+      if (rr < T) {
+        const size_t off = static_cast<size_t>(rr) * C + col;
+        xv[k] = *reinterpret_cast<const bf16x8*>(x + off);
+        dv[k] = *reinterpret_cast<const bf16x8*>(dy + off);
       }
-      store8(dx + off, v);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int rr = r + k * stride;
+      if (rr < T) {
+        bf16x8 o;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = __bfloat1622float2(xv[k].v[e]);
+          const float2 b = __bfloat1622float2(dv[k].v[e]);
+          o.v[e] = __floats2bfloat162_rn(b.x * gelu_tanh_grad(a.x), b.y * gelu_tanh_grad(a.y));
+          const float2 q = __bfloat1622float2(o.v[e]);
+          acc[2 * e] += q.x;
+          acc[2 * e + 1] += q.y;
+        }
+        *reinterpret_cast<bf16x8*>(dx + static_cast<size_t>(rr) * C + col) = o;
+      }
     }
   }
 #pragma unroll
-  for (int e = 0; e < 8; ++e) red[warp][lane * 8 + e] = acc[e];
-  __syncthreads();
-  const int c = threadIdx.x;
-  float s = 0.f;
-#pragma unroll
-  for (int w = 0; w < 8; ++w) s += red[w][c];
-  if (blockIdx.x * 256 + c < C) atomicAdd(out + blockIdx.x * 256 + c, s);
+  for (int e = 0; e < 8; e += 4)
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(out + col + e), "f"(acc[e]), "f"(acc[e + 1]), "f"(acc[e + 2]), "f"(acc[e + 3])
+                 : "memory");
 }
 
 // ------------------------------------------------------------------------------ init / casts
@@ -648,15 +672,15 @@ extern "C" int cb_rope_dev(void* x, int T, int nheads, int dh, int ld, int S, co
 extern "C" int cb_gelu_bwd_colsum(const void* x, const void* dy, void* dx, float* out, int T, int C,
                                   void* stream) {
   if (C % 8 != 0 || T <= 0) return -1;
-  const int col_groups = (C + 255) / 256;
-  int row_chunks = (sm_count() * 4 + col_groups - 1) / col_groups;
-  if (row_chunks > (T + 63) / 64) row_chunks = (T + 63) / 64;
-  if (row_chunks < 1) row_chunks = 1;
-  const int rpb = (T + row_chunks - 1) / row_chunks;
-  dim3 grid(col_groups, (T + rpb - 1) / rpb);
+  const int col_groups = (C / 8 + COLSUM_THREADS - 1) / COLSUM_THREADS;
+  // two blocks per SM: enough loads in flight for the memory system, and few enough blocks that
+  // their atomic adds on the same `out` entries (one per block and column) do not queue up
+  int row_blocks = (sm_count() * 2 + col_groups - 1) / col_groups;
+  if (row_blocks > T) row_blocks = T;
+  dim3 grid(col_groups, row_blocks);
   gelu_bwd_colsum_kernel<<<grid, COLSUM_THREADS, 0, CB_ST(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
-      static_cast<__nv_bfloat16*>(dx), out, T, C, rpb);
+      static_cast<__nv_bfloat16*>(dx), out, T, C);
   CB_RET();
 }
 extern "C" int cb_colsum(const void* x, float* out, int T, int C, int ld, void* stream) {
