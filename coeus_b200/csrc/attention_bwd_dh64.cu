@@ -24,9 +24,10 @@
 //                 of five slots)
 //   warp 1        MMA issuer: products and scores      warp 2   MMA issuer: dQ
 //   warp 3        stores the staged dV / dK tiles (bulk stores)
-//   warps 4..7    softmax / dS of the first half; dV epilogue (staged in the item's K tile)
-//   warps 8..11   softmax / dS of the second half; dK epilogue (staged in the item's V tile)
-//   warps 12..15  dQ drain (TMEM -> shared memory -> bulk reduce-add into the fp32 accumulator)
+//   warps 4..11   softmax / dS of the first half (two threads per K/V row, 32 query columns each);
+//                 warps 4..7 also the dV epilogue (staged in the item's K tile)
+//   warps 12..19  softmax / dS of the second half; warps 12..15 also the dK epilogue (V tile)
+//   warps 20..23  dQ drain (TMEM -> shared memory -> bulk reduce-add into the fp32 accumulator)
 // delta_i = rowsum(dO_i o O_i) comes from a pre-kernel, a post-kernel scales and casts dQ (both in
 // attention_bwd.cu).  The reference (plugins/model-transformer/src/lib.rs:300-372) computes the
 // attention gradient on the CPU in fp32 with materialised probabilities.
@@ -44,7 +45,8 @@ namespace {
 
 struct B64 {
   static constexpr int DH = 64, BQ = 128, BKV = 128, HQ = 64;
-  static constexpr int THREADS = 512;
+  static constexpr int NSUB = 2;                          // softmax threads per K/V row and half
+  static constexpr int THREADS = 32 * (4 + 2 * NSUB * 4 + 4);
   static constexpr bool DQ_OWN_WARP = true;               // dQ issued by warp 2 (else by warp 1)
   static constexpr int NSLOT = 5;                         // ring of half-tile slots (2.5 steps)
   static constexpr int KV_BYTES = BKV * DH * 2;           // K_j or V_j
@@ -183,8 +185,8 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(bar(C::B_KVE + s), C::DQ_OWN_WARP ? 3 : 2);     // both MMA issuers, and the store warp once the dV / dK
                                            // staged in the finished item's K/V buffer have left
       mbar_init(bar(C::B_SF + s), 1);
-      mbar_init(bar(C::B_PF + s), 4);      // one arrival per softmax warp of the half
-      mbar_init(bar(C::B_STF + s), 4);
+      mbar_init(bar(C::B_PF + s), 4 * C::NSUB);      // one arrival per softmax warp of the half
+      mbar_init(bar(C::B_STF + s), 4 * C::NSUB);
       mbar_init(bar(C::B_DF + s), 1);
       mbar_init(bar(C::B_DQF + s), 1);
       mbar_init(bar(C::B_DQE + s), 4);     // one arrival per dQ-drain warp
@@ -220,11 +222,9 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   auto sQ = [&](int slot) { return sbase + C::OFF_Q + slot * C::SLOT_BYTES; };   // half of Q_i
   auto sDO = [&](int slot) { return sQ(slot) + C::HALF_BYTES; };                  // half of dO_i
 
-  // 512 threads start with 128 registers each.  The first warpgroup (producer, MMA issue) and the
-  // dQ-drain warpgroup hand registers to the two softmax warpgroups: 128 * (72 + 72 + 184 + 184)
-  // = 65536.
+  // 768 threads at 80 registers each: the softmax threads hold one 16-column chunk of S^T and dP^T
+  // at a time, so no role needs registers moved to it.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
     if (warp == 0) {
       // -------------------------------------------------------------- producer
       if (lane == 0) {
@@ -325,8 +325,11 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t pt = tmem_u + hf * 128, dst = pt + 64;
 #pragma unroll
         for (int kk = 0; kk < HQ / 16; ++kk) {
-          umma_bf16_ts(tmem_u + C::DV_COL, pt + kk * 8, bdo + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
-          umma_bf16_ts(tmem_u + C::DK_COL, dst + kk * 8, bq + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
+          // the packed P^T / dS^T of query columns [32 s, 32 s + 32) sit at columns 32 s .. 32 s + 15
+          // of the half's S^T / dP^T (each softmax thread writes over columns it has read itself)
+          const uint32_t ao = static_cast<uint32_t>((kk >> 1) * 32 + (kk & 1) * 8);
+          umma_bf16_ts(tmem_u + C::DV_COL, pt + ao, bdo + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
+          umma_bf16_ts(tmem_u + C::DK_COL, dst + ao, bq + 128 * kk, idesc_pv, kk > 0 ? 1u : acc0);
         }
         umma_commit(bar(C::B_QE + slot));       // the slot may be refilled
       };
@@ -516,21 +519,26 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
       }
     }
-  } else if (warp < 12) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;" ::: "memory");
+  } else if (warp < 4 + 8 * C::NSUB) {
     // ---------------------------------------------------------------- softmax / dS of one half
-    const int hf = (warp - 4) >> 2;
+    // Two threads per K/V row and half, 32 query columns each: four softmax warps per scheduler
+    // hide the tensor-memory and shared-memory latencies of a step by multithreading, where two
+    // threads with 64 columns each could not by instruction-level parallelism alone.
+    const int sw_id = warp - 4;
+    const int hf = sw_id / (4 * C::NSUB);
+    const int sub = (sw_id >> 2) % C::NSUB;   // which 32 of the half's 64 query columns
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;        // K/V row within the tile = tensor-memory lane
-    const int gt = threadIdx.x - 128 - hf * 128;   // 0..127 within the half's warpgroup
+    const int gt = (sw_id % (4 * C::NSUB)) * 32 + lane;   // index within the half's warps
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + hf * 128, d_addr = s_addr + 64;
+    const uint32_t s_addr = lane_addr + hf * 128 + sub * 32, d_addr = s_addr + 64;
     const float c = p.scale_log2;
     // the thread's share of a tile's statistics: lse (times log2 e) of one query column for the
     // first 64 threads, delta of one column for the others
     auto load_stat = [&](const BwdWalk& w, int it) {
       const size_t stat_base = (static_cast<size_t>(w.b) * p.nh + w.h) * p.S;
       const int qi = (w.i_start(p) + it) * BQ + hf * HQ + (gt & 63);
+      if (gt >= 128) return 0.f;
       if (gt < 64) return qi < p.S ? p.lse[stat_base + qi] * 1.4426950408889634f : INFINITY;
       return qi < p.S ? p.delta[stat_base + qi] : 0.f;
     };
@@ -586,7 +594,7 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int q0 = (w.i_start(p) + it) * BQ;
         float* s_lse = s_stat + (g & 1) * 2 * BQ + hf * HQ;
         float* s_dl = s_lse + BQ;
-        (gt < 64 ? s_lse : s_dl)[gt & 63] = stat_next;
+        if (gt < 128) (gt < 64 ? s_lse : s_dl)[gt & 63] = stat_next;
         // the next step's statistics land during this step's work
         if (it + 1 < w.n_it) {
           stat_next = load_stat(w, it + 1);
@@ -608,41 +616,30 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           break;
         }
         tc_fence_after();
-        long long* tr = (blockIdx.x == 0 && g < 32 && quarter == 0 && lane == 0) ? p.trace : nullptr;
+        long long* tr = (blockIdx.x == 0 && g < 32 && quarter == 0 && sub == 0 && lane == 0) ? p.trace : nullptr;
         if (tr) tr[g * 16 + hf * 3] = clock64();
         const bool mask = (p.causal && kv0 + BKV - 1 > q0) || (kv0 + BKV > p.S);
         // dS^T in shared memory: two groups of 64 query columns, each [128 K/V rows][128 bytes],
         // 128-byte swizzled (the layout the dQ product reads as a transposed A operand)
         const uint32_t srow = sDST(g & 1) + hf * (BKV * 128) + r * 128;
-        // two chunks of 32 query columns; the second chunk's loads are in flight during the first
-        // chunk's arithmetic.  P^T / dS^T (packed, 16 columns) go over columns read before.
-        uint32_t s0[32], d0[32], s1[32], d1[32];
-        tmem_ld_32x32b_x32(s_addr, s0);
-        tmem_ld_32x32b_x32(d_addr, d0);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(s_addr + 32, s1);
-        tmem_ld_32x32b_x32(d_addr + 32, d1);
+        // two chunks of 16 query columns.  P^T / dS^T (packed, 8 columns a chunk) go over columns
+        // this thread has read before.
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
-          uint32_t pk[16], dk[16];
-          const uint32_t* sv = ch ? s1 : s0;
-          const uint32_t* dv = ch ? d1 : d0;
-          if (ch) tmem_ld_wait();
+          uint32_t sv[16], dv[16], pk[8], dk[8];
+          tmem_ld_32x32b_x16(s_addr + ch * 16, sv);
+          tmem_ld_32x32b_x16(d_addr + ch * 16, dv);
+          tmem_ld_wait();
+          const int cq = sub * 32 + ch * 16;     // first query column of the chunk within the half
+          if (mask)
+            bwd_chunk<true>(sv, dv, s_lse + cq, s_dl + cq, c, lim, q0 + hf * HQ + cq, pk, dk);
+          else
+            bwd_chunk<false>(sv, dv, s_lse + cq, s_dl + cq, c, lim, 0, pk, dk);
+          tmem_st_32x32b_x8(s_addr + ch * 8, pk);
+          tmem_st_32x32b_x8(d_addr + ch * 8, dk);
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            if (mask)
-              bwd_chunk<true>(sv + sub * 16, dv + sub * 16, s_lse + ch * 32 + sub * 16,
-                              s_dl + ch * 32 + sub * 16, c, lim, q0 + hf * HQ + ch * 32 + sub * 16,
-                              pk + sub * 8, dk + sub * 8);
-            else
-              bwd_chunk<false>(sv + sub * 16, dv + sub * 16, s_lse + ch * 32 + sub * 16,
-                               s_dl + ch * 32 + sub * 16, c, lim, 0, pk + sub * 8, dk + sub * 8);
-          }
-          tmem_st_32x32b_x16(s_addr + ch * 16, pk);
-          tmem_st_32x32b_x16(d_addr + ch * 16, dk);
-#pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            const uint32_t sw = static_cast<uint32_t>((ch * 4 + gq) ^ (r & 7)) << 4;
+          for (int gq = 0; gq < 2; ++gq) {
+            const uint32_t sw = static_cast<uint32_t>((sub * 4 + ch * 2 + gq) ^ (r & 7)) << 4;
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sw),
                          "r"(dk[4 * gq]), "r"(dk[4 * gq + 1]), "r"(dk[4 * gq + 2]), "r"(dk[4 * gq + 3])
                          : "memory");
@@ -655,18 +652,17 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_PF + hf));
         if (tr) tr[g * 16 + hf * 3 + 2] = clock64();
-        if (blockIdx.x == 0 && g < 32 && lane == 0 && p.trace)
+        if (blockIdx.x == 0 && g < 32 && lane == 0 && sub == 0 && p.trace)
           p.trace[512 + 256 * hf + g * 8 + 2 + quarter] = clock64();
         // the previous item's dV / dK leave after this item's first softmax, whose scores were
         // issued while that item was finishing
-        if (it == 0 && n > 0 && !epilogue(n - 1)) { ok = false; break; }
+        if (sub == 0 && it == 0 && n > 0 && !epilogue(n - 1)) { ok = false; break; }
       }
       w.next(p);
       ++n;
     }
-    if (ok && n > 0) epilogue(n - 1);
+    if (sub == 0 && ok && n > 0) epilogue(n - 1);
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
     // ---------------------------------------------------------------- dQ drain
     // Each warp moves its 32 query rows on its own: tensor memory -> registers -> a swizzled
     // staging tile in shared memory -> bulk reduce-add into the fp32 accumulator (whole 128-byte
