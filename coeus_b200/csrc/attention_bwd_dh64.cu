@@ -22,7 +22,7 @@
 //    epilogue of an item runs after the softmax of the next item's first step.
 //   warp 0        TMA producer (K_j, V_j per item, two buffers; Q_i, dO_i by halves through a ring
 //                 of five slots)
-//   warp 1        MMA issuer: products and scores      warp 2   MMA issuer: dQ
+//   warp 1        MMA issuer: products, scores, dQ     warp 2   idle (the dQ issuer if DQ_OWN_WARP)
 //   warp 3        stores the staged dV / dK tiles (bulk stores)
 //   warps 4..11   softmax / dS of the first half (two threads per K/V row, 32 query columns each);
 //                 warps 4..7 also the dV epilogue (staged in the item's K tile)
@@ -47,7 +47,8 @@ struct B64 {
   static constexpr int DH = 64, BQ = 128, BKV = 128, HQ = 64;
   static constexpr int NSUB = 2;                          // softmax threads per K/V row and half
   static constexpr int THREADS = 32 * (4 + 2 * NSUB * 4 + 4);
-  static constexpr bool DQ_OWN_WARP = true;               // dQ issued by warp 2 (else by warp 1)
+  static constexpr bool DQ_OWN_WARP = false;   // dQ issued by warp 2 (else by warp 1, after a
+                                               // step's second half: measured 3 % faster)
   static constexpr int NSLOT = 5;                         // ring of half-tile slots (2.5 steps)
   static constexpr int KV_BYTES = BKV * DH * 2;           // K_j or V_j
   static constexpr int HALF_BYTES = HQ * DH * 2;          // 64 query rows of Q_i or dO_i

@@ -101,17 +101,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
-// The same wait by polling with a short sleep between polls (test_wait only, no suspension): for
-// waits whose reaction time is on the critical path -- a suspended try_wait was seen to resume
-// some hundreds of clocks after the phase completed, while a poll loop without the sleep takes
-// issue slots from the working warps of its scheduler.
+// The same wait by plain polling (test_wait only, no suspension), for waits whose reaction time
+// is on a kernel's critical path (measured against the suspending form and against polling with
+// a nanosleep between polls in the attention backward kernel: ~1 % faster than either).
 __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity,
                                                volatile uint32_t* abort_flag) {
   if (mbar_test_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t n = 0;
   while (true) {
-    asm volatile("nanosleep.u32 20;" ::: "memory");
     if (mbar_test_wait(bar, parity)) return true;
     if ((++n & 255u) == 0u) {
       if (*abort_flag) return false;
