@@ -606,8 +606,11 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_STF + hf));
         bool got = mbar_wait(bar(C::B_STF + hf), g & 1u, abort_flag);
-        // the dS^T buffer of this parity was last read by the dQ product of step g - 2
-        if (got && g > 1) got = mbar_wait(bar(C::B_DF + (g & 1)), ((g >> 1) - 1) & 1u, abort_flag);
+        // The dS^T buffer of this parity was last read by the dQ product of step g - 2.  When one
+        // warp issues all MMAs that product was issued before this step's scores and has completed
+        // before them (a thread's MMAs complete in issue order): no wait of its own.
+        if (C::DQ_OWN_WARP && got && g > 1)
+          got = mbar_wait(bar(C::B_DF + (g & 1)), ((g >> 1) - 1) & 1u, abort_flag);
         // the scores last: they are what this step is really waiting for, and every wait costs a
         // few hundred clocks even when its phase completed long ago
         if (got) got = mbar_wait_poll(bar(C::B_SF + hf), g & 1u, abort_flag);
