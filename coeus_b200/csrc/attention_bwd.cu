@@ -112,7 +112,7 @@ __global__ void attn_dq_finalize_kernel(const float* __restrict__ acc,
   }
 }
 
-template <int DH>
+template <int DH, bool DROP>
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -382,9 +382,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           float p1 = fast_exp2(__uint_as_float(sv[e + 1]) * p.scale_log2 - s_lse[qc + 1]);
           if (row_dead || (diag && kv_idx > q0 + qc)) p0 = 0.f;
           if (row_dead || (diag && kv_idx > q0 + qc + 1)) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dv[e]) - s_dl[qc]);
-          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - s_dl[qc + 1]);
-          pk[e >> 1] = pack_bf16x2(p0, p1);
+          float m0 = 1.f, m1 = 1.f;
+          if constexpr (DROP) {
+            // the forward pass's mask: element (query, key) of the [B nh S, S] probability matrix
+            const unsigned long long gq =
+                ((static_cast<unsigned long long>(b) * p.nh + h) * p.S + (q0 + qc)) *
+                    static_cast<unsigned long long>(p.S >> 2) + static_cast<unsigned long long>(kv_idx >> 2);
+            m0 = dropout_factor(dropout_bits(gq, p.drop_key), kv_idx & 3, p.drop_thr, p.drop_scale);
+            m1 = dropout_factor(dropout_bits(gq + (p.S >> 2), p.drop_key), kv_idx & 3, p.drop_thr,
+                                p.drop_scale);
+          }
+          const float d0 = p0 * (__uint_as_float(dv[e]) * m0 - s_dl[qc]);
+          const float d1 = p1 * (__uint_as_float(dv[e + 1]) * m1 - s_dl[qc + 1]);
+          pk[e >> 1] = pack_bf16x2(p0 * m0, p1 * m1);
           dk[e >> 1] = pack_bf16x2(d0, d1);
         }
         const uint32_t off = ((c * 32) / 64) * (BKV * 128) + r * 128;
@@ -507,20 +517,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-template <int DH>
+template <int DH, bool DROP>
 static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const CUtensorMap& tdo, const AttnBwdArgs& a, cudaStream_t st) {
   using Cfg = AttnBwdCfg<DH>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attn_bwd_kernel<DH, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
       return -10;
     configured = true;
   }
   const int n_kv_tiles = (a.S + ATB_BKV - 1) / ATB_BKV;
-  attn_bwd_kernel<DH><<<n_kv_tiles * a.B * a.nh, ATB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv,
-                                                                                    tdo, a);
+  attn_bwd_kernel<DH, DROP><<<n_kv_tiles * a.B * a.nh, ATB_THREADS, Cfg::SMEM_BYTES, st>>>(
+      tq, tk, tv, tdo, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -533,14 +543,16 @@ extern "C" int cb_attn_bwd_set_trace(long long* device_buffer) {
   return 0;
 }
 
-extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const void* v,
-                           const void* o, const float* lse, float* delta, float* dq_acc,
-                           void* dqkv, int B, int S, int nh, int dh, int lddo, int ldq, int ldk,
-                           int ldv, int ldo, int ldd, float scale, int causal, int* status,
-                           void* stream) {
+// drop_thr in [0, 255] and drop_key: the dropout of the forward pass (0: none; else S % 4 == 0).
+extern "C" int cb_attn_bwd_dropout(const void* dO, const void* q, const void* k, const void* v,
+                                   const void* o, const float* lse, float* delta, float* dq_acc,
+                                   void* dqkv, int B, int S, int nh, int dh, int lddo, int ldq,
+                                   int ldk, int ldv, int ldo, int ldd, float scale, int causal,
+                                   int drop_thr, unsigned int drop_key, int* status, void* stream) {
   using namespace cb;
   if (dh != 64 && dh != 128) return -1;
   if (B <= 0 || S <= 0 || nh <= 0 || (ldd % 8) != 0) return -2;
+  if (drop_thr < 0 || drop_thr > 255 || (drop_thr > 0 && (S % 4) != 0)) return -13;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int H = nh * dh;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
@@ -578,8 +590,12 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
   a.causal = causal;
   a.status = status;
   a.trace = g_attn_bwd_trace_host;
+  a.drop_thr = drop_thr;
+  a.drop_key = drop_key;
+  a.drop_scale = 256.0f / static_cast<float>(256 - drop_thr);
   int rc = dh == 64 ? launch_attn_bwd_dh64(tq, tk, tv, tdo, tdq, tdk, tdv, a, st)
-                    : launch_attn_bwd<128>(tq, tk, tv, tdo, a, st);
+           : drop_thr > 0 ? launch_attn_bwd<128, true>(tq, tk, tv, tdo, a, st)
+                          : launch_attn_bwd<128, false>(tq, tk, tv, tdo, a, st);
   if (rc != 0) return rc;
   {
     const size_t work = rows * (H / 8);
@@ -588,6 +604,15 @@ extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const v
                                                     rows, H, ldd, scale);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+extern "C" int cb_attn_bwd(const void* dO, const void* q, const void* k, const void* v,
+                           const void* o, const float* lse, float* delta, float* dq_acc,
+                           void* dqkv, int B, int S, int nh, int dh, int lddo, int ldq, int ldk,
+                           int ldv, int ldo, int ldd, float scale, int causal, int* status,
+                           void* stream) {
+  return cb_attn_bwd_dropout(dO, q, k, v, o, lse, delta, dq_acc, dqkv, B, S, nh, dh, lddo, ldq, ldk,
+                             ldv, ldo, ldd, scale, causal, 0, 0u, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------

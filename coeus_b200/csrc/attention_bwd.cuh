@@ -20,6 +20,11 @@ struct AttnBwdArgs {
   int causal;
   int* status;
   long long* trace;     // optional timeline of block 0 (a debugging aid), else nullptr
+  // dropout on the probabilities (drop_thr = 0: none), the mask of the forward pass: element
+  // (query q, key kv) of head (b, h) has index ((b nh + h) S + q) S + kv, S % 4 == 0
+  int drop_thr;
+  uint32_t drop_key;
+  float drop_scale;
 };
 
 // Head dimension 64 (attention_bwd_dh64.cu).
@@ -28,5 +33,6 @@ struct AttnBwdArgs {
 int launch_attn_bwd_dh64(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const CUtensorMap& tdo, const CUtensorMap& tdq, const CUtensorMap& tdk,
                          const CUtensorMap& tdv, const AttnBwdArgs& a, cudaStream_t st);
+// (with a.drop_thr > 0 the kernels apply the forward pass's dropout mask)
 
 }  // namespace cb

@@ -127,11 +127,18 @@ struct BwdWalk {
 };
 
 // One 16-column chunk of a half: p = exp2(s c - lse), ds = p (dp - delta), both packed to bf16.
-// `lim` > query index hides the element (causal mask and rows beyond the sequence).
-template <bool MASK>
+// `lim` > query index hides the element (causal mask and rows beyond the sequence).  With DROP
+// the forward pass's dropout is applied: P^T holds the dropped probabilities (the dV operand),
+// dS = p (m dp - delta) with m = 0 or the keep scale; `g0` is the hash group of the chunk's first
+// query column for this thread's key (consecutive queries are `gstep` groups apart), `lane4` the
+// key's byte within its group.
+template <bool MASK, bool DROP>
 __device__ __forceinline__ void bwd_chunk(const uint32_t* sv, const uint32_t* dv,
                                           const float* s_lse, const float* s_dl, float c, int lim,
-                                          int q_first, uint32_t* pk, uint32_t* dk) {
+                                          int q_first, uint32_t* pk, uint32_t* dk,
+                                          unsigned long long g0 = 0, unsigned long long gstep = 0,
+                                          int lane4 = 0, int thr = 0, uint32_t key = 0,
+                                          float dscale = 1.f) {
 #pragma unroll
   for (int e = 0; e < 16; e += 4) {
     const float4 L = *reinterpret_cast<const float4*>(s_lse + e);
@@ -146,18 +153,26 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* sv, const uint32_t* dv
       if (lim > q_first + e + 2) p2 = 0.f;
       if (lim > q_first + e + 3) p3 = 0.f;
     }
-    const float d0 = p0 * (__uint_as_float(dv[e]) - D.x);
-    const float d1 = p1 * (__uint_as_float(dv[e + 1]) - D.y);
-    const float d2 = p2 * (__uint_as_float(dv[e + 2]) - D.z);
-    const float d3 = p3 * (__uint_as_float(dv[e + 3]) - D.w);
-    pk[e >> 1] = pack_bf16x2(p0, p1);
-    pk[(e >> 1) + 1] = pack_bf16x2(p2, p3);
+    float m0 = 1.f, m1 = 1.f, m2 = 1.f, m3 = 1.f;
+    if (DROP) {
+      m0 = dropout_factor(dropout_bits(g0 + (e + 0) * gstep, key), lane4, thr, dscale);
+      m1 = dropout_factor(dropout_bits(g0 + (e + 1) * gstep, key), lane4, thr, dscale);
+      m2 = dropout_factor(dropout_bits(g0 + (e + 2) * gstep, key), lane4, thr, dscale);
+      m3 = dropout_factor(dropout_bits(g0 + (e + 3) * gstep, key), lane4, thr, dscale);
+    }
+    const float d0 = p0 * (__uint_as_float(dv[e]) * m0 - D.x);
+    const float d1 = p1 * (__uint_as_float(dv[e + 1]) * m1 - D.y);
+    const float d2 = p2 * (__uint_as_float(dv[e + 2]) * m2 - D.z);
+    const float d3 = p3 * (__uint_as_float(dv[e + 3]) * m3 - D.w);
+    pk[e >> 1] = pack_bf16x2(p0 * m0, p1 * m1);
+    pk[(e >> 1) + 1] = pack_bf16x2(p2 * m2, p3 * m3);
     dk[e >> 1] = pack_bf16x2(d0, d1);
     dk[(e >> 1) + 1] = pack_bf16x2(d2, d3);
   }
 }
 
 // tmQ / tmdO: boxes of 64 rows (one half of a query tile); tmK / tmV: boxes of 128 rows.
+template <bool DROP>
 __global__ void __launch_bounds__(B64::THREADS, 1)
 attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -635,10 +650,19 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tmem_ld_32x32b_x16(d_addr + ch * 16, dv);
           tmem_ld_wait();
           const int cq = sub * 32 + ch * 16;     // first query column of the chunk within the half
-          if (mask)
-            bwd_chunk<true>(sv, dv, s_lse + cq, s_dl + cq, c, lim, q0 + hf * HQ + cq, pk, dk);
-          else
-            bwd_chunk<false>(sv, dv, s_lse + cq, s_dl + cq, c, lim, 0, pk, dk);
+          if constexpr (DROP) {
+            // hash group of (query q0 + hf HQ + cq, key kv_idx) in the [B nh S, S] matrix
+            const unsigned long long gq =
+                ((static_cast<unsigned long long>(w.b) * p.nh + w.h) * p.S + (q0 + hf * HQ + cq)) *
+                    static_cast<unsigned long long>(p.S >> 2) + static_cast<unsigned long long>(kv_idx >> 2);
+            bwd_chunk<true, true>(sv, dv, s_lse + cq, s_dl + cq, c, mask ? lim : INT_MIN,
+                                  q0 + hf * HQ + cq, pk, dk, gq, static_cast<unsigned long long>(p.S >> 2),
+                                  kv_idx & 3, p.drop_thr, p.drop_key, p.drop_scale);
+          } else if (mask) {
+            bwd_chunk<true, false>(sv, dv, s_lse + cq, s_dl + cq, c, lim, q0 + hf * HQ + cq, pk, dk);
+          } else {
+            bwd_chunk<false, false>(sv, dv, s_lse + cq, s_dl + cq, c, lim, 0, pk, dk);
+          }
           tmem_st_32x32b_x8(s_addr + ch * 8, pk);
           tmem_st_32x32b_x8(d_addr + ch * 8, dk);
 #pragma unroll
@@ -746,15 +770,23 @@ int launch_attn_bwd_dh64(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
                          const CUtensorMap& tdv, const AttnBwdArgs& a, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_dh64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attn_bwd_dh64_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             B64::SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_bwd_dh64_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                              B64::SMEM_BYTES) != cudaSuccess)
       return -10;
     configured = true;
   }
   const int n_items = ((a.S + B64::BKV - 1) / B64::BKV) * a.B * a.nh;
   const int grid = n_items < sm_count() ? n_items : sm_count();
-  attn_bwd_dh64_kernel<<<grid, B64::THREADS, B64::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv,
-                                                                    a);
+  if (a.drop_thr > 0)
+    attn_bwd_dh64_kernel<true><<<grid, B64::THREADS, B64::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq,
+                                                                            tdk, tdv, a);
+  else
+    attn_bwd_dh64_kernel<false><<<grid, B64::THREADS, B64::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq,
+                                                                             tdk, tdv, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

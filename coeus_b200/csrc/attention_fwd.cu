@@ -41,6 +41,12 @@ struct AttnFwdArgs {
   float scale_log2;    // softmax scale * log2(e)
   int causal;
   int* status;
+  // dropout on the probabilities (training only; drop_thr = 0: none): P is dropped before P.V,
+  // the row sums and the LSE are those of the full softmax.  The mask is the one of
+  // dropout_bits() over the [B*nh*S, S] probability matrix in row-major order (S % 4 == 0).
+  int drop_thr;
+  uint32_t drop_key;
+  float drop_scale;
 };
 
 // Optional device timeline of CTA 0 (clock64 stamps; see cb_attn_fwd_set_trace): softmax warp 0
@@ -155,7 +161,7 @@ struct AFWalk {
   __device__ bool last_of_tile() const { return j == (t ? n1 : n0) - 1; }
 };
 
-template <int DH, bool POLY>
+template <int DH, bool POLY, bool DROP>
 __global__ void __launch_bounds__(AF_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const AttnFwdArgs p) {
@@ -540,6 +546,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // P = exp2(s * scale - m) as packed bf16 over the first half of the score buffer; row sum
       const float sc = p.scale_log2, nm = -m_used;
       if (tr) tr[tri + 2] = clock64();
+      if constexpr (DROP) {
+        // four consecutive keys share one hash; the index of this row's first key of the tile is
+        // a multiple of four (S and the tile width are)
+        const unsigned long long g0 =
+            ((static_cast<unsigned long long>(w.b) * p.nh + w.h) * p.S + q_idx) *
+                static_cast<unsigned long long>(p.S >> 2) + static_cast<unsigned long long>(kv0 >> 2);
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const uint32_t bits = dropout_bits(g0 + (c * 32 + e) / 4, p.drop_key);
+            float pe[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              pe[j] = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e + j]), sc, nm));
+              l[j] += pe[j];
+              pe[j] *= dropout_factor(bits, j, p.drop_thr, p.drop_scale);
+            }
+            pk[e >> 1] = pack_bf16x2(pe[0], pe[1]);
+            pk[(e >> 1) + 1] = pack_bf16x2(pe[2], pe[3]);
+          }
+          tmem_st_32x32b_x16(s_addr + c * 16, pk);
+        }
+      } else {
 #pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
         uint32_t pk[16];
@@ -559,6 +590,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pk[e >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
+      }
       }
       if (tr) tr[tri + 3] = clock64();
       tmem_st_wait();
@@ -616,13 +648,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-template <int DH, bool POLY>
+template <int DH, bool POLY, bool DROP = false>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const AttnFwdArgs& a, int max_ctas, cudaStream_t st) {
   using Cfg = AFCfg<DH>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel<DH, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attn_fwd_kernel<DH, POLY, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
       return -10;
     configured = true;
@@ -632,7 +664,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (items < grid) grid = items;
-  attn_fwd_kernel<DH, POLY><<<grid, AF_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, a);
+  attn_fwd_kernel<DH, POLY, DROP><<<grid, AF_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -649,13 +681,16 @@ extern "C" int cb_attn_fwd_set_trace(long long* device_buffer, int cta) {
 // nkv divides nh, query head h reads K/V head h / (nh / nkv)); they may be column slices of one
 // fused projection output.  o: [B*S, nh*dh] pitch ldo.  lse: fp32 [B, nh, S].
 // poly != 0 evaluates a quarter of the exponentials as a polynomial on the FMA pipe.
-extern "C" int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
-                              int B, int S, int nh, int nkv, int dh, int ldq, int ldk, int ldv,
-                              int ldo, float scale, int causal, int poly, int* status,
-                              int max_ctas, void* stream) {
+// drop_thr in [0, 255] (0: no dropout; needs S % 4 == 0 otherwise), drop_key: see AttnFwdArgs.
+extern "C" int cb_attn_fwd_dropout(const void* q, const void* k, const void* v, void* o, float* lse,
+                                   int B, int S, int nh, int nkv, int dh, int ldq, int ldk,
+                                   int ldv, int ldo, float scale, int causal, int poly,
+                                   int drop_thr, unsigned int drop_key, int* status, int max_ctas,
+                                   void* stream) {
   using namespace cb;
   if (dh != 64 && dh != 128) return -1;
   if (B <= 0 || S <= 0 || nh <= 0 || nkv <= 0 || (nh % nkv) != 0 || (ldo % 8) != 0) return -2;
+  if (drop_thr < 0 || drop_thr > 255 || (drop_thr > 0 && (S % 4) != 0)) return -6;
   CUtensorMap tq, tk, tv;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
   const uint32_t bkv = dh == 64 ? AFCfg<64>::BKV : AFCfg<128>::BKV;
@@ -670,10 +705,24 @@ extern "C" int cb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal;
   a.status = status;
+  a.drop_thr = drop_thr;
+  a.drop_key = drop_key;
+  a.drop_scale = 256.0f / static_cast<float>(256 - drop_thr);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (drop_thr > 0)
+    return dh == 64 ? launch_attn_fwd<64, false, true>(tq, tk, tv, a, max_ctas, st)
+                    : launch_attn_fwd<128, false, true>(tq, tk, tv, a, max_ctas, st);
   if (poly)
     return dh == 64 ? launch_attn_fwd<64, true>(tq, tk, tv, a, max_ctas, st)
                     : launch_attn_fwd<128, true>(tq, tk, tv, a, max_ctas, st);
   return dh == 64 ? launch_attn_fwd<64, false>(tq, tk, tv, a, max_ctas, st)
                   : launch_attn_fwd<128, false>(tq, tk, tv, a, max_ctas, st);
+}
+
+extern "C" int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                           int B, int S, int nh, int nkv, int dh, int ldq, int ldk, int ldv,
+                           int ldo, float scale, int causal, int poly, int* status, int max_ctas,
+                           void* stream) {
+  return cb_attn_fwd_dropout(q, k, v, o, lse, B, S, nh, nkv, dh, ldq, ldk, ldv, ldo, scale, causal,
+                             poly, 0, 0u, status, max_ctas, stream);
 }

@@ -68,6 +68,10 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
 __device__ __forceinline__ uint32_t dropout_bits(unsigned long long group, uint32_t key) {
   return mix32(static_cast<uint32_t>(group) ^ mix32(static_cast<uint32_t>(group >> 32) ^ key));
 }
+// 0 for a dropped element, `scale` for a kept one: byte `lane` (0..3) of the group's hash.
+__device__ __forceinline__ float dropout_factor(uint32_t bits, int lane, int thr, float scale) {
+  return static_cast<int>((bits >> (8 * lane)) & 255u) < thr ? 0.f : scale;
+}
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {

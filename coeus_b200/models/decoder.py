@@ -451,12 +451,11 @@ class DecoderLM:
         else:
             Hkv = cfg.kv_dim
             q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+            # dropout on the probabilities happens inside the flash kernel (the materialised path
+            # where it cannot: see ops/attention.py); grouped-query attention: the forward kernel
+            # indexes K/V by head // group itself
             da = self._drop(cfg.attention_dropout, l, 2)
-            if da is not None:   # dropout on the probabilities: the materialised path
-                attn, lse = A.attention_dropout_fwd(q, k, v, B, S, nh, dh, *da, causal=True)
-            else:
-                # grouped-query attention: the forward kernel indexes K/V by head // group itself
-                attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True)
+            attn, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=True, dropout=da)
         d0, d1 = self._drop(cfg.dropout, l, 0), self._drop(cfg.dropout, l, 1)
         x_mid = G.linear_fwd(attn, self.w[p + "attn.o_weights"], bias("attn.o_bias"), resid=x,
                              max_ctas=mc, dropout=d0)
@@ -696,13 +695,13 @@ class DecoderLM:
             dqkv = self._buf("dqkv", (dattn.shape[0], 3 * H))
             if self.cp is not None:
                 self.cp.attention_bwd(dattn, qkv, a["attn"], a["lse"], B, S, nh, dh, dqkv=dqkv)
-            elif da is not None:
+            elif da is not None and not A.flash_dropout_ok(q, S, dh):
                 dqkv = self._buf("dqkv_drop", (dattn.shape[0], cfg.qkv_dim))
                 A.attention_dropout_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, *da,
                                         causal=True, dqkv=dqkv)
             elif self.gqa:
                 A.attention_bwd(dattn, q, self._expand_kv(k), self._expand_kv(v), a["attn"],
-                                a["lse"], B, S, nh, dh, causal=True, dqkv=dqkv)
+                                a["lse"], B, S, nh, dh, causal=True, dqkv=dqkv, dropout=da)
                 # the gradients of a K/V head are the sum over the query heads of its group
                 Tn, g = dqkv.shape[0], nh // cfg.kv_heads
                 narrow = self._buf("dqkv_gqa", (Tn, cfg.qkv_dim))
@@ -713,7 +712,7 @@ class DecoderLM:
                 dqkv = narrow
             else:
                 A.attention_bwd(dattn, q, k, v, a["attn"], a["lse"], B, S, nh, dh, causal=True,
-                                dqkv=dqkv)
+                                dqkv=dqkv, dropout=da)
             if cfg.pos == "rope":
                 self._rope(dqkv, B, S, True)
             G.linear_wgrad(a["n1"], dqkv, self.g[p + "attn.qkv_weights"], max_ctas=mc)

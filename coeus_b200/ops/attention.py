@@ -41,14 +41,26 @@ def _ref_fwd(q, k, v, B, S, nh, dh, scale, causal):
     return o, lse, p, (qf, kf, vf)
 
 
+def flash_dropout_ok(q: torch.Tensor, S: int, dh: int) -> bool:
+    """Whether the flash kernels can apply dropout themselves for this call (else the
+    materialised path :func:`attention_dropout_fwd` / ``_bwd`` is the one to use)."""
+    return q.is_cuda and S % 4 == 0 and dh in (64, 128)
+
+
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: int, nh: int,
-                  dh: int, *, causal: bool = True, scale: Optional[float] = None
+                  dh: int, *, causal: bool = True, scale: Optional[float] = None,
+                  dropout: Optional[Tuple[int, int]] = None
                   ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Returns ``(o [B*S, nh*dh], lse [B, nh, S] fp32)``.  ``k`` and ``v`` may hold fewer heads
     than ``q`` (``[B*S, nkv*dh]``, ``nkv`` dividing ``nh``): grouped-query attention, query head
-    ``h`` reading K/V head ``h // (nh // nkv)`` inside the kernel."""
+    ``h`` reading K/V head ``h // (nh // nkv)`` inside the kernel.  ``dropout = (thr, key)``
+    drops the probabilities inside the kernel (mask of :func:`..elementwise.dropout_mask` over the
+    ``[B*nh*S, S]`` probability matrix; nothing is stored, the backward pass recomputes it)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
     nkv = k.shape[1] // dh
+    thr, key = dropout if dropout is not None else (0, 0)
+    if thr and not flash_dropout_ok(q, S, dh):
+        return attention_dropout_fwd(q, k, v, B, S, nh, dh, thr, key, causal=causal, scale=scale)
     if not q.is_cuda:
         o, lse, _, _ = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
         return o.to(q.dtype), lse
@@ -57,10 +69,11 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: 
     o = torch.empty((B * S, nh * dh), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
     st = _lib.status_buffer(q.device)
-    rc = _lib.lib().cb_attn_fwd(
+    rc = _lib.lib().cb_attn_fwd_dropout(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), B, S, nh, nkv, dh,
         q.stride(0), k.stride(0), v.stride(0), o.stride(0), ctypes.c_float(scale),
-        int(causal), FWD_POLY, _lib.ptr(st), 0, _lib.stream_ptr())
+        int(causal), FWD_POLY, int(thr), ctypes.c_uint(key & 0xFFFFFFFF), _lib.ptr(st), 0,
+        _lib.stream_ptr())
     _lib.check_rc(rc, "cb_attn_fwd")
     return o, lse
 
@@ -68,12 +81,18 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: 
 def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                   o: torch.Tensor, lse: torch.Tensor, B: int, S: int, nh: int, dh: int, *,
                   causal: bool = True, scale: Optional[float] = None,
-                  dqkv: Optional[torch.Tensor] = None
+                  dqkv: Optional[torch.Tensor] = None,
+                  dropout: Optional[Tuple[int, int]] = None
                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Returns ``(dq, dk, dv)`` as column slices of one fused ``[B*S, 3*nh*dh]`` bf16 buffer
-    (``dqkv`` if given), ready to be the input of the QKV projection's backward GEMMs."""
+    (``dqkv`` if given), ready to be the input of the QKV projection's backward GEMMs.
+    ``dropout``: the ``(thr, key)`` the forward pass was given."""
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
     H = nh * dh
+    thr, key = dropout if dropout is not None else (0, 0)
+    if thr and not flash_dropout_ok(q, S, dh):
+        return attention_dropout_bwd(do, q, k, v, o, lse, B, S, nh, dh, thr, key, causal=causal,
+                                     scale=scale, dqkv=dqkv)
     if not q.is_cuda:
         _, lse_own, p, (qf, kf, vf) = _ref_fwd(q, k, v, B, S, nh, dh, scale, causal)
         # probabilities relative to the normaliser that was passed in (it covers more keys than
@@ -96,19 +115,20 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
     dq_acc = torch.zeros((B * S, H), dtype=torch.float32, device=q.device)
     delta = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
     st = _lib.status_buffer(q.device)
-    rc = _lib.lib().cb_attn_bwd(
+    rc = _lib.lib().cb_attn_bwd_dropout(
         _lib.ptr(do), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse),
         _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(out), B, S, nh, dh, do.stride(0), q.stride(0),
         k.stride(0), v.stride(0), o.stride(0), out.stride(0), ctypes.c_float(scale), int(causal),
-        _lib.ptr(st), _lib.stream_ptr())
+        int(thr), ctypes.c_uint(key & 0xFFFFFFFF), _lib.ptr(st), _lib.stream_ptr())
     _lib.check_rc(rc, "cb_attn_bwd", launches=3)
     return out[:, :H], out[:, H:2 * H], out[:, 2 * H:]
 
 
 # ------------------------------------------------------------------------------ dropout path
-# Attention with dropout on the probabilities materialises the score matrix with tensor ops (on
-# either device): the flash kernels have no dropout, and a rate > 0 is a training-only option
-# that no benchmark of this framework uses.  The mask is the counter-based one of
+# Attention with dropout on the probabilities by materialising the score matrix with tensor ops
+# (on either device): the oracle of the flash kernels' own dropout and the path of the cases they
+# do not cover (CPU tensors, a sequence length that is not a multiple of four).  The mask is the
+# counter-based one of
 # :func:`coeus_b200.ops.elementwise.dropout_mask` over the ``[B*nh*S, S]`` probability matrix, so
 # nothing is stored between the passes and CPU and GPU agree.
 def attention_dropout_fwd(q, k, v, B, S, nh, dh, thr, key, *, causal=True, scale=None):

@@ -291,6 +291,43 @@ def test_attention_fwd_shapes_and_grouped_query(dh, nh, nkv, B, S, causal):
         A.FWD_POLY = before
 
 
+@pytest.mark.parametrize("dh,nh,nkv,B,S,causal", [
+    (64, 4, 4, 2, 256, True), (64, 6, 2, 1, 384, True), (64, 3, 3, 2, 200, False),
+    (128, 2, 2, 2, 256, True), (128, 4, 1, 1, 320, False), (64, 16, 16, 8, 256, True),
+])
+def test_attention_dropout_inside_the_flash_kernels(dh, nh, nkv, B, S, causal):
+    """Dropout on the probabilities applied by the forward and backward flash kernels themselves
+    (mask recomputed from the element index, nothing stored) against the materialised fp32
+    restatement with the same mask."""
+    torch.manual_seed(21)
+    H, Hkv = nh * dh, nkv * dh
+    thr, key = E.dropout_threshold(0.2), E.dropout_key(7, 3, 1, 0, 5, 2)
+    qkv = _bf(torch.randn(B * S, H + 2 * Hkv, device=DEV))
+    q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+    assert A.flash_dropout_ok(q, S, dh)
+    o, lse = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal, dropout=(thr, key))
+    orf, lser = A.attention_dropout_fwd(q.cpu(), k.cpu(), v.cpu(), B, S, nh, dh, thr, key,
+                                        causal=causal)
+    torch.cuda.synchronize()
+    _status_clean()
+    assert (o.float().cpu() - orf.float()).abs().max() < 0.04
+    assert (lse.cpu() - lser).abs().max() < 0.02
+    # a fifth of the probabilities is gone: the output differs from the one without dropout
+    o0, _ = A.attention_fwd(q, k, v, B, S, nh, dh, causal=causal)
+    assert (o.float() - o0.float()).abs().max() > 0.05
+    if nkv != nh:
+        return               # the backward kernels take expanded K/V heads (the model sums them)
+    do = _bf(torch.randn(B * S, H, device=DEV))
+    got = A.attention_bwd(do, q, k, v, o, lse, B, S, nh, dh, causal=causal, dropout=(thr, key))
+    ref = A.attention_dropout_bwd(do.cpu(), q.cpu(), k.cpu(), v.cpu(), orf, lser, B, S, nh, dh,
+                                  thr, key, causal=causal)
+    torch.cuda.synchronize()
+    _status_clean()
+    for g_, r_, name in zip(got, ref, ("dq", "dk", "dv")):
+        err = (g_.float().cpu() - r_.float()).abs().max().item()
+        assert err < 0.02 * r_.float().abs().max().item() + 0.04, (name, err)
+
+
 def test_dropout_mask_is_the_same_on_the_device_in_the_gemm_and_on_the_host():
     """One mask function in three places: the stand-alone kernel, the GEMM epilogue (dropout on
     the value before the residual is added) and the tensor-op restatement on the host."""
