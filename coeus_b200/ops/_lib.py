@@ -95,7 +95,17 @@ def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream_ptr() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device as a raw handle.  Asked of the runtime
+    binding directly: ``torch.cuda.current_stream()`` builds a Python stream object through
+    several layers of device-index resolution, which was a third of the host time of a training
+    step (one call per kernel launch)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
