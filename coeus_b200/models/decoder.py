@@ -18,6 +18,7 @@ graph is built: ``forward_loss`` keeps the activations the hand-written ``backwa
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -149,8 +150,17 @@ class DecoderLM:
                  pad_multiple: int = 8 * 1024, training: bool = True,
                  dtype: torch.dtype = torch.bfloat16, epx=None,
                  layers: Optional[Tuple[int, int]] = None, embed: bool = True,
-                 head: bool = True, cp=None, recompute: bool = False) -> None:
-        """``recompute=True`` keeps only each block's input for the backward pass and runs the
+                 head: bool = True, cp=None, recompute: bool = False,
+                 lm_head_chunks: Optional[int] = None) -> None:
+        """``lm_head_chunks = n > 1`` (default: ``COEUS_LM_HEAD_CHUNKS``, else 1) computes the LM
+        head and the cross-entropy in ``n`` slices of the vocabulary, so that the ``[tokens,
+        vocabulary]`` logits are never held at once: per slice the logits go through the
+        (max, sum-exp, target-logit) kernel of the vocabulary-parallel loss; the backward pass
+        recomputes a slice's logits, turns them into their gradient in place and feeds the head's
+        weight- and data-gradient GEMMs from it.  One more LM-head product per step for
+        ``1/n`` of the logits memory (1 GB at the benchmark's 16384 x 32000, 4 GB at a 128k
+        vocabulary).
+        ``recompute=True`` keeps only each block's input for the backward pass and runs the
         block's forward again there (activation checkpointing: about one third more compute for
         a per-layer activation footprint of one ``[T, H]`` tensor instead of roughly
         ``[T, 14 H]``).
@@ -168,6 +178,9 @@ class DecoderLM:
         self.device = torch.device(device)
         self.cp = cp
         self.recompute = bool(recompute)
+        if lm_head_chunks is None:
+            lm_head_chunks = int(os.environ.get("COEUS_LM_HEAD_CHUNKS", "1"))
+        self.lm_head_chunks = max(1, int(lm_head_chunks))
         self.gqa = cfg.kv_heads != cfg.num_heads
         if self.gqa and cp is not None:
             raise ProcessingError.unsupported(
@@ -573,12 +586,15 @@ class DecoderLM:
         """LM head and cross-entropy on the final-norm output; stores ``save`` for backward."""
         T = xf.shape[0]
         w, b_mn = self.output_weight()
-        logits = G.gemm(xf, w, b_mn=b_mn, out=self._buf("logits", (T, self.cfg.vocab_padded)),
-                        max_ctas=self.max_ctas)
         scale = grad_scale if grad_scale is not None else 1.0 / T
-        loss_tok = E.cross_entropy_fwd_bwd(logits, targets.reshape(-1), scale,
-                                           vocab=self.cfg.vocab_size)
-        save["dlogits"] = logits
+        if self.lm_head_chunks > 1:
+            loss_tok = self._chunked_head_loss(xf, targets.reshape(-1), save, scale)
+        else:
+            logits = G.gemm(xf, w, b_mn=b_mn, out=self._buf("logits", (T, self.cfg.vocab_padded)),
+                            max_ctas=self.max_ctas)
+            loss_tok = E.cross_entropy_fwd_bwd(logits, targets.reshape(-1), scale,
+                                               vocab=self.cfg.vocab_size)
+            save["dlogits"] = logits
         save["aux_scale"] = scale * T   # the auxiliary losses follow the scaling of the main loss
         self._saved = save
         loss = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -587,6 +603,62 @@ class DecoderLM:
         if self.moe:   # router load-balancing terms (already multiplied by their coefficient)
             loss = loss + torch.stack([m.last_aux for m in self.moe]).sum()
         return loss
+
+    # ---- LM head and loss in slices of the vocabulary (lm_head_chunks > 1)
+    def _head_chunks(self) -> List[Tuple[int, int, int]]:
+        """``(first column, end column, valid columns)`` of every slice of the padded vocabulary;
+        widths are multiples of 256 columns."""
+        V, Vp = self.cfg.vocab_size, self.cfg.vocab_padded
+        width = -(-Vp // self.lm_head_chunks)
+        width = -(-width // 256) * 256
+        return [(c0, min(Vp, c0 + width), max(0, min(V, c0 + width) - c0))
+                for c0 in range(0, Vp, width)]
+
+    def _head_slice_logits(self, xf: torch.Tensor, c0: int, c1: int) -> torch.Tensor:
+        w, b_mn = self.output_weight()
+        wc = w[:, c0:c1] if b_mn else w[c0:c1]
+        buf = self._buf("logits_slice", (xf.shape[0], self._head_chunks()[0][1]))
+        return G.gemm(xf, wc, b_mn=b_mn, out=buf[:, :c1 - c0], max_ctas=self.max_ctas)
+
+    def _chunked_head_loss(self, xf: torch.Tensor, targets: torch.Tensor, save: dict,
+                           scale: float) -> torch.Tensor:
+        """Per-token loss from per-slice (max, sum-exp, target-logit) statistics."""
+        m = s = tl = None
+        for c0, c1, valid in self._head_chunks():
+            if valid == 0:
+                continue
+            st = E.cross_entropy_stats(self._head_slice_logits(xf, c0, c1)[:, :valid], targets, c0)
+            if m is None:
+                m, s, tl = st[:, 0].clone(), st[:, 1].clone(), st[:, 2].clone()
+            else:
+                mn = torch.maximum(m, st[:, 0])
+                s = s * torch.exp(m - mn) + st[:, 1] * torch.exp(st[:, 0] - mn)
+                m, tl = mn, tl + st[:, 2]
+        lse = m + torch.log(s)
+        save["head_chunked"] = {"lse": lse, "targets": targets, "scale": scale}
+        return (lse - tl) * (targets >= 0)
+
+    def _chunked_head_backward(self, sv: dict) -> torch.Tensor:
+        """Head gradients slice by slice; returns d loss / d (final-norm output) in bf16."""
+        hc, xf = sv["head_chunked"], sv["final"]["xf"]
+        w, b_mn = self.output_weight()
+        mc = self.max_ctas
+        dxf = torch.zeros((xf.shape[0], xf.shape[1]), dtype=torch.float32, device=xf.device)
+        for c0, c1, valid in self._head_chunks():
+            dlog = self._head_slice_logits(xf, c0, c1)
+            if valid > 0:
+                E.cross_entropy_bwd_from_lse(dlog[:, :valid], hc["targets"], hc["lse"], c0,
+                                             hc["scale"])
+            if valid < c1 - c0:
+                dlog[:, valid:].zero_()      # padding columns of the vocabulary: no gradient
+            if self.cfg.tie_embeddings:
+                G.gemm(dlog, xf, a_mn=True, b_mn=True, out=self.g["token_embed"][c0:c1],
+                       accumulate=True, ksplit=2, max_ctas=mc)
+                G.gemm(dlog, w[c0:c1], b_mn=True, out=dxf, accumulate=True, max_ctas=mc)
+            else:
+                G.linear_wgrad(xf, dlog, self.g["output_proj"][:, c0:c1], max_ctas=mc)
+                G.gemm(dlog, w[:, c0:c1], out=dxf, accumulate=True, max_ctas=mc)
+        return dxf.to(xf.dtype)
 
     # ------------------------------------------------------------------ backward
     def zero_grad(self) -> None:
@@ -628,8 +700,13 @@ class DecoderLM:
         rms = cfg.norm == "rmsnorm"
         fn = self.layout.norm_names[2]
         mc = self.max_ctas
-        dlog = sv["dlogits"]
         fin = sv["final"]
+        if "head_chunked" in sv:
+            dxf = self._chunked_head_backward(sv)
+            return N.norm_bwd(dxf, fin["x"], self.w[fn + "_scale"], fin["mean"], fin["rstd"],
+                              self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None,
+                              rms)
+        dlog = sv["dlogits"]
         w, b_mn = self.output_weight()
         if cfg.tie_embeddings:
             # d token_embed[V,H] += dlogits^T[V,T] @ xf[T,H]

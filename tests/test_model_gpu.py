@@ -72,6 +72,30 @@ def test_dropout_on_the_kernel_path_matches_the_host_path():
         assert err <= 0.06 * want.abs().max().item() + 2e-4, (n, err)
 
 
+@pytest.mark.parametrize("tie", [False, True])
+def test_lm_head_in_vocabulary_slices_matches_the_whole_head(tie):
+    """``lm_head_chunks``: loss and every gradient as with the logits held at once."""
+    cfg = DecoderConfig(hidden_dim=256, num_layers=1, num_heads=4, intermediate_dim=512,
+                        vocab_size=5000, max_seq_len=128, tie_embeddings=tie)
+    torch.manual_seed(4)
+    batch = torch.randint(0, cfg.vocab_size, (4, 101), device="cuda")
+    x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+    y[1, 5] = -100
+    got = []
+    for chunks in (1, 3):
+        m = DecoderLM(cfg, device="cuda", seed=2, lm_head_chunks=chunks)
+        m.zero_grad()
+        loss = m.forward_loss(x, y)
+        m.backward()
+        torch.cuda.synchronize()
+        _lib.check_status(torch.device("cuda", 0))
+        got.append((float(loss), m.g32.clone()))
+    assert len(m._head_chunks()) > 1
+    assert abs(got[0][0] - got[1][0]) < 2e-3
+    ref = got[0][1]
+    assert (got[1][1] - ref).abs().max() < 0.02 * ref.abs().max() + 1e-4
+
+
 def test_training_reduces_loss():
     cfg = CFGS["gpt"]
     m = DecoderLM(cfg, device="cuda")

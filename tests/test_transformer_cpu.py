@@ -13,6 +13,7 @@ from coeus_b200.core.model import BasicGenerationConfig
 from coeus_b200.foundation.error import ConfigError, ProcessingError
 from coeus_b200.foundation.types import Version
 from coeus_b200.models.config import DecoderConfig, Transformer250MConfig
+from coeus_b200.models.decoder import DecoderLM
 from coeus_b200.ops import elementwise as E
 from coeus_b200.ops import norm as N
 from coeus_b200.plugins.builtin import TransformerModel, TransformerModelPlugin
@@ -503,3 +504,25 @@ def test_grouped_query_attention_trains_saves_and_serves():
     rid = cb.submit(prompt[0, :70].tolist(), 4)              # second time through cached pages
     b = cb.run()[rid]
     assert a == alone and b == alone and cb.prefix.hits == 1
+
+
+@pytest.mark.parametrize("tie", [False, True])
+def test_lm_head_in_vocabulary_slices_matches_the_whole_head(tie):
+    """The LM head and loss computed in slices of the vocabulary (the logits never held at once)
+    give the loss and the gradients of the whole-head path."""
+    cfg = DecoderConfig(vocab_size=1000, hidden_dim=64, num_layers=2, num_heads=4,
+                        intermediate_dim=128, max_seq_len=32, tie_embeddings=tie)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 1000, (2, 17))
+    tg = ids[:, 1:].clone()
+    tg[0, 3] = -100
+    out = []
+    for chunks in (1, 3):
+        m = DecoderLM(cfg, device="cpu", seed=1, dtype=torch.float32, lm_head_chunks=chunks)
+        m.zero_grad()
+        loss = m.forward_loss(ids[:, :-1], tg)
+        m.backward()
+        out.append((loss.clone(), m.g32.clone()))
+    assert len(m._head_chunks()) == 2
+    assert torch.allclose(out[0][0], out[1][0], atol=1e-6)
+    assert (out[0][1] - out[1][1]).abs().max() < 1e-6
