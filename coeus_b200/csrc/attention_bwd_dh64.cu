@@ -198,8 +198,9 @@ attn_bwd_dh64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::B_KVF + s), 1);
-      mbar_init(bar(C::B_KVE + s), C::DQ_OWN_WARP ? 3 : 2);     // both MMA issuers, and the store warp once the dV / dK
-                                           // staged in the finished item's K/V buffer have left
+      // the MMA issuer(s), and warp 3 once the dV / dK staged in the finished item's K/V buffer
+      // have been stored
+      mbar_init(bar(C::B_KVE + s), C::DQ_OWN_WARP ? 3 : 2);
       mbar_init(bar(C::B_SF + s), 1);
       mbar_init(bar(C::B_PF + s), 4 * C::NSUB);      // one arrival per softmax warp of the half
       mbar_init(bar(C::B_STF + s), 4 * C::NSUB);
