@@ -701,11 +701,18 @@ class DecoderLM:
         fn = self.layout.norm_names[2]
         mc = self.max_ctas
         fin = sv["final"]
+        # the result is the gradient of the last block's output: its column sums are the bias
+        # gradient of that block's down projection, taken by the same kernel
+        cols = None
+        if self.layer_ids and self._down_bias_rides_on_norm():
+            last = self.layer_ids[-1]
+            cols = self.g[f"layers.{last}.ff.down_bias"]
+            sv["down_bias_summed"] = last
         if "head_chunked" in sv:
             dxf = self._chunked_head_backward(sv)
             return N.norm_bwd(dxf, fin["x"], self.w[fn + "_scale"], fin["mean"], fin["rstd"],
                               self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None,
-                              rms)
+                              rms, colsum=cols)
         dlog = sv["dlogits"]
         w, b_mn = self.output_weight()
         if cfg.tie_embeddings:
@@ -717,7 +724,18 @@ class DecoderLM:
             G.linear_wgrad(fin["xf"], dlog, self.g["output_proj"], max_ctas=mc)
             dxf = G.linear_dgrad(dlog, w, max_ctas=mc)
         return N.norm_bwd(dxf, fin["x"], self.w[fn + "_scale"], fin["mean"], fin["rstd"],
-                          self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None, rms)
+                          self.g[fn + "_scale"], None if rms else self.g[fn + "_bias"], None, rms,
+                          colsum=cols)
+
+    def _bias_rides_on_norm(self) -> bool:
+        """Whether the bias gradients of the projections that write into the residual stream are
+        summed by the norm-backward kernel that produces that stream's gradient (not when
+        residual dropout scales the gradient between the two)."""
+        return bool(self.cfg.use_bias and not (self._drop_active and self.cfg.dropout))
+
+    def _down_bias_rides_on_norm(self) -> bool:
+        return bool(self._bias_rides_on_norm() and not self.moe
+                    and self.cfg.activation != "swiglu")
 
     def backward_blocks(self, dx: torch.Tensor, sv: dict, on_layer_done=None) -> torch.Tensor:
         """Backward through this model's blocks; returns d loss / d (first block input)."""
@@ -727,6 +745,8 @@ class DecoderLM:
         rms = cfg.norm == "rmsnorm"
         n1n, n2n, fn = self.layout.norm_names
         mc = self.max_ctas
+        ride_o, ride_down = self._bias_rides_on_norm(), self._down_bias_rides_on_norm()
+        down_summed = sv.pop("down_bias_summed", None)   # layer whose down bias is already done
         for l in reversed(self.layer_ids):
             a = sv[l]
             if "n1" not in a:            # activation checkpointing: rebuild the block's tensors
@@ -755,15 +775,18 @@ class DecoderLM:
                 # ... which also sums its output's columns: the up projection's bias gradient
                 du = E.gelu_bwd(a["u"], dact, self.g[p + "ff.up_bias"] if cfg.use_bias else None)
                 G.linear_wgrad(a["n2"], du, self.g[p + "ff.up_weights"], max_ctas=mc)
-                if cfg.use_bias:
+                if cfg.use_bias and down_summed != l:
                     E.colsum_into(dxd, self.g[p + "ff.down_bias"])
                 dn2 = G.linear_dgrad(du, self.w[p + "ff.up_weights"], max_ctas=mc)
+            # dx_mid is the gradient of the attention block's output: its column sums are the
+            # output projection's bias gradient
             dx_mid = N.norm_bwd(dn2, a["x_mid"], self.w[p + n2n + "_scale"], a["mean2"], a["rstd2"],
                                 self.g[p + n2n + "_scale"],
-                                None if rms else self.g[p + n2n + "_bias"], dx, rms)
+                                None if rms else self.g[p + n2n + "_bias"], dx, rms,
+                                colsum=self.g[p + "attn.o_bias"] if ride_o else None)
             dxm = E.dropout_apply(dx_mid, *d0) if d0 is not None else dx_mid
             G.linear_wgrad(a["attn"], dxm, self.g[p + "attn.o_weights"], max_ctas=mc)
-            if cfg.use_bias:
+            if cfg.use_bias and not ride_o:
                 E.colsum_into(dxm, self.g[p + "attn.o_bias"])
             dattn = G.linear_dgrad(dxm, self.w[p + "attn.o_weights"], max_ctas=mc)
             qkv = a["qkv"]
@@ -796,9 +819,15 @@ class DecoderLM:
             if cfg.use_bias:
                 E.colsum_into(dqkv, self.g[p + "attn.qkv_bias"])
             dn1 = G.linear_dgrad(dqkv, self.w[p + "attn.qkv_weights"], max_ctas=mc)
+            # dx is the gradient of the previous block's output: the column sums are that block's
+            # down-projection bias gradient
+            cols = None
+            if ride_down and l - 1 >= self.layer_ids[0]:
+                cols = self.g[f"layers.{l - 1}.ff.down_bias"]
+                down_summed = l - 1
             dx = N.norm_bwd(dn1, a["x"], self.w[p + n1n + "_scale"], a["mean1"], a["rstd1"],
                             self.g[p + n1n + "_scale"],
-                            None if rms else self.g[p + n1n + "_bias"], dx_mid, rms)
+                            None if rms else self.g[p + n1n + "_bias"], dx_mid, rms, colsum=cols)
             if on_layer_done is not None:
                 on_layer_done(l)
         return dx

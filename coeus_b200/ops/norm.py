@@ -36,7 +36,8 @@ def norm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor],
     rstd = torch.empty(T, dtype=torch.float32, device=x.device)
     rc = _lib.lib().cb_norm_fwd(_lib.ptr(x), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(y),
                                 _lib.ptr(mean), _lib.ptr(rstd), T, H,
-                                _lib.ctypes.c_float(eps), int(rms), _lib.stream_ptr())
+                                _lib.ctypes.c_float(eps), int(rms),
+                                _lib.ptr(_lib.status_buffer(x.device)), _lib.stream_ptr())
     _lib.check_rc(rc, "cb_norm_fwd")
     return y, mean, rstd
 
@@ -44,8 +45,11 @@ def norm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor],
 def norm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor,
              mean: Optional[torch.Tensor], rstd: torch.Tensor, dgamma: torch.Tensor,
              dbeta: Optional[torch.Tensor], dres: Optional[torch.Tensor] = None,
-             rms: bool = False) -> torch.Tensor:
-    """Returns ``dx (+ dres)``; accumulates into the fp32 ``dgamma`` / ``dbeta``."""
+             rms: bool = False, colsum: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Returns ``dx (+ dres)``; accumulates into the fp32 ``dgamma`` / ``dbeta``.  With ``colsum``
+    (fp32 ``[H]``) the column sums of the returned tensor are added to it as well: the result is
+    the gradient of a residual stream, so these are the bias gradient of the linear layer that
+    wrote into that stream, taken in the same pass."""
     T, H = x.shape
     if not x.is_cuda:
         xf, dyf, g = x.float(), dy.float(), gamma.float()
@@ -63,11 +67,26 @@ def norm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor,
         dgamma.add_((dyf * xh).sum(0))
         if dres is not None:
             dx = dx + dres.float()
-        return dx.to(x.dtype)
+        dx = dx.to(x.dtype)
+        if colsum is not None:
+            colsum.add_(dx.float().sum(0))
+        return dx
     assert dy.is_contiguous() and x.is_contiguous()
     dx = torch.empty_like(x)
-    rc = _lib.lib().cb_norm_bwd(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(gamma), _lib.ptr(mean),
-                                _lib.ptr(rstd), _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dgamma),
-                                _lib.ptr(dbeta), T, H, int(rms), _lib.stream_ptr())
+
+    def launch(cols):
+        return _lib.lib().cb_norm_bwd(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(gamma), _lib.ptr(mean),
+                                      _lib.ptr(rstd), _lib.ptr(dres), _lib.ptr(dx),
+                                      _lib.ptr(dgamma), _lib.ptr(dbeta), _lib.ptr(cols), T, H,
+                                      int(rms), _lib.ptr(_lib.status_buffer(x.device)),
+                                      _lib.stream_ptr())
+
+    rc = launch(colsum)
+    if rc == -3:        # this shape runs a kernel that does not sum columns: a pass of its own
+        from .elementwise import colsum_into
+        rc = launch(None)
+        _lib.check_rc(rc, "cb_norm_bwd")
+        colsum_into(dx, colsum)
+        return dx
     _lib.check_rc(rc, "cb_norm_bwd")
     return dx

@@ -77,7 +77,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--compare-torch", action="store_true")
-    ap.add_argument("--variant", type=int, default=-1, help="kernel variant (norm_bwd: 0, 1, 2)")
+    ap.add_argument("--variant", type=int, default=-1, help="kernel variant (norm_bwd: 0, 1, 2 rows in registers, 3 row-pipelined; norm_fwd: 0, 1)")
     a = ap.parse_args(argv)
     from ..ops import attention as A
     from ..ops import decode as D
@@ -86,9 +86,12 @@ def main(argv=None) -> int:
     from ..ops import norm as N
     dev = "cuda"
     bf = torch.bfloat16
-    if a.variant >= 0 and a.kernel == "norm_bwd":
+    if a.variant >= 0 and a.kernel in ("norm_bwd", "rmsnorm_bwd"):
         from ..ops import _lib
         _lib.lib().cb_norm_bwd_variant(a.variant)
+    if a.variant >= 0 and a.kernel in ("norm_fwd", "rmsnorm_fwd"):
+        from ..ops import _lib
+        _lib.lib().cb_norm_fwd_variant(a.variant)
     hbm, tf, src = peaks()
     flops = nbytes = 0.0
     torch_fn = None

@@ -73,7 +73,7 @@ def test_gemm_epilogues():
     _status_clean()
 
 
-@pytest.mark.parametrize("H", [64, 768, 1024, 2048, 4096])
+@pytest.mark.parametrize("H", [64, 768, 1000, 1024, 1536, 2048, 4096])
 @pytest.mark.parametrize("rms", [False, True])
 def test_norm_fwd_bwd(H, rms):
     torch.manual_seed(3)
@@ -97,6 +97,58 @@ def test_norm_fwd_bwd(H, rms):
     assert (dg.cpu() - dgr).abs().max() < 0.02 * dgr.abs().max() + 0.05
     if not rms:
         assert (db.cpu() - dbr).abs().max() < 0.02 * dbr.abs().max() + 0.05
+    _status_clean()
+
+
+@pytest.mark.parametrize("T,H,rms,with_res", [(40000, 1024, False, True), (40000, 1024, True, False),
+                                              (9001, 2048, False, True), (9001, 2048, True, True),
+                                              (3, 512, False, False), (700, 4096, False, True)])
+def test_norm_many_rows_and_column_sums(T, H, rms, with_res):
+    """More rows than one round of the persistent warps (every warp's ring of row buffers wraps
+    several times), with and without the residual gradient, and the column sums of the result
+    taken in the same pass (the width that the row-pipelined kernel does not cover falls back to
+    a separate pass)."""
+    torch.manual_seed(5)
+    x = _bf(torch.randn(T, H, device=DEV) * 1.5 - 0.25)
+    g = _bf(torch.randn(H, device=DEV))
+    b = None if rms else _bf(torch.randn(H, device=DEV))
+    dy = _bf(torch.randn(T, H, device=DEV))
+    dres = _bf(torch.randn(T, H, device=DEV)) if with_res else None
+    y, mean, rstd = N.norm_fwd(x, g, b, 1e-5, rms)
+    xf = x.float()
+    if rms:
+        rr = torch.rsqrt((xf * xf).mean(-1) + 1e-5)
+        xh = xf * rr[:, None]
+        yr = xh * g.float()
+    else:
+        mu = xf.mean(-1)
+        rr = torch.rsqrt(((xf - mu[:, None]) ** 2).mean(-1) + 1e-5)
+        xh = (xf - mu[:, None]) * rr[:, None]
+        yr = xh * g.float() + b.float()
+        assert (mean - mu).abs().max() < 1e-3
+    assert (rstd - rr).abs().max() < 1e-3 * float(rr.max())
+    assert (y.float() - yr).abs().max() < 0.06
+    dg = torch.zeros(H, device=DEV)
+    db = None if rms else torch.zeros(H, device=DEV)
+    cols = torch.zeros(H, device=DEV)
+    dx = N.norm_bwd(dy, x, g, mean, rstd, dg, db, dres, rms, colsum=cols)
+    dgv = dy.float() * g.float()
+    dxr = rr[:, None] * (dgv - (0 if rms else dgv.mean(-1, keepdim=True))
+                         - xh * (dgv * xh).mean(-1, keepdim=True))
+    if with_res:
+        dxr = dxr + dres.float()
+    assert (dx.float() - dxr).abs().max() < 0.08
+    dgr = (dy.float() * xh).sum(0)
+    assert (dg - dgr).abs().max() < 0.02 * float(dgr.abs().max()) + 0.05
+    if not rms:
+        dbr = dy.float().sum(0)
+        assert (db - dbr).abs().max() < 0.02 * float(dbr.abs().max()) + 0.05
+    cr = dxr.sum(0)
+    assert (cols - cr).abs().max() < 4e-3 * float(cr.abs().max()) + 0.1
+    dx2 = N.norm_bwd(dy, x, g, mean, rstd, torch.zeros_like(dg), None if rms else torch.zeros_like(db),
+                     dres, rms)
+    assert torch.equal(dx, dx2)
+    _status_clean()
 
 
 def test_embedding_and_positions():
