@@ -10,6 +10,17 @@ direction; sends are not waited for until their buffer is reused and, on CPU ran
 the next micro-batch are posted before the current one is computed (on GPUs a receive is posted
 when it is needed, see ``_Channel``), which is what overlaps the transfers with the math.  The reference is a single process and has no pipeline (no send/recv anywhere in its
 sources); this is one of the parallelism strategies the larger training configurations need.
+
+On GPUs there is a second transport, ``transport="peer"``: the sender pushes the tensor into a
+slot of the receiver's memory over NVLink (a copy kernel on the compute stream followed by a
+release store of a 64-bit epoch flag), the receiver's stream waits for the flag with a bounded
+spin of one warp and computes straight out of the slot.  Nothing is a rendezvous: a send never
+waits for the receiver to have posted anything, so any schedule that finishes with asynchronous
+sends finishes.  NCCL point-to-point is a rendezvous of two kernels, and a spinning NCCL kernel
+can hold back the compute kernels queued behind it; :func:`nccl_order_deadlocks` is an event
+model of that, under which the interleaved schedule stops for ``micro_batches > stages`` (two
+ranks each spin in a send whose receive the other rank posts only after compute that the spin
+holds back).  The interleaved stage therefore uses the peer transport on GPUs.
 """
 from __future__ import annotations
 
@@ -85,6 +96,177 @@ def schedule_interleaved(stage: int, stages: int, micro_batches: int, chunks: in
     return steps
 
 
+def comm_order(stage: int, stages: int, micro_batches: int, chunks: int = 1
+               ) -> List[Tuple[str, tuple]]:
+    """The order in which one rank's ``train_step`` issues receives, compute units and sends:
+    ``("recv" | "send", (kind, src, dst))`` and ``("compute", unit)``.  ``kind`` names the stream of
+    messages (``f`` / ``b`` inside a chunk, ``fw`` / ``bw`` between chunks)."""
+    P, V, s = stages, stages * chunks, stage
+    if chunks == 1:
+        units = [(kind, 0, i) for kind, i in schedule_1f1b(s, P, micro_batches)]
+    else:
+        units = schedule_interleaved(s, P, micro_batches, chunks)
+    ops: List[Tuple[str, tuple]] = []
+    for kind, c, i in units:
+        k = c * P + s
+        if kind == "F":
+            if k != 0:
+                ops.append(("recv", ("f" if s > 0 else "fw", (s - 1) % P, s)))
+            ops.append(("compute", (kind, c, i)))
+            if k != V - 1:
+                ops.append(("send", ("f" if s < P - 1 else "fw", s, (s + 1) % P)))
+        else:
+            if k != V - 1:
+                ops.append(("recv", ("b" if s < P - 1 else "bw", (s + 1) % P, s)))
+            ops.append(("compute", (kind, c, i)))
+            if k != 0:
+                ops.append(("send", ("b" if s > 0 else "bw", s, (s - 1) % P)))
+    return ops
+
+
+def nccl_order_deadlocks(stages: int, micro_batches: int, chunks: int = 1) -> bool:
+    """Event model of :func:`comm_order` run with NCCL point-to-point kernels on GPUs.
+
+    A send or receive kernel starts once the compute issued before it is done and the previous
+    message between the same two ranks in the same group is through; it finishes once its
+    counterpart on the other rank has started (a rendezvous).  A compute unit starts when the
+    compute before it is done, its input has arrived and no communication kernel that this rank
+    has started is still spinning (the pessimistic part: a spinning kernel is assumed to hold back
+    the kernels queued behind it).  Returns True when some rank cannot finish its list."""
+    ranks = [comm_order(s, stages, micro_batches, chunks) for s in range(stages)]
+    started = [[False] * len(r) for r in ranks]
+    finished = [[False] * len(r) for r in ranks]
+    sends: Dict[tuple, list] = {}
+    recvs: Dict[tuple, list] = {}
+    for r, ops in enumerate(ranks):
+        for idx, (kind, d) in enumerate(ops):
+            if kind == "send":
+                sends.setdefault(d, []).append((r, idx))
+            elif kind == "recv":
+                recvs.setdefault(d, []).append((r, idx))
+    peer = {}
+    for d, lst in sends.items():
+        for a, b in zip(lst, recvs[d]):
+            peer[a], peer[b] = b, a
+    progress = True
+    while progress:
+        progress = False
+        for r, ops in enumerate(ranks):
+            for idx, (kind, d) in enumerate(ops):
+                if finished[r][idx]:
+                    continue
+                if not started[r][idx]:
+                    ok = all(finished[r][j] for j in range(idx) if ops[j][0] == "compute")
+                    if kind == "compute":
+                        ok = ok and all(finished[r][j] for j in range(idx)
+                                        if ops[j][0] == "recv" or started[r][j])
+                    else:
+                        key = (d[0], frozenset(d[1:]))
+                        ok = ok and all(finished[r][j] for j in range(idx)
+                                        if ops[j][0] != "compute"
+                                        and (ops[j][1][0], frozenset(ops[j][1][1:])) == key)
+                    if ok:
+                        started[r][idx] = progress = True
+                        if kind == "compute":
+                            finished[r][idx] = True
+                if started[r][idx] and not finished[r][idx] and started[peer[(r, idx)][0]][peer[(r, idx)][1]]:
+                    finished[r][idx] = progress = True
+    return not all(all(f) for f in finished)
+
+
+class PeerRing:
+    """Receive slots of one rank for the pipeline's message streams, in a symmetric NVLink-mapped
+    buffer: ``count[kind]`` slots of one activation tensor each plus one 64-bit epoch flag per
+    slot.  The j-th message of a stream in a step always uses slot j, so nothing is overwritten
+    within a step; the next step's message j is produced only after work that follows, on every
+    rank in between, the consumption of this step's (the pipeline's own data dependencies), so no
+    acknowledgement travels back."""
+
+    KINDS = ("f", "b", "fw", "bw")
+
+    def __init__(self, group, device, shape, dtype, counts: Dict[str, int],
+                 limit_ms: float = 30000.0) -> None:
+        from .symm import SymmetricBuffer
+        self.shape, self.dtype = tuple(shape), dtype
+        self.numel = 1
+        for n in self.shape:
+            self.numel *= n
+        item = torch.empty((), dtype=dtype).element_size()
+        self.slot_bytes = (self.numel * item + 255) // 256 * 256
+        self.counts = {k: int(counts.get(k, 0)) for k in self.KINDS}
+        self.data_off, self.flag_off = {}, {}
+        off = 0
+        for k in self.KINDS:
+            self.data_off[k] = off
+            off += self.counts[k] * self.slot_bytes
+        for k in self.KINDS:
+            self.flag_off[k] = off
+            off += (self.counts[k] * 8 + 255) // 256 * 256
+        self.buf = SymmetricBuffer(max(off, 256), group, torch.device(device))
+        self.device = torch.device(device)
+        self.limit_ns = int(limit_ms * 1e6)
+        self.epoch = 0
+        self.copy_bytes = self.numel * item
+
+    def next_step(self) -> None:
+        self.epoch += 1
+
+    def push(self, kind: str, j: int, peer: int, t: torch.Tensor) -> None:
+        """Copy ``t`` into slot ``j`` of stream ``kind`` on group rank ``peer`` and raise its flag."""
+        import ctypes
+        from ..ops import _lib
+        t = t.contiguous()
+        lib = _lib.lib()
+        dst = self.buf.ptrs[peer] + self.data_off[kind] + j * self.slot_bytes
+        nbytes = (self.copy_bytes + 15) // 16 * 16
+        rc = lib.cb_peer_copy(_lib.ptr(t), ctypes.c_void_p(dst), ctypes.c_size_t(nbytes), 0,
+                              _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_peer_copy")
+        flag = (ctypes.c_void_p * 1)(self.buf.ptrs[peer] + self.flag_off[kind] + j * 8)
+        rc = lib.cb_signal_peers(flag, 0, 1, 0, ctypes.c_ulonglong(self.epoch), _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_signal_peers")
+
+    def take(self, kind: str, j: int) -> torch.Tensor:
+        """Make the stream wait (bounded) for message ``j`` of stream ``kind``; returns the slot."""
+        import ctypes
+        from ..ops import _lib
+        lib = _lib.lib()
+        flag = self.buf.local_ptr + self.flag_off[kind] + j * 8
+        rc = lib.cb_wait_flags(ctypes.c_void_p(flag), 0, 1, ctypes.c_ulonglong(self.epoch),
+                               ctypes.c_ulonglong(self.limit_ns),
+                               _lib.ptr(_lib.status_buffer(self.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, "cb_wait_flags")
+        off = self.data_off[kind] + j * self.slot_bytes
+        return self.buf.view(self.dtype, off, self.numel).view(self.shape)
+
+    def close(self) -> None:
+        self.buf.close()
+
+
+class _PeerChannel:
+    """The interface of :class:`_Channel` over a :class:`PeerRing`."""
+
+    def __init__(self, ring: PeerRing, kind: str, peer: int, recv: bool) -> None:
+        self.ring, self.kind, self.peer, self.recv = ring, kind, peer, recv
+        self.n = 0
+        self.pending: List = []
+
+    def post_recv(self, force: bool = False) -> None:
+        pass
+
+    def take(self) -> torch.Tensor:
+        t = self.ring.take(self.kind, self.n)
+        self.n += 1
+        return t
+
+    def send(self, t: torch.Tensor) -> None:
+        self.ring.push(self.kind, self.n, self.peer, t)
+        self.n += 1
+
+    def drain(self) -> None:
+        pass
+
+
 class _Channel:
     """One direction between two neighbouring stages: posts receives ahead and keeps sends alive."""
 
@@ -130,14 +312,42 @@ class _Channel:
         self.pending.clear()
 
 
+def _check_transport(transport: str, device) -> str:
+    if transport not in ("nccl", "peer"):
+        raise ProcessingError.invalid_input(f"unknown pipeline transport {transport!r}")
+    if transport == "peer" and torch.device(device).type != "cuda":
+        raise ProcessingError.unsupported("the peer-memory pipeline transport on a CPU rank",
+                                          "it moves tensors with NVLink peer stores")
+    return transport
+
+
+def _ring_for(ring: Optional[PeerRing], group, device, shape, dtype, counts,
+              limit_ms: float = 30000.0) -> PeerRing:
+    """The ring that fits these messages: the one at hand, or a new one (every rank of the group
+    reaches this at the same step, so the allocation is collective)."""
+    want = {k: int(counts.get(k, 0)) for k in PeerRing.KINDS}
+    if ring is not None and ring.shape == tuple(shape) and ring.dtype == dtype \
+            and ring.counts == want:
+        return ring
+    if ring is not None:
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)       # nobody still pushes into the buffer that goes away
+        ring.close()
+    return PeerRing(group, device, shape, dtype, want, limit_ms)
+
+
 class PipelineStage:
     """One rank's share of a pipelined decoder plus the 1F1B step loop."""
 
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16, train_cfg=None, schedule=None) -> None:
+                 dtype: torch.dtype = torch.bfloat16, train_cfg=None, schedule=None,
+                 transport: str = "nccl", peer_wait_ms: float = 30000.0) -> None:
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
         self.schedule = schedule          # object with at(step) -> learning rate
+        self.transport = _check_transport(transport, device)
+        self._ring: Optional[PeerRing] = None
+        self.peer_wait_ms = peer_wait_ms       # bound of one wait for a message, peer transport
         self.group = group
         self.stage = dist.get_rank(group) if group is not None else 0
         self.stages = dist.get_world_size(group) if group is not None else 1
@@ -193,8 +403,18 @@ class PipelineStage:
         b, S = ref.shape[1], ref.shape[2]
         T, H = b * S, self.cfg.hidden_dim
         act_dtype = m.p16.dtype
-        chans: Dict[str, _Channel] = {}
-        if self.stages > 1:
+        chans: Dict[str, object] = {}
+        if self.stages > 1 and self.transport == "peer":
+            self._ring = _ring_for(self._ring, self.group, self.device, (T, H), act_dtype,
+                                   {"f": M, "b": M}, self.peer_wait_ms)
+            self._ring.next_step()
+            if not self.first:
+                chans["rf"] = _PeerChannel(self._ring, "f", self.stage - 1, True)
+                chans["sb"] = _PeerChannel(self._ring, "b", self.stage - 1, False)
+            if not self.last:
+                chans["sf"] = _PeerChannel(self._ring, "f", self.stage + 1, False)
+                chans["rb"] = _PeerChannel(self._ring, "b", self.stage + 1, True)
+        elif self.stages > 1:
             if not self.first:
                 chans["rf"] = _Channel(self.fwd_group, self._ranks[self.stage - 1], (T, H),
                                        act_dtype, self.device, M, True)
@@ -262,7 +482,8 @@ class InterleavedPipelineStage:
 
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, chunks: int = 2,
                  seed: int = 0, dtype: torch.dtype = torch.bfloat16, train_cfg=None,
-                 schedule=None) -> None:
+                 schedule=None, transport: Optional[str] = None,
+                 peer_wait_ms: float = 30000.0) -> None:
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
         self.schedule = schedule
@@ -272,6 +493,16 @@ class InterleavedPipelineStage:
         if self.stages < 2 or chunks < 2:
             raise ProcessingError.invalid_input(
                 "the interleaved pipeline needs at least two ranks and two chunks per rank")
+        on_gpu = torch.device(device).type == "cuda"
+        self.transport = _check_transport(transport or ("peer" if on_gpu else "nccl"), device)
+        if on_gpu and self.transport == "nccl" \
+                and nccl_order_deadlocks(self.stages, micro_batches, chunks):
+            raise ProcessingError.unsupported(
+                "this interleaved schedule over NCCL point-to-point on GPUs",
+                "its order of sends and receives can stop under rendezvous semantics; "
+                "use transport='peer'")
+        self._ring: Optional[PeerRing] = None
+        self.peer_wait_ms = peer_wait_ms
         self.M, self.v, self.cfg = micro_batches, chunks, cfg
         self.device = torch.device(device)
         P, V = self.stages, self.stages * chunks
@@ -350,10 +581,19 @@ class InterleavedPipelineStage:
         nxt, prv = self._ranks[(s + 1) % P], self._ranks[(s - 1) % P]
         n_wrap = M * (v - 1)
 
+        if self.transport == "peer":
+            self._ring = _ring_for(self._ring, self.group, self.device, (T, H), dt,
+                                   {"f": M * v, "b": M * v, "fw": n_wrap, "bw": n_wrap},
+                                   self.peer_wait_ms)
+            self._ring.next_step()
+            nxt, prv = (s + 1) % P, (s - 1) % P      # group ranks index the ring's peer pointers
+
         def chan(key, peer, count, recv):
+            if self.transport == "peer":
+                return _PeerChannel(self._ring, key, peer, recv)
             return _Channel(self._groups[key], peer, (T, H), dt, self.device, count, recv)
 
-        ch: Dict[str, _Channel] = {}
+        ch: Dict[str, object] = {}
         if s > 0:                       # inside a chunk: s-1 -> s forward, s -> s-1 backward
             ch["rf"] = chan("f", prv, M * v, True)
             ch["sb"] = chan("b", prv, M * v, False)

@@ -8,7 +8,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from coeus_b200.parallel.pp import schedule_1f1b, schedule_interleaved, split_layers
+from coeus_b200.parallel.pp import (comm_order, nccl_order_deadlocks, schedule_1f1b,
+                                     schedule_interleaved, split_layers)
 
 
 def test_split_layers():
@@ -153,6 +154,30 @@ def test_interleaved_schedule_runs_without_deadlock_and_in_fifo_order(P, M, v):
                 progress = True
     assert all(pc[s] == len(steps[s]) for s in range(P)), "deadlock"
     assert len(done_b) == V * M
+
+
+def test_launch_order_model_of_nccl_point_to_point():
+    """The event model of rendezvous sends and receives: the 1F1B order always finishes, the
+    interleaved order only while there are no more micro-batches than stages; the peer-memory
+    transport, whose sends never wait, is what the interleaved stage uses on GPUs."""
+    for P, M in [(2, 2), (2, 8), (4, 4), (4, 8), (8, 16)]:
+        assert not nccl_order_deadlocks(P, M)
+    for P, v, M in [(2, 2, 2), (4, 2, 4), (8, 2, 8)]:
+        assert not nccl_order_deadlocks(P, M, v)
+    for P, v, M in [(2, 2, 4), (2, 4, 8), (4, 2, 8), (3, 3, 9), (8, 2, 16)]:
+        assert nccl_order_deadlocks(P, M, v)
+    # the order that the model walks is the order of the step loop: every unit computes once,
+    # between the receive of its input and the send of its output
+    ops = comm_order(1, 4, 8, 2)
+    units = [d for kind, d in ops if kind == "compute"]
+    assert units == schedule_interleaved(1, 4, 8, 2)
+    assert sum(kind == "send" for kind, _ in ops) == sum(kind == "recv" for kind, _ in ops) == 32
+    from coeus_b200.foundation.error import ProcessingError
+    from coeus_b200.parallel.pp import _check_transport
+    with pytest.raises(ProcessingError):
+        _check_transport("peer", "cpu")
+    with pytest.raises(ProcessingError):
+        _check_transport("carrier pigeon", "cpu")
 
 
 def _worker_interleaved(rank, world, port, ids, tgt, out):

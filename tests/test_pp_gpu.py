@@ -1,5 +1,6 @@
-"""Pipeline parallelism over NCCL point-to-point on two GPUs against one GPU with gradient
-accumulation."""
+"""Pipeline parallelism on two GPUs against one GPU with gradient accumulation: the 1F1B schedule
+over NCCL point-to-point and over NVLink peer memory, and the interleaved schedule (two chunks of
+blocks per rank) over peer memory."""
 import os
 
 import pytest
@@ -21,7 +22,7 @@ def _train_cfg():
     return TrainConfig(learning_rate=0.05, eps=1.0, weight_decay=0.0)
 
 
-def _worker(rank, world, port, ids, tgt, out):
+def _worker(rank, world, port, ids, tgt, mode, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -29,19 +30,29 @@ def _worker(rank, world, port, ids, tgt, out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     from coeus_b200.ops import _lib
-    from coeus_b200.parallel.pp import PipelineStage
-    st = PipelineStage(_cfg(), dist.group.WORLD, dev, micro_batches=ids.shape[0], seed=4,
-                       train_cfg=_train_cfg())
+    from coeus_b200.parallel.pp import InterleavedPipelineStage, PipelineStage
+    if mode == "interleaved":
+        st = InterleavedPipelineStage(_cfg(), dist.group.WORLD, dev, micro_batches=ids.shape[0],
+                                      chunks=2, seed=4, train_cfg=_train_cfg(),
+                                      peer_wait_ms=5000.0)
+        assert st.transport == "peer"
+        models = st.models
+    else:
+        st = PipelineStage(_cfg(), dist.group.WORLD, dev, micro_batches=ids.shape[0], seed=4,
+                           train_cfg=_train_cfg(), transport=mode, peer_wait_ms=5000.0)
+        models = [st.model]
     ids, tgt = ids.to(dev), tgt.to(dev)
-    losses = [float(st.train_step(ids, tgt)) for _ in range(2)]
+    losses = [float(st.train_step(ids, tgt)) for _ in range(3)]
     torch.cuda.synchronize()
     _lib.check_status(dev)
-    out.put((rank, losses, {k: v.float().cpu().numpy().copy() for k, v in st.model.master.items()}))
+    weights = {k: v.float().cpu().numpy().copy() for m in models for k, v in m.master.items()}
+    out.put((rank, losses, weights))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_stage_pipeline_matches_one_gpu():
+@pytest.mark.parametrize("mode", ["nccl", "peer", "interleaved"])
+def test_two_stage_pipeline_matches_one_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from mp_util import run_ranks
@@ -54,7 +65,7 @@ def test_two_stage_pipeline_matches_one_gpu():
     full = DecoderLM(_cfg(), "cuda", seed=4)
     opt = AdamW(_train_cfg().adamw(), 0, full.n_flat, full.layout.decay_end, "cuda")
     ref_losses = []
-    for _ in range(2):
+    for _ in range(3):
         full.zero_grad()
         tot = 0.0
         for i in range(M):
@@ -63,8 +74,8 @@ def test_two_stage_pipeline_matches_one_gpu():
             full.backward()
         opt.step(full.p32, full.g32, full.p16, 1.0)
         ref_losses.append(tot)
-    res = {r[0]: r for r in run_ranks(_worker, 2, (ids, tgt), results=2)}
-    for step in range(2):
+    res = {r[0]: r for r in run_ranks(_worker, 2, (ids, tgt, mode), results=2, timeout=150.0)}
+    for step in range(3):
         assert abs(res[1][1][step] - ref_losses[step]) < 2e-2
     for rank in range(2):
         for name, got in res[rank][2].items():
