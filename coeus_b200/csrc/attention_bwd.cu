@@ -65,52 +65,49 @@ struct AttnBwdCfg {
 };
 
 // delta[b,h,s] = sum_d dO[s, h*dh + d] * O[s, h*dh + d]
-// dh / 8 threads per (token, head), eight columns a thread; four work items a thread and round,
-// their loads issued together (eight 16-byte loads in flight a thread).
+// A warp takes one token at a time: its nh * dh / 8 vectors of eight columns go round the lanes,
+// four vectors a lane and round with their loads issued together (eight 16-byte loads in flight
+// a lane); the dh / 8 lanes of a head add up with shuffles.  All index arithmetic is 32-bit and
+// per token, not per vector.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO,
                                   const __nv_bfloat16* __restrict__ O, float* __restrict__ delta,
-                                  int B, int S, int nh, int dh, int lddo, int ldo) {
+                                  int rows, int S, int nh, int dh, int lddo, int ldo) {
   constexpr int UNR = 4;
-  const int tpg = dh / 8;  // threads per (token, head)
-  const size_t total = static_cast<size_t>(B) * S * nh * tpg;
-  const size_t padded = ((total + 31) / 32) * 32;
-  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < padded;
-       i0 += stride * UNR) {
-    uint4 a[UNR], b[UNR];
-    size_t tok[UNR];
-    int h[UNR];
+  const int lane = threadIdx.x & 31;
+  const int tpg = dh >> 3;              // lanes per head: 8 (dh 64) or 16 (dh 128)
+  const int nvec = nh * tpg;            // vectors per token
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int GW = (gridDim.x * blockDim.x) >> 5;
+  for (int tok = gw; tok < rows; tok += GW) {
+    const int bb = tok / S, ss = tok - bb * S;
+    const __nv_bfloat16* pa = dO + static_cast<size_t>(tok) * lddo;
+    const __nv_bfloat16* pb = O + static_cast<size_t>(tok) * ldo;
+    float* out = delta + static_cast<size_t>(bb) * nh * S + ss;
+    for (int c0 = 0; c0 < nvec; c0 += 32 * UNR) {
+      uint4 a[UNR], b[UNR];
 #pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const size_t i = i0 + u * stride;
-      a[u] = make_uint4(0u, 0u, 0u, 0u);
-      b[u] = make_uint4(0u, 0u, 0u, 0u);
-      tok[u] = 0;
-      h[u] = 0;
-      if (i < total) {
-        const int part = static_cast<int>(i % tpg);
-        h[u] = static_cast<int>((i / tpg) % nh);
-        tok[u] = i / (static_cast<size_t>(tpg) * nh);
-        a[u] = *reinterpret_cast<const uint4*>(dO + tok[u] * lddo + h[u] * dh + part * 8);
-        b[u] = *reinterpret_cast<const uint4*>(O + tok[u] * ldo + h[u] * dh + part * 8);
+      for (int u = 0; u < UNR; ++u) {
+        const int c = c0 + u * 32 + lane;
+        a[u] = make_uint4(0u, 0u, 0u, 0u);
+        b[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < nvec) {
+          a[u] = *reinterpret_cast<const uint4*>(pa + c * 8);
+          b[u] = *reinterpret_cast<const uint4*>(pb + c * 8);
+        }
       }
-    }
 #pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const size_t i = i0 + u * stride;
-      if (i >= padded) break;          // uniform over the warp: stride and padded are multiples of 32
-      const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
-      const uint32_t bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
-      float s = 0.f;
+      for (int u = 0; u < UNR; ++u) {
+        const int c = c0 + u * 32 + lane;
+        const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+        const uint32_t bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+        float s = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 fa = unpack_bf16x2(aw[e]), fb = unpack_bf16x2(bw[e]);
-        s += fa.x * fb.x + fa.y * fb.y;
-      }
-      for (int o = tpg / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (i < total && (i % tpg) == 0) {
-        const size_t bb = tok[u] / S, ss = tok[u] % S;
-        delta[(bb * nh + h[u]) * S + ss] = s;
+        for (int e = 0; e < 4; ++e) {
+          const float2 fa = unpack_bf16x2(aw[e]), fb = unpack_bf16x2(bw[e]);
+          s += fa.x * fb.x + fa.y * fb.y;
+        }
+        for (int o = tpg >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (c < nvec && (lane & (tpg - 1)) == 0) out[static_cast<size_t>(c / tpg) * S] = s;
       }
     }
   }
@@ -595,11 +592,11 @@ extern "C" int cb_attn_bwd_dropout(const void* dO, const void* q, const void* k,
     if (make_tmap_bf16_3d(&tdv, out + 2 * H, H, S, B, ldd, slab, 128) != 0) return -9;
   }
   {
-    const size_t work = rows * nh * (dh / 8);   // four work items a thread
-    const int blocks = static_cast<int>(std::min<size_t>((work + 1023) / 1024, sm_count() * 32));
+    // a warp per token, eight warps a block
+    const int blocks = static_cast<int>(std::min<size_t>((rows + 7) / 8, sm_count() * 16));
     attn_delta_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dO),
-                                              static_cast<const __nv_bfloat16*>(o), delta, B, S,
-                                              nh, dh, lddo, ldo);
+                                              static_cast<const __nv_bfloat16*>(o), delta,
+                                              static_cast<int>(rows), S, nh, dh, lddo, ldo);
   }
   AttnBwdArgs a;
   a.B = B; a.S = S; a.nh = nh;
