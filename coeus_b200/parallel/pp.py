@@ -24,6 +24,7 @@ holds back).  The interleaved stage therefore uses the peer transport on GPUs.
 """
 from __future__ import annotations
 
+import functools
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -174,18 +175,91 @@ def nccl_order_deadlocks(stages: int, micro_batches: int, chunks: int = 1) -> bo
     return not all(all(f) for f in finished)
 
 
+def ring_depths(stages: int, micro_batches: int, chunks: int = 1) -> Dict[str, int]:
+    """See :func:`_ring_depths` (this wrapper keeps the results of earlier calls)."""
+    return dict(_ring_depths_cached(stages, micro_batches, chunks))
+
+
+@functools.lru_cache(maxsize=None)
+def _ring_depths_cached(stages: int, micro_batches: int, chunks: int) -> tuple:
+    return tuple(sorted(_ring_depths(stages, micro_batches, chunks).items()))
+
+
+def _ring_depths(stages: int, micro_batches: int, chunks: int = 1) -> Dict[str, int]:
+    """How many receive slots a stream of messages needs when the receiver copies a message out
+    of its slot as it takes it and nothing is acknowledged.
+
+    Message ``k`` of a stream may overwrite message ``j`` (``k > j``) only if its send is ordered
+    after the receipt of ``j`` by the step's own dependencies: program order on each rank plus
+    "a message is received after it is sent".  For every receipt the earliest point of every
+    rank's program that is ordered after it is propagated to a fixed point; the first later send
+    of the stream at or past the sender's point gives the distance that is safe for ``j``, and the
+    depth of a kind of stream (``f`` / ``b`` inside a chunk, ``fw`` / ``bw`` between chunks) is
+    the largest distance over its messages and ranks.  A receipt that no later send of the step
+    follows is followed by the next step's first message (all of a step's receipts precede the
+    next step's sends: its forward traffic starts at the first rank, which finishes a step last,
+    and its backward traffic follows that forward traffic), i.e. by the message ``count - j``
+    places on."""
+    ranks = [comm_order(s, stages, micro_batches, chunks) for s in range(stages)]
+    sends: Dict[tuple, list] = {}
+    recvs: Dict[tuple, list] = {}
+    for r, ops in enumerate(ranks):
+        for idx, (kind, d) in enumerate(ops):
+            if kind == "send":
+                sends.setdefault(d, []).append((r, idx))
+            elif kind == "recv":
+                recvs.setdefault(d, []).append((r, idx))
+    # for every send event, the receive it lands in
+    lands: List[Dict[int, Tuple[int, int]]] = [dict() for _ in ranks]
+    for d, lst in sends.items():
+        for (r, idx), dest in zip(lst, recvs[d]):
+            lands[r][idx] = dest
+    send_idx = [sorted(m) for m in lands]
+    depth: Dict[str, int] = {}
+    for d, rlist in recvs.items():
+        slist = sends[d]
+        sender = slist[0][0]
+        need = 1
+        for j, (r0, i0) in enumerate(rlist):
+            earliest = [len(ops) for ops in ranks]       # first op of each rank ordered after
+            earliest[r0] = i0 + 1
+            done_from = [len(ops) for ops in ranks]      # sends at or past this index are relaxed
+            changed = True
+            while changed:
+                changed = False
+                for r in range(stages):
+                    if earliest[r] < done_from[r]:
+                        for idx in send_idx[r]:
+                            if earliest[r] <= idx < done_from[r]:
+                                rr, ii = lands[r][idx]
+                                if ii + 1 < earliest[rr]:
+                                    earliest[rr] = ii + 1
+                        done_from[r] = earliest[r]
+                        changed = True
+            k = next((k for k in range(j + 1, len(slist)) if slist[k][1] >= earliest[sender]),
+                     len(slist))
+            need = max(need, k - j)
+        depth[d[0]] = max(depth.get(d[0], 1), need)
+    return depth
+
+
 class PeerRing:
     """Receive slots of one rank for the pipeline's message streams, in a symmetric NVLink-mapped
-    buffer: ``count[kind]`` slots of one activation tensor each plus one 64-bit epoch flag per
-    slot.  The j-th message of a stream in a step always uses slot j, so nothing is overwritten
-    within a step; the next step's message j is produced only after work that follows, on every
-    rank in between, the consumption of this step's (the pipeline's own data dependencies), so no
-    acknowledgement travels back."""
+    buffer: ``depths[kind]`` slots of one activation tensor each plus one 64-bit flag per slot.
+
+    Both ends of a stream count its messages (over all steps): message ``n`` goes to slot
+    ``n % depth`` and raises that slot's flag to ``n + 1``; the receiver's stream waits for the
+    flag to reach ``n + 1``.  With ``copy_out`` the receiver copies the tensor out of the slot as
+    it takes it, and the depth only has to cover the messages whose send is not ordered after
+    that receipt (:func:`ring_depths`); without it the tensor is used in place for the rest of
+    the step, and the depth is the number of messages of a step.  Either way no acknowledgement
+    travels back: the pipeline's own data dependencies order every overwrite after the last read
+    of what it overwrites."""
 
     KINDS = ("f", "b", "fw", "bw")
 
-    def __init__(self, group, device, shape, dtype, counts: Dict[str, int],
-                 limit_ms: float = 30000.0) -> None:
+    def __init__(self, group, device, shape, dtype, depths: Dict[str, int],
+                 limit_ms: float = 30000.0, copy_out: bool = False) -> None:
         from .symm import SymmetricBuffer
         self.shape, self.dtype = tuple(shape), dtype
         self.numel = 1
@@ -193,51 +267,57 @@ class PeerRing:
             self.numel *= n
         item = torch.empty((), dtype=dtype).element_size()
         self.slot_bytes = (self.numel * item + 255) // 256 * 256
-        self.counts = {k: int(counts.get(k, 0)) for k in self.KINDS}
+        self.depths = {k: int(depths.get(k, 0)) for k in self.KINDS}
+        self.copy_out = copy_out
         self.data_off, self.flag_off = {}, {}
         off = 0
         for k in self.KINDS:
             self.data_off[k] = off
-            off += self.counts[k] * self.slot_bytes
+            off += self.depths[k] * self.slot_bytes
         for k in self.KINDS:
             self.flag_off[k] = off
-            off += (self.counts[k] * 8 + 255) // 256 * 256
+            off += (self.depths[k] * 8 + 255) // 256 * 256
         self.buf = SymmetricBuffer(max(off, 256), group, torch.device(device))
         self.device = torch.device(device)
         self.limit_ns = int(limit_ms * 1e6)
-        self.epoch = 0
         self.copy_bytes = self.numel * item
+        self.sent = {k: 0 for k in self.KINDS}       # messages pushed / taken so far, per stream
+        self.taken = {k: 0 for k in self.KINDS}
 
-    def next_step(self) -> None:
-        self.epoch += 1
-
-    def push(self, kind: str, j: int, peer: int, t: torch.Tensor) -> None:
-        """Copy ``t`` into slot ``j`` of stream ``kind`` on group rank ``peer`` and raise its flag."""
+    def push(self, kind: str, peer: int, t: torch.Tensor) -> None:
+        """Copy ``t`` into the next slot of stream ``kind`` on group rank ``peer``, raise its flag."""
         import ctypes
         from ..ops import _lib
         t = t.contiguous()
         lib = _lib.lib()
-        dst = self.buf.ptrs[peer] + self.data_off[kind] + j * self.slot_bytes
+        n = self.sent[kind]
+        slot = n % self.depths[kind]
+        self.sent[kind] = n + 1
+        dst = self.buf.ptrs[peer] + self.data_off[kind] + slot * self.slot_bytes
         nbytes = (self.copy_bytes + 15) // 16 * 16
         rc = lib.cb_peer_copy(_lib.ptr(t), ctypes.c_void_p(dst), ctypes.c_size_t(nbytes), 0,
                               _lib.stream_ptr())
         _lib.check_rc(rc, "cb_peer_copy")
-        flag = (ctypes.c_void_p * 1)(self.buf.ptrs[peer] + self.flag_off[kind] + j * 8)
-        rc = lib.cb_signal_peers(flag, 0, 1, 0, ctypes.c_ulonglong(self.epoch), _lib.stream_ptr())
+        flag = (ctypes.c_void_p * 1)(self.buf.ptrs[peer] + self.flag_off[kind] + slot * 8)
+        rc = lib.cb_signal_peers(flag, 0, 1, 0, ctypes.c_ulonglong(n + 1), _lib.stream_ptr())
         _lib.check_rc(rc, "cb_signal_peers")
 
-    def take(self, kind: str, j: int) -> torch.Tensor:
-        """Make the stream wait (bounded) for message ``j`` of stream ``kind``; returns the slot."""
+    def take(self, kind: str) -> torch.Tensor:
+        """Make the stream wait (bounded) for the next message of stream ``kind``; returns it."""
         import ctypes
         from ..ops import _lib
         lib = _lib.lib()
-        flag = self.buf.local_ptr + self.flag_off[kind] + j * 8
-        rc = lib.cb_wait_flags(ctypes.c_void_p(flag), 0, 1, ctypes.c_ulonglong(self.epoch),
+        n = self.taken[kind]
+        slot = n % self.depths[kind]
+        self.taken[kind] = n + 1
+        flag = self.buf.local_ptr + self.flag_off[kind] + slot * 8
+        rc = lib.cb_wait_flags(ctypes.c_void_p(flag), 0, 1, ctypes.c_ulonglong(n + 1),
                                ctypes.c_ulonglong(self.limit_ns),
                                _lib.ptr(_lib.status_buffer(self.device)), _lib.stream_ptr())
         _lib.check_rc(rc, "cb_wait_flags")
-        off = self.data_off[kind] + j * self.slot_bytes
-        return self.buf.view(self.dtype, off, self.numel).view(self.shape)
+        off = self.data_off[kind] + slot * self.slot_bytes
+        t = self.buf.view(self.dtype, off, self.numel).view(self.shape)
+        return t.clone() if self.copy_out else t
 
     def close(self) -> None:
         self.buf.close()
@@ -248,20 +328,16 @@ class _PeerChannel:
 
     def __init__(self, ring: PeerRing, kind: str, peer: int, recv: bool) -> None:
         self.ring, self.kind, self.peer, self.recv = ring, kind, peer, recv
-        self.n = 0
         self.pending: List = []
 
     def post_recv(self, force: bool = False) -> None:
         pass
 
     def take(self) -> torch.Tensor:
-        t = self.ring.take(self.kind, self.n)
-        self.n += 1
-        return t
+        return self.ring.take(self.kind)
 
     def send(self, t: torch.Tensor) -> None:
-        self.ring.push(self.kind, self.n, self.peer, t)
-        self.n += 1
+        self.ring.push(self.kind, self.peer, t)
 
     def drain(self) -> None:
         pass
@@ -321,19 +397,30 @@ def _check_transport(transport: str, device) -> str:
     return transport
 
 
-def _ring_for(ring: Optional[PeerRing], group, device, shape, dtype, counts,
-              limit_ms: float = 30000.0) -> PeerRing:
+def _check_slots(peer_slots: str) -> str:
+    if peer_slots not in ("bounded", "message"):
+        raise ProcessingError.invalid_input(f"unknown slot policy {peer_slots!r}")
+    return peer_slots
+
+
+def _ring_for(ring: Optional[PeerRing], group, device, shape, dtype, counts, bounded: bool,
+              stages: int, micro_batches: int, chunks: int, limit_ms: float = 30000.0) -> PeerRing:
     """The ring that fits these messages: the one at hand, or a new one (every rank of the group
-    reaches this at the same step, so the allocation is collective)."""
+    reaches this at the same step, so the allocation is collective).  ``bounded``: slots for the
+    messages that can be on their way at once, copied out on receipt; else a slot per message of
+    a step, used in place."""
     want = {k: int(counts.get(k, 0)) for k in PeerRing.KINDS}
+    if bounded:
+        need = ring_depths(stages, micro_batches, chunks)
+        want = {k: min(want[k], need.get(k, 1)) if want[k] else 0 for k in want}
     if ring is not None and ring.shape == tuple(shape) and ring.dtype == dtype \
-            and ring.counts == want:
+            and ring.depths == want and ring.copy_out == bounded:
         return ring
     if ring is not None:
         torch.cuda.synchronize(device)
         dist.barrier(group=group)       # nobody still pushes into the buffer that goes away
         ring.close()
-    return PeerRing(group, device, shape, dtype, want, limit_ms)
+    return PeerRing(group, device, shape, dtype, want, limit_ms, copy_out=bounded)
 
 
 class PipelineStage:
@@ -341,13 +428,15 @@ class PipelineStage:
 
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, train_cfg=None, schedule=None,
-                 transport: str = "nccl", peer_wait_ms: float = 30000.0) -> None:
+                 transport: str = "nccl", peer_wait_ms: float = 30000.0,
+                 peer_slots: str = "bounded") -> None:
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
         self.schedule = schedule          # object with at(step) -> learning rate
         self.transport = _check_transport(transport, device)
         self._ring: Optional[PeerRing] = None
         self.peer_wait_ms = peer_wait_ms       # bound of one wait for a message, peer transport
+        self.peer_slots = _check_slots(peer_slots)
         self.group = group
         self.stage = dist.get_rank(group) if group is not None else 0
         self.stages = dist.get_world_size(group) if group is not None else 1
@@ -406,8 +495,8 @@ class PipelineStage:
         chans: Dict[str, object] = {}
         if self.stages > 1 and self.transport == "peer":
             self._ring = _ring_for(self._ring, self.group, self.device, (T, H), act_dtype,
-                                   {"f": M, "b": M}, self.peer_wait_ms)
-            self._ring.next_step()
+                                   {"f": M, "b": M}, self.peer_slots == "bounded", self.stages, M,
+                                   1, self.peer_wait_ms)
             if not self.first:
                 chans["rf"] = _PeerChannel(self._ring, "f", self.stage - 1, True)
                 chans["sb"] = _PeerChannel(self._ring, "b", self.stage - 1, False)
@@ -483,7 +572,7 @@ class InterleavedPipelineStage:
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, chunks: int = 2,
                  seed: int = 0, dtype: torch.dtype = torch.bfloat16, train_cfg=None,
                  schedule=None, transport: Optional[str] = None,
-                 peer_wait_ms: float = 30000.0) -> None:
+                 peer_wait_ms: float = 30000.0, peer_slots: str = "bounded") -> None:
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
         self.schedule = schedule
@@ -503,6 +592,7 @@ class InterleavedPipelineStage:
                 "use transport='peer'")
         self._ring: Optional[PeerRing] = None
         self.peer_wait_ms = peer_wait_ms
+        self.peer_slots = _check_slots(peer_slots)
         self.M, self.v, self.cfg = micro_batches, chunks, cfg
         self.device = torch.device(device)
         P, V = self.stages, self.stages * chunks
@@ -584,8 +674,7 @@ class InterleavedPipelineStage:
         if self.transport == "peer":
             self._ring = _ring_for(self._ring, self.group, self.device, (T, H), dt,
                                    {"f": M * v, "b": M * v, "fw": n_wrap, "bw": n_wrap},
-                                   self.peer_wait_ms)
-            self._ring.next_step()
+                                   self.peer_slots == "bounded", P, M, v, self.peer_wait_ms)
             nxt, prv = (s + 1) % P, (s - 1) % P      # group ranks index the ring's peer pointers
 
         def chan(key, peer, count, recv):

@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from coeus_b200.parallel.pp import (comm_order, nccl_order_deadlocks, schedule_1f1b,
+from coeus_b200.parallel.pp import (comm_order, nccl_order_deadlocks, ring_depths, schedule_1f1b,
                                      schedule_interleaved, split_layers)
 
 
@@ -178,6 +178,73 @@ def test_launch_order_model_of_nccl_point_to_point():
         _check_transport("peer", "cpu")
     with pytest.raises(ProcessingError):
         _check_transport("carrier pigeon", "cpu")
+
+
+@pytest.mark.parametrize("P,M,v", [(2, 4, 1), (4, 8, 1), (8, 16, 1), (2, 2, 2), (2, 8, 2), (4, 8, 2),
+                                   (3, 6, 3), (4, 8, 4), (8, 16, 2)])
+def test_ring_depths_hold_under_any_execution_order(P, M, v):
+    """The slot counts of the peer-memory transport: with sends that never wait, ranks that run
+    in any order (random, and each rank in turn pushed as far ahead as it can go) and several
+    steps back to back, a message never lands in a slot whose previous message has not been taken
+    yet; and the depths do not grow with the number of micro-batches."""
+    import random
+    depth = ring_depths(P, M, v)
+    assert all(1 <= d <= 2 * P for d in depth.values())
+    assert ring_depths(P, 4 * M, v) == depth or M <= P
+    steps = 3
+    progs = [comm_order(s, P, M, v) * steps for s in range(P)]
+    for seed in range(40):
+        rng = random.Random(seed)
+        favourite = seed % P if seed < 2 * P else None      # this rank runs whenever it can
+        pc = [0] * P
+        sent, taken = {}, {}
+        while any(pc[r] < len(progs[r]) for r in range(P)):
+            runnable = []
+            for r in range(P):
+                if pc[r] == len(progs[r]):
+                    continue
+                kind, d = progs[r][pc[r]]
+                if kind != "recv" or sent.get(d, 0) > taken.get(d, 0):
+                    runnable.append(r)
+            assert runnable, "the step does not finish with sends that never wait"
+            r = favourite if favourite in runnable else rng.choice(runnable)
+            kind, d = progs[r][pc[r]]
+            if kind == "send":
+                n = sent.get(d, 0)
+                # slot n % depth held message n - depth: it must have been taken already
+                assert n - depth[d[0]] < taken.get(d, 0), (d, n, taken.get(d, 0))
+                sent[d] = n + 1
+            elif kind == "recv":
+                taken[d] = taken.get(d, 0) + 1
+            pc[r] += 1
+    # the depths are exact: hold back one receipt and run everything that does not depend on it;
+    # the sends of its stream that still go out are the ones that may overtake it
+    two = [comm_order(s, P, M, v) * 2 for s in range(P)]
+    need = {}
+    streams = sorted({d for prog in two for kind, d in prog if kind == "recv"})
+    for d in streams:
+        count = sum(1 for kind, dd in two[d[2]] if kind == "recv" and dd == d)
+        for j in range(count // 2):           # receipts of the first step
+            pc = [0] * P
+            sent, taken = {}, {}
+            moved = True
+            while moved:
+                moved = False
+                for r in range(P):
+                    while pc[r] < len(two[r]):
+                        kind, dd = two[r][pc[r]]
+                        if kind == "recv":
+                            if dd == d and taken.get(dd, 0) == j:
+                                break                         # the receipt that is held back
+                            if sent.get(dd, 0) <= taken.get(dd, 0):
+                                break
+                            taken[dd] = taken.get(dd, 0) + 1
+                        elif kind == "send":
+                            sent[dd] = sent.get(dd, 0) + 1
+                        pc[r] += 1
+                        moved = True
+            need[d[0]] = max(need.get(d[0], 1), sent.get(d, 0) - j)
+    assert need == depth
 
 
 def _worker_interleaved(rank, world, port, ids, tgt, out):

@@ -31,27 +31,39 @@ def _worker(rank, world, port, ids, tgt, mode, out):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     from coeus_b200.ops import _lib
     from coeus_b200.parallel.pp import InterleavedPipelineStage, PipelineStage
+    mode, _, slots = mode.partition("-")
+    slots = slots or "bounded"
     if mode == "interleaved":
         st = InterleavedPipelineStage(_cfg(), dist.group.WORLD, dev, micro_batches=ids.shape[0],
                                       chunks=2, seed=4, train_cfg=_train_cfg(),
-                                      peer_wait_ms=5000.0)
+                                      peer_wait_ms=5000.0, peer_slots=slots)
         assert st.transport == "peer"
         models = st.models
     else:
         st = PipelineStage(_cfg(), dist.group.WORLD, dev, micro_batches=ids.shape[0], seed=4,
-                           train_cfg=_train_cfg(), transport=mode, peer_wait_ms=5000.0)
+                           train_cfg=_train_cfg(), transport=mode, peer_wait_ms=5000.0,
+                           peer_slots=slots)
         models = [st.model]
     ids, tgt = ids.to(dev), tgt.to(dev)
     losses = [float(st.train_step(ids, tgt)) for _ in range(3)]
     torch.cuda.synchronize()
     _lib.check_status(dev)
+    if getattr(st, "_ring", None) is not None:
+        # bounded: a handful of slots however many micro-batches; message: one per message
+        from coeus_b200.parallel.pp import ring_depths
+        bounded = ring_depths(world, ids.shape[0], len(models))
+        for kind in ("f", "b"):
+            n = ids.shape[0] * len(models)
+            assert st._ring.depths[kind] == (n if slots == "message" else bounded[kind])
+            assert bounded[kind] <= 3 < n + 1
     weights = {k: v.float().cpu().numpy().copy() for m in models for k, v in m.master.items()}
     out.put((rank, losses, weights))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["nccl", "peer", "interleaved"])
+@pytest.mark.parametrize("mode", ["nccl", "peer", "peer-message", "interleaved",
+                                  "interleaved-message"])
 def test_two_stage_pipeline_matches_one_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
