@@ -248,6 +248,8 @@ class ParallelConfig:
     ep: int = 1
     cp: int = 1
     pp_chunks: int = 1         # > 1: interleaved 1F1B with this many model chunks per rank
+    pp_transport: str = "auto"  # "nccl" (point-to-point) | "peer" (pushes into NVLink peer memory,
+                               # GPUs only) | "auto": nccl for 1F1B, peer for interleaved on GPUs
     sp: bool = True            # sequence-parallel activations inside a tensor-parallel group
     ulysses: bool = False      # context parallelism by head all-to-all instead of a K/V ring
     zero_stage: int = 2        # 0: replicated optimizer state (all-reduce comparator);
@@ -267,6 +269,9 @@ class ParallelConfig:
                                       "activations between blocks sequence-sharded")
         if self.pp_chunks < 1:
             raise ConfigError.invalid("pp_chunks", self.pp_chunks, "Must be >= 1")
+        if self.pp_transport not in ("auto", "nccl", "peer"):
+            raise ConfigError.invalid("pp_transport", self.pp_transport,
+                                      "Must be one of auto, nccl, peer")
         for k in ("dp", "tp", "pp", "ep", "cp"):
             if getattr(self, k) < 1:
                 raise ConfigError.invalid(k, getattr(self, k), "Parallel degree must be >= 1")

@@ -105,13 +105,14 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
 
     if strategy == "pp":
         from ..parallel.pp import InterleavedPipelineStage, PipelineStage
+        transport = None if parallel.pp_transport == "auto" else parallel.pp_transport
         if parallel.pp_chunks > 1:
             st = InterleavedPipelineStage(cfg, group, device, micro_batches,
                                           chunks=parallel.pp_chunks, seed=seed, dtype=dtype,
-                                          train_cfg=tc, schedule=schedule)
+                                          train_cfg=tc, schedule=schedule, transport=transport)
         else:
             st = PipelineStage(cfg, group, device, micro_batches, seed=seed, dtype=dtype,
-                               train_cfg=tc, schedule=schedule)
+                               train_cfg=tc, schedule=schedule, transport=transport or "nccl")
 
         def feed(ids, targets):
             M = micro_batches

@@ -136,3 +136,11 @@ def test_launcher_rejects_products_and_wrong_sizes():
         build_trainer(_cfg(), ParallelConfig(tp=2), "cpu")      # no process group of 2 here
     with pytest.raises(Exception):
         build_trainer(_cfg(), ParallelConfig(zero_stage=3), "cpu")
+
+
+def test_pipeline_transport_is_a_checked_option():
+    from coeus_b200.foundation.error import ConfigError
+    assert ParallelConfig(pp=2).pp_transport == "auto"
+    ParallelConfig(pp=2, pp_transport="peer").validate()
+    with pytest.raises(ConfigError):
+        ParallelConfig(pp=2, pp_transport="smoke signals").validate()
