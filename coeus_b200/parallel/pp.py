@@ -8,15 +8,18 @@ point-to-point sends (NCCL on GPUs, Gloo on CPU ranks).  The forward and the bac
 use separate process groups, so a receive that was posted early never blocks a send of the other
 direction; sends are not waited for until their buffer is reused and, on CPU ranks, receives for
 the next micro-batch are posted before the current one is computed (on GPUs a receive is posted
-when it is needed, see ``_Channel``), which is what overlaps the transfers with the math.  The reference is a single process and has no pipeline (no send/recv anywhere in its
-sources); this is one of the parallelism strategies the larger training configurations need.
+when it is needed, see ``_Channel``), which is what overlaps the transfers with the math.  The
+reference is a single process and has no pipeline (no send/recv anywhere in its sources); this
+is one of the parallelism strategies the larger training configurations need.
 
 On GPUs there is a second transport, ``transport="peer"``: the sender pushes the tensor into a
 slot of the receiver's memory over NVLink (a copy kernel on the compute stream followed by a
-release store of a 64-bit epoch flag), the receiver's stream waits for the flag with a bounded
-spin of one warp and computes straight out of the slot.  Nothing is a rendezvous: a send never
-waits for the receiver to have posted anything, so any schedule that finishes with asynchronous
-sends finishes.  NCCL point-to-point is a rendezvous of two kernels, and a spinning NCCL kernel
+release store of the slot's 64-bit flag, the message's sequence number), the receiver's stream
+waits for the flag with a bounded spin of one warp and copies the tensor out of the slot (or,
+with a slot per message of a step, computes straight out of it).  The number of slots comes
+from the step's own order of sends and receipts (:func:`ring_depths`).  Nothing is a
+rendezvous: a send never waits for the receiver to have posted anything, so any schedule that
+finishes with asynchronous sends finishes.  NCCL point-to-point is a rendezvous of two kernels, and a spinning NCCL kernel
 can hold back the compute kernels queued behind it; :func:`nccl_order_deadlocks` is an event
 model of that, under which the interleaved schedule stops for ``micro_batches > stages`` (two
 ranks each spin in a send whose receive the other rank posts only after compute that the spin
