@@ -365,3 +365,77 @@ def test_pipeline_checkpoint_resumes_on_another_number_of_stages(tmp_path):
     res = {r[0]: r[1] for r in run_ranks(_worker_ckpt, 3, (ids, tgt, str(tmp_path), "load"),
                                          results=3)}
     assert abs(res[2] - want) < 1e-5
+
+
+def test_peer_ring_addresses_and_sequence_numbers(monkeypatch):
+    """The two ends of a peer-memory stream agree on where message n lives and what its flag
+    says: checked against a recording stand-in for the kernel library and the symmetric buffer
+    (no GPU): the sender's destination is the receiver's slot n mod depth, the flag raised is the
+    one waited for, its value is n + 1, and the regions of the four kinds of stream are disjoint."""
+    import ctypes
+    import coeus_b200.parallel.pp as pp
+    import coeus_b200.parallel.symm as symm
+    from coeus_b200.ops import _lib
+
+    bases = [0x10000000, 0x20000000]
+    calls = []
+
+    class FakeBuffer:
+        def __init__(self, nbytes, group, device):
+            self.nbytes, self.rank = nbytes, group
+            self.ptrs = list(bases)
+            self.local_ptr = bases[group]
+
+        def view(self, dtype, byte_offset=0, numel=None):
+            calls.append(("view", self.rank, byte_offset, numel))
+            return torch.zeros(numel, dtype=dtype)
+
+        def close(self):
+            pass
+
+    def val(x):
+        return x.value if hasattr(x, "value") else int(x)
+
+    class FakeLib:
+        def cb_peer_copy(self, src, dst, nbytes, blocks, stream):
+            calls.append(("copy", val(dst), val(nbytes)))
+            return 0
+
+        def cb_signal_peers(self, flags, slot, n, my_rank, value, stream):
+            assert (slot, n, my_rank) == (0, 1, 0)
+            calls.append(("signal", int(flags[0]), val(value)))
+            return 0
+
+        def cb_wait_flags(self, flag, slot, n, value, limit, status, stream):
+            assert (slot, n) == (0, 1)
+            calls.append(("wait", val(flag), val(value)))
+            return 0
+
+    monkeypatch.setattr(symm, "SymmetricBuffer", FakeBuffer)
+    monkeypatch.setattr(_lib, "lib", lambda: FakeLib())
+    monkeypatch.setattr(_lib, "stream_ptr", lambda: ctypes.c_void_p(0))
+    monkeypatch.setattr(_lib, "status_buffer", lambda device: None)
+    depths = {"f": 3, "b": 2, "fw": 2, "bw": 1}
+    shape, dtype = (6, 40), torch.bfloat16            # 480 bytes: a slot is padded to 512
+    send = pp.PeerRing(0, "cpu", shape, dtype, depths, copy_out=True)     # "group" = rank here
+    recv = pp.PeerRing(1, "cpu", shape, dtype, depths, copy_out=True)
+    assert send.slot_bytes == 512 and send.data_off == recv.data_off
+    regions = sorted((send.data_off[k], send.data_off[k] + depths[k] * 512) for k in depths)
+    assert all(a[1] <= b[0] for a, b in zip(regions, regions[1:]))
+    assert min(send.flag_off.values()) >= regions[-1][1]
+    t = torch.zeros(shape, dtype=dtype)
+    for n in range(7):
+        calls.clear()
+        send.push("f", 1, t)
+        got = recv.take("f")
+        assert got.shape == shape
+        copy, signal, wait, view = calls
+        slot = n % 3
+        assert copy == ("copy", bases[1] + send.data_off["f"] + slot * 512, 480)
+        assert signal == ("signal", bases[1] + send.flag_off["f"] + slot * 8, n + 1)
+        assert wait == ("wait", signal[1], n + 1)
+        assert view == ("view", 1, recv.data_off["f"] + slot * 512, 240)
+    # another kind of stream counts on its own and lives elsewhere
+    calls.clear()
+    send.push("bw", 1, t)
+    assert calls[0][1] == bases[1] + send.data_off["bw"] and calls[1][2] == 1
