@@ -391,6 +391,14 @@ class _Channel:
         self.pending.clear()
 
 
+def _new_group(ranks, members_only: bool):
+    """A process group over ``ranks``.  ``members_only``: only these ranks make the call (several
+    pipelines side by side create their groups independently of one another)."""
+    if members_only:
+        return dist.new_group(ranks, use_local_synchronization=True)
+    return dist.new_group(ranks)
+
+
 def _check_transport(transport: str, device) -> str:
     if transport not in ("nccl", "peer"):
         raise ProcessingError.invalid_input(f"unknown pipeline transport {transport!r}")
@@ -432,10 +440,15 @@ class PipelineStage:
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, train_cfg=None, schedule=None,
                  transport: str = "nccl", peer_wait_ms: float = 30000.0,
-                 peer_slots: str = "bounded") -> None:
+                 peer_slots: str = "bounded", dp_group=None) -> None:
+        """``dp_group``: the ranks that hold the same stage in other replicas of the pipeline;
+        their gradients are averaged before the optimizer step (every replica is fed its own
+        part of the batch)."""
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
         self.schedule = schedule          # object with at(step) -> learning rate
+        self.dp_group = dp_group
+        self.dp_size = dist.get_world_size(dp_group) if dp_group is not None else 1
         self.transport = _check_transport(transport, device)
         self._ring: Optional[PeerRing] = None
         self.peer_wait_ms = peer_wait_ms       # bound of one wait for a message, peer transport
@@ -455,9 +468,10 @@ class PipelineStage:
                          self.device)
         if self.stages > 1:
             ranks = dist.get_process_group_ranks(group)
-            # two groups: traffic of one direction never queues behind the other
-            self.fwd_group = dist.new_group(ranks)
-            self.bwd_group = dist.new_group(ranks)
+            # two groups: traffic of one direction never queues behind the other (with replicas
+            # only the members of this pipeline make the call)
+            self.fwd_group = _new_group(ranks, dp_group is not None)
+            self.bwd_group = _new_group(ranks, dp_group is not None)
             self._ranks = ranks
             # global gradient norm: every stage holds its own tensors
             self.opt.norm_hook = lambda g32, sumsq: dist.all_reduce(sumsq, group=self.group)
@@ -535,7 +549,8 @@ class PipelineStage:
                 x = m.forward_blocks(x, b, S, save)
                 if self.last:
                     xf = m.forward_final_norm(x, save)
-                    loss = m.loss_from_hidden(xf, targets[i], save, grad_scale=1.0 / (T * M))
+                    loss = m.loss_from_hidden(xf, targets[i], save,
+                                              grad_scale=1.0 / (T * M * self.dp_size))
                     loss_sum += loss / M
                 else:
                     chans["sf"].send(x)
@@ -554,6 +569,8 @@ class PipelineStage:
         for c in chans.values():
             c.drain()
         m._ws_tag = ""
+        if self.dp_group is not None:      # the loss scale already holds 1 / replicas
+            dist.all_reduce(m.g32, group=self.dp_group)
         if self.schedule is not None:
             self.opt.set_learning_rate(self.schedule.at(self.step_index))
         self.opt.step(m.p32, m.g32, m.p16, 1.0)
@@ -575,10 +592,14 @@ class InterleavedPipelineStage:
     def __init__(self, cfg: DecoderConfig, group, device, micro_batches: int, chunks: int = 2,
                  seed: int = 0, dtype: torch.dtype = torch.bfloat16, train_cfg=None,
                  schedule=None, transport: Optional[str] = None,
-                 peer_wait_ms: float = 30000.0, peer_slots: str = "bounded") -> None:
+                 peer_wait_ms: float = 30000.0, peer_slots: str = "bounded",
+                 dp_group=None) -> None:
+        """``dp_group``: as for :class:`PipelineStage`."""
         from ..optim.adamw import AdamW
         from ..train.trainer import TrainConfig
         self.schedule = schedule
+        self.dp_group = dp_group
+        self.dp_size = dist.get_world_size(dp_group) if dp_group is not None else 1
         self.group = group
         self.stage = dist.get_rank(group)
         self.stages = dist.get_world_size(group)
@@ -612,7 +633,7 @@ class InterleavedPipelineStage:
                                    self.device))
         ranks = dist.get_process_group_ranks(group)
         self._ranks = ranks
-        self._groups = {k: dist.new_group(ranks) for k in ("f", "fw", "b", "bw")}
+        self._groups = {k: _new_group(ranks, dp_group is not None) for k in ("f", "fw", "b", "bw")}
         self.steps = schedule_interleaved(self.stage, P, micro_batches, chunks)
         # workspace slots: micro-batches of one chunk that are alive together never share one
         self._slot: Dict[Tuple[int, int], int] = {}
@@ -715,7 +736,8 @@ class InterleavedPipelineStage:
                 x = m.forward_blocks(x, b, S, save)
                 if k == V - 1:
                     xf = m.forward_final_norm(x, save)
-                    loss = m.loss_from_hidden(xf, targets[i], save, grad_scale=1.0 / (T * M))
+                    loss = m.loss_from_hidden(xf, targets[i], save,
+                                              grad_scale=1.0 / (T * M * self.dp_size))
                     loss_sum += loss / M
                 else:
                     ch["sf" if s < P - 1 else "sfw"].send(x)
@@ -734,6 +756,9 @@ class InterleavedPipelineStage:
                     ch["sb" if s > 0 else "sbw"].send(dx)
         for c_ in ch.values():
             c_.drain()
+        if self.dp_group is not None:      # the loss scale already holds 1 / replicas
+            for m in self.models:
+                dist.all_reduce(m.g32, group=self.dp_group)
         if self.train_cfg.grad_clip is not None:
             # one norm over all chunks of all ranks, handed to every chunk's optimizer
             total = torch.zeros(1, dtype=torch.float32, device=self.device)

@@ -55,6 +55,9 @@ def build_trainer(cfg: DecoderConfig, parallel: ParallelConfig, device,
     if active == ["dp", "tp"]:
         return _build_dp_tp(cfg, parallel, device, train_cfg or TrainConfig(), group, world, rank,
                             seed, dtype, recompute, schedule)
+    if active == ["dp", "pp"]:
+        return _build_dp_pp(cfg, parallel, device, train_cfg or TrainConfig(), group, world, rank,
+                            seed, dtype, schedule, micro_batches)
     if len(active) > 1:
         raise ConfigError.conflict(active[0], active[1],
                                    "one parallelism strategy spans the process group at a time")
@@ -185,3 +188,47 @@ def _build_dp_tp(cfg, parallel, device, tc, group, world, rank, seed, dtype, rec
         sl = slice(d_idx * per, (d_idx + 1) * per)
         return tr.train_step(ids[sl].contiguous(), targets[sl].contiguous())
     return ParallelRun("dp+tp", tr, model, rank, world, feed)
+
+
+def _build_dp_pp(cfg, parallel, device, tc, group, world, rank, seed, dtype, schedule,
+                 micro_batches):
+    """Replicas of a pipeline: ``pp`` consecutive ranks form a pipeline, ranks that hold the same
+    stage in different replicas average their gradients.  Every replica is fed its own part of
+    the batch, cut into ``micro_batches`` micro-batches."""
+    from ..parallel.pp import InterleavedPipelineStage, PipelineStage
+    dp, pp = parallel.dp, parallel.pp
+    if tc.grad_accum > 1:
+        raise ConfigError.invalid("grad_accum", tc.grad_accum,
+                                  "A pipeline accumulates over its micro_batches")
+    if dp * pp != world:
+        raise ConfigError.invalid("dp*pp", dp * pp, f"must equal the size of the process group ({world})")
+    ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+    d_idx, p_idx = rank // pp, rank % pp
+    pp_group = dp_group = None
+    # every rank creates every group, in the same order
+    for d in range(dp):
+        g = dist.new_group([ranks[d * pp + p] for p in range(pp)])
+        if d == d_idx:
+            pp_group = g
+    for p in range(pp):
+        g = dist.new_group([ranks[d * pp + p] for d in range(dp)])
+        if p == p_idx:
+            dp_group = g
+    transport = None if parallel.pp_transport == "auto" else parallel.pp_transport
+    if parallel.pp_chunks > 1:
+        st = InterleavedPipelineStage(cfg, pp_group, device, micro_batches,
+                                      chunks=parallel.pp_chunks, seed=seed, dtype=dtype,
+                                      train_cfg=tc, schedule=schedule, transport=transport,
+                                      dp_group=dp_group)
+    else:
+        st = PipelineStage(cfg, pp_group, device, micro_batches, seed=seed, dtype=dtype,
+                           train_cfg=tc, schedule=schedule, transport=transport or "nccl",
+                           dp_group=dp_group)
+
+    def feed(ids, targets):
+        per = ids.shape[0] // dp
+        sl = slice(d_idx * per, (d_idx + 1) * per)
+        M = micro_batches
+        b = per // M
+        return st.train_step(ids[sl].reshape(M, b, -1), targets[sl].reshape(M, b, -1))
+    return ParallelRun("dp+pp", st, getattr(st, "model", None) or st.models[0], rank, world, feed)

@@ -129,6 +129,36 @@ def test_data_parallel_replicas_of_a_tensor_parallel_model():
         assert abs(got[0] - ref[0]) < 1e-4 and abs(got[-1] - ref[-1]) < 5e-3, (got, ref)
 
 
+def _worker_dp_pp(rank, world, port, chunks, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    run = build_trainer(_cfg(layers=4), ParallelConfig(dp=2, pp=2, pp_chunks=chunks), "cpu",
+                        _tc(0.02 if chunks == 1 else None), micro_batches=2, seed=3,
+                        dtype=torch.float32)
+    ids, tgt = _batch()
+    t = torch.tensor([float(run.step(ids, tgt)) for _ in range(4)])
+    dist.all_reduce(t)               # the last stage of each replica reports its replica's loss
+    out.put((rank, run.strategy, (t / 2).tolist()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("chunks", [1, 2])
+def test_data_parallel_replicas_of_a_pipeline(chunks):
+    """Two pipelines of two stages side by side (plain with gradient clipping by the global
+    norm, and interleaved): the same losses as one rank on the whole batch."""
+    from mp_util import run_ranks
+    ids, tgt = _batch()
+    single = build_trainer(_cfg(layers=4), ParallelConfig(), "cpu",
+                           _tc(0.02 if chunks == 1 else None), seed=3, dtype=torch.float32)
+    ref = [float(single.step(ids, tgt)) for _ in range(4)]
+    res = run_ranks(_worker_dp_pp, 4, (chunks,), results=4)
+    for _, strategy, got in res:
+        assert strategy == "dp+pp"
+        assert abs(got[0] - ref[0]) < 1e-4 and abs(got[-1] - ref[-1]) < 5e-3, (got, ref)
+
+
 def test_launcher_rejects_products_and_wrong_sizes():
     with pytest.raises(Exception):
         build_trainer(_cfg(), ParallelConfig(pp=2, tp=2), "cpu")
