@@ -399,6 +399,17 @@ def _new_group(ranks, members_only: bool):
     return dist.new_group(ranks)
 
 
+def _other_replica_saves(dp_group) -> bool:
+    """With replicas of the pipeline the first one writes the checkpoint (all hold the same
+    state); the others wait until it is written."""
+    if dp_group is None:
+        return False
+    first = dist.get_rank(dp_group) == 0
+    if not first:
+        dist.barrier(group=dp_group)
+    return not first
+
+
 def _check_transport(transport: str, device) -> str:
     if transport not in ("nccl", "peer"):
         raise ProcessingError.invalid_input(f"unknown pipeline transport {transport!r}")
@@ -487,10 +498,14 @@ class PipelineStage:
         """Name-keyed training checkpoint (weights and Adam moments of this stage's tensors);
         loads into any number of stages."""
         from ..checkpoint.named import model_state, save_named
+        if _other_replica_saves(self.dp_group):
+            return
         barrier = (lambda: dist.barrier(group=self.group)) if self.stages > 1 else None
         save_named(directory, self.stage, model_state(self.model, self.opt),
                    {"stages": self.stages, "opt_step": self.opt.step_count,
                     "train_step": self.step_index, "config": self.cfg.to_dict()}, barrier)
+        if self.dp_group is not None:
+            dist.barrier(group=self.dp_group)
 
     def load_checkpoint(self, directory: str) -> dict:
         from ..checkpoint.named import load_named, model_state
@@ -669,10 +684,14 @@ class InterleavedPipelineStage:
     def save_checkpoint(self, directory: str) -> None:
         """Name-keyed checkpoint of all chunks of this rank; loads into any pipeline shape."""
         from ..checkpoint.named import save_named
+        if _other_replica_saves(self.dp_group):
+            return
         save_named(directory, self.stage, self._state(),
                    {"stages": self.stages, "chunks": self.v, "opt_step": self.opts[0].step_count,
                     "train_step": self.step_index, "config": self.cfg.to_dict()},
                    lambda: dist.barrier(group=self.group))
+        if self.dp_group is not None:
+            dist.barrier(group=self.dp_group)
 
     def load_checkpoint(self, directory: str) -> dict:
         from ..checkpoint.named import load_named

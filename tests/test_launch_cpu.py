@@ -137,7 +137,20 @@ def _worker_dp_pp(rank, world, port, chunks, out):
                         _tc(0.02 if chunks == 1 else None), micro_batches=2, seed=3,
                         dtype=torch.float32)
     ids, tgt = _batch()
-    t = torch.tensor([float(run.step(ids, tgt)) for _ in range(4)])
+    losses = [float(run.step(ids, tgt)) for _ in range(3)]
+    # a checkpoint written by the first replica, loaded by both: the next step is the same
+    import tempfile
+    box = [tempfile.mkdtemp() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    run.trainer.save_checkpoint(box[0])
+    dist.barrier()
+    assert sorted(f for f in os.listdir(box[0]) if f.startswith("part")) == \
+        ["part0.safetensors", "part1.safetensors"]
+    nxt = float(run.step(ids, tgt))
+    run.trainer.load_checkpoint(box[0])
+    again = float(run.step(ids, tgt))
+    assert abs(again - nxt) < 1e-6
+    t = torch.tensor(losses + [nxt])
     dist.all_reduce(t)               # the last stage of each replica reports its replica's loss
     out.put((rank, run.strategy, (t / 2).tolist()))
     dist.barrier()
