@@ -3,10 +3,12 @@
 // statistics over the whole [S*H] buffer it is handed; these kernels implement the standard
 // per-token operator, which coincides with the reference at S = 1.
 //
-// One row is handled by WPR warps of a 128-thread block (WPR = 1 for H <= 2048, 4 up to 8192);
-// a row lives in registers between the statistics pass and the normalisation pass, so x is
-// read from HBM once.  Backward accumulates dgamma/dbeta per thread over a grid-stride loop of
-// rows and finishes with one fp32 atomic add per column per block.
+// Two families of kernels.  Rows of up to 2048 columns go through the row-pipelined kernels in
+// the second half of this file (per-warp rings of row buffers in shared memory filled by bulk
+// copies).  Wider rows use the kernels below: one row is handled by WPR warps of a 128-thread
+// block (WPR = 4 up to 8192 columns) and lives in registers between the statistics pass and the
+// normalisation pass, so x is read from HBM once; backward accumulates dgamma/dbeta per thread
+// over a grid-stride loop of rows and finishes with one fp32 atomic add per column per block.
 #include "common.cuh"
 #include "ptx.cuh"
 
