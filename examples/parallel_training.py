@@ -5,7 +5,8 @@
         examples/parallel_training.py --strategy tp                        # 2 ranks (CPU: Gloo)
 
 ``--strategy`` is one of dp, dp0 (replicated optimizer state), tp, pp, pp_interleaved, ep, cp,
-ulysses; the group size comes from the launcher.  Every rank is handed the same global batch and
+ulysses, dp_tp and dp_pp (replicas of a two-rank tensor-parallel model / pipeline, four ranks or
+more); the group size comes from the launcher.  Every rank is handed the same global batch and
 ``ParallelRun.step`` gives it the part its strategy needs.  The reference has no parallel training
 (its training example is a toy regression, examples/training_example.rs)."""
 from __future__ import annotations
@@ -51,7 +52,9 @@ def main(argv=None) -> dict:
            "tp": ParallelConfig(tp=world), "pp": ParallelConfig(pp=world),
            "pp_interleaved": ParallelConfig(pp=world, pp_chunks=2),
            "ep": ParallelConfig(dp=world, ep=world), "cp": ParallelConfig(cp=world),
-           "ulysses": ParallelConfig(cp=world, ulysses=True)}[a.strategy] if world > 1 \
+           "ulysses": ParallelConfig(cp=world, ulysses=True),
+           "dp_tp": ParallelConfig(dp=world // 2, tp=2),        # four ranks or more
+           "dp_pp": ParallelConfig(dp=world // 2, pp=2)}[a.strategy] if world > 1 \
         else ParallelConfig()
     run = build_trainer(cfg, par, device, TrainConfig(learning_rate=3e-3, grad_clip=1.0),
                         micro_batches=2, dtype=torch.bfloat16 if device.startswith("cuda")
