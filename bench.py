@@ -66,7 +66,7 @@ class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs
     (read-only queries)."""
 
-    def __init__(self, index: int, period: float = 0.2) -> None:
+    def __init__(self, index: int, period: float = 0.05) -> None:
         super().__init__(daemon=True)
         self.index, self.period = index, period
         self.samples, self.reasons = [], set()
