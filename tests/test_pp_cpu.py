@@ -266,6 +266,16 @@ def _worker_interleaved(rank, world, port, ids, tgt, out):
     assert other.load_checkpoint(tmp)["train_step"] == 2
     for a_, b_ in zip(st.models, other.models):
         assert torch.equal(a_.p32, b_.p32)
+    # on GPUs the NCCL transport is refused where its launch order can stop (no device is touched
+    # before that check), and a CPU rank cannot ask for the peer-memory transport
+    from coeus_b200.foundation.error import ProcessingError
+    assert ids.shape[0] > world
+    with pytest.raises(ProcessingError):
+        InterleavedPipelineStage(cfg, dist.group.WORLD, "cuda", micro_batches=ids.shape[0],
+                                 chunks=2, transport="nccl")
+    with pytest.raises(ProcessingError):
+        InterleavedPipelineStage(cfg, dist.group.WORLD, "cpu", micro_batches=ids.shape[0],
+                                 chunks=2, transport="peer")
     params = {}
     for m in st.models:
         params.update({k: v.numpy().copy() for k, v in m.master.items()})
